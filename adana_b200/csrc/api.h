@@ -1,0 +1,94 @@
+// C ABI of libadana_b200.so.  Every entry point takes raw device pointers and the CUDA
+// stream (as void*) to launch on, returns 0 on success (a negative value for a rejected
+// argument, a positive cudaError_t for a failed launch) and never allocates device memory
+// unless its comment says so.  Python binds these with ctypes (adana_b200/ops/_lib.py).
+#pragma once
+#include <stdint.h>
+
+// GEMM epilogues
+enum {
+  EPI_BF16 = 0,       // C(bf16) = alpha * acc
+  EPI_GELU_DUAL = 1,  // C(bf16) = acc (pre-activation), C2(bf16) = gelu(acc)
+  EPI_RESID_F32 = 2,  // C(f32)  = R(f32) + alpha * acc
+  EPI_DGELU = 3,      // C(bf16) = acc * gelu'(R(bf16))
+  EPI_F32 = 4,        // C(f32)  = beta * C + alpha * acc
+  EPI_SWIGLU = 5,     // B = [gate; up] rows; C(bf16)=[gate|up] pre-activations, C2 = silu(g)*u
+  EPI_DSWIGLU = 6,    // acc = dH; R = [gate|up]; C = [dGate|dUp]
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
+// a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
+int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                    long long ldb, long long ldc, int a_mn, int b_mn, int epi, void* C2,
+                    long long ldc2, const void* R, long long ldr, float alpha, float beta,
+                    int b_off2, int* status, void* stream);
+
+// ---- normalisation (norm.cu) -------------------------------------------------------------
+// y(bf16|f32) = norm(x(f32|bf16)) * w ; kind 0 = LayerNorm (mean-subtracting, weight only),
+// kind 1 = RMSNorm.  Saves mean/rstd (fp32, one per row) for backward.
+int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void* y, int y_is_bf16,
+                   float* mean, float* rstd, int rows, int cols, float eps, int kind,
+                   void* stream);
+// dx(f32) (+)= d norm / dx ; dw_partial[blocks, cols] fp32 partial sums reduced by
+// adana_colsum_f32.  accumulate_dx: dx += result (residual-stream gradient accumulation).
+int adana_norm_bwd(const void* dy, int dy_is_bf16, const void* x, int x_is_bf16, const float* w,
+                   const float* mean, const float* rstd, float* dx, int accumulate_dx,
+                   float* dw_partial, int n_partial_rows, int rows, int cols, int kind,
+                   void* stream);
+int adana_colsum_f32(const float* partial, int n_partial_rows, int cols, float* out,
+                     int accumulate, void* stream);
+
+// ---- per-head QK-norm + rotary embedding (rope.cu) --------------------------------------------
+int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int q_off, int k_off,
+                          const float* wq, const float* wk, const float* freqs, void* q_out,
+                          void* k_out, float* stats, int B, int S, int Hq, int Hk, int hd,
+                          float eps, int kind, void* stream);
+int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, long long row_stride,
+                          int q_off, int k_off, const float* wq, const float* wk,
+                          const float* freqs, const float* stats, void* dqkv, float* dwq_partial,
+                          float* dwk_partial, int n_partial, int B, int S, int Hq, int Hk, int hd,
+                          int kind, void* stream);
+
+// ---- embedding (embedding.cu) ----------------------------------------------------------------
+int adana_embedding_fwd(const long long* idx, const void* table, int table_is_bf16, float* out,
+                        int n_tokens, int dim, int vocab, void* stream);
+int adana_embedding_bwd(const long long* idx, const float* dout, float* dtable, int n_tokens,
+                        int dim, int vocab, void* stream);
+
+// ---- cross entropy over a chunk of fp32 logits (ce.cu) -----------------------------------------
+int adana_ce_fwd_bwd(float* logits, long long ld, const long long* targets, int rows, int vocab,
+                     float z_coeff, float grad_scale, void* dlogits_bf16, long long ldd,
+                     float* sums /*[4]: ce, lse^2, correct, valid*/, float* lse_out,
+                     void* stream);
+
+// ---- optimizer (optim.cu) ----------------------------------------------------------------------
+struct AdanaOptHyper {
+  float lr;            // scheduled learning rate of the group (g2 = g3 = lr)
+  float alpha;         // delta / (delta + t)
+  float step;          // t (1-based)
+  float one_minus_kappa;
+  float clipsnr;       // < 0: no clipping
+  float eps;
+  float gamma3;        // gamma_3_factor
+  float wd_factor;     // 1 - wd * sched / (1 + t / wd_ts)   (already folded on the host)
+  float grad_scale;    // multiplies the raw gradient (1/acc_steps, 1/world); the clip
+                       // coefficient is read from clip_coef_ptr on the device
+  int kind;            // 0 = adana/dana-mk4, 1 = dana-star(-mk4), 2 = adamw (bias-corrected)
+  float beta1, beta2, bc1, bc2;  // adamw only
+};
+int adana_opt_step(float* p, const float* g, float* m, float* v, float* tau, void* p_bf16,
+                   long long n, const struct AdanaOptHyper* h, const float* clip_coef_ptr,
+                   float* diag /*[4] or null*/, void* stream);
+int adana_sumsq_f32(const float* x, long long n, float* out /*accumulates*/, void* stream);
+
+// ---- utility -------------------------------------------------------------------------------------
+int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+int adana_version(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,475 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a:  TMA -> shared memory (128B swizzle)
+// -> tcgen05.mma with fp32 accumulators in tensor memory -> fused epilogues.
+//
+//   D[M,N] = epilogue( A[M,K] * B[N,K]^T )
+//
+// Operand layouts ("major" = which index is contiguous in global memory):
+//   A K-major : memory [M rows][K contiguous]      (activations in a forward pass)
+//   A MN-major: memory [K rows][M contiguous]      (dY^T in a weight-gradient GEMM)
+//   B K-major : memory [N rows][K contiguous]      (nn.Linear weight [out,in] in forward)
+//   B MN-major: memory [K rows][N contiguous]      (weight in dgrad, activations in wgrad)
+// so forward, dgrad and wgrad all read the tensors as they are stored; nothing is transposed
+// in memory.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns tensor memory and issues the MMAs,
+// warps 2..5 run the epilogue (each warp reads its own 32-lane quarter of tensor memory).
+// Two 256-column accumulators are double-buffered so that the epilogue of tile i overlaps
+// the main loop of tile i+1.  Every wait is bounded (see common.cuh).
+//
+// Replaces the cuBLASLt calls behind nn.Linear in the reference model code
+// (src/models/enoki.py:111,150,176-178; src/models/qwen3.py:104-106,173-175,235).
+#include "api.h"
+#include "common.cuh"
+
+namespace adana {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int CHUNK_BYTES = BK * 128;  // one 64-wide MN-major chunk: BK rows of 128 B
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct GemmArgs {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  void* C2;
+  long long ldc2;
+  const void* R;
+  long long ldr;
+  float alpha, beta;
+  int b_off2;  // gated-MLP epilogues: offset (rows of B / columns of C,R) of the "up" half
+  int tiles_m, tiles_n, group_m;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& mi,
+                                            int& ni) {
+  const int per_group = group_m * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * group_m;
+  const int gm = min(group_m, tiles_m - first_m);
+  const int r = t - g * per_group;
+  mi = first_m + (r % gm);
+  ni = r / gm;
+}
+
+template <int EPI>
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float (&v)[32], int ncols_ok) {
+  // dst is 16-byte aligned (column offsets are multiples of 32, ld multiples of 8)
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j * 8 < ncols_ok) {
+      uint4 q;
+      q.x = pack_bf16x2(v[j * 8 + 0], v[j * 8 + 1]);
+      q.y = pack_bf16x2(v[j * 8 + 2], v[j * 8 + 3]);
+      q.z = pack_bf16x2(v[j * 8 + 4], v[j * 8 + 5]);
+      q.w = pack_bf16x2(v[j * 8 + 6], v[j * 8 + 7]);
+      *reinterpret_cast<uint4*>(dst + j * 8) = q;
+    }
+  }
+}
+
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&v)[32], int ncols_ok) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (j * 8 < ncols_ok) {
+      uint4 q = *reinterpret_cast<const uint4*>(src + j * 8);
+      float2 a = unpack_bf16x2(q.x), b = unpack_bf16x2(q.y), c = unpack_bf16x2(q.z),
+             d = unpack_bf16x2(q.w);
+      v[j * 8 + 0] = a.x; v[j * 8 + 1] = a.y; v[j * 8 + 2] = b.x; v[j * 8 + 3] = b.y;
+      v[j * 8 + 4] = c.x; v[j * 8 + 5] = c.y; v[j * 8 + 6] = d.x; v[j * 8 + 7] = d.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[j * 8 + i] = 0.f;
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr bool GATED_FWD = (EPI == EPI_SWIGLU);
+  constexpr int TILE_N = GATED_FWD ? BN / 2 : BN;  // output columns covered by one tile
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 4);
+    mbar_init(&tempty_bar[1], 4);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int mi, ni;
+        tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        const int m0 = mi * BM;
+        const int n0 = ni * TILE_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status,
+                         ST_TIMEOUT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], k0, m0);  // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sA + c * CHUNK_BYTES, &tmA, &full_bar[stage], m0 + c * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            const int n1 = GATED_FWD ? (args.b_off2 + n0) : (n0 + 128);
+            tma_load_2d(sB, &tmB, &full_bar[stage], k0, n0);  // box {64 k, 128 n}
+            tma_load_2d(sB + 128 * 128, &tmB, &full_bar[stage], k0, n1);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * CHUNK_BYTES, &tmB, &full_bar[stage], n0 + c * 64, k0);
+          }
+          ++issued;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Aborting: let the copies that are still in flight land before the CTA exits.
+        const int pending = issued < STAGES ? (int)issued : STAGES;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) {
+            s = STAGES - 1;
+            ph ^= 1;
+          }
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full_bar[s], ph) && globaltimer_ns() - t0 < 20000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t use = (uint32_t)(it >> 1);
+        if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status,
+                       ST_TIMEOUT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, args.status,
+                         ST_TIMEOUT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+            else
+              da = make_smem_desc_sw128(sA + kk * 2048, CHUNK_BYTES, 1024);
+            if constexpr (!B_MN)
+              db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+            else
+              db = make_smem_desc_sw128(sB + kk * 2048, CHUNK_BYTES, 1024);
+            umma_ss(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) --------------------------------
+    const int quad = warp & 3;  // tensor-memory lane quarter this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      int mi, ni;
+      tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      const int buf = it & 1;
+      const uint32_t use = (uint32_t)(it >> 1);
+      if (!mbar_wait(&tfull_bar[buf], use & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = mi * BM + quad * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
+      const int n0 = ni * TILE_N;
+
+      if constexpr (EPI == EPI_SWIGLU) {
+        // accumulator columns [0,128) = gate, [128,256) = up
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, rg);
+          tmem_ld_32x32b_x32(taddr + 128 + c * 32, ru);
+          tmem_wait_ld();
+          const int col = n0 + c * 32;
+          const int ncols_ok = args.N - col;
+          if (row_ok && ncols_ok > 0) {
+            float g[32], u[32], h[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              g[i] = __uint_as_float(rg[i]);
+              u[i] = __uint_as_float(ru[i]);
+              h[i] = g[i] * sigmoidf_(g[i]) * u[i];
+            }
+            __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
+            store_bf16x32<EPI>(gu + col, g, ncols_ok);
+            store_bf16x32<EPI>(gu + args.b_off2 + col, u, ncols_ok);
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
+                               h, ncols_ok);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_wait_ld();
+          const int col = n0 + c * 32;
+          const int ncols_ok = args.N - col;
+          if (!row_ok || ncols_ok <= 0) continue;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
+
+          if constexpr (EPI == EPI_BF16) {
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                               ncols_ok);
+          } else if constexpr (EPI == EPI_GELU_DUAL) {
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                               ncols_ok);
+            float h[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) h[i] = gelu_erf(v[i]);
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
+                               h, ncols_ok);
+          } else if constexpr (EPI == EPI_RESID_F32) {
+            const float* rp = reinterpret_cast<const float*>(args.R) + (long long)row * args.ldr + col;
+            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j * 4 < ncols_ok) {
+                float4 x = *reinterpret_cast<const float4*>(rp + j * 4);
+                x.x += v[j * 4 + 0];
+                x.y += v[j * 4 + 1];
+                x.z += v[j * 4 + 2];
+                x.w += v[j * 4 + 3];
+                *reinterpret_cast<float4*>(cp + j * 4) = x;
+              }
+            }
+          } else if constexpr (EPI == EPI_DGELU) {
+            float z[32];
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
+                         ncols_ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(z[i]);
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                               ncols_ok);
+          } else if constexpr (EPI == EPI_F32) {
+            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j * 4 < ncols_ok) {
+                float4 x = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+                if (args.beta != 0.f) {
+                  float4 o = *reinterpret_cast<const float4*>(cp + j * 4);
+                  x.x += args.beta * o.x;
+                  x.y += args.beta * o.y;
+                  x.z += args.beta * o.z;
+                  x.w += args.beta * o.w;
+                }
+                *reinterpret_cast<float4*>(cp + j * 4) = x;
+              }
+            }
+          } else if constexpr (EPI == EPI_DSWIGLU) {
+            // v = dH chunk; R holds [gate | up] pre-activations, C receives [dGate | dUp]
+            const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr;
+            float g[32], u[32];
+            load_bf16x32(gu + col, g, ncols_ok);
+            load_bf16x32(gu + args.b_off2 + col, u, ncols_ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float s = sigmoidf_(g[i]);
+              const float dh = v[i];
+              const float dgate = dh * u[i] * s * (1.f + g[i] * (1.f - s));
+              const float dup = dh * g[i] * s;
+              g[i] = dgate;
+              u[i] = dup;
+            }
+            __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
+            store_bf16x32<EPI>(dgu + col, g, ncols_ok);
+            store_bf16x32<EPI>(dgu + args.b_off2 + col, u, ncols_ok);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
+                       int sm_count, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = args.tiles_m * args.tiles_n;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(tmA, tmB, args);
+  return (int)cudaGetLastError();
+}
+
+static int g_sm_count = 0;
+
+}  // namespace adana
+
+using namespace adana;
+
+extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                               int epi, void* C2, long long ldc2, const void* R, long long ldr,
+                               float alpha, float beta, int b_off2, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) != 0 || (ldc % 4) != 0) return -100;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = encode_tmap_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, BM, 2);
+  else
+    rc = encode_tmap_2d(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK, 2);
+  if (rc) return -101;
+  const bool gated_fwd = (epi == EPI_SWIGLU);
+  // B holds N rows (K-major) or N columns (MN-major); the gated forward reads 2*N of them.
+  const uint64_t b_extent = gated_fwd ? (uint64_t)(b_off2 + N) : (uint64_t)N;
+  if (!b_mn)
+    rc = encode_tmap_2d(&tmB, B, (uint64_t)K, b_extent, (uint64_t)ldb, 64, 128, 2);
+  else
+    rc = encode_tmap_2d(&tmB, B, b_extent, (uint64_t)K, (uint64_t)ldb, 64, BK, 2);
+  if (rc) return -102;
+
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K;
+  args.C = C; args.ldc = ldc; args.C2 = C2; args.ldc2 = ldc2; args.R = R; args.ldr = ldr;
+  args.alpha = alpha; args.beta = beta; args.b_off2 = b_off2;
+  args.tiles_m = (M + BM - 1) / BM;
+  const int tile_n = gated_fwd ? BN / 2 : BN;
+  args.tiles_n = (N + tile_n - 1) / tile_n;
+  args.group_m = 16;
+  args.status = status;
+
+#define ADANA_GEMM_CASE(AM, BMN, E)                                                     \
+  if (a_mn == (AM ? 1 : 0) && b_mn == (BMN ? 1 : 0) && epi == E)                        \
+    return launch_gemm<AM, BMN, E>(tmA, tmB, args, g_sm_count, stream);
+  // forward (activations x weight^T)
+  ADANA_GEMM_CASE(false, false, EPI_BF16)
+  ADANA_GEMM_CASE(false, false, EPI_GELU_DUAL)
+  ADANA_GEMM_CASE(false, false, EPI_RESID_F32)
+  ADANA_GEMM_CASE(false, false, EPI_F32)
+  ADANA_GEMM_CASE(false, false, EPI_SWIGLU)
+  // dgrad (dY x weight)
+  ADANA_GEMM_CASE(false, true, EPI_BF16)
+  ADANA_GEMM_CASE(false, true, EPI_DGELU)
+  ADANA_GEMM_CASE(false, true, EPI_DSWIGLU)
+  ADANA_GEMM_CASE(false, true, EPI_F32)
+  ADANA_GEMM_CASE(false, true, EPI_RESID_F32)
+  // wgrad (dY^T x X)
+  ADANA_GEMM_CASE(true, true, EPI_F32)
+  ADANA_GEMM_CASE(true, true, EPI_BF16)
+  // generic extras
+  ADANA_GEMM_CASE(true, false, EPI_BF16)
+  ADANA_GEMM_CASE(true, false, EPI_F32)
+#undef ADANA_GEMM_CASE
+  return -103;
+}

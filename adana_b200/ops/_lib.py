@@ -1,0 +1,140 @@
+"""ctypes binding of the in-tree sm_100a kernel library (`adana_b200/lib/libadana_b200.so`).
+
+The library exposes a plain C ABI (see `csrc/api.h`): raw device pointers plus the CUDA
+stream.  Keeping torch headers out of the kernels makes a full rebuild take seconds.
+
+On a machine with a GPU the library is required: `lib()` raises if it cannot be loaded,
+so that no op silently falls back to a PyTorch implementation.  On a CPU-only machine
+`available()` is False and the ops use their PyTorch reference paths.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libadana_b200.so"
+_lib = None
+_status = {}
+
+STATUS_NAMES = {
+    0: "ok",
+    1: "timeout: TMA producer waited for a free shared-memory stage",
+    2: "timeout: MMA issuer waited for TMA data",
+    3: "timeout: epilogue waited for an accumulator",
+    4: "timeout: MMA issuer waited for the epilogue",
+    5: "timeout: wait on a peer flag",
+    6: "bad argument seen on the device",
+    7: "timeout inside the attention kernel",
+}
+
+
+class AdanaOptHyper(Structure):
+    _fields_ = [
+        ("lr", c_float), ("alpha", c_float), ("step", c_float), ("one_minus_kappa", c_float),
+        ("clipsnr", c_float), ("eps", c_float), ("gamma3", c_float), ("wd_factor", c_float),
+        ("grad_scale", c_float), ("kind", c_int),
+        ("beta1", c_float), ("beta2", c_float), ("bc1", c_float), ("bc2", c_float),
+    ]
+
+
+def _declare(lib):
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "adana_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, P, L, P, L, F, F, I, P, P],
+        "adana_norm_fwd": [P, I, P, P, I, P, P, I, I, F, I, P],
+        "adana_norm_bwd": [P, I, P, I, P, P, P, P, I, P, I, I, I, I, P],
+        "adana_colsum_f32": [P, I, I, P, I, P],
+        "adana_qknorm_rope_fwd": [P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
+        "adana_qknorm_rope_bwd": [P, P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+        "adana_embedding_fwd": [P, P, I, P, I, I, I, P],
+        "adana_embedding_bwd": [P, P, P, I, I, I, P],
+        "adana_ce_fwd_bwd": [P, L, P, I, I, F, F, P, L, P, P, P],
+        "adana_opt_step": [P, P, P, P, P, P, L, POINTER(AdanaOptHyper), P, P, P],
+        "adana_sumsq_f32": [P, L, P, P],
+        "adana_cast_f32_to_bf16": [P, P, L, P],
+        "adana_version": [],
+    }
+    for name, args in sigs.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+    return lib
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    """True when CUDA kernels can run: a GPU is visible and the library loads."""
+    if not torch.cuda.is_available():
+        return False
+    return lib() is not None
+
+
+def lib():
+    """Load (building first if the .so is missing and nvcc exists) and return the library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        try:
+            from adana_b200 import build as _build
+
+            _build.build()
+        except Exception as e:  # pragma: no cover - depends on toolchain
+            if torch.cuda.is_available():
+                raise RuntimeError(
+                    f"adana_b200: kernel library missing and could not be built: {e}"
+                ) from e
+            return None
+    try:
+        _lib = _declare(ctypes.CDLL(str(_LIB_PATH)))
+    except OSError as e:
+        if torch.cuda.is_available():
+            raise RuntimeError(f"adana_b200: cannot load {_LIB_PATH}: {e}") from e
+        return None
+    return _lib
+
+
+def has(name: str) -> bool:
+    l = lib()
+    return l is not None and hasattr(l, name)
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_buffer(device=None) -> torch.Tensor:
+    """One int32 status word per device; kernels write a code there when a wait times out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=dev)
+        _status[key] = buf
+    return buf
+
+
+def check_status(device=None) -> None:
+    """Synchronising check of the device status word; raises on a recorded timeout."""
+    buf = status_buffer(device)
+    code = int(buf[0].item())
+    if code != 0:
+        buf.zero_()
+        raise RuntimeError(f"adana_b200 kernel reported: {STATUS_NAMES.get(code, code)}")
+
+
+def check_rc(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"adana_b200: {what} failed with code {rc}")

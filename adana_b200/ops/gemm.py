@@ -1,0 +1,185 @@
+"""bf16 GEMMs on the tcgen05 tensor cores (csrc/gemm_tcgen05.cu) with fused epilogues.
+
+`gemm()` is the thin wrapper over the C entry point; `linear_fwd / linear_dgrad /
+linear_wgrad` name the three GEMMs of an `nn.Linear` so that callers never transpose a
+tensor in memory: the kernel reads MN-major operands directly.
+
+Each function has a PyTorch fp32-accumulate reference (`*_ref`) that runs on CPU and is
+what the GPU tests compare against.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+EPI_BF16, EPI_GELU_DUAL, EPI_RESID_F32, EPI_DGELU, EPI_F32, EPI_SWIGLU, EPI_DSWIGLU = range(7)
+
+
+def _check2d(t: torch.Tensor, name: str):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with a contiguous last dimension, got {tuple(t.shape)} / {t.stride()}")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bf16")
+    if t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name}: row pitch must be a multiple of 8 elements and the base 16-byte aligned")
+
+
+def gemm(A, B, C, *, M, N, K, a_mn=False, b_mn=False, epi=EPI_BF16, C2=None, R=None,
+         alpha=1.0, beta=0.0, b_off2=0):
+    """C = epilogue(A · Bᵀ) on the tensor cores; all tensors are pre-allocated by the caller."""
+    _check2d(A, "A")
+    _check2d(B, "B")
+    lib = _lib.lib()
+    rc = lib.adana_gemm_bf16(
+        A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K,
+        A.stride(0), B.stride(0), C.stride(0), int(a_mn), int(b_mn), int(epi),
+        _lib.ptr(C2), 0 if C2 is None else C2.stride(0),
+        _lib.ptr(R), 0 if R is None else R.stride(0),
+        float(alpha), float(beta), int(b_off2),
+        _lib.status_buffer(A.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_gemm_bf16")
+    return C
+
+
+# ----------------------------------------------------------------------------------------------
+# nn.Linear GEMMs: x [M,K] (bf16), w [N,K] (bf16, the nn.Linear weight), dy [M,N] (bf16)
+# ----------------------------------------------------------------------------------------------
+def use_cuda(*ts) -> bool:
+    return all(t is None or t.is_cuda for t in ts) and _lib.available()
+
+
+def linear_fwd(x, w, out=None):
+    M, K = x.shape
+    N = w.shape[0]
+    if not use_cuda(x, w):
+        return (x.float() @ w.float().t()).to(torch.bfloat16)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    return gemm(x, w, out, M=M, N=N, K=K)
+
+
+def linear_fwd_f32(x, w, out=None, alpha=1.0):
+    """fp32 output (used for the logits chunks of the fused cross-entropy)."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not use_cuda(x, w):
+        return (x.float() @ w.float().t()) * alpha
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    return gemm(x, w, out, M=M, N=N, K=K, epi=EPI_F32, alpha=alpha, beta=0.0)
+
+
+def linear_gelu_fwd(x, w):
+    """Returns (z, gelu(z)) in one pass: z is kept for backward, gelu(z) feeds the next GEMM."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not use_cuda(x, w):
+        z = (x.float() @ w.float().t())
+        return z.to(torch.bfloat16), F.gelu(z).to(torch.bfloat16)
+    z = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    gemm(x, w, z, M=M, N=N, K=K, epi=EPI_GELU_DUAL, C2=h)
+    return z, h
+
+
+def linear_resid_fwd(x, w, resid, alpha=1.0, out=None):
+    """out(f32) = resid(f32) + alpha * x·wᵀ ; `out` may alias `resid`."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not use_cuda(x, w, resid):
+        return resid + alpha * (x.float() @ w.float().t())
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    return gemm(x, w, out, M=M, N=N, K=K, epi=EPI_RESID_F32, R=resid, alpha=alpha)
+
+
+def linear_swiglu_fwd(x, w_gu):
+    """w_gu = [gate rows; up rows] ([2*H, K]).  Returns (gu [M,2H] pre-activations, h [M,H])."""
+    M, K = x.shape
+    H = w_gu.shape[0] // 2
+    if not use_cuda(x, w_gu):
+        gu = x.float() @ w_gu.float().t()
+        g, u = gu[:, :H], gu[:, H:]
+        return gu.to(torch.bfloat16), (F.silu(g) * u).to(torch.bfloat16)
+    gu = torch.empty((M, 2 * H), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty((M, H), dtype=torch.bfloat16, device=x.device)
+    gemm(x, w_gu, gu, M=M, N=H, K=K, epi=EPI_SWIGLU, C2=h, b_off2=H)
+    return gu, h
+
+
+def linear_dgrad(dy, w, out=None):
+    """dx [M,K] = dy [M,N] · w [N,K]."""
+    M, N = dy.shape
+    K = w.shape[1]
+    if not use_cuda(dy, w):
+        return (dy.float() @ w.float()).to(torch.bfloat16)
+    if out is None:
+        out = torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
+    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True)
+
+
+def linear_dgrad_f32(dy, w, out=None, beta=0.0, resid=None):
+    """fp32 dx; with `resid` computes resid + dy·w (gradient of a residual branch)."""
+    M, N = dy.shape
+    K = w.shape[1]
+    if not use_cuda(dy, w):
+        r = dy.float() @ w.float()
+        if resid is not None:
+            return resid + r
+        return r if out is None or beta == 0.0 else beta * out + r
+    if out is None:
+        out = torch.empty((M, K), dtype=torch.float32, device=dy.device)
+    if resid is not None:
+        return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_RESID_F32, R=resid)
+    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_F32, beta=beta)
+
+
+def linear_dgrad_dgelu(dy, w, z):
+    """dz = (dy · w) * gelu'(z): gradient through `gelu` fused in the dgrad epilogue."""
+    M, N = dy.shape
+    K = w.shape[1]
+    if not use_cuda(dy, w, z):
+        dh = dy.float() @ w.float()
+        zf = z.float().requires_grad_(True)
+        with torch.enable_grad():
+            g, = torch.autograd.grad(F.gelu(zf).sum(), zf)
+        return (dh * g).to(torch.bfloat16)
+    out = torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
+    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_DGELU, R=z)
+
+
+def linear_dgrad_dswiglu(dy, w_down, gu):
+    """d[gate|up] = swiglu'(gate, up) ∘ (dy · w_down): w_down [d, H], gu [M, 2H]."""
+    M, N = dy.shape
+    H = w_down.shape[1]
+    if not use_cuda(dy, w_down, gu):
+        dh = dy.float() @ w_down.float()
+        g, u = gu[:, :H].float(), gu[:, H:].float()
+        s = torch.sigmoid(g)
+        dg = dh * u * s * (1 + g * (1 - s))
+        du = dh * g * s
+        return torch.cat([dg, du], dim=1).to(torch.bfloat16)
+    out = torch.empty((M, 2 * H), dtype=torch.bfloat16, device=dy.device)
+    return gemm(dy, w_down, out, M=M, N=H, K=N, b_mn=True, epi=EPI_DSWIGLU, R=gu, b_off2=H)
+
+
+def linear_wgrad(dy, x, out=None, accumulate=False, alpha=1.0):
+    """dw [N,K] (fp32) (+)= dyᵀ [N,M] · x [M,K]; both operands are read as stored."""
+    M, N = dy.shape
+    K = x.shape[1]
+    if not use_cuda(dy, x):
+        r = alpha * (dy.float().t() @ x.float())
+        if out is None:
+            return r
+        if accumulate:
+            out += r
+        else:
+            out.copy_(r)
+        return out
+    if out is None:
+        out = torch.empty((N, K), dtype=torch.float32, device=dy.device)
+        accumulate = False
+    return gemm(dy, x, out, M=N, N=K, K=M, a_mn=True, b_mn=True, epi=EPI_F32,
+                alpha=alpha, beta=1.0 if accumulate else 0.0)
