@@ -38,20 +38,28 @@ int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void* y, int y_
 int adana_norm_bwd(const void* dy, int dy_is_bf16, const void* x, int x_is_bf16, const float* w,
                    const float* mean, const float* rstd, float* dx, int accumulate_dx,
                    float* dw_partial, int n_partial_rows, int rows, int cols, int kind,
-                   void* stream);
+                   void* dx_bf16 /*optional bf16 copy of the final dx*/, void* stream);
 int adana_colsum_f32(const float* partial, int n_partial_rows, int cols, float* out,
                      int accumulate, void* stream);
 
 // ---- per-head QK-norm + rotary embedding (rope.cu) --------------------------------------------
-int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int q_off, int k_off,
-                          const float* wq, const float* wk, const float* freqs, void* q_out,
-                          void* k_out, float* stats, int B, int S, int Hq, int Hk, int hd,
-                          float eps, int kind, void* stream);
+// q/k are read in place from the fused projection output: element (token, head h, i) of q is at
+// qkv[token * row_stride + q_off + h * q_hstride + i].  kind: 0 LayerNorm, 1 RMSNorm, 2 none.
+int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int q_off, int q_hstride,
+                          int k_off, int k_hstride, const float* wq, const float* wk,
+                          const float* freqs, void* q_out, void* k_out, long long n_tokens, int S,
+                          int Hq, int Hk, int hd, float eps, int kind, void* stream);
 int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, long long row_stride,
-                          int q_off, int k_off, const float* wq, const float* wk,
-                          const float* freqs, const float* stats, void* dqkv, float* dwq_partial,
-                          float* dwk_partial, int n_partial, int B, int S, int Hq, int Hk, int hd,
-                          int kind, void* stream);
+                          int q_off, int q_hstride, int k_off, int k_hstride, const float* wq,
+                          const float* wk, const float* freqs, void* dqkv, float* dwq_partial,
+                          float* dwk_partial, int n_partial, long long n_tokens, int S, int Hq,
+                          int Hk, int hd, float eps, int kind, void* stream);
+int adana_sigmoid_gate_fwd(const void* a, const void* gate, long long gate_row_stride, int gate_off,
+                           int gate_hstride, void* out, long long n_tokens, int H, int hd,
+                           void* stream);
+int adana_sigmoid_gate_bwd(const void* dout, const void* a, const void* gate,
+                           long long gate_row_stride, int gate_off, int gate_hstride, void* da,
+                           void* dgate_base, long long n_tokens, int H, int hd, void* stream);
 
 // ---- embedding (embedding.cu) ----------------------------------------------------------------
 int adana_embedding_fwd(const long long* idx, const void* table, int table_is_bf16, float* out,
@@ -77,13 +85,15 @@ struct AdanaOptHyper {
   float wd_factor;     // 1 - wd * sched / (1 + t / wd_ts)   (already folded on the host)
   float grad_scale;    // multiplies the raw gradient (1/acc_steps, 1/world); the clip
                        // coefficient is read from clip_coef_ptr on the device
-  int kind;            // 0 = adana/dana-mk4, 1 = dana-star(-mk4), 2 = adamw (bias-corrected)
+  int kind;            // 0 adana/dana-mk4, 1 dana-star(-mk4), 2 adamw, 3 adamw + independent decay
   float beta1, beta2, bc1, bc2;  // adamw only
 };
 int adana_opt_step(float* p, const float* g, float* m, float* v, float* tau, void* p_bf16,
                    long long n, const struct AdanaOptHyper* h, const float* clip_coef_ptr,
                    float* diag /*[4] or null*/, void* stream);
 int adana_sumsq_f32(const float* x, long long n, float* out /*accumulates*/, void* stream);
+int adana_clip_coef(const float* sumsq, float norm_scale, float max_norm, float* out /*[2]: coef, norm*/,
+                    void* stream);
 
 // ---- utility -------------------------------------------------------------------------------------
 int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);

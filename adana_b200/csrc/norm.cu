@@ -1,0 +1,295 @@
+// LayerNorm (weight only, mean-subtracting) and RMSNorm, forward and backward.
+// One CTA per row (grid-stride), the row is held in registers between the statistics pass
+// and the normalisation pass, fp32 statistics, 16-byte vector loads/stores.
+//
+//   forward : y = (x - mean) * rstd * w      (RMSNorm: mean = 0, rstd = rsqrt(mean(x^2)+eps))
+//   backward: dx = rstd * (g - mean(g) - xhat * mean(g * xhat)),  g = dy * w   (LN)
+//             dx = rstd * (g - xhat * mean(g * xhat))                           (RMS)
+//             dw = sum_rows dy * xhat   (per-CTA partial rows, reduced by adana_colsum_f32)
+//
+// Replaces F.layer_norm / the eager RMSNorm chain of the reference
+// (src/models/base.py:24-33, src/models/qwen3.py:66-77); the residual-stream gradient is
+// accumulated in place (accumulate_dx) so no separate add kernel runs.
+#include "api.h"
+#include "common.cuh"
+
+namespace adana {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAXV = 8;  // float4 per thread held in registers -> cols <= 8192
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  uint2 u = *reinterpret_cast<const uint2*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 u;
+  u.x = pack_bf16x2(v.x, v.y);
+  u.y = pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TX, typename TY, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
+                float eps) {
+  __shared__ float red[32];
+  const int nv = cols >> 2;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const TX* xr = x + (size_t)row * cols;
+    float4 v[NORM_MAXV];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        v[i] = load4<TX>(xr + c * 4);
+        s += (KIND == 0) ? (v[i].x + v[i].y + v[i].z + v[i].w)
+                         : (v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w);
+      }
+    }
+    float mean = 0.f, rstd;
+    if (KIND == 0) {
+      mean = block_sum(s, red) / cols;
+      float q = 0.f;
+#pragma unroll
+      for (int i = 0; i < NORM_MAXV; ++i) {
+        const int c = threadIdx.x + i * NORM_THREADS;
+        if (c < nv) {
+          const float a = v[i].x - mean, b = v[i].y - mean, cc = v[i].z - mean, d = v[i].w - mean;
+          q += a * a + b * b + cc * cc + d * d;
+        }
+      }
+      rstd = rsqrtf(block_sum(q, red) / cols + eps);
+    } else {
+      rstd = rsqrtf(block_sum(s, red) / cols + eps);
+    }
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+    TY* yr = y + (size_t)row * cols;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + c * 4);
+        float4 o;
+        o.x = (v[i].x - mean) * rstd * ww.x;
+        o.y = (v[i].y - mean) * rstd * ww.y;
+        o.z = (v[i].z - mean) * rstd * ww.z;
+        o.w = (v[i].w - mean) * rstd * ww.w;
+        store4<TY>(yr + c * 4, o);
+      }
+    }
+  }
+}
+
+template <typename TDY, typename TX, int KIND>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
+                const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                float* __restrict__ dx, int accumulate_dx, float* __restrict__ dw_partial, int rows,
+                int cols, __nv_bfloat16* __restrict__ dx16) {
+  __shared__ float red[32];
+  const int nv = cols >> 2;
+  float4 dwacc[NORM_MAXV];
+  float4 wreg[NORM_MAXV];
+#pragma unroll
+  for (int i = 0; i < NORM_MAXV; ++i) {
+    dwacc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int c = threadIdx.x + i * NORM_THREADS;
+    wreg[i] = (c < nv) ? *reinterpret_cast<const float4*>(w + c * 4) : make_float4(0, 0, 0, 0);
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = (KIND == 0) ? mean_in[row] : 0.f;
+    const float rstd = rstd_in[row];
+    const TDY* dyr = dy + (size_t)row * cols;
+    const TX* xr = x + (size_t)row * cols;
+    float4 g[NORM_MAXV], xh[NORM_MAXV];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        const float4 d = load4<TDY>(dyr + c * 4);
+        const float4 xv = load4<TX>(xr + c * 4);
+        xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd,
+                            (xv.w - mean) * rstd);
+        dwacc[i].x += d.x * xh[i].x;
+        dwacc[i].y += d.y * xh[i].y;
+        dwacc[i].z += d.z * xh[i].z;
+        dwacc[i].w += d.w * xh[i].w;
+        g[i] = make_float4(d.x * wreg[i].x, d.y * wreg[i].y, d.z * wreg[i].z, d.w * wreg[i].w);
+        s1 += g[i].x + g[i].y + g[i].z + g[i].w;
+        s2 += g[i].x * xh[i].x + g[i].y * xh[i].y + g[i].z * xh[i].z + g[i].w * xh[i].w;
+      }
+    }
+    const float m2 = block_sum(s2, red) / cols;
+    const float m1 = (KIND == 0) ? block_sum(s1, red) / cols : 0.f;
+    float* dxr = dx + (size_t)row * cols;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        float4 o;
+        o.x = rstd * (g[i].x - m1 - xh[i].x * m2);
+        o.y = rstd * (g[i].y - m1 - xh[i].y * m2);
+        o.z = rstd * (g[i].z - m1 - xh[i].z * m2);
+        o.w = rstd * (g[i].w - m1 - xh[i].w * m2);
+        if (accumulate_dx) {
+          const float4 p = *reinterpret_cast<const float4*>(dxr + c * 4);
+          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+        }
+        *reinterpret_cast<float4*>(dxr + c * 4) = o;
+        if (dx16) store4<__nv_bfloat16>(dx16 + (size_t)row * cols + c * 4, o);
+      }
+    }
+  }
+  if (dw_partial) {
+    float* out = dw_partial + (size_t)blockIdx.x * cols;
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) *reinterpret_cast<float4*>(out + c * 4) = dwacc[i];
+    }
+  }
+}
+
+__global__ void colsum_kernel(const float* __restrict__ partial, int n_rows, int cols,
+                              float* __restrict__ out, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int r = 0; r < n_rows; ++r) s += partial[(size_t)r * cols + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                     long long n) {
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const long long stride = (long long)gridDim.x * blockDim.x * 4;
+  for (long long i = i4; i < n; i += stride) {
+    if (i + 3 < n) {
+      store4<__nv_bfloat16>(dst + i, *reinterpret_cast<const float4*>(src + i));
+    } else {
+      for (long long j = i; j < n; ++j) dst[j] = __float2bfloat16(src[j]);
+    }
+  }
+}
+
+}  // namespace adana
+
+using namespace adana;
+
+static int norm_grid(int rows) {
+  const int cap = 148 * 8;
+  return rows < cap ? rows : cap;
+}
+
+extern "C" int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void* y,
+                              int y_is_bf16, float* mean, float* rstd, int rows, int cols,
+                              float eps, int kind, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0) return 0;
+  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV) return -1;
+  const int grid = norm_grid(rows);
+#define NF(TX, TY, K)                                                                          \
+  norm_fwd_kernel<TX, TY, K><<<grid, NORM_THREADS, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, \
+                                                            rows, cols, eps)
+  if (kind == 0) {
+    if (!x_is_bf16 && y_is_bf16) NF(float, __nv_bfloat16, 0);
+    else if (!x_is_bf16 && !y_is_bf16) NF(float, float, 0);
+    else if (x_is_bf16 && y_is_bf16) NF(__nv_bfloat16, __nv_bfloat16, 0);
+    else NF(__nv_bfloat16, float, 0);
+  } else {
+    if (!x_is_bf16 && y_is_bf16) NF(float, __nv_bfloat16, 1);
+    else if (!x_is_bf16 && !y_is_bf16) NF(float, float, 1);
+    else if (x_is_bf16 && y_is_bf16) NF(__nv_bfloat16, __nv_bfloat16, 1);
+    else NF(__nv_bfloat16, float, 1);
+  }
+#undef NF
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_norm_bwd(const void* dy, int dy_is_bf16, const void* x, int x_is_bf16,
+                              const float* w, const float* mean, const float* rstd, float* dx,
+                              int accumulate_dx, float* dw_partial, int n_partial_rows, int rows,
+                              int cols, int kind, void* dx_bf16, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0) return 0;
+  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV) return -1;
+  int grid = norm_grid(rows);
+  if (dw_partial) {
+    if (n_partial_rows <= 0) return -2;
+    // every CTA writes its partial row, so the grid must equal the number of partial rows
+    grid = n_partial_rows;
+  }
+#define NB(TD, TX, K)                                                                        \
+  norm_bwd_kernel<TD, TX, K><<<grid, NORM_THREADS, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, \
+                                                            rstd, dx, accumulate_dx, dw_partial,  \
+                                                            rows, cols, (__nv_bfloat16*)dx_bf16)
+  if (kind == 0) {
+    if (dy_is_bf16 && !x_is_bf16) NB(__nv_bfloat16, float, 0);
+    else if (!dy_is_bf16 && !x_is_bf16) NB(float, float, 0);
+    else if (dy_is_bf16 && x_is_bf16) NB(__nv_bfloat16, __nv_bfloat16, 0);
+    else NB(float, __nv_bfloat16, 0);
+  } else {
+    if (dy_is_bf16 && !x_is_bf16) NB(__nv_bfloat16, float, 1);
+    else if (!dy_is_bf16 && !x_is_bf16) NB(float, float, 1);
+    else if (dy_is_bf16 && x_is_bf16) NB(__nv_bfloat16, __nv_bfloat16, 1);
+    else NB(float, __nv_bfloat16, 1);
+  }
+#undef NB
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_colsum_f32(const float* partial, int n_partial_rows, int cols, float* out,
+                                int accumulate, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  colsum_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, n_partial_rows, cols, out, accumulate);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (n <= 0) return 0;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  cast_f32_bf16_kernel<<<(int)blocks, 256, 0, st>>>(src, (__nv_bfloat16*)dst, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_version(void) { return 1; }

@@ -46,10 +46,13 @@ def _declare(lib):
     sigs = {
         "adana_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, P, L, P, L, F, F, I, P, P],
         "adana_norm_fwd": [P, I, P, P, I, P, P, I, I, F, I, P],
-        "adana_norm_bwd": [P, I, P, I, P, P, P, P, I, P, I, I, I, I, P],
+        "adana_norm_bwd": [P, I, P, I, P, P, P, P, I, P, I, I, I, I, P, P],
         "adana_colsum_f32": [P, I, I, P, I, P],
-        "adana_qknorm_rope_fwd": [P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
-        "adana_qknorm_rope_bwd": [P, P, P, L, I, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+        "adana_qknorm_rope_fwd": [P, L, I, I, I, I, P, P, P, P, P, L, I, I, I, I, F, I, P],
+        "adana_qknorm_rope_bwd": [P, P, P, L, I, I, I, I, P, P, P, P, P, P, I, L, I, I, I, I, F, I, P],
+        "adana_sigmoid_gate_fwd": [P, P, L, I, I, P, L, I, I, P],
+        "adana_sigmoid_gate_bwd": [P, P, P, L, I, I, P, P, L, I, I, P],
+        "adana_clip_coef": [P, F, F, P, P],
         "adana_embedding_fwd": [P, P, I, P, I, I, I, P],
         "adana_embedding_bwd": [P, P, P, I, I, I, P],
         "adana_ce_fwd_bwd": [P, L, P, I, I, F, F, P, L, P, P, P],

@@ -54,7 +54,11 @@ def linear_fwd(x, w, out=None):
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w):
-        return (x.float() @ w.float().t()).to(torch.bfloat16)
+        r = (x.float() @ w.float().t()).to(x.dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     return gemm(x, w, out, M=M, N=N, K=K)
@@ -77,7 +81,7 @@ def linear_gelu_fwd(x, w):
     N = w.shape[0]
     if not use_cuda(x, w):
         z = (x.float() @ w.float().t())
-        return z.to(torch.bfloat16), F.gelu(z).to(torch.bfloat16)
+        return z.to(x.dtype), F.gelu(z).to(x.dtype)
     z = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     h = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     gemm(x, w, z, M=M, N=N, K=K, epi=EPI_GELU_DUAL, C2=h)
@@ -89,7 +93,11 @@ def linear_resid_fwd(x, w, resid, alpha=1.0, out=None):
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w, resid):
-        return resid + alpha * (x.float() @ w.float().t())
+        r = resid + alpha * (x.float() @ w.float().t())
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if out is None:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     return gemm(x, w, out, M=M, N=N, K=K, epi=EPI_RESID_F32, R=resid, alpha=alpha)
@@ -102,22 +110,26 @@ def linear_swiglu_fwd(x, w_gu):
     if not use_cuda(x, w_gu):
         gu = x.float() @ w_gu.float().t()
         g, u = gu[:, :H], gu[:, H:]
-        return gu.to(torch.bfloat16), (F.silu(g) * u).to(torch.bfloat16)
+        return gu.to(x.dtype), (F.silu(g) * u).to(x.dtype)
     gu = torch.empty((M, 2 * H), dtype=torch.bfloat16, device=x.device)
     h = torch.empty((M, H), dtype=torch.bfloat16, device=x.device)
     gemm(x, w_gu, gu, M=M, N=H, K=K, epi=EPI_SWIGLU, C2=h, b_off2=H)
     return gu, h
 
 
-def linear_dgrad(dy, w, out=None):
-    """dx [M,K] = dy [M,N] · w [N,K]."""
+def linear_dgrad(dy, w, out=None, alpha=1.0):
+    """dx [M,K] = alpha * dy [M,N] · w [N,K]."""
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w):
-        return (dy.float() @ w.float()).to(torch.bfloat16)
+        r = (alpha * (dy.float() @ w.float())).to(dy.dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
     if out is None:
         out = torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
-    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True)
+    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, alpha=alpha)
 
 
 def linear_dgrad_f32(dy, w, out=None, beta=0.0, resid=None):
@@ -136,8 +148,8 @@ def linear_dgrad_f32(dy, w, out=None, beta=0.0, resid=None):
     return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_F32, beta=beta)
 
 
-def linear_dgrad_dgelu(dy, w, z):
-    """dz = (dy · w) * gelu'(z): gradient through `gelu` fused in the dgrad epilogue."""
+def linear_dgrad_dgelu(dy, w, z, alpha=1.0):
+    """dz = alpha * (dy · w) * gelu'(z): gradient through `gelu` fused in the dgrad epilogue."""
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w, z):
@@ -145,24 +157,24 @@ def linear_dgrad_dgelu(dy, w, z):
         zf = z.float().requires_grad_(True)
         with torch.enable_grad():
             g, = torch.autograd.grad(F.gelu(zf).sum(), zf)
-        return (dh * g).to(torch.bfloat16)
+        return (alpha * dh * g).to(dy.dtype)
     out = torch.empty((M, K), dtype=torch.bfloat16, device=dy.device)
-    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_DGELU, R=z)
+    return gemm(dy, w, out, M=M, N=K, K=N, b_mn=True, epi=EPI_DGELU, R=z, alpha=alpha)
 
 
-def linear_dgrad_dswiglu(dy, w_down, gu):
-    """d[gate|up] = swiglu'(gate, up) ∘ (dy · w_down): w_down [d, H], gu [M, 2H]."""
+def linear_dgrad_dswiglu(dy, w_down, gu, alpha=1.0):
+    """d[gate|up] = swiglu'(gate, up) ∘ alpha (dy · w_down): w_down [d, H], gu [M, 2H]."""
     M, N = dy.shape
     H = w_down.shape[1]
     if not use_cuda(dy, w_down, gu):
-        dh = dy.float() @ w_down.float()
+        dh = alpha * (dy.float() @ w_down.float())
         g, u = gu[:, :H].float(), gu[:, H:].float()
         s = torch.sigmoid(g)
         dg = dh * u * s * (1 + g * (1 - s))
         du = dh * g * s
-        return torch.cat([dg, du], dim=1).to(torch.bfloat16)
+        return torch.cat([dg, du], dim=1).to(dy.dtype)
     out = torch.empty((M, 2 * H), dtype=torch.bfloat16, device=dy.device)
-    return gemm(dy, w_down, out, M=M, N=H, K=N, b_mn=True, epi=EPI_DSWIGLU, R=gu, b_off2=H)
+    return gemm(dy, w_down, out, M=M, N=H, K=N, b_mn=True, epi=EPI_DSWIGLU, R=gu, b_off2=H, alpha=alpha)
 
 
 def linear_wgrad(dy, x, out=None, accumulate=False, alpha=1.0):

@@ -1,0 +1,633 @@
+"""Kernel engine: flat sharded state, manual forward/backward over the sm_100a ops, gradient
+reduction and the fused optimizer step.
+
+What the engine owns, per unit (one per transformer block + a root unit):
+
+    master   fp32 [padded / world]   this rank's shard of the parameters (world = 1: everything)
+    m, v, τ  fp32 [padded / world]   optimizer moments of that shard
+    grads    fp32 [padded]           full-size main-gradient buffer; weight-gradient GEMMs
+                                     accumulate into it across micro-steps
+    weights  bf16 [padded]           compute copy of ALL parameters of the unit, resident
+
+The bf16 copies stay resident (a 2.5 B-parameter model is 5 GB of a 180 GB device), so the
+parameters cross NVLink once per optimizer step — the all-gather of the freshly updated bf16
+shards, unit by unit, overlapping the first forward of the next step — instead of twice per
+micro-step as in a reshard-after-forward design.  Gradients are reduce-scattered per unit as
+soon as the unit's backward finishes on the last micro-step (overlapping the rest of the
+backward), the squared-norm partials are produced from the reduced shards, one scalar
+all-reduce gives the clip coefficient on the device, and one fused kernel per unit range
+applies clip + update + weight decay and writes the bf16 shard for the next gather.
+
+Modes: `sharded` (the `fsdp` backend; state partitioned, ZeRO-style) and replicated (the
+`nccl`/`gloo` DDP backends; gradients all-reduced, every rank updates everything).  The math
+matches the reference's FSDP2 / DDP training step (src/distributed/fsdp.py:88-173,
+src/distributed/ddp.py:46-59, src/optim/base.py:234-294).
+
+`attach(model, ...)` wires the engine into a model: `model(idx, targets=...)` then runs the
+kernel path and `loss.backward()` runs the manual backward through a one-node autograd bridge.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import _lib
+from ..ops import misc as M
+from ..ops import optim as O
+from ..optim.logtime import wd_multiplier
+from ..parallel.comm import Comm, wait
+from . import blocks as BK
+from .layout import UnitLayout, build_layouts, engine_supported
+
+FUSED_OPTS = {"adana": (O.KIND_ADANA, False), "dana-mk4": (O.KIND_ADANA, True),
+              "dana-star": (O.KIND_DANA_STAR, False), "dana-star-mk4": (O.KIND_DANA_STAR, True),
+              "adamw": (O.KIND_ADAMW, False), "adamw-decaying-wd": (O.KIND_ADAMW_IWD, False)}
+
+
+class _Bridge(torch.autograd.Function):
+    """One autograd node for the whole model: backward() runs the engine's manual backward."""
+
+    @staticmethod
+    def forward(ctx, anchor, engine, loss):
+        ctx.engine = engine
+        return loss.detach().clone()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        ctx.engine._backward(grad_out)
+        return None, None, None
+
+
+class Unit:
+    def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt):
+        self.layout = layout
+        self.padded = layout.padded
+        self.shard_len = layout.padded // world if sharded else layout.padded
+        self.shard_off = rank * self.shard_len if sharded else 0
+        f32 = dict(dtype=torch.float32, device=device)
+        self.master = torch.zeros(self.shard_len, **f32)
+        self.grads = torch.zeros(self.padded, **f32)
+        self.grad_shard = torch.zeros(self.shard_len, **f32) if (sharded and world > 1) else self.grads
+        self.low_precision = cdt != torch.float32
+        if self.low_precision:
+            self.weights = torch.zeros(self.padded, dtype=cdt, device=device)
+            self.w_shard = (torch.zeros(self.shard_len, dtype=cdt, device=device)
+                            if (sharded and world > 1) else self.weights)
+        else:
+            # fp32 compute: the master buffer is the compute buffer when it is complete
+            self.weights = self.master if self.shard_len == self.padded else torch.zeros(self.padded, **f32)
+            self.w_shard = self.master
+        self.state: Dict[str, torch.Tensor] = {}
+        self.grad_work = None
+        self.gather_work = None
+        self.grads_dirty = False
+        # 1-D parameters are consumed in fp32 by the norm kernels
+        one_d = [s for s in layout.slots if len(s.shape) == 1]
+        self.small_off = min((s.offset for s in one_d), default=layout.numel)
+        assert all(len(s.shape) == 1 for s in layout.slots if s.offset >= self.small_off)
+        self.small_len = layout.numel - self.small_off
+        self.small_f32: Optional[torch.Tensor] = None
+
+    def ensure_state(self, names):
+        for n in names:
+            if n not in self.state:
+                self.state[n] = torch.zeros_like(self.master)
+
+    def view(self, flat: torch.Tensor, slot) -> torch.Tensor:
+        return flat[slot.offset: slot.offset + slot.numel].view(slot.shape)
+
+
+@dataclass
+class EngineConfig:
+    acc_steps: int = 1
+    grad_clip: float = 0.0
+    z_loss_coeff: float = 0.0
+    hoyer_loss_coeff: float = 0.0
+    activation_checkpointing: bool = False
+    checkpoint_every_n: int = 1
+    reduce_dtype: str = "float32"
+    log_diagnostics: bool = False
+
+
+class Engine:
+    def __init__(self, model, cfg, comm: Optional[Comm] = None, sharded: bool = True,
+                 device=None, compute_dtype: Optional[torch.dtype] = None):
+        reason = engine_supported(model, cfg)
+        if reason is not None:
+            raise ValueError(f"kernel engine unavailable: {reason}")
+        self.model = model
+        self.cfg = cfg
+        self.comm = comm or Comm()
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.sharded = sharded and self.world > 1
+        self.device = torch.device(device if device is not None else next(model.parameters()).device)
+        if compute_dtype is None:
+            compute_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32,
+                             "float16": torch.bfloat16}[getattr(cfg, "dtype", "bfloat16")]
+            if self.device.type == "cpu" and getattr(cfg, "dtype", "float32") == "float32":
+                compute_dtype = torch.float32
+        self.cdt = compute_dtype
+        self.ecfg = EngineConfig(
+            acc_steps=getattr(cfg, "acc_steps", 1), grad_clip=getattr(cfg, "grad_clip", 0.0),
+            z_loss_coeff=getattr(cfg, "z_loss_coeff", 0.0), hoyer_loss_coeff=getattr(cfg, "hoyer_loss_coeff", 0.0),
+            activation_checkpointing=getattr(cfg, "activation_checkpointing", False),
+            checkpoint_every_n=getattr(cfg, "checkpoint_every_n", 1))
+        self.loss_scale = 1.0 / max(1, self.ecfg.acc_steps)
+        self.enabled = True
+
+        self.layouts = build_layouts(model, self.world if self.sharded else 1)
+        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt)
+                                  for l in self.layouts]
+        self.spec = self._block_spec()
+        self.freqs = model.freqs_cis.to(self.device).contiguous()
+        self._anchor = torch.zeros((), device=self.device, requires_grad=True)
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._clip = torch.ones(2, dtype=torch.float32, device=self.device)
+        self._diag = torch.zeros(4, dtype=torch.float32, device=self.device)
+        self._pending = None
+        self.micro_step = 0            # micro-steps accumulated since the last optimizer step
+        self.sync_on_backward = None   # None: automatic (last of acc_steps); bool: forced by the backend
+        self.opt_step_count = 0
+        self.last_grad_norm = None
+        self.launches = 0
+
+        self._load_from_module()
+        self._bind_views()
+        self._sync_small()
+        self._rebind_module_params()
+
+    # ---------------------------------------------------------------------------------------------
+    # construction helpers
+    # ---------------------------------------------------------------------------------------------
+    def _block_spec(self) -> BK.BlockSpec:
+        m, c = self.model, self.cfg
+        hd = m.head_dim
+        if m.arch == "enoki":
+            mlp = m.transformer.h[0].mlp.c_fc.weight.shape[0]
+            qk_kind = BK.R.NONORM if getattr(c, "no_qknorm", False) else BK.R.LAYERNORM
+            return BK.BlockSpec(d=c.n_embd, n_head=c.n_head, n_kv_head=c.n_head, hd=hd, mlp=mlp,
+                                mlp_kind="gelu", norm_kind=BK.N.LAYERNORM, qk_kind=qk_kind, gate=False,
+                                eps=1e-5, qk_eps=1e-5, scale=float(getattr(c, "residual_stream_scalar", 1.0)),
+                                seq_len=c.sequence_length)
+        blk = m.transformer.h[0]
+        rms = getattr(c, "normalization_layer_type", "rmsnorm") == "rmsnorm"
+        eps = float(getattr(c, "rmsnorm_eps", 1e-5)) if rms else 1e-5
+        qk_kind = BK.R.NONORM if getattr(c, "no_qknorm", False) else (BK.R.RMSNORM if rms else BK.R.LAYERNORM)
+        return BK.BlockSpec(d=c.n_embd, n_head=c.n_head, n_kv_head=blk.attn.n_kv_head, hd=hd,
+                            mlp=blk.mlp.gate_proj.weight.shape[0], mlp_kind="swiglu",
+                            norm_kind=BK.N.RMSNORM if rms else BK.N.LAYERNORM, qk_kind=qk_kind,
+                            gate=blk.attn.gate, eps=eps, qk_eps=eps,
+                            scale=float(getattr(c, "residual_stream_scalar", 1.0)), seq_len=c.sequence_length)
+
+    def _load_from_module(self):
+        """Copy the module's (full, fp32) parameters into master shards and compute buffers."""
+        params = dict(self.model.named_parameters())
+        with torch.no_grad():
+            for u in self.units:
+                full = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
+                for s in u.layout.slots:
+                    full[s.offset:s.offset + s.numel].copy_(params[s.name].detach().reshape(-1).float())
+                u.master.copy_(full[u.shard_off:u.shard_off + u.shard_len])
+                if u.weights.data_ptr() != u.master.data_ptr():
+                    u.weights.copy_(full)
+                del full
+
+    def _bind_views(self):
+        """Per-unit dictionaries of weight / gradient views used by the block functions."""
+        sp = self.spec
+        for u in self.units:
+            lay = u.layout
+            if u.shard_len == u.padded:
+                u.small_f32 = u.master[u.small_off:u.small_off + u.small_len]
+            else:
+                u.small_f32 = torch.zeros(u.small_len, dtype=torch.float32, device=self.device)
+
+            def small(slot, u=u):
+                o = slot.offset - u.small_off
+                return u.small_f32[o:o + slot.numel]
+
+            W, Gd = {}, {}
+            if lay.name == "root":
+                for key, suffix in (("lm_head", "lm_head.weight"), ("wte", "transformer.wte.weight")):
+                    sl = lay.slot(suffix)
+                    W[key], Gd[key] = u.view(u.weights, sl), u.view(u.grads, sl)
+                sl = lay.slot("transformer.ln_f.weight")
+                W["ln_f"], Gd["ln_f"] = small(sl), u.view(u.grads, sl)
+            else:
+                def fused(suffixes, rows_cols):
+                    first = lay.slot(suffixes[0])
+                    off = first.offset
+                    for sfx in suffixes:
+                        sl = lay.slot(sfx)
+                        assert sl.offset == off, f"{sl.name} is not adjacent in the flat layout"
+                        off += sl.numel
+                    n = off - first.offset
+                    r, c = rows_cols
+                    assert n == r * c
+                    return (u.weights[first.offset:first.offset + n].view(r, c),
+                            u.grads[first.offset:first.offset + n].view(r, c))
+                if self.model.arch == "enoki":
+                    W["qkv"], Gd["qkv"] = fused(["attn.c_attn.weight"], (sp.proj_out, sp.d))
+                    W["o"], Gd["o"] = fused(["attn.c_proj.weight"], (sp.d, sp.n_head * sp.hd))
+                    W["fc"], Gd["fc"] = fused(["mlp.c_fc.weight"], (sp.mlp, sp.d))
+                    W["down"], Gd["down"] = fused(["mlp.c_proj.weight"], (sp.d, sp.mlp))
+                    qn, kn = "attn.q_layernorm.weight", "attn.k_layernorm.weight"
+                else:
+                    W["qkv"], Gd["qkv"] = fused(["attn.q_proj.weight", "attn.k_proj.weight", "attn.v_proj.weight"],
+                                                (sp.proj_out, sp.d))
+                    W["o"], Gd["o"] = fused(["attn.o_proj.weight"], (sp.d, sp.n_head * sp.hd))
+                    W["fc"], Gd["fc"] = fused(["mlp.gate_proj.weight", "mlp.up_proj.weight"], (2 * sp.mlp, sp.d))
+                    W["down"], Gd["down"] = fused(["mlp.down_proj.weight"], (sp.d, sp.mlp))
+                    qn, kn = "attn.q_norm.weight", "attn.k_norm.weight"
+                for key, suffix in (("ln_1", "ln_1.weight"), ("ln_2", "ln_2.weight"), ("q_norm", qn), ("k_norm", kn)):
+                    if lay.has(suffix):
+                        sl = lay.slot(suffix)
+                        W[key], Gd[key] = small(sl), u.view(u.grads, sl)
+            u.W, u.Gd = W, Gd
+
+    def _rebind_module_params(self):
+        """Point the module's parameters at the engine's storage (or release them when sharded)."""
+        params = dict(self.model.named_parameters())
+        with torch.no_grad():
+            for u in self.units:
+                for s in u.layout.slots:
+                    p = params[s.name]
+                    if u.shard_len == u.padded:
+                        p.data = u.view(u.master, s)
+                        p.grad = u.view(u.grads, s)
+                    else:
+                        p.data = torch.empty(0, dtype=torch.float32, device=self.device)
+                        p.grad = None
+        self.model._engine = self
+
+    # ---------------------------------------------------------------------------------------------
+    # forward / backward
+    # ---------------------------------------------------------------------------------------------
+    def handles(self, model, idx, targets, get_logits) -> bool:
+        return self.enabled and targets is not None and not get_logits
+
+    def _wait_unit(self, u: Unit):
+        if u.gather_work is not None:
+            wait(u.gather_work)
+            u.gather_work = None
+
+    def _sync_small(self):
+        """Sharded mode: norm weights are consumed in fp32, so their master values (owned by
+        whichever rank's shard covers them) are exchanged exactly with one small all-reduce of
+        a zero-padded buffer instead of being read back from the bf16 compute copy."""
+        if not (self.sharded and self.world > 1):
+            return
+        total = sum(u.small_len for u in self.units)
+        if self._small_all is None or self._small_all.numel() != total:
+            self._small_all = torch.zeros(total, dtype=torch.float32, device=self.device)
+        buf = self._small_all
+        buf.zero_()
+        pos = 0
+        for u in self.units:
+            lo, hi = u.shard_off, u.shard_off + u.shard_len
+            a, b = max(u.small_off, lo), min(u.small_off + u.small_len, hi)
+            if a < b:
+                buf[pos + a - u.small_off: pos + b - u.small_off].copy_(u.master[a - lo:b - lo])
+            pos += u.small_len
+        self.comm.all_reduce_sum(buf)
+        pos = 0
+        for u in self.units:
+            u.small_f32.copy_(buf[pos:pos + u.small_len])
+            pos += u.small_len
+
+    _small_all = None
+
+    def forward(self, idx, targets, compute_accuracy: bool = False):
+        model, sp, ecfg = self.model, self.spec, self.ecfg
+        need_grad = model.training and torch.is_grad_enabled()
+        B, S = idx.shape
+        T = B * S
+        assert S <= self.cfg.sequence_length
+        idx_flat = idx.reshape(-1)
+        root = self.units[-1]
+        self._wait_unit(root)
+        x = M.embedding_fwd(idx_flat, root.W["wte"])
+        x0 = x
+        saved: List = []
+        ckpt = ecfg.activation_checkpointing and need_grad
+        for i, u in enumerate(self.units[:-1]):
+            self._wait_unit(u)
+            keep = need_grad and not (ckpt and i % ecfg.checkpoint_every_n == 0)
+            x_in = x
+            x, sv = BK.block_forward(x, u.W, sp, self.freqs, B, S, self.cdt, need_grad=keep)
+            saved.append(sv if keep else ({"x_only": x_in} if need_grad else None))
+        acc = self.micro_step > 0
+        out, dx, dx_lp = BK.head_forward_backward(
+            x, targets, root.W, root.Gd, sp.norm_kind, sp.eps, ecfg.z_loss_coeff, self.loss_scale,
+            self.cdt, need_grad, acc)
+        loss = out["loss"]
+        aux = {"z_loss": out["z"]}
+        hoyer_grad = None
+        if ecfg.hoyer_loss_coeff != 0.0:
+            hv, hoyer_grad = BK.hoyer_value_and_grad(x0, ecfg.hoyer_loss_coeff, self.loss_scale, need_grad)
+            aux["hoyer_loss"] = hv
+            loss = loss + ecfg.hoyer_loss_coeff * hv
+        accuracy = (out["correct"] / T) if compute_accuracy else None
+        if need_grad:
+            self._pending = dict(dx=dx, dx_lp=dx_lp, saved=saved, idx=idx_flat, B=B, S=S,
+                                 hoyer_grad=hoyer_grad, acc=acc)
+            loss = _Bridge.apply(self._anchor, self, loss)
+        return {"logits": None, "loss": loss, "aux_losses": aux, "router_logits": None, "accuracy": accuracy}
+
+    def _backward(self, grad_out):
+        pend = self._pending
+        if pend is None:
+            raise RuntimeError("engine backward called without a pending forward")
+        self._pending = None
+        sp = self.spec
+        dx, dx_lp, saved, B, S, acc = pend["dx"], pend["dx_lp"], pend["saved"], pend["B"], pend["S"], pend["acc"]
+        sync = self.sync_on_backward
+        if sync is None:
+            sync = (self.micro_step + 1) >= self.ecfg.acc_steps
+        root = self.units[-1]
+        with torch.no_grad():
+            for i in range(len(self.units) - 2, -1, -1):
+                u = self.units[i]
+                sv = saved[i]
+                saved[i] = None
+                if "x_only" in sv:  # activation checkpoint: rebuild the block's activations
+                    _, sv = BK.block_forward(sv["x_only"], u.W, sp, self.freqs, B, S, self.cdt, need_grad=True)
+                BK.block_backward(dx, dx_lp, sv, u.W, u.Gd, sp, self.freqs, B, S, acc)
+                u.grads_dirty = True
+                del sv
+                if sync:
+                    self._reduce_unit(u)
+            if pend["hoyer_grad"] is not None:
+                dx += pend["hoyer_grad"]
+            if not acc:
+                root.Gd["wte"].zero_()
+            M.embedding_bwd(pend["idx"], dx, root.Gd["wte"])
+            root.grads_dirty = True
+            if sync:
+                self._reduce_unit(root)
+        self.micro_step += 1
+
+    # ---------------------------------------------------------------------------------------------
+    # gradient reduction, clipping, optimizer
+    # ---------------------------------------------------------------------------------------------
+    def _reduce_unit(self, u: Unit):
+        if self.world == 1:
+            return
+        if self.sharded:
+            u.grad_work = self.comm.reduce_scatter_sum(u.grads, u.grad_shard, async_op=True)
+        else:
+            u.grad_work = self.comm.all_reduce_sum(u.grads, async_op=True)
+
+    def finish_grad_sync(self):
+        for u in self.units:
+            if u.grad_work is not None:
+                wait(u.grad_work)
+                u.grad_work = None
+
+    def grad_norm_and_clip(self, max_norm: float):
+        """Global L2 norm of the (rank-averaged) gradient; leaves the clip coefficient on the device.
+        Returns a 0-d tensor holding the norm."""
+        self.finish_grad_sync()
+        self._sumsq.zero_()
+        for u in self.units:
+            O.sumsq_accumulate(u.grad_shard, self._sumsq)
+        if self.sharded:
+            self.comm.all_reduce_sum(self._sumsq)
+        O.clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
+        self.last_grad_norm = self._clip[1]
+        return self._clip[1]
+
+    def optimizer_step(self, opt: "EngineOptimizer"):
+        """Fused update of every unit shard, then the gather of the new compute weights."""
+        self.finish_grad_sync()
+        if self.ecfg.grad_clip == 0.0 or opt.clip_pending is False:
+            self._clip[0] = 1.0
+        kind, use_clip = FUSED_OPTS[opt.opt_name]
+        state_names = ["m", "v"] + (["tau"] if kind == O.KIND_DANA_STAR else [])
+        t = opt.step_count + 1
+        g_decay, g_nodecay = opt.param_groups[0], opt.param_groups[1]
+        diag = None
+        if opt.want_diagnostics:
+            self._diag.zero_()
+            diag = self._diag
+        for u in self.units:
+            u.ensure_state(state_names)
+            lo, hi = u.shard_off, u.shard_off + u.shard_len
+            for (a, b, grp) in ((0, u.layout.decay_end, g_decay), (u.layout.decay_end, u.layout.numel, g_nodecay)):
+                s, e = max(a, lo), min(b, hi)
+                if s >= e:
+                    continue
+                ls, le = s - lo, e - lo
+                hyper = opt.hyper_for(grp, t)
+                O.fused_step(u.master[ls:le], u.grad_shard[ls:le], u.state["m"][ls:le], u.state["v"][ls:le],
+                             u.state["tau"][ls:le] if "tau" in u.state else None,
+                             u.w_shard[ls:le] if u.low_precision else None,
+                             kind=kind, grad_scale=1.0 / self.world, clip_coef_t=self._clip, diag=diag, **hyper)
+            self._after_update(u)
+        self._sync_small()
+        opt.step_count = t
+        self.opt_step_count += 1
+        self.micro_step = 0
+        if diag is not None:
+            opt.absorb_diagnostics(diag, sum(u.layout.numel for u in self.units))
+
+    def _after_update(self, u: Unit):
+        """Make the unit's compute weights current again after its shard was updated."""
+        if self.world > 1 and self.sharded:
+            u.gather_work = self.comm.all_gather(u.w_shard, u.weights, async_op=True)
+        elif not u.low_precision and u.weights.data_ptr() != u.master.data_ptr():
+            u.weights.copy_(u.master)
+
+    def refresh_from_master(self):
+        """Re-derive compute weights from the master copy (after an external optimizer or a load)."""
+        with torch.no_grad():
+            for u in self.units:
+                if u.low_precision or u.w_shard.data_ptr() != u.master.data_ptr():
+                    u.w_shard.copy_(u.master)
+                self._after_update(u)
+            self._sync_small()
+
+    def zero_grad(self):
+        self.micro_step = 0
+
+    # ---------------------------------------------------------------------------------------------
+    # state dict (full tensors, reference key names) and sharded access
+    # ---------------------------------------------------------------------------------------------
+    def _gather_full(self, shard: torch.Tensor, u: Unit) -> torch.Tensor:
+        if u.shard_len == u.padded:
+            return shard
+        full = torch.empty(u.padded, dtype=shard.dtype, device=shard.device)
+        self.comm.all_gather(shard.contiguous(), full)
+        return full
+
+    def full_param_dict(self, which: str = "master") -> Dict[str, torch.Tensor]:
+        """name -> full fp32 tensor (collective when sharded).  `which`: master | m | v | tau."""
+        out = {}
+        for u in self.units:
+            src = u.master if which == "master" else u.state.get(which)
+            if src is None:
+                continue
+            full = self._gather_full(src, u)
+            for s in u.layout.slots:
+                out[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+        return out
+
+    def load_full_param_dict(self, tensors: Dict[str, torch.Tensor], which: str = "master"):
+        with torch.no_grad():
+            for u in self.units:
+                if which != "master":
+                    u.ensure_state([which])
+                dst = u.master if which == "master" else u.state[which]
+                lo, hi = u.shard_off, u.shard_off + u.shard_len
+                for s in u.layout.slots:
+                    if s.name not in tensors:
+                        continue
+                    a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
+                    if a >= b:
+                        continue
+                    src = tensors[s.name].reshape(-1)[a - s.offset:b - s.offset]
+                    dst[a - lo:b - lo].copy_(src.to(dst.dtype))
+        if which == "master":
+            self.refresh_from_master()
+
+    def state_dict(self):
+        return self.full_param_dict("master")
+
+    def num_params(self) -> int:
+        return sum(s.numel for u in self.units for s in u.layout.slots)
+
+
+class EngineOptimizer(torch.optim.Optimizer):
+    """`torch.optim.Optimizer` facade over the engine's fused update.
+
+    LR schedulers, `param_groups[i]['lr']`, `state_dict()` in the reference's layout
+    (`state[idx] = {step, m, v[, tau]}`, groups `{lr, delta, epsilon, weight_decay,
+    weighted_step_count, param_names}` with decay parameters first, each group sorted by
+    name) all behave as with the per-tensor classes; the math runs in `Engine.optimizer_step`.
+    """
+
+    def __init__(self, engine: Engine, opt_name: str, args, group_specs):
+        if opt_name not in FUSED_OPTS:
+            raise ValueError(f"{opt_name} has no fused engine implementation")
+        self.engine = engine
+        self.opt_name = opt_name
+        self.lr = args.lr
+        self.kappa = getattr(args, "kappa", 1.0)
+        self.clipsnr = getattr(args, "clipsnr", None) if FUSED_OPTS[opt_name][1] else None
+        self.wd_decaying = getattr(args, "wd_decaying", False)
+        self.wd_ts = getattr(args, "wd_ts", 1.0)
+        self.gamma_3_factor = getattr(args, "gamma_3_factor", 1.0)
+        self.betas = (getattr(args, "beta1", 0.9), getattr(args, "beta2", 0.95))
+        self.step_count = 0
+        self.clip_pending = None
+        self.want_diagnostics = False
+        self.diagnostics: Dict[str, float] = {}
+        dev = engine.device
+        groups = []
+        for spec in group_specs:
+            g = {"params": [nn.Parameter(torch.zeros(1, device=dev), requires_grad=False)],
+                 "param_names": list(spec["param_names"] if "param_names" in spec else spec["params"])}
+            if "weight_decay" in spec:
+                g["weight_decay"] = spec["weight_decay"]
+            groups.append(g)
+        if opt_name.startswith("adamw"):
+            defaults = dict(lr=args.lr, betas=self.betas, epsilon=1e-8, eps=1e-8, weight_decay=args.weight_decay)
+        else:
+            defaults = dict(lr=args.lr, delta=getattr(args, "delta", 8.0), epsilon=1e-8,
+                            weight_decay=args.weight_decay, weighted_step_count=0)
+        super().__init__(groups, defaults)
+
+    def hyper_for(self, group, t: int) -> dict:
+        lr = group["lr"]
+        sched = lr / self.lr if self.lr != 0 else 0.0
+        wd = group["weight_decay"]
+        if self.opt_name == "adamw":
+            wdf = 1.0 - lr * wd
+        elif self.opt_name == "adamw-decaying-wd":
+            wdf = wd_multiplier(wd, sched, t, self.wd_decaying, self.wd_ts) if wd != 0 else 1.0
+        else:
+            wdf = wd_multiplier(wd, sched, t, self.wd_decaying, self.wd_ts)
+        delta = group.get("delta", 8.0)
+        return dict(lr=lr, alpha=delta / (delta + t), step=t, kappa=self.kappa, clipsnr=self.clipsnr,
+                    eps=group.get("epsilon", 1e-8), gamma3=self.gamma_3_factor, wd_factor=wdf, betas=self.betas)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        for g in self.param_groups:
+            if "weighted_step_count" in g:
+                g["weighted_step_count"] += g["lr"] / self.lr if self.lr else 0.0
+        self.engine.optimizer_step(self)
+        self.clip_pending = None
+        return None
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.engine.zero_grad()
+
+    def absorb_diagnostics(self, diag: torch.Tensor, numel: int):
+        af, g2, mfac, m2 = (float(x) for x in diag.tolist())
+        w = self.engine.world if self.engine.sharded else 1
+        # sums over this rank's shard; a sharded engine reports rank-local means
+        n = max(1, numel // w)
+        self.diagnostics = {"current_alpha": af / n, "gradient_norm": math.sqrt(max(g2, 0.0)),
+                            "auto_factor_mean": mfac / n, "m_norm": math.sqrt(max(m2, 0.0)),
+                            "current_kappa_factor": (af / mfac) if mfac else 0.0}
+
+    # ---- checkpoint format -----------------------------------------------------------------------
+    def _ordered_names(self):
+        return [n for g in self.param_groups for n in g["param_names"]]
+
+    def state_dict(self):
+        names = self._ordered_names()
+        kind = FUSED_OPTS[self.opt_name][0]
+        keys = {"m": "m", "v": "v", "tau": "tau"}
+        if kind in (O.KIND_ADAMW, O.KIND_ADAMW_IWD):
+            keys = {"m": "exp_avg", "v": "exp_avg_sq"}
+        fulls = {k: self.engine.full_param_dict(k) for k in keys}
+        state = {}
+        for i, n in enumerate(names):
+            if not fulls["m"] or n not in fulls["m"]:
+                continue
+            st = {"step": self.step_count}
+            for k, outk in keys.items():
+                if fulls[k] and n in fulls[k]:
+                    st[outk] = fulls[k][n]
+            state[i] = st
+        groups, off = [], 0
+        for g in self.param_groups:
+            gg = {k: v for k, v in g.items() if k != "params"}
+            gg["params"] = list(range(off, off + len(g["param_names"])))
+            off += len(g["param_names"])
+            groups.append(gg)
+        return {"state": state, "param_groups": groups}
+
+    def load_state_dict(self, sd):
+        names = self._ordered_names()
+        kind = FUSED_OPTS[self.opt_name][0]
+        keymap = {"m": "m", "v": "v", "tau": "tau"}
+        if kind in (O.KIND_ADAMW, O.KIND_ADAMW_IWD):
+            keymap = {"m": "exp_avg", "v": "exp_avg_sq"}
+        state = sd.get("state", {})
+        for k, srck in keymap.items():
+            tensors = {}
+            for i, n in enumerate(names):
+                st = state.get(i, state.get(str(i)))
+                if st is not None and srck in st:
+                    tensors[n] = st[srck]
+            if tensors:
+                self.engine.load_full_param_dict(tensors, which=k)
+        steps = [int(st["step"]) for st in state.values() if "step" in st]
+        if steps:
+            self.step_count = max(steps)
+        for g, sg in zip(self.param_groups, sd.get("param_groups", [])):
+            for k, v in sg.items():
+                if k not in ("params",):
+                    g[k] = v
+
+
+def attach(model, cfg, comm: Optional[Comm] = None, sharded: bool = True, device=None,
+           compute_dtype=None) -> Engine:
+    return Engine(model, cfg, comm=comm, sharded=sharded, device=device, compute_dtype=compute_dtype)
