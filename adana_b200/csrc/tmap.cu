@@ -27,6 +27,15 @@ int encode_tmap_nd(CUtensorMap* out, const void* base, int rank, const uint64_t*
                    int swizzle_128) {
   std::call_once(g_once, load_encode);
   if (!g_encode) return -1;
+  // The encoder is a driver-API call and needs a context current on THIS thread; a thread that
+  // has only ever been handed tensors (PyTorch's autograd worker) may not have one bound yet.
+  // cudaSetDevice binds the device's primary context to the calling thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return -5;
+    ctx_bound = true;
+  }
   if (rank < 1 || rank > 5) return -2;
   if ((reinterpret_cast<uintptr_t>(base) & 0xF) != 0) return -3;
   cuuint64_t gdim[5];

@@ -69,6 +69,29 @@ def _declare(lib):
     return lib
 
 
+class _CountingLibrary:
+    """Proxy over the ctypes library that counts entry-point calls (each launches one kernel)."""
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self.calls = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._cdll, name)  # AttributeError for a missing symbol keeps hasattr() honest
+
+        def counted(*args, _fn=fn):
+            self.calls += 1
+            return _fn(*args)
+
+        self.__dict__[name] = counted
+        return counted
+
+
+def launch_count() -> int:
+    """Number of kernel-library entry points called so far in this process."""
+    return 0 if _lib is None else _lib.calls
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
@@ -97,7 +120,7 @@ def lib():
                 ) from e
             return None
     try:
-        _lib = _declare(ctypes.CDLL(str(_LIB_PATH)))
+        _lib = _CountingLibrary(_declare(ctypes.CDLL(str(_LIB_PATH))))
     except OSError as e:
         if torch.cuda.is_available():
             raise RuntimeError(f"adana_b200: cannot load {_LIB_PATH}: {e}") from e

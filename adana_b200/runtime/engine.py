@@ -191,6 +191,9 @@ class Engine:
                 full = torch.zeros(u.padded, dtype=torch.float32, device=self.device)
                 for s in u.layout.slots:
                     full[s.offset:s.offset + s.numel].copy_(params[s.name].detach().reshape(-1).float())
+                if self.world > 1:
+                    # every rank starts from rank 0's initialisation, whatever its own seed was
+                    self.comm.broadcast(full, src=0)
                 u.master.copy_(full[u.shard_off:u.shard_off + u.shard_len])
                 if u.weights.data_ptr() != u.master.data_ptr():
                     u.weights.copy_(full)

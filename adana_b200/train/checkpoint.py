@@ -1,0 +1,369 @@
+"""Checkpoint I/O.
+
+On-disk layouts (a run directory holds `ckpts/latest` and `ckpts/<iteration>`):
+
+  replicated / single   `<ckpt>/main.pt` = {"model", "optimizer", "scheduler", "itr"} — the
+                        reference's file (src/optim/utils.py:300-310), readable by both sides,
+                        including the `_orig_mod.` / `module.` key prefixes of compiled / DDP runs.
+  sharded (fsdp)        `<ckpt>/sharded/rank{r:05d}.pt` = this rank's flat fp32 shards
+                        (parameters + optimizer moments of every unit) and
+                        `<ckpt>/sharded/layout.json` = unit layouts + world size;
+                        `<ckpt>/meta.pt` = {"scheduler", "itr"} (same file as the reference,
+                        src/optim/utils.py:291-298).  Every rank writes only what it owns, no
+                        gather, so the time to checkpoint does not grow with the model.
+                        Loading with a different world size re-slices the saved flat ranges.
+                        `export_full()` / `import_dcp()` convert to `main.pt` and from a
+                        `torch.distributed.checkpoint` directory written by the reference.
+  every rank            `<ckpt>/worker_{rank}.pt` = RNG states (torch CPU/GPU, numpy, python) and
+                        the data-reader position (reference src/optim/utils.py:364-415).
+
+Writes go to a temporary name and are renamed into place, so an interrupted job never leaves a
+torn file; with `SLURM_TMPDIR` set, files are written node-locally and a background thread
+rsyncs + atomically renames them into the project directory
+(reference src/optim/utils.py:15-71, 236-257).  `AsyncWriter` moves serialisation off the
+training thread (`--async_checkpoint`).
+"""
+from __future__ import annotations
+
+import json
+import os
+import random
+import shutil
+import subprocess
+import threading
+from pathlib import Path
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+_rsync_thread: Optional[threading.Thread] = None
+_PREFIXES = ("_orig_mod.", "module.")
+
+
+# ---- helpers ------------------------------------------------------------------------------------------
+def _rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+def _atomic_save(obj, path: Path) -> None:
+    path.parent.mkdir(parents=True, exist_ok=True)
+    tmp = path.with_name(path.name + f".tmp{os.getpid()}")
+    torch.save(obj, tmp)
+    os.replace(tmp, path)
+
+
+def _load(path, map_location="cpu"):
+    try:
+        return torch.load(path, map_location=map_location)
+    except Exception:
+        return torch.load(path, map_location=map_location, weights_only=False)
+
+
+def strip_prefixes(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    out = {}
+    for k, v in sd.items():
+        changed = True
+        while changed:
+            changed = False
+            for p in _PREFIXES:
+                if k.startswith(p):
+                    k, changed = k[len(p):], True
+        out[k] = v
+    return out
+
+
+class AsyncWriter:
+    """Serialises checkpoint payloads on a background thread (one write in flight at a time)."""
+
+    def __init__(self):
+        self._thread: Optional[threading.Thread] = None
+        self.error: Optional[BaseException] = None
+
+    def submit(self, obj, path: Path):
+        self.wait()
+
+        def run():
+            try:
+                _atomic_save(obj, path)
+            except BaseException as e:  # surfaced on the next wait()
+                self.error = e
+
+        self._thread = threading.Thread(target=run, daemon=True, name="adana-ckpt-writer")
+        self._thread.start()
+
+    def wait(self):
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self.error is not None:
+            e, self.error = self.error, None
+            raise RuntimeError(f"asynchronous checkpoint write failed: {e}") from e
+
+
+_async_writer = AsyncWriter()
+
+
+# ---- node-local staging + rsync (SLURM) ------------------------------------------------------------------
+def _local_dir(ckpt_dir: Path):
+    tmp = os.environ.get("SLURM_TMPDIR")
+    if tmp:
+        return Path(tmp) / "ckpts" / ckpt_dir.name, ckpt_dir, True
+    return ckpt_dir, ckpt_dir, False
+
+
+def wait_for_rsync():
+    global _rsync_thread
+    if _rsync_thread is not None:
+        _rsync_thread.join()
+        _rsync_thread = None
+
+
+def rsync_if_slurm(ckpt_dir: Path):
+    """Rank 0, after all ranks finished writing: copy the node-local checkpoint to the project
+    directory in the background and swap it into place with a rename."""
+    global _rsync_thread
+    local, project, is_slurm = _local_dir(ckpt_dir)
+    if not is_slurm:
+        return
+
+    def run():
+        staging = project.with_name(project.name + ".incoming")
+        staging.mkdir(parents=True, exist_ok=True)
+        subprocess.run(["rsync", "-a", "--delete", f"{local}/", f"{staging}/"], check=False)
+        old = project.with_name(project.name + ".old")
+        if project.exists():
+            if old.exists():
+                shutil.rmtree(old, ignore_errors=True)
+            os.replace(project, old)
+        os.replace(staging, project)
+        shutil.rmtree(old, ignore_errors=True)
+
+    wait_for_rsync()
+    _rsync_thread = threading.Thread(target=run, daemon=True, name="adana-ckpt-rsync")
+    _rsync_thread.start()
+
+
+# ---- model / optimizer -------------------------------------------------------------------------------------
+def _engine_of(model):
+    return getattr(model, "_engine", None) or getattr(getattr(model, "module", None), "_engine", None)
+
+
+def _is_sharded(model) -> bool:
+    eng = _engine_of(model)
+    return eng is not None and eng.sharded
+
+
+def model_state_dict(model) -> Dict[str, torch.Tensor]:
+    """Full fp32 state dict under every backend (collective when the engine is sharded)."""
+    eng = _engine_of(model)
+    if eng is not None and eng.sharded:
+        return {k: v.cpu() for k, v in eng.full_param_dict("master").items()}
+    if isinstance(model, torch.nn.parallel.DistributedDataParallel):
+        model = model.module
+    return model.state_dict()
+
+
+def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_backend=None, async_write=False):
+    ckpt_dir = Path(ckpt_dir)
+    local, _, is_slurm = _local_dir(ckpt_dir)
+    if is_slurm:
+        wait_for_rsync()
+    local.mkdir(parents=True, exist_ok=True)
+    eng = _engine_of(model)
+    sched_sd = scheduler.state_dict() if scheduler is not None else None
+    if eng is not None and eng.sharded:
+        payload = {"world": eng.world, "rank": eng.rank, "opt_step": getattr(opt, "step_count", 0), "units": {}}
+        for u in eng.units:
+            entry = {"master": u.master.detach().cpu()}
+            for k, t in u.state.items():
+                entry[k] = t.detach().cpu()
+            payload["units"][u.layout.name] = entry
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in opt.param_groups]
+        payload["param_groups"] = groups
+        path = local / "sharded" / f"rank{eng.rank:05d}.pt"
+        if async_write:
+            _async_writer.submit(payload, path)
+        else:
+            _atomic_save(payload, path)
+        if eng.rank == 0:
+            layout = {"world": eng.world, "compute_dtype": str(eng.cdt), "units": [
+                {"name": u.layout.name, "numel": u.layout.numel, "padded": u.layout.padded,
+                 "decay_end": u.layout.decay_end,
+                 "slots": [{"name": s.name, "shape": list(s.shape), "offset": s.offset, "decay": s.decay}
+                           for s in u.layout.slots]} for u in eng.units]}
+            (local / "sharded").mkdir(parents=True, exist_ok=True)
+            tmp = local / "sharded" / "layout.json.tmp"
+            tmp.write_text(json.dumps(layout))
+            os.replace(tmp, local / "sharded" / "layout.json")
+            _atomic_save({"scheduler": sched_sd, "itr": itr}, local / "meta.pt")
+        return
+    if _rank() != 0:
+        return
+    ckpt = {"model": model_state_dict(model), "optimizer": opt.state_dict(), "scheduler": sched_sd, "itr": itr}
+    if async_write:
+        ckpt = {k: (_to_cpu(v)) for k, v in ckpt.items()}
+        _async_writer.submit(ckpt, local / "main.pt")
+    else:
+        _atomic_save(ckpt, local / "main.pt")
+
+
+def _to_cpu(obj):
+    if torch.is_tensor(obj):
+        return obj.detach().cpu().clone()
+    if isinstance(obj, dict):
+        return {k: _to_cpu(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to_cpu(v) for v in obj)
+    return obj
+
+
+def _load_sharded(eng, opt, sharded_dir: Path):
+    layout = json.loads((sharded_dir / "layout.json").read_text())
+    saved_world = layout["world"]
+    files = {}
+
+    def saved(rank):
+        if rank not in files:
+            files[rank] = _load(sharded_dir / f"rank{rank:05d}.pt")
+        return files[rank]
+
+    by_name = {u["name"]: u for u in layout["units"]}
+    opt_step = None
+    for u in eng.units:
+        lu = by_name[u.layout.name]
+        if [s["name"] for s in lu["slots"]] != [s.name for s in u.layout.slots]:
+            raise RuntimeError(f"checkpoint layout of {u.layout.name} does not match this model")
+        s_shard = lu["padded"] // saved_world
+        lo, hi = u.shard_off, u.shard_off + u.shard_len
+        hi_used = min(hi, lu["numel"])
+        keys = None
+        for r in range(saved_world):
+            a, b = max(lo, r * s_shard), min(hi_used, (r + 1) * s_shard)
+            if a >= b:
+                continue
+            entry = saved(r)["units"][u.layout.name]
+            opt_step = saved(r).get("opt_step", opt_step)
+            keys = [k for k in entry if k != "master"]
+            u.ensure_state(keys)
+            for k, t in entry.items():
+                dst = u.master if k == "master" else u.state[k]
+                dst[a - lo:b - lo].copy_(t[a - r * s_shard:b - r * s_shard])
+    if opt is not None and opt_step is not None and hasattr(opt, "step_count"):
+        opt.step_count = int(opt_step)
+    any_file = saved(0)
+    if opt is not None and "param_groups" in any_file:
+        for g, sg in zip(opt.param_groups, any_file["param_groups"]):
+            for k, v in sg.items():
+                g[k] = v
+    eng.refresh_from_master()
+
+
+def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_backend=None) -> int:
+    """Restores model, optimizer and scheduler; returns the iteration stored in the checkpoint."""
+    ckpt_path = Path(ckpt_path)
+    ckpt_dir = ckpt_path.parent if ckpt_path.suffix == ".pt" else ckpt_path
+    eng = _engine_of(model)
+    if (ckpt_dir / "sharded" / "layout.json").exists() and eng is not None:
+        _load_sharded(eng, opt, ckpt_dir / "sharded")
+        meta = _load(ckpt_dir / "meta.pt")
+        if scheduler is not None and meta.get("scheduler") is not None:
+            scheduler.load_state_dict(meta["scheduler"])
+        return meta["itr"]
+    if (ckpt_dir / "sharded").is_dir() and not (ckpt_dir / "main.pt").exists():
+        model_sd, opt_sd = import_dcp(ckpt_dir / "sharded")
+        meta = _load(ckpt_dir / "meta.pt")
+        ckpt = {"model": model_sd, "optimizer": opt_sd, "scheduler": meta.get("scheduler"), "itr": meta["itr"]}
+    else:
+        ckpt = _load(ckpt_dir / "main.pt")
+    sd = strip_prefixes(ckpt["model"])
+    if eng is not None:
+        eng.load_full_param_dict({k: v.to(eng.device) for k, v in sd.items()})
+    else:
+        target = model.module if isinstance(model, torch.nn.parallel.DistributedDataParallel) else model
+        target.load_state_dict(sd)
+    if opt is not None and ckpt.get("optimizer") is not None:
+        opt.load_state_dict(ckpt["optimizer"])
+    if scheduler is not None and ckpt.get("scheduler") is not None:
+        scheduler.load_state_dict(ckpt["scheduler"])
+    return ckpt["itr"]
+
+
+def export_full(model, opt, scheduler, itr, out_path: Path):
+    """Gather a sharded run into a single reference-format `main.pt` (all ranks call; rank 0 writes)."""
+    sd = model_state_dict(model)
+    osd = opt.state_dict()
+    if _rank() == 0:
+        _atomic_save({"model": sd, "optimizer": _to_cpu(osd),
+                      "scheduler": scheduler.state_dict() if scheduler is not None else None, "itr": itr},
+                     Path(out_path))
+
+
+def import_dcp(sharded_dir: Path):
+    """Read a `torch.distributed.checkpoint` directory (as written by the reference under FSDP)
+    into plain full tensors: returns (model_state_dict, optimizer_state_dict | None)."""
+    from torch.distributed.checkpoint import FileSystemReader
+    from torch.distributed.checkpoint.state_dict_loader import _load_state_dict
+    from torch.distributed.checkpoint.default_planner import _EmptyStateDictLoadPlanner
+
+    sd: Dict = {}
+    _load_state_dict(sd, storage_reader=FileSystemReader(str(sharded_dir)),
+                     planner=_EmptyStateDictLoadPlanner(), no_dist=True)
+    return strip_prefixes(sd.get("model", {})), sd.get("optimizer")
+
+
+# ---- per-rank worker state -------------------------------------------------------------------------------------
+def save_worker_state(ckpt_dir: Path, train_reader=None, verbose=True):
+    local, _, _ = _local_dir(Path(ckpt_dir))
+    state = {"rng_torch_cpu": torch.random.get_rng_state(), "rng_np": np.random.get_state(),
+             "rng_python": random.getstate(), "rng_torch_gpu": None}
+    if torch.cuda.is_available():
+        try:
+            state["rng_torch_gpu"] = torch.cuda.get_rng_state()
+        except RuntimeError:
+            pass
+    rank = _rank()
+    if train_reader is not None and hasattr(train_reader, "state_dict"):
+        ds = train_reader.state_dict()
+        state["dataloader_state"] = ds
+        if verbose:
+            inner = getattr(train_reader, "current_reader", train_reader)
+            preview = inner.preview_next_samples(3) if hasattr(inner, "preview_next_samples") else None
+            print(f"[Rank {rank}] Checkpoint: data_seed={getattr(train_reader, 'seed', None)}, "
+                  f"file_idx={ds.get('current_file_idx')}, step={ds.get('step')}, next={preview}")
+    _atomic_save(state, local / f"worker_{rank}.pt")
+
+
+def load_worker_state(ckpt_dir: Path, train_reader=None, verbose=True):
+    rank = _rank()
+    path = Path(ckpt_dir) / f"worker_{rank}.pt"
+    if not path.exists():
+        print(f"[Rank {rank}] Warning: no worker state at {path}; RNG and data position start fresh")
+        return
+    state = _load(path)
+    torch.random.set_rng_state(state["rng_torch_cpu"])
+    if state.get("rng_torch_gpu") is not None and torch.cuda.is_available():
+        try:
+            torch.cuda.set_rng_state(state["rng_torch_gpu"])
+        except RuntimeError:
+            pass
+    np.random.set_state(state["rng_np"])
+    random.setstate(state["rng_python"])
+    if train_reader is not None and "dataloader_state" in state:
+        train_reader.load_state_dict(state["dataloader_state"])
+        if verbose:
+            inner = getattr(train_reader, "current_reader", train_reader)
+            preview = inner.preview_next_samples(3) if hasattr(inner, "preview_next_samples") else None
+            print(f"[Rank {rank}] Restored: data_seed={getattr(train_reader, 'seed', None)}, "
+                  f"step={state['dataloader_state'].get('step')}, next={preview}")
+
+
+def checkpoint_exists(ckpt_dir: Path) -> bool:
+    ckpt_dir = Path(ckpt_dir)
+    return (ckpt_dir / "main.pt").exists() or (ckpt_dir / "meta.pt").exists()
+
+
+def finish_pending_writes():
+    _async_writer.wait()
+    wait_for_rsync()

@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Headline benchmark: whole-job training tokens/s of Enoki-36 (36 layers, d 2304, ~2.5 B
+parameters) with dana-star-mk4 under the fsdp backend, bf16 compute / fp32 state, on N GPUs of
+one node, synthetic Zipf(1.0) tokens, random-init weights.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Weak scaling: every GPU processes 64 sequences of 2048 tokens per optimizer step (8 micro-steps
+of 8 sequences), i.e. global batch 64*N (512 at N = 8).  One JSON line is printed by rank 0.
+
+Two measurements of the same metric:
+  value  device-timed: K optimizer steps bracketed by barrier + synchronize, CUDA events, max
+         over ranks; the step's token batches already sit on the device.
+  e2e    the same K steps driven through the public training API (`Trainer.train_step`): every
+         micro-batch is gathered from the token file into pinned host memory, copied to the
+         device, and the step's loss is read back to the host.
+
+`--impl reference` runs the unmodified reference (baseline/_ref/src) through its own `main()` /
+`train()` on the same model, optimizer, batch and data shape and prints the same line with
+"impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = dict(model="enoki", n_layer=36, n_head=36, n_embd=2304, qkv_dim=64, mlp_hidden_dim=9216,
+             sequence_length=2048, vocab_size=50304)
+OPT = dict(opt="dana-star-mk4", kappa=0.85, delta=8.0, clipsnr=2.0, lr=4.6e-5, weight_decay=4.0 / 100.0,
+           wd_ts=100.0, grad_clip=0.5, z_loss_coeff=1e-4)
+PER_GPU_SEQS = 64
+MICRO_BATCH = 8
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--micro_batch", type=int, default=MICRO_BATCH)
+    p.add_argument("--per_gpu_seqs", type=int, default=PER_GPU_SEQS)
+    p.add_argument("--n_layer", type=int, default=MODEL["n_layer"], help="override for smoke runs only")
+    p.add_argument("--no_e2e", action="store_true")
+    p.add_argument("--ref_no_compile", action="store_true")
+    return p.parse_args()
+
+
+def dist_env(gpus: int):
+    """Single-GPU runs are started without torchrun: provide the rendezvous variables."""
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("LOCAL_RANK", "0")
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(29500 + os.getpid() % 2000))
+    return int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+
+
+def write_tokens(n_tokens: int, seed: int = 0) -> Path:
+    """Synthetic Zipf(1.0) corpus in the fineweb-10BT layout (train.bin / val.bin, uint16)."""
+    from adana_b200.data.datasets import make_zipf_tokens
+
+    root = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data")) / "fineweb-10BT"
+    root.mkdir(parents=True, exist_ok=True)
+    tr, va = root / "train.bin", root / "val.bin"
+    if not tr.exists() or tr.stat().st_size != 2 * n_tokens:
+        tmp = root / f"train.{os.getpid()}.tmp"
+        make_zipf_tokens(n_tokens, 50304, 1.0, seed).tofile(tmp)
+        os.replace(tmp, tr)
+    if not va.exists():
+        tmp = root / f"val.{os.getpid()}.tmp"
+        make_zipf_tokens(300_000, 50304, 1.0, seed + 1).tofile(tmp)
+        os.replace(tmp, va)
+    return root.parent
+
+
+def emit(payload: dict):
+    print(json.dumps(payload), flush=True)
+
+
+# =================================================================================================
+# our implementation
+# =================================================================================================
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+
+    from adana_b200 import distributed
+    from adana_b200.config import flags
+    from adana_b200.data import DataReader
+    from adana_b200.models.utils import get_model
+    from adana_b200.ops import _lib
+    from adana_b200.optim.registry import build_optimizer
+    from adana_b200.optim.schedule import build_scheduler
+    from adana_b200.main import named_param_groups
+    from adana_b200.train.loop import Trainer
+    from adana_b200.utils.timing import ClockSampler
+
+    rank, local_rank, world = dist_env(a.gpus)
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    acc = a.per_gpu_seqs // a.micro_batch
+    args = flags.defaults()
+    for k, v in {**MODEL, **OPT}.items():
+        setattr(args, k, v)
+    args.n_layer = a.n_layer
+    args.dtype, args.device = "bfloat16", f"cuda:{local_rank}"
+    args.distributed_backend = "fsdp"
+    # the backend's split rule (acc //= gcd(acc, N); batch //= N / gcd) maps this to
+    # micro-batch `micro_batch` and `acc` accumulation steps on every rank
+    args.batch_size, args.acc_steps = a.micro_batch, acc * world
+    args.wd_decaying, args.weight_tying, args.init_scheme = True, False, "ScaledGPT"
+    args.scheduler, args.iterations, args.warmup_steps = "cos_inf", 100000, 1000
+    args.final_div_factor, args.dataset, args.log_interval = 0.1, "fineweb", 0
+    steps_total = a.warmup + a.steps
+    tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
+    if rank == 0:
+        args.datasets_dir = str(write_tokens(tokens_needed))
+    torch.cuda.set_device(local_rank)
+    backend = distributed.make_backend_from_args(args)
+    backend.comm.barrier()
+    args.datasets_dir = str(Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data")))
+    args = backend.get_adjusted_args_for_process(args)
+    assert (args.batch_size, args.acc_steps) == (a.micro_batch, acc)
+    torch.manual_seed(0)
+    with torch.device(args.device):   # initialise on the GPU: seconds instead of minutes for 2.5 B parameters
+        model = get_model(args)
+    model = backend.transform_model(model)
+    specs, _ = named_param_groups(model, backend)
+    opt = build_optimizer(args, model, specs, engine=backend.engine)
+    backend.engine_optimizer = hasattr(opt, "engine")
+    sched = build_scheduler(args, opt)
+    train_reader = DataReader(Path(args.datasets_dir) / "fineweb-10BT" / "train.bin", args.batch_size,
+                              args.sequence_length, seed=1337, auto_shard=True, keep_in_ram=True)
+    val_reader = DataReader(Path(args.datasets_dir) / "fineweb-10BT" / "val.bin", args.batch_size,
+                            args.sequence_length, seed=1337, auto_shard=False, keep_in_ram=True)
+    trainer = Trainer(model, opt, {"train": train_reader, "val": val_reader}, sched, "/tmp/adana_bench_exp",
+                      backend, args)
+    model.train()
+    tokens_per_step = a.per_gpu_seqs * world * args.sequence_length
+
+    # ---- device-timed region: batches pre-staged on the device ---------------------------------------
+    dev_batches = []
+    for _ in range(acc * 2):
+        x, y = train_reader.sample_batch()
+        dev_batches.append((x.to(args.device), y.to(args.device)))
+
+    def step_device(i):
+        for m in range(acc):
+            x, y = dev_batches[(i * acc + m) % len(dev_batches)]
+            with backend.get_context_for_microstep_forward(model, m, acc):
+                out = model(x, targets=y)
+            (out["loss"] / acc).backward()
+        backend.clip_grad_norm_(None, args.grad_clip)
+        opt.step()
+        sched.step()
+        opt.zero_grad()
+
+    for i in range(a.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    backend.comm.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(a.steps):
+        step_device(a.warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    backend.comm.barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = _lib.launch_count() - launches0
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=args.device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / a.steps
+    _lib.check_status()
+
+    # ---- end-to-end region: public API, pinned host batches, loss read back every step ----------------
+    e2e = None
+    if not a.no_e2e:
+        trainer.stager.lookahead = True
+        for _ in range(1):
+            out, loss = trainer.train_step()
+            float(loss.item())
+        torch.cuda.synchronize()
+        backend.comm.barrier()
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            out, loss = trainer.train_step()
+            float(loss.item())      # device -> host read of the step's result
+        torch.cuda.synchronize()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=args.device)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {"value": tokens_per_step * a.steps / float(dt.item()), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(trainer.stager.bytes_per_batch * acc), "d2h_bytes_per_step": 4,
+               "ms_per_step": 1e3 * float(dt.item()) / a.steps}
+        _lib.check_status()
+    final_loss = float(out["loss"].item()) if not a.no_e2e else None
+    mem = torch.cuda.max_memory_allocated() / 2 ** 30
+    if rank == 0:
+        emit({"metric": "tokens/sec/box FSDP dana-star-mk4 enoki-36", "value": tokens_per_step / (ms_per_step / 1e3),
+              "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
+              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+              "data": "synthetic Zipf(1.0) tokens, random-init weights", "impl": "ours",
+              "config": {"model": f"enoki-36 (L{args.n_layer}, d2304, mlp9216, hd64, V50304)",
+                         "global_batch": a.per_gpu_seqs * world, "seq_len": args.sequence_length,
+                         "micro_batch": a.micro_batch, "acc_steps": acc, "optimizer": "dana-star-mk4",
+                         "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2"},
+              "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+              "peak_mem_gib": round(mem, 2), "final_loss": final_loss})
+    backend.finalize()
+
+
+# =================================================================================================
+# reference implementation (unmodified sources under baseline/_ref)
+# =================================================================================================
+def run_reference(a):
+    ref_src = ROOT / "baseline" / "_ref" / "src"
+    if not (ref_src / "main.py").exists():
+        emit({"impl": "reference", "unavailable": "baseline/_ref/src is missing (reference not installed)"})
+        return
+    rank, local_rank, world = dist_env(a.gpus)
+    try:
+        import torch
+        import torch.distributed as dist
+
+        # launcher-side accommodations (no reference file is touched): the GPT-2 BPE files cannot be
+        # downloaded here, and the reference creates a tokenizer object in every model constructor
+        import tiktoken
+
+        class _NoTokenizer:
+            eot_token = 50256
+
+            def encode(self, *_, **__):
+                return [0]
+
+            encode_ordinary = encode
+
+            def decode(self, *_):
+                return ""
+
+        tiktoken.get_encoding = lambda name: _NoTokenizer()
+        sys.path.insert(0, str(ref_src))
+        os.chdir(ref_src)
+        import main as ref_main  # the reference's entry module
+
+        acc = a.per_gpu_seqs // a.micro_batch
+        steps_total = a.warmup + a.steps
+        tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
+        data_root = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data"))
+        if rank == 0:
+            write_tokens(tokens_needed)
+        argv = ["--model", "enoki", "--n_layer", str(a.n_layer), "--n_head", "36", "--n_embd", "2304",
+                "--qkv_dim", "64", "--mlp_hidden_dim", "9216", "--sequence_length", "2048", "--vocab_size", "50304",
+                "--weight_tying", "False", "--init-scheme", "ScaledGPT", "--dtype", "bfloat16",
+                "--distributed_backend", "fsdp", "--device", f"cuda:{local_rank}",
+                # the reference's split rule (acc //= gcd(acc, N); batch //= N / gcd) turns this into
+                # micro-batch `micro_batch` and `acc` accumulation steps per rank
+                "--batch_size", str(a.micro_batch), "--acc_steps", str(acc * world),
+                "--opt", "dana-star-mk4", "--kappa", "0.85", "--delta", "8", "--clipsnr", "2.0", "--lr", "4.6e-5",
+                "--weight_decay", "0.04", "--wd_decaying", "--wd_ts", "100", "--grad_clip", "0.5",
+                "--z_loss_coeff", "1e-4", "--scheduler", "cos_inf", "--iterations", str(steps_total),
+                "--warmup_steps", "1", "--final_div_factor", "0.1", "--dataset", "fineweb",
+                "--datasets_dir", str(data_root), "--log_interval", "1000000", "--eval_interval", "1000000",
+                "--latest_ckpt_interval", "0", "--results_base_folder", "/tmp/adana_ref_exps",
+                "--run_prefix", f"bench{os.getpid()}"]
+        if not a.ref_no_compile:
+            argv.append("--compile")
+        sys.argv = ["main.py"] + argv
+        args, parser = ref_main.get_args()
+
+        # time K optimizer steps from outside: wrap the optimizer's step() of the object the
+        # reference builds (the same hook point its own DynamicsLogger uses)
+        marks = {"n": 0, "e0": None, "e1": None}
+        orig_build = ref_main.build_optimizer
+
+        def build_and_hook(*bargs, **bkw):
+            opt = orig_build(*bargs, **bkw)
+            orig_step = opt.step
+
+            def timed_step(self_, *sa, **skw):
+                r = orig_step(*sa, **skw)
+                marks["n"] += 1
+                if marks["n"] == a.warmup:
+                    torch.cuda.synchronize()
+                    if dist.is_initialized():
+                        dist.barrier()
+                    marks["e0"] = torch.cuda.Event(enable_timing=True)
+                    marks["e0"].record()
+                    marks["t0"] = time.perf_counter()
+                elif marks["n"] == a.warmup + a.steps:
+                    marks["e1"] = torch.cuda.Event(enable_timing=True)
+                    marks["e1"].record()
+                    torch.cuda.synchronize()
+                    marks["t1"] = time.perf_counter()
+                return r
+
+            import types
+
+            # a bound method, as torch's LR schedulers expect of `optimizer.step`
+            opt.step = types.MethodType(timed_step, opt)
+            return opt
+
+        ref_main.build_optimizer = build_and_hook
+        # keep the process group alive after the reference's main() so the timings can be reduced
+        import distributed as ref_dist_pkg
+        from distributed import fsdp as ref_fsdp
+
+        ref_fsdp.FSDPDistributedBackend.finalize = lambda self: None
+        # the evaluation at iteration 0 / last iteration is not part of the timed region; keep it short
+        args.eval_batches = 1
+        clocks = None
+        from adana_b200.utils.timing import ClockSampler
+
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ref_main.main(args, parser)
+        clocks = sampler.stop() if rank == 0 else None
+        ms = torch.tensor([marks["e0"].elapsed_time(marks["e1"])], dtype=torch.float64, device=f"cuda:{local_rank}")
+        wall = torch.tensor([marks["t1"] - marks["t0"]], dtype=torch.float64, device=f"cuda:{local_rank}")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(wall, op=dist.ReduceOp.MAX)
+        ms_per_step = float(ms.item()) / a.steps
+        tokens_per_step = a.per_gpu_seqs * world * 2048
+        mem = torch.cuda.max_memory_allocated() / 2 ** 30
+        if rank == 0:
+            emit({"metric": "tokens/sec/box FSDP dana-star-mk4 enoki-36", "value": tokens_per_step / (ms_per_step / 1e3),
+                  "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+                  "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                  "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic Zipf(1.0) tokens, random-init weights",
+                  "impl": "reference",
+                  "config": {"model": f"enoki-36 (L{a.n_layer}, d2304, mlp9216, hd64, V50304)",
+                             "global_batch": a.per_gpu_seqs * world, "seq_len": 2048, "micro_batch": a.micro_batch,
+                             "acc_steps": acc, "optimizer": "dana-star-mk4", "parallelism": f"fsdp{world}",
+                             "compile": not a.ref_no_compile},
+                  "clocks": clocks,
+                  "e2e": {"value": tokens_per_step * a.steps / float(wall.item()), "unit": "tokens/s",
+                          "h2d_bytes_per_step": 2 * 8 * a.micro_batch * 2048 * acc, "d2h_bytes_per_step": 4,
+                          "note": "the reference's own loop: pinned host batches, .item() on the grad norm every step"},
+                  "gpu_launches": None, "peak_mem_gib": round(mem, 2)})
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+    except Exception as e:  # any failure of the reference arm is reported, never raised
+        if rank == 0:
+            emit({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"})
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,0 +1,69 @@
+import argparse
+
+import pytest
+
+from adana_b200.config import compute_dimensions, compute_lr, flags
+from adana_b200.config.scaling import apply_scaling_rule
+from adana_b200.main import get_args, get_exp_name
+
+
+def test_scaling_dimensions():
+    d = compute_dimensions("enoki", 36)
+    assert (d["n_layer"], d["n_embd"], d["mlp_hidden_dim"], d["qkv_dim"]) == (27, 2304, 9216, 64)
+    assert d["non_emb_params"] == 12 * 2304 ** 2 * 27
+    assert d["total_params"] == d["non_emb_params"] + 2 * 2304 * 50304
+    q = compute_dimensions("qwen3", 16)
+    assert (q["n_layer"], q["n_embd"], q["mlp_hidden_dim"], q["qkv_dim"]) == (32, 2048, 6144, 128)
+    e3 = compute_dimensions("enoki", 3)
+    assert (e3["n_layer"], e3["n_embd"]) == (2, 192)
+    with pytest.raises(ValueError):
+        compute_dimensions("nope", 4)
+
+
+def test_lr_laws():
+    P = 12 * 768 ** 2 * 9
+    assert compute_lr("enoki", "adamw", P) == pytest.approx(12.8 * (1.67e4 + P) ** -0.515)
+    assert compute_lr("enoki", "dana-star-mk4", P, kappa=0.85) == pytest.approx(223.0 * (2.40e6 + P) ** -0.724)
+    # closest-kappa fallback and the batch-512 table with fallback to the batch-32 one
+    assert compute_lr("enoki", "adana", P, kappa=0.82) == pytest.approx(17.6 * (3.66e4 + P) ** -0.624)
+    assert compute_lr("enoki", "adana", P, kappa=0.85, batch_size=512) == pytest.approx(85.3 * (3.04e4 + P) ** -0.654)
+    assert compute_lr("enoki", "d-muon", P, batch_size=512) == pytest.approx(2.19 * (5.64e4 + P) ** -0.417)
+    assert compute_lr("enoki", "lion", P) is None
+    assert compute_lr("qwen3", "adamw", P) == pytest.approx(2.16e4 * (7.20e4 + P) ** -0.873)
+
+
+def test_apply_scaling_rule_sets_shape_lr_iterations():
+    a = flags.defaults()
+    a.scaling_rule, a.heads, a.opt, a.kappa = "enoki", 12, "dana-mk4", 0.85
+    a.batch_size, a.acc_steps, a.sequence_length = 32, 1, 2048
+    apply_scaling_rule(a, verbose=False)
+    assert (a.model, a.n_layer, a.n_embd, a.n_head, a.weight_tying) == ("enoki", 9, 768, 12, False)
+    total = 12 * 768 ** 2 * 9 + 2 * 768 * 50304
+    assert a.iterations == int(20 * total / (32 * 2048))
+    assert a.lr == pytest.approx(23.0 * (1.46e4 + 12 * 768 ** 2 * 9) ** -0.627)
+
+
+def test_flag_surface_and_aliases():
+    args, parser = get_args(["--model", "enoki", "--opt", "dana-star-mk4", "--distributed_backend", "ddp",
+                             "--init-scheme", "ScaledGPT", "--residual-stream-scalar", "0.5", "--no-qknorm",
+                             "--collect-tau-stats", "--weight_tying", "False", "--nesterov", "True",
+                             "--iterations", "1000", "--kappa", "0.85"])
+    assert args.distributed_backend == "nccl" and args.init_scheme == "ScaledGPT" and args.no_qknorm
+    assert args.residual_stream_scalar == 0.5 and args.collect_tau_stats and args.weight_tying is False
+    assert args.nesterov is True and args.full_eval_at == []
+    assert args.adema_beta3 == pytest.approx(1 - 8.0 / 1000) and args.adema_alpha == pytest.approx(1000 ** 0.15)
+    assert len(flags.OPTIMIZERS) == 24
+    with pytest.raises(SystemExit):
+        get_args(["--opt", "not-an-optimizer"])
+    with pytest.raises(ValueError):
+        get_args(["--tp_size", "2", "--distributed_backend", "nccl"])
+
+
+def test_exp_name():
+    args, parser = get_args(["--model", "enoki", "--opt", "adana", "--dataset", "fineweb", "--batch_size", "32",
+                             "--lr", "0.002", "--seed", "3", "--wandb"])
+    name = get_exp_name(args, parser)
+    assert name.startswith("32x1_model-enoki_dataset-fineweb_opt-adana__")
+    assert "lr-0.002" in name and "seed" not in name and "wandb" not in name
+    args.run_prefix = "x" * 250
+    assert "__hash_" in get_exp_name(args, parser)

@@ -1,0 +1,102 @@
+import numpy as np
+import pytest
+import torch
+
+from adana_b200.data import DataReader, MultiFileDataReader, PinnedBatchStager, make_zipf_tokens, write_zipf_dataset
+from adana_b200.data.datasets import zipf_entropy
+
+
+@pytest.fixture(scope="module")
+def stream():
+    return make_zipf_tokens(60_000, vocab=1000, exponent=1.0, seed=0)
+
+
+def test_zipf_stream(stream):
+    assert stream.dtype == np.uint16 and stream.max() < 1000
+    counts = np.bincount(stream, minlength=1000)
+    assert counts[0] > counts[9] > counts[99]
+    assert counts[0] / counts[1] == pytest.approx(2.0, rel=0.15)
+    assert 5.0 < zipf_entropy(1000) < 6.5
+    assert zipf_entropy(50304) == pytest.approx(7.5664, abs=2e-3)
+
+
+def test_reader_matches_the_documented_index_plan(stream):
+    S, B = 64, 4
+    r = DataReader(stream, B, S, seed=7, auto_shard=False)
+    rng = np.random.default_rng(7)
+    order = rng.permutation((len(stream) - S - 1) // S - 1)
+    off = rng.integers(S)
+    x, y = r.sample_batch()
+    starts = order[:B] * S + off
+    assert x.dtype == torch.int64 and x.shape == (B, S)
+    for i, s in enumerate(starts):
+        assert np.array_equal(x[i].numpy(), stream[s:s + S].astype(np.int64))
+        assert np.array_equal(y[i].numpy(), stream[s + 1:s + S + 1].astype(np.int64))
+
+
+def test_rank_sharding_is_disjoint_and_covers_global_batches(stream):
+    S, B, N = 32, 4, 4
+    single = DataReader(stream, B, S, seed=3, world_size=1, rank=0)
+    ranks = [DataReader(stream, B, S, seed=3, world_size=N, rank=r) for r in range(N)]
+    for step in range(3):
+        per_rank = [r.sample_batch()[0] for r in ranks]
+        for r in range(N):
+            assert torch.equal(per_rank[r], single.sample_batch()[0])  # global batch N*step + r
+
+
+def test_epoch_rollover_and_resume(stream):
+    S, B = 128, 8
+    r = DataReader(stream, B, S, seed=1, auto_shard=False)
+    per_epoch = r.num_batches()
+    for _ in range(per_epoch - 2):
+        r.sample_batch()
+    st = r.state_dict()
+    nxt = [r.sample_batch()[0] for _ in range(5)]      # crosses into epoch 1
+    assert r.last_epoch == 1
+    r2 = DataReader(stream, B, S, seed=1, auto_shard=False)
+    r2.load_state_dict(st)
+    assert len(r2.preview_next_samples(2)) == 2 and r2.step == st["step"]  # peeking does not advance
+    for t in nxt:
+        assert torch.equal(r2.sample_batch()[0], t)
+
+
+def test_with_replacement(stream):
+    r = DataReader(stream, 4, 32, seed=5, with_replacement=True, world_size=2, rank=1)
+    a = r.sample_batch()[0]
+    r.set_step(0)
+    assert torch.equal(a, r.sample_batch()[0])
+    idx = np.random.default_rng(5 + 0 * 2 + 1).integers(len(stream) - 32 - 1, size=4)
+    assert np.array_equal(a[0].numpy(), stream[idx[0]:idx[0] + 32].astype(np.int64))
+
+
+def test_multi_file_reader_switches_and_resumes(tmp_path):
+    files = write_zipf_dataset(tmp_path, n_train=60_000, n_val=5_000, vocab=500, n_files=3)
+    train = {k: v for k, v in files.items() if k.startswith("train_")}
+    r = MultiFileDataReader(train, 4, 64, seed=11, auto_shard=False)
+    n = r.current_file_num_batches()
+    seen = []
+    for i in range(n + 3):
+        if i == n - 1:
+            st = r.state_dict()
+        seen.append(r.sample_batch()[0])
+    assert r.current_file_idx == 1 and r.step == 3
+    r2 = MultiFileDataReader(train, 4, 64, seed=11, auto_shard=False)
+    r2.load_state_dict(st)
+    for t in seen[n - 1:]:
+        assert torch.equal(r2.sample_batch()[0], t)
+    single = DataReader(np.fromfile(train["train_0001"], dtype=np.uint16), 4, 64, seed=11 + 1000, auto_shard=False)
+    assert torch.equal(seen[n], single.sample_batch()[0])
+
+
+def test_pinned_stager_cpu_path(stream):
+    r1 = DataReader(stream, 4, 32, seed=2, auto_shard=False)
+    r2 = DataReader(stream, 4, 32, seed=2, auto_shard=False)
+    for look in (True, False):
+        r1.set_step(0)
+        r2.set_step(0)
+        st = PinnedBatchStager(r1, "cpu", lookahead=look)
+        for _ in range(4):
+            x, y = st.next_batch()
+            xr, yr = r2.sample_batch()
+            assert torch.equal(x, xr) and torch.equal(y, yr)
+        assert st.bytes_per_batch == 2 * 4 * 32 * 8

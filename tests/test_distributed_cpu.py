@@ -1,0 +1,248 @@
+"""Multi-process paths on CPU ranks over Gloo: sharded engine == single process, DDP engine,
+sharded checkpoint with re-sharding, heartbeat watchdog (host-side failure detection)."""
+import copy
+import os
+import socket
+import sys
+import time
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _spawn(fn, world, *args):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    deadline = time.time() + 240
+    while len(results) < world and time.time() < deadline:
+        try:
+            r, val = q.get(timeout=1.0)
+            results[r] = val
+        except Exception:
+            if not any(p.is_alive() for p in procs) and q.empty():
+                break
+    for p in procs:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.terminate()
+    for r in range(world):
+        assert r in results, f"rank {r} produced no result"
+        if isinstance(results[r], str) and results[r].startswith("ERROR"):
+            raise AssertionError(results[r])
+    return results
+
+
+def _plain(obj):
+    """Tensors travel back to the parent as NumPy arrays (no shared-memory handles that die with the child)."""
+    if torch.is_tensor(obj):
+        return obj.detach().cpu().numpy()
+    if isinstance(obj, dict):
+        return {k: _plain(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_plain(v) for v in obj)
+    return obj
+
+
+def _t(x):
+    return torch.from_numpy(x) if not torch.is_tensor(x) else x
+
+
+def _entry(fn, rank, world, port, q, args):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    try:
+        q.put((rank, _plain(fn(rank, world, *args))))
+    except Exception as e:  # pragma: no cover - reported to the parent
+        import traceback
+
+        q.put((rank, "ERROR " + traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------------
+def _make(a, comm, sharded):
+    from adana_b200.models.utils import get_model
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    torch.manual_seed(0)
+    m = get_model(a)
+    eng = attach(m, a, comm=comm, sharded=sharded, device="cpu")
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    return m, eng, EngineOptimizer(eng, a.opt, a, specs)
+
+
+def _train_worker(rank, world, sharded, steps, ckpt_dir, save_at):
+    from conftest import tiny_args
+    from adana_b200.parallel.comm import Comm
+    from adana_b200.train import checkpoint as ck
+
+    dist.init_process_group("gloo")
+    a = tiny_args("enoki", opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True,
+                  wd_ts=3.0, acc_steps=2)
+    m, eng, opt = _make(a, Comm(), sharded)
+    m.train()
+    losses = []
+    for step in range(steps):
+        for micro in range(2):
+            g = torch.Generator().manual_seed(1000 * step + 10 * micro + rank)
+            idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g)
+            eng.sync_on_backward = micro == 1
+            out = m(idx, targets=idx.roll(-1, 1))
+            (out["loss"] / 2).backward()
+            losses.append(out["loss"].item())
+        eng.grad_norm_and_clip(0.5)
+        opt.step()
+        opt.zero_grad()
+        if ckpt_dir and step + 1 == save_at:
+            ck.save_checkpoint(m, opt, None, step + 1, Path(ckpt_dir))
+            dist.barrier()
+    full = eng.full_param_dict("master")
+    return {"losses": losses, "params": {k: v.clone() for k, v in full.items()},
+            "norm": float(eng.last_grad_norm), "sharded": eng.sharded,
+            "module_param_numel": sum(p.numel() for p in m.parameters())}
+
+
+def _single_reference(steps, world):
+    """Single process that sees every rank's micro-batches: the averaged-gradient equivalent."""
+    from conftest import tiny_args
+    from adana_b200.parallel.comm import Comm
+
+    a = tiny_args("enoki", opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True,
+                  wd_ts=3.0, acc_steps=2 * world)
+    m, eng, opt = _make(a, Comm(), False)
+    m.train()
+    for step in range(steps):
+        n = 0
+        for micro in range(2):
+            for r in range(world):
+                g = torch.Generator().manual_seed(1000 * step + 10 * micro + r)
+                idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g)
+                eng.sync_on_backward = False
+                out = m(idx, targets=idx.roll(-1, 1))
+                (out["loss"] / (2 * world)).backward()
+                n += 1
+        eng.grad_norm_and_clip(0.5)
+        opt.step()
+        opt.zero_grad()
+    return eng.full_param_dict("master"), float(eng.last_grad_norm)
+
+
+@pytest.mark.parametrize("sharded", [True, False])
+def test_two_rank_engine_matches_single_process(sharded):
+    res = _spawn(_train_worker, 2, sharded, 3, None, 0)
+    ref_params, ref_norm = _single_reference(3, 2)
+    assert res[0]["sharded"] == sharded
+    if sharded:
+        assert res[0]["module_param_numel"] == 0          # full fp32 parameters are not kept per rank
+    assert res[0]["norm"] == pytest.approx(ref_norm, rel=1e-4)
+    for k, v in ref_params.items():
+        for r in (0, 1):
+            d = (_t(res[r]["params"][k]) - v).abs()
+            assert d.mean().item() < 3e-6 and d.max().item() < 1e-3, (k, r, d.max().item())
+        assert torch.equal(_t(res[0]["params"][k]), _t(res[1]["params"][k]))
+
+
+def _resume_worker(rank, world, ckpt_dir, steps_after):
+    from conftest import tiny_args
+    from adana_b200.parallel.comm import Comm
+    from adana_b200.train import checkpoint as ck
+
+    dist.init_process_group("gloo")
+    a = tiny_args("enoki", opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True,
+                  wd_ts=3.0, acc_steps=2)
+    torch.manual_seed(99)
+    m, eng, opt = _make(a, Comm(), True)
+    itr = ck.load_checkpoint(m, opt, None, Path(ckpt_dir))
+    return {"itr": itr, "step_count": opt.step_count, "params": eng.full_param_dict("master"),
+            "tau": eng.full_param_dict("tau")}
+
+
+def test_sharded_checkpoint_reshards_on_load(tmp_path):
+    d = tmp_path / "ckpt"
+    saved = _spawn(_train_worker, 2, True, 2, str(d), 2)
+    assert (d / "sharded" / "layout.json").exists() and (d / "sharded" / "rank00001.pt").exists()
+    assert (d / "meta.pt").exists()
+    for world in (1, 3):
+        res = _spawn(_resume_worker, world, str(d), 0)
+        assert res[0]["itr"] == 2 and res[0]["step_count"] == 2
+        for k, v in saved[0]["params"].items():
+            assert torch.equal(_t(res[0]["params"][k]), _t(v)), (world, k)
+        assert any(abs(t).sum() > 0 for t in res[0]["tau"].values())
+
+
+# ---- failure detection on the host ----------------------------------------------------------------------------
+def _watchdog_worker(rank, world, quit_rank):
+    from adana_b200.runtime.watchdog import HeartbeatWatchdog, PeerFailure
+
+    dist.init_process_group("gloo")
+    wd = HeartbeatWatchdog.from_env(timeout_s=1.5)
+    wd.beat(0)
+    dist.barrier()
+    wd.start()
+    t0 = time.time()
+    for it in range(1, 200):
+        if rank == quit_rank and it == 3:
+            return "left"                     # leaves between steps, nothing in flight
+        wd.beat(it)
+        try:
+            wd.raise_if_failed()
+        except PeerFailure as e:
+            wd.stop()
+            return f"detected after {time.time() - t0:.1f}s: {e}"
+        time.sleep(0.1)
+    wd.stop()
+    return "never detected"
+
+
+def test_heartbeat_watchdog_reports_a_vanished_rank():
+    res = _spawn(_watchdog_worker, 3, 2)
+    assert res[2] == "left"
+    for r in (0, 1):
+        assert res[r].startswith("detected") and "rank 2" in res[r], res[r]
+
+
+def test_watchdog_with_fake_store_and_clock():
+    from adana_b200.runtime.watchdog import HeartbeatWatchdog
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+    now = [100.0]
+    store = Store()
+    a = HeartbeatWatchdog(store, 0, 2, timeout_s=5.0, clock=lambda: now[0])
+    b = HeartbeatWatchdog(store, 1, 2, timeout_s=5.0, clock=lambda: now[0])
+    assert a.check_once() is None            # peer has not published yet: no verdict
+    a.beat(1), b.beat(1)
+    now[0] += 4.0
+    assert a.check_once() is None
+    now[0] += 2.0                            # rank 1 silent for 6 s
+    a.beat(2)
+    msg = a.check_once()
+    assert msg is not None and "rank 1" in msg and b.check_once() is None

@@ -1,0 +1,206 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from adana_b200.ops import _lib, attention, gemm, misc, norm, optim, rope
+
+DEV = "cuda"
+
+
+def rnd(*s, scale=0.5, dtype=torch.bfloat16):
+    return (torch.randn(*s, device=DEV) * scale).to(dtype)
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    assert _lib.available(), "kernel library must load on a GPU box"
+    yield
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 768, 512), (1000, 520, 328), (256, 2304, 192), (4096, 1024, 2048)])
+def test_gemm_fwd_dgrad_wgrad(M, N, K):
+    torch.manual_seed(0)
+    x, w, dy = rnd(M, K), rnd(N, K), rnd(M, N)
+    assert rel_err(gemm.linear_fwd(x, w), x.float() @ w.float().t()) < 8e-3
+    assert rel_err(gemm.linear_dgrad(dy, w), dy.float() @ w.float()) < 8e-3
+    ref = dy.float().t() @ x.float()
+    dw = gemm.linear_wgrad(dy, x)
+    assert rel_err(dw, ref) < 1e-3
+    gemm.linear_wgrad(dy, x, out=dw, accumulate=True, alpha=0.5)
+    assert rel_err(dw, 1.5 * ref) < 1e-3
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 1024, 768, 512
+    x, w, dy = rnd(M, K), rnd(N, K), rnd(M, N)
+    ref = x.float() @ w.float().t()
+    z, h = gemm.linear_gelu_fwd(x, w)
+    assert rel_err(z, ref) < 8e-3 and rel_err(h, torch.nn.functional.gelu(ref)) < 8e-3
+    r = torch.randn(M, N, device=DEV)
+    assert rel_err(gemm.linear_resid_fwd(x, w, r, alpha=0.5), r + 0.5 * ref) < 1e-4
+    r2 = r.clone()
+    gemm.linear_resid_fwd(x, w, r2, alpha=0.5, out=r2)
+    assert rel_err(r2, r + 0.5 * ref) < 1e-4
+    zz = rnd(M, K)
+    zf = zz.float().requires_grad_(True)
+    g, = torch.autograd.grad(torch.nn.functional.gelu(zf).sum(), zf)
+    assert rel_err(gemm.linear_dgrad_dgelu(dy, w, zz, alpha=0.7), 0.7 * (dy.float() @ w.float()) * g) < 8e-3
+    assert rel_err(gemm.linear_fwd_f32(x, w), ref) < 1e-4
+
+
+def test_gemm_swiglu():
+    torch.manual_seed(2)
+    M, H, K = 512, 384, 256
+    x, wgu = rnd(M, K), rnd(2 * H, K)
+    gu, h = gemm.linear_swiglu_fwd(x, wgu)
+    ref = x.float() @ wgu.float().t()
+    assert rel_err(gu, ref) < 8e-3
+    assert rel_err(h, torch.nn.functional.silu(ref[:, :H]) * ref[:, H:]) < 8e-3
+    wd, dyd = rnd(K, H), rnd(M, K)
+    dgu = gemm.linear_dgrad_dswiglu(dyd, wd, gu, alpha=0.5)
+    dh = 0.5 * (dyd.float() @ wd.float())
+    g, u = gu[:, :H].float(), gu[:, H:].float()
+    s = torch.sigmoid(g)
+    assert rel_err(dgu, torch.cat([dh * u * s * (1 + g * (1 - s)), dh * g * s], 1)) < 8e-3
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("cols", [192, 2304, 1000])
+def test_norm_fwd_bwd(kind, cols):
+    torch.manual_seed(3)
+    rows = 777
+    x = torch.randn(rows, cols, device=DEV) * 2 + 0.3
+    w = torch.rand(cols, device=DEV) + 0.5
+    y, mean, rstd = norm.norm_fwd(x, w, 1e-5, kind, torch.bfloat16)
+    yr, mr, rr = norm.norm_fwd_ref(x, w, 1e-5, kind, torch.float32)
+    assert rel_err(y, yr) < 8e-3 and rel_err(rstd, rr) < 1e-5
+    dy = rnd(rows, cols)
+    acc = torch.randn(rows, cols, device=DEV)
+    acc_ref = acc.clone()
+    lp = torch.empty(rows, cols, device=DEV, dtype=torch.bfloat16)
+    dx, dw = norm.norm_bwd(dy, x, w, mean, rstd, kind, dx_accum=acc, dx_lowp=lp)
+    dxr, dwr = norm.norm_bwd_ref(dy, x, w, mr, rr, kind, dx_accum=acc_ref)
+    assert rel_err(dx, dxr) < 1e-4 and rel_err(dw, dwr) < 1e-3 and rel_err(lp, dxr) < 8e-3
+
+
+@pytest.mark.parametrize("hd,kind,gate", [(64, 0, False), (128, 1, True), (64, 2, False)])
+def test_qknorm_rope(hd, kind, gate):
+    torch.manual_seed(4)
+    B, S, Hq, Hk = 2, 96, 4, 2
+    T = B * S
+    qs = 2 * hd if gate else hd
+    width = Hq * qs + 2 * Hk * hd
+    qkv = rnd(T, width, scale=1.0)
+    wq, wk = torch.rand(hd, device=DEV) + 0.5, torch.rand(hd, device=DEV) + 0.5
+    freqs = rope.precompute_freqs_cis(hd, S).to(DEV)
+    args = (0, qs, Hq * qs, hd, wq, wk, freqs, S, Hq, Hk, hd, 1e-5, kind)
+    q, k = rope.qknorm_rope_fwd(qkv, *args)
+    qr, kr = rope.qknorm_rope_fwd_ref(qkv.float(), *args)
+    assert rel_err(q, qr) < 1e-2 and rel_err(k, kr) < 1e-2
+    dq, dk = rnd(T, Hq, hd), rnd(T, Hk, hd)
+    dqkv = torch.zeros_like(qkv)
+    dwq, dwk = rope.qknorm_rope_bwd(dq, dk, qkv, dqkv, *args)
+    dref = torch.zeros(T, width, device=DEV)
+    dwq_r, dwk_r = rope.qknorm_rope_bwd_ref(dq.float(), dk.float(), qkv.float(), dref, *args)
+    assert rel_err(dqkv, dref) < 1e-2
+    if kind != 2:
+        assert rel_err(dwq, dwq_r) < 5e-3 and rel_err(dwk, dwk_r) < 5e-3
+
+
+def test_embedding():
+    torch.manual_seed(5)
+    V, d, T = 1000, 192, 5000
+    table = torch.randn(V, d, device=DEV)
+    idx = torch.randint(0, V, (T,), device=DEV)
+    idx[:100] = 7  # collisions
+    assert torch.equal(misc.embedding_fwd(idx, table), table[idx])
+    tb = table.to(torch.bfloat16)
+    assert torch.equal(misc.embedding_fwd(idx, tb), tb[idx].float())
+    dout = torch.randn(T, d, device=DEV)
+    dt = torch.zeros(V, d, device=DEV)
+    misc.embedding_bwd(idx, dout, dt)
+    ref = torch.zeros(V, d, device=DEV).index_add_(0, idx, dout)
+    assert rel_err(dt, ref) < 1e-5
+
+
+@pytest.mark.parametrize("V,d", [(50304, 192), (512, 128)])
+def test_linear_ce(V, d):
+    torch.manual_seed(6)
+    T = 700
+    h = rnd(T, d, scale=1.0)
+    w = rnd(V, d, scale=0.05)
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    tgt[:5] = -1
+    out = misc.linear_ce(h, w, tgt, z_coeff=1e-2, loss_scale=0.5, chunk_rows=256)
+    ref = misc.linear_ce_ref(h, w, tgt, 1e-2, 0.5)
+    for k in ("ce_sum", "z_sum", "valid"):
+        assert abs(out[k].item() - ref[k].item()) / (abs(ref[k].item()) + 1e-6) < 2e-3, k
+    assert abs(out["correct"].item() - ref["correct"].item()) <= 2
+    assert rel_err(out["dh"], ref["dh"]) < 2e-2
+    assert rel_err(out["dw"], ref["dw"]) < 2e-2
+
+
+@pytest.mark.parametrize("kind,clipsnr", [(0, None), (0, 2.0), (1, None), (1, 2.0), (2, None), (3, None)])
+def test_fused_optimizer(kind, clipsnr):
+    torch.manual_seed(7)
+    n = 100_003
+    mk = lambda: (torch.randn(n, device=DEV), torch.randn(n, device=DEV) * 1e-2,
+                  torch.randn(n, device=DEV) * 1e-3, torch.rand(n, device=DEV) * 1e-4, torch.rand(n, device=DEV) * 0.6)
+    p, g, m, v, tau = mk()
+    cpu = [t.cpu().clone() for t in (p, g, m, v, tau)]
+    p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    clip = torch.tensor([0.7, 0.0], device=DEV)
+    kw = dict(kind=kind, lr=3e-3, alpha=8 / 15, step=7, kappa=0.85, clipsnr=clipsnr, eps=1e-8, gamma3=1.0,
+              wd_factor=0.999, grad_scale=0.5, betas=(0.9, 0.95))
+    diag = torch.zeros(4, device=DEV)
+    optim.fused_step(p, g, m, v, tau, p16, clip_coef_t=clip, diag=diag, **kw)
+    pc, gc, mc, vc, tc = cpu
+    dc = torch.zeros(4)
+    optim.fused_step(pc, gc, mc, vc, tc, None, clip_coef_t=clip.cpu(), diag=dc, **kw)
+    assert rel_err(p.cpu(), pc) < 1e-5 and rel_err(m.cpu(), mc) < 1e-5 and rel_err(v.cpu(), vc) < 1e-5
+    if kind == 1:
+        assert rel_err(tau.cpu(), tc) < 1e-5
+    assert rel_err(p16.cpu(), pc) < 8e-3
+    if kind in (0, 1):
+        assert rel_err(diag.cpu(), dc) < 1e-3
+
+
+def test_sumsq_and_clip():
+    x = torch.randn(1_000_001, device=DEV)
+    out = torch.zeros(1, device=DEV)
+    optim.sumsq_accumulate(x, out)
+    assert abs(out.item() - x.double().pow(2).sum().item()) / out.item() < 1e-4
+    c = torch.zeros(2, device=DEV)
+    optim.clip_coef(out, 0.5, 1.0, c)
+    norm_ = math.sqrt(out.item()) * 0.5
+    assert abs(c[1].item() - norm_) / norm_ < 1e-5 and abs(c[0].item() - min(1.0, 1.0 / (norm_ + 1e-6))) < 1e-6
+
+
+def test_sigmoid_gate():
+    torch.manual_seed(8)
+    T, H, hd = 300, 4, 64
+    proj = rnd(T, H * 2 * hd + 128, scale=1.0)
+    a = rnd(T, H * hd)
+    out = misc.sigmoid_gate_fwd(a, proj, hd, 2 * hd, H, hd)
+    g = torch.as_strided(proj, (T, H, hd), (proj.stride(0), 2 * hd, 1), hd).float()
+    assert rel_err(out, (a.float().view(T, H, hd) * torch.sigmoid(g)).view(T, -1)) < 8e-3
+    dout = rnd(T, H * hd)
+    dproj = torch.zeros_like(proj)
+    da = misc.sigmoid_gate_bwd(dout, a, proj, dproj, hd, 2 * hd, H, hd)
+    s = torch.sigmoid(g)
+    assert rel_err(da, (dout.float().view(T, H, hd) * s).view(T, -1)) < 8e-3
+    dg = torch.as_strided(dproj, (T, H, hd), (dproj.stride(0), 2 * hd, 1), hd).float()
+    assert rel_err(dg, dout.float().view(T, H, hd) * a.float().view(T, H, hd) * s * (1 - s)) < 1e-2

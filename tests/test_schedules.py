@@ -1,0 +1,57 @@
+import math
+
+import pytest
+import torch
+
+from adana_b200.optim.schedule import CosInf, PowerLaw, WSD, build_scheduler, cos_inf_schedule, wsd_schedule
+
+
+def test_cos_inf():
+    s = cos_inf_schedule(1000, 100, 100.0, 0.1, 0)
+    assert s(0) == pytest.approx(0.01)
+    assert s(50) == pytest.approx(0.5 + 0.5 / 100)
+    assert s(100) == pytest.approx(1.0)
+    floor = 1 / 100 / 0.1
+    assert s(550) == pytest.approx(floor + 0.5 * (1 - floor))
+    assert s(1000) == pytest.approx(floor) and s(5000) == pytest.approx(floor)
+    s2 = CosInf(1000, 100, 100.0, 1.0, 200)
+    assert s2(800) == pytest.approx(0.01) and s2(799) > 0.01
+
+
+@pytest.mark.parametrize("kind", ["linear", "exp", "cosine", "miror_cosine", "square", "sqrt"])
+def test_wsd_shapes(kind):
+    s = wsd_schedule(1000, final_lr_factor=0.1, n_warmup=100, init_div_factor=100, fract_decay=0.2, decay_type=kind)
+    assert s(0) == pytest.approx(0.01) and s(100) == 1.0 and s(799) == 1.0
+    assert s(1000) == pytest.approx(0.1)
+    x = 0.5
+    expect = {"linear": 0.1 + 0.9 * 0.5, "exp": 0.1 ** 0.5, "cosine": 0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * x)),
+              "square": 0.1 + 0.9 * (1 - 0.25), "sqrt": 0.1 + 0.9 * (1 - math.sqrt(0.5))}
+    expect["miror_cosine"] = 2 * expect["linear"] - expect["cosine"]
+    assert s(900) == pytest.approx(expect[kind])
+    with pytest.raises(ValueError):
+        WSD(10, decay_type="bogus")
+
+
+def test_powerlaw():
+    s = PowerLaw(1000, 10, init_value=1.0, saturation_value=0.2, power=-0.5, time_scale=4.0)
+    assert s(5) == pytest.approx(0.5) and s(10) == pytest.approx(1.0)
+    assert s(10 + 12) == pytest.approx((1 + 3) ** -0.5)
+    assert s(10 ** 6) == pytest.approx(0.2)
+
+
+def test_scheduler_factory_drives_optimizer_lr():
+    from adana_b200.config import flags
+
+    a = flags.defaults()
+    a.scheduler, a.iterations, a.warmup_steps, a.lr, a.final_div_factor = "cos_inf", 100, 10, 1e-2, 0.1
+    p = torch.nn.Parameter(torch.zeros(2))
+    opt = torch.optim.SGD([p], lr=a.lr)
+    sch = build_scheduler(a, opt)
+    lrs = []
+    for _ in range(100):
+        lrs.append(opt.param_groups[0]["lr"])
+        opt.step()
+        sch.step()
+    assert lrs[0] == pytest.approx(1e-4) and max(lrs) == pytest.approx(1e-2) and lrs[-1] < 2e-3
+    import pickle
+    pickle.dumps(sch.state_dict())  # schedules are picklable objects, not closures
