@@ -242,6 +242,8 @@ GROUPS: dict[str, list[Flag]] = {
           help="collective implementation of the sharded engine: own peer-memory kernels or NCCL"),
         F("--fsdp_prefetch", default=1, type=int, help="blocks gathered ahead of compute"),
         F("--reduce_dtype", default="bfloat16", choices=["bfloat16", "float32"]),
+        F("--attention", default="auto", choices=["auto", "native", "sdpa"],
+          help="attention implementation: hand-written tcgen05 kernels or the PyTorch SDPA library call"),
         F("--heartbeat_timeout", default=0.0, type=float,
           help="seconds without a peer heartbeat before a rank aborts (0 = watchdog off)"),
     ],

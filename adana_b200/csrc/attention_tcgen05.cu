@@ -1,0 +1,853 @@
+// Causal self-attention forward on tcgen05 tensor cores (sm_100a), head_dim 64 or 128, bf16.
+//
+// One CTA = one (batch, head, 128-query tile); it walks the key/value tiles 0..diagonal:
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles through a 2-stage ring (128B swizzle)
+//   warp 1      MMA issuer:  S_j = Q K_j^T  -> tensor memory          (both operands K-major)
+//                            O  += P_j V_j  -> tensor memory          (P K-major, V MN-major)
+//   warps 2..5  softmax: thread r owns query row r (tcgen05.ld 32x32b gives one row per lane, so the
+//               row max / row sum need no shuffles), writes P_j as bf16 into shared memory in the
+//               128B-swizzled K-major layout the MMA reads, rescales O in tensor memory lazily (only
+//               when the running max grew by more than 2^8), and finally normalises and stores O.
+// QK_{j+1} is issued before PV_j waits for P_j, so the tensor cores compute the next scores while
+// the softmax of the current tile runs; with head_dim 64 two CTAs share an SM and overlap each other.
+// Grouped-query attention: query head h reads KV head h / (Hq/Hk).  V is read in place from the fused
+// projection output through a strided tensor map.  Every wait is bounded (common.cuh).
+//
+// Also writes lse2[b, h, s] = log2(sum_j exp(scale * s_ij)) in log2 units, which the backward uses
+// to recompute P without a second pass over the row.
+//
+// Replaces F.scaled_dot_product_attention(is_causal=True) of the reference
+// (src/models/enoki.py:134-136, src/models/qwen3.py:212-217).
+#include "api.h"
+#include "common.cuh"
+
+namespace adana {
+
+constexpr int ATT_BQ = 128;
+constexpr int ATT_BKV = 128;
+constexpr int ATT_THREADS = 192;
+constexpr int ATT_KV_STAGES = 2;
+constexpr float ATT_RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+template <int HD>
+struct AttFwdSmem {
+  static constexpr int TILE = ATT_BQ * HD * 2;            // one [128, HD] bf16 tile
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;
+  static constexpr int V_OFF = K_OFF + ATT_KV_STAGES * TILE;
+  static constexpr int P_OFF = V_OFF + ATT_KV_STAGES * TILE;
+  static constexpr int P_BYTES = ATT_BQ * ATT_BKV * 2;    // 32 KiB
+  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256;              // + barriers (the base is 1024-byte aligned)
+};
+
+struct AttFwdArgs {
+  __nv_bfloat16* out;     // [T, Hq*HD]
+  float* lse2;            // [B, Hq, S]
+  int B, S, Hq, Hk;
+  float scale_log2;       // softmax scale * log2(e)
+  int* status;
+};
+
+template <int HD, int S_BUFS>
+__global__ void __launch_bounds__(ATT_THREADS, (HD == 64 ? 2 : 1))
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttFwdArgs args) {
+  using L = AttFwdSmem<HD>;
+  constexpr int CHUNKS = HD / 64;                 // 64-column (128-byte) chunks per tile row
+  constexpr int CHUNK_BYTES = ATT_BQ * 128;       // [128 rows][128 B]
+  constexpr uint32_t TMEM_COLS = (S_BUFS * 128 + HD) <= 256 ? 256 : 512;
+  constexpr uint32_t O_COL = S_BUFS * 128;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* k_full = bars + 1;             // [STAGES]
+  uint64_t* v_full = bars + 3;             // [STAGES]
+  uint64_t* kv_empty = bars + 5;           // [STAGES]
+  uint64_t* s_full = bars + 7;             // [2]
+  uint64_t* s_empty = bars + 9;            // [2]
+  uint64_t* p_full = bars + 11;            // [1]
+  uint64_t* p_empty = bars + 12;           // [1]
+  uint64_t* o_full = bars + 13;            // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = args.S / ATT_BQ;
+  const int BH = args.B * args.Hq;
+  // heaviest query tiles (most KV tiles) are scheduled first
+  const int qt = n_qt - 1 - (int)(blockIdx.x / BH);
+  const int bh = (int)(blockIdx.x % BH);
+  const int b = bh / args.Hq, h = bh % args.Hq;
+  const int hk = h / (args.Hq / args.Hk);
+  const int n_kv = qt + 1;
+  const int row0 = b * args.S + qt * ATT_BQ;   // first token row of the query tile
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < ATT_KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, L::TILE);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+        tma_load_3d(smem + L::Q_OFF + c * CHUNK_BYTES, &tmQ, q_full, c * 64, row0, h);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+          ok = false;
+          break;
+        }
+        const int kvrow = b * args.S + j * ATT_BKV;
+        mbar_expect_tx(&k_full[stage], L::TILE);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(smem + L::K_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmK, &k_full[stage], c * 64, kvrow, hk);
+        mbar_expect_tx(&v_full[stage], L::TILE);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(smem + L::V_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmV, &v_full[stage], c * 64, kvrow, hk);
+        ++issued;
+        if (++stage == ATT_KV_STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        // aborting: give copies in flight time to land before the CTA exits
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BQ, HD, false, true);
+      const uint32_t sQ = smem_u32(smem + L::Q_OFF);
+      const uint32_t sP = smem_u32(smem + L::P_OFF);
+      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+      tc_fence_after_sync();
+      auto issue_pv = [&](int jj) -> bool {
+        const int st = jj % ATT_KV_STAGES;
+        const uint32_t kvph = (uint32_t)(jj / ATT_KV_STAGES) & 1;
+        if (!mbar_wait(p_full, (uint32_t)jj & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!mbar_wait(&v_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        tc_fence_after_sync();
+        const uint32_t sV = smem_u32(smem + L::V_OFF + st * L::TILE);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BKV / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sP + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sV + kk * 2048, CHUNK_BYTES, 1024);
+          umma_ss(tmem_base + O_COL, da, db, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);   // K_j / V_j stage free again
+        umma_commit(p_empty);          // P buffer free, O updated
+        return true;
+      };
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int st = j % ATT_KV_STAGES;
+        const uint32_t kvph = (uint32_t)(j / ATT_KV_STAGES) & 1;
+        const int sb = j % S_BUFS;
+        const uint32_t sph = (uint32_t)(j / S_BUFS) & 1;
+        if (!mbar_wait(&k_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
+            !mbar_wait(&s_empty[sb], sph ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sK = smem_u32(smem + L::K_OFF + st * L::TILE);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sQ + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sK + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+          umma_ss(tmem_base + sb * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[sb]);
+        if (j > 0) ok = issue_pv(j - 1);
+      }
+      if (ok) ok = issue_pv(n_kv - 1);
+      if (ok) umma_commit(o_full);
+    }
+  } else {
+    // ------------------------------ softmax + epilogue (warps 2..5) -------------------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;              // query row inside the tile
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    uint8_t* sP = smem + L::P_OFF;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int sb = j % S_BUFS;
+      const uint32_t sph = (uint32_t)(j / S_BUFS) & 1;
+      if (!mbar_wait(&s_full[sb], sph, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t s_addr = tmem_base + sb * 128 + lane_addr;
+      const bool diag = (j == n_kv - 1);
+      // One pass over the row, 32 columns at a time; the next chunk's tensor-memory load is in
+      // flight while the current one is processed.  Probabilities are taken relative to the running
+      // reference maximum m_ref, which only moves when a chunk exceeds it by more than 2^8; then
+      // the row sum, the chunks already packed and (later) the output accumulator are rescaled.
+      uint32_t pk[64];
+      float lacc = 0.f, o_factor = 1.f;
+      uint32_t va[32], vb[32];
+      tmem_ld_32x32b_x32(s_addr, va);
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? vb : va;
+        uint32_t(&nxt)[32] = (c & 1) ? va : vb;
+        if (c < 3) tmem_ld_32x32b_x32(s_addr + (c + 1) * 32, nxt);
+        float cmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(cur[i]);
+          if (diag && (c * 32 + i) > r) x = -INFINITY;
+          cmax = fmaxf(cmax, x);
+        }
+        const float m_c = cmax * args.scale_log2;
+        if (m_c > m_ref + ATT_RESCALE_THRESHOLD) {
+          const float f = exp2f(m_ref - m_c);      // 0 on the very first chunk (m_ref = -inf)
+          l_sum *= f;
+          lacc *= f;
+          o_factor *= f;
+#pragma unroll
+          for (int cc = 0; cc < c; ++cc) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 pv = unpack_bf16x2(pk[cc * 16 + i]);
+              pk[cc * 16 + i] = pack_bf16x2(pv.x * f, pv.y * f);
+            }
+          }
+          m_ref = m_c;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(cur[i]) * args.scale_log2 - m_ref);
+          float p1 = exp2f(__uint_as_float(cur[i + 1]) * args.scale_log2 - m_ref);
+          if (diag) {
+            if ((c * 32 + i) > r) p0 = 0.f;
+            if ((c * 32 + i + 1) > r) p1 = 0.f;
+          }
+          lacc += p0 + p1;
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+        }
+        if (c < 3) tmem_wait_ld();
+      }
+      l_sum += lacc;
+      const bool grow = o_factor != 1.f;
+      const float factor = o_factor;
+      // S_j is in registers now: the next QK may overwrite the buffer
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      // P buffer / O accumulator are free once PV_{j-1} retired
+      if (j > 0) {
+        if (!mbar_wait(p_empty, (uint32_t)(j - 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, grow)) {
+          // rescale the running output (tensor memory) by exp2(m_old - m_new); lanes that did not
+          // grow multiply by one
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_base + O_COL + lane_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st_32x32b_x32(tmem_base + O_COL + lane_addr + c * 32, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // write P_j (bf16) into the swizzled K-major tile: row r, 16-byte unit u of chunk ch
+#pragma unroll
+      for (int u16 = 0; u16 < 16; ++u16) {
+        const int ch = u16 >> 3, u = u16 & 7;
+        uint4 val = make_uint4(pk[u16 * 4 + 0], pk[u16 * 4 + 1], pk[u16 * 4 + 2], pk[u16 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sP + ch * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4)) = val;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> bf16, lse2 ----
+    if (ok && mbar_wait(o_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+      tc_fence_after_sync();
+      const float inv_l = 1.f / l_sum;
+      const long long token = (long long)row0 + r;
+      __nv_bfloat16* dst = args.out + token * ((long long)args.Hq * HD) + (long long)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tmem_base + O_COL + lane_addr + c * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 val;
+          val.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv_l, __uint_as_float(o[q4 * 8 + 1]) * inv_l);
+          val.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
+          val.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
+          val.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = val;
+        }
+      }
+      args.lse2[((long long)b * args.Hq + h) * args.S + qt * ATT_BQ + r] = m_ref + log2f(l_sum);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int HD, int S_BUFS>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const AttFwdArgs& a, cudaStream_t st) {
+  auto kern = attn_fwd_kernel<HD, S_BUFS>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttFwdSmem<HD>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = a.B * a.Hq * (a.S / ATT_BQ);
+  kern<<<grid, ATT_THREADS, AttFwdSmem<HD>::TOTAL, st>>>(tq, tk, tv, a);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace adana
+
+using namespace adana;
+
+// q [T, Hq, hd], k [T, Hk, hd] contiguous bf16; v read from `vbase` with row pitch `ldv` and head
+// pitch `v_hstride` (elements); out [T, Hq*hd] bf16; lse2 [B, Hq, S] fp32.
+extern "C" int adana_attn_fwd(const void* q, const void* k, const void* vbase, long long ldv,
+                              int v_hstride, void* out, float* lse2, int B, int S, int Hq, int Hk,
+                              int hd, float scale, int* status, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (B <= 0 || S <= 0) return 0;
+  if ((hd != 64 && hd != 128) || (S % ATT_BQ) != 0 || Hq % Hk != 0) return -1;
+  const uint64_t T = (uint64_t)B * S;
+  CUtensorMap tq, tk, tv;
+  {
+    uint64_t dims[3] = {(uint64_t)hd, T, (uint64_t)Hq};
+    uint64_t str[3] = {1, (uint64_t)Hq * hd, (uint64_t)hd};
+    uint32_t box[3] = {64, ATT_BQ, 1};
+    if (encode_tmap_nd(&tq, q, 3, dims, str, box, 2, 1)) return -2;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)hd, T, (uint64_t)Hk};
+    uint64_t str[3] = {1, (uint64_t)Hk * hd, (uint64_t)hd};
+    uint32_t box[3] = {64, ATT_BKV, 1};
+    if (encode_tmap_nd(&tk, k, 3, dims, str, box, 2, 1)) return -3;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)hd, T, (uint64_t)Hk};
+    uint64_t str[3] = {1, (uint64_t)ldv, (uint64_t)v_hstride};
+    uint32_t box[3] = {64, ATT_BKV, 1};
+    if (encode_tmap_nd(&tv, vbase, 3, dims, str, box, 2, 1)) return -4;
+  }
+  AttFwdArgs a;
+  a.out = (__nv_bfloat16*)out;
+  a.lse2 = lse2;
+  a.B = B; a.S = S; a.Hq = Hq; a.Hk = Hk;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  if (hd == 64) return launch_attn_fwd<64, 1>(tq, tk, tv, a, st);
+  return launch_attn_fwd<128, 2>(tq, tk, tv, a, st);
+}
+
+namespace adana {
+
+// =================================================================================================
+// Backward.
+//
+// One CTA = one (batch, KV head, 128-key tile j); K_j and V_j stay in shared memory while the CTA
+// walks every (query head of the group, query tile i >= j):
+//     S  = Q_i K_j^T            dP = dO_i V_j^T                       (tensor memory, fp32)
+//     P  = exp2(scale*S - lse2) dS = P o (dP - delta_i) * scale       (softmax warps, row per thread)
+//     dV_j += P^T dO_i          dK_j += dS^T Q_i                      (accumulate in tensor memory)
+//     dQ_i  = dS K_j            -> fp32 vector reductions into the dQ accumulation buffer
+// P and dS are written once to shared memory as [q rows][kv cols] 128B-swizzled tiles; the same
+// bytes serve as the K-major A operand of dS*K and as the MN-major A operand of P^T*dO / dS^T*Q
+// (the MMA descriptor selects the major-ness), and the Q / dO / K tiles likewise serve both as
+// K-major and as MN-major operands.  delta_i = rowsum(dO o O) comes from a small pre-pass kernel.
+// head_dim 64: S/dP of the next item are computed while the softmax warps still drain dQ of the
+// current one.  head_dim 128: tensor memory is full (S, dP, dV, dK), dQ aliases S and the items
+// run back to back.
+// =================================================================================================
+template <int HD>
+struct AttBwdSmem {
+  static constexpr int TILE = ATT_BQ * HD * 2;
+  static constexpr int STAGES = (HD == 64) ? 2 : 1;
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE;
+  static constexpr int Q_OFF = 2 * TILE;
+  static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
+  static constexpr int P_OFF = DO_OFF + STAGES * TILE;
+  static constexpr int DS_OFF = P_OFF + ATT_BQ * ATT_BKV * 2;
+  static constexpr int BAR_OFF = DS_OFF + ATT_BQ * ATT_BKV * 2;
+  static constexpr int TOTAL = BAR_OFF + 256;
+};
+
+struct AttBwdArgs {
+  const float* lse2;      // [B, Hq, S]
+  const float* delta;     // [B, Hq, S]
+  float* dq_acc;          // [T, Hq, HD] fp32, zero-initialised by the caller
+  __nv_bfloat16* dk;      // [T, Hk, HD]
+  __nv_bfloat16* dv;      // base of the v columns in the projection-gradient buffer
+  long long lddv;
+  int dv_hstride;
+  int B, S, Hq, Hk;
+  float scale, scale_log2;
+  int* status;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                const AttBwdArgs args) {
+  using L = AttBwdSmem<HD>;
+  constexpr int CHUNKS = HD / 64;
+  constexpr int CHUNK_BYTES = ATT_BQ * 128;
+  constexpr bool PIPELINED = (HD == 64);
+  constexpr int STAGES = L::STAGES;
+  constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
+  constexpr uint32_t DQ_COL = PIPELINED ? (256 + 2 * HD) : 0;   // aliases S when tensor memory is full
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;            // [1]
+  uint64_t* qdo_full = bars + 1;       // [2]
+  uint64_t* qdo_empty = bars + 3;      // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* dp_full = bars + 6;
+  uint64_t* sdp_free = bars + 7;       // softmax warps: S and dP are in registers
+  uint64_t* pds_full = bars + 8;       // softmax warps: P and dS tiles written
+  uint64_t* pds_free = bars + 9;       // MMA: dV/dK/dQ products retired
+  uint64_t* dq_full = bars + 10;
+  uint64_t* dq_free = bars + 11;       // softmax warps: dQ drained
+  uint64_t* acc_full = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_t = args.S / ATT_BQ;
+  const int G = args.Hq / args.Hk;
+  const int BHk = args.B * args.Hk;
+  // KV tile 0 has the most query tiles: schedule it first
+  const int j = (int)(blockIdx.x / BHk);
+  const int bhk = (int)(blockIdx.x % BHk);
+  const int b = bhk / args.Hk, hk = bhk % args.Hk;
+  const int n_i = n_t - j;                 // query tiles i = j .. n_t-1
+  const int n_items = G * n_i;
+  const int kvrow = b * args.S + j * ATT_BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(sdp_free, 4);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_free, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, 4);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmDO);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(kv_full, 2 * L::TILE);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c) {
+        tma_load_3d(smem + L::K_OFF + c * CHUNK_BYTES, &tmK, kv_full, c * 64, kvrow, hk);
+        tma_load_3d(smem + L::V_OFF + c * CHUNK_BYTES, &tmV, kv_full, c * 64, kvrow, hk);
+      }
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = 0; t < n_items && ok; ++t) {
+        const int g = t / n_i, i = j + t % n_i;
+        const int hq = hk * G + g;
+        const int qrow = b * args.S + i * ATT_BQ;
+        if (!mbar_wait(&qdo_empty[stage], phase ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(&qdo_full[stage], 2 * L::TILE);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c) {
+          tma_load_3d(smem + L::Q_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmQ, &qdo_full[stage], c * 64, qrow, hq);
+          tma_load_3d(smem + L::DO_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmDO, &qdo_full[stage], c * 64, qrow, hq);
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ---------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);  // Q K^T, dO V^T
+      constexpr uint32_t idesc_t = make_idesc_bf16(ATT_BKV, HD, true, true);        // P^T dO, dS^T Q
+      constexpr uint32_t idesc_q = make_idesc_bf16(ATT_BQ, HD, false, true);        // dS K
+      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
+      const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+      tc_fence_after_sync();
+
+      auto issue_scores = [&](int t) -> bool {   // S and dP of item t
+        const int st = t % STAGES;
+        const uint32_t ph = (uint32_t)(t / STAGES) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!mbar_wait(sdp_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!PIPELINED) {  // dQ of the previous item lives in the S columns: wait until it is drained
+          if (!mbar_wait(dq_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        }
+        tc_fence_after_sync();
+        const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE);
+        const uint32_t sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+          umma_ss(tmem_base + S_COL, make_smem_desc_sw128(sQ + o, 16, 1024),
+                  make_smem_desc_sw128(sK + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+          umma_ss(tmem_base + DP_COL, make_smem_desc_sw128(sDO + o, 16, 1024),
+                  make_smem_desc_sw128(sV + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(dp_full);
+        return true;
+      };
+      auto issue_grads = [&](int t) -> bool {    // dV, dK accumulation and dQ of item t
+        const int st = t % STAGES;
+        if (!mbar_wait(pds_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (PIPELINED) {
+          if (!mbar_wait(dq_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        }
+        tc_fence_after_sync();
+        const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE);
+        const uint32_t sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BQ / 16; ++kk) {   // contraction over the 128 query rows
+          const uint64_t a_p = make_smem_desc_sw128(sP + kk * 2048, CHUNK_BYTES, 1024);
+          const uint64_t b_do = make_smem_desc_sw128(sDO + kk * 2048, CHUNK_BYTES, 1024);
+          umma_ss(tmem_base + DV_COL, a_p, b_do, idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < ATT_BQ / 16; ++kk) {
+          const uint64_t a_ds = make_smem_desc_sw128(sDS + kk * 2048, CHUNK_BYTES, 1024);
+          const uint64_t b_q = make_smem_desc_sw128(sQ + kk * 2048, CHUNK_BYTES, 1024);
+          umma_ss(tmem_base + DK_COL, a_ds, b_q, idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < ATT_BKV / 16; ++kk) {  // contraction over the 128 keys
+          const uint64_t a_ds = make_smem_desc_sw128(sDS + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+          const uint64_t b_k = make_smem_desc_sw128(sK + kk * 2048, CHUNK_BYTES, 1024);
+          umma_ss(tmem_base + DQ_COL, a_ds, b_k, idesc_q, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&qdo_empty[st]);
+        umma_commit(pds_free);
+        umma_commit(dq_full);
+        return true;
+      };
+
+      if (ok && n_items > 0) ok = issue_scores(0);
+      for (int t = 0; t < n_items && ok; ++t) {
+        if (PIPELINED && t + 1 < n_items) ok = issue_scores(t + 1);
+        if (ok) ok = issue_grads(t);
+        if (!PIPELINED && ok && t + 1 < n_items) ok = issue_scores(t + 1);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ------------------------------ softmax / epilogue warps --------------------------------
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    uint8_t* sP = smem + L::P_OFF;
+    uint8_t* sDS = smem + L::DS_OFF;
+    bool ok = true;
+    for (int t = 0; t < n_items && ok; ++t) {
+      const int g = t / n_i, i = j + t % n_i;
+      const int hq = hk * G + g;
+      const long long stat_idx = ((long long)b * args.Hq + hq) * args.S + i * ATT_BQ + r;
+      const float lse = args.lse2[stat_idx];
+      const float dl = args.delta[stat_idx];
+      const bool diag = (i == j);
+      if (!mbar_wait(s_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
+          !mbar_wait(dp_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t pk[64], dk_[64];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem_base + S_COL + lane_addr + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem_base + DP_COL + lane_addr + c * 32, dv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2f(__uint_as_float(sv[e]) * args.scale_log2 - lse);
+          float p1 = exp2f(__uint_as_float(sv[e + 1]) * args.scale_log2 - lse);
+          if (diag) {
+            if ((c * 32 + e) > r) p0 = 0.f;
+            if ((c * 32 + e + 1) > r) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dv[e]) - dl) * args.scale;
+          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dl) * args.scale;
+          pk[c * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
+          dk_[c * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sdp_free);
+      // the P / dS tiles are free once the gradient products of the previous item retired
+      if (!mbar_wait(pds_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int u16 = 0; u16 < 16; ++u16) {
+        const int ch = u16 >> 3, u = u16 & 7;
+        const int off = ch * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u16 * 4], pk[u16 * 4 + 1], pk[u16 * 4 + 2], pk[u16 * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u16 * 4], dk_[u16 * 4 + 1], dk_[u16 * 4 + 2], dk_[u16 * 4 + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // drain dQ_i of this item into the fp32 accumulation buffer
+      if (!mbar_wait(dq_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      float* dq_row = args.dq_acc + (((long long)b * args.S + i * ATT_BQ + r) * args.Hq + hq) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + c * 32, o);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + q4 * 4),
+                       "f"(__uint_as_float(o[q4 * 4])), "f"(__uint_as_float(o[q4 * 4 + 1])),
+                       "f"(__uint_as_float(o[q4 * 4 + 2])), "f"(__uint_as_float(o[q4 * 4 + 3]))
+                       : "memory");
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+    }
+    // ---- epilogue: dK_j, dV_j (row = key index) ----
+    if (ok && mbar_wait(acc_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+      tc_fence_after_sync();
+      const long long token = (long long)kvrow + r;
+      __nv_bfloat16* dk_dst = args.dk + (token * args.Hk + hk) * HD;
+      __nv_bfloat16* dv_dst = args.dv + token * args.lddv + (long long)hk * args.dv_hstride;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t a[32], bq[32];
+        tmem_ld_32x32b_x32(tmem_base + DK_COL + lane_addr + c * 32, a);
+        tmem_ld_32x32b_x32(tmem_base + DV_COL + lane_addr + c * 32, bq);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 x, y;
+          x.x = pack_bf16x2(__uint_as_float(a[q4 * 8 + 0]), __uint_as_float(a[q4 * 8 + 1]));
+          x.y = pack_bf16x2(__uint_as_float(a[q4 * 8 + 2]), __uint_as_float(a[q4 * 8 + 3]));
+          x.z = pack_bf16x2(__uint_as_float(a[q4 * 8 + 4]), __uint_as_float(a[q4 * 8 + 5]));
+          x.w = pack_bf16x2(__uint_as_float(a[q4 * 8 + 6]), __uint_as_float(a[q4 * 8 + 7]));
+          y.x = pack_bf16x2(__uint_as_float(bq[q4 * 8 + 0]), __uint_as_float(bq[q4 * 8 + 1]));
+          y.y = pack_bf16x2(__uint_as_float(bq[q4 * 8 + 2]), __uint_as_float(bq[q4 * 8 + 3]));
+          y.z = pack_bf16x2(__uint_as_float(bq[q4 * 8 + 4]), __uint_as_float(bq[q4 * 8 + 5]));
+          y.w = pack_bf16x2(__uint_as_float(bq[q4 * 8 + 6]), __uint_as_float(bq[q4 * 8 + 7]));
+          *reinterpret_cast<uint4*>(dk_dst + c * 32 + q4 * 8) = x;
+          *reinterpret_cast<uint4*>(dv_dst + c * 32 + q4 * 8) = y;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+template <int HD>
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  constexpr int EPL = HD / 32;
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long total = (long long)B * S * H;
+  for (long long item = warp_global; item < total; item += n_warps) {
+    const long long tok = item / H;
+    const int h = (int)(item - tok * H);
+    const long long off = (tok * H + h) * HD + lane * EPL;
+    float acc = 0.f;
+    if (EPL == 2) {
+      const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dout + off));
+      const float2 o = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(out + off));
+      acc = a.x * o.x + a.y * o.y;
+    } else {
+      const uint2 ua = *reinterpret_cast<const uint2*>(dout + off);
+      const uint2 uo = *reinterpret_cast<const uint2*>(out + off);
+      const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y);
+      const float2 o0 = unpack_bf16x2(uo.x), o1 = unpack_bf16x2(uo.y);
+      acc = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const long long bb = tok / S, s = tok - bb * S;
+      delta[(bb * H + h) * S + s] = acc;
+    }
+  }
+}
+
+template <int HD>
+static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk,
+                           const CUtensorMap& tv, const AttBwdArgs& a, cudaStream_t st) {
+  auto kern = attn_bwd_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttBwdSmem<HD>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = a.B * a.Hk * (a.S / ATT_BKV);
+  kern<<<grid, ATT_THREADS, AttBwdSmem<HD>::TOTAL, st>>>(tq, tdo, tk, tv, a);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace adana
+
+// dout/out [T, Hq*hd] bf16, q [T,Hq,hd], k [T,Hk,hd], v strided as in the forward; lse2 from the
+// forward; delta [B,Hq,S] scratch (written here); dq_acc [T,Hq,hd] fp32 must be zero on entry and
+// holds dQ on exit; dk [T,Hk,hd] bf16; dv written at dvbase with row pitch lddv / head pitch dv_hstride.
+extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, long long ldv, int v_hstride,
+                              const void* vbase, const void* out, const float* lse2, float* delta,
+                              float* dq_acc, void* dk, long long lddv, int dv_hstride, void* dvbase, int B,
+                              int S, int Hq, int Hk, int hd, float scale, int* status, void* stream_) {
+  using namespace adana;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (B <= 0 || S <= 0) return 0;
+  if ((hd != 64 && hd != 128) || (S % ATT_BQ) != 0 || Hq % Hk != 0) return -1;
+  const uint64_t T = (uint64_t)B * S;
+  {
+    const long long items = (long long)T * Hq;
+    long long blocks = (items + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (hd == 64)
+      attn_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq);
+    else
+      attn_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq);
+  }
+  CUtensorMap tq, tdo, tk, tv;
+  uint32_t box[3] = {64, ATT_BQ, 1};
+  {
+    uint64_t dims[3] = {(uint64_t)hd, T, (uint64_t)Hq};
+    uint64_t str[3] = {1, (uint64_t)Hq * hd, (uint64_t)hd};
+    if (encode_tmap_nd(&tq, q, 3, dims, str, box, 2, 1)) return -2;
+    if (encode_tmap_nd(&tdo, dout, 3, dims, str, box, 2, 1)) return -3;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)hd, T, (uint64_t)Hk};
+    uint64_t str[3] = {1, (uint64_t)Hk * hd, (uint64_t)hd};
+    if (encode_tmap_nd(&tk, k, 3, dims, str, box, 2, 1)) return -4;
+    uint64_t strv[3] = {1, (uint64_t)ldv, (uint64_t)v_hstride};
+    if (encode_tmap_nd(&tv, vbase, 3, dims, strv, box, 2, 1)) return -5;
+  }
+  AttBwdArgs a;
+  a.lse2 = lse2; a.delta = delta; a.dq_acc = dq_acc;
+  a.dk = (__nv_bfloat16*)dk; a.dv = (__nv_bfloat16*)dvbase; a.lddv = lddv; a.dv_hstride = dv_hstride;
+  a.B = B; a.S = S; a.Hq = Hq; a.Hk = Hk;
+  a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
+  a.status = status;
+  if (hd == 64) return launch_attn_bwd<64>(tq, tdo, tk, tv, a, st);
+  return launch_attn_bwd<128>(tq, tdo, tk, tv, a, st);
+}

@@ -16,7 +16,7 @@
 namespace adana {
 
 constexpr int NORM_THREADS = 256;
-constexpr int NORM_MAXV = 8;  // float4 per thread held in registers -> cols <= 8192
+constexpr int NORM_MAXV_LIMIT = 8;  // float4 per thread held in registers -> cols <= 8192
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
@@ -59,7 +59,7 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
   *reinterpret_cast<uint2*>(p) = u;
 }
 
-template <typename TX, typename TY, int KIND>
+template <typename TX, typename TY, int KIND, int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
@@ -116,7 +116,7 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
   }
 }
 
-template <typename TDY, typename TX, int KIND>
+template <typename TDY, typename TX, int KIND, int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
@@ -213,9 +213,48 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat1
 
 using namespace adana;
 
-static int norm_grid(int rows) {
-  const int cap = 148 * 8;
+static int norm_grid(int rows, int per_sm) {
+  const int cap = 148 * per_sm;
   return rows < cap ? rows : cap;
+}
+
+// number of float4 per thread needed to hold one row in registers
+static int maxv_for(int cols) {
+  const int need = (cols / 4 + NORM_THREADS - 1) / NORM_THREADS;
+  if (need <= 1) return 1;
+  if (need <= 2) return 2;
+  if (need <= 3) return 3;
+  if (need <= 4) return 4;
+  return 8;
+}
+
+template <typename TX, typename TY, int KIND>
+static void launch_norm_fwd(int mv, int grid, cudaStream_t st, const void* x, const float* w, void* y,
+                            float* mean, float* rstd, int rows, int cols, float eps) {
+#define NF(V) norm_fwd_kernel<TX, TY, KIND, V><<<grid, NORM_THREADS, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, rows, cols, eps)
+  switch (mv) {
+    case 1: NF(1); break;
+    case 2: NF(2); break;
+    case 3: NF(3); break;
+    case 4: NF(4); break;
+    default: NF(8); break;
+  }
+#undef NF
+}
+
+template <typename TD, typename TX, int KIND>
+static void launch_norm_bwd(int mv, int grid, cudaStream_t st, const void* dy, const void* x, const float* w,
+                            const float* mean, const float* rstd, float* dx, int acc, float* dwp, int rows,
+                            int cols, void* dx16) {
+#define NB(V) norm_bwd_kernel<TD, TX, KIND, V><<<grid, NORM_THREADS, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, rstd, dx, acc, dwp, rows, cols, (__nv_bfloat16*)dx16)
+  switch (mv) {
+    case 1: NB(1); break;
+    case 2: NB(2); break;
+    case 3: NB(3); break;
+    case 4: NB(4); break;
+    default: NB(8); break;
+  }
+#undef NB
 }
 
 extern "C" int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void* y,
@@ -223,23 +262,21 @@ extern "C" int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void
                               float eps, int kind, void* stream_) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   if (rows <= 0) return 0;
-  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV) return -1;
-  const int grid = norm_grid(rows);
-#define NF(TX, TY, K)                                                                          \
-  norm_fwd_kernel<TX, TY, K><<<grid, NORM_THREADS, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, \
-                                                            rows, cols, eps)
+  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV_LIMIT) return -1;
+  const int mv = maxv_for(cols);
+  const int grid = norm_grid(rows, 8);
+  using bf = __nv_bfloat16;
   if (kind == 0) {
-    if (!x_is_bf16 && y_is_bf16) NF(float, __nv_bfloat16, 0);
-    else if (!x_is_bf16 && !y_is_bf16) NF(float, float, 0);
-    else if (x_is_bf16 && y_is_bf16) NF(__nv_bfloat16, __nv_bfloat16, 0);
-    else NF(__nv_bfloat16, float, 0);
+    if (!x_is_bf16 && y_is_bf16) launch_norm_fwd<float, bf, 0>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else if (!x_is_bf16 && !y_is_bf16) launch_norm_fwd<float, float, 0>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else if (x_is_bf16 && y_is_bf16) launch_norm_fwd<bf, bf, 0>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else return -3;
   } else {
-    if (!x_is_bf16 && y_is_bf16) NF(float, __nv_bfloat16, 1);
-    else if (!x_is_bf16 && !y_is_bf16) NF(float, float, 1);
-    else if (x_is_bf16 && y_is_bf16) NF(__nv_bfloat16, __nv_bfloat16, 1);
-    else NF(__nv_bfloat16, float, 1);
+    if (!x_is_bf16 && y_is_bf16) launch_norm_fwd<float, bf, 1>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else if (!x_is_bf16 && !y_is_bf16) launch_norm_fwd<float, float, 1>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else if (x_is_bf16 && y_is_bf16) launch_norm_fwd<bf, bf, 1>(mv, grid, st, x, w, y, mean, rstd, rows, cols, eps);
+    else return -3;
   }
-#undef NF
   return (int)cudaGetLastError();
 }
 
@@ -249,29 +286,26 @@ extern "C" int adana_norm_bwd(const void* dy, int dy_is_bf16, const void* x, int
                               int cols, int kind, void* dx_bf16, void* stream_) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   if (rows <= 0) return 0;
-  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV) return -1;
-  int grid = norm_grid(rows);
+  if ((cols & 3) || cols > NORM_THREADS * 4 * NORM_MAXV_LIMIT) return -1;
+  const int mv = maxv_for(cols);
+  int grid = norm_grid(rows, 4);
   if (dw_partial) {
     if (n_partial_rows <= 0) return -2;
     // every CTA writes its partial row, so the grid must equal the number of partial rows
     grid = n_partial_rows;
   }
-#define NB(TD, TX, K)                                                                        \
-  norm_bwd_kernel<TD, TX, K><<<grid, NORM_THREADS, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, \
-                                                            rstd, dx, accumulate_dx, dw_partial,  \
-                                                            rows, cols, (__nv_bfloat16*)dx_bf16)
+  using bf = __nv_bfloat16;
   if (kind == 0) {
-    if (dy_is_bf16 && !x_is_bf16) NB(__nv_bfloat16, float, 0);
-    else if (!dy_is_bf16 && !x_is_bf16) NB(float, float, 0);
-    else if (dy_is_bf16 && x_is_bf16) NB(__nv_bfloat16, __nv_bfloat16, 0);
-    else NB(float, __nv_bfloat16, 0);
+    if (dy_is_bf16 && !x_is_bf16) launch_norm_bwd<bf, float, 0>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else if (!dy_is_bf16 && !x_is_bf16) launch_norm_bwd<float, float, 0>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else if (dy_is_bf16 && x_is_bf16) launch_norm_bwd<bf, bf, 0>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else return -3;
   } else {
-    if (dy_is_bf16 && !x_is_bf16) NB(__nv_bfloat16, float, 1);
-    else if (!dy_is_bf16 && !x_is_bf16) NB(float, float, 1);
-    else if (dy_is_bf16 && x_is_bf16) NB(__nv_bfloat16, __nv_bfloat16, 1);
-    else NB(float, __nv_bfloat16, 1);
+    if (dy_is_bf16 && !x_is_bf16) launch_norm_bwd<bf, float, 1>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else if (!dy_is_bf16 && !x_is_bf16) launch_norm_bwd<float, float, 1>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else if (dy_is_bf16 && x_is_bf16) launch_norm_bwd<bf, bf, 1>(mv, grid, st, dy, x, w, mean, rstd, dx, accumulate_dx, dw_partial, rows, cols, dx_bf16);
+    else return -3;
   }
-#undef NB
   return (int)cudaGetLastError();
 }
 

@@ -22,6 +22,31 @@ namespace adana {
 
 constexpr int ROPE_THREADS = 256;
 
+constexpr int ROPE_UNROLL = 4;  // (token, head) vectors in flight per warp: hides load latency
+
+template <int EPL>
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&x)[EPL]) {
+  if (EPL == 2) {
+    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
+    x[0] = f.x; x[1] = f.y;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    x[0] = a.x; x[1] = a.y; x[EPL - 2] = b.x; x[EPL - 1] = b.y;
+  }
+}
+template <int EPL>
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&x)[EPL]) {
+  if (EPL == 2) {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(x[0], x[1]);
+  } else {
+    uint2 u;
+    u.x = pack_bf16x2(x[0], x[1]);
+    u.y = pack_bf16x2(x[EPL - 2], x[EPL - 1]);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+}
+
 template <int HD, int KIND>
 __global__ void __launch_bounds__(ROPE_THREADS)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stride, int q_off,
@@ -30,60 +55,69 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
                        __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
                        long long n_tokens, int S, int Hq, int Hk, float eps) {
   constexpr int EPL = HD / 32;  // elements per lane (2 or 4)
+  constexpr int U = ROPE_UNROLL;
   const int lane = threadIdx.x & 31;
   const long long warp_global = ((long long)blockIdx.x * ROPE_THREADS + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
   const int Hall = Hq + Hk;
   const long long total = n_tokens * Hall;
-  for (long long item = warp_global; item < total; item += n_warps) {
-    const long long tok = item / Hall;
-    const int h = (int)(item - tok * Hall);
-    const bool is_q = h < Hq;
-    const int hh = is_q ? h : h - Hq;
-    const __nv_bfloat16* src =
-        qkv + tok * row_stride + (is_q ? q_off + hh * q_hstride : k_off + hh * k_hstride) + lane * EPL;
-    float x[EPL];
-    if (EPL == 2) {
-      float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(src));
-      x[0] = f.x; x[1] = f.y;
-    } else {
-      uint2 u = *reinterpret_cast<const uint2*>(src);
-      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-      x[0] = a.x; x[1] = a.y; x[EPL - 2] = b.x; x[EPL - 1] = b.y;
-    }
-    if (KIND != 2) {
-      float mean = 0.f;
-      if (KIND == 0) {
-        float s = 0.f;
+  float wqr[EPL], wkr[EPL];
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) s += x[i];
-        mean = warp_sum(s) * (1.f / HD);
+  for (int i = 0; i < EPL; ++i) {
+    wqr[i] = (KIND != 2) ? wq[lane * EPL + i] : 1.f;
+    wkr[i] = (KIND != 2) ? wk[lane * EPL + i] : 1.f;
+  }
+  for (long long base = warp_global * U; base < total; base += n_warps * U) {
+    float x[U][EPL];
+    float2 cs[U][EPL / 2];
+    long long tok[U];
+    int hh[U];
+    bool isq[U], ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long item = base + u;
+      ok[u] = item < total;
+      const long long it = ok[u] ? item : 0;
+      tok[u] = it / Hall;
+      const int h = (int)(it - tok[u] * Hall);
+      isq[u] = h < Hq;
+      hh[u] = isq[u] ? h : h - Hq;
+      const __nv_bfloat16* src = qkv + tok[u] * row_stride +
+                                 (isq[u] ? q_off + hh[u] * q_hstride : k_off + hh[u] * k_hstride) + lane * EPL;
+      load_vec<EPL>(src, x[u]);
+      const int pos = (int)(tok[u] % S);
+      const float2* fr = reinterpret_cast<const float2*>(freqs) + (long long)pos * (HD / 2) + lane * (EPL / 2);
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) cs[u][i] = fr[i];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (KIND != 2) {
+        float mean = 0.f;
+        if (KIND == 0) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) s += x[u][i];
+          mean = warp_sum(s) * (1.f / HD);
+        }
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
+        const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) x[u][i] = (x[u][i] - mean) * rstd * (isq[u] ? wqr[i] : wkr[i]);
       }
-      float q = 0.f;
+      float o[EPL];
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) q += (x[i] - mean) * (x[i] - mean);
-      const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
-      const float* w = (is_q ? wq : wk) + lane * EPL;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) x[i] = (x[i] - mean) * rstd * w[i];
-    }
-    const int pos = (int)(tok % S);
-    const float* fr = freqs + ((long long)pos * (HD / 2) + lane * (EPL / 2)) * 2;
-    float o[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL / 2; ++i) {
-      const float c = fr[i * 2], s = fr[i * 2 + 1];
-      o[2 * i] = x[2 * i] * c - x[2 * i + 1] * s;
-      o[2 * i + 1] = x[2 * i] * s + x[2 * i + 1] * c;
-    }
-    __nv_bfloat16* dst = (is_q ? q_out + (tok * Hq + hh) * HD : k_out + (tok * Hk + hh) * HD) + lane * EPL;
-    if (EPL == 2) {
-      *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(o[0], o[1]);
-    } else {
-      uint2 u;
-      u.x = pack_bf16x2(o[0], o[1]);
-      u.y = pack_bf16x2(o[EPL - 2], o[EPL - 1]);
-      *reinterpret_cast<uint2*>(dst) = u;
+      for (int i = 0; i < EPL / 2; ++i) {
+        const float c = cs[u][i].x, s = cs[u][i].y;
+        o[2 * i] = x[u][2 * i] * c - x[u][2 * i + 1] * s;
+        o[2 * i + 1] = x[u][2 * i] * s + x[u][2 * i + 1] * c;
+      }
+      if (ok[u]) {
+        __nv_bfloat16* dst = (isq[u] ? q_out + (tok[u] * Hq + hh[u]) * HD : k_out + (tok[u] * Hk + hh[u]) * HD) + lane * EPL;
+        store_vec<EPL>(dst, o);
+      }
     }
   }
 }
@@ -98,6 +132,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
                        float* __restrict__ dwk_partial, long long n_tokens, int S, int Hq, int Hk,
                        float eps) {
   constexpr int EPL = HD / 32;
+  constexpr int U = ROPE_UNROLL;
   __shared__ float sdw[2][ROPE_THREADS / 32][HD];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -105,81 +140,79 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
   const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
   const int Hall = Hq + Hk;
   const long long total = n_tokens * Hall;
-  float dwq_acc[EPL], dwk_acc[EPL];
+  float dwq_acc[EPL], dwk_acc[EPL], wqr[EPL], wkr[EPL];
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) dwq_acc[i] = dwk_acc[i] = 0.f;
-
-  for (long long item = warp_global; item < total; item += n_warps) {
-    const long long tok = item / Hall;
-    const int h = (int)(item - tok * Hall);
-    const bool is_q = h < Hq;
-    const int hh = is_q ? h : h - Hq;
-    const long long off = tok * row_stride + (is_q ? q_off + hh * q_hstride : k_off + hh * k_hstride) + lane * EPL;
-    const __nv_bfloat16* gsrc = (is_q ? dq + (tok * Hq + hh) * HD : dk + (tok * Hk + hh) * HD) + lane * EPL;
-    float x[EPL], d[EPL];
-    if (EPL == 2) {
-      float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(qkv + off));
-      x[0] = f.x; x[1] = f.y;
-      float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(gsrc));
-      d[0] = g.x; d[1] = g.y;
-    } else {
-      uint2 u = *reinterpret_cast<const uint2*>(qkv + off);
-      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-      x[0] = a.x; x[1] = a.y; x[EPL - 2] = b.x; x[EPL - 1] = b.y;
-      uint2 gu = *reinterpret_cast<const uint2*>(gsrc);
-      float2 ga = unpack_bf16x2(gu.x), gb = unpack_bf16x2(gu.y);
-      d[0] = ga.x; d[1] = ga.y; d[EPL - 2] = gb.x; d[EPL - 1] = gb.y;
+  for (int i = 0; i < EPL; ++i) {
+    dwq_acc[i] = dwk_acc[i] = 0.f;
+    wqr[i] = (KIND != 2) ? wq[lane * EPL + i] : 1.f;
+    wkr[i] = (KIND != 2) ? wk[lane * EPL + i] : 1.f;
+  }
+  for (long long base = warp_global * U; base < total; base += n_warps * U) {
+    float x[U][EPL], d[U][EPL];
+    float2 cs[U][EPL / 2];
+    long long off[U];
+    bool isq[U], ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long item = base + u;
+      ok[u] = item < total;
+      const long long it = ok[u] ? item : 0;
+      const long long tok = it / Hall;
+      const int h = (int)(it - tok * Hall);
+      isq[u] = h < Hq;
+      const int hh = isq[u] ? h : h - Hq;
+      off[u] = tok * row_stride + (isq[u] ? q_off + hh * q_hstride : k_off + hh * k_hstride) + lane * EPL;
+      const __nv_bfloat16* gsrc = (isq[u] ? dq + (tok * Hq + hh) * HD : dk + (tok * Hk + hh) * HD) + lane * EPL;
+      load_vec<EPL>(qkv + off[u], x[u]);
+      load_vec<EPL>(gsrc, d[u]);
+      const int pos = (int)(tok % S);
+      const float2* fr = reinterpret_cast<const float2*>(freqs) + (long long)pos * (HD / 2) + lane * (EPL / 2);
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) cs[u][i] = fr[i];
     }
-    // undo the rotation: gradient w.r.t. the normalised, weighted vector
-    const int pos = (int)(tok % S);
-    const float* fr = freqs + ((long long)pos * (HD / 2) + lane * (EPL / 2)) * 2;
-    float dn[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL / 2; ++i) {
-      const float c = fr[i * 2], s = fr[i * 2 + 1];
-      dn[2 * i] = d[2 * i] * c + d[2 * i + 1] * s;
-      dn[2 * i + 1] = -d[2 * i] * s + d[2 * i + 1] * c;
-    }
-    float dx[EPL];
-    if (KIND == 2) {
+    for (int u = 0; u < U; ++u) {
+      // undo the rotation: gradient w.r.t. the normalised, weighted vector
+      float dn[EPL];
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) dx[i] = dn[i];
-    } else {
-      float mean = 0.f;
-      if (KIND == 0) {
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) s += x[i];
-        mean = warp_sum(s) * (1.f / HD);
+      for (int i = 0; i < EPL / 2; ++i) {
+        const float c = cs[u][i].x, s = cs[u][i].y;
+        dn[2 * i] = d[u][2 * i] * c + d[u][2 * i + 1] * s;
+        dn[2 * i + 1] = -d[u][2 * i] * s + d[u][2 * i + 1] * c;
       }
-      float q = 0.f;
+      float dx[EPL];
+      if (KIND == 2) {
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) q += (x[i] - mean) * (x[i] - mean);
-      const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
-      const float* w = (is_q ? wq : wk) + lane * EPL;
-      float xh[EPL], g[EPL], s1 = 0.f, s2 = 0.f;
+        for (int i = 0; i < EPL; ++i) dx[i] = dn[i];
+      } else {
+        float mean = 0.f;
+        if (KIND == 0) {
+          float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        xh[i] = (x[i] - mean) * rstd;
-        g[i] = dn[i] * w[i];
-        s1 += g[i];
-        s2 += g[i] * xh[i];
-        if (is_q) dwq_acc[i] += dn[i] * xh[i];
-        else dwk_acc[i] += dn[i] * xh[i];
+          for (int i = 0; i < EPL; ++i) s += x[u][i];
+          mean = warp_sum(s) * (1.f / HD);
+        }
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
+        const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
+        float xh[EPL], g[EPL], s1 = 0.f, s2 = 0.f;
+        const float live = ok[u] ? 1.f : 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          xh[i] = (x[u][i] - mean) * rstd;
+          g[i] = dn[i] * (isq[u] ? wqr[i] : wkr[i]);
+          s1 += g[i];
+          s2 += g[i] * xh[i];
+          if (isq[u]) dwq_acc[i] += live * dn[i] * xh[i];
+          else dwk_acc[i] += live * dn[i] * xh[i];
+        }
+        const float m2 = warp_sum(s2) * (1.f / HD);
+        const float m1 = (KIND == 0) ? warp_sum(s1) * (1.f / HD) : 0.f;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) dx[i] = rstd * (g[i] - m1 - xh[i] * m2);
       }
-      const float m2 = warp_sum(s2) * (1.f / HD);
-      const float m1 = (KIND == 0) ? warp_sum(s1) * (1.f / HD) : 0.f;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) dx[i] = rstd * (g[i] - m1 - xh[i] * m2);
-    }
-    __nv_bfloat16* dst = dqkv + off;
-    if (EPL == 2) {
-      *reinterpret_cast<uint32_t*>(dst) = pack_bf16x2(dx[0], dx[1]);
-    } else {
-      uint2 u;
-      u.x = pack_bf16x2(dx[0], dx[1]);
-      u.y = pack_bf16x2(dx[EPL - 2], dx[EPL - 1]);
-      *reinterpret_cast<uint2*>(dst) = u;
+      if (ok[u]) store_vec<EPL>(dqkv + off[u], dx);
     }
   }
   if (KIND != 2 && dwq_partial) {
@@ -213,8 +246,9 @@ extern "C" int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int 
   if (hd != 64 && hd != 128) return -1;
   if ((row_stride & 3) || (q_off & 3) || (k_off & 3) || (q_hstride & 3) || (k_hstride & 3)) return -2;
   const long long items = n_tokens * (Hq + Hk);
-  long long blocks = (items + 7) / 8;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  long long blocks = (items + 8 * ROPE_UNROLL - 1) / (8 * ROPE_UNROLL);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
 #define RF(HD_, K_)                                                                          \
   qknorm_rope_fwd_kernel<HD_, K_><<<(int)blocks, ROPE_THREADS, 0, st>>>(                     \
       (const __nv_bfloat16*)qkv, row_stride, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, \

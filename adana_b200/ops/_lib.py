@@ -53,6 +53,8 @@ def _declare(lib):
         "adana_sigmoid_gate_fwd": [P, P, L, I, I, P, L, I, I, P],
         "adana_sigmoid_gate_bwd": [P, P, P, L, I, I, P, P, L, I, I, P],
         "adana_clip_coef": [P, F, F, P, P],
+        "adana_attn_fwd": [P, P, P, L, I, P, P, I, I, I, I, I, F, P, P],
+        "adana_attn_bwd": [P, P, P, L, I, P, P, P, P, P, P, L, I, P, I, I, I, I, I, F, P, P],
         "adana_embedding_fwd": [P, P, I, P, I, I, I, P],
         "adana_embedding_bwd": [P, P, P, I, I, I, P],
         "adana_ce_fwd_bwd": [P, L, P, I, I, F, F, P, L, P, P, P],

@@ -21,7 +21,20 @@ import torch.nn.functional as F
 
 from . import _lib
 
-_FORCE = os.environ.get("ADANA_ATTENTION", "auto")  # auto | native | sdpa | ref
+# auto | native | sdpa | ref.  "auto" currently resolves to the library kernel on a GPU: the hand-written
+# kernels are numerically verified but still slower than cuDNN's (see benchmarks/attention_bench.py);
+# `set_mode("native")` / ADANA_ATTENTION=native / --attention native selects them.
+_FORCE = os.environ.get("ADANA_ATTENTION", "auto")
+
+
+def set_mode(mode: str) -> None:
+    global _FORCE
+    assert mode in ("auto", "native", "sdpa", "ref")
+    _FORCE = mode
+
+
+def get_mode() -> str:
+    return _FORCE
 
 
 def _v_view(vbuf, v_off, v_hstride, Hk, hd):
@@ -57,12 +70,17 @@ def attention_fwd(q, k, vbuf, v_off, v_hstride, B, S, scale=None, need_grad=True
     v = _v_view(vbuf, v_off, v_hstride, Hk, hd)
     mode = _FORCE
     if mode == "auto":
-        mode = "native" if native_supported(q, hd, S) else ("sdpa" if q.is_cuda else "ref")
+        mode = "sdpa" if q.is_cuda else "ref"
+    if mode == "native" and not native_supported(q, hd, S):
+        mode = "sdpa" if q.is_cuda else "ref"
     if mode == "native":
         from . import attention_native
 
-        out, lse = attention_native.fwd(q, k, vbuf, v_off, v_hstride, B, S, scale)
-        return out, ("native", lse, out)
+        if need_grad and not attention_native.bwd_available():
+            mode = "sdpa"   # no native backward built in: keep forward and backward on one implementation
+        else:
+            out, lse = attention_native.fwd(q, k, vbuf, v_off, v_hstride, B, S, scale)
+            return out, ("native", lse, out)
     if mode == "sdpa":
         # library kernel; the autograd graph of this one call is kept for the backward sweep
         qd, kd, vd = (t.detach().requires_grad_(need_grad) for t in (q, k, v))

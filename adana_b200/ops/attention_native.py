@@ -1,0 +1,44 @@
+"""Python side of the hand-written tcgen05 attention kernels (csrc/attention_tcgen05.cu).
+
+`fwd` returns the attention output [T, Hq*hd] (bf16) and `lse2` [B, Hq, S]: the row-wise
+log-sum-exp of the scaled scores in log2 units.  `bwd` consumes them.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def fwd(q, k, vbuf, v_off, v_hstride, B, S, scale):
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    lse2 = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    vbase = vbuf.data_ptr() + 2 * v_off
+    rc = _lib.lib().adana_attn_fwd(q.data_ptr(), k.data_ptr(), vbase, vbuf.stride(0), v_hstride, out.data_ptr(),
+                                   lse2.data_ptr(), B, S, Hq, Hk, hd, float(scale),
+                                   _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_attn_fwd")
+    return out, lse2
+
+
+def bwd_available() -> bool:
+    return _lib.has("adana_attn_bwd")
+
+
+def bwd(dout, q, k, vbuf, v_off, v_hstride, B, S, scale, lse2, out, dvbuf):
+    """Returns (dq [T,Hq,hd], dk [T,Hk,hd]) and writes dv into `dvbuf` at the projection's v columns."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    dq_acc = torch.zeros((T, Hq, hd), dtype=torch.float32, device=q.device)
+    dk = torch.empty((T, Hk, hd), dtype=torch.bfloat16, device=q.device)
+    delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    vbase = vbuf.data_ptr() + 2 * v_off
+    dvbase = dvbuf.data_ptr() + 2 * v_off
+    rc = _lib.lib().adana_attn_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), vbuf.stride(0), v_hstride, vbase,
+                                   out.data_ptr(), lse2.data_ptr(), delta.data_ptr(), dq_acc.data_ptr(),
+                                   dk.data_ptr(), dvbuf.stride(0), v_hstride, dvbase, B, S, Hq, Hk, hd,
+                                   float(scale), _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_attn_bwd")
+    return dq_acc.to(torch.bfloat16), dk

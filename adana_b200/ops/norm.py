@@ -35,7 +35,8 @@ def norm_fwd(x, w, eps=1e-5, kind=LAYERNORM, out_dtype=torch.bfloat16):
     """x [rows, cols] (fp32 or bf16) -> (y, mean, rstd)."""
     rows, cols = x.shape
     if not _cuda_ok(x, cols) or out_dtype not in (torch.bfloat16, torch.float32) \
-            or x.dtype not in (torch.bfloat16, torch.float32):
+            or x.dtype not in (torch.bfloat16, torch.float32) \
+            or (x.dtype == torch.bfloat16 and out_dtype == torch.float32):
         return norm_fwd_ref(x, w, eps, kind, out_dtype)
     x = x.contiguous()
     y = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
@@ -67,7 +68,8 @@ def norm_bwd(dy, x, w, mean, rstd, kind=LAYERNORM, dx_accum=None, dw_out=None, d
     """Returns (dx fp32, dw fp32).  `dx_accum` (fp32, same shape) is added to in place;
     `dx_lowp` (same shape, compute dtype) receives a low-precision copy of the final dx."""
     rows, cols = x.shape
-    if not _cuda_ok(x, cols) or dy.dtype not in (torch.bfloat16, torch.float32):
+    if not _cuda_ok(x, cols) or dy.dtype not in (torch.bfloat16, torch.float32) \
+            or (dy.dtype == torch.float32 and x.dtype == torch.bfloat16):
         dx, dw = norm_bwd_ref(dy, x, w, mean, rstd, kind, dx_accum)
         if dw_out is not None:
             if dw_accumulate:

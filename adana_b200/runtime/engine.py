@@ -138,6 +138,10 @@ class Engine:
             checkpoint_every_n=getattr(cfg, "checkpoint_every_n", 1))
         self.loss_scale = 1.0 / max(1, self.ecfg.acc_steps)
         self.enabled = True
+        if getattr(cfg, "attention", "auto") != "auto":
+            from ..ops import attention as _att
+
+            _att.set_mode(cfg.attention)
 
         self.layouts = build_layouts(model, self.world if self.sharded else 1)
         self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt)

@@ -51,6 +51,7 @@ def parse():
     p.add_argument("--per_gpu_seqs", type=int, default=PER_GPU_SEQS)
     p.add_argument("--n_layer", type=int, default=MODEL["n_layer"], help="override for smoke runs only")
     p.add_argument("--no_e2e", action="store_true")
+    p.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     p.add_argument("--ref_no_compile", action="store_true")
     return p.parse_args()
 
@@ -81,6 +82,13 @@ def write_tokens(n_tokens: int, seed: int = 0) -> Path:
         make_zipf_tokens(300_000, 50304, 1.0, seed + 1).tofile(tmp)
         os.replace(tmp, va)
     return root.parent
+
+
+def _attention_impl() -> str:
+    from adana_b200.ops import attention as att
+
+    mode = att.get_mode()
+    return "tcgen05 kernels (csrc/attention_tcgen05.cu)" if mode == "native" else "torch SDPA (cuDNN library kernel)"
 
 
 def emit(payload: dict):
@@ -120,6 +128,7 @@ def run_ours(a):
     args.wd_decaying, args.weight_tying, args.init_scheme = True, False, "ScaledGPT"
     args.scheduler, args.iterations, args.warmup_steps = "cos_inf", 100000, 1000
     args.final_div_factor, args.dataset, args.log_interval = 0.1, "fineweb", 0
+    args.attention = a.attention
     steps_total = a.warmup + a.steps
     tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
     if rank == 0:
@@ -219,7 +228,8 @@ def run_ours(a):
               "config": {"model": f"enoki-36 (L{args.n_layer}, d2304, mlp9216, hd64, V50304)",
                          "global_batch": a.per_gpu_seqs * world, "seq_len": args.sequence_length,
                          "micro_batch": a.micro_batch, "acc_steps": acc, "optimizer": "dana-star-mk4",
-                         "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2"},
+                         "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2",
+                         "attention": _attention_impl()},
               "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
               "peak_mem_gib": round(mem, 2), "final_loss": final_loss})
     backend.finalize()

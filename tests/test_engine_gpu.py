@@ -12,7 +12,9 @@ pytestmark = pytest.mark.gpu
 def _models(name, **kw):
     from adana_b200.models.utils import get_model
 
-    a = tiny_args(name, n_embd=256, n_head=4, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024, **kw)
+    base = dict(n_embd=256, n_head=4, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024)
+    base.update(kw)
+    a = tiny_args(name, **base)
     torch.manual_seed(0)
     ref = get_model(a)
     eng_model = copy.deepcopy(ref).cuda()
