@@ -95,6 +95,27 @@ int adana_sumsq_f32(const float* x, long long n, float* out /*accumulates*/, voi
 int adana_clip_coef(const float* sumsq, float norm_scale, float max_norm, float* out /*[2]: coef, norm*/,
                     void* stream);
 
+// ---- peer-memory collectives (comm_p2p.cu); *_ptrs are arrays of `world` device addresses, one per rank ----
+int adana_p2p_barrier(const unsigned long long* flag_ptrs, int rank, int world, int slot_base, unsigned int seq,
+                      unsigned long long timeout_ns, int* status, void* stream);
+int adana_p2p_reduce_scatter(const unsigned long long* grad_ptrs, int world, long long shard_off, long long n,
+                             float* out, float* sumsq, void* stream);
+int adana_p2p_publish_f32(const unsigned long long* slot_ptrs, int rank, int world, const float* value, void* stream);
+int adana_p2p_push_f32(const float* src, const unsigned long long* dst_ptrs, int world, long long dst_off, long long n,
+                       void* stream);
+int adana_clip_coef_multi(const float* partials, int world, float norm_scale, float max_norm, float* out, void* stream);
+int adana_p2p_opt_step_push(float* p, const float* g, float* m, float* v, float* tau,
+                            const unsigned long long* weight_ptrs, int world, long long push_off, long long n,
+                            const struct AdanaOptHyper* h, const float* clip_coef_ptr, void* stream);
+
+// ---- attention (attention_tcgen05.cu) ----
+int adana_attn_fwd(const void* q, const void* k, const void* vbase, long long ldv, int v_hstride, void* out,
+                   float* lse2, int B, int S, int Hq, int Hk, int hd, float scale, int* status, void* stream);
+int adana_attn_bwd(const void* dout, const void* q, const void* k, long long ldv, int v_hstride, const void* vbase,
+                   const void* out, const float* lse2, float* delta, float* dq_acc, void* dk, long long lddv,
+                   int dv_hstride, void* dvbase, int B, int S, int Hq, int Hk, int hd, float scale, int* status,
+                   void* stream);
+
 // ---- utility -------------------------------------------------------------------------------------
 int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
 int adana_version(void);

@@ -1,0 +1,286 @@
+// Peer-memory collectives over NVLink / NVSwitch for the sharded engine, written as plain kernels
+// on mapped peer pointers (every rank maps every other rank's arena once at start-up):
+//
+//   p2p_barrier            flag barrier: write my sequence number into every peer's flag slot, then
+//                          wait (bounded) until every slot of my own flag array reached it
+//   p2p_reduce_scatter     one-shot pull: my shard of the gradient unit = sum over ranks of their copy
+//                          (fp32, 16-byte loads straight from peer memory), fused with the squared-norm
+//                          partial that the gradient clip needs
+//   p2p_publish_f32        each rank stores one float (its squared-norm partial) into slot [rank] of
+//                          every peer: a scalar all-gather; after a barrier everybody sums locally
+//   p2p_opt_step_push      the fused optimizer step whose bf16 output is stored directly into every
+//                          rank's resident weight buffer: the parameter all-gather is the optimizer's
+//                          epilogue, no staging buffer and no separate collective
+//
+// On a full-bandwidth switch one-shot algorithms are the right shape: every GPU talks to every peer
+// directly, nothing is forwarded.  No TMA, no cluster features and no in-switch reduction are used
+// here; loads and stores are ordinary global accesses.  Every spin is bounded and reports
+// ST_TIMEOUT_PEER_FLAG through the status word instead of hanging.
+//
+// Replaces the NCCL reduce-scatter / all-gather issued by FSDP2 in the reference
+// (src/distributed/fsdp.py:105-116) and the per-tensor optimizer launches (src/optim/adana.py:160-227).
+#include "api.h"
+#include "common.cuh"
+
+namespace adana {
+
+constexpr int MAX_RANKS = 8;
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// flags.p[r] = base of rank r's flag array (uint32 slots).  Thread t < world talks to peer t.
+__global__ void p2p_barrier_kernel(PeerPtrs flags, int rank, int world, int slot_base, uint32_t seq,
+                                   unsigned long long timeout_ns, int* status) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  st_release_sys_u32(reinterpret_cast<uint32_t*>(flags.p[t]) + slot_base + rank, seq);
+  const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.p[rank]) + slot_base + t;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  // sequence numbers only grow; compare with wrap-around in mind
+  while ((int32_t)(ld_acquire_sys_u32(mine) - seq) < 0) {
+    if (((++spins) & 0x3f) == 0 && globaltimer_ns() - t0 > timeout_ns) {
+      if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+      return;
+    }
+  }
+}
+
+// out[i] = sum_r grads_r[shard_off + i], sumsq += sum out[i]^2      (n multiple of 4)
+__global__ void __launch_bounds__(256)
+p2p_reduce_scatter_kernel(PeerPtrs grads, int world, long long shard_off, long long n, float* __restrict__ out,
+                          float* __restrict__ sumsq) {
+  float ss = 0.f;
+  const long long nv = n >> 2;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) {
+        const float4 v = *(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_off) + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+  }
+  if (sumsq) {
+    __shared__ float red[8];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += red[w];
+      atomicAdd(sumsq, t);
+    }
+  }
+}
+
+__global__ void p2p_publish_f32_kernel(PeerPtrs slots, int rank, int world, const float* __restrict__ value) {
+  const int t = threadIdx.x;
+  if (t < world) reinterpret_cast<float*>(slots.p[t])[rank] = *value;
+}
+
+// coef = min(1, max_norm / (norm + 1e-6)) from the per-rank squared-norm partials
+__global__ void clip_coef_multi_kernel(const float* __restrict__ partials, int world, float norm_scale, float max_norm,
+                                       float* __restrict__ out) {
+  float s = 0.f;
+  for (int r = 0; r < world; ++r) s += partials[r];
+  const float norm = sqrtf(s) * norm_scale;
+  out[0] = max_norm > 0.f ? fminf(1.f, max_norm / (norm + 1e-6f)) : 1.f;
+  out[1] = norm;
+}
+
+// dst_r[dst_off + i] = src[i] on every rank r (fp32; the exact copy of the small norm weights)
+__global__ void p2p_push_f32_kernel(const float* __restrict__ src, PeerPtrs dst, int world, long long dst_off,
+                                    long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float v = src[i];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) reinterpret_cast<float*>(dst.p[r])[dst_off + i] = v;
+  }
+}
+
+__device__ __forceinline__ float sgn(float x) { return (x > 0.f) - (x < 0.f); }
+
+// Fused optimizer step (same math as optim.cu) over [0, n) of a flat shard, 8 elements per thread;
+// the bf16 result of element i is stored at weights_r[push_off + i] on every rank r.
+template <int KIND>
+__global__ void __launch_bounds__(256)
+p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                         float* __restrict__ tau, PeerPtrs weights, int world, long long push_off, long long n,
+                         const AdanaOptHyper h, const float* __restrict__ clip_coef_ptr) {
+  const float gs = h.grad_scale * (clip_coef_ptr ? *clip_coef_ptr : 1.f);
+  const float tpow = (KIND == 0) ? __powf(1.f + h.step, h.one_minus_kappa) : 0.f;
+  const float floor_p = 1.f / (1.f + h.step);
+  const long long n8 = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i8 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i8 < n8; i8 += stride) {
+    const long long base = i8 << 3;
+    float pv[8], gv[8], mv[8], vv[8], tv[8];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float4 a = *reinterpret_cast<const float4*>(p + base + q * 4);
+      const float4 b = *reinterpret_cast<const float4*>(g + base + q * 4);
+      const float4 c = *reinterpret_cast<const float4*>(m + base + q * 4);
+      const float4 d = *reinterpret_cast<const float4*>(v + base + q * 4);
+      pv[q * 4] = a.x; pv[q * 4 + 1] = a.y; pv[q * 4 + 2] = a.z; pv[q * 4 + 3] = a.w;
+      gv[q * 4] = b.x; gv[q * 4 + 1] = b.y; gv[q * 4 + 2] = b.z; gv[q * 4 + 3] = b.w;
+      mv[q * 4] = c.x; mv[q * 4 + 1] = c.y; mv[q * 4 + 2] = c.z; mv[q * 4 + 3] = c.w;
+      vv[q * 4] = d.x; vv[q * 4 + 1] = d.y; vv[q * 4 + 2] = d.z; vv[q * 4 + 3] = d.w;
+      if (KIND == 1) {
+        const float4 e = *reinterpret_cast<const float4*>(tau + base + q * 4);
+        tv[q * 4] = e.x; tv[q * 4 + 1] = e.y; tv[q * 4 + 2] = e.z; tv[q * 4 + 3] = e.w;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gi = gv[k] * gs;
+      float pi = pv[k], mi = mv[k], vi = vv[k];
+      if (KIND == 0 || KIND == 1) {
+        mi = mi + h.alpha * (gi - mi);
+        vi = vi * (1.f - h.alpha) + h.alpha * gi * gi;
+        const float denom = sqrtf(vi) + h.eps;
+        float norm, af, longterm;
+        if (KIND == 0) {
+          norm = 1.f / denom;
+          af = tpow * fabsf(mi) * norm;
+          if (h.clipsnr >= 0.f) af = fminf(af, h.clipsnr);
+          longterm = sgn(mi) * af + mi * norm;
+        } else {
+          float ti = tv[k];
+          const float ag = fabsf(gi);
+          ti = ti + h.alpha * (ag / (ag + denom) - ti);
+          tv[k] = ti;
+          const float ct = fminf(ti, 0.5f);
+          const float reg = fmaxf(ct / (1.f - ct), floor_p);
+          const float eff = fmaxf(ti * h.step, 1.f);
+          norm = sqrtf(reg) / denom;
+          const float mn = fabsf(mi) * norm;
+          af = __powf(eff, h.one_minus_kappa) * mn / reg;
+          if (h.clipsnr >= 0.f) af = fminf(af, h.clipsnr);
+          longterm = sgn(mi) * (reg * af + mn);
+        }
+        pi += (-h.lr) * gi * norm + (-h.lr) * h.gamma3 * longterm;
+        pi *= h.wd_factor;
+      } else {
+        if (KIND == 2) pi *= h.wd_factor;
+        mi = h.beta1 * mi + (1.f - h.beta1) * gi;
+        vi = h.beta2 * vi + (1.f - h.beta2) * gi * gi;
+        pi -= (h.lr / h.bc1) * mi / (sqrtf(vi) / sqrtf(h.bc2) + h.eps);
+        if (KIND == 3) pi *= h.wd_factor;
+      }
+      pv[k] = pi; mv[k] = mi; vv[k] = vi;
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      *reinterpret_cast<float4*>(p + base + q * 4) = make_float4(pv[q * 4], pv[q * 4 + 1], pv[q * 4 + 2], pv[q * 4 + 3]);
+      *reinterpret_cast<float4*>(m + base + q * 4) = make_float4(mv[q * 4], mv[q * 4 + 1], mv[q * 4 + 2], mv[q * 4 + 3]);
+      *reinterpret_cast<float4*>(v + base + q * 4) = make_float4(vv[q * 4], vv[q * 4 + 1], vv[q * 4 + 2], vv[q * 4 + 3]);
+      if (KIND == 1)
+        *reinterpret_cast<float4*>(tau + base + q * 4) = make_float4(tv[q * 4], tv[q * 4 + 1], tv[q * 4 + 2], tv[q * 4 + 3]);
+    }
+    uint4 packed;
+    packed.x = pack_bf16x2(pv[0], pv[1]);
+    packed.y = pack_bf16x2(pv[2], pv[3]);
+    packed.z = pack_bf16x2(pv[4], pv[5]);
+    packed.w = pack_bf16x2(pv[6], pv[7]);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(weights.p[r]) + push_off + base) = packed;
+    }
+  }
+}
+
+}  // namespace adana
+
+using namespace adana;
+
+static PeerPtrs make_ptrs(const unsigned long long* ptrs, int world) {
+  PeerPtrs pp;
+  for (int r = 0; r < MAX_RANKS; ++r) pp.p[r] = r < world ? reinterpret_cast<void*>(ptrs[r]) : nullptr;
+  return pp;
+}
+
+static int grid_for(long long work_items) {
+  long long b = (work_items + 255) / 256;
+  const long long cap = 148 * 8;
+  return (int)(b < 1 ? 1 : (b < cap ? b : cap));
+}
+
+extern "C" int adana_p2p_barrier(const unsigned long long* flag_ptrs, int rank, int world, int slot_base,
+                                 unsigned int seq, unsigned long long timeout_ns, int* status, void* stream_) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  p2p_barrier_kernel<<<1, 32, 0, st>>>(make_ptrs(flag_ptrs, world), rank, world, slot_base, seq, timeout_ns, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_p2p_reduce_scatter(const unsigned long long* grad_ptrs, int world, long long shard_off,
+                                        long long n, float* out, float* sumsq, void* stream_) {
+  if (world < 1 || world > MAX_RANKS || (n & 3) || (shard_off & 3)) return -1;
+  if (n == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  p2p_reduce_scatter_kernel<<<grid_for(n / 4), 256, 0, st>>>(make_ptrs(grad_ptrs, world), world, shard_off, n, out, sumsq);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_p2p_publish_f32(const unsigned long long* slot_ptrs, int rank, int world, const float* value,
+                                     void* stream_) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  p2p_publish_f32_kernel<<<1, 32, 0, st>>>(make_ptrs(slot_ptrs, world), rank, world, value);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_p2p_push_f32(const float* src, const unsigned long long* dst_ptrs, int world, long long dst_off,
+                                  long long n, void* stream_) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  if (n <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  p2p_push_f32_kernel<<<grid_for(n), 256, 0, st>>>(src, make_ptrs(dst_ptrs, world), world, dst_off, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_clip_coef_multi(const float* partials, int world, float norm_scale, float max_norm, float* out,
+                                     void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  clip_coef_multi_kernel<<<1, 1, 0, st>>>(partials, world, norm_scale, max_norm, out);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_p2p_opt_step_push(float* p, const float* g, float* m, float* v, float* tau,
+                                       const unsigned long long* weight_ptrs, int world, long long push_off,
+                                       long long n, const AdanaOptHyper* h, const float* clip_coef_ptr,
+                                       void* stream_) {
+  if (world < 1 || world > MAX_RANKS || (n & 7) || (push_off & 7)) return -1;
+  if (n == 0) return 0;
+  if (h->kind == 1 && !tau) return -2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = grid_for(n / 8);
+  const PeerPtrs w = make_ptrs(weight_ptrs, world);
+  switch (h->kind) {
+    case 0: p2p_opt_step_push_kernel<0><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    case 1: p2p_opt_step_push_kernel<1><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    case 2: p2p_opt_step_push_kernel<2><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    case 3: p2p_opt_step_push_kernel<3><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    default: return -3;
+  }
+  return (int)cudaGetLastError();
+}

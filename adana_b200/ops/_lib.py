@@ -53,6 +53,12 @@ def _declare(lib):
         "adana_sigmoid_gate_fwd": [P, P, L, I, I, P, L, I, I, P],
         "adana_sigmoid_gate_bwd": [P, P, P, L, I, I, P, P, L, I, I, P],
         "adana_clip_coef": [P, F, F, P, P],
+        "adana_p2p_barrier": [P, I, I, I, ctypes.c_uint, ctypes.c_ulonglong, P, P],
+        "adana_p2p_reduce_scatter": [P, I, L, L, P, P, P],
+        "adana_p2p_publish_f32": [P, I, I, P, P],
+        "adana_p2p_push_f32": [P, P, I, L, L, P],
+        "adana_clip_coef_multi": [P, I, F, F, P, P],
+        "adana_p2p_opt_step_push": [P, P, P, P, P, P, I, L, L, POINTER(AdanaOptHyper), P, P],
         "adana_attn_fwd": [P, P, P, L, I, P, P, I, I, I, I, I, F, P, P],
         "adana_attn_bwd": [P, P, P, L, I, P, P, P, P, P, P, L, I, P, I, I, I, I, I, F, P, P],
         "adana_embedding_fwd": [P, P, I, P, I, I, I, P],

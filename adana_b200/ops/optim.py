@@ -39,6 +39,20 @@ def clip_coef(sumsq: torch.Tensor, norm_scale: float, max_norm: float, out: torc
     return out
 
 
+def make_hyper(*, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor, grad_scale=1.0, betas=(0.9, 0.999)):
+    """The C struct of per-launch optimizer scalars."""
+    h = _lib.AdanaOptHyper()
+    h.lr, h.alpha, h.step = float(lr), float(alpha), float(step)
+    h.one_minus_kappa = float(1.0 - kappa)
+    h.clipsnr = -1.0 if clipsnr is None else float(clipsnr)
+    h.eps, h.gamma3, h.wd_factor, h.grad_scale = float(eps), float(gamma3), float(wd_factor), float(grad_scale)
+    h.kind = int(kind)
+    b1, b2 = betas
+    h.beta1, h.beta2 = float(b1), float(b2)
+    h.bc1, h.bc2 = float(1 - b1 ** step), float(1 - b2 ** step)
+    return h
+
+
 def fused_step(p, g, m, v, tau, p16, *, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor,
                grad_scale=1.0, clip_coef_t=None, betas=(0.9, 0.999), diag=None):
     """One fused update of a flat fp32 range.  All tensors are 1-D and contiguous."""
@@ -46,15 +60,8 @@ def fused_step(p, g, m, v, tau, p16, *, kind, lr, alpha, step, kappa, clipsnr, e
     if n == 0:
         return
     if p.is_cuda and _lib.available():
-        h = _lib.AdanaOptHyper()
-        h.lr, h.alpha, h.step = float(lr), float(alpha), float(step)
-        h.one_minus_kappa = float(1.0 - kappa)
-        h.clipsnr = -1.0 if clipsnr is None else float(clipsnr)
-        h.eps, h.gamma3, h.wd_factor, h.grad_scale = float(eps), float(gamma3), float(wd_factor), float(grad_scale)
-        h.kind = int(kind)
-        b1, b2 = betas
-        h.beta1, h.beta2 = float(b1), float(b2)
-        h.bc1, h.bc2 = float(1 - b1 ** step), float(1 - b2 ** step)
+        h = make_hyper(kind=kind, lr=lr, alpha=alpha, step=step, kappa=kappa, clipsnr=clipsnr, eps=eps, gamma3=gamma3,
+                       wd_factor=wd_factor, grad_scale=grad_scale, betas=betas)
         rc = _lib.lib().adana_opt_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _lib.ptr(tau),
                                        _lib.ptr(p16), n, ctypes.byref(h), _lib.ptr(clip_coef_t), _lib.ptr(diag),
                                        _lib.stream_ptr())

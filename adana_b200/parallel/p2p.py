@@ -1,0 +1,124 @@
+"""Peer-memory data plane: symmetric arena + the hand-written collectives of csrc/comm_p2p.cu.
+
+Every rank allocates one arena through `torch.distributed._symmetric_memory`, the ranks exchange
+handles once (`rendezvous`) and from then on every rank holds a device pointer to every other
+rank's arena.  The engine places its gradient buffers, its resident bf16 weight buffers and the
+fp32 norm-weight mirrors inside the arena, so "the same tensor on rank r" is `peer_base[r] + offset`
+and the kernels read / write peers directly over NVLink:
+
+    barrier()                       flag barrier with a bounded wait (status word on time-out)
+    reduce_scatter_sumsq(...)       pull-reduce my shard from all ranks + squared-norm partial
+    global_clip_coef(...)           publish partials to all peers, barrier, sum locally
+    opt_step_push(...)              fused optimizer step storing bf16 results into every rank's weights
+    push_f32(...)                   exact fp32 copy of my slice of the norm weights to every rank
+
+A fake-peer mode (`P2PPlane.fake(...)`: all "ranks" are allocations on one GPU) runs the same
+kernels on a single device for tests; only kernels that do not wait on another rank are run there.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+FLAG_BYTES = 4096       # uint32 flag slots at the start of the arena
+SLOT_BYTES = 4096       # float slots for published scalars
+ALIGN = 256
+
+
+def _u64_array(vals):
+    return (ctypes.c_ulonglong * len(vals))(*[int(v) for v in vals])
+
+
+class P2PPlane:
+    def __init__(self, rank: int, world: int, device, arena: torch.Tensor, peer_bases: List[int], timeout_s=20.0):
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.arena = arena
+        self.peer_bases = peer_bases
+        self.base = arena.data_ptr()
+        self.cursor = FLAG_BYTES + SLOT_BYTES
+        self.seq = 0
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.stream = torch.cuda.Stream(device=self.device)
+        self._flag_ptrs = _u64_array(peer_bases)
+        self._slot_ptrs = _u64_array([b + FLAG_BYTES for b in peer_bases])
+        self.slots = arena[FLAG_BYTES:FLAG_BYTES + SLOT_BYTES].view(torch.float32)
+        self.handle = None
+
+    # ---- construction ---------------------------------------------------------------------------------
+    @classmethod
+    def create(cls, nbytes: int, device, group=None, timeout_s=20.0) -> "P2PPlane":
+        import torch.distributed._symmetric_memory as symm
+
+        group = group or dist.group.WORLD
+        total = nbytes + FLAG_BYTES + SLOT_BYTES + ALIGN
+        arena = symm.empty(total, dtype=torch.uint8, device=device)
+        arena.zero_()
+        handle = symm.rendezvous(arena, group)
+        plane = cls(dist.get_rank(group), dist.get_world_size(group), device, arena,
+                    [int(p) for p in handle.buffer_ptrs], timeout_s)
+        plane.handle = handle
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+        return plane
+
+    @classmethod
+    def fake(cls, nbytes: int, world: int, device) -> List["P2PPlane"]:
+        """`world` planes on ONE device whose "peers" are each other's arenas (single-GPU tests)."""
+        total = nbytes + FLAG_BYTES + SLOT_BYTES + ALIGN
+        arenas = [torch.zeros(total, dtype=torch.uint8, device=device) for _ in range(world)]
+        bases = [a.data_ptr() for a in arenas]
+        return [cls(r, world, device, arenas[r], bases) for r in range(world)]
+
+    def alloc(self, numel: int, dtype) -> torch.Tensor:
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        start = (self.cursor + ALIGN - 1) // ALIGN * ALIGN
+        if start + nbytes > self.arena.numel():
+            raise MemoryError("symmetric arena exhausted")
+        self.cursor = start + nbytes
+        return self.arena[start:start + nbytes].view(dtype)
+
+    def owns(self, t: torch.Tensor) -> bool:
+        return self.base <= t.data_ptr() < self.base + self.arena.numel()
+
+    def peer_ptrs(self, t: torch.Tensor):
+        off = t.data_ptr() - self.base
+        return _u64_array([b + off for b in self.peer_bases])
+
+    # ---- collectives (all enqueue on the current stream) -----------------------------------------------------
+    def barrier(self):
+        self.seq += 1
+        rc = _lib.lib().adana_p2p_barrier(self._flag_ptrs, self.rank, self.world, 0, self.seq & 0xFFFFFFFF,
+                                          self.timeout_ns, _lib.status_buffer(self.device).data_ptr(),
+                                          _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_barrier")
+
+    def reduce_scatter_sumsq(self, full: torch.Tensor, shard_off: int, shard_out: torch.Tensor, sumsq: Optional[torch.Tensor]):
+        rc = _lib.lib().adana_p2p_reduce_scatter(self.peer_ptrs(full), self.world, shard_off, shard_out.numel(),
+                                                 shard_out.data_ptr(), _lib.ptr(sumsq), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_reduce_scatter")
+
+    def global_clip_coef(self, local_sumsq: torch.Tensor, norm_scale: float, max_norm: float, out: torch.Tensor):
+        """All ranks' squared-norm partials -> clip coefficient on the device (out[0]) and the norm (out[1])."""
+        lib = _lib.lib()
+        rc = lib.adana_p2p_publish_f32(self._slot_ptrs, self.rank, self.world, local_sumsq.data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_publish_f32")
+        self.barrier()
+        rc = lib.adana_clip_coef_multi(self.slots.data_ptr(), self.world, float(norm_scale), float(max_norm),
+                                       out.data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_clip_coef_multi")
+
+    def opt_step_push(self, p, g, m, v, tau, weights_full: torch.Tensor, push_off: int, hyper, clip_coef_t):
+        rc = _lib.lib().adana_p2p_opt_step_push(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _lib.ptr(tau),
+                                                self.peer_ptrs(weights_full), self.world, push_off, p.numel(),
+                                                ctypes.byref(hyper), _lib.ptr(clip_coef_t), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_opt_step_push")
+
+    def push_f32(self, src: torch.Tensor, dst_full: torch.Tensor, dst_off: int):
+        rc = _lib.lib().adana_p2p_push_f32(src.data_ptr(), self.peer_ptrs(dst_full), self.world, dst_off, src.numel(),
+                                           _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_push_f32")

@@ -63,20 +63,25 @@ class _Bridge(torch.autograd.Function):
 
 
 class Unit:
-    def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt):
+    def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt, plane=None):
         self.layout = layout
+        self.plane = plane
         self.padded = layout.padded
         self.shard_len = layout.padded // world if sharded else layout.padded
         self.shard_off = rank * self.shard_len if sharded else 0
         f32 = dict(dtype=torch.float32, device=device)
         self.master = torch.zeros(self.shard_len, **f32)
-        self.grads = torch.zeros(self.padded, **f32)
+        self.grads = plane.alloc(self.padded, torch.float32) if plane is not None else torch.zeros(self.padded, **f32)
         self.grad_shard = torch.zeros(self.shard_len, **f32) if (sharded and world > 1) else self.grads
         self.low_precision = cdt != torch.float32
         if self.low_precision:
-            self.weights = torch.zeros(self.padded, dtype=cdt, device=device)
-            self.w_shard = (torch.zeros(self.shard_len, dtype=cdt, device=device)
-                            if (sharded and world > 1) else self.weights)
+            self.weights = (plane.alloc(self.padded, cdt) if plane is not None
+                            else torch.zeros(self.padded, dtype=cdt, device=device))
+            if plane is not None:      # peers store into `weights` directly: my shard is a slice of it
+                self.w_shard = self.weights[self.shard_off:self.shard_off + self.shard_len]
+            else:
+                self.w_shard = (torch.zeros(self.shard_len, dtype=cdt, device=device)
+                                if (sharded and world > 1) else self.weights)
         else:
             # fp32 compute: the master buffer is the compute buffer when it is complete
             self.weights = self.master if self.shard_len == self.padded else torch.zeros(self.padded, **f32)
@@ -144,7 +149,8 @@ class Engine:
             _att.set_mode(cfg.attention)
 
         self.layouts = build_layouts(model, self.world if self.sharded else 1)
-        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt)
+        self.plane = self._make_plane()
+        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, self.plane)
                                   for l in self.layouts]
         self.spec = self._block_spec()
         self.freqs = model.freqs_cis.to(self.device).contiguous()
@@ -167,6 +173,26 @@ class Engine:
     # ---------------------------------------------------------------------------------------------
     # construction helpers
     # ---------------------------------------------------------------------------------------------
+    def _make_plane(self):
+        """Peer-memory data plane for the sharded engine on GPUs (`--fsdp_comm auto|p2p`); None selects
+        torch.distributed collectives (NCCL / Gloo)."""
+        want = getattr(self.cfg, "fsdp_comm", "auto")
+        if not self.sharded or self.device.type != "cuda" or self.cdt == torch.float32 or want == "nccl":
+            return None
+        if self.world > 8 or not _lib.has("adana_p2p_barrier"):
+            return None
+        nbytes = sum(l.padded * 6 + l.numel * 4 + 4096 for l in self.layouts)
+        try:
+            from ..parallel.p2p import P2PPlane
+
+            return P2PPlane.create(nbytes, self.device, group=self.comm.group)
+        except Exception as e:
+            if want == "p2p":
+                raise
+            if self.rank == 0:
+                print(f"[engine] peer-memory plane unavailable ({type(e).__name__}: {e}); using NCCL collectives")
+            return None
+
     def _block_spec(self) -> BK.BlockSpec:
         m, c = self.model, self.cfg
         hd = m.head_dim
@@ -210,6 +236,8 @@ class Engine:
             lay = u.layout
             if u.shard_len == u.padded:
                 u.small_f32 = u.master[u.small_off:u.small_off + u.small_len]
+            elif self.plane is not None:
+                u.small_f32 = self.plane.alloc(max(u.small_len, 1), torch.float32)[:u.small_len]
             else:
                 u.small_f32 = torch.zeros(u.small_len, dtype=torch.float32, device=self.device)
 
@@ -287,6 +315,14 @@ class Engine:
         whichever rank's shard covers them) are exchanged exactly with one small all-reduce of
         a zero-padded buffer instead of being read back from the bf16 compute copy."""
         if not (self.sharded and self.world > 1):
+            return
+        if self.plane is not None:
+            for u in self.units:
+                lo, hi = u.shard_off, u.shard_off + u.shard_len
+                a, b = max(u.small_off, lo), min(u.small_off + u.small_len, hi)
+                if a < b:
+                    self.plane.push_f32(u.master[a - lo:b - lo], u.small_f32, a - u.small_off)
+            self.plane.barrier()
             return
         total = sum(u.small_len for u in self.units)
         if self._small_all is None or self._small_all.numel() != total:
@@ -384,12 +420,28 @@ class Engine:
     def _reduce_unit(self, u: Unit):
         if self.world == 1:
             return
+        if self.plane is not None:
+            # peers may read this unit's gradients once every rank has finished its backward of the unit
+            ev = torch.cuda.Event()
+            ev.record()
+            with torch.cuda.stream(self.plane.stream):
+                self.plane.stream.wait_event(ev)
+                self.plane.barrier()
+                self.plane.reduce_scatter_sumsq(u.grads, u.shard_off, u.grad_shard, self._sumsq)
+            u.grad_work = None
+            self._plane_pending = True
+            return
         if self.sharded:
             u.grad_work = self.comm.reduce_scatter_sum(u.grads, u.grad_shard, async_op=True)
         else:
             u.grad_work = self.comm.all_reduce_sum(u.grads, async_op=True)
 
+    _plane_pending = False
+
     def finish_grad_sync(self):
+        if self._plane_pending:
+            torch.cuda.current_stream().wait_stream(self.plane.stream)
+            self._plane_pending = False
         for u in self.units:
             if u.grad_work is not None:
                 wait(u.grad_work)
@@ -399,6 +451,11 @@ class Engine:
         """Global L2 norm of the (rank-averaged) gradient; leaves the clip coefficient on the device.
         Returns a 0-d tensor holding the norm."""
         self.finish_grad_sync()
+        if self.plane is not None:
+            # the reduce-scatter kernels already accumulated this rank's squared-norm partial
+            self.plane.global_clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
+            self.last_grad_norm = self._clip[1]
+            return self._clip[1]
         self._sumsq.zero_()
         for u in self.units:
             O.sumsq_accumulate(u.grad_shard, self._sumsq)
@@ -430,12 +487,20 @@ class Engine:
                     continue
                 ls, le = s - lo, e - lo
                 hyper = opt.hyper_for(grp, t)
+                if self.plane is not None:
+                    h = O.make_hyper(kind=kind, grad_scale=1.0 / self.world, **hyper)
+                    self.plane.opt_step_push(u.master[ls:le], u.grad_shard[ls:le], u.state["m"][ls:le],
+                                             u.state["v"][ls:le], u.state["tau"][ls:le] if "tau" in u.state else None,
+                                             u.weights, s, h, self._clip)
+                    continue
                 O.fused_step(u.master[ls:le], u.grad_shard[ls:le], u.state["m"][ls:le], u.state["v"][ls:le],
                              u.state["tau"][ls:le] if "tau" in u.state else None,
                              u.w_shard[ls:le] if u.low_precision else None,
                              kind=kind, grad_scale=1.0 / self.world, clip_coef_t=self._clip, diag=diag, **hyper)
             self._after_update(u)
-        self._sync_small()
+        self._sync_small()     # (peer-memory plane: ends with the barrier that completes the weight pushes)
+        if self.plane is not None:
+            self._sumsq.zero_()
         opt.step_count = t
         self.opt_step_count += 1
         self.micro_step = 0
@@ -444,6 +509,8 @@ class Engine:
 
     def _after_update(self, u: Unit):
         """Make the unit's compute weights current again after its shard was updated."""
+        if self.plane is not None:
+            return  # the optimizer kernel stored the new weights into every rank's buffer
         if self.world > 1 and self.sharded:
             u.gather_work = self.comm.all_gather(u.w_shard, u.weights, async_op=True)
         elif not u.low_precision and u.weights.data_ptr() != u.master.data_ptr():
@@ -453,6 +520,9 @@ class Engine:
         """Re-derive compute weights from the master copy (after an external optimizer or a load)."""
         with torch.no_grad():
             for u in self.units:
+                if self.plane is not None:
+                    self.comm.all_gather(u.master.to(self.cdt), u.weights)
+                    continue
                 if u.low_precision or u.w_shard.data_ptr() != u.master.data_ptr():
                     u.w_shard.copy_(u.master)
                 self._after_update(u)

@@ -246,3 +246,39 @@ def test_watchdog_with_fake_store_and_clock():
     a.beat(2)
     msg = a.check_once()
     assert msg is not None and "rank 1" in msg and b.check_once() is None
+
+
+# ---- expert parallelism ----------------------------------------------------------------------------------------
+def _ep_worker(rank, world):
+    from conftest import tiny_args
+    from adana_b200.models.qwen3 import Qwen3MLP
+    from adana_b200.models.moe import MoE
+    from adana_b200.parallel.expert_parallel import ExpertParallelMoE
+
+    dist.init_process_group("gloo")
+    a = tiny_args("qwen3", moe=True, moe_num_experts=4, moe_num_shared_experts=0, moe_num_experts_per_tok=2,
+                  moe_expert_capacity_factor=0.0)
+    torch.manual_seed(0)
+    dense = MoE(a, Qwen3MLP)                       # same weights on every rank
+    torch.manual_seed(1)
+    ep = ExpertParallelMoE(a, Qwen3MLP)
+    with torch.no_grad():
+        ep.router.weight.copy_(dense.router.weight)
+        for e in range(ep.per_rank):
+            ep.experts[e].load_state_dict(dense.experts[rank * ep.per_rank + e].state_dict())
+    torch.manual_seed(100 + rank)
+    x = torch.randn(2, 8, a.n_embd, requires_grad=True)
+    y_ref, _ = dense(x)
+    y, info = ep(x)
+    y.sum().backward()
+    g_ep = x.grad.clone()
+    x.grad = None
+    y_ref.sum().backward()
+    return {"err": (y - y_ref).abs().max().item(), "gerr": (g_ep - x.grad).abs().max().item(),
+            "router_grad": ep.router.weight.grad.abs().sum().item()}
+
+
+def test_expert_parallel_matches_local_moe_and_backpropagates():
+    res = _spawn(_ep_worker, 2)
+    for r in (0, 1):
+        assert res[r]["err"] < 1e-5 and res[r]["gerr"] < 1e-5 and res[r]["router_grad"] > 0

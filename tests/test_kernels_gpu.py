@@ -252,3 +252,76 @@ def test_attention_backward_native(hd, Hq, Hk, S):
     untouched = dbuf.clone()
     untouched.as_strided((T, Hk, hd), (width, hd, 1), v_off).zero_()
     assert untouched.abs().max().item() == 0.0
+
+
+# ---- peer-memory collectives in fake-peer mode: every "rank" is an allocation on this one GPU ----------
+def test_p2p_reduce_scatter_and_clip_fake_peers():
+    from adana_b200.parallel.p2p import P2PPlane
+
+    torch.manual_seed(11)
+    world, n = 4, 64 * 4 * 257
+    planes = P2PPlane.fake(n * 4 + 4096, world, DEV)
+    grads = [pl.alloc(n, torch.float32) for pl in planes]
+    for g in grads:
+        g.copy_(torch.randn(n, device=DEV))
+    total = torch.stack(grads).sum(0)
+    shard = n // world
+    partial = []
+    for r, pl in enumerate(planes):
+        out = torch.empty(shard, device=DEV)
+        ss = torch.zeros(1, device=DEV)
+        pl.reduce_scatter_sumsq(grads[r], r * shard, out, ss)
+        assert rel_err(out, total[r * shard:(r + 1) * shard]) < 1e-6
+        assert abs(ss.item() - out.double().pow(2).sum().item()) / ss.item() < 1e-4
+        partial.append(ss)
+    # every rank publishes its partial into every arena; the flag barrier itself is exercised on real peers
+    lib = _lib.lib()
+    for r, pl in enumerate(planes):
+        _lib.check_rc(lib.adana_p2p_publish_f32(pl._slot_ptrs, r, world, partial[r].data_ptr(), _lib.stream_ptr()), "publish")
+    out = torch.zeros(2, device=DEV)
+    _lib.check_rc(lib.adana_clip_coef_multi(planes[2].slots.data_ptr(), world, 1.0 / world, 1.0, out.data_ptr(),
+                                            _lib.stream_ptr()), "clip")
+    norm = total.double().norm().item() / world
+    assert abs(out[1].item() - norm) / norm < 1e-4 and abs(out[0].item() - min(1.0, 1.0 / (norm + 1e-6))) < 1e-5
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_p2p_opt_step_push_fake_peers(kind):
+    from adana_b200.parallel.p2p import P2PPlane
+
+    torch.manual_seed(12)
+    world, n = 4, 64 * 4 * 129
+    shard = n // world
+    planes = P2PPlane.fake(n * 2 + 4096, world, DEV)
+    weights = [pl.alloc(n, torch.bfloat16) for pl in planes]
+    kw = dict(kind=kind, lr=3e-3, alpha=8 / 11, step=3, kappa=0.85, clipsnr=2.0, eps=1e-8, gamma3=1.0, wd_factor=0.999,
+              grad_scale=0.25, betas=(0.9, 0.95))
+    clip = torch.tensor([0.8, 0.0], device=DEV)
+    expect = torch.empty(n, device=DEV)
+    for r, pl in enumerate(planes):
+        p, g = torch.randn(shard, device=DEV), torch.randn(shard, device=DEV) * 1e-2
+        m, v, tau = torch.randn(shard, device=DEV) * 1e-3, torch.rand(shard, device=DEV) * 1e-4, torch.rand(shard, device=DEV) * 0.6
+        ref = [t.clone() for t in (p, g, m, v, tau)]
+        pl.opt_step_push(p, g, m, v, tau, weights[r], r * shard, optim.make_hyper(**kw), clip)
+        optim.fused_step(ref[0], ref[1], ref[2], ref[3], ref[4], None, clip_coef_t=clip, **kw)
+        assert rel_err(p, ref[0]) < 1e-6 and rel_err(m, ref[2]) < 1e-6 and rel_err(v, ref[3]) < 1e-6
+        expect[r * shard:(r + 1) * shard] = ref[0]
+    for w in weights:        # every rank's resident copy now holds every shard
+        assert rel_err(w, expect) < 8e-3
+
+
+def test_p2p_push_f32_and_barrier_timeout():
+    from adana_b200.parallel.p2p import P2PPlane
+
+    planes = P2PPlane.fake(1 << 16, 2, DEV)
+    dst = [pl.alloc(256, torch.float32) for pl in planes]
+    src = torch.randn(64, device=DEV)
+    planes[0].push_f32(src, dst[0], 128)
+    for d in dst:
+        assert torch.equal(d[128:192], src) and d[:128].abs().sum().item() == 0
+    # a barrier whose peer never arrives gives up after its time limit and reports it through the status word
+    planes[0].timeout_ns = int(0.2e9)
+    planes[0].barrier()
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer flag"):
+        _lib.check_status()

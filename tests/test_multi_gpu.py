@@ -1,0 +1,70 @@
+"""Sharded engine on real peers: the peer-memory plane against the NCCL plane (needs >= 2 GPUs)."""
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT / "tests"))
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, plane):
+    import torch.distributed as dist
+
+    from conftest import tiny_args
+    from adana_b200.models.utils import get_model
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.comm import Comm
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    a = tiny_args("enoki", n_embd=256, n_head=4, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024,
+                  opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True, wd_ts=3.0,
+                  acc_steps=2, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane)
+    torch.manual_seed(0)
+    m = get_model(a).to(a.device)
+    eng = attach(m, a, comm=Comm(), sharded=True, device=a.device)
+    assert (eng.plane is not None) == (plane == "p2p")
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = EngineOptimizer(eng, a.opt, a, specs)
+    m.train()
+    losses, norms = [], []
+    for step in range(4):
+        for micro in range(2):
+            g = torch.Generator().manual_seed(1000 * step + 10 * micro + rank)
+            idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g).to(a.device)
+            eng.sync_on_backward = micro == 1
+            out = m(idx, targets=idx.roll(-1, 1))
+            (out["loss"] / 2).backward()
+        norms.append(float(eng.grad_norm_and_clip(0.5)))
+        opt.step()
+        opt.zero_grad()
+        losses.append(out["loss"].item())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    full = eng.full_param_dict("master")
+    return {"losses": losses, "norms": norms, "params": {k: v.float().cpu() for k, v in full.items()}}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_p2p_plane_matches_nccl_plane():
+    from test_distributed_cpu import _spawn, _t
+
+    world = 2
+    res = {plane: _spawn(_worker, world, plane) for plane in ("nccl", "p2p")}
+    for r in range(world):
+        assert res["p2p"][r]["losses"][-1] < res["p2p"][r]["losses"][0]
+    for a, b in zip(res["nccl"][0]["norms"], res["p2p"][0]["norms"]):
+        assert abs(a - b) / a < 2e-2
+    for k, v in res["nccl"][0]["params"].items():
+        d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs()
+        assert d.mean().item() < 2e-4, (k, d.mean().item())
+        assert torch.equal(_t(res["p2p"][0]["params"][k]), _t(res["p2p"][1]["params"][k]))
