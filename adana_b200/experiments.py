@@ -1,0 +1,223 @@
+"""Experiment orchestration on top of `adana_b200.launch`: grid sweeps, self-resubmitting restart jobs
+and the batch-size / memory benchmark.  One module with three sub-commands replaces the reference's shell
+drivers (`scripts/sweep.sh`, `scripts/restart_{enoki,qwen3}.sh`, `scripts/benchmark_batch.sh`,
+`scripts/config.sh`, `scripts/cluster_list*.sh`):
+
+    python -m adana_b200.experiments sweep   --arch enoki --opt adana --heads 8 12 --lr_mult 0.5 1 2 [--slurm] [--dry]
+    python -m adana_b200.experiments restart --arch enoki --opt dana-star-mk4 --heads 16 --iterations_to_run 2000 ...
+    python -m adana_b200.experiments benchmark-batch --heads 28 36 --batch 4 8 16 --nproc 4
+    python -m adana_b200.experiments jobs            # squeue one-liner for this user
+
+* sweep: every (heads x LR multiplier) point becomes one launch (or one `sbatch --wrap` of the restart
+  driver under `--slurm`), all in one wandb group; the base LR comes from the scaling rules.
+* restart: runs the launcher with `--auto_resume`; when the run exits cleanly because
+  `--iterations_to_run` was reached and the final iteration has not been, it starts (or, under SLURM,
+  `sbatch`es) itself again with RESTART_COUNT+1 — a job that fits in a scheduler slot and continues
+  from the `latest` checkpoint.
+* benchmark-batch: 5-iteration runs over heads x tp x micro-batch, records out-of-memory failures, the
+  `[Memory] ... peak_allocated=` line and the last `iter_dt=`; prints the largest batch that fits.
+Environment (`config.sh` equivalent): `ADANA_CONFIG` may name a file of KEY=VALUE lines (WANDB_*,
+DATASETS_DIR, RESULTS_BASE_FOLDER, TIKTOKEN_CACHE_DIR, HF_HOME) that is loaded into the environment.
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+import os
+import re
+import shlex
+import subprocess
+import sys
+from pathlib import Path
+
+from . import launch as L
+from .config.scaling import compute_dimensions, compute_lr
+
+
+def load_user_config(path=None) -> dict:
+    path = path or os.environ.get("ADANA_CONFIG")
+    loaded = {}
+    if path and Path(path).exists():
+        for line in Path(path).read_text().splitlines():
+            line = line.split("#", 1)[0].strip()
+            if line.startswith("export "):
+                line = line[len("export "):]
+            if "=" in line:
+                k, v = line.split("=", 1)
+                loaded[k.strip()] = v.strip().strip('"').strip("'")
+    os.environ.update({k: v for k, v in loaded.items() if k not in os.environ})
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    return loaded
+
+
+def _launch_cmd(args_list):
+    return [sys.executable, "-m", "adana_b200.launch", *[str(a) for a in args_list]]
+
+
+def _sbatch(cmd, job_name, nproc, time, mem, account=None, dry=False):
+    sb = ["sbatch", f"--job-name={job_name}", f"--gres=gpu:{nproc}", f"--time={time}", f"--mem={mem}", "--nodes=1",
+          f"--cpus-per-task={8 * nproc}"]
+    if account:
+        sb.append(f"--account={account}")
+    sb += ["--wrap", " ".join(shlex.quote(c) for c in cmd)]
+    print(" ".join(shlex.quote(c) for c in sb))
+    return 0 if dry else subprocess.call(sb)
+
+
+# ---- sweep ------------------------------------------------------------------------------------------------------
+def cmd_sweep(a, extra):
+    points = []
+    for heads in a.heads:
+        dims = compute_dimensions(a.arch, heads)
+        base_lr = compute_lr(a.arch, a.opt, dims["non_emb_params"], kappa=a.kappa, batch_size=a.batch_size * a.acc_steps)
+        if base_lr is None:
+            raise SystemExit(f"no LR law for {a.opt}; pass --base_lr")
+        base_lr = a.base_lr or base_lr
+        tokens = a.batch_size * a.acc_steps * 2048
+        print(f"--- heads={heads} (non_emb={dims['non_emb_params'] / 1e6:.1f}M total={dims['total_params'] / 1e6:.1f}M "
+              f"iters={int(20 * dims['total_params'] / tokens)}, base_lr={base_lr:.6e}) ---")
+        for mult in a.lr_mult:
+            largs = ["--arch", a.arch, "--opt", a.opt, "--heads", heads, "--nproc", a.nproc, "--batch_size", a.batch_size,
+                     "--acc_steps", a.acc_steps, "--kappa", a.kappa, "--clipsnr", a.clipsnr, "--gamma_3_factor",
+                     a.gamma_3_factor, "--lr", f"{mult * base_lr:.6e}", "--scheduler", a.scheduler,
+                     "--distributed_backend", a.distributed_backend, "--wandb_group", a.wandb_group]
+            if a.wd_ts_const is not None:
+                largs += ["--wd_ts_const", a.wd_ts_const]
+            elif a.wd_ts_divisor is not None:
+                largs += ["--wd_ts_divisor", a.wd_ts_divisor]
+            if a.tp_size > 1:
+                largs += ["--tp_size", a.tp_size]
+            if a.iterations_to_run:
+                largs += ["--iterations_to_run", a.iterations_to_run]
+            largs += extra
+            points.append((heads, mult, largs))
+    rc = 0
+    for heads, mult, largs in points:
+        name = f"{a.arch}-{a.opt}-h{heads}-lr{mult}"
+        if a.slurm:
+            cmd = [sys.executable, "-m", "adana_b200.experiments", "restart", *[str(x) for x in largs]]
+            rc |= _sbatch(cmd, name, a.nproc, a.time, a.mem, a.account, dry=a.dry)
+        else:
+            cmd = _launch_cmd(largs + (["--dry"] if a.dry else []))
+            print(" ".join(shlex.quote(c) for c in cmd))
+            rc |= subprocess.call(cmd)
+    print(f"{len(points)} job(s) {'printed' if a.dry else 'submitted'}")
+    return rc
+
+
+# ---- restart -----------------------------------------------------------------------------------------------------
+def cmd_restart(a, extra):
+    count = int(os.environ.get("RESTART_COUNT", "0"))
+    print(f"[restart] attempt {count}")
+    largs = list(extra)
+    if "--no_auto_resume" in largs:
+        largs.remove("--no_auto_resume")
+    rc = subprocess.call(_launch_cmd(largs))
+    if rc != 0:
+        print(f"[restart] launch exited with {rc}; not resubmitting")
+        return rc
+    if "--iterations_to_run" not in largs or count + 1 >= a.max_restarts:
+        return 0
+    env = {**os.environ, "RESTART_COUNT": str(count + 1)}
+    me = [sys.executable, "-m", "adana_b200.experiments", "restart", "--max_restarts", str(a.max_restarts), *largs]
+    if os.environ.get("SLURM_JOB_ID"):
+        info = subprocess.run(["scontrol", "show", "job", os.environ["SLURM_JOB_ID"]], capture_output=True, text=True).stdout
+        gres = (re.search(r"gres/gpu[:=](\S+)", info) or re.search(r"gpu[:=](\d+)", info))
+        time = re.search(r"TimeLimit=(\S+)", info)
+        return _sbatch(me, os.environ.get("SLURM_JOB_NAME", "adana-restart"), gres.group(1) if gres else 1,
+                       time.group(1) if time else "3:00:00", os.environ.get("SLURM_MEM_PER_NODE", "0"),
+                       os.environ.get("SLURM_JOB_ACCOUNT"))
+    if a.finished_marker and Path(a.finished_marker).exists():
+        return 0
+    return subprocess.call(me, env=env)
+
+
+# ---- batch-size / memory benchmark --------------------------------------------------------------------------------
+def parse_run_log(text: str) -> dict:
+    """Pull the facts the benchmark records out of a trainer log."""
+    oom = bool(re.search(r"out of memory|OutOfMemoryError|CUDA error: out of memory", text, re.I))
+    mem = re.findall(r"peak_allocated=([0-9.]+) GiB", text)
+    dts = re.findall(r"iter_dt=([0-9.eE+-]+)s", text)
+    return {"oom": oom, "peak_allocated_gib": float(mem[-1]) if mem else None, "iter_dt": float(dts[-1]) if dts else None}
+
+
+def cmd_benchmark_batch(a, extra):
+    results = []
+    for heads, tp, batch in itertools.product(a.heads, a.tp, a.batch):
+        largs = ["--arch", a.arch, "--opt", a.opt, "--heads", heads, "--nproc", a.nproc, "--batch_size", batch * (a.nproc // tp),
+                 "--acc_steps", 1, "--iterations", 5, "--warmup_steps", 1, "--no_wandb", "--no_auto_resume",
+                 "--distributed_backend", "fsdp", "--log_interval", 1, "--eval_interval", 1000000,
+                 "--latest_ckpt_interval", 0, "--dataset", a.dataset, *extra]
+        if tp > 1:
+            largs += ["--tp_size", tp]
+        if a.dry:
+            print(" ".join(shlex.quote(str(c)) for c in _launch_cmd(largs)))
+            continue
+        proc = subprocess.run(_launch_cmd(largs), capture_output=True, text=True)
+        rec = {"heads": heads, "tp": tp, "micro_batch": batch, "returncode": proc.returncode,
+               **parse_run_log(proc.stdout + proc.stderr)}
+        rec["ok"] = proc.returncode == 0 and not rec["oom"]
+        results.append(rec)
+        print(json.dumps(rec), flush=True)
+    best = {}
+    for r in results:
+        if r["ok"]:
+            key = (r["heads"], r["tp"])
+            best[key] = max(best.get(key, 0), r["micro_batch"])
+    for (heads, tp), b in sorted(best.items()):
+        print(f"heads={heads} tp={tp}: max micro-batch {b}")
+    return 0
+
+
+def cmd_jobs(a, extra):
+    return subprocess.call(["squeue", "-u", os.environ.get("USER", ""), "-o", "%.10i %.40j %.8T %.10M %.6D %R"])
+
+
+def main(argv=None) -> int:
+    load_user_config()
+    p = argparse.ArgumentParser(allow_abbrev=False)
+    sub = p.add_subparsers(dest="cmd", required=True)
+    s = sub.add_parser("sweep")
+    s.add_argument("--arch", default="enoki")
+    s.add_argument("--opt", default="adana")
+    s.add_argument("--heads", type=int, nargs="+", default=[8])
+    s.add_argument("--lr_mult", type=float, nargs="+", default=[1.0])
+    s.add_argument("--base_lr", type=float, default=None)
+    s.add_argument("--kappa", type=float, default=0.85)
+    s.add_argument("--clipsnr", type=float, default=0.25)
+    s.add_argument("--gamma_3_factor", type=float, default=1.0)
+    s.add_argument("--wd_ts_divisor", type=float, default=10)
+    s.add_argument("--wd_ts_const", type=float, default=None)
+    s.add_argument("--batch_size", type=int, default=8)
+    s.add_argument("--acc_steps", type=int, default=16)
+    s.add_argument("--nproc", type=int, default=4)
+    s.add_argument("--scheduler", default="cos_inf")
+    s.add_argument("--distributed_backend", default="fsdp")
+    s.add_argument("--tp_size", type=int, default=1)
+    s.add_argument("--wandb_group", default="fsdp-experiment")
+    s.add_argument("--iterations_to_run", type=int, default=None)
+    s.add_argument("--slurm", action="store_true")
+    s.add_argument("--account", default=None)
+    s.add_argument("--time", default="3:00:00")
+    s.add_argument("--mem", default="0")
+    s.add_argument("--dry", action="store_true")
+    r = sub.add_parser("restart")
+    r.add_argument("--max_restarts", type=int, default=50)
+    r.add_argument("--finished_marker", default=None)
+    b = sub.add_parser("benchmark-batch")
+    b.add_argument("--arch", default="enoki")
+    b.add_argument("--opt", default="dana-star-mk4")
+    b.add_argument("--heads", type=int, nargs="+", default=[28, 32, 36, 44, 48])
+    b.add_argument("--tp", type=int, nargs="+", default=[1, 4])
+    b.add_argument("--batch", type=int, nargs="+", default=[4, 8, 16, 32])
+    b.add_argument("--nproc", type=int, default=4)
+    b.add_argument("--dataset", default="synthetic-zipf")
+    b.add_argument("--dry", action="store_true")
+    sub.add_parser("jobs")
+    a, extra = p.parse_known_args(argv)
+    return {"sweep": cmd_sweep, "restart": cmd_restart, "benchmark-batch": cmd_benchmark_batch, "jobs": cmd_jobs}[a.cmd](a, extra)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
