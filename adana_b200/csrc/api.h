@@ -14,6 +14,7 @@ enum {
   EPI_F32 = 4,        // C(f32)  = beta * C + alpha * acc
   EPI_SWIGLU = 5,     // B = [gate; up] rows; C(bf16)=[gate|up] pre-activations, C2 = silu(g)*u
   EPI_DSWIGLU = 6,    // acc = dH; R = [gate|up]; C = [dGate|dUp]
+  EPI_AXPBY_BF16 = 7, // C(bf16) = alpha * acc + beta * R(bf16); C may alias R
 };
 
 #ifdef __cplusplus

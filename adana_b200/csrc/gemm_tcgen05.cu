@@ -337,6 +337,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(z[i]);
             store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
                                ncols_ok);
+          } else if constexpr (EPI == EPI_AXPBY_BF16) {
+            float z[32];
+            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
+                         ncols_ok);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
+            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                               ncols_ok);
           } else if constexpr (EPI == EPI_F32) {
             float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
 #pragma unroll
@@ -458,12 +466,14 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   ADANA_GEMM_CASE(false, false, EPI_RESID_F32)
   ADANA_GEMM_CASE(false, false, EPI_F32)
   ADANA_GEMM_CASE(false, false, EPI_SWIGLU)
+  ADANA_GEMM_CASE(false, false, EPI_AXPBY_BF16)
   // dgrad (dY x weight)
   ADANA_GEMM_CASE(false, true, EPI_BF16)
   ADANA_GEMM_CASE(false, true, EPI_DGELU)
   ADANA_GEMM_CASE(false, true, EPI_DSWIGLU)
   ADANA_GEMM_CASE(false, true, EPI_F32)
   ADANA_GEMM_CASE(false, true, EPI_RESID_F32)
+  ADANA_GEMM_CASE(false, true, EPI_AXPBY_BF16)
   // wgrad (dY^T x X)
   ADANA_GEMM_CASE(true, true, EPI_F32)
   ADANA_GEMM_CASE(true, true, EPI_BF16)

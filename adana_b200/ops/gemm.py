@@ -14,7 +14,7 @@ import torch.nn.functional as F
 
 from . import _lib
 
-EPI_BF16, EPI_GELU_DUAL, EPI_RESID_F32, EPI_DGELU, EPI_F32, EPI_SWIGLU, EPI_DSWIGLU = range(7)
+EPI_BF16, EPI_GELU_DUAL, EPI_RESID_F32, EPI_DGELU, EPI_F32, EPI_SWIGLU, EPI_DSWIGLU, EPI_AXPBY_BF16 = range(8)
 
 
 def _check2d(t: torch.Tensor, name: str):

@@ -542,10 +542,13 @@ class Engine:
         return full
 
     def full_param_dict(self, which: str = "master") -> Dict[str, torch.Tensor]:
-        """name -> full fp32 tensor (collective when sharded).  `which`: master | m | v | tau."""
+        """name -> full fp32 tensor (collective when sharded).  `which`: master | grad | m | v | tau.
+        `grad` is the rank-summed gradient of the last synchronised backward, before averaging and clipping."""
         out = {}
+        if which == "grad":
+            self.finish_grad_sync()
         for u in self.units:
-            src = u.master if which == "master" else u.state.get(which)
+            src = u.master if which == "master" else u.grad_shard if which == "grad" else u.state.get(which)
             if src is None:
                 continue
             full = self._gather_full(src, u)

@@ -113,11 +113,13 @@ class Trainer:
             self.substep = self.curr_iter * cfg.acc_steps
         else:
             self.train_reader.set_step(0)
-        if self.master and getattr(cfg, "log_dynamics", False):
+        engine = getattr(self.backend.get_raw_model(self.model), "_engine", None)
+        gathers = engine is not None and engine.sharded and engine.world > 1   # then every rank takes part
+        if getattr(cfg, "log_dynamics", False) and (self.master or gathers):
             from ..logging.dynamics import DynamicsLogger, load_logger_config
 
             self.dlogger = DynamicsLogger(self.model, self.opt, load_logger_config(cfg.dynamics_logger_cfg),
-                                          cfg.results_base_folder, wandb=cfg.wandb)
+                                          self.exp_dir, wandb=cfg.wandb and self.master, write=self.master)
             self.dlogger.iteration = self.curr_iter
         if self.master and getattr(cfg, "collect_tau_stats", False) and cfg.opt in ("dana-star-mk4", "dana-star"):
             from ..logging.tau_stats import TauStatsCollector

@@ -325,3 +325,22 @@ def test_p2p_push_f32_and_barrier_timeout():
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="peer flag"):
         _lib.check_status()
+
+
+def test_newton_schulz_tcgen05_chain_matches_pytorch():
+    from adana_b200.ops import muon_ns
+    from adana_b200.optim.muon import newton_schulz5
+
+    torch.manual_seed(5)
+    for shape in ((256, 512), (768, 256), (384, 384)):
+        G = torch.randn(*shape, device=DEV, dtype=torch.bfloat16)
+        assert muon_ns.supported(G)
+        before = _lib.launch_count()
+        got = muon_ns.newton_schulz5_cuda(G, 5)
+        assert _lib.launch_count() - before == 15                 # three GEMM launches per iteration, nothing else
+        want = newton_schulz5(G.float(), 5)                       # fp32 oracle of the same iteration
+        assert got.shape == G.shape
+        err = (got.float() - want).norm() / want.norm()
+        assert err < 0.05, (shape, float(err))
+        sv = torch.linalg.svdvals(got.float())
+        assert 0.5 < float(sv.median()) < 1.3
