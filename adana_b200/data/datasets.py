@@ -215,3 +215,63 @@ def _with(args, **kw):
     for k, v in kw.items():
         setattr(a, k, v)
     return a
+
+
+# ---- command line: download (optional) and tokenise a corpus -----------------------------------
+def iter_parquet_texts(folder: Path, text_key: str = "text", batch_rows: int = 1000):
+    """Stream the text column of every `*.parquet` under `folder` (sorted), row group by row group."""
+    import pyarrow.parquet as pq
+
+    files = sorted(Path(folder).rglob("*.parquet"))
+    if not files:
+        raise FileNotFoundError(f"no .parquet files under {folder}")
+    for f in files:
+        pf = pq.ParquetFile(f)
+        for batch in pf.iter_batches(batch_size=batch_rows, columns=[text_key]):
+            yield from batch.column(0).to_pylist()
+
+
+def download_snapshot(spec: CorpusSpec, target: Path) -> Path:
+    """Fetch the parquet files of a Hugging Face sample (needs network and `huggingface_hub`)."""
+    try:
+        from huggingface_hub import snapshot_download
+    except ImportError as e:
+        raise RuntimeError("huggingface_hub is needed to download; use --skip-download with local parquet files") from e
+    pattern = f"sample/{spec.hf_name.split('-')[-1]}/*" if spec.hf_name and spec.hf_name.startswith("sample-") else None
+    return Path(snapshot_download(spec.hf_path, repo_type="dataset", local_dir=str(target),
+                                  allow_patterns=[pattern] if pattern else None))
+
+
+def main(argv=None) -> int:
+    """`python -m adana_b200.data.datasets --dataset fineweb_100 --download-dir ./fineweb --output-dir ./datasets`
+    — the two steps of the reference's `process_fineweb_100bt.py` (download the sample, tokenise it into
+    `train_XXXX.bin` + `val.bin`) for any corpus of the table; `--skip-download` tokenises local parquet files."""
+    import argparse
+
+    p = argparse.ArgumentParser(description="Download and tokenise a pre-training corpus")
+    p.add_argument("--dataset", default="fineweb_100", choices=sorted(CORPORA))
+    p.add_argument("--download-dir", default="./fineweb/")
+    p.add_argument("--output-dir", default="./datasets/")
+    p.add_argument("--skip-download", action="store_true")
+    p.add_argument("--tokens-per-file", type=int, default=1_000_000_000)
+    p.add_argument("--val-docs", type=int, default=1470)
+    a = p.parse_args(argv)
+    spec = CORPORA[a.dataset]
+    src = Path(a.download_dir)
+    if not a.skip_download:
+        print(f"step 1: downloading {spec.hf_path} ({spec.hf_name}) to {src}")
+        download_snapshot(spec, src)
+    root = Path(a.output_dir) / spec.subdir
+    if _existing_files(root, spec) is not None:
+        print(f"{root} already holds token files; nothing to do")
+        return 0
+    print(f"step 2: tokenising {src} into {root}")
+    prepare_corpus(spec, root, texts=iter_parquet_texts(src, spec.text_key), val_docs=a.val_docs,
+                   tokens_per_file=a.tokens_per_file)
+    found = _existing_files(root, spec) or {}
+    print(f"wrote {len(found)} files under {root}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
