@@ -23,6 +23,9 @@ extern "C" {
 
 // D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
 // a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
+// Tile shape policy of adana_gemm_bf16: 0 = per shape (default), 1 = one CTA per 128x256 tile,
+// 2 = CTA pair (cta_group::2) per 256x256 tile.  Returns the previous mode.
+int adana_gemm_set_mode(int mode);
 int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                     long long ldb, long long ldc, int a_mn, int b_mn, int epi, void* C2,
                     long long ldc2, const void* R, long long ldr, float alpha, float beta,

@@ -91,6 +91,129 @@ __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, float (&v
   }
 }
 
+// One warp's share of a finished accumulator: 32 rows (one per lane) x BN columns read from tensor
+// memory at `taddr`, pushed through the epilogue EPI and stored.  `n0` = first output column.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(const GemmArgs& args, uint32_t taddr, int row, bool row_ok,
+                                              int n0) {
+  if constexpr (EPI == EPI_SWIGLU) {
+    // accumulator columns [0,128) = gate, [128,256) = up
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rg[32], ru[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, rg);
+      tmem_ld_32x32b_x32(taddr + 128 + c * 32, ru);
+      tmem_wait_ld();
+      const int col = n0 + c * 32;
+      const int ncols_ok = args.N - col;
+      if (row_ok && ncols_ok > 0) {
+        float g[32], u[32], h[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          g[i] = __uint_as_float(rg[i]);
+          u[i] = __uint_as_float(ru[i]);
+          h[i] = g[i] * sigmoidf_(g[i]) * u[i];
+        }
+        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
+        store_bf16x32<EPI>(gu + col, g, ncols_ok);
+        store_bf16x32<EPI>(gu + args.b_off2 + col, u, ncols_ok);
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
+                           h, ncols_ok);
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, r);
+      tmem_wait_ld();
+      const int col = n0 + c * 32;
+      const int ncols_ok = args.N - col;
+      if (!row_ok || ncols_ok <= 0) continue;
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
+
+      if constexpr (EPI == EPI_BF16) {
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                           ncols_ok);
+      } else if constexpr (EPI == EPI_GELU_DUAL) {
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                           ncols_ok);
+        float h[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) h[i] = gelu_erf(v[i]);
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
+                           h, ncols_ok);
+      } else if constexpr (EPI == EPI_RESID_F32) {
+        const float* rp = reinterpret_cast<const float*>(args.R) + (long long)row * args.ldr + col;
+        float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j * 4 < ncols_ok) {
+            float4 x = *reinterpret_cast<const float4*>(rp + j * 4);
+            x.x += v[j * 4 + 0];
+            x.y += v[j * 4 + 1];
+            x.z += v[j * 4 + 2];
+            x.w += v[j * 4 + 3];
+            *reinterpret_cast<float4*>(cp + j * 4) = x;
+          }
+        }
+      } else if constexpr (EPI == EPI_DGELU) {
+        float z[32];
+        load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
+                     ncols_ok);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(z[i]);
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                           ncols_ok);
+      } else if constexpr (EPI == EPI_AXPBY_BF16) {
+        float z[32];
+        load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
+                     ncols_ok);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
+        store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
+                           ncols_ok);
+      } else if constexpr (EPI == EPI_F32) {
+        float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j * 4 < ncols_ok) {
+            float4 x = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            if (args.beta != 0.f) {
+              float4 o = *reinterpret_cast<const float4*>(cp + j * 4);
+              x.x += args.beta * o.x;
+              x.y += args.beta * o.y;
+              x.z += args.beta * o.z;
+              x.w += args.beta * o.w;
+            }
+            *reinterpret_cast<float4*>(cp + j * 4) = x;
+          }
+        }
+      } else if constexpr (EPI == EPI_DSWIGLU) {
+        // v = dH chunk; R holds [gate | up] pre-activations, C receives [dGate | dUp]
+        const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr;
+        float g[32], u[32];
+        load_bf16x32(gu + col, g, ncols_ok);
+        load_bf16x32(gu + args.b_off2 + col, u, ncols_ok);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = sigmoidf_(g[i]);
+          const float dh = v[i];
+          const float dgate = dh * u[i] * s * (1.f + g[i] * (1.f - s));
+          const float dup = dh * g[i] * s;
+          g[i] = dgate;
+          u[i] = dup;
+        }
+        __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
+        store_bf16x32<EPI>(dgu + col, g, ncols_ok);
+        store_bf16x32<EPI>(dgu + args.b_off2 + col, u, ncols_ok);
+      }
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -266,122 +389,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
       const int n0 = ni * TILE_N;
 
-      if constexpr (EPI == EPI_SWIGLU) {
-        // accumulator columns [0,128) = gate, [128,256) = up
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, rg);
-          tmem_ld_32x32b_x32(taddr + 128 + c * 32, ru);
-          tmem_wait_ld();
-          const int col = n0 + c * 32;
-          const int ncols_ok = args.N - col;
-          if (row_ok && ncols_ok > 0) {
-            float g[32], u[32], h[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              g[i] = __uint_as_float(rg[i]);
-              u[i] = __uint_as_float(ru[i]);
-              h[i] = g[i] * sigmoidf_(g[i]) * u[i];
-            }
-            __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
-            store_bf16x32<EPI>(gu + col, g, ncols_ok);
-            store_bf16x32<EPI>(gu + args.b_off2 + col, u, ncols_ok);
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
-                               h, ncols_ok);
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_wait_ld();
-          const int col = n0 + c * 32;
-          const int ncols_ok = args.N - col;
-          if (!row_ok || ncols_ok <= 0) continue;
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * args.alpha;
-
-          if constexpr (EPI == EPI_BF16) {
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
-                               ncols_ok);
-          } else if constexpr (EPI == EPI_GELU_DUAL) {
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
-                               ncols_ok);
-            float h[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) h[i] = gelu_erf(v[i]);
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C2) + (long long)row * args.ldc2 + col,
-                               h, ncols_ok);
-          } else if constexpr (EPI == EPI_RESID_F32) {
-            const float* rp = reinterpret_cast<const float*>(args.R) + (long long)row * args.ldr + col;
-            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (j * 4 < ncols_ok) {
-                float4 x = *reinterpret_cast<const float4*>(rp + j * 4);
-                x.x += v[j * 4 + 0];
-                x.y += v[j * 4 + 1];
-                x.z += v[j * 4 + 2];
-                x.w += v[j * 4 + 3];
-                *reinterpret_cast<float4*>(cp + j * 4) = x;
-              }
-            }
-          } else if constexpr (EPI == EPI_DGELU) {
-            float z[32];
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
-                         ncols_ok);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= gelu_erf_grad(z[i]);
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
-                               ncols_ok);
-          } else if constexpr (EPI == EPI_AXPBY_BF16) {
-            float z[32];
-            load_bf16x32(reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr + col, z,
-                         ncols_ok);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
-            store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
-                               ncols_ok);
-          } else if constexpr (EPI == EPI_F32) {
-            float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (j * 4 < ncols_ok) {
-                float4 x = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-                if (args.beta != 0.f) {
-                  float4 o = *reinterpret_cast<const float4*>(cp + j * 4);
-                  x.x += args.beta * o.x;
-                  x.y += args.beta * o.y;
-                  x.z += args.beta * o.z;
-                  x.w += args.beta * o.w;
-                }
-                *reinterpret_cast<float4*>(cp + j * 4) = x;
-              }
-            }
-          } else if constexpr (EPI == EPI_DSWIGLU) {
-            // v = dH chunk; R holds [gate | up] pre-activations, C receives [dGate | dUp]
-            const __nv_bfloat16* gu = reinterpret_cast<const __nv_bfloat16*>(args.R) + (long long)row * args.ldr;
-            float g[32], u[32];
-            load_bf16x32(gu + col, g, ncols_ok);
-            load_bf16x32(gu + args.b_off2 + col, u, ncols_ok);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float s = sigmoidf_(g[i]);
-              const float dh = v[i];
-              const float dgate = dh * u[i] * s * (1.f + g[i] * (1.f - s));
-              const float dup = dh * g[i] * s;
-              g[i] = dgate;
-              u[i] = dup;
-            }
-            __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
-            store_bf16x32<EPI>(dgu + col, g, ncols_ok);
-            store_bf16x32<EPI>(dgu + args.b_off2 + col, u, ncols_ok);
-          }
-        }
-      }
+      epilogue_rows<EPI>(args, taddr, row, row_ok, n0);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -393,6 +401,218 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster (on the two SMs of a TPC) compute one 256 x 256 tile
+// with cta_group::2 MMAs.  Each CTA stages only ITS 128 rows of A and ITS 128 of the 256 rows
+// (columns) of B, so a k-block costs 32 KiB of shared-memory fill per SM instead of 48 KiB and
+// half as many MMA instructions; the accumulator rows [0,128) live in the leader's tensor memory
+// and rows [128,256) in the peer's.  Protocol (leader = cluster rank 0):
+//   full[s]   on the leader only: one arrive.expect_tx (leader, both CTAs' bytes) + TMA bytes of both
+//   empty[s]  in each CTA: one commit per CTA from the leader's MMA thread
+//   tfull[b]  in each CTA: one commit per CTA;  tempty[b] on the leader: 8 arrivals (4 epilogue
+//   warps of each CTA).  The kernel ends with a cluster barrier so that neither CTA leaves while
+//   its partner may still touch its shared memory, barriers or tensor memory.
+constexpr int P_STAGES = 6;
+constexpr int P_TILE_BYTES = 128 * BK * 2;          // 16 KiB: this CTA's A rows, or its B rows
+constexpr int P_STAGE_BYTES = 2 * P_TILE_BYTES;     // 32 KiB
+constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int P_BM = 256;
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * P_STAGE_BYTES);
+  uint64_t* full_bar = bars;                       // [P_STAGES]  (used on the leader)
+  uint64_t* empty_bar = bars + P_STAGES;           // [P_STAGES]
+  uint64_t* tfull_bar = bars + 2 * P_STAGES;       // [2]
+  uint64_t* tempty_bar = bars + 2 * P_STAGES + 2;  // [2]         (used on the leader)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  constexpr bool GATED_FWD = (EPI == EPI_SWIGLU);
+  constexpr int TILE_N = GATED_FWD ? BN / 2 : BN;
+  const int num_tiles = args.tiles_m * args.tiles_n;
+  const int num_kb = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 8);
+    mbar_init(&tempty_bar[1], 8);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything remote is sent to them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ---------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      const uint32_t lead_full0 = mapa_smem(smem_u32(&full_bar[0]), 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs) {
+        int mi, ni;
+        tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        const int m0 = mi * P_BM + (int)rank * 128;  // this CTA's rows of A and of the output
+        const int n0 = ni * TILE_N;
+        // this CTA's 128 rows (columns) of B: second half of the tile, or the "up" rows when gated
+        const int nb0 = GATED_FWD ? (leader ? n0 : args.b_off2 + n0) : n0 + (int)rank * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status,
+                         ST_TIMEOUT_SMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * P_STAGE_BYTES;
+          uint8_t* sB = sA + P_TILE_BYTES;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
+          const uint32_t bar = lead_full0 + stage * 8;
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, bar, k0, m0);  // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d_pair(sA + c * CHUNK_BYTES, &tmA, bar, m0 + c * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, bar, k0, nb0);  // box {64 k, 128 n}
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_2d_pair(sB + c * CHUNK_BYTES, &tmB, bar, nb0 + c * 64, k0);
+          }
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Aborting: copies still in flight land within microseconds; give them a millisecond
+        // before this CTA heads for the final cluster barrier.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) -------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(P_BM, BN, A_MN, B_MN);
+      const uint32_t own_empty0 = smem_u32(&empty_bar[0]);
+      const uint32_t peer_empty0 = mapa_smem(own_empty0, 1);
+      const uint32_t own_tfull0 = smem_u32(&tfull_bar[0]);
+      const uint32_t peer_tfull0 = mapa_smem(own_tfull0, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs, ++it) {
+        const int buf = it & 1;
+        const uint32_t use = (uint32_t)(it >> 1);
+        if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status,
+                       ST_TIMEOUT_TMEM_EMPTY)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_TIMEOUT_SMEM_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sA = smem_u32(smem + stage * P_STAGE_BYTES);
+          const uint32_t sB = sA + P_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
+            else
+              da = make_smem_desc_sw128(sA + kk * 2048, CHUNK_BYTES, 1024);
+            if constexpr (!B_MN)
+              db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
+            else
+              db = make_smem_desc_sw128(sB + kk * 2048, CHUNK_BYTES, 1024);
+            umma_ss_pair(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          // the stage is free in BOTH CTAs once these MMAs retire
+          umma_commit_pair(own_empty0 + stage * 8);
+          umma_commit_pair(peer_empty0 + stage * 8);
+          if (++stage == P_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(own_tfull0 + buf * 8);
+          umma_commit_pair(peer_tfull0 + buf * 8);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5 of both CTAs) -----------------------
+    const int quad = warp & 3;
+    const uint32_t lead_tempty0 = mapa_smem(smem_u32(&tempty_bar[0]), 0);
+    int it = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += npairs, ++it) {
+      int mi, ni;
+      tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      const int buf = it & 1;
+      const uint32_t use = (uint32_t)(it >> 1);
+      if (!mbar_wait(&tfull_bar[buf], use & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const int row = mi * P_BM + (int)rank * 128 + quad * 32 + lane;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
+      epilogue_rows<EPI>(args, taddr, row, row_ok, ni * TILE_N);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_tempty0 + buf * 8);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -413,11 +633,45 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return (int)cudaGetLastError();
 }
 
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs args, int sm_count,
+                            cudaStream_t stream) {
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN, EPI>;
+  static int max_pairs = 0;  // co-resident CTA pairs, asked once per instantiation
+  if (max_pairs == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((sm_count / 2) * 2);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    max_pairs = n < sm_count / 2 ? n : sm_count / 2;
+  }
+  args.tiles_m = (args.M + P_BM - 1) / P_BM;
+  const int tiles = args.tiles_m * args.tiles_n;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, GEMM_THREADS, P_SMEM, stream>>>(tmA, tmB, args);
+  return (int)cudaGetLastError();
+}
+
 static int g_sm_count = 0;
+static int g_gemm_mode = 0;  // 0: choose per shape, 1: single-CTA tiles, 2: CTA-pair tiles
 
 }  // namespace adana
 
 using namespace adana;
+
+extern "C" int adana_gemm_set_mode(int mode) {
+  const int old = g_gemm_mode;
+  if (mode >= 0 && mode <= 2) g_gemm_mode = mode;
+  return old;
+}
 
 extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
                                long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
@@ -457,9 +711,16 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   args.group_m = 16;
   args.status = status;
 
+  // CTA-pair tiles are 256 rows tall: worth it when the pairs still get at least ~2 full waves.
+  bool use_pair = g_gemm_mode == 2;
+  if (g_gemm_mode == 0) {
+    const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
+    use_pair = pair_tiles >= 2 * (g_sm_count / 2);
+  }
 #define ADANA_GEMM_CASE(AM, BMN, E)                                                     \
   if (a_mn == (AM ? 1 : 0) && b_mn == (BMN ? 1 : 0) && epi == E)                        \
-    return launch_gemm<AM, BMN, E>(tmA, tmB, args, g_sm_count, stream);
+    return use_pair ? launch_gemm_pair<AM, BMN, E>(tmA, tmB, args, g_sm_count, stream)  \
+                    : launch_gemm<AM, BMN, E>(tmA, tmB, args, g_sm_count, stream);
   // forward (activations x weight^T)
   ADANA_GEMM_CASE(false, false, EPI_BF16)
   ADANA_GEMM_CASE(false, false, EPI_GELU_DUAL)

@@ -17,6 +17,15 @@ from . import _lib
 EPI_BF16, EPI_GELU_DUAL, EPI_RESID_F32, EPI_DGELU, EPI_F32, EPI_SWIGLU, EPI_DSWIGLU, EPI_AXPBY_BF16 = range(8)
 
 
+MODE_AUTO, MODE_SINGLE_CTA, MODE_CTA_PAIR = 0, 1, 2
+
+
+def set_mode(mode: int) -> int:
+    """Tile policy of the GEMM kernel: MODE_AUTO picks per shape between one CTA per 128x256 tile and a CTA
+    pair (cta_group::2) per 256x256 tile.  Returns the previous mode."""
+    return _lib.lib().adana_gemm_set_mode(int(mode))
+
+
 def _check2d(t: torch.Tensor, name: str):
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with a contiguous last dimension, got {tuple(t.shape)} / {t.stride()}")

@@ -3,7 +3,7 @@
 on the layer shapes of the flagship model and reports TFLOP/s and the fraction of the measured
 cuBLAS peak (MEASURED_PEAKS.json when present).
 
-    python benchmarks/gemm_bench.py [--shapes enoki36|square] [--iters 20] [--variant fwd|dgrad|wgrad|all]
+    python benchmarks/gemm_bench.py [--shapes enoki36|square] [--iters 20] [--variant fwd|dgrad|wgrad|all] [--mode 0|1|2]
 
 CUDA events on the launching stream, 3 warm-up calls, operands far larger than L2.
 """
@@ -44,7 +44,9 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--variant", default="all", choices=["fwd", "dgrad", "wgrad", "all"])
     ap.add_argument("--no_cublas", action="store_true")
+    ap.add_argument("--mode", type=int, default=0, help="0 per shape, 1 one CTA per tile, 2 CTA pair per tile")
     a = ap.parse_args()
+    gemm.set_mode(a.mode)
     peak = None
     pk = ROOT / "MEASURED_PEAKS.json"
     if pk.exists():
@@ -67,7 +69,7 @@ def main():
                 continue
             t = timeit(mine, a.iters)
             tf = 2 * M * N * K / t / 1e9
-            row = {"variant": name, "M": M, "N": N, "K": K, "ms": round(t, 4), "tflops": round(tf, 1)}
+            row = {"variant": name, "mode": a.mode, "M": M, "N": N, "K": K, "ms": round(t, 4), "tflops": round(tf, 1)}
             if not a.no_cublas:
                 tl = timeit(lib, a.iters)
                 row["cublas_tflops"] = round(2 * M * N * K / tl / 1e9, 1)

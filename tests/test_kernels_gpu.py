@@ -29,8 +29,16 @@ def _status():
     _lib.check_status()
 
 
+@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
+def gemm_mode(request):
+    """Every GEMM test runs once per tile policy (one CTA per tile / cta_group::2 pair per tile)."""
+    old = gemm.set_mode(request.param)
+    yield request.param
+    gemm.set_mode(old)
+
+
 @pytest.mark.parametrize("M,N,K", [(1024, 768, 512), (1000, 520, 328), (256, 2304, 192), (4096, 1024, 2048)])
-def test_gemm_fwd_dgrad_wgrad(M, N, K):
+def test_gemm_fwd_dgrad_wgrad(M, N, K, gemm_mode):
     torch.manual_seed(0)
     x, w, dy = rnd(M, K), rnd(N, K), rnd(M, N)
     assert rel_err(gemm.linear_fwd(x, w), x.float() @ w.float().t()) < 8e-3
@@ -42,7 +50,7 @@ def test_gemm_fwd_dgrad_wgrad(M, N, K):
     assert rel_err(dw, 1.5 * ref) < 1e-3
 
 
-def test_gemm_epilogues():
+def test_gemm_epilogues(gemm_mode):
     torch.manual_seed(1)
     M, N, K = 1024, 768, 512
     x, w, dy = rnd(M, K), rnd(N, K), rnd(M, N)
@@ -61,7 +69,7 @@ def test_gemm_epilogues():
     assert rel_err(gemm.linear_fwd_f32(x, w), ref) < 1e-4
 
 
-def test_gemm_swiglu():
+def test_gemm_swiglu(gemm_mode):
     torch.manual_seed(2)
     M, H, K = 512, 384, 256
     x, wgu = rnd(M, K), rnd(2 * H, K)
