@@ -194,6 +194,8 @@ GROUPS: dict[str, list[Flag]] = {
         F("--heads", type=int), T("--parallel_block"),
         F("--use_pretrained", default="none", type=str), T("--from_dense"),
         F("--init_std", default=0.02, type=float),
+        F("--init_compat", default="none", type=str, choices=["none", "reference"],
+          help="reference: initial weights bit-identical to the reference's for the same --seed (enoki, qwen3)"),
         F("--init-scheme", "--init_scheme", dest="init_scheme", default="KarpathyGPT2", type=str,
           choices=["KarpathyGPT2", "Standard", "ScaledGPT"]),
         F("--residual-stream-scalar", "--residual_stream_scalar", dest="residual_stream_scalar",

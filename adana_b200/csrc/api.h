@@ -15,6 +15,7 @@ enum {
   EPI_SWIGLU = 5,     // B = [gate; up] rows; C(bf16)=[gate|up] pre-activations, C2 = silu(g)*u
   EPI_DSWIGLU = 6,    // acc = dH; R = [gate|up]; C = [dGate|dUp]
   EPI_AXPBY_BF16 = 7, // C(bf16) = alpha * acc + beta * R(bf16); C may alias R
+  EPI_F32_ATOMIC = 8, // C(f32) += alpha * acc with vector atomics (internal: stream-K partial tiles)
 };
 
 #ifdef __cplusplus
@@ -24,7 +25,8 @@ extern "C" {
 // D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
 // a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
 // Tile shape policy of adana_gemm_bf16: 0 = per shape (default), 1 = one CTA per 128x256 tile,
-// 2 = CTA pair (cta_group::2) per 256x256 tile.  Returns the previous mode.
+// 2 = CTA pair (cta_group::2) per 256x256 tile, with stream-K for fp32 outputs whose whole-tile
+// waves would idle the machine, 3 = CTA pair without stream-K.  Returns the previous mode.
 int adana_gemm_set_mode(int mode);
 int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                     long long ldb, long long ldc, int a_mn, int b_mn, int epi, void* C2,

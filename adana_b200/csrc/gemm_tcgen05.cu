@@ -45,6 +45,7 @@ struct GemmArgs {
   float alpha, beta;
   int b_off2;  // gated-MLP epilogues: offset (rows of B / columns of C,R) of the "up" half
   int tiles_m, tiles_n, group_m;
+  int streamk;  // CTA-pair kernel only: split the K loops evenly over the pairs (atomic fp32 epilogue)
   int* status;
 };
 
@@ -175,6 +176,16 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& args, uint32_t tad
         for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
         store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
                            ncols_ok);
+      } else if constexpr (EPI == EPI_F32_ATOMIC) {
+        // several CTAs hold partial sums of this tile (split K): add them into C in L2
+        float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j * 4 < ncols_ok)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + j * 4),
+                         "f"(v[j * 4]), "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]), "f"(v[j * 4 + 3])
+                         : "memory");
+        }
       } else if constexpr (EPI == EPI_F32) {
         float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
 #pragma unroll
@@ -209,6 +220,8 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& args, uint32_t tad
         __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc;
         store_bf16x32<EPI>(dgu + col, g, ncols_ok);
         store_bf16x32<EPI>(dgu + args.b_off2 + col, u, ncols_ok);
+      } else {
+        static_assert(EPI < 0, "epilogue not implemented");
       }
     }
   }
@@ -415,11 +428,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 //   tfull[b]  in each CTA: one commit per CTA;  tempty[b] on the leader: 8 arrivals (4 epilogue
 //   warps of each CTA).  The kernel ends with a cluster barrier so that neither CTA leaves while
 //   its partner may still touch its shared memory, barriers or tensor memory.
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 7;
 constexpr int P_TILE_BYTES = 128 * BK * 2;          // 16 KiB: this CTA's A rows, or its B rows
 constexpr int P_STAGE_BYTES = 2 * P_TILE_BYTES;     // 32 KiB
 constexpr int P_SMEM = P_STAGES * P_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int P_BM = 256;
+
+// Work of one CTA pair: whole tiles dealt round-robin, or (stream-K) one contiguous, equal share of
+// all (tile, k-block) units cut at tile boundaries into segments; every segment is accumulated from
+// zero and added into C by the atomic epilogue, so partial tiles need no fix-up pass.
+struct PairWork {
+  int tile, kb0, kb1;  // current segment: k-blocks [kb0, kb1) of `tile`
+  long long u, u_end;
+  int num_kb, step;
+  bool sk;
+  __device__ PairWork(int pair, int npairs, int num_tiles, int num_kb_, bool streamk)
+      : tile(0), kb0(0), kb1(0), num_kb(num_kb_), step(npairs), sk(streamk) {
+    if (sk) {
+      const long long total = (long long)num_tiles * num_kb;
+      u = total * pair / npairs;
+      u_end = total * (pair + 1) / npairs;
+    } else {
+      u = pair;
+      u_end = num_tiles;
+    }
+  }
+  __device__ bool next() {
+    if (u >= u_end) return false;
+    if (sk) {
+      tile = (int)(u / num_kb);
+      kb0 = (int)(u - (long long)tile * num_kb);
+      const long long left = u_end - u;
+      kb1 = (left < (long long)(num_kb - kb0)) ? kb0 + (int)left : num_kb;
+      u += kb1 - kb0;
+    } else {
+      tile = (int)u;
+      kb0 = 0;
+      kb1 = num_kb;
+      u += step;
+    }
+    return true;
+  }
+};
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
@@ -478,14 +528,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs) {
+      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+      while (ok && w.next()) {
         int mi, ni;
-        tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
         const int m0 = mi * P_BM + (int)rank * 128;  // this CTA's rows of A and of the output
         const int n0 = ni * TILE_N;
         // this CTA's 128 rows (columns) of B: second half of the tile, or the "up" rows when gated
         const int nb0 = GATED_FWD ? (leader ? n0 : args.b_off2 + n0) : n0 + (int)rank * 128;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status,
                          ST_TIMEOUT_SMEM_EMPTY)) {
             ok = false;
@@ -536,7 +587,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs, ++it) {
+      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+      for (; ok && w.next(); ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
         if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status,
@@ -546,7 +598,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_TIMEOUT_SMEM_FULL)) {
             ok = false;
             break;
@@ -565,7 +617,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
               db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
             else
               db = make_smem_desc_sw128(sB + kk * 2048, CHUNK_BYTES, 1024);
-            umma_ss_pair(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_ss_pair(tmem_d, da, db, idesc, (kb != w.kb0 || kk != 0) ? 1u : 0u);
           }
           // the stage is free in BOTH CTAs once these MMAs retire
           umma_commit_pair(own_empty0 + stage * 8);
@@ -587,9 +639,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t lead_tempty0 = mapa_smem(smem_u32(&tempty_bar[0]), 0);
     int it = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += npairs, ++it) {
+    PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+    for (; ok && w.next(); ++it) {
       int mi, ni;
-      tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
       if (!mbar_wait(&tfull_bar[buf], use & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) {
@@ -655,13 +708,25 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   }
   args.tiles_m = (args.M + P_BM - 1) / P_BM;
   const int tiles = args.tiles_m * args.tiles_n;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  if (args.streamk) {
+    const long long units = (long long)tiles * ((args.K + BK - 1) / BK);
+    pairs = units < max_pairs ? (int)units : max_pairs;
+  }
   kern<<<2 * pairs, GEMM_THREADS, P_SMEM, stream>>>(tmA, tmB, args);
   return (int)cudaGetLastError();
 }
 
+static int launch_gemm_pair_dispatch_atomic(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                            const GemmArgs& args, int sm_count, cudaStream_t stream) {
+  if (a_mn && b_mn) return launch_gemm_pair<true, true, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
+  if (!a_mn && b_mn) return launch_gemm_pair<false, true, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
+  if (a_mn && !b_mn) return launch_gemm_pair<true, false, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
+  return launch_gemm_pair<false, false, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
+}
+
 static int g_sm_count = 0;
-static int g_gemm_mode = 0;  // 0: choose per shape, 1: single-CTA tiles, 2: CTA-pair tiles
+static int g_gemm_mode = 0;  // 0: per shape, 1: single-CTA tiles, 2: CTA-pair tiles (+stream-K), 3: pair, no stream-K
 
 }  // namespace adana
 
@@ -669,7 +734,7 @@ using namespace adana;
 
 extern "C" int adana_gemm_set_mode(int mode) {
   const int old = g_gemm_mode;
-  if (mode >= 0 && mode <= 2) g_gemm_mode = mode;
+  if (mode >= 0 && mode <= 3) g_gemm_mode = mode;
   return old;
 }
 
@@ -712,10 +777,27 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   args.status = status;
 
   // CTA-pair tiles are 256 rows tall: worth it when the pairs still get at least ~2 full waves.
-  bool use_pair = g_gemm_mode == 2;
-  if (g_gemm_mode == 0) {
-    const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
-    use_pair = pair_tiles >= 2 * (g_sm_count / 2);
+  const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
+  const int npairs = g_sm_count / 2;
+  bool use_pair = g_gemm_mode >= 2;
+  if (g_gemm_mode == 0) use_pair = pair_tiles >= 2 * npairs;
+  // fp32 accumulate-or-overwrite outputs (weight gradients: few tiles, long K) can split their K
+  // loops evenly over all pairs and add partial tiles atomically.  Measured on B200 the fp32 vector
+  // atomics of the partial tiles cost more than the idle tail they remove (16384x6912x2304 weight
+  // gradient: 0.56 ms against 0.41 ms with whole tiles), so the per-shape policy (mode 0) does not
+  // take this path; mode 2 keeps it selectable.
+  args.streamk = 0;
+  if (epi == EPI_F32 && (beta == 0.f || beta == 1.f) && g_gemm_mode == 2 &&
+      (K + BK - 1) / BK >= 8) {
+    const long long waves = (pair_tiles + npairs - 1) / npairs;
+    if ((double)pair_tiles < 0.9 * (double)(waves * npairs)) {
+      if (beta == 0.f) {
+        cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream);
+        if (e != cudaSuccess) return (int)e;
+      }
+      args.streamk = 1;
+      return launch_gemm_pair_dispatch_atomic(a_mn, b_mn, tmA, tmB, args, g_sm_count, stream);
+    }
   }
 #define ADANA_GEMM_CASE(AM, BMN, E)                                                     \
   if (a_mn == (AM ? 1 : 0) && b_mn == (BMN ? 1 : 0) && epi == E)                        \

@@ -1,9 +1,10 @@
 // Per-head QK-norm fused with the rotary embedding, forward and backward.
 //
-// One warp owns one (token, head) vector of head_dim = 64 or 128 elements; a lane holds
-// head_dim/32 consecutive elements, so the interleaved RoPE pairs (2i, 2i+1) are lane-local and
-// the norm statistics are one warp reduction.  Reads q and k straight out of the fused
-// projection output (any row pitch / head pitch), writes rotated q,k as [token, head, hd] bf16.
+// A (token, head) vector of head_dim = 64 or 128 elements is owned by head_dim/8 neighbouring lanes,
+// each holding 8 consecutive elements (one 16-byte access), so the interleaved RoPE pairs
+// (2i, 2i+1) are lane-local and the norm statistics are a 3- or 4-step shuffle reduction inside the
+// lane group.  Reads q and k straight out of the fused projection output (row pitch / head pitch
+// multiples of 8 elements), writes rotated q,k as [token, head, hd] bf16.
 //
 //   q' = rope(norm(q) * wq),  k' = rope(norm(k) * wk)
 //   norm kind 0: LayerNorm over head_dim (weight only, eps), 1: RMSNorm, 2: none
@@ -21,30 +22,62 @@
 namespace adana {
 
 constexpr int ROPE_THREADS = 256;
+constexpr int ROPE_EPL = 8;     // elements per lane: one 16-byte load of bf16
+constexpr int ROPE_UNROLL = 2;  // vectors in flight per lane group: hides load latency
 
-constexpr int ROPE_UNROLL = 4;  // (token, head) vectors in flight per warp: hides load latency
-
-template <int EPL>
-__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&x)[EPL]) {
-  if (EPL == 2) {
-    const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
-    x[0] = f.x; x[1] = f.y;
-  } else {
-    const uint2 u = *reinterpret_cast<const uint2*>(p);
-    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-    x[0] = a.x; x[1] = a.y; x[EPL - 2] = b.x; x[EPL - 1] = b.y;
-  }
+// A (token, head) vector of HD elements is owned by LPV = HD/8 neighbouring lanes (8 for head_dim
+// 64, 16 for 128), so a warp works on 32/LPV vectors at a time, every global access is 16 bytes per
+// lane, the interleaved RoPE pairs (2i, 2i+1) stay lane-local and a norm statistic costs log2(LPV)
+// shuffles shared by all the vectors of the warp.
+template <int LPV>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPV / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
-template <int EPL>
-__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&x)[EPL]) {
-  if (EPL == 2) {
-    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(x[0], x[1]);
-  } else {
-    uint2 u;
-    u.x = pack_bf16x2(x[0], x[1]);
-    u.y = pack_bf16x2(x[EPL - 2], x[EPL - 1]);
-    *reinterpret_cast<uint2*>(p) = u;
-  }
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&x)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&x)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(x[0], x[1]);
+  u.y = pack_bf16x2(x[2], x[3]);
+  u.z = pack_bf16x2(x[4], x[5]);
+  u.w = pack_bf16x2(x[6], x[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&x)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+// Which vector a lane group works on, and where it lives.
+struct RopeItem {
+  long long src_off;  // element offset of this lane's 8 values inside the projection output
+  long long out_off;  // element offset inside q_out / k_out ([token, head, hd])
+  int pos;
+  bool isq, ok;
+};
+
+template <int HD>
+__device__ __forceinline__ RopeItem rope_item(long long item, long long total, int Hq, int Hk, int S,
+                                              long long row_stride, int q_off, int q_hstride, int k_off,
+                                              int k_hstride, int sub) {
+  RopeItem r;
+  r.ok = item < total;
+  const long long it = r.ok ? item : 0;
+  const int Hall = Hq + Hk;
+  const long long tok = it / Hall;
+  const int h = (int)(it - tok * Hall);
+  r.isq = h < Hq;
+  const int hh = r.isq ? h : h - Hq;
+  r.src_off = tok * row_stride + (r.isq ? q_off + hh * q_hstride : k_off + hh * k_hstride) + sub * ROPE_EPL;
+  r.out_off = (tok * (r.isq ? Hq : Hk) + hh) * HD + sub * ROPE_EPL;
+  r.pos = (int)(tok % S);
+  return r;
 }
 
 template <int HD, int KIND>
@@ -54,41 +87,28 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
                        const float* __restrict__ wk, const float* __restrict__ freqs,
                        __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
                        long long n_tokens, int S, int Hq, int Hk, float eps) {
-  constexpr int EPL = HD / 32;  // elements per lane (2 or 4)
+  constexpr int LPV = HD / ROPE_EPL;
+  constexpr int VPW = 32 / LPV;
   constexpr int U = ROPE_UNROLL;
   const int lane = threadIdx.x & 31;
+  const int sub = lane % LPV, grp = lane / LPV;
   const long long warp_global = ((long long)blockIdx.x * ROPE_THREADS + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
-  const int Hall = Hq + Hk;
-  const long long total = n_tokens * Hall;
-  float wqr[EPL], wkr[EPL];
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    wqr[i] = (KIND != 2) ? wq[lane * EPL + i] : 1.f;
-    wkr[i] = (KIND != 2) ? wk[lane * EPL + i] : 1.f;
+  const long long total = n_tokens * (Hq + Hk);
+  float wqr[8], wkr[8];
+  if (KIND != 2) {
+    load8f(wq + sub * ROPE_EPL, wqr);
+    load8f(wk + sub * ROPE_EPL, wkr);
   }
-  for (long long base = warp_global * U; base < total; base += n_warps * U) {
-    float x[U][EPL];
-    float2 cs[U][EPL / 2];
-    long long tok[U];
-    int hh[U];
-    bool isq[U], ok[U];
+  for (long long base = warp_global * (VPW * U); base < total; base += n_warps * (VPW * U)) {
+    float x[U][8], cs[U][8];
+    RopeItem it[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long item = base + u;
-      ok[u] = item < total;
-      const long long it = ok[u] ? item : 0;
-      tok[u] = it / Hall;
-      const int h = (int)(it - tok[u] * Hall);
-      isq[u] = h < Hq;
-      hh[u] = isq[u] ? h : h - Hq;
-      const __nv_bfloat16* src = qkv + tok[u] * row_stride +
-                                 (isq[u] ? q_off + hh[u] * q_hstride : k_off + hh[u] * k_hstride) + lane * EPL;
-      load_vec<EPL>(src, x[u]);
-      const int pos = (int)(tok[u] % S);
-      const float2* fr = reinterpret_cast<const float2*>(freqs) + (long long)pos * (HD / 2) + lane * (EPL / 2);
-#pragma unroll
-      for (int i = 0; i < EPL / 2; ++i) cs[u][i] = fr[i];
+      it[u] = rope_item<HD>(base + u * VPW + grp, total, Hq, Hk, S, row_stride, q_off, q_hstride, k_off,
+                            k_hstride, sub);
+      load8(qkv + it[u].src_off, x[u]);
+      load8f(freqs + (long long)it[u].pos * HD + sub * ROPE_EPL, cs[u]);  // 4 (cos, sin) pairs
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -97,27 +117,24 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
         if (KIND == 0) {
           float s = 0.f;
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) s += x[u][i];
-          mean = warp_sum(s) * (1.f / HD);
+          for (int i = 0; i < 8; ++i) s += x[u][i];
+          mean = group_sum<LPV>(s) * (1.f / HD);
         }
         float q = 0.f;
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
-        const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
+        for (int i = 0; i < 8; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
+        const float rstd = rsqrtf(group_sum<LPV>(q) * (1.f / HD) + eps);
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) x[u][i] = (x[u][i] - mean) * rstd * (isq[u] ? wqr[i] : wkr[i]);
+        for (int i = 0; i < 8; ++i) x[u][i] = (x[u][i] - mean) * rstd * (it[u].isq ? wqr[i] : wkr[i]);
       }
-      float o[EPL];
+      float o[8];
 #pragma unroll
-      for (int i = 0; i < EPL / 2; ++i) {
-        const float c = cs[u][i].x, s = cs[u][i].y;
+      for (int i = 0; i < 4; ++i) {
+        const float c = cs[u][2 * i], s = cs[u][2 * i + 1];
         o[2 * i] = x[u][2 * i] * c - x[u][2 * i + 1] * s;
         o[2 * i + 1] = x[u][2 * i] * s + x[u][2 * i + 1] * c;
       }
-      if (ok[u]) {
-        __nv_bfloat16* dst = (isq[u] ? q_out + (tok[u] * Hq + hh[u]) * HD : k_out + (tok[u] * Hk + hh[u]) * HD) + lane * EPL;
-        store_vec<EPL>(dst, o);
-      }
+      if (it[u].ok) store8((it[u].isq ? q_out : k_out) + it[u].out_off, o);
     }
   }
 }
@@ -131,95 +148,95 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
                        __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dwq_partial,
                        float* __restrict__ dwk_partial, long long n_tokens, int S, int Hq, int Hk,
                        float eps) {
-  constexpr int EPL = HD / 32;
+  constexpr int LPV = HD / ROPE_EPL;
+  constexpr int VPW = 32 / LPV;
   constexpr int U = ROPE_UNROLL;
   __shared__ float sdw[2][ROPE_THREADS / 32][HD];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int sub = lane % LPV, grp = lane / LPV;
   const long long warp_global = ((long long)blockIdx.x * ROPE_THREADS + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
-  const int Hall = Hq + Hk;
-  const long long total = n_tokens * Hall;
-  float dwq_acc[EPL], dwk_acc[EPL], wqr[EPL], wkr[EPL];
+  const long long total = n_tokens * (Hq + Hk);
+  float dwq_acc[8], dwk_acc[8], wqr[8], wkr[8];
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) {
-    dwq_acc[i] = dwk_acc[i] = 0.f;
-    wqr[i] = (KIND != 2) ? wq[lane * EPL + i] : 1.f;
-    wkr[i] = (KIND != 2) ? wk[lane * EPL + i] : 1.f;
+  for (int i = 0; i < 8; ++i) dwq_acc[i] = dwk_acc[i] = 0.f;
+  if (KIND != 2) {
+    load8f(wq + sub * ROPE_EPL, wqr);
+    load8f(wk + sub * ROPE_EPL, wkr);
   }
-  for (long long base = warp_global * U; base < total; base += n_warps * U) {
-    float x[U][EPL], d[U][EPL];
-    float2 cs[U][EPL / 2];
-    long long off[U];
-    bool isq[U], ok[U];
+  for (long long base = warp_global * (VPW * U); base < total; base += n_warps * (VPW * U)) {
+    float x[U][8], d[U][8], cs[U][8];
+    RopeItem it[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long item = base + u;
-      ok[u] = item < total;
-      const long long it = ok[u] ? item : 0;
-      const long long tok = it / Hall;
-      const int h = (int)(it - tok * Hall);
-      isq[u] = h < Hq;
-      const int hh = isq[u] ? h : h - Hq;
-      off[u] = tok * row_stride + (isq[u] ? q_off + hh * q_hstride : k_off + hh * k_hstride) + lane * EPL;
-      const __nv_bfloat16* gsrc = (isq[u] ? dq + (tok * Hq + hh) * HD : dk + (tok * Hk + hh) * HD) + lane * EPL;
-      load_vec<EPL>(qkv + off[u], x[u]);
-      load_vec<EPL>(gsrc, d[u]);
-      const int pos = (int)(tok % S);
-      const float2* fr = reinterpret_cast<const float2*>(freqs) + (long long)pos * (HD / 2) + lane * (EPL / 2);
-#pragma unroll
-      for (int i = 0; i < EPL / 2; ++i) cs[u][i] = fr[i];
+      it[u] = rope_item<HD>(base + u * VPW + grp, total, Hq, Hk, S, row_stride, q_off, q_hstride, k_off,
+                            k_hstride, sub);
+      load8(qkv + it[u].src_off, x[u]);
+      load8((it[u].isq ? dq : dk) + it[u].out_off, d[u]);
+      load8f(freqs + (long long)it[u].pos * HD + sub * ROPE_EPL, cs[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       // undo the rotation: gradient w.r.t. the normalised, weighted vector
-      float dn[EPL];
+      float dn[8];
 #pragma unroll
-      for (int i = 0; i < EPL / 2; ++i) {
-        const float c = cs[u][i].x, s = cs[u][i].y;
+      for (int i = 0; i < 4; ++i) {
+        const float c = cs[u][2 * i], s = cs[u][2 * i + 1];
         dn[2 * i] = d[u][2 * i] * c + d[u][2 * i + 1] * s;
         dn[2 * i + 1] = -d[u][2 * i] * s + d[u][2 * i + 1] * c;
       }
-      float dx[EPL];
+      float dx[8];
       if (KIND == 2) {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) dx[i] = dn[i];
+        for (int i = 0; i < 8; ++i) dx[i] = dn[i];
       } else {
         float mean = 0.f;
         if (KIND == 0) {
           float s = 0.f;
 #pragma unroll
-          for (int i = 0; i < EPL; ++i) s += x[u][i];
-          mean = warp_sum(s) * (1.f / HD);
+          for (int i = 0; i < 8; ++i) s += x[u][i];
+          mean = group_sum<LPV>(s) * (1.f / HD);
         }
         float q = 0.f;
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
-        const float rstd = rsqrtf(warp_sum(q) * (1.f / HD) + eps);
-        float xh[EPL], g[EPL], s1 = 0.f, s2 = 0.f;
-        const float live = ok[u] ? 1.f : 0.f;
+        for (int i = 0; i < 8; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
+        const float rstd = rsqrtf(group_sum<LPV>(q) * (1.f / HD) + eps);
+        float xh[8], g[8], s1 = 0.f, s2 = 0.f;
+        const float live = it[u].ok ? 1.f : 0.f;
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) {
+        for (int i = 0; i < 8; ++i) {
           xh[i] = (x[u][i] - mean) * rstd;
-          g[i] = dn[i] * (isq[u] ? wqr[i] : wkr[i]);
+          g[i] = dn[i] * (it[u].isq ? wqr[i] : wkr[i]);
           s1 += g[i];
           s2 += g[i] * xh[i];
-          if (isq[u]) dwq_acc[i] += live * dn[i] * xh[i];
+          if (it[u].isq) dwq_acc[i] += live * dn[i] * xh[i];
           else dwk_acc[i] += live * dn[i] * xh[i];
         }
-        const float m2 = warp_sum(s2) * (1.f / HD);
-        const float m1 = (KIND == 0) ? warp_sum(s1) * (1.f / HD) : 0.f;
+        const float m2 = group_sum<LPV>(s2) * (1.f / HD);
+        const float m1 = (KIND == 0) ? group_sum<LPV>(s1) * (1.f / HD) : 0.f;
 #pragma unroll
-        for (int i = 0; i < EPL; ++i) dx[i] = rstd * (g[i] - m1 - xh[i] * m2);
+        for (int i = 0; i < 8; ++i) dx[i] = rstd * (g[i] - m1 - xh[i] * m2);
       }
-      if (ok[u]) store_vec<EPL>(dqkv + off[u], dx);
+      if (it[u].ok) store8(dqkv + it[u].src_off, dx);
     }
   }
   if (KIND != 2 && dwq_partial) {
+    // fold the VPW lane groups of the warp (same columns, different vectors), then the warps
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      sdw[0][warp][lane * EPL + i] = dwq_acc[i];
-      sdw[1][warp][lane * EPL + i] = dwk_acc[i];
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int o = LPV; o < 32; o <<= 1) {
+        dwq_acc[i] += __shfl_xor_sync(0xffffffffu, dwq_acc[i], o);
+        dwk_acc[i] += __shfl_xor_sync(0xffffffffu, dwk_acc[i], o);
+      }
+    }
+    if (grp == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sdw[0][warp][sub * ROPE_EPL + i] = dwq_acc[i];
+        sdw[1][warp][sub * ROPE_EPL + i] = dwk_acc[i];
+      }
     }
     __syncthreads();
     for (int c = threadIdx.x; c < 2 * HD; c += ROPE_THREADS) {
@@ -244,9 +261,10 @@ extern "C" int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   if (n_tokens <= 0) return 0;
   if (hd != 64 && hd != 128) return -1;
-  if ((row_stride & 3) || (q_off & 3) || (k_off & 3) || (q_hstride & 3) || (k_hstride & 3)) return -2;
+  if ((row_stride & 7) || (q_off & 7) || (k_off & 7) || (q_hstride & 7) || (k_hstride & 7)) return -2;  // 16-byte lanes
   const long long items = n_tokens * (Hq + Hk);
-  long long blocks = (items + 8 * ROPE_UNROLL - 1) / (8 * ROPE_UNROLL);
+  const int per_block = (ROPE_THREADS / 32) * (32 / (hd / ROPE_EPL)) * ROPE_UNROLL;
+  long long blocks = (items + per_block - 1) / per_block;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
 #define RF(HD_, K_)                                                                          \
@@ -272,6 +290,7 @@ extern "C" int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void*
   if (n_tokens <= 0) return 0;
   if (hd != 64 && hd != 128) return -1;
   if (kind != 2 && n_partial <= 0) return -3;
+  if ((row_stride & 7) || (q_off & 7) || (k_off & 7) || (q_hstride & 7) || (k_hstride & 7)) return -2;
   const int blocks = kind != 2 ? n_partial : 148 * 8;
 #define RB(HD_, K_)                                                                          \
   qknorm_rope_bwd_kernel<HD_, K_><<<blocks, ROPE_THREADS, 0, st>>>(                          \

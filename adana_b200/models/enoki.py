@@ -122,8 +122,13 @@ class Enoki(BaseLM):
         ))
         self.lm_head = nn.Linear(config.n_embd, config.vocab_size, bias=False)
         scheme, std = cfg_get(config, "init_scheme", "KarpathyGPT2"), cfg_get(config, "init_std", 0.02)
-        self.apply(lambda m: init_module_weights(m, scheme, std))
-        depth_scaled_init_(self.named_parameters(), ("c_proj.weight",), scheme, std, config.n_layer)
+        if cfg_get(config, "init_compat", "none") == "reference":
+            from .init_compat import reference_compatible_init_
+
+            reference_compatible_init_(self, config, "enoki", ("c_proj.weight",))
+        else:
+            self.apply(lambda m: init_module_weights(m, scheme, std))
+            depth_scaled_init_(self.named_parameters(), ("c_proj.weight",), scheme, std, config.n_layer)
 
     @staticmethod
     def get_tp_plan():

@@ -126,8 +126,13 @@ class Qwen3(BaseLM):
         if config.weight_tying:
             self.transformer.wte.weight = self.lm_head.weight
         scheme, std = cfg_get(config, "init_scheme", "KarpathyGPT2"), cfg_get(config, "init_std", 0.02)
-        self.apply(lambda m: init_module_weights(m, scheme, std))
-        depth_scaled_init_(self.named_parameters(), self.residual_out_suffixes, scheme, std, config.n_layer)
+        if cfg_get(config, "init_compat", "none") == "reference" and self.arch == "qwen3":
+            from .init_compat import reference_compatible_init_
+
+            reference_compatible_init_(self, config, "qwen3", tuple(self.residual_out_suffixes))
+        else:
+            self.apply(lambda m: init_module_weights(m, scheme, std))
+            depth_scaled_init_(self.named_parameters(), self.residual_out_suffixes, scheme, std, config.n_layer)
 
     @staticmethod
     def get_tp_plan():

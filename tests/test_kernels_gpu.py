@@ -29,9 +29,10 @@ def _status():
     _lib.check_status()
 
 
-@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
+@pytest.fixture(params=[0, 1, 2, 3], ids=["auto", "single_cta", "cta_pair_streamk", "cta_pair"])
 def gemm_mode(request):
-    """Every GEMM test runs once per tile policy (one CTA per tile / cta_group::2 pair per tile)."""
+    """Every GEMM test runs once per tile policy (per shape / one CTA per tile / cta_group::2 pair per tile
+    with and without stream-K for fp32 outputs)."""
     old = gemm.set_mode(request.param)
     yield request.param
     gemm.set_mode(old)
@@ -48,6 +49,26 @@ def test_gemm_fwd_dgrad_wgrad(M, N, K, gemm_mode):
     assert rel_err(dw, ref) < 1e-3
     gemm.linear_wgrad(dy, x, out=dw, accumulate=True, alpha=0.5)
     assert rel_err(dw, 1.5 * ref) < 1e-3
+
+
+def test_gemm_wgrad_stream_k_partial_tiles():
+    """81 pair tiles on 74 pairs: the K loops are split over all pairs and partial tiles meet in C atomically."""
+    torch.manual_seed(3)
+    M, N, K = 4096, 2304, 2304
+    x, dy = rnd(M, K), rnd(M, N)
+    ref = dy.float().t() @ x.float()
+    old = gemm.set_mode(2)
+    try:
+        dw = torch.full((N, K), 7.0, device=DEV)            # overwrite mode must not see old contents
+        gemm.linear_wgrad(dy, x, out=dw)
+        assert rel_err(dw, ref) < 1e-3
+        gemm.linear_wgrad(dy, x, out=dw, accumulate=True, alpha=0.25)
+        assert rel_err(dw, 1.25 * ref) < 1e-3
+        view = torch.zeros(N, K + 64, device=DEV)[:, :K]    # row pitch larger than the row
+        gemm.linear_wgrad(dy, x, out=view)
+        assert rel_err(view, ref) < 1e-3
+    finally:
+        gemm.set_mode(old)
 
 
 def test_gemm_epilogues(gemm_mode):
