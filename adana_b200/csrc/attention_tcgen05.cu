@@ -35,9 +35,7 @@ struct AttFwdSmem {
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = TILE;
   static constexpr int V_OFF = K_OFF + ATT_KV_STAGES * TILE;
-  static constexpr int P_OFF = V_OFF + ATT_KV_STAGES * TILE;
-  static constexpr int P_BYTES = ATT_BQ * ATT_BKV * 2;    // 32 KiB
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int BAR_OFF = V_OFF + ATT_KV_STAGES * TILE;
   static constexpr int TOTAL = BAR_OFF + 256;              // + barriers (the base is 1024-byte aligned)
 };
 
@@ -56,8 +54,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   using L = AttFwdSmem<HD>;
   constexpr int CHUNKS = HD / 64;                 // 64-column (128-byte) chunks per tile row
   constexpr int CHUNK_BYTES = ATT_BQ * 128;       // [128 rows][128 B]
-  constexpr uint32_t TMEM_COLS = (S_BUFS * 128 + HD) <= 256 ? 256 : 512;
+  // tensor memory columns: S buffers | O accumulator | P (bf16 pairs: 64 columns for 128 keys)
   constexpr uint32_t O_COL = S_BUFS * 128;
+  constexpr uint32_t P_COL = O_COL + HD;
+  constexpr uint32_t TMEM_COLS = (P_COL + ATT_BKV / 2) <= 256 ? 256 : 512;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -157,7 +157,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BQ, HD, false, true);
       const uint32_t sQ = smem_u32(smem + L::Q_OFF);
-      const uint32_t sP = smem_u32(smem + L::P_OFF);
       bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
       tc_fence_after_sync();
       auto issue_pv = [&](int jj) -> bool {
@@ -169,9 +168,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t sV = smem_u32(smem + L::V_OFF + st * L::TILE);
 #pragma unroll
         for (int kk = 0; kk < ATT_BKV / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(sP + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
+          // A = P_j straight from tensor memory: 16 keys = 8 columns of packed bf16 pairs per step
           const uint64_t db = make_smem_desc_sw128(sV + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss(tmem_base + O_COL, da, db, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem_base + O_COL, tmem_base + P_COL + kk * 8, db, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&kv_empty[st]);   // K_j / V_j stage free again
         umma_commit(p_empty);          // P buffer free, O updated
@@ -206,7 +205,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int quad = warp & 3;
     const int r = quad * 32 + lane;              // query row inside the tile
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    uint8_t* sP = smem + L::P_OFF;
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
@@ -223,28 +221,37 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // flight while the current one is processed.  Probabilities are taken relative to the running
       // reference maximum m_ref, which only moves when a chunk exceeds it by more than 2^8; then
       // the row sum, the chunks already packed and (later) the output accumulator are rescaled.
+      // Only the diagonal tile pays for masking.  The arithmetic is packed two columns per
+      // instruction (f32x2 FMA / add, three-input max) because this loop, not the tensor pipe,
+      // bounds the kernel at head_dim 64.
       uint32_t pk[64];
-      float lacc = 0.f, o_factor = 1.f;
+      float2 lacc2 = make_float2(0.f, 0.f);
+      float o_factor = 1.f;
       uint32_t va[32], vb[32];
       tmem_ld_32x32b_x32(s_addr, va);
       tmem_wait_ld();
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t(&cur)[32] = (c & 1) ? vb : va;
         uint32_t(&nxt)[32] = (c & 1) ? va : vb;
         if (c < 3) tmem_ld_32x32b_x32(s_addr + (c + 1) * 32, nxt);
-        float cmax = -INFINITY;
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(cur[i]);
-          if (diag && (c * 32 + i) > r) x = -INFINITY;
-          cmax = fmaxf(cmax, x);
+          for (int i = 0; i < 32; ++i)
+            if ((c * 32 + i) > r) cur[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
         }
+        float cmax = fmax3(__uint_as_float(cur[0]), __uint_as_float(cur[1]), __uint_as_float(cur[2]));
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2)
+          cmax = fmax3(cmax, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+        cmax = fmaxf(cmax, __uint_as_float(cur[31]));
         const float m_c = cmax * args.scale_log2;
         if (m_c > m_ref + ATT_RESCALE_THRESHOLD) {
-          const float f = exp2f(m_ref - m_c);      // 0 on the very first chunk (m_ref = -inf)
+          const float f = ex2_approx(m_ref - m_c);      // 0 on the very first chunk (m_ref = -inf)
           l_sum *= f;
-          lacc *= f;
+          lacc2.x *= f;
+          lacc2.y *= f;
           o_factor *= f;
 #pragma unroll
           for (int cc = 0; cc < c; ++cc) {
@@ -256,19 +263,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           m_ref = m_c;
         }
+        const float2 nm2 = make_float2(-m_ref, -m_ref);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(cur[i]) * args.scale_log2 - m_ref);
-          float p1 = exp2f(__uint_as_float(cur[i + 1]) * args.scale_log2 - m_ref);
-          if (diag) {
-            if ((c * 32 + i) > r) p0 = 0.f;
-            if ((c * 32 + i + 1) > r) p1 = 0.f;
-          }
-          lacc += p0 + p1;
-          pk[c * 16 + (i >> 1)] = pack_bf16x2(p0, p1);
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(cur[i]), __uint_as_float(cur[i + 1])), sc2, nm2);
+          const float2 p2 = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+          lacc2 = __fadd2_rn(lacc2, p2);
+          pk[c * 16 + (i >> 1)] = pack_bf16x2(p2.x, p2.y);
         }
         if (c < 3) tmem_wait_ld();
       }
+      const float lacc = lacc2.x + lacc2.y;
       l_sum += lacc;
       const bool grow = o_factor != 1.f;
       const float factor = o_factor;
@@ -298,14 +303,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_wait_st();
         }
       }
-      // write P_j (bf16) into the swizzled K-major tile: row r, 16-byte unit u of chunk ch
-#pragma unroll
-      for (int u16 = 0; u16 < 16; ++u16) {
-        const int ch = u16 >> 3, u = u16 & 7;
-        uint4 val = make_uint4(pk[u16 * 4 + 0], pk[u16 * 4 + 1], pk[u16 * 4 + 2], pk[u16 * 4 + 3]);
-        *reinterpret_cast<uint4*>(sP + ch * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4)) = val;
+      // P_j (bf16 pairs) goes to tensor memory, where the PV MMA reads it as its A operand: lane r
+      // writes its row's 64 packed columns
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        tmem_st_32x32b_x32(tmem_base + P_COL + lane_addr, lo);
+        tmem_st_32x32b_x32(tmem_base + P_COL + lane_addr + 32, hi);
+        tmem_wait_st();
       }
-      fence_proxy_async_smem();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);

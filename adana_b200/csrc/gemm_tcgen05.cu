@@ -45,7 +45,7 @@ struct GemmArgs {
   float alpha, beta;
   int b_off2;  // gated-MLP epilogues: offset (rows of B / columns of C,R) of the "up" half
   int tiles_m, tiles_n, group_m;
-  int streamk;  // CTA-pair kernel only: split the K loops evenly over the pairs (atomic fp32 epilogue)
+  int streamk;  // CTA-pair kernel, fp32 output: 0 whole tiles, 1 every K loop cut, 2 only the last wave's
   int* status;
 };
 
@@ -439,34 +439,37 @@ constexpr int P_BM = 256;
 // zero and added into C by the atomic epilogue, so partial tiles need no fix-up pass.
 struct PairWork {
   int tile, kb0, kb1;  // current segment: k-blocks [kb0, kb1) of `tile`
+  bool partial;        // the segment is a share of a tile: its result is ADDED into C atomically
+  int next_tile, whole_end, step, num_kb;
   long long u, u_end;
-  int num_kb, step;
-  bool sk;
-  __device__ PairWork(int pair, int npairs, int num_tiles, int num_kb_, bool streamk)
-      : tile(0), kb0(0), kb1(0), num_kb(num_kb_), step(npairs), sk(streamk) {
-    if (sk) {
-      const long long total = (long long)num_tiles * num_kb;
-      u = total * pair / npairs;
-      u_end = total * (pair + 1) / npairs;
-    } else {
-      u = pair;
-      u_end = num_tiles;
-    }
+  int split_first;
+  // mode 0: whole tiles round-robin.  1: every tile's K loop is cut (pure stream-K).
+  // 2: the full waves are whole tiles; only the tiles of the last, incomplete wave are cut.
+  __device__ PairWork(int pair, int npairs, int num_tiles, int num_kb_, int mode)
+      : tile(0), kb0(0), kb1(0), partial(false), next_tile(pair), step(npairs), num_kb(num_kb_) {
+    whole_end = mode == 0 ? num_tiles : mode == 1 ? 0 : (num_tiles / npairs) * npairs;
+    split_first = whole_end;
+    const long long total = (long long)(num_tiles - whole_end) * num_kb;
+    u = total * pair / npairs;
+    u_end = total * (pair + 1) / npairs;
   }
   __device__ bool next() {
-    if (u >= u_end) return false;
-    if (sk) {
-      tile = (int)(u / num_kb);
-      kb0 = (int)(u - (long long)tile * num_kb);
-      const long long left = u_end - u;
-      kb1 = (left < (long long)(num_kb - kb0)) ? kb0 + (int)left : num_kb;
-      u += kb1 - kb0;
-    } else {
-      tile = (int)u;
+    if (next_tile < whole_end) {
+      tile = next_tile;
       kb0 = 0;
       kb1 = num_kb;
-      u += step;
+      partial = false;
+      next_tile += step;
+      return true;
     }
+    if (u >= u_end) return false;
+    const int t = (int)(u / num_kb);
+    tile = split_first + t;
+    kb0 = (int)(u - (long long)t * num_kb);
+    const long long left = u_end - u;
+    kb1 = (left < (long long)(num_kb - kb0)) ? kb0 + (int)left : num_kb;
+    u += kb1 - kb0;
+    partial = true;
     return true;
   }
 };
@@ -528,7 +531,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk);
       while (ok && w.next()) {
         int mi, ni;
         tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
@@ -587,7 +590,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+      PairWork w(pair, npairs, num_tiles, num_kb, args.streamk);
       for (; ok && w.next(); ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
@@ -639,7 +642,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const uint32_t lead_tempty0 = mapa_smem(smem_u32(&tempty_bar[0]), 0);
     int it = 0;
     bool ok = true;
-    PairWork w(pair, npairs, num_tiles, num_kb, args.streamk != 0);
+    PairWork w(pair, npairs, num_tiles, num_kb, args.streamk);
     for (; ok && w.next(); ++it) {
       int mi, ni;
       tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
@@ -653,7 +656,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int row = mi * P_BM + (int)rank * 128 + quad * 32 + lane;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(quad * 32) << 16);
-      epilogue_rows<EPI>(args, taddr, row, row_ok, ni * TILE_N);
+      if constexpr (EPI == EPI_F32) {
+        if (w.partial) epilogue_rows<EPI_F32_ATOMIC>(args, taddr, row, row_ok, ni * TILE_N);
+        else epilogue_rows<EPI_F32>(args, taddr, row, row_ok, ni * TILE_N);
+      } else {
+        epilogue_rows<EPI>(args, taddr, row, row_ok, ni * TILE_N);
+      }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_tempty0 + buf * 8);
@@ -717,14 +725,6 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   return (int)cudaGetLastError();
 }
 
-static int launch_gemm_pair_dispatch_atomic(int a_mn, int b_mn, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                                            const GemmArgs& args, int sm_count, cudaStream_t stream) {
-  if (a_mn && b_mn) return launch_gemm_pair<true, true, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
-  if (!a_mn && b_mn) return launch_gemm_pair<false, true, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
-  if (a_mn && !b_mn) return launch_gemm_pair<true, false, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
-  return launch_gemm_pair<false, false, EPI_F32_ATOMIC>(tmA, tmB, args, sm_count, stream);
-}
-
 static int g_sm_count = 0;
 static int g_gemm_mode = 0;  // 0: per shape, 1: single-CTA tiles, 2: CTA-pair tiles (+stream-K), 3: pair, no stream-K
 
@@ -780,23 +780,26 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
   const int npairs = g_sm_count / 2;
   bool use_pair = g_gemm_mode >= 2;
-  if (g_gemm_mode == 0) use_pair = pair_tiles >= 2 * npairs;
-  // fp32 accumulate-or-overwrite outputs (weight gradients: few tiles, long K) can split their K
-  // loops evenly over all pairs and add partial tiles atomically.  Measured on B200 the fp32 vector
-  // atomics of the partial tiles cost more than the idle tail they remove (16384x6912x2304 weight
-  // gradient: 0.56 ms against 0.41 ms with whole tiles), so the per-shape policy (mode 0) does not
-  // take this path; mode 2 keeps it selectable.
+  if (g_gemm_mode == 0) use_pair = pair_tiles >= 2 * npairs || (epi == EPI_F32 && pair_tiles >= npairs);
+  // fp32 accumulate-or-overwrite outputs (weight gradients: few tiles, long K).  Whole tiles leave
+  // the machine idle in the last wave (243 tiles on 74 pairs: a fourth wave for 21 tiles).  Cutting
+  // EVERY K loop and adding partial tiles atomically (mode 2) costs more in fp32 vector atomics than
+  // it saves (measured 0.56 ms against 0.41 ms for the 16384x6912x2304 weight gradient), so the
+  // per-shape policy cuts only the tiles of that last, incomplete wave: the full waves store
+  // normally and at most one atomic partial per pair is added.
   args.streamk = 0;
-  if (epi == EPI_F32 && (beta == 0.f || beta == 1.f) && g_gemm_mode == 2 &&
-      (K + BK - 1) / BK >= 8) {
-    const long long waves = (pair_tiles + npairs - 1) / npairs;
-    if ((double)pair_tiles < 0.9 * (double)(waves * npairs)) {
+  if (epi == EPI_F32 && (beta == 0.f || beta == 1.f) && use_pair && (K + BK - 1) / BK >= 8 &&
+      (g_gemm_mode == 0 || g_gemm_mode == 2)) {
+    const long long rem = pair_tiles % npairs;
+    const bool tail_idle = rem != 0 && rem * 10 < npairs * 9;
+    if (g_gemm_mode == 2 || tail_idle) {
+      args.streamk = g_gemm_mode == 2 ? 1 : 2;
       if (beta == 0.f) {
+        // partial tiles are added, not stored: start them from zero
         cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, stream);
         if (e != cudaSuccess) return (int)e;
+        args.beta = 0.f;
       }
-      args.streamk = 1;
-      return launch_gemm_pair_dispatch_atomic(a_mn, b_mn, tmA, tmB, args, g_sm_count, stream);
     }
   }
 #define ADANA_GEMM_CASE(AM, BMN, E)                                                     \

@@ -122,8 +122,11 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                 float* __restrict__ dx, int accumulate_dx, float* __restrict__ dw_partial, int rows,
                 int cols, __nv_bfloat16* __restrict__ dx16) {
-  __shared__ float red[32];
+  // per-row partial sums of the warps, double-buffered by row parity so that one barrier per row
+  // separates the writes from the reads and the next row's writes cannot overtake them
+  __shared__ float2 red[2][NORM_THREADS / 32];
   const int nv = cols >> 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float4 dwacc[NORM_MAXV];
   float4 wreg[NORM_MAXV];
 #pragma unroll
@@ -132,21 +135,33 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     const int c = threadIdx.x + i * NORM_THREADS;
     wreg[i] = (c < nv) ? *reinterpret_cast<const float4*>(w + c * 4) : make_float4(0, 0, 0, 0);
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  int parity = 0;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
     const float mean = (KIND == 0) ? mean_in[row] : 0.f;
     const float rstd = rstd_in[row];
     const TDY* dyr = dy + (size_t)row * cols;
     const TX* xr = x + (size_t)row * cols;
-    float4 g[NORM_MAXV], xh[NORM_MAXV];
+    float* dxr = dx + (size_t)row * cols;
+    float4 g[NORM_MAXV], xh[NORM_MAXV], prev[NORM_MAXV];
+    // every load of the row is issued before anything waits on one of them
+    float4 dv[NORM_MAXV], xv[NORM_MAXV];
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nv) {
+        dv[i] = load4<TDY>(dyr + c * 4);
+        xv[i] = load4<TX>(xr + c * 4);
+        if (accumulate_dx) prev[i] = *reinterpret_cast<const float4*>(dxr + c * 4);
+      }
+    }
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nv) {
-        const float4 d = load4<TDY>(dyr + c * 4);
-        const float4 xv = load4<TX>(xr + c * 4);
-        xh[i] = make_float4((xv.x - mean) * rstd, (xv.y - mean) * rstd, (xv.z - mean) * rstd,
-                            (xv.w - mean) * rstd);
+        const float4 d = dv[i];
+        xh[i] = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
+                            (xv[i].w - mean) * rstd);
         dwacc[i].x += d.x * xh[i].x;
         dwacc[i].y += d.y * xh[i].y;
         dwacc[i].z += d.z * xh[i].z;
@@ -156,9 +171,19 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
         s2 += g[i].x * xh[i].x + g[i].y * xh[i].y + g[i].z * xh[i].z + g[i].w * xh[i].w;
       }
     }
-    const float m2 = block_sum(s2, red) / cols;
-    const float m1 = (KIND == 0) ? block_sum(s1, red) / cols : 0.f;
-    float* dxr = dx + (size_t)row * cols;
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) red[parity][warp] = make_float2(s1, s2);
+    __syncthreads();
+    float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < NORM_THREADS / 32; ++wv) {
+      const float2 t = red[parity][wv];
+      t1 += t.x;
+      t2 += t.y;
+    }
+    const float m2 = t2 / cols;
+    const float m1 = (KIND == 0) ? t1 / cols : 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
@@ -169,8 +194,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
         o.z = rstd * (g[i].z - m1 - xh[i].z * m2);
         o.w = rstd * (g[i].w - m1 - xh[i].w * m2);
         if (accumulate_dx) {
-          const float4 p = *reinterpret_cast<const float4*>(dxr + c * 4);
-          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+          o.x += prev[i].x; o.y += prev[i].y; o.z += prev[i].z; o.w += prev[i].w;
         }
         *reinterpret_cast<float4*>(dxr + c * 4) = o;
         if (dx16) store4<__nv_bfloat16>(dx16 + (size_t)row * cols + c * 4, o);

@@ -2,7 +2,7 @@
 
 One pure elementwise update (`logtime_update_`) serves four users: the per-tensor
 `torch.optim.Optimizer` classes below (CPU, oracle and DDP paths), the flat-shard update
-of the sharded engine (`adana_b200/parallel/fsdp.py`), the CUDA kernel's numerics tests,
+of the sharded engine (`adana_b200/runtime/engine.py`), the CUDA kernel's numerics tests,
 and Manau's non-matrix parameters.
 
 Update rule per element, with t the 1-based step of the parameter, alpha = delta/(delta+t),

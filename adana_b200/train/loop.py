@@ -113,6 +113,9 @@ class Trainer:
             self.substep = self.curr_iter * cfg.acc_steps
         else:
             self.train_reader.set_step(0)
+        from ..logging.metrics import MetricsSink
+
+        self.sink = MetricsSink(self.exp_dir, wandb if (cfg.wandb and wandb is not None) else None, enabled=self.master)
         engine = getattr(self.backend.get_raw_model(self.model), "_engine", None)
         gathers = engine is not None and engine.sharded and engine.world > 1   # then every rank takes part
         if getattr(cfg, "log_dynamics", False) and (self.master or gathers):
@@ -178,15 +181,15 @@ class Trainer:
             self.stats["val_loss"].append(loss)
             self.stats["val_pp"].append(pp)
             self.stats["val_acc"].append(acc)
-            if cfg.wandb and wandb is not None:
-                prefix = "final-val" if (it == cfg.iterations or full_eval) else "val"
-                logs = {"tokens": tokens, "iter": it, f"{prefix}/loss": loss, f"{prefix}/perplexity": pp,
-                        f"{prefix}/acc": acc, **aux}
-                if cfg.moe and cfg.plot_router_logits:
-                    from ..logging.routing import visualize_routing
+            prefix = "final-val" if (it == cfg.iterations or full_eval) else "val"
+            logs = {"tokens": tokens, "iter": it, f"{prefix}/loss": loss, f"{prefix}/perplexity": pp,
+                    f"{prefix}/acc": acc, **aux}
+            if cfg.wandb and wandb is not None and cfg.moe and cfg.plot_router_logits:
+                from ..logging.routing import visualize_routing
 
-                    logs.update(visualize_routing(router, cfg))
-                wandb.log(logs, step=it)
+                logs.update(visualize_routing(router, cfg))
+            self.sink.log(logs, step=it)
+            if cfg.wandb and wandb is not None:
                 if cfg.eval_seq_prefix != "none" and (it % (cfg.eval_interval * 5) == 0 or it == cfg.iterations):
                     table = wandb.Table(columns=["itr", "val-pp", "text"])
                     text = self.backend.get_raw_model(self.model).generate_from_string(
@@ -268,7 +271,7 @@ class Trainer:
         if cfg.opt == "prodigy":
             eff = log_prodigy_lr(opt)
             print(f"effective_lr={eff[0]:.2e}")
-        if cfg.wandb and wandb is not None:
+        if self.master:
             gns = [float(g) for g in self.grad_norms]
             logs = {"tokens": tokens, "iter": self.curr_iter, "train/loss": train_loss,
                     "train/perplexity": 2.71828 ** train_loss, "lr": lrs[0], "iter_dt": dt,
@@ -281,7 +284,7 @@ class Trainer:
                 from ..logging.schedules import get_parameter_norms
 
                 logs["model_norm"] = get_parameter_norms(self.backend.get_raw_model(self.model), order=cfg.norm_order)
-            wandb.log(logs, step=self.curr_iter)
+            self.sink.log(logs, step=self.curr_iter)
         self.grad_norms = []
 
     # ---- main loop ---------------------------------------------------------------------------------------------

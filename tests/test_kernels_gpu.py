@@ -51,13 +51,15 @@ def test_gemm_fwd_dgrad_wgrad(M, N, K, gemm_mode):
     assert rel_err(dw, 1.5 * ref) < 1e-3
 
 
-def test_gemm_wgrad_stream_k_partial_tiles():
-    """81 pair tiles on 74 pairs: the K loops are split over all pairs and partial tiles meet in C atomically."""
+@pytest.mark.parametrize("mode", [0, 2], ids=["last_wave_split", "every_tile_split"])
+def test_gemm_wgrad_stream_k_partial_tiles(mode):
+    """81 pair tiles on 74 pairs.  Per-shape policy: 74 whole tiles, the other 7 split along K over all pairs;
+    mode 2: every K loop split.  Partial tiles meet in C through fp32 vector atomics."""
     torch.manual_seed(3)
     M, N, K = 4096, 2304, 2304
     x, dy = rnd(M, K), rnd(M, N)
     ref = dy.float().t() @ x.float()
-    old = gemm.set_mode(2)
+    old = gemm.set_mode(mode)
     try:
         dw = torch.full((N, K), 7.0, device=DEV)            # overwrite mode must not see old contents
         gemm.linear_wgrad(dy, x, out=dw)
