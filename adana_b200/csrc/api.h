@@ -126,6 +126,13 @@ int adana_attn_bwd(const void* dout, const void* q, const void* k, long long ldv
 int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
 int adana_version(void);
 
+// ---- attention JVP (attention_jvp_tcgen05.cu) ---------------------------------------------------
+// Primal output and forward-mode tangent of causal attention in one pass.  q, tq [T, Hq, hd];
+// k, tk, v, tv [T, Hk, hd]; out, tout [T, Hq*hd]; contiguous bf16, T = B*S, S % 128 == 0, hd 64 | 128.
+int adana_attn_jvp(const void* q, const void* tq, const void* k, const void* tk, const void* v,
+                   const void* tv, void* out, void* tout, int B, int S, int Hq, int Hk, int hd,
+                   float scale, int* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -661,24 +661,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_after_sync();
       uint32_t pk[64], dk_[64];
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nl2 = make_float2(-lse, -lse);
+      const float2 s2 = make_float2(args.scale, args.scale), nd2 = make_float2(-dl * args.scale, -dl * args.scale);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tmem_base + S_COL + lane_addr + c * 32, sv);
         tmem_ld_32x32b_x32(tmem_base + DP_COL + lane_addr + c * 32, dv);
         tmem_wait_ld();
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if ((c * 32 + e) > r) sv[e] = 0xff800000u;   // -inf: the probability is exactly 0
+        }
+        // two columns per instruction: p = exp2(s*c' - lse), dS = p * (dP*c - delta*c)
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2f(__uint_as_float(sv[e]) * args.scale_log2 - lse);
-          float p1 = exp2f(__uint_as_float(sv[e + 1]) * args.scale_log2 - lse);
-          if (diag) {
-            if ((c * 32 + e) > r) p0 = 0.f;
-            if ((c * 32 + e + 1) > r) p1 = 0.f;
-          }
-          const float d0 = p0 * (__uint_as_float(dv[e]) - dl) * args.scale;
-          const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dl) * args.scale;
-          pk[c * 16 + (e >> 1)] = pack_bf16x2(p0, p1);
-          dk_[c * 16 + (e >> 1)] = pack_bf16x2(d0, d1);
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), sc2, nl2);
+          const float2 p2 = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2, nd2);
+          const float2 d2 = __fmul2_rn(p2, t2);
+          pk[c * 16 + (e >> 1)] = pack_bf16x2(p2.x, p2.y);
+          dk_[c * 16 + (e >> 1)] = pack_bf16x2(d2.x, d2.y);
         }
       }
       tc_fence_before_sync();

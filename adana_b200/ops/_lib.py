@@ -62,6 +62,7 @@ def _declare(lib):
         "adana_p2p_opt_step_push": [P, P, P, P, P, P, I, L, L, POINTER(AdanaOptHyper), P, P],
         "adana_attn_fwd": [P, P, P, L, I, P, P, I, I, I, I, I, F, P, P],
         "adana_attn_bwd": [P, P, P, L, I, P, P, P, P, P, P, L, I, P, I, I, I, I, I, F, P, P],
+        "adana_attn_jvp": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, P, P],
         "adana_embedding_fwd": [P, P, I, P, I, I, I, P],
         "adana_embedding_bwd": [P, P, P, I, I, I, P],
         "adana_ce_fwd_bwd": [P, L, P, I, I, F, F, P, L, P, P, P],

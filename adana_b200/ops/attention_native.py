@@ -42,3 +42,42 @@ def bwd(dout, q, k, vbuf, v_off, v_hstride, B, S, scale, lse2, out, dvbuf):
                                    float(scale), _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "adana_attn_bwd")
     return dq_acc.to(torch.bfloat16), dk
+
+
+# ---- forward-mode derivative ------------------------------------------------------------------------------------
+def jvp_available() -> bool:
+    return _lib.available() and _lib.has("adana_attn_jvp")
+
+
+def jvp(q, k, v, tq, tk, tv, B, S, scale=None):
+    """Causal attention and its directional derivative in one kernel (csrc/attention_jvp_tcgen05.cu).
+
+    q, tq [T, Hq, hd]; k, tk, v, tv [T, Hk, hd]; contiguous bf16; returns (out, tangent_out), each [T, Hq*hd]."""
+    T, Hq, hd = q.shape
+    Hk = k.shape[1]
+    scale = hd ** -0.5 if scale is None else scale
+    for t in (q, k, v, tq, tk, tv):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("attention jvp takes contiguous bf16 tensors")
+    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    tout = torch.empty_like(out)
+    rc = _lib.lib().adana_attn_jvp(q.data_ptr(), tq.data_ptr(), k.data_ptr(), tk.data_ptr(), v.data_ptr(),
+                                   tv.data_ptr(), out.data_ptr(), tout.data_ptr(), B, S, Hq, Hk, hd, float(scale),
+                                   _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_attn_jvp")
+    return out, tout
+
+
+def jvp_ref(q, k, v, tq, tk, tv, B, S, scale=None):
+    """fp32 oracle: torch.func.jvp through a plain PyTorch causal attention of the same layout."""
+    from .attention import attention_ref
+
+    hd = q.shape[-1]
+    scale = hd ** -0.5 if scale is None else scale
+
+    def f(q_, k_, v_):
+        return attention_ref(q_, k_, v_, B, S, scale)[0]
+
+    prim = tuple(t.float() for t in (q, k, v))
+    tang = tuple(t.float() for t in (tq, tk, tv))
+    return torch.func.jvp(f, prim, tang)

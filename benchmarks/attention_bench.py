@@ -5,7 +5,7 @@ hand-written tcgen05 kernels against PyTorch SDPA (library comparator), bf16, se
     python benchmarks/attention_bench.py [--B 8] [--heads 12 16 36] [--hd 64 128] [--S 1024 2048 4096 8192]
                                          [--what fwd bwd jvp] [--iters 10]
 
-TFLOP/s counts the causal half: forward 4*B*H*S^2*hd/2, backward 2.5x that.
+TFLOP/s counts the causal half: forward 4*B*H*S^2*hd/2, backward 2.5x that, JVP 3x (six GEMM chains per tile).
 """
 import argparse
 import json
@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--S", type=int, nargs="+", default=[1024, 2048, 4096, 8192])
     ap.add_argument("--what", nargs="+", default=["fwd", "bwd"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--jvp_comparator", action="store_true", help="also time torch.func.jvp over math attention (S <= 2048)")
     a = ap.parse_args()
     torch.manual_seed(0)
     for hd in a.hd:
@@ -75,6 +76,23 @@ def main():
                     tl = timeit(lambda: torch.autograd.grad(o, (qd, kd, vd), g, retain_graph=True), a.iters)
                     row.update(bwd_ms=round(t, 4), bwd_tflops=round(2.5 * flops_fwd / t / 1e9, 1),
                                sdpa_bwd_ms=round(tl, 4), sdpa_bwd_tflops=round(2.5 * flops_fwd / tl / 1e9, 1))
+                if "jvp" in a.what and attention_native.jvp_available():
+                    v = torch.randn(T, H, hd, device="cuda").bfloat16()
+                    tq, tk, tv = (torch.randn(T, H, hd, device="cuda").bfloat16() for _ in range(3))
+                    t = timeit(lambda: attention_native.jvp(q, k, v, tq, tk, tv, B, S, scale), a.iters)
+                    row.update(jvp_ms=round(t, 4), jvp_tflops=round(3.0 * flops_fwd / t / 1e9, 1))
+                    if a.jvp_comparator and S <= 2048:
+                        # comparator: torch.func.jvp over the math attention (fp32 scores are materialised)
+                        vv4 = v.view(B, S, H, hd).transpose(1, 2)
+                        tq4, tk4, tv4 = (x.view(B, S, H, hd).transpose(1, 2) for x in (tq, tk, tv))
+
+                        def math_attn(q_, k_, v_):
+                            s_ = (q_ @ k_.transpose(-1, -2)) * scale
+                            s_ = s_.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+                            return torch.softmax(s_, -1) @ v_
+
+                        tl = timeit(lambda: torch.func.jvp(math_attn, (q4, k4, vv4), (tq4, tk4, tv4)), max(2, a.iters // 3))
+                        row.update(torch_jvp_ms=round(tl, 4), torch_jvp_tflops=round(3.0 * flops_fwd / tl / 1e9, 1))
                 print(json.dumps(row), flush=True)
     torch.cuda.synchronize()
     _lib.check_status()

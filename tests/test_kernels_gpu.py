@@ -375,3 +375,21 @@ def test_newton_schulz_tcgen05_chain_matches_pytorch():
         assert err < 0.05, (shape, float(err))
         sv = torch.linalg.svdvals(got.float())
         assert 0.5 < float(sv.median()) < 1.3
+
+
+@pytest.mark.parametrize("hd,Hq,Hk,S", [(64, 4, 4, 256), (64, 4, 2, 512), (128, 2, 2, 256), (128, 4, 1, 384)])
+def test_attention_jvp_matches_torch_func_jvp(hd, Hq, Hk, S):
+    from adana_b200.ops import attention_native as an
+
+    torch.manual_seed(17)
+    B = 2
+    T = B * S
+    q, k, v = rnd(T, Hq, hd, scale=1.0), rnd(T, Hk, hd, scale=1.0), rnd(T, Hk, hd, scale=1.0)
+    tq, tk, tv = rnd(T, Hq, hd, scale=1.0), rnd(T, Hk, hd, scale=1.0), rnd(T, Hk, hd, scale=1.0)
+    out, tout = an.jvp(q, k, v, tq, tk, tv, B, S)
+    ref_out, ref_tout = an.jvp_ref(q, k, v, tq, tk, tv, B, S)
+    assert rel_err(out, ref_out) < 1.5e-2
+    assert rel_err(tout, ref_tout) < 2.5e-2
+    # the primal half agrees with the forward kernel
+    fwd_out, _ = an.fwd(q, k, v, 0, hd, B, S, hd ** -0.5)
+    assert rel_err(out, fwd_out) < 1e-2
