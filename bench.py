@@ -244,6 +244,31 @@ def run_reference(a):
         emit({"impl": "reference", "unavailable": "baseline/_ref/src is missing (reference not installed)"})
         return
     rank, local_rank, world = dist_env(a.gpus)
+    # a rank that fails or never joins would leave the others waiting in their first collective: a failing
+    # rank leaves a note that every rank's watchdog thread polls, and the whole arm has a time limit
+    import threading
+
+    limit = float(os.environ.get("ADANA_REF_TIMEOUT", "1500"))
+    note = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data")) / f"ref_failed.{os.environ.get('MASTER_PORT', '0')}"
+    note.parent.mkdir(parents=True, exist_ok=True)
+    if rank == 0 and note.exists():
+        note.unlink()
+    done = threading.Event()
+
+    def watch():
+        t_start = time.time()
+        while not done.wait(2.0):
+            why = None
+            if note.exists():
+                why = "a rank failed: " + note.read_text()[:300]
+            elif time.time() - t_start > limit:
+                why = f"the reference did not finish within {limit:.0f} s on {world} GPU(s)"
+            if why:
+                if rank == 0:
+                    emit({"impl": "reference", "unavailable": why})
+                os._exit(0)
+
+    threading.Thread(target=watch, daemon=True).start()
     try:
         import torch
         import torch.distributed as dist
@@ -272,8 +297,18 @@ def run_reference(a):
         steps_total = a.warmup + a.steps
         tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
         data_root = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data"))
+        # rank 0 writes the corpus; the others must not reach the reference's dataset code (which would try
+        # to download a missing corpus) before the files exist, and no process group is up yet to wait on
+        marker = data_root / f"ready.{tokens_needed}.{os.environ.get('MASTER_PORT', '0')}"
         if rank == 0:
             write_tokens(tokens_needed)
+            marker.write_text("ok")
+        else:
+            t_wait = time.time()
+            while not marker.exists():
+                if time.time() - t_wait > 600:
+                    raise RuntimeError("rank 0 did not finish writing the synthetic corpus within 600 s")
+                time.sleep(0.5)
         argv = ["--model", "enoki", "--n_layer", str(a.n_layer), "--n_head", "36", "--n_embd", "2304",
                 "--qkv_dim", "64", "--mlp_hidden_dim", "9216", "--sequence_length", "2048", "--vocab_size", "50304",
                 "--weight_tying", "False", "--init-scheme", "ScaledGPT", "--dtype", "bfloat16",
@@ -364,12 +399,18 @@ def run_reference(a):
                           "h2d_bytes_per_step": 2 * 8 * a.micro_batch * 2048 * acc, "d2h_bytes_per_step": 4,
                           "note": "the reference's own loop: pinned host batches, .item() on the grad norm every step"},
                   "gpu_launches": None, "peak_mem_gib": round(mem, 2)})
+        done.set()
         if dist.is_initialized():
             dist.barrier()
             dist.destroy_process_group()
     except Exception as e:  # any failure of the reference arm is reported, never raised
+        done.set()
+        if world > 1:
+            note.write_text(f"rank {rank}: {type(e).__name__}: {str(e)[:200]}")
         if rank == 0:
             emit({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"})
+        else:
+            print(f"[reference arm, rank {rank}] {type(e).__name__}: {str(e)[:300]}", file=sys.stderr, flush=True)
 
 
 if __name__ == "__main__":
