@@ -18,8 +18,6 @@
 //
 // Replaces F.scaled_dot_product_attention(is_causal=True) of the reference
 // (src/models/enoki.py:134-136, src/models/qwen3.py:212-217).
-#include <cstdlib>
-
 #include "api.h"
 #include "common.cuh"
 
@@ -452,7 +450,6 @@ struct AttBwdArgs {
   int B, S, Hq, Hk;
   float scale, scale_log2;
   int* status;
-  int dbg_skip_dq;
 };
 
 template <int HD>
@@ -721,7 +718,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         tmem_wait_ld();
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
-          if (args.dbg_skip_dq) continue;
           asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + q4 * 4),
                        "f"(__uint_as_float(o[q4 * 4])), "f"(__uint_as_float(o[q4 * 4 + 1])),
                        "f"(__uint_as_float(o[q4 * 4 + 2])), "f"(__uint_as_float(o[q4 * 4 + 3]))
@@ -862,7 +858,6 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
   a.B = B; a.S = S; a.Hq = Hq; a.Hk = Hk;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
-  a.dbg_skip_dq = getenv("ADANA_DBG_SKIP_DQ") != nullptr;
   if (hd == 64) return launch_attn_bwd<64>(tq, tdo, tk, tv, a, st);
   return launch_attn_bwd<128>(tq, tdo, tk, tv, a, st);
 }
