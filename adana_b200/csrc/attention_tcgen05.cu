@@ -435,7 +435,9 @@ struct AttBwdSmem {
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int P_OFF = DO_OFF + STAGES * TILE;
   static constexpr int DS_OFF = P_OFF + ATT_BQ * ATT_BKV * 2;
-  static constexpr int BAR_OFF = DS_OFF + ATT_BQ * ATT_BKV * 2;
+  static constexpr int DQ_OFF = DS_OFF + ATT_BQ * ATT_BKV * 2;   // fp32 staging of 64 dQ columns: 2 boxes [128][32]
+  static constexpr int DQ_BOX = ATT_BQ * 128;
+  static constexpr int BAR_OFF = DQ_OFF + 2 * DQ_BOX;
   static constexpr int TOTAL = BAR_OFF + 256;
 };
 
@@ -456,7 +458,7 @@ template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                const AttBwdArgs args) {
+                const __grid_constant__ CUtensorMap tmDQ, const AttBwdArgs args) {
   using L = AttBwdSmem<HD>;
   constexpr int CHUNKS = HD / 64;
   constexpr int CHUNK_BYTES = ATT_BQ * 128;
@@ -710,24 +712,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after_sync();
-      float* dq_row = args.dq_acc + (((long long)b * args.S + i * ATT_BQ + r) * args.Hq + hq) * HD;
+      // dQ_i of this item: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the
+      // fp32 accumulation buffer.  The adds happen in L2, 128 bytes at a time, instead of 16 vector atomics
+      // per thread.  Every warp stages and sends its own 32 rows, so only warp-level synchronisation is needed.
+      uint8_t* sDQw = smem + L::DQ_OFF + quad * 32 * 128;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + c * 32, o);
-        tmem_wait_ld();
+      for (int half = 0; half < HD / 64; ++half) {
+        if (lane == 0) tma_wait_group_read0();      // this warp's previous reduce has read its staging rows
+        __syncwarp();
 #pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4) {
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + q4 * 4),
-                       "f"(__uint_as_float(o[q4 * 4])), "f"(__uint_as_float(o[q4 * 4 + 1])),
-                       "f"(__uint_as_float(o[q4 * 4 + 2])), "f"(__uint_as_float(o[q4 * 4 + 3]))
-                       : "memory");
+        for (int c = 0; c < 2; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + half * 64 + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            *reinterpret_cast<uint4*>(sDQw + c * L::DQ_BOX + lane * 128 + ((u ^ (lane & 7)) << 4)) =
+                make_uint4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int tok0 = b * args.S + i * ATT_BQ + quad * 32;
+          tma_reduce_add_3d(&tmDQ, sDQw, half * 64, hq, tok0);
+          tma_reduce_add_3d(&tmDQ, sDQw + L::DQ_BOX, half * 64 + 32, hq, tok0);
+          tma_commit_group();
         }
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
     }
+    if (lane == 0) tma_wait_group_read0();   // staging rows are not needed any more
+    __syncwarp();
     // ---- epilogue: dK_j, dV_j (row = key index) ----
     if (ok && mbar_wait(acc_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
       tc_fence_after_sync();
@@ -801,7 +818,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const 
 
 template <int HD>
 static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const CUtensorMap& tk,
-                           const CUtensorMap& tv, const AttBwdArgs& a, cudaStream_t st) {
+                           const CUtensorMap& tv, const CUtensorMap& tdq, const AttBwdArgs& a, cudaStream_t st) {
   auto kern = attn_bwd_kernel<HD>;
   static bool configured = false;
   if (!configured) {
@@ -810,7 +827,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
     configured = true;
   }
   const int grid = a.B * a.Hk * (a.S / ATT_BKV);
-  kern<<<grid, ATT_THREADS, AttBwdSmem<HD>::TOTAL, st>>>(tq, tdo, tk, tv, a);
+  kern<<<grid, ATT_THREADS, AttBwdSmem<HD>::TOTAL, st>>>(tq, tdo, tk, tv, tdq, a);
   return (int)cudaGetLastError();
 }
 
@@ -858,6 +875,13 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
   a.B = B; a.S = S; a.Hq = Hq; a.Hk = Hk;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
-  if (hd == 64) return launch_attn_bwd<64>(tq, tdo, tk, tv, a, st);
-  return launch_attn_bwd<128>(tq, tdo, tk, tv, a, st);
+  CUtensorMap tdq;   // dq_acc [T, Hq, hd] fp32 seen as (hd, Hq, T); one reduce moves a [32 tokens][1 head][32 cols] box
+  {
+    uint64_t dims[3] = {(uint64_t)hd, (uint64_t)Hq, T};
+    uint64_t str[3] = {1, (uint64_t)hd, (uint64_t)Hq * hd};
+    uint32_t box[3] = {32, 1, 32};
+    if (encode_tmap_nd(&tdq, dq_acc, 3, dims, str, box, 4, 1)) return -6;
+  }
+  if (hd == 64) return launch_attn_bwd<64>(tq, tdo, tk, tv, tdq, a, st);
+  return launch_attn_bwd<128>(tq, tdo, tk, tv, tdq, a, st);
 }

@@ -474,10 +474,20 @@ struct PairWork {
   }
 };
 
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const GemmArgs args) {
+// The B operand of the "gathering" variant: one tensor map per rank over that rank's slice of the
+// weight rows (its own memory or a peer's, mapped over NVLink).  The CTA fetches B in 32-row boxes,
+// each from the rank that owns those rows, so the all-gather of the sharded weight happens tile
+// by tile inside the GEMM's TMA pipeline and no gathered copy of the weight ever exists.
+constexpr int MAX_SHARDS = 8;
+struct ShardedB {
+  CUtensorMap map[MAX_SHARDS];
+  int rows_per_shard;   // rows of the weight matrix held by every rank (a multiple of 32)
+  int n_shards;
+};
+
+template <bool A_MN, bool B_MN, int EPI, bool SHARDED>
+__device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                               const ShardedB* __restrict__ shards, const GemmArgs& args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -526,7 +536,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     // ------------------------------ TMA producer (both CTAs) ---------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
+      if constexpr (!SHARDED) tma_prefetch_desc(&tmB);
       const uint32_t lead_full0 = mapa_smem(smem_u32(&full_bar[0]), 0);
       int stage = 0;
       uint32_t phase = 0;
@@ -557,7 +567,29 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             for (int c = 0; c < 2; ++c)
               tma_load_2d_pair(sA + c * CHUNK_BYTES, &tmA, bar, m0 + c * 64, k0);
           }
-          if constexpr (!B_MN) {
+          if constexpr (SHARDED) {
+            const int rps = shards->rows_per_shard;
+            if constexpr (!B_MN) {
+              // weight rows = output columns: 4 boxes {64 k, 32 n}, each from the rank owning the rows
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int row = nb0 + q * 32;
+                const int owner = min(row / rps, shards->n_shards - 1);
+                tma_load_2d_pair(sB + q * 32 * 128, &shards->map[owner], bar, k0, row - owner * rps);
+              }
+            } else {
+              // weight rows = the contraction index: 2 boxes {64 n, 32 k} per 64-column chunk
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const int row = k0 + q * 32;
+                const int owner = min(row / rps, shards->n_shards - 1);
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                  tma_load_2d_pair(sB + c * CHUNK_BYTES + q * 32 * 128, &shards->map[owner], bar, nb0 + c * 64,
+                                   row - owner * rps);
+              }
+            }
+          } else if constexpr (!B_MN) {
             tma_load_2d_pair(sB, &tmB, bar, k0, nb0);  // box {64 k, 128 n}
           } else {
 #pragma unroll
@@ -677,6 +709,21 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   }
 }
 
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmArgs args) {
+  gemm_pair_body<A_MN, B_MN, EPI, false>(tmA, tmB, nullptr, args);
+}
+
+// All-gather fused into the GEMM: B is read shard by shard from the ranks that own it.
+template <bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ ShardedB shards,
+                        const GemmArgs args) {
+  gemm_pair_body<false, B_MN, EPI, true>(tmA, shards.map[0], &shards, args);
+}
+
 // ------------------------------------------------------------------------------------------------
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args,
@@ -722,6 +769,33 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
     pairs = units < max_pairs ? (int)units : max_pairs;
   }
   kern<<<2 * pairs, GEMM_THREADS, P_SMEM, stream>>>(tmA, tmB, args);
+  return (int)cudaGetLastError();
+}
+
+template <bool B_MN, int EPI>
+static int launch_gemm_gather(const CUtensorMap& tmA, const ShardedB& shards, GemmArgs args, int sm_count,
+                              cudaStream_t stream) {
+  auto kern = gemm_bf16_gather_kernel<B_MN, EPI>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((sm_count / 2) * 2);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = sm_count / 2;
+    }
+    max_pairs = n < sm_count / 2 ? n : sm_count / 2;
+  }
+  args.tiles_m = (args.M + P_BM - 1) / P_BM;
+  const int tiles = args.tiles_m * args.tiles_n;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, GEMM_THREADS, P_SMEM, stream>>>(tmA, shards, args);
   return (int)cudaGetLastError();
 }
 
@@ -827,5 +901,51 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   ADANA_GEMM_CASE(true, false, EPI_BF16)
   ADANA_GEMM_CASE(true, false, EPI_F32)
 #undef ADANA_GEMM_CASE
+  return -103;
+}
+
+// C = epilogue(A * W^T) (b_mn = 0, W [N, K] split by rows over the ranks: N = n_shards * rows_per_shard) or
+// C = epilogue(A * W) (b_mn = 1, W [K, N] split by rows: K = n_shards * rows_per_shard), where shard r of W
+// lives at B_shards[r] (this rank's memory or a peer's) with row pitch ldb.  The gather of W is part of the
+// GEMM's TMA pipeline; nothing is staged.
+extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards,
+                                      int rows_per_shard, void* C, int M, int N, int K, long long lda,
+                                      long long ldb, long long ldc, int b_mn, int epi, void* C2, long long ldc2,
+                                      const void* R, long long ldr, float alpha, int* status, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n_shards < 1 || n_shards > MAX_SHARDS || rows_per_shard <= 0 || (rows_per_shard % 32) != 0) return -110;
+  if ((N % 8) != 0 || (ldc % 4) != 0) return -100;
+  if ((!b_mn && (long long)n_shards * rows_per_shard < N) || (b_mn && (long long)n_shards * rows_per_shard < K))
+    return -111;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tmA;
+  if (encode_tmap_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, BM, 2)) return -101;
+  ShardedB sh;
+  sh.rows_per_shard = rows_per_shard;
+  sh.n_shards = n_shards;
+  for (int r = 0; r < n_shards; ++r) {
+    const uint64_t inner = b_mn ? (uint64_t)N : (uint64_t)K;
+    if (encode_tmap_2d(&sh.map[r], B_shards[r], inner, (uint64_t)rows_per_shard, (uint64_t)ldb, 64, 32, 2)) return -102;
+  }
+  for (int r = n_shards; r < MAX_SHARDS; ++r) sh.map[r] = sh.map[0];
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K;
+  args.C = C; args.ldc = ldc; args.C2 = C2; args.ldc2 = ldc2; args.R = R; args.ldr = ldr;
+  args.alpha = alpha; args.beta = 0.f; args.b_off2 = 0;
+  args.tiles_m = (M + P_BM - 1) / P_BM;
+  args.tiles_n = (N + BN - 1) / BN;
+  args.group_m = 16;
+  args.streamk = 0;
+  args.status = status;
+  if (!b_mn && epi == EPI_BF16) return launch_gemm_gather<false, EPI_BF16>(tmA, sh, args, g_sm_count, stream);
+  if (!b_mn && epi == EPI_GELU_DUAL) return launch_gemm_gather<false, EPI_GELU_DUAL>(tmA, sh, args, g_sm_count, stream);
+  if (!b_mn && epi == EPI_RESID_F32) return launch_gemm_gather<false, EPI_RESID_F32>(tmA, sh, args, g_sm_count, stream);
+  if (b_mn && epi == EPI_BF16) return launch_gemm_gather<true, EPI_BF16>(tmA, sh, args, g_sm_count, stream);
+  if (b_mn && epi == EPI_DGELU) return launch_gemm_gather<true, EPI_DGELU>(tmA, sh, args, g_sm_count, stream);
   return -103;
 }

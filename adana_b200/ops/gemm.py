@@ -204,3 +204,53 @@ def linear_wgrad(dy, x, out=None, accumulate=False, alpha=1.0):
         accumulate = False
     return gemm(dy, x, out, M=N, N=K, K=M, a_mn=True, b_mn=True, epi=EPI_F32,
                 alpha=alpha, beta=1.0 if accumulate else 0.0)
+
+
+# ----------------------------------------------------------------------------------------------
+# All-gather fused into the GEMM: the weight is row-sharded over ranks and every CTA pair fetches its
+# B tiles straight from the owning rank (local or peer memory) — no gathered copy of the weight.
+# ----------------------------------------------------------------------------------------------
+def _ptr_array(shards):
+    """list of tensors / ints, or a ready ctypes array -> (c_uint64 array, count)."""
+    import ctypes
+
+    if isinstance(shards, ctypes.Array):
+        return shards, len(shards)
+    vals = [int(s.data_ptr()) if torch.is_tensor(s) else int(s) for s in shards]
+    return (ctypes.c_uint64 * len(vals))(*vals), len(vals)
+
+
+def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, out=None, C2=None, R=None, alpha=1.0,
+                out_dtype=torch.bfloat16):
+    """C[M,N] = epi(x · Wᵀ) (b_mn False, W [N,K] row-sharded) or epi(x · W) (b_mn True, W [K,N] row-sharded)."""
+    _check2d(x, "x")
+    M, K = x.shape
+    arr, n = _ptr_array(shards)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    rc = _lib.lib().adana_gemm_bf16_gather(
+        x.data_ptr(), arr, n, int(rows_per_shard), out.data_ptr(), M, N, K, x.stride(0), int(ldb), out.stride(0),
+        int(b_mn), int(epi), _lib.ptr(C2), 0 if C2 is None else C2.stride(0), _lib.ptr(R), 0 if R is None else R.stride(0),
+        float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_gemm_bf16_gather")
+    return out
+
+
+def linear_fwd_gathered(x, w_shards, rows_per_shard, out=None):
+    """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows: shard r = rows [r·rows_per_shard, (r+1)·rows_per_shard)."""
+    _, n = _ptr_array(w_shards)
+    return gather_gemm(x, w_shards, rows_per_shard, n * rows_per_shard, ldb=x.shape[1], out=out)
+
+
+def linear_gelu_fwd_gathered(x, w_shards, rows_per_shard):
+    _, n = _ptr_array(w_shards)
+    N = n * rows_per_shard
+    z = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty_like(z)
+    gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h)
+    return z, h
+
+
+def linear_dgrad_gathered(dy, w_shards, rows_per_shard, K_out, out=None):
+    """dx [M, K_out] = dy [M, N] · W with W [N, K_out] split by rows (the contraction index is sharded)."""
+    return gather_gemm(dy, w_shards, rows_per_shard, K_out, ldb=K_out, b_mn=True, out=out)

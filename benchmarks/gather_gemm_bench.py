@@ -1,0 +1,108 @@
+#!/usr/bin/env python
+"""All-gather fused into the GEMM (csrc/gemm_tcgen05.cu: gemm_bf16_gather_kernel) against the unfused baseline
+(NCCL all-gather of the weight shards, then the plain GEMM), on the Enoki-36 projection shapes.
+
+    torchrun --nproc-per-node N --master-addr 127.0.0.1 benchmarks/gather_gemm_bench.py [--iters 20]
+    python benchmarks/gather_gemm_bench.py --fake 8          # one GPU: shards are separate local allocations
+
+Roofline of the fused kernel: the slower of FLOPs / measured GEMM peak and remote weight bytes / NVLink rate
+(770 GB/s measured per direction); times are CUDA events, max over ranks.
+"""
+import argparse
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+from adana_b200.ops import _lib, gemm  # noqa: E402
+
+SHAPES = [(16384, 6912, 2304), (16384, 9216, 2304), (16384, 2304, 9216)]     # M, N (weight rows), K
+
+
+def timeit(fn, iters, pre=lambda: None):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    pre()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--fake", type=int, default=0, help="emulate this many ranks with local allocations on one GPU")
+    a = ap.parse_args()
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    real = a.fake == 0
+    if real:
+        import torch.distributed as dist
+
+        from adana_b200.parallel.p2p import P2PPlane
+
+        dist.init_process_group("nccl")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    else:
+        rank, world = 0, a.fake
+    for (M, N, K) in SHAPES:
+        rps = N // world
+        if rps % 32:
+            continue
+        x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        full = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+        if real:
+            plane = P2PPlane.create(rps * K * 2 + (1 << 16), torch.device("cuda"))
+            mine = plane.alloc(rps * K, torch.bfloat16).view(rps, K)
+            mine.normal_(0, 0.5)
+            torch.cuda.synchronize()
+            plane.barrier()
+            ptrs = plane.peer_ptrs(mine)
+            sync = plane.barrier
+
+            def baseline():
+                dist.all_gather_into_tensor(full.view(-1), mine.view(-1))
+                gemm.linear_fwd(x, full, out=y)
+        else:
+            shards = [(torch.randn(rps, K, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+            ptrs, mine, sync = shards, shards[0], (lambda: None)
+
+            def baseline():
+                torch.cat(shards, out=full)
+                gemm.linear_fwd(x, full, out=y)
+        t_fused = timeit(lambda: gemm.linear_fwd_gathered(x, ptrs, rps, out=y), a.iters, sync)
+        t_base = timeit(baseline, a.iters, sync)
+        t_plain = timeit(lambda: gemm.linear_fwd(x, full, out=y), a.iters, sync)
+        if real:
+            tt = torch.tensor([t_fused, t_base, t_plain], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t_fused, t_base, t_plain = tt.tolist()
+            plane.barrier()
+        flops = 2.0 * M * N * K
+        remote = (world - 1) * rps * K * 2
+        row = {"mode": "nvlink peers" if real else "local shards", "world": world, "M": M, "N": N, "K": K,
+               "fused_ms": round(t_fused, 4), "fused_tflops": round(flops / t_fused / 1e9, 1),
+               "allgather_then_gemm_ms": round(t_base, 4), "resident_gemm_ms": round(t_plain, 4),
+               "remote_weight_mb": round(remote / 1e6, 1)}
+        if peaks.get("bf16_tflops"):
+            t_roof = max(flops / (peaks["bf16_tflops"] * 1e9), remote / 770e6 if real else 0.0)
+            row["roofline_ms"] = round(t_roof, 4)
+            row["of_roofline"] = round(t_roof / t_fused, 3)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+if __name__ == "__main__":
+    main()

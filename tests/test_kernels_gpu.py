@@ -393,3 +393,29 @@ def test_attention_jvp_matches_torch_func_jvp(hd, Hq, Hk, S):
     # the primal half agrees with the forward kernel
     fwd_out, _ = an.fwd(q, k, v, 0, hd, B, S, hd ** -0.5)
     assert rel_err(out, fwd_out) < 1e-2
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_gather_gemm_reads_row_sharded_weights_in_place(world):
+    """The all-gather fused into the GEMM, with every rank's shard a separate allocation on this GPU."""
+    torch.manual_seed(21)
+    M, K = 1024, 512
+    rps = 96                                   # rows per shard: a multiple of 32, not of the 128-row half tile
+    N = world * rps
+    x, w = rnd(M, K), rnd(N, K)
+    shards = [w[r * rps:(r + 1) * rps].clone() for r in range(world)]      # separate allocations
+    ref = x.float() @ w.float().t()
+    y = gemm.linear_fwd_gathered(x, shards, rps)
+    assert y.shape == (M, N) and rel_err(y, ref) < 8e-3
+    z, h = gemm.linear_gelu_fwd_gathered(x, shards, rps)
+    assert rel_err(z, ref) < 8e-3 and rel_err(h, torch.nn.functional.gelu(ref)) < 8e-3
+    # dgrad: the contraction index (rows of W) is the sharded one
+    dy = rnd(M, N)
+    dx = gemm.linear_dgrad_gathered(dy, shards, rps, K)
+    assert rel_err(dx, dy.float() @ w.float()) < 8e-3
+    # same bits as the plain CTA-pair kernel on the gathered weight
+    old = gemm.set_mode(3)
+    try:
+        assert torch.equal(y, gemm.linear_fwd(x, w))
+    finally:
+        gemm.set_mode(old)

@@ -68,3 +68,48 @@ def test_p2p_plane_matches_nccl_plane():
         d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs()
         assert d.mean().item() < 2e-4, (k, d.mean().item())
         assert torch.equal(_t(res["p2p"][0]["params"][k]), _t(res["p2p"][1]["params"][k]))
+
+
+def _gather_gemm_worker(rank, world):
+    """All-gather fused into the GEMM over real peers: every rank holds `rps` rows of W in symmetric memory and
+    computes the full y = x Wᵀ (and dx = dy W) reading the other shards through peer pointers."""
+    import torch.distributed as dist
+
+    from adana_b200.ops import _lib, gemm
+    from adana_b200.parallel.p2p import P2PPlane
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    M, K, rps = 2048, 1024, 352
+    N = world * rps
+    plane = P2PPlane.create(rps * K * 2 + (1 << 16), torch.device("cuda", rank))
+    torch.manual_seed(5)
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()                 # same on every rank
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    dy = (torch.randn(M, N, device="cuda") * 0.5).bfloat16()
+    mine = plane.alloc(rps * K, torch.bfloat16).view(rps, K)
+    mine.copy_(w[rank * rps:(rank + 1) * rps])
+    torch.cuda.synchronize()
+    plane.barrier()                                                          # every shard is in place
+    ptrs = plane.peer_ptrs(mine)
+    y = gemm.linear_fwd_gathered(x, ptrs, rps)
+    dx = gemm.linear_dgrad_gathered(dy, ptrs, rps, K)
+    torch.cuda.synchronize()
+    plane.barrier()                                                          # nobody frees a shard still being read
+    torch.cuda.synchronize()
+    _lib.check_status()
+    ref_y, ref_dx = x.float() @ w.float().t(), dy.float() @ w.float()
+    err_y = ((y.float() - ref_y).norm() / ref_y.norm()).item()
+    err_dx = ((dx.float() - ref_dx).norm() / ref_dx.norm()).item()
+    return {"err_y": err_y, "err_dx": err_dx}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gather_gemm_over_nvlink_peers():
+    from test_distributed_cpu import _spawn
+
+    world = min(torch.cuda.device_count(), 8)
+    res = _spawn(_gather_gemm_worker, world)
+    for r in range(world):
+        assert res[r]["err_y"] < 8e-3 and res[r]["err_dx"] < 8e-3, res[r]
