@@ -164,6 +164,7 @@ class Engine:
         self.opt_step_count = 0
         self.last_grad_norm = None
         self.launches = 0
+        self._meter_pairs = []
 
         self._load_from_module()
         self._bind_views()
@@ -307,8 +308,10 @@ class Engine:
 
     def _wait_unit(self, u: Unit):
         if u.gather_work is not None:
+            e0 = self._meter_begin()
             wait(u.gather_work)
             u.gather_work = None
+            self._meter_end(e0)
 
     def _sync_small(self):
         """Sharded mode: norm weights are consumed in fp32, so their master values (owned by
@@ -438,7 +441,38 @@ class Engine:
 
     _plane_pending = False
 
+    # ---- exposed-communication meter ------------------------------------------------------------------
+    # Time the COMPUTE stream spends waiting for communication: the join with the gradient reduce-scatter
+    # stream after backward, and the barrier / scalar-exchange kernels of the optimizer phase.  Event pairs
+    # are recorded only while `meter_comm` is on and are read (with a synchronise) by `exposed_comm_ms()`.
+    meter_comm = False
+
+    def _meter_begin(self):
+        if not (self.meter_comm and self.device.type == "cuda"):
+            return None
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def _meter_end(self, e0):
+        if e0 is None:
+            return
+        e1 = torch.cuda.Event(enable_timing=True)
+        e1.record()
+        self._meter_pairs.append((e0, e1))
+
+    def exposed_comm_ms(self, reset: bool = True) -> float:
+        """Milliseconds the compute stream waited on communication since the last call."""
+        if not self._meter_pairs:
+            return 0.0
+        torch.cuda.synchronize(self.device)
+        total = sum(a.elapsed_time(b) for a, b in self._meter_pairs)
+        if reset:
+            self._meter_pairs = []
+        return total
+
     def finish_grad_sync(self):
+        e0 = self._meter_begin() if (self._plane_pending or any(u.grad_work is not None for u in self.units)) else None
         if self._plane_pending:
             torch.cuda.current_stream().wait_stream(self.plane.stream)
             self._plane_pending = False
@@ -446,6 +480,7 @@ class Engine:
             if u.grad_work is not None:
                 wait(u.grad_work)
                 u.grad_work = None
+        self._meter_end(e0)
 
     def grad_norm_and_clip(self, max_norm: float):
         """Global L2 norm of the (rank-averaged) gradient; leaves the clip coefficient on the device.
@@ -453,14 +488,18 @@ class Engine:
         self.finish_grad_sync()
         if self.plane is not None:
             # the reduce-scatter kernels already accumulated this rank's squared-norm partial
+            e0 = self._meter_begin()
             self.plane.global_clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
+            self._meter_end(e0)
             self.last_grad_norm = self._clip[1]
             return self._clip[1]
         self._sumsq.zero_()
         for u in self.units:
             O.sumsq_accumulate(u.grad_shard, self._sumsq)
         if self.sharded:
+            e0 = self._meter_begin()
             self.comm.all_reduce_sum(self._sumsq)
+            self._meter_end(e0)
         O.clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
         self.last_grad_norm = self._clip[1]
         return self._clip[1]
@@ -498,7 +537,9 @@ class Engine:
                              u.w_shard[ls:le] if u.low_precision else None,
                              kind=kind, grad_scale=1.0 / self.world, clip_coef_t=self._clip, diag=diag, **hyper)
             self._after_update(u)
+        e0 = self._meter_begin()
         self._sync_small()     # (peer-memory plane: ends with the barrier that completes the weight pushes)
+        self._meter_end(e0)
         if self.plane is not None:
             self._sumsq.zero_()
         opt.step_count = t

@@ -181,6 +181,9 @@ def run_ours(a):
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()
+    engine = getattr(backend, "engine", None)
+    if engine is not None and world > 1:
+        engine.meter_comm = True       # event pairs around every point where the compute stream waits on communication
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record()
@@ -195,6 +198,13 @@ def run_ours(a):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ms_per_step = float(ms.item()) / a.steps
+    exposed = None
+    if engine is not None and world > 1:
+        ex = torch.tensor([engine.exposed_comm_ms()], dtype=torch.float64, device=args.device)
+        engine.meter_comm = False
+        dist.all_reduce(ex, op=dist.ReduceOp.MAX)
+        exposed = {"ms_per_step": float(ex.item()) / a.steps, "fraction_of_step": float(ex.item()) / a.steps / ms_per_step,
+                   "what": "time the compute stream waited on gradient reduce-scatter joins, barriers and scalar exchanges (max over ranks)"}
     _lib.check_status()
 
     # ---- end-to-end region: public API, pinned host batches, loss read back every step ----------------
@@ -230,7 +240,7 @@ def run_ours(a):
                          "micro_batch": a.micro_batch, "acc_steps": acc, "optimizer": "dana-star-mk4",
                          "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2",
                          "attention": _attention_impl()},
-              "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+              "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "exposed_comm": exposed,
               "peak_mem_gib": round(mem, 2), "final_loss": final_loss})
     backend.finalize()
 
