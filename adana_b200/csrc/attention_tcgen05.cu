@@ -783,33 +783,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d].  HD/8 neighbouring lanes own one (token, head) vector, each
+// with one 16-byte load per operand; the sum is a 3- or 4-step shuffle inside the lane group.
 template <int HD>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
                                   float* __restrict__ delta, int B, int S, int H) {
-  constexpr int EPL = HD / 32;
+  constexpr int LPV = HD / 8;
+  constexpr int VPW = 32 / LPV;
   const int lane = threadIdx.x & 31;
+  const int sub = lane % LPV, grp = lane / LPV;
   const long long warp_global = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   const long long total = (long long)B * S * H;
-  for (long long item = warp_global; item < total; item += n_warps) {
-    const long long tok = item / H;
-    const int h = (int)(item - tok * H);
-    const long long off = (tok * H + h) * HD + lane * EPL;
-    float acc = 0.f;
-    if (EPL == 2) {
-      const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(dout + off));
-      const float2 o = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(out + off));
-      acc = a.x * o.x + a.y * o.y;
-    } else {
-      const uint2 ua = *reinterpret_cast<const uint2*>(dout + off);
-      const uint2 uo = *reinterpret_cast<const uint2*>(out + off);
-      const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y);
-      const float2 o0 = unpack_bf16x2(uo.x), o1 = unpack_bf16x2(uo.y);
-      acc = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) {
+  for (long long base = warp_global * VPW; base < total; base += n_warps * VPW) {
+    const long long item = base + grp;
+    const bool ok = item < total;
+    const long long it = ok ? item : 0;
+    const long long off = it * HD + sub * 8;
+    const uint4 ua = *reinterpret_cast<const uint4*>(dout + off);
+    const uint4 uo = *reinterpret_cast<const uint4*>(out + off);
+    const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), a2 = unpack_bf16x2(ua.z), a3 = unpack_bf16x2(ua.w);
+    const float2 o0 = unpack_bf16x2(uo.x), o1 = unpack_bf16x2(uo.y), o2 = unpack_bf16x2(uo.z), o3 = unpack_bf16x2(uo.w);
+    float acc = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y + a2.x * o2.x + a2.y * o2.y + a3.x * o3.x + a3.y * o3.y;
+#pragma unroll
+    for (int o = LPV / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (ok && sub == 0) {
+      const long long tok = it / H;
+      const int h = (int)(it - tok * H);
       const long long bb = tok / S, s = tok - bb * S;
       delta[(bb * H + h) * S + s] = acc;
     }

@@ -480,9 +480,11 @@ struct PairWork {
 // by tile inside the GEMM's TMA pipeline and no gathered copy of the weight ever exists.
 constexpr int MAX_SHARDS = 8;
 struct ShardedB {
-  CUtensorMap map[MAX_SHARDS];
+  CUtensorMap map[MAX_SHARDS];       // 32-row boxes: used where a tile straddles two ranks' slices
+  CUtensorMap map_big[MAX_SHARDS];   // whole-tile boxes (128 rows K-major / 64 rows MN-major) for the common case
   int rows_per_shard;   // rows of the weight matrix held by every rank (a multiple of 32)
   int n_shards;
+  int use_big;          // 0 when a slice has fewer rows than a whole-tile box
 };
 
 template <bool A_MN, bool B_MN, int EPI, bool SHARDED>
@@ -569,24 +571,39 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
           }
           if constexpr (SHARDED) {
             const int rps = shards->rows_per_shard;
+            const int last = shards->n_shards - 1;
             if constexpr (!B_MN) {
-              // weight rows = output columns: 4 boxes {64 k, 32 n}, each from the rank owning the rows
+              // weight rows = output columns.  One {64 k, 128 n} box when the 128 rows belong to one rank,
+              // else 4 boxes {64 k, 32 n}, each from the rank owning those rows
+              const int o_lo = min(nb0 / rps, last), o_hi = min((nb0 + 127) / rps, last);
+              if (o_lo == o_hi && shards->use_big) {
+                tma_load_2d_pair(sB, &shards->map_big[o_lo], bar, k0, nb0 - o_lo * rps);
+              } else {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const int row = nb0 + q * 32;
-                const int owner = min(row / rps, shards->n_shards - 1);
-                tma_load_2d_pair(sB + q * 32 * 128, &shards->map[owner], bar, k0, row - owner * rps);
+                for (int q = 0; q < 4; ++q) {
+                  const int row = nb0 + q * 32;
+                  const int owner = min(row / rps, last);
+                  tma_load_2d_pair(sB + q * 32 * 128, &shards->map[owner], bar, k0, row - owner * rps);
+                }
               }
             } else {
-              // weight rows = the contraction index: 2 boxes {64 n, 32 k} per 64-column chunk
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                const int row = k0 + q * 32;
-                const int owner = min(row / rps, shards->n_shards - 1);
+              // weight rows = the contraction index: {64 n, 64 k} boxes per 64-column chunk, or two
+              // {64 n, 32 k} boxes where the k-block straddles two ranks
+              const int o_lo = min(k0 / rps, last), o_hi = min((k0 + 63) / rps, last);
+              if (o_lo == o_hi && shards->use_big) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
-                  tma_load_2d_pair(sB + c * CHUNK_BYTES + q * 32 * 128, &shards->map[owner], bar, nb0 + c * 64,
-                                   row - owner * rps);
+                  tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_big[o_lo], bar, nb0 + c * 64, k0 - o_lo * rps);
+              } else {
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const int row = k0 + q * 32;
+                  const int owner = min(row / rps, last);
+#pragma unroll
+                  for (int c = 0; c < 2; ++c)
+                    tma_load_2d_pair(sB + c * CHUNK_BYTES + q * 32 * 128, &shards->map[owner], bar, nb0 + c * 64,
+                                     row - owner * rps);
+                }
               }
             }
           } else if constexpr (!B_MN) {
@@ -928,11 +945,19 @@ extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards
   ShardedB sh;
   sh.rows_per_shard = rows_per_shard;
   sh.n_shards = n_shards;
+  const uint32_t big_rows = b_mn ? 64 : 128;
+  sh.use_big = rows_per_shard >= (int)big_rows;
   for (int r = 0; r < n_shards; ++r) {
     const uint64_t inner = b_mn ? (uint64_t)N : (uint64_t)K;
     if (encode_tmap_2d(&sh.map[r], B_shards[r], inner, (uint64_t)rows_per_shard, (uint64_t)ldb, 64, 32, 2)) return -102;
+    if (encode_tmap_2d(&sh.map_big[r], B_shards[r], inner, (uint64_t)rows_per_shard, (uint64_t)ldb, 64,
+                       sh.use_big ? big_rows : 32, 2))
+      return -102;
   }
-  for (int r = n_shards; r < MAX_SHARDS; ++r) sh.map[r] = sh.map[0];
+  for (int r = n_shards; r < MAX_SHARDS; ++r) {
+    sh.map[r] = sh.map[0];
+    sh.map_big[r] = sh.map_big[0];
+  }
   GemmArgs args;
   args.M = M; args.N = N; args.K = K;
   args.C = C; args.ldc = ldc; args.C2 = C2; args.ldc2 = ldc2; args.R = R; args.ldr = ldr;

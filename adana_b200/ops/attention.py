@@ -21,9 +21,10 @@ import torch.nn.functional as F
 
 from . import _lib
 
-# auto | native | sdpa | ref.  "auto" currently resolves to the library kernel on a GPU: the hand-written
-# kernels are numerically verified but still slower than cuDNN's (see benchmarks/attention_bench.py);
-# `set_mode("native")` / ADANA_ATTENTION=native / --attention native selects them.
+# auto | native | sdpa | ref.  "auto" resolves to the hand-written tcgen05 kernels whenever they cover the
+# shape (bf16, head_dim 64 or 128, sequence length a multiple of 128) and to the library kernel otherwise.
+# cuDNN's kernels are still faster in isolation (see benchmarks/attention_bench.py): `set_mode("sdpa")` /
+# ADANA_ATTENTION=sdpa / --attention sdpa selects them.
 _FORCE = os.environ.get("ADANA_ATTENTION", "auto")
 
 
@@ -70,7 +71,7 @@ def attention_fwd(q, k, vbuf, v_off, v_hstride, B, S, scale=None, need_grad=True
     v = _v_view(vbuf, v_off, v_hstride, Hk, hd)
     mode = _FORCE
     if mode == "auto":
-        mode = "sdpa" if q.is_cuda else "ref"
+        mode = "native" if native_supported(q, hd, S) else ("sdpa" if q.is_cuda else "ref")
     if mode == "native" and not native_supported(q, hd, S):
         mode = "sdpa" if q.is_cuda else "ref"
     if mode == "native":

@@ -88,7 +88,8 @@ def _attention_impl() -> str:
     from adana_b200.ops import attention as att
 
     mode = att.get_mode()
-    return "tcgen05 kernels (csrc/attention_tcgen05.cu)" if mode == "native" else "torch SDPA (cuDNN library kernel)"
+    native = mode == "native" or (mode == "auto" and att._lib.available() and att._lib.has("adana_attn_bwd"))
+    return "tcgen05 kernels (csrc/attention_tcgen05.cu)" if native else "torch SDPA (cuDNN library kernel)"
 
 
 def emit(payload: dict):

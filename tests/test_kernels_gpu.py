@@ -395,12 +395,13 @@ def test_attention_jvp_matches_torch_func_jvp(hd, Hq, Hk, S):
     assert rel_err(out, fwd_out) < 1e-2
 
 
-@pytest.mark.parametrize("world", [2, 8])
-def test_gather_gemm_reads_row_sharded_weights_in_place(world):
-    """The all-gather fused into the GEMM, with every rank's shard a separate allocation on this GPU."""
+@pytest.mark.parametrize("world,rps", [(2, 96), (8, 96), (4, 352), (8, 864)])
+def test_gather_gemm_reads_row_sharded_weights_in_place(world, rps):
+    """The all-gather fused into the GEMM, with every rank's shard a separate allocation on this GPU.
+    rps = rows per shard: a multiple of 32 but not of the 128-row half tile, so tiles straddle shards
+    (32-row boxes) and, for the larger shards, also lie inside one (whole-tile boxes)."""
     torch.manual_seed(21)
     M, K = 1024, 512
-    rps = 96                                   # rows per shard: a multiple of 32, not of the 128-row half tile
     N = world * rps
     x, w = rnd(M, K), rnd(N, K)
     shards = [w[r * rps:(r + 1) * rps].clone() for r in range(world)]      # separate allocations
