@@ -24,15 +24,16 @@ extern "C" {
 
 // D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
 // a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
-// All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks (rows_per_shard each, a
-// multiple of 32); B_shards[r] points at rank r's slice (local or peer memory, row pitch ldb).  b_mn = 0:
-// C[M,N] = epi(A[M,K] * W[N,K]^T); b_mn = 1: C[M,N] = epi(A[M,K] * W[K,N]).  Each CTA pair fetches its B tiles in
-// 32-row boxes straight from the owning rank, so no gathered copy of W exists.  epi: EPI_BF16, EPI_GELU_DUAL,
+// All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks: rank r holds rows
+// [row_starts[r], row_starts[r+1]) (multiples of 32; nullptr = equal slices of rows_per_shard rows) at B_shards[r]
+// (local or peer memory, row pitch ldb).  b_mn = 0: C[M,N] = epi(A[M,K] * W[N,K]^T); b_mn = 1: C[M,N] = epi(A[M,K] *
+// W[K,N]).  Each CTA pair fetches its B tiles straight from the owning rank — whole-tile TMA boxes inside a slice,
+// 32-row boxes where a tile straddles two slices — so no gathered copy of W exists.  epi: EPI_BF16, EPI_GELU_DUAL,
 // EPI_RESID_F32 (b_mn = 0) or EPI_BF16, EPI_DGELU (b_mn = 1).
-int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards, int rows_per_shard, void* C,
-                           int M, int N, int K, long long lda, long long ldb, long long ldc, int b_mn, int epi,
-                           void* C2, long long ldc2, const void* R, long long ldr, float alpha, int* status,
-                           void* stream);
+int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards, int rows_per_shard,
+                           const int* row_starts, void* C, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, int b_mn, int epi, void* C2, long long ldc2, const void* R, long long ldr,
+                           float alpha, int* status, void* stream);
 // Tile shape policy of adana_gemm_bf16: 0 = per shape (default), 1 = one CTA per 128x256 tile,
 // 2 = CTA pair (cta_group::2) per 256x256 tile, with stream-K for fp32 outputs whose whole-tile
 // waves would idle the machine, 3 = CTA pair without stream-K.  Returns the previous mode.

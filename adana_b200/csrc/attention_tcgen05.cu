@@ -26,6 +26,7 @@ namespace adana {
 constexpr int ATT_BQ = 128;
 constexpr int ATT_BKV = 128;
 constexpr int ATT_THREADS = 192;
+constexpr int ATT_BWD_THREADS = 320;   // TMA warp, MMA warp, two softmax warpgroups (each takes half of the key columns)
 constexpr int ATT_KV_STAGES = 2;
 constexpr float ATT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -455,7 +456,7 @@ struct AttBwdArgs {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                 const __grid_constant__ CUtensorMap tmDQ, const AttBwdArgs args) {
@@ -503,11 +504,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(sdp_free, 4);
-    mbar_init(pds_full, 4);
+    mbar_init(sdp_free, 8);
+    mbar_init(pds_full, 8);
     mbar_init(pds_free, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, 4);
+    mbar_init(dq_free, 8);
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -643,7 +644,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ------------------------------ softmax / epilogue warps --------------------------------
+    // Eight warps: warp w reads the tensor-memory lane quarter w % 4 (query rows), and the two warps of a
+    // quarter split the 128 key columns of the tile (wg = column half).  No row reductions are needed in
+    // the backward (lse and delta come from memory), so the halves are independent.
     const int quad = warp & 3;
+    const int wg = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     uint8_t* sP = smem + L::P_OFF;
@@ -662,11 +667,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after_sync();
-      uint32_t pk[64], dk_[64];
+      uint32_t pk[32], dk_[32];
       const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nl2 = make_float2(-lse, -lse);
       const float2 s2 = make_float2(args.scale, args.scale), nd2 = make_float2(-dl * args.scale, -dl * args.scale);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = wg * 2 + cc;             // 32-column chunk of the tile
         uint32_t sv[32], dv[32];
         tmem_ld_32x32b_x32(tmem_base + S_COL + lane_addr + c * 32, sv);
         tmem_ld_32x32b_x32(tmem_base + DP_COL + lane_addr + c * 32, dv);
@@ -683,8 +689,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const float2 p2 = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2, nd2);
           const float2 d2 = __fmul2_rn(p2, t2);
-          pk[c * 16 + (e >> 1)] = pack_bf16x2(p2.x, p2.y);
-          dk_[c * 16 + (e >> 1)] = pack_bf16x2(d2.x, d2.y);
+          pk[cc * 16 + (e >> 1)] = pack_bf16x2(p2.x, p2.y);
+          dk_[cc * 16 + (e >> 1)] = pack_bf16x2(d2.x, d2.y);
         }
       }
       tc_fence_before_sync();
@@ -696,11 +702,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
 #pragma unroll
-      for (int u16 = 0; u16 < 16; ++u16) {
-        const int ch = u16 >> 3, u = u16 & 7;
-        const int off = ch * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u16 * 4], pk[u16 * 4 + 1], pk[u16 * 4 + 2], pk[u16 * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u16 * 4], dk_[u16 * 4 + 1], dk_[u16 * 4 + 2], dk_[u16 * 4 + 3]);
+      for (int u = 0; u < 8; ++u) {
+        const int off = wg * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);   // chunk wg = this half's 64 columns
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -715,27 +720,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // dQ_i of this item: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the
       // fp32 accumulation buffer.  The adds happen in L2, 128 bytes at a time, instead of 16 vector atomics
       // per thread.  Every warp stages and sends its own 32 rows, so only warp-level synchronisation is needed.
-      uint8_t* sDQw = smem + L::DQ_OFF + quad * 32 * 128;
+      uint8_t* sDQw = smem + L::DQ_OFF + wg * L::DQ_BOX + quad * 32 * 128;   // this warp's 32 rows of box `wg`
 #pragma unroll 1
       for (int half = 0; half < HD / 64; ++half) {
         if (lane == 0) tma_wait_group_read0();      // this warp's previous reduce has read its staging rows
         __syncwarp();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        {
           uint32_t o[32];
-          tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + half * 64 + c * 32, o);
+          tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + half * 64 + wg * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            *reinterpret_cast<uint4*>(sDQw + c * L::DQ_BOX + lane * 128 + ((u ^ (lane & 7)) << 4)) =
+            *reinterpret_cast<uint4*>(sDQw + lane * 128 + ((u ^ (lane & 7)) << 4)) =
                 make_uint4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
         }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           const int tok0 = b * args.S + i * ATT_BQ + quad * 32;
-          tma_reduce_add_3d(&tmDQ, sDQw, half * 64, hq, tok0);
-          tma_reduce_add_3d(&tmDQ, sDQw + L::DQ_BOX, half * 64 + 32, hq, tok0);
+          tma_reduce_add_3d(&tmDQ, sDQw, half * 64 + wg * 32, hq, tok0);
           tma_commit_group();
         }
       }
@@ -752,7 +755,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       __nv_bfloat16* dk_dst = args.dk + (token * args.Hk + hk) * HD;
       __nv_bfloat16* dv_dst = args.dv + token * args.lddv + (long long)hk * args.dv_hstride;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = wg; c < HD / 32; c += 2) {
         uint32_t a[32], bq[32];
         tmem_ld_32x32b_x32(tmem_base + DK_COL + lane_addr + c * 32, a);
         tmem_ld_32x32b_x32(tmem_base + DV_COL + lane_addr + c * 32, bq);
@@ -827,7 +830,7 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
     configured = true;
   }
   const int grid = a.B * a.Hk * (a.S / ATT_BKV);
-  kern<<<grid, ATT_THREADS, AttBwdSmem<HD>::TOTAL, st>>>(tq, tdo, tk, tv, tdq, a);
+  kern<<<grid, ATT_BWD_THREADS, AttBwdSmem<HD>::TOTAL, st>>>(tq, tdo, tk, tv, tdq, a);
   return (int)cudaGetLastError();
 }
 

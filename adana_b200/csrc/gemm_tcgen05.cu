@@ -482,9 +482,15 @@ constexpr int MAX_SHARDS = 8;
 struct ShardedB {
   CUtensorMap map[MAX_SHARDS];       // 32-row boxes: used where a tile straddles two ranks' slices
   CUtensorMap map_big[MAX_SHARDS];   // whole-tile boxes (128 rows K-major / 64 rows MN-major) for the common case
-  int rows_per_shard;   // rows of the weight matrix held by every rank (a multiple of 32)
+  int start[MAX_SHARDS + 1];   // rank r holds weight rows [start[r], start[r+1]); every start is a multiple of 32
   int n_shards;
-  int use_big;          // 0 when a slice has fewer rows than a whole-tile box
+  int use_big;                 // 0 when some slice has fewer rows than a whole-tile box
+  __device__ __forceinline__ int owner_of(int row) const {
+    int o = 0;
+#pragma unroll
+    for (int r = 1; r < MAX_SHARDS; ++r) o += (r < n_shards && row >= start[r]) ? 1 : 0;
+    return o;
+  }
 };
 
 template <bool A_MN, bool B_MN, int EPI, bool SHARDED>
@@ -570,39 +576,38 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
               tma_load_2d_pair(sA + c * CHUNK_BYTES, &tmA, bar, m0 + c * 64, k0);
           }
           if constexpr (SHARDED) {
-            const int rps = shards->rows_per_shard;
-            const int last = shards->n_shards - 1;
             if constexpr (!B_MN) {
               // weight rows = output columns.  One {64 k, 128 n} box when the 128 rows belong to one rank,
               // else 4 boxes {64 k, 32 n}, each from the rank owning those rows
-              const int o_lo = min(nb0 / rps, last), o_hi = min((nb0 + 127) / rps, last);
+              const int o_lo = shards->owner_of(nb0), o_hi = shards->owner_of(nb0 + 127);
               if (o_lo == o_hi && shards->use_big) {
-                tma_load_2d_pair(sB, &shards->map_big[o_lo], bar, k0, nb0 - o_lo * rps);
+                tma_load_2d_pair(sB, &shards->map_big[o_lo], bar, k0, nb0 - shards->start[o_lo]);
               } else {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                   const int row = nb0 + q * 32;
-                  const int owner = min(row / rps, last);
-                  tma_load_2d_pair(sB + q * 32 * 128, &shards->map[owner], bar, k0, row - owner * rps);
+                  const int owner = shards->owner_of(row);
+                  tma_load_2d_pair(sB + q * 32 * 128, &shards->map[owner], bar, k0, row - shards->start[owner]);
                 }
               }
             } else {
               // weight rows = the contraction index: {64 n, 64 k} boxes per 64-column chunk, or two
               // {64 n, 32 k} boxes where the k-block straddles two ranks
-              const int o_lo = min(k0 / rps, last), o_hi = min((k0 + 63) / rps, last);
+              const int o_lo = shards->owner_of(k0), o_hi = shards->owner_of(k0 + 63);
               if (o_lo == o_hi && shards->use_big) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c)
-                  tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_big[o_lo], bar, nb0 + c * 64, k0 - o_lo * rps);
+                  tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_big[o_lo], bar, nb0 + c * 64,
+                                   k0 - shards->start[o_lo]);
               } else {
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                   const int row = k0 + q * 32;
-                  const int owner = min(row / rps, last);
+                  const int owner = shards->owner_of(row);
 #pragma unroll
                   for (int c = 0; c < 2; ++c)
                     tma_load_2d_pair(sB + c * CHUNK_BYTES + q * 32 * 128, &shards->map[owner], bar, nb0 + c * 64,
-                                     row - owner * rps);
+                                     row - shards->start[owner]);
                 }
               }
             }
@@ -921,20 +926,34 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   return -103;
 }
 
-// C = epilogue(A * W^T) (b_mn = 0, W [N, K] split by rows over the ranks: N = n_shards * rows_per_shard) or
-// C = epilogue(A * W) (b_mn = 1, W [K, N] split by rows: K = n_shards * rows_per_shard), where shard r of W
-// lives at B_shards[r] (this rank's memory or a peer's) with row pitch ldb.  The gather of W is part of the
-// GEMM's TMA pipeline; nothing is staged.
+// C = epilogue(A * W^T) (b_mn = 0, W [N, K] split by rows over the ranks) or C = epilogue(A * W) (b_mn = 1,
+// W [K, N] split by rows), where rank r holds rows [row_starts[r], row_starts[r+1]) of W at B_shards[r] (this rank's
+// memory or a peer's) with row pitch ldb; every start is a multiple of 32.  row_starts == nullptr: equal slices
+// of rows_per_shard rows.  Slices cut on multiples of 128 rows (64 for b_mn = 1) are fetched with whole-tile boxes
+// only.  The gather of W is part of the GEMM's TMA pipeline; nothing is staged.
 extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards,
-                                      int rows_per_shard, void* C, int M, int N, int K, long long lda,
-                                      long long ldb, long long ldc, int b_mn, int epi, void* C2, long long ldc2,
-                                      const void* R, long long ldr, float alpha, int* status, void* stream_) {
+                                      int rows_per_shard, const int* row_starts, void* C, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int b_mn, int epi, void* C2,
+                                      long long ldc2, const void* R, long long ldr, float alpha, int* status,
+                                      void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (n_shards < 1 || n_shards > MAX_SHARDS || rows_per_shard <= 0 || (rows_per_shard % 32) != 0) return -110;
+  if (n_shards < 1 || n_shards > MAX_SHARDS) return -110;
   if ((N % 8) != 0 || (ldc % 4) != 0) return -100;
-  if ((!b_mn && (long long)n_shards * rows_per_shard < N) || (b_mn && (long long)n_shards * rows_per_shard < K))
-    return -111;
+  ShardedB sh;
+  sh.n_shards = n_shards;
+  for (int r = 0; r <= MAX_SHARDS; ++r) {
+    const int rr = r < n_shards ? r : n_shards;
+    sh.start[r] = row_starts ? row_starts[rr] : rr * rows_per_shard;
+  }
+  const uint32_t big_rows = b_mn ? 64 : 128;
+  sh.use_big = 1;
+  for (int r = 0; r < n_shards; ++r) {
+    const int rows = sh.start[r + 1] - sh.start[r];
+    if (rows <= 0 || (rows % 32) != 0 || (sh.start[r] % 32) != 0) return -110;
+    if (rows < (int)big_rows) sh.use_big = 0;
+  }
+  if (sh.start[0] != 0 || sh.start[n_shards] < (b_mn ? K : N)) return -111;
   if (g_sm_count == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -942,16 +961,11 @@ extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards
   }
   CUtensorMap tmA;
   if (encode_tmap_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, BM, 2)) return -101;
-  ShardedB sh;
-  sh.rows_per_shard = rows_per_shard;
-  sh.n_shards = n_shards;
-  const uint32_t big_rows = b_mn ? 64 : 128;
-  sh.use_big = rows_per_shard >= (int)big_rows;
   for (int r = 0; r < n_shards; ++r) {
     const uint64_t inner = b_mn ? (uint64_t)N : (uint64_t)K;
-    if (encode_tmap_2d(&sh.map[r], B_shards[r], inner, (uint64_t)rows_per_shard, (uint64_t)ldb, 64, 32, 2)) return -102;
-    if (encode_tmap_2d(&sh.map_big[r], B_shards[r], inner, (uint64_t)rows_per_shard, (uint64_t)ldb, 64,
-                       sh.use_big ? big_rows : 32, 2))
+    const uint64_t rows = (uint64_t)(sh.start[r + 1] - sh.start[r]);
+    if (encode_tmap_2d(&sh.map[r], B_shards[r], inner, rows, (uint64_t)ldb, 64, 32, 2)) return -102;
+    if (encode_tmap_2d(&sh.map_big[r], B_shards[r], inner, rows, (uint64_t)ldb, 64, sh.use_big ? big_rows : 32, 2))
       return -102;
   }
   for (int r = n_shards; r < MAX_SHARDS; ++r) {

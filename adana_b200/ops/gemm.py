@@ -220,37 +220,55 @@ def _ptr_array(shards):
     return (ctypes.c_uint64 * len(vals))(*vals), len(vals)
 
 
+def tile_aligned_row_starts(n_rows: int, world: int, tile: int = 128):
+    """Split `n_rows` weight rows over `world` ranks on multiples of `tile` (the last slice takes the remainder), so
+    that every B tile of the gathering GEMM lies inside one rank's slice.  Returns world + 1 offsets."""
+    tiles = (n_rows + tile - 1) // tile
+    base, extra = divmod(tiles, world)
+    starts, pos = [0], 0
+    for r in range(world):
+        pos = min(n_rows, pos + (base + (1 if r < extra else 0)) * tile)
+        starts.append(pos)
+    return starts
+
+
 def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, out=None, C2=None, R=None, alpha=1.0,
-                out_dtype=torch.bfloat16):
-    """C[M,N] = epi(x · Wᵀ) (b_mn False, W [N,K] row-sharded) or epi(x · W) (b_mn True, W [K,N] row-sharded)."""
+                out_dtype=torch.bfloat16, row_starts=None):
+    """C[M,N] = epi(x · Wᵀ) (b_mn False, W [N,K] row-sharded) or epi(x · W) (b_mn True, W [K,N] row-sharded).
+    `row_starts` (world + 1 offsets, multiples of 32) gives uneven slices; otherwise every slice has
+    `rows_per_shard` rows."""
+    import ctypes
+
     _check2d(x, "x")
     M, K = x.shape
     arr, n = _ptr_array(shards)
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    starts = None if row_starts is None else (ctypes.c_int * (n + 1))(*[int(v) for v in row_starts])
     rc = _lib.lib().adana_gemm_bf16_gather(
-        x.data_ptr(), arr, n, int(rows_per_shard), out.data_ptr(), M, N, K, x.stride(0), int(ldb), out.stride(0),
-        int(b_mn), int(epi), _lib.ptr(C2), 0 if C2 is None else C2.stride(0), _lib.ptr(R), 0 if R is None else R.stride(0),
-        float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+        x.data_ptr(), arr, n, int(rows_per_shard or 0), starts, out.data_ptr(), M, N, K, x.stride(0), int(ldb),
+        out.stride(0), int(b_mn), int(epi), _lib.ptr(C2), 0 if C2 is None else C2.stride(0), _lib.ptr(R),
+        0 if R is None else R.stride(0), float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "adana_gemm_bf16_gather")
     return out
 
 
-def linear_fwd_gathered(x, w_shards, rows_per_shard, out=None):
-    """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows: shard r = rows [r·rows_per_shard, (r+1)·rows_per_shard)."""
+def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None):
+    """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows over the shards (equal slices or `row_starts`)."""
     _, n = _ptr_array(w_shards)
-    return gather_gemm(x, w_shards, rows_per_shard, n * rows_per_shard, ldb=x.shape[1], out=out)
+    N = row_starts[-1] if row_starts is not None else n * rows_per_shard
+    return gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], out=out, row_starts=row_starts)
 
 
-def linear_gelu_fwd_gathered(x, w_shards, rows_per_shard):
+def linear_gelu_fwd_gathered(x, w_shards, rows_per_shard=None, row_starts=None):
     _, n = _ptr_array(w_shards)
-    N = n * rows_per_shard
+    N = row_starts[-1] if row_starts is not None else n * rows_per_shard
     z = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
     h = torch.empty_like(z)
-    gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h)
+    gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=row_starts)
     return z, h
 
 
-def linear_dgrad_gathered(dy, w_shards, rows_per_shard, K_out, out=None):
+def linear_dgrad_gathered(dy, w_shards, rows_per_shard, K_out, out=None, row_starts=None):
     """dx [M, K_out] = dy [M, N] · W with W [N, K_out] split by rows (the contraction index is sharded)."""
-    return gather_gemm(dy, w_shards, rows_per_shard, K_out, ldb=K_out, b_mn=True, out=out)
+    return gather_gemm(dy, w_shards, rows_per_shard, K_out, ldb=K_out, b_mn=True, out=out, row_starts=row_starts)

@@ -55,9 +55,8 @@ def main():
     else:
         rank, world = 0, a.fake
     for (M, N, K) in SHAPES:
-        rps = N // world
-        if rps % 32:
-            continue
+        starts = gemm.tile_aligned_row_starts(N, world)      # slices cut on whole 128-row tiles (uneven)
+        rps = max(b - a for a, b in zip(starts, starts[1:]))  # allocation size per rank
         x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
         y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         full = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
@@ -69,18 +68,21 @@ def main():
             plane.barrier()
             ptrs = plane.peer_ptrs(mine)
             sync = plane.barrier
+            padded = torch.empty(world * rps, K, device="cuda", dtype=torch.bfloat16)
 
             def baseline():
-                dist.all_gather_into_tensor(full.view(-1), mine.view(-1))
+                dist.all_gather_into_tensor(padded.view(-1), mine.view(-1))
+                for r in range(world):      # compact the (slightly uneven) slices into the weight matrix
+                    full[starts[r]:starts[r + 1]].copy_(padded[r * rps:r * rps + starts[r + 1] - starts[r]])
                 gemm.linear_fwd(x, full, out=y)
         else:
-            shards = [(torch.randn(rps, K, device="cuda") * 0.5).bfloat16() for _ in range(world)]
+            shards = [(torch.randn(b - a_, K, device="cuda") * 0.5).bfloat16() for a_, b in zip(starts, starts[1:])]
             ptrs, mine, sync = shards, shards[0], (lambda: None)
 
             def baseline():
                 torch.cat(shards, out=full)
                 gemm.linear_fwd(x, full, out=y)
-        t_fused = timeit(lambda: gemm.linear_fwd_gathered(x, ptrs, rps, out=y), a.iters, sync)
+        t_fused = timeit(lambda: gemm.linear_fwd_gathered(x, ptrs, None, out=y, row_starts=starts), a.iters, sync)
         t_base = timeit(baseline, a.iters, sync)
         t_plain = timeit(lambda: gemm.linear_fwd(x, full, out=y), a.iters, sync)
         if real:
@@ -89,7 +91,7 @@ def main():
             t_fused, t_base, t_plain = tt.tolist()
             plane.barrier()
         flops = 2.0 * M * N * K
-        remote = (world - 1) * rps * K * 2
+        remote = (N - (starts[rank + 1] - starts[rank])) * K * 2
         row = {"mode": "nvlink peers" if real else "local shards", "world": world, "M": M, "N": N, "K": K,
                "fused_ms": round(t_fused, 4), "fused_tflops": round(flops / t_fused / 1e9, 1),
                "allgather_then_gemm_ms": round(t_base, 4), "resident_gemm_ms": round(t_plain, 4),

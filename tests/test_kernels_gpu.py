@@ -420,3 +420,10 @@ def test_gather_gemm_reads_row_sharded_weights_in_place(world, rps):
         assert torch.equal(y, gemm.linear_fwd(x, w))
     finally:
         gemm.set_mode(old)
+    # uneven slices cut on whole tiles: every B tile comes from one rank
+    starts = gemm.tile_aligned_row_starts(N, world)
+    assert starts[0] == 0 and starts[-1] == N and all(s % 128 == 0 for s in starts[:-1])
+    if all(b > a for a, b in zip(starts, starts[1:])):
+        cut = [w[a:b].clone() for a, b in zip(starts, starts[1:])]
+        assert torch.equal(gemm.linear_fwd_gathered(x, cut, row_starts=starts), y)
+        assert rel_err(gemm.linear_dgrad_gathered(dy, cut, None, K, row_starts=starts), dy.float() @ w.float()) < 8e-3
