@@ -1,0 +1,59 @@
+"""The command-line training path end to end on CPU: data -> model -> backend -> train -> eval -> checkpoint ->
+early stop (`--iterations_to_run`) -> `--auto_resume` -> summary.json / metrics.jsonl; a resumed run must land on
+the same weights and losses as an uninterrupted one."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _run(results, data, extra):
+    cmd = [sys.executable, "-m", "adana_b200.main", "--model", "enoki", "--n_layer", "2", "--n_head", "2", "--n_embd", "64",
+           "--qkv_dim", "32", "--mlp_hidden_dim", "128", "--sequence_length", "64", "--batch_size", "4", "--acc_steps", "2",
+           "--vocab_size", "512", "--dataset", "synthetic-zipf", "--datasets_dir", str(data), "--opt", "dana-star-mk4",
+           "--kappa", "0.85", "--clipsnr", "2.0", "--wd_decaying", "--wd_ts", "5", "--lr", "1e-3", "--iterations", "12",
+           "--warmup_steps", "2", "--scheduler", "cos_inf", "--eval_interval", "4", "--eval_batches", "2",
+           "--log_interval", "2", "--latest_ckpt_interval", "5", "--results_base_folder", str(results), "--device", "cpu",
+           "--dtype", "float32", "--distributed_backend", "single", "--seed", "3", *extra]
+    p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    return p.stdout
+
+
+def _exp_dir(results):
+    dirs = [d for d in Path(results).iterdir() if d.is_dir()]
+    assert len(dirs) == 1, dirs
+    return dirs[0]
+
+
+@pytest.mark.timeout(900)
+def test_interrupted_and_resumed_run_equals_uninterrupted_run(tmp_path):
+    data = tmp_path / "data"
+    out = _run(tmp_path / "a", data, ["--iterations_to_run", "7"])
+    assert "iterations_to_run reached" in out
+    exp = _exp_dir(tmp_path / "a")
+    ck = torch.load(exp / "ckpts" / "latest" / "main.pt", map_location="cpu", weights_only=False)
+    assert ck["itr"] == 7 and {"model", "optimizer", "scheduler", "itr"} <= set(ck)
+    assert (exp / "ckpts" / "latest" / "worker_0.pt").exists()
+    out = _run(tmp_path / "a", data, ["--auto_resume"])
+    assert ">Eval: Iter=12" in out and "Iter=2 " not in out.split("Resum")[-1]      # continued, did not start over
+    summary = json.loads((exp / "summary.json").read_text())
+    assert summary["args"]["iterations"] == 12 and "val_loss" in summary
+    rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
+    iters = [r["iter"] for r in rows if "train/loss" in r]
+    assert iters == sorted(iters) and iters[-1] == 12 and any("final-val/loss" in r for r in rows)
+
+    _run(tmp_path / "b", data, [])
+    exp_b = _exp_dir(tmp_path / "b")
+    sb = json.loads((exp_b / "summary.json").read_text())
+    assert abs(summary["val_loss"][-1] - sb["val_loss"][-1]) < 1e-6            # same final validation loss
+    rows_b = [json.loads(l) for l in (exp_b / "metrics.jsonl").read_text().splitlines()]
+    la = {r["iter"]: r["train/loss"] for r in rows if "train/loss" in r}
+    lb = {r["iter"]: r["train/loss"] for r in rows_b if "train/loss" in r}
+    for it in (8, 10, 12):
+        assert abs(la[it] - lb[it]) < 1e-6, (it, la[it], lb[it])
