@@ -57,3 +57,40 @@ def test_interrupted_and_resumed_run_equals_uninterrupted_run(tmp_path):
     lb = {r["iter"]: r["train/loss"] for r in rows_b if "train/loss" in r}
     for it in (8, 10, 12):
         assert abs(la[it] - lb[it]) < 1e-6, (it, la[it], lb[it])
+
+
+@pytest.mark.timeout(900)
+def test_two_rank_fsdp_cli_run_writes_sharded_checkpoint_and_resumes(tmp_path):
+    import os
+    import socket
+
+    def launch(extra):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), "-m", "adana_b200.main", "--model", "enoki", "--n_layer", "2",
+               "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim", "128", "--sequence_length", "64",
+               "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset", "synthetic-zipf",
+               "--datasets_dir", str(tmp_path / "data"), "--opt", "dana-star-mk4", "--kappa", "0.85", "--clipsnr", "2.0",
+               "--wd_decaying", "--wd_ts", "5", "--lr", "1e-3", "--warmup_steps", "2", "--scheduler", "cos_inf",
+               "--eval_interval", "4", "--eval_batches", "2", "--log_interval", "2", "--latest_ckpt_interval", "4",
+               "--results_base_folder", str(tmp_path / "exps"), "--device", "cpu", "--dtype", "float32",
+               "--distributed_backend", "fsdp", "--seed", "3", *extra]
+        env = {**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1"}
+        p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600, env=env)
+        assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+        return p.stdout + p.stderr
+
+    out = launch(["--iterations", "8", "--iterations_to_run", "5"])
+    exp = _exp_dir(tmp_path / "exps")
+    latest = exp / "ckpts" / "latest"
+    assert (latest / "sharded" / "layout.json").exists() and (latest / "sharded" / "rank00001.pt").exists()
+    assert (latest / "meta.pt").exists() and (latest / "worker_1.pt").exists()
+    assert torch.load(latest / "meta.pt", map_location="cpu", weights_only=False)["itr"] == 5
+    out = launch(["--iterations", "8", "--auto_resume"])
+    assert ">Eval: Iter=8" in out
+    rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
+    iters = [r["iter"] for r in rows if "train/loss" in r]
+    assert iters == sorted(set(iters)) and iters[-1] == 8                     # no iteration logged twice
+    assert json.loads((exp / "summary.json").read_text())["args"]["distributed_backend"] == "fsdp"
