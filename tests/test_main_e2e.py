@@ -94,3 +94,28 @@ def test_two_rank_fsdp_cli_run_writes_sharded_checkpoint_and_resumes(tmp_path):
     iters = [r["iter"] for r in rows if "train/loss" in r]
     assert iters == sorted(set(iters)) and iters[-1] == 8                     # no iteration logged twice
     assert json.loads((exp / "summary.json").read_text())["args"]["distributed_backend"] == "fsdp"
+
+
+@pytest.mark.timeout(600)
+def test_two_rank_sharded_muon_cli_run(tmp_path):
+    """`--opt d-muon` under the sharded engine: gather -> Newton-Schulz -> scatter through the command line."""
+    import os
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "adana_b200.main", "--model", "qwen3", "--n_layer", "2", "--n_head", "2",
+           "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim", "128", "--sequence_length", "64", "--batch_size", "8",
+           "--acc_steps", "2", "--vocab_size", "512", "--dataset", "synthetic-zipf", "--datasets_dir", str(tmp_path / "data"),
+           "--opt", "d-muon", "--momentum", "0.95", "--nesterov", "True", "--beta1", "0.8", "--beta2", "0.999", "--lr", "2e-3",
+           "--iterations", "6", "--warmup_steps", "2", "--scheduler", "cos_inf", "--eval_interval", "3", "--eval_batches", "2",
+           "--log_interval", "2", "--results_base_folder", str(tmp_path / "exps"), "--device", "cpu", "--dtype", "float32",
+           "--distributed_backend", "fsdp", "--seed", "3"]
+    env = {**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1"}
+    p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=500, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    rows = [json.loads(l) for l in (_exp_dir(tmp_path / "exps") / "metrics.jsonl").read_text().splitlines()]
+    val = [r["val/loss"] for r in rows if "val/loss" in r] + [r["final-val/loss"] for r in rows if "final-val/loss" in r]
+    assert len(val) >= 3 and val[-1] < val[0]
