@@ -7,5 +7,6 @@ written for JAX/Optax; the rules are restated here in NumPy with the convention 
 """
 from .ode import DanaHparams, ODEInputs, solve_risk_ode  # noqa: F401
 from .plrf import PowerLawRF, train_plrf  # noqa: F401
+from .sweeps import compare_rules, final_risk_exponent, sweep, tau_order_statistics  # noqa: F401
 from .rules import (ademamix_rule, adana_rule, dana_mk4_rule, dana_star_mk4_rule, powerlaw_schedule,  # noqa: F401
                     scale_by_learning_rate)

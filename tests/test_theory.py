@@ -132,3 +132,28 @@ def test_risk_ode_follows_simulated_sgd_and_momentum():
     _, approx = solve_risk_ode(inp, DanaHparams(lambda t: 1.0, lambda t: 0.2 * lr, lambda t: 0.0, lambda t: 1.0), batch, 500, 0.02,
                                approximate=True)
     assert np.max(np.abs(full - approx) / full) < 0.05
+
+
+def test_shared_gradient_comparison_and_kappa_sweep():
+    from adana_b200.logging.tau_stats import compute_tau_order_statistics
+    from adana_b200.theory import compare_rules, final_risk_exponent, sweep, tau_order_statistics
+
+    p = PowerLawRF.initialize_random(1.0, 0.7, 120, 30, seed=2)
+    lr = 0.3 / p.population_trace
+    rules = {"sgd": ((lambda w: 0), (lambda g, s, w=None: (-lr * g, s))),
+             "dana-star-mk4": scale_by_learning_rate(dana_star_mk4_rule(kappa=0.85, clipsnr=2.0), 0.02)}
+    res = compare_rules(p, rules, steps=400, batch=8, seed=0)
+    assert res["sgd"].shape == res["dana-star-mk4"].shape == res["steps"].shape
+    assert res["sgd"][-1] < res["sgd"][0] and res["dana-star-mk4"][-1] < res["dana-star-mk4"][0]
+    # same seed -> identical batches: re-running one rule alone reproduces its curve exactly
+    alone = compare_rules(p, {"sgd": rules["sgd"]}, steps=400, batch=8, seed=0)
+    np.testing.assert_array_equal(alone["sgd"], res["sgd"])
+    assert final_risk_exponent(res["steps"], res["sgd"], p.limit_risk()) < 0
+    sw = sweep(p, lambda k: scale_by_learning_rate(adana_rule(kappa=k), 0.01), [0.7, 1.0], steps=200, batch=8)
+    assert {"0.7", "1", "steps"} <= set(sw)
+    tau = res["_final_states"]["dana-star-mk4"].tau
+    hi, lo = tau_order_statistics(tau)
+    hi2, lo2 = compute_tau_order_statistics(np.asarray(tau))
+    np.testing.assert_allclose(hi, hi2)
+    np.testing.assert_allclose(lo, lo2)
+    assert hi[0] == tau.max() and lo[0] == tau.min()
