@@ -183,16 +183,24 @@ class Engine:
         if self.world > 8 or not _lib.has("adana_p2p_barrier"):
             return None
         nbytes = sum(l.padded * 6 + l.numel * 4 + 4096 for l in self.layouts)
+        plane, err = None, None
         try:
             from ..parallel.p2p import P2PPlane
 
-            return P2PPlane.create(nbytes, self.device, group=self.comm.group)
+            plane = P2PPlane.create(nbytes, self.device, group=self.comm.group)
         except Exception as e:
-            if want == "p2p":
-                raise
-            if self.rank == 0:
-                print(f"[engine] peer-memory plane unavailable ({type(e).__name__}: {e}); using NCCL collectives")
-            return None
+            err = e
+        # every rank must take the same plane: one rank without peer memory sends all of them to NCCL
+        ok = torch.tensor([0.0 if plane is None else 1.0], device=self.device)
+        self.comm.all_reduce_sum(ok)
+        if int(ok.item()) == self.world:
+            return plane
+        if want == "p2p":
+            raise RuntimeError(f"--fsdp_comm p2p: the peer-memory plane could not be set up on every rank ({err})")
+        if self.rank == 0:
+            print(f"[engine] peer-memory plane unavailable on {self.world - int(ok.item())} rank(s) ({err}); "
+                  f"using NCCL collectives")
+        return None
 
     def _block_spec(self) -> BK.BlockSpec:
         m, c = self.model, self.cfg
