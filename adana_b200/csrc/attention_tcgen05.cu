@@ -654,7 +654,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* sP = smem + L::P_OFF;
     uint8_t* sDS = smem + L::DS_OFF;
     bool ok = true;
-    for (int t = 0; t < n_items && ok; ++t) {
+    uint32_t pk[32], dk_[32];   // this thread's 64 columns of P and dS of the item being prepared
+
+    // S_t, dP_t -> P_t, dS_t in registers (frees the S / dP columns for the next item's scores)
+    auto compute = [&](int t) -> bool {
       const int g = t / n_i, i = j + t % n_i;
       const int hq = hk * G + g;
       const long long stat_idx = ((long long)b * args.Hq + hq) * args.S + i * ATT_BQ + r;
@@ -662,12 +665,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const float dl = args.delta[stat_idx];
       const bool diag = (i == j);
       if (!mbar_wait(s_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
-          !mbar_wait(dp_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
-        ok = false;
-        break;
-      }
+          !mbar_wait(dp_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN))
+        return false;
       tc_fence_after_sync();
-      uint32_t pk[32], dk_[32];
       const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nl2 = make_float2(-lse, -lse);
       const float2 s2 = make_float2(args.scale, args.scale), nd2 = make_float2(-dl * args.scale, -dl * args.scale);
 #pragma unroll
@@ -696,11 +696,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(sdp_free);
-      // the P / dS tiles are free once the gradient products of the previous item retired
-      if (!mbar_wait(pds_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
-        ok = false;
-        break;
-      }
+      return true;
+    };
+    // registers -> the swizzled P / dS tiles (free once the gradient products of the previous item retired)
+    auto publish = [&](int t) -> bool {
+      if (!mbar_wait(pds_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int off = wg * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);   // chunk wg = this half's 64 columns
@@ -711,16 +711,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // drain dQ_i of this item into the fp32 accumulation buffer
-      if (!mbar_wait(dq_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
-        ok = false;
-        break;
-      }
+      return true;
+    };
+    // dQ_i of item t: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the fp32
+    // accumulation buffer.  The adds happen in L2, 128 bytes at a time, instead of 16 vector atomics per thread.
+    // Every warp stages and sends its own 32 rows of its 32-column box, so warp-level synchronisation suffices.
+    auto drain = [&](int t) -> bool {
+      const int g = t / n_i, i = j + t % n_i;
+      const int hq = hk * G + g;
+      if (!mbar_wait(dq_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
       tc_fence_after_sync();
-      // dQ_i of this item: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the
-      // fp32 accumulation buffer.  The adds happen in L2, 128 bytes at a time, instead of 16 vector atomics
-      // per thread.  Every warp stages and sends its own 32 rows, so only warp-level synchronisation is needed.
-      uint8_t* sDQw = smem + L::DQ_OFF + wg * L::DQ_BOX + quad * 32 * 128;   // this warp's 32 rows of box `wg`
+      uint8_t* sDQw = smem + L::DQ_OFF + wg * L::DQ_BOX + quad * 32 * 128;
 #pragma unroll 1
       for (int half = 0; half < HD / 64; ++half) {
         if (lane == 0) tma_wait_group_read0();      // this warp's previous reduce has read its staging rows
@@ -745,6 +746,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
+      return true;
+    };
+
+    if (PIPELINED) {
+      // P / dS of item t+1 are computed while the tensor cores run the gradient products of item t
+      ok = n_items > 0 && compute(0) && publish(0);
+      for (int t = 0; t < n_items && ok; ++t) {
+        const bool more = t + 1 < n_items;
+        if (more) ok = compute(t + 1);
+        if (ok) ok = drain(t);
+        if (ok && more) ok = publish(t + 1);
+      }
+    } else {
+      // dQ aliases the S columns: the next scores cannot start before this item's dQ is drained
+      for (int t = 0; t < n_items && ok; ++t) ok = compute(t) && publish(t) && drain(t);
     }
     if (lane == 0) tma_wait_group_read0();   // staging rows are not needed any more
     __syncwarp();

@@ -259,7 +259,7 @@ def run_reference(a):
     # rank leaves a note that every rank's watchdog thread polls, and the whole arm has a time limit
     import threading
 
-    limit = float(os.environ.get("ADANA_REF_TIMEOUT", "1500"))
+    limit = float(os.environ.get("ADANA_REF_TIMEOUT", "900"))
     note = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data")) / f"ref_failed.{os.environ.get('MASTER_PORT', '0')}"
     note.parent.mkdir(parents=True, exist_ok=True)
     if rank == 0 and note.exists():
