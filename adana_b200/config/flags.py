@@ -244,6 +244,9 @@ GROUPS: dict[str, list[Flag]] = {
           help="collective implementation of the sharded engine: own peer-memory kernels or NCCL"),
         F("--fsdp_prefetch", default=1, type=int, help="blocks gathered ahead of compute"),
         F("--reduce_dtype", default="bfloat16", choices=["bfloat16", "float32"]),
+        F("--fsdp_weights", default="resident", choices=["resident", "gathered"],
+          help="resident: every rank keeps the bf16 weights, refreshed by the optimizer step; gathered (Enoki, bf16, "
+               "peer-memory plane): every rank keeps only its row slices and the GEMMs fetch weight tiles from the owners"),
         F("--attention", default="auto", choices=["auto", "native", "sdpa"],
           help="attention implementation: hand-written tcgen05 kernels or the PyTorch SDPA library call"),
         F("--heartbeat_timeout", default=0.0, type=float,

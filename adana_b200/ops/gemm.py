@@ -26,6 +26,29 @@ def set_mode(mode: int) -> int:
     return _lib.lib().adana_gemm_set_mode(int(mode))
 
 
+class ShardedWeight:
+    """A weight matrix [N, K] (bf16) that is NOT held in one piece: rank r holds rows [row_starts[r], row_starts[r+1])
+    at address `ptrs[r]` (its own memory or a peer's).  `linear_fwd`, `linear_gelu_fwd`, `linear_resid_fwd`,
+    `linear_dgrad` and `linear_dgrad_dgelu` accept it in place of a tensor and run the gathering GEMM, which fetches
+    every B tile from its owner.  `local` optionally keeps this process's tensors alive (and serves the CPU path)."""
+
+    def __init__(self, ptrs, row_starts, N: int, K: int, local=None):
+        import ctypes
+
+        vals = [int(p.data_ptr()) if torch.is_tensor(p) else int(p) for p in ptrs]
+        self.ptrs = (ctypes.c_uint64 * len(vals))(*vals)
+        self.row_starts = [int(v) for v in row_starts]
+        assert len(self.row_starts) == len(vals) + 1 and self.row_starts[0] == 0 and self.row_starts[-1] == N
+        self.shape = (N, K)
+        self.local = local
+
+    def full(self) -> torch.Tensor:
+        """The gathered matrix, from the local tensors (single-process use and CPU reference path)."""
+        if self.local is None or len(self.local) != len(self.row_starts) - 1:
+            raise RuntimeError("this ShardedWeight has no local copy of every slice")
+        return torch.cat([t.reshape(-1, self.shape[1]) for t in self.local], 0)
+
+
 def _check2d(t: torch.Tensor, name: str):
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with a contiguous last dimension, got {tuple(t.shape)} / {t.stride()}")
@@ -60,6 +83,10 @@ def use_cuda(*ts) -> bool:
 
 
 def linear_fwd(x, w, out=None):
+    if isinstance(w, ShardedWeight):
+        if not (x.is_cuda and _lib.available()):
+            return linear_fwd(x, w.full(), out)
+        return gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], out=out, row_starts=w.row_starts)
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w):
@@ -86,6 +113,13 @@ def linear_fwd_f32(x, w, out=None, alpha=1.0):
 
 def linear_gelu_fwd(x, w):
     """Returns (z, gelu(z)) in one pass: z is kept for backward, gelu(z) feeds the next GEMM."""
+    if isinstance(w, ShardedWeight):
+        if not (x.is_cuda and _lib.available()):
+            return linear_gelu_fwd(x, w.full())
+        z = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+        h = torch.empty_like(z)
+        gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=w.row_starts)
+        return z, h
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w):
@@ -99,6 +133,13 @@ def linear_gelu_fwd(x, w):
 
 def linear_resid_fwd(x, w, resid, alpha=1.0, out=None):
     """out(f32) = resid(f32) + alpha * x·wᵀ ; `out` may alias `resid`."""
+    if isinstance(w, ShardedWeight):
+        if not (x.is_cuda and _lib.available()):
+            return linear_resid_fwd(x, w.full(), resid, alpha, out)
+        if out is None:
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+        return gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], epi=EPI_RESID_F32, out=out, R=resid, alpha=alpha,
+                           row_starts=w.row_starts)
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w, resid):
@@ -128,6 +169,11 @@ def linear_swiglu_fwd(x, w_gu):
 
 def linear_dgrad(dy, w, out=None, alpha=1.0):
     """dx [M,K] = alpha * dy [M,N] · w [N,K]."""
+    if isinstance(w, ShardedWeight):
+        if not (dy.is_cuda and _lib.available()):
+            return linear_dgrad(dy, w.full(), out, alpha)
+        return gather_gemm(dy, w.ptrs, None, w.shape[1], ldb=w.shape[1], b_mn=True, out=out, alpha=alpha,
+                           row_starts=w.row_starts)
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w):
@@ -159,6 +205,12 @@ def linear_dgrad_f32(dy, w, out=None, beta=0.0, resid=None):
 
 def linear_dgrad_dgelu(dy, w, z, alpha=1.0):
     """dz = alpha * (dy · w) * gelu'(z): gradient through `gelu` fused in the dgrad epilogue."""
+    if isinstance(w, ShardedWeight):
+        if not (dy.is_cuda and _lib.available()):
+            return linear_dgrad_dgelu(dy, w.full(), z, alpha)
+        out = torch.empty((dy.shape[0], w.shape[1]), dtype=torch.bfloat16, device=dy.device)
+        return gather_gemm(dy, w.ptrs, None, w.shape[1], ldb=w.shape[1], b_mn=True, epi=EPI_DGELU, out=out, R=z, alpha=alpha,
+                           row_starts=w.row_starts)
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w, z):

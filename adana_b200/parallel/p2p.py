@@ -118,6 +118,15 @@ class P2PPlane:
                                                 ctypes.byref(hyper), _lib.ptr(clip_coef_t), _lib.stream_ptr())
         _lib.check_rc(rc, "adana_p2p_opt_step_push")
 
+    def opt_step_push_to(self, p, g, m, v, tau, dst_ptrs, push_off: int, hyper, clip_coef_t):
+        """Fused optimizer step whose bf16 results are stored at `push_off` into the buffers whose device addresses
+        are given in `dst_ptrs` (own or peer memory) instead of into every rank's copy."""
+        arr = _u64_array([int(x) for x in dst_ptrs])
+        rc = _lib.lib().adana_p2p_opt_step_push(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _lib.ptr(tau),
+                                                arr, len(dst_ptrs), push_off, p.numel(), ctypes.byref(hyper),
+                                                _lib.ptr(clip_coef_t), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_opt_step_push")
+
     def push_f32(self, src: torch.Tensor, dst_full: torch.Tensor, dst_off: int):
         rc = _lib.lib().adana_p2p_push_f32(src.data_ptr(), self.peer_ptrs(dst_full), self.world, dst_off, src.numel(),
                                            _lib.stream_ptr())

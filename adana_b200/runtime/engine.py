@@ -63,8 +63,11 @@ class _Bridge(torch.autograd.Function):
 
 
 class Unit:
-    def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt, plane=None):
+    def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt, plane=None,
+                 resident_weights: bool = True):
         self.layout = layout
+        self.slices = {}     # gathered mode: key -> (slice buffer, row_starts, flat offset, rows, cols)
+        self.segments = []   # gathered mode: (flat_lo, flat_hi, owner rank, address of the owner's slice buffer)
         self.plane = plane
         self.padded = layout.padded
         self.shard_len = layout.padded // world if sharded else layout.padded
@@ -74,7 +77,11 @@ class Unit:
         self.grads = plane.alloc(self.padded, torch.float32) if plane is not None else torch.zeros(self.padded, **f32)
         self.grad_shard = torch.zeros(self.shard_len, **f32) if (sharded and world > 1) else self.grads
         self.low_precision = cdt != torch.float32
-        if self.low_precision:
+        if self.low_precision and not resident_weights:
+            # gathered mode: no rank holds the unit's bf16 weights in one piece (see Engine._make_slices)
+            self.weights = None
+            self.w_shard = None
+        elif self.low_precision:
             self.weights = (plane.alloc(self.padded, cdt) if plane is not None
                             else torch.zeros(self.padded, dtype=cdt, device=device))
             if plane is not None:      # peers store into `weights` directly: my shard is a slice of it
@@ -150,9 +157,19 @@ class Engine:
 
         self.layouts = build_layouts(model, self.world if self.sharded else 1)
         self.plane = self._make_plane()
-        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, self.plane)
+        # `--fsdp_weights gathered`: the block matrices are never all-gathered.  With the peer-memory plane every
+        # rank keeps only its row slice of each matrix and the GEMMs fetch B tiles from the owners; without it
+        # (one GPU) the slices are views of the resident matrix, which exercises the same GEMM path.
+        self.gathered = (getattr(cfg, "fsdp_weights", "resident") == "gathered" and self.device.type == "cuda"
+                         and self.cdt == torch.bfloat16 and getattr(model, "arch", "") == "enoki"
+                         and not getattr(cfg, "moe", False))
+        split = self.gathered and self.plane is not None
+        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, self.plane,
+                                       resident_weights=not (split and l.name != "root"))
                                   for l in self.layouts]
         self.spec = self._block_spec()
+        if split:
+            self._make_slices()
         self.freqs = model.freqs_cis.to(self.device).contiguous()
         self._anchor = torch.zeros((), device=self.device, requires_grad=True)
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -202,6 +219,38 @@ class Engine:
                   f"using NCCL collectives")
         return None
 
+    # ---- gathered weights ----------------------------------------------------------------------------------
+    _MATS = (("qkv", "attn.c_attn.weight"), ("o", "attn.c_proj.weight"), ("fc", "mlp.c_fc.weight"),
+             ("down", "mlp.c_proj.weight"))
+
+    def _make_slices(self):
+        """Row slices of every block matrix in the symmetric arena, cut on whole 128-row tiles; rank r keeps rows
+        [row_starts[r], row_starts[r+1]).  `segments` maps flat ranges of the unit to (owner, owner's buffer)."""
+        from ..ops.gemm import tile_aligned_row_starts
+
+        for u in self.units:
+            if u.weights is not None:
+                continue
+            for key, suffix in self._MATS:
+                sl = u.layout.slot(suffix)
+                rows, cols = sl.shape
+                starts = tile_aligned_row_starts(rows, self.world)
+                if any(b <= a for a, b in zip(starts, starts[1:])):
+                    raise ValueError(f"--fsdp_weights gathered: {sl.name} has fewer 128-row tiles than ranks")
+                most = max(b - a for a, b in zip(starts, starts[1:]))
+                buf = self.plane.alloc(most * cols, self.cdt)
+                ptrs = self.plane.peer_ptrs(buf)
+                u.slices[key] = (buf, starts, sl.offset, rows, cols, ptrs)
+                for r in range(self.world):
+                    u.segments.append((sl.offset + starts[r] * cols, sl.offset + starts[r + 1] * cols, r, int(ptrs[r])))
+            u.segments.sort()
+
+    def _fill_slices(self, u: Unit, full: torch.Tensor):
+        """Copy this rank's rows of every matrix out of a full copy of the unit's parameters."""
+        for key, (buf, starts, off, rows, cols, _) in u.slices.items():
+            a, b = starts[self.rank], starts[self.rank + 1]
+            buf[:(b - a) * cols].copy_(full[off + a * cols: off + b * cols])
+
     def _block_spec(self) -> BK.BlockSpec:
         m, c = self.model, self.cfg
         hd = m.head_dim
@@ -234,7 +283,9 @@ class Engine:
                     # every rank starts from rank 0's initialisation, whatever its own seed was
                     self.comm.broadcast(full, src=0)
                 u.master.copy_(full[u.shard_off:u.shard_off + u.shard_len])
-                if u.weights.data_ptr() != u.master.data_ptr():
+                if u.weights is None:
+                    self._fill_slices(u, full)
+                elif u.weights.data_ptr() != u.master.data_ptr():
                     u.weights.copy_(full)
                 del full
 
@@ -272,14 +323,18 @@ class Engine:
                     n = off - first.offset
                     r, c = rows_cols
                     assert n == r * c
-                    return (u.weights[first.offset:first.offset + n].view(r, c),
-                            u.grads[first.offset:first.offset + n].view(r, c))
+                    gview = u.grads[first.offset:first.offset + n].view(r, c)
+                    if u.weights is None:
+                        return None, gview                 # gathered: the weight entry is set below
+                    return u.weights[first.offset:first.offset + n].view(r, c), gview
                 if self.model.arch == "enoki":
                     W["qkv"], Gd["qkv"] = fused(["attn.c_attn.weight"], (sp.proj_out, sp.d))
                     W["o"], Gd["o"] = fused(["attn.c_proj.weight"], (sp.d, sp.n_head * sp.hd))
                     W["fc"], Gd["fc"] = fused(["mlp.c_fc.weight"], (sp.mlp, sp.d))
                     W["down"], Gd["down"] = fused(["mlp.c_proj.weight"], (sp.d, sp.mlp))
                     qn, kn = "attn.q_layernorm.weight", "attn.k_layernorm.weight"
+                    if self.gathered:
+                        self._bind_gathered(u, W)
                 else:
                     W["qkv"], Gd["qkv"] = fused(["attn.q_proj.weight", "attn.k_proj.weight", "attn.v_proj.weight"],
                                                 (sp.proj_out, sp.d))
@@ -292,6 +347,22 @@ class Engine:
                         sl = lay.slot(suffix)
                         W[key], Gd[key] = small(sl), u.view(u.grads, sl)
             u.W, u.Gd = W, Gd
+
+    def _bind_gathered(self, u: Unit, W: dict):
+        """Replace the four block matrices of `W` by `ShardedWeight`s."""
+        from ..ops.gemm import ShardedWeight, tile_aligned_row_starts
+
+        for key, _ in self._MATS:
+            if u.weights is None:      # true row slices, one per rank, addressed through peer pointers
+                buf, starts, off, rows, cols, ptrs = u.slices[key]
+                W[key] = ShardedWeight(list(ptrs), starts, rows, cols, local=None)
+            else:                      # one process: up to 8 virtual slices that are views of the resident matrix
+                w = W[key]
+                rows, cols = w.shape
+                k = max(1, min(8, rows // 128))
+                starts = tile_aligned_row_starts(rows, k)
+                views = [w[a:b] for a, b in zip(starts, starts[1:])]
+                W[key] = ShardedWeight(views, starts, rows, cols, local=views)
 
     def _rebind_module_params(self):
         """Point the module's parameters at the engine's storage (or release them when sharded)."""
@@ -534,6 +605,35 @@ class Engine:
                     continue
                 ls, le = s - lo, e - lo
                 hyper = opt.hyper_for(grp, t)
+                if self.plane is not None and u.weights is None:
+                    # gathered weights: the new bf16 values of a flat range go to the ONE rank that owns those
+                    # rows; ranges without a bf16 copy (norm weights, padding) only update their state
+                    h = O.make_hyper(kind=kind, grad_scale=1.0 / self.world, **hyper)
+                    tau = u.state.get("tau")
+
+                    def step(a, b, dst=None, dst_off=0):
+                        x0, x1 = a - lo, b - lo
+                        tv = tau[x0:x1] if tau is not None else None
+                        if dst is None:
+                            O.fused_step(u.master[x0:x1], u.grad_shard[x0:x1], u.state["m"][x0:x1], u.state["v"][x0:x1],
+                                         tv, None, kind=kind, grad_scale=1.0 / self.world, clip_coef_t=self._clip,
+                                         diag=None, **hyper)
+                        else:
+                            self.plane.opt_step_push_to(u.master[x0:x1], u.grad_shard[x0:x1], u.state["m"][x0:x1],
+                                                        u.state["v"][x0:x1], tv, [dst], dst_off, h, self._clip)
+
+                    pos = s
+                    for (flo, fhi, _owner, ptr) in u.segments:
+                        a2, b2 = max(flo, s), min(fhi, e)
+                        if a2 >= b2:
+                            continue
+                        if pos < a2:
+                            step(pos, a2)
+                        step(a2, b2, ptr, a2 - flo)
+                        pos = b2
+                    if pos < e:
+                        step(pos, e)
+                    continue
                 if self.plane is not None:
                     h = O.make_hyper(kind=kind, grad_scale=1.0 / self.world, **hyper)
                     self.plane.opt_step_push(u.master[ls:le], u.grad_shard[ls:le], u.state["m"][ls:le],
@@ -569,6 +669,9 @@ class Engine:
         """Re-derive compute weights from the master copy (after an external optimizer or a load)."""
         with torch.no_grad():
             for u in self.units:
+                if u.weights is None:            # gathered: every rank refills its own row slices
+                    self._fill_slices(u, self._gather_full(u.master, u))
+                    continue
                 if self.plane is not None:
                     self.comm.all_gather(u.master.to(self.cdt), u.weights)
                     continue

@@ -12,7 +12,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, plane):
+def _worker(rank, world, plane, weights="resident"):
     import torch.distributed as dist
 
     from conftest import tiny_args
@@ -26,11 +26,12 @@ def _worker(rank, world, plane):
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     a = tiny_args("enoki", n_embd=256, n_head=4, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024,
                   opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True, wd_ts=3.0,
-                  acc_steps=2, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane)
+                  acc_steps=2, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane, fsdp_weights=weights)
     torch.manual_seed(0)
     m = get_model(a).to(a.device)
     eng = attach(m, a, comm=Comm(), sharded=True, device=a.device)
     assert (eng.plane is not None) == (plane == "p2p")
+    assert (eng.units[0].weights is None) == (weights == "gathered")
     specs = m.get_parameter_group_specs()
     for g in specs:
         g["param_names"] = g["params"]
@@ -113,3 +114,19 @@ def test_gather_gemm_over_nvlink_peers():
     res = _spawn(_gather_gemm_worker, world)
     for r in range(world):
         assert res[r]["err_y"] < 8e-3 and res[r]["err_dx"] < 8e-3, res[r]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gathered_weights_over_peers_match_resident_weights():
+    """Every rank keeps only its row slices of the block matrices; forward / backward GEMMs fetch the other rows
+    from the peers and the optimizer stores each new bf16 value at its owner.  Same result as resident weights."""
+    from test_distributed_cpu import _spawn, _t
+
+    world = 2
+    res = {w: _spawn(_worker, world, "p2p", w) for w in ("resident", "gathered")}
+    for a, b in zip(res["resident"][0]["losses"], res["gathered"][0]["losses"]):
+        assert abs(a - b) < 5e-3
+    for k, v in res["resident"][0]["params"].items():
+        d = (_t(res["gathered"][0]["params"][k]) - _t(v)).abs()
+        assert d.max().item() < 5e-3, (k, d.max().item())
+        assert torch.equal(_t(res["gathered"][0]["params"][k]), _t(res["gathered"][1]["params"][k]))
