@@ -53,6 +53,8 @@ def parse():
     p.add_argument("--no_e2e", action="store_true")
     p.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     p.add_argument("--ref_no_compile", action="store_true")
+    p.add_argument("--fsdp_weights", default="resident", choices=["resident", "gathered"],
+                   help="ours: keep the bf16 block matrices resident on every rank, or as row slices fetched by the GEMMs")
     return p.parse_args()
 
 
@@ -130,6 +132,7 @@ def run_ours(a):
     args.scheduler, args.iterations, args.warmup_steps = "cos_inf", 100000, 1000
     args.final_div_factor, args.dataset, args.log_interval = 0.1, "fineweb", 0
     args.attention = a.attention
+    args.fsdp_weights = a.fsdp_weights
     steps_total = a.warmup + a.steps
     tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
     if rank == 0:
@@ -240,7 +243,7 @@ def run_ours(a):
                          "global_batch": a.per_gpu_seqs * world, "seq_len": args.sequence_length,
                          "micro_batch": a.micro_batch, "acc_steps": acc, "optimizer": "dana-star-mk4",
                          "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2",
-                         "attention": _attention_impl()},
+                         "attention": _attention_impl(), "fsdp_weights": a.fsdp_weights},
               "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "exposed_comm": exposed,
               "peak_mem_gib": round(mem, 2), "final_loss": final_loss})
     backend.finalize()
