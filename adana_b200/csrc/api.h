@@ -30,10 +30,14 @@ extern "C" {
 // W[K,N]).  Each CTA pair fetches its B tiles straight from the owning rank — whole-tile TMA boxes inside a slice,
 // 32-row boxes where a tile straddles two slices — so no gathered copy of W exists.  epi: EPI_BF16, EPI_GELU_DUAL,
 // EPI_RESID_F32 (b_mn = 0) or EPI_BF16, EPI_DGELU (b_mn = 1).
+// With `stage` (a [rows of W, ldb] bf16 matrix of this rank), `flags` (2 + rows / 64 ints) and `my_rank`, extra
+// warps of the same kernel copy the remote slices into `stage` once, while the tiles on my_rank's own slice run,
+// and the other tiles read the staged copy: every weight byte crosses the link once.  Slices must then be cut on
+// multiples of 128 rows (64 for b_mn = 1), and launches that share `stage`/`flags` be ordered on one stream.
 int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards, int rows_per_shard,
                            const int* row_starts, void* C, int M, int N, int K, long long lda, long long ldb,
                            long long ldc, int b_mn, int epi, void* C2, long long ldc2, const void* R, long long ldr,
-                           float alpha, int* status, void* stream);
+                           float alpha, int my_rank, void* stage, int* flags, int* status, void* stream);
 // Tile shape policy of adana_gemm_bf16: 0 = per shape (default), 1 = one CTA per 128x256 tile,
 // 2 = CTA pair (cta_group::2) per 256x256 tile, with stream-K for fp32 outputs whose whole-tile
 // waves would idle the machine, 3 = CTA pair without stream-K.  Returns the previous mode.

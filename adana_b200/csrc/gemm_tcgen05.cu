@@ -474,14 +474,37 @@ struct PairWork {
   }
 };
 
-// The B operand of the "gathering" variant: one tensor map per rank over that rank's slice of the
-// weight rows (its own memory or a peer's, mapped over NVLink).  The CTA fetches B in 32-row boxes,
-// each from the rank that owns those rows, so the all-gather of the sharded weight happens tile
-// by tile inside the GEMM's TMA pipeline and no gathered copy of the weight ever exists.
+// The B operand of the "gathering" variants: one tensor map per rank over that rank's slice of the
+// weight rows (its own memory or a peer's, mapped over NVLink).
+//
+// Direct variant (SHARDED == 1): the CTA fetches every B box from the rank that owns those rows, so no gathered
+// copy of the weight exists.  Peer memory is not cached in the reader's L2, so a remote tile crosses the link once
+// per row tile that uses it: right for skinny problems, link-bound for M of many row tiles.
+//
+// Staged variant (SHARDED == 2): eight extra warps per CTA copy the remote slices, once, with plain 16-byte loads
+// from the peers into a local staging matrix, taking 4-row units from a ticket counter in the order in which the
+// tiles will want them, and count finished units per chunk (128 weight rows, or one 64-row k-block).  The tile
+// order (or the k-loop) is rotated so that work on this rank's own slice comes first; a producer that reaches a
+// remote chunk waits (bounded) for its counter, then reads the chunk from the staging matrix with TMA.  Every byte
+// of the weight crosses NVLink once and the copy runs under the tiles of the local slice.
 constexpr int MAX_SHARDS = 8;
+constexpr int GATHER_COPY_WARPS = 8;
+constexpr int GATHER_THREADS = GEMM_THREADS + 32 * GATHER_COPY_WARPS;
+constexpr int STAGE_UNIT_ROWS = 4;
 struct ShardedB {
   CUtensorMap map[MAX_SHARDS];       // 32-row boxes: used where a tile straddles two ranks' slices
   CUtensorMap map_big[MAX_SHARDS];   // whole-tile boxes (128 rows K-major / 64 rows MN-major) for the common case
+  CUtensorMap map_stage;             // whole-tile boxes over the staging matrix (rows by their global index)
+  const void* ptr[MAX_SHARDS];       // base address of each rank's slice
+  void* stage;                 // staging matrix [rows_total, pitch] of this rank
+  int* flags;                  // [0] next unit ticket, [1] units finished, [2 + c] units finished of chunk c
+  long long pitch_bytes;       // row pitch of the slices and of the staging matrix
+  int row_bytes;               // bytes of one weight row (a multiple of 16)
+  int rows_total;
+  int me;                      // the rank whose slice is local: never staged, never waited for
+  int chunk_rows;              // 128 (weight rows = output columns) or 64 (weight rows = contraction index)
+  int rot_tile;                // tile (or k-block) rotation that puts the local slice first
+  int rot_row;                 // the same in weight rows: where the copy order starts
   int start[MAX_SHARDS + 1];   // rank r holds weight rows [start[r], start[r+1]); every start is a multiple of 32
   int n_shards;
   int use_big;                 // 0 when some slice has fewer rows than a whole-tile box
@@ -491,9 +514,114 @@ struct ShardedB {
     for (int r = 1; r < MAX_SHARDS; ++r) o += (r < n_shards && row >= start[r]) ? 1 : 0;
     return o;
   }
+  __device__ __forceinline__ int units_of_chunk(int c) const {
+    const int rows = min(chunk_rows, rows_total - c * chunk_rows);
+    return (rows + STAGE_UNIT_ROWS - 1) / STAGE_UNIT_ROWS;
+  }
+  __device__ __forceinline__ int total_units() const {
+    return (rows_total + STAGE_UNIT_ROWS - 1) / STAGE_UNIT_ROWS;
+  }
 };
 
-template <bool A_MN, bool B_MN, int EPI, bool SHARDED>
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Producer side of the staged variant: has chunk `c` of the staging matrix been filled?  `all_ready` caches the
+// answer "every unit is done", after which no counter is read any more.  Bounded like every other wait here.
+__device__ __forceinline__ bool stage_wait(const ShardedB* sh, int c, bool& all_ready, volatile int* abort_flag,
+                                           int* status) {
+  if (all_ready) return true;
+  if (ld_acquire_gpu(sh->flags + 1) >= sh->total_units()) {
+    all_ready = true;
+    fence_proxy_async_all();
+    return true;
+  }
+  const int target = sh->units_of_chunk(c);
+  const int* f = sh->flags + 2 + c;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(f) < target) {
+    if (((++spins) & 0x3fu) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > ADANA_WAIT_TIMEOUT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, (int)ST_TIMEOUT_PEER_FLAG);
+        return false;
+      }
+    }
+  }
+  fence_proxy_async_all();  // the chunk was written through the generic proxy; TMA reads it through the async one
+  return true;
+}
+
+__device__ __forceinline__ void copy_vec16(const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int lane) {
+  // eight loads in flight per lane (4 KiB per warp), the ragged end predicated rather than serialised
+  for (int i = lane; i < n; i += 8 * 32) {
+    uint4 t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i + j * 32 < n) t[j] = ld_peer_v4(src + i + j * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i + j * 32 < n) dst[i + j * 32] = t[j];
+  }
+}
+
+// Copier warps of the staged variant: take 4-row units in rotated row order until none is left.
+__device__ __forceinline__ void stage_copy_loop(const ShardedB* sh, int lane) {
+  const int total = sh->total_units();
+  const int nv = sh->row_bytes >> 4;
+  const bool dense = sh->pitch_bytes == (long long)sh->row_bytes;
+  int u = 0;
+  if (lane == 0) u = atomicAdd(sh->flags, 1);
+  u = __shfl_sync(0xffffffffu, u, 0);
+  while (u < total) {
+    int next = 0;
+    if (lane == 0) next = atomicAdd(sh->flags, 1);  // the next ticket is on its way while this unit is copied
+    int row = u * STAGE_UNIT_ROWS + sh->rot_row;
+    if (row >= sh->rows_total) row -= sh->rows_total;
+    const int rows = min(STAGE_UNIT_ROWS, sh->rows_total - row);
+    const int owner = sh->owner_of(row);
+    if (owner != sh->me) {
+      const char* src = reinterpret_cast<const char*>(sh->ptr[owner]) + (long long)(row - sh->start[owner]) * sh->pitch_bytes;
+      char* dst = reinterpret_cast<char*>(sh->stage) + (long long)row * sh->pitch_bytes;
+      if (dense) {
+        copy_vec16(reinterpret_cast<const uint4*>(src), reinterpret_cast<uint4*>(dst), nv * rows, lane);
+      } else {
+        for (int r = 0; r < rows; ++r)
+          copy_vec16(reinterpret_cast<const uint4*>(src + r * sh->pitch_bytes),
+                     reinterpret_cast<uint4*>(dst + r * sh->pitch_bytes), nv, lane);
+      }
+      fence_proxy_async_all();
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence();
+        red_release_gpu_add(sh->flags + 2 + row / sh->chunk_rows, 1);
+      }
+    }
+    if (lane == 0) red_release_gpu_add(sh->flags + 1, 1);
+    u = __shfl_sync(0xffffffffu, next, 0);
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI, int SHARDED>
 __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
                                                const ShardedB* __restrict__ shards, const GemmArgs& args) {
   extern __shared__ uint8_t smem_raw[];
@@ -550,14 +678,40 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       uint32_t phase = 0;
       bool ok = true;
       PairWork w(pair, npairs, num_tiles, num_kb, args.streamk);
+      bool all_ready = false;  // staged variant: every remote chunk is known to be in the staging matrix
       while (ok && w.next()) {
         int mi, ni;
         tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        if constexpr (SHARDED == 2 && !B_MN) {  // tiles on this rank's own slice first
+          ni += shards->rot_tile;
+          if (ni >= args.tiles_n) ni -= args.tiles_n;
+        }
         const int m0 = mi * P_BM + (int)rank * 128;  // this CTA's rows of A and of the output
         const int n0 = ni * TILE_N;
         // this CTA's 128 rows (columns) of B: second half of the tile, or the "up" rows when gated
         const int nb0 = GATED_FWD ? (leader ? n0 : args.b_off2 + n0) : n0 + (int)rank * 128;
+        bool b_staged = false;  // staged variant, weight rows = output columns: one owner per tile half
+        if constexpr (SHARDED == 2 && !B_MN) {
+          b_staged = nb0 >= shards->rows_total || shards->owner_of(nb0) != shards->me;
+          if (b_staged && nb0 < shards->rows_total &&
+              !stage_wait(shards, nb0 / shards->chunk_rows, all_ready, abort_flag, args.status)) {
+            ok = false;
+            break;
+          }
+        }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          int kbr = kb;
+          if constexpr (SHARDED == 2 && B_MN) {  // the k-loop starts on this rank's own slice
+            kbr += shards->rot_tile;
+            if (kbr >= num_kb) kbr -= num_kb;
+            const int kr = kbr * BK;
+            b_staged = kr >= shards->rows_total || shards->owner_of(kr) != shards->me;
+            if (b_staged && kr < shards->rows_total &&
+                !stage_wait(shards, kbr, all_ready, abort_flag, args.status)) {
+              ok = false;
+              break;
+            }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, args.status,
                          ST_TIMEOUT_SMEM_EMPTY)) {
             ok = false;
@@ -567,7 +721,7 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
           uint8_t* sB = sA + P_TILE_BYTES;
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * P_STAGE_BYTES);
           const uint32_t bar = lead_full0 + stage * 8;
-          const int k0 = kb * BK;
+          const int k0 = kbr * BK;
           if constexpr (!A_MN) {
             tma_load_2d_pair(sA, &tmA, bar, k0, m0);  // box {64 k, 128 m}
           } else {
@@ -575,7 +729,21 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
             for (int c = 0; c < 2; ++c)
               tma_load_2d_pair(sA + c * CHUNK_BYTES, &tmA, bar, m0 + c * 64, k0);
           }
-          if constexpr (SHARDED) {
+          if constexpr (SHARDED == 2) {
+            // slices are cut on whole chunks here: the local slice is read in place, the rest from staging
+            const int me = shards->me;
+            if constexpr (!B_MN) {
+              if (b_staged) tma_load_2d_pair(sB, &shards->map_stage, bar, k0, nb0);
+              else tma_load_2d_pair(sB, &shards->map_big[me], bar, k0, nb0 - shards->start[me]);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                if (b_staged) tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_stage, bar, nb0 + c * 64, k0);
+                else tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_big[me], bar, nb0 + c * 64,
+                                      k0 - shards->start[me]);
+              }
+            }
+          } else if constexpr (SHARDED == 1) {
             if constexpr (!B_MN) {
               // weight rows = output columns.  One {64 k, 128 n} box when the 128 rows belong to one rank,
               // else 4 boxes {64 k, 32 n}, each from the rank owning those rows
@@ -690,6 +858,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
         }
       }
     }
+  } else if (warp >= GEMM_THREADS / 32) {
+    // ------------------------------ copier warps (staged variant only) -----------------------
+    if constexpr (SHARDED == 2) stage_copy_loop(shards, lane);
   } else {
     // ------------------------------ epilogue (warps 2..5 of both CTAs) -----------------------
     const int quad = warp & 3;
@@ -700,6 +871,10 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
     for (; ok && w.next(); ++it) {
       int mi, ni;
       tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      if constexpr (SHARDED == 2 && !B_MN) {
+        ni += shards->rot_tile;
+        if (ni >= args.tiles_n) ni -= args.tiles_n;
+      }
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
       if (!mbar_wait(&tfull_bar[buf], use & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) {
@@ -735,7 +910,7 @@ template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const GemmArgs args) {
-  gemm_pair_body<A_MN, B_MN, EPI, false>(tmA, tmB, nullptr, args);
+  gemm_pair_body<A_MN, B_MN, EPI, 0>(tmA, tmB, nullptr, args);
 }
 
 // All-gather fused into the GEMM: B is read shard by shard from the ranks that own it.
@@ -743,7 +918,15 @@ template <bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_gather_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ ShardedB shards,
                         const GemmArgs args) {
-  gemm_pair_body<false, B_MN, EPI, true>(tmA, shards.map[0], &shards, args);
+  gemm_pair_body<false, B_MN, EPI, 1>(tmA, shards.map[0], &shards, args);
+}
+
+// The same with every remote slice brought over the link once (see ShardedB).
+template <bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER_THREADS, 1)
+gemm_bf16_gather_staged_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ ShardedB shards,
+                               const GemmArgs args) {
+  gemm_pair_body<false, B_MN, EPI, 2>(tmA, shards.map[0], &shards, args);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -794,17 +977,18 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, Gemm
   return (int)cudaGetLastError();
 }
 
-template <bool B_MN, int EPI>
-static int launch_gemm_gather(const CUtensorMap& tmA, const ShardedB& shards, GemmArgs args, int sm_count,
-                              cudaStream_t stream) {
-  auto kern = gemm_bf16_gather_kernel<B_MN, EPI>;
+template <bool B_MN, int EPI, bool STAGED>
+static int launch_gemm_gather_impl(const CUtensorMap& tmA, const ShardedB& shards, GemmArgs args, int sm_count,
+                                   cudaStream_t stream) {
+  auto kern = STAGED ? gemm_bf16_gather_staged_kernel<B_MN, EPI> : gemm_bf16_gather_kernel<B_MN, EPI>;
+  constexpr int threads = STAGED ? GATHER_THREADS : GEMM_THREADS;
   static int max_pairs = 0;
   if (max_pairs == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((sm_count / 2) * 2);
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(threads);
     cfg.dynamicSmemBytes = P_SMEM;
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
@@ -817,8 +1001,20 @@ static int launch_gemm_gather(const CUtensorMap& tmA, const ShardedB& shards, Ge
   args.tiles_m = (args.M + P_BM - 1) / P_BM;
   const int tiles = args.tiles_m * args.tiles_n;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, GEMM_THREADS, P_SMEM, stream>>>(tmA, shards, args);
+  if (STAGED) {
+    const int nchunks = (shards.rows_total + shards.chunk_rows - 1) / shards.chunk_rows;
+    cudaError_t e = cudaMemsetAsync(shards.flags, 0, sizeof(int) * (2 + nchunks), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  kern<<<2 * pairs, threads, P_SMEM, stream>>>(tmA, shards, args);
   return (int)cudaGetLastError();
+}
+
+template <bool B_MN, int EPI>
+static int launch_gemm_gather(const CUtensorMap& tmA, const ShardedB& shards, const GemmArgs& args, int sm_count,
+                              cudaStream_t stream) {
+  return shards.stage ? launch_gemm_gather_impl<B_MN, EPI, true>(tmA, shards, args, sm_count, stream)
+                      : launch_gemm_gather_impl<B_MN, EPI, false>(tmA, shards, args, sm_count, stream);
 }
 
 static int g_sm_count = 0;
@@ -930,12 +1126,16 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
 // W [K, N] split by rows), where rank r holds rows [row_starts[r], row_starts[r+1]) of W at B_shards[r] (this rank's
 // memory or a peer's) with row pitch ldb; every start is a multiple of 32.  row_starts == nullptr: equal slices
 // of rows_per_shard rows.  Slices cut on multiples of 128 rows (64 for b_mn = 1) are fetched with whole-tile boxes
-// only.  The gather of W is part of the GEMM's TMA pipeline; nothing is staged.
+// only.  stage == nullptr: every B box is fetched from its owner each time it is used, nothing is staged.
+// stage != nullptr (a [rows of W, ldb] bf16 matrix of this rank) with flags (2 + rows / 64 ints) and my_rank: the
+// remote slices are copied into `stage` once, inside the same kernel, while the tiles on my_rank's own slice run;
+// needs every slice cut on multiples of 128 rows (64 for b_mn = 1).  Launches that share `stage` and `flags` must
+// be ordered on one stream.
 extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards, int n_shards,
                                       int rows_per_shard, const int* row_starts, void* C, int M, int N, int K,
                                       long long lda, long long ldb, long long ldc, int b_mn, int epi, void* C2,
-                                      long long ldc2, const void* R, long long ldr, float alpha, int* status,
-                                      void* stream_) {
+                                      long long ldc2, const void* R, long long ldr, float alpha, int my_rank,
+                                      void* stage, int* flags, int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (n_shards < 1 || n_shards > MAX_SHARDS) return -110;
@@ -971,6 +1171,41 @@ extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards
   for (int r = n_shards; r < MAX_SHARDS; ++r) {
     sh.map[r] = sh.map[0];
     sh.map_big[r] = sh.map_big[0];
+  }
+  for (int r = 0; r < MAX_SHARDS; ++r) sh.ptr[r] = B_shards[r < n_shards ? r : 0];
+  sh.map_stage = sh.map_big[0];
+  sh.stage = nullptr;
+  sh.flags = flags;
+  sh.pitch_bytes = ldb * 2;
+  sh.row_bytes = (b_mn ? N : K) * 2;
+  sh.rows_total = b_mn ? K : N;
+  sh.me = my_rank;
+  sh.chunk_rows = (int)big_rows;
+  sh.rot_tile = 0;
+  sh.rot_row = 0;
+  if (stage != nullptr) {
+    if (flags == nullptr || my_rank < 0 || my_rank >= n_shards || !sh.use_big) return -112;
+    if ((sh.row_bytes % 16) != 0 || (sh.pitch_bytes % 16) != 0 || (reinterpret_cast<uintptr_t>(stage) % 16) != 0)
+      return -112;
+    for (int r = 0; r < n_shards; ++r) {
+      if ((sh.start[r] % (int)big_rows) != 0) return -112;
+      if ((reinterpret_cast<uintptr_t>(B_shards[r]) % 16) != 0) return -112;
+    }
+    if (sh.start[n_shards] != sh.rows_total) return -112;
+    sh.stage = stage;
+    const uint64_t inner = b_mn ? (uint64_t)N : (uint64_t)K;
+    if (encode_tmap_2d(&sh.map_stage, stage, inner, (uint64_t)sh.rows_total, (uint64_t)ldb, 64, big_rows, 2))
+      return -102;
+    if (!b_mn) {
+      // first whole tile of the local slice; a tile that straddles the slice's start goes last, with the
+      // neighbour's rows that are copied last
+      const int tiles_n = (N + BN - 1) / BN;
+      sh.rot_tile = ((sh.start[my_rank] + BN - 1) / BN) % tiles_n;
+      sh.rot_row = sh.rot_tile * BN >= sh.rows_total ? 0 : sh.rot_tile * BN;
+    } else {
+      sh.rot_tile = sh.start[my_rank] / BK;
+      sh.rot_row = sh.start[my_rank];
+    }
   }
   GemmArgs args;
   args.M = M; args.N = N; args.K = K;

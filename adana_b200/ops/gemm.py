@@ -30,9 +30,11 @@ class ShardedWeight:
     """A weight matrix [N, K] (bf16) that is NOT held in one piece: rank r holds rows [row_starts[r], row_starts[r+1])
     at address `ptrs[r]` (its own memory or a peer's).  `linear_fwd`, `linear_gelu_fwd`, `linear_resid_fwd`,
     `linear_dgrad` and `linear_dgrad_dgelu` accept it in place of a tensor and run the gathering GEMM, which fetches
-    every B tile from its owner.  `local` optionally keeps this process's tensors alive (and serves the CPU path)."""
+    every B tile from its owner.  `local` optionally keeps this process's tensors alive (and serves the CPU path).
+    `me` names the slice that lives in this process's own memory: with it the GEMM brings the other slices over the
+    link once into a staging matrix (inside the same kernel) instead of re-fetching them per row tile."""
 
-    def __init__(self, ptrs, row_starts, N: int, K: int, local=None):
+    def __init__(self, ptrs, row_starts, N: int, K: int, local=None, me=None):
         import ctypes
 
         vals = [int(p.data_ptr()) if torch.is_tensor(p) else int(p) for p in ptrs]
@@ -41,6 +43,7 @@ class ShardedWeight:
         assert len(self.row_starts) == len(vals) + 1 and self.row_starts[0] == 0 and self.row_starts[-1] == N
         self.shape = (N, K)
         self.local = local
+        self.me = me
 
     def full(self) -> torch.Tensor:
         """The gathered matrix, from the local tensors (single-process use and CPU reference path)."""
@@ -86,7 +89,7 @@ def linear_fwd(x, w, out=None):
     if isinstance(w, ShardedWeight):
         if not (x.is_cuda and _lib.available()):
             return linear_fwd(x, w.full(), out)
-        return gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], out=out, row_starts=w.row_starts)
+        return gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], out=out, row_starts=w.row_starts, me=w.me)
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w):
@@ -118,7 +121,7 @@ def linear_gelu_fwd(x, w):
             return linear_gelu_fwd(x, w.full())
         z = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
         h = torch.empty_like(z)
-        gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=w.row_starts)
+        gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=w.row_starts, me=w.me)
         return z, h
     M, K = x.shape
     N = w.shape[0]
@@ -139,7 +142,7 @@ def linear_resid_fwd(x, w, resid, alpha=1.0, out=None):
         if out is None:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
         return gather_gemm(x, w.ptrs, None, w.shape[0], ldb=w.shape[1], epi=EPI_RESID_F32, out=out, R=resid, alpha=alpha,
-                           row_starts=w.row_starts)
+                           row_starts=w.row_starts, me=w.me)
     M, K = x.shape
     N = w.shape[0]
     if not use_cuda(x, w, resid):
@@ -173,7 +176,7 @@ def linear_dgrad(dy, w, out=None, alpha=1.0):
         if not (dy.is_cuda and _lib.available()):
             return linear_dgrad(dy, w.full(), out, alpha)
         return gather_gemm(dy, w.ptrs, None, w.shape[1], ldb=w.shape[1], b_mn=True, out=out, alpha=alpha,
-                           row_starts=w.row_starts)
+                           row_starts=w.row_starts, me=w.me)
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w):
@@ -210,7 +213,7 @@ def linear_dgrad_dgelu(dy, w, z, alpha=1.0):
             return linear_dgrad_dgelu(dy, w.full(), z, alpha)
         out = torch.empty((dy.shape[0], w.shape[1]), dtype=torch.bfloat16, device=dy.device)
         return gather_gemm(dy, w.ptrs, None, w.shape[1], ldb=w.shape[1], b_mn=True, epi=EPI_DGELU, out=out, R=z, alpha=alpha,
-                           row_starts=w.row_starts)
+                           row_starts=w.row_starts, me=w.me)
     M, N = dy.shape
     K = w.shape[1]
     if not use_cuda(dy, w, z):
@@ -284,11 +287,29 @@ def tile_aligned_row_starts(n_rows: int, world: int, tile: int = 128):
     return starts
 
 
+_stage_ws = {}
+STAGE_MIN_ROWS = 512     # below this the remote tiles are used by at most two row tiles: fetch them directly
+
+
+def _stage_workspace(device, nbytes: int):
+    """(staging bytes, flag words) of `device`, grown on demand and shared by every staged gather GEMM there: such
+    launches must therefore be ordered on one stream, which the engine's compute stream does."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _stage_ws.get(key)
+    if ws is None or ws[0].numel() < nbytes:
+        ws = (torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device),
+              torch.zeros(4096, dtype=torch.int32, device=device))
+        _stage_ws[key] = ws
+    return ws
+
+
 def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, out=None, C2=None, R=None, alpha=1.0,
-                out_dtype=torch.bfloat16, row_starts=None):
+                out_dtype=torch.bfloat16, row_starts=None, me=None, staged=None):
     """C[M,N] = epi(x · Wᵀ) (b_mn False, W [N,K] row-sharded) or epi(x · W) (b_mn True, W [K,N] row-sharded).
     `row_starts` (world + 1 offsets, multiples of 32) gives uneven slices; otherwise every slice has
-    `rows_per_shard` rows."""
+    `rows_per_shard` rows.  `me`: the slice in this process's own memory.  `staged` (default: whenever `me` is
+    given, the slices are cut on whole tiles and x has at least STAGE_MIN_ROWS rows) copies the other slices once
+    into a local staging matrix inside the kernel; otherwise every tile is fetched from its owner on each use."""
     import ctypes
 
     _check2d(x, "x")
@@ -297,30 +318,46 @@ def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, 
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     starts = None if row_starts is None else (ctypes.c_int * (n + 1))(*[int(v) for v in row_starts])
+    w_rows = K if b_mn else N
+    cut = 64 if b_mn else 128
+    bounds = list(row_starts) if row_starts is not None else [r * rows_per_shard for r in range(n + 1)]
+    can_stage = me is not None and all(v % cut == 0 for v in bounds[:-1]) and bounds[-1] == w_rows and w_rows // cut < 4000
+    if staged is None:
+        staged = can_stage and M >= STAGE_MIN_ROWS and n > 1
+    elif staged and not can_stage:
+        raise ValueError("staged gather needs `me` and slices cut on multiples of %d rows" % cut)
+    stage_ptr = flags_ptr = None
+    if staged:
+        stage, flags = _stage_workspace(x.device, w_rows * int(ldb) * 2)
+        stage_ptr, flags_ptr = stage.data_ptr(), flags.data_ptr()
     rc = _lib.lib().adana_gemm_bf16_gather(
         x.data_ptr(), arr, n, int(rows_per_shard or 0), starts, out.data_ptr(), M, N, K, x.stride(0), int(ldb),
         out.stride(0), int(b_mn), int(epi), _lib.ptr(C2), 0 if C2 is None else C2.stride(0), _lib.ptr(R),
-        0 if R is None else R.stride(0), float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+        0 if R is None else R.stride(0), float(alpha), int(me or 0), stage_ptr, flags_ptr,
+        _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "adana_gemm_bf16_gather")
     return out
 
 
-def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None):
+def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None, me=None, staged=None):
     """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows over the shards (equal slices or `row_starts`)."""
     _, n = _ptr_array(w_shards)
     N = row_starts[-1] if row_starts is not None else n * rows_per_shard
-    return gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], out=out, row_starts=row_starts)
+    return gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], out=out, row_starts=row_starts, me=me,
+                       staged=staged)
 
 
-def linear_gelu_fwd_gathered(x, w_shards, rows_per_shard=None, row_starts=None):
+def linear_gelu_fwd_gathered(x, w_shards, rows_per_shard=None, row_starts=None, me=None, staged=None):
     _, n = _ptr_array(w_shards)
     N = row_starts[-1] if row_starts is not None else n * rows_per_shard
     z = torch.empty((x.shape[0], N), dtype=torch.bfloat16, device=x.device)
     h = torch.empty_like(z)
-    gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=row_starts)
+    gather_gemm(x, w_shards, rows_per_shard, N, ldb=x.shape[1], epi=EPI_GELU_DUAL, out=z, C2=h, row_starts=row_starts,
+                me=me, staged=staged)
     return z, h
 
 
-def linear_dgrad_gathered(dy, w_shards, rows_per_shard, K_out, out=None, row_starts=None):
+def linear_dgrad_gathered(dy, w_shards, rows_per_shard, K_out, out=None, row_starts=None, me=None, staged=None):
     """dx [M, K_out] = dy [M, N] · W with W [N, K_out] split by rows (the contraction index is sharded)."""
-    return gather_gemm(dy, w_shards, rows_per_shard, K_out, ldb=K_out, b_mn=True, out=out, row_starts=row_starts)
+    return gather_gemm(dy, w_shards, rows_per_shard, K_out, ldb=K_out, b_mn=True, out=out, row_starts=row_starts,
+                       me=me, staged=staged)

@@ -352,17 +352,17 @@ class Engine:
         """Replace the four block matrices of `W` by `ShardedWeight`s."""
         from ..ops.gemm import ShardedWeight, tile_aligned_row_starts
 
-        for key, _ in self._MATS:
+        for idx, (key, _) in enumerate(self._MATS):
             if u.weights is None:      # true row slices, one per rank, addressed through peer pointers
                 buf, starts, off, rows, cols, ptrs = u.slices[key]
-                W[key] = ShardedWeight(list(ptrs), starts, rows, cols, local=None)
+                W[key] = ShardedWeight(list(ptrs), starts, rows, cols, local=None, me=self.rank)
             else:                      # one process: up to 8 virtual slices that are views of the resident matrix
                 w = W[key]
                 rows, cols = w.shape
                 k = max(1, min(8, rows // 128))
                 starts = tile_aligned_row_starts(rows, k)
                 views = [w[a:b] for a, b in zip(starts, starts[1:])]
-                W[key] = ShardedWeight(views, starts, rows, cols, local=views)
+                W[key] = ShardedWeight(views, starts, rows, cols, local=views, me=idx % k)
 
     def _rebind_module_params(self):
         """Point the module's parameters at the engine's storage (or release them when sharded)."""

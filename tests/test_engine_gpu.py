@@ -116,17 +116,23 @@ def test_gathered_weights_match_resident_weights_on_one_gpu():
             idx = torch.randint(0, a.vocab_size, (4, a.sequence_length), generator=g).cuda()
             out = m(idx, targets=idx.roll(-1, 1))
             out["loss"].backward()
+            if step == 0:
+                grads0 = {k: v.float().clone() for k, v in eng.full_param_dict("grad").items()}
             eng.grad_norm_and_clip(0.5)
             opt.step()
             opt.zero_grad()
             losses.append(out["loss"].item())
-        return losses, eng.full_param_dict("master")
+        return losses, eng.full_param_dict("master"), grads0
 
-    la, pa = run("resident")
-    lb, pb = run("gathered")
+    la, pa, ga = run("resident")
+    lb, pb, gb = run("gathered")
+    # the first backward, before any optimizer step: the same gradients up to bf16 rounding of the dgrads, whose
+    # k-loop starts on another slice
+    for k in ga:
+        assert ((ga[k] - gb[k]).norm() / (ga[k].norm() + 1e-12)).item() < 1e-2, k
     for x, y in zip(la, lb):
         assert abs(x - y) < 2e-3, (la, lb)
     for k in pa:
         d = (pa[k] - pb[k]).abs()
         # sign-like updates: a different bf16 rounding of one gradient element may flip a step of size ~lr
-        assert d.mean().item() < 1e-4 and d.max().item() < 2e-2, (k, d.mean().item(), d.max().item())
+        assert d.mean().item() < 1.5e-3 and d.max().item() < 3e-2, (k, d.mean().item(), d.max().item())

@@ -84,7 +84,7 @@ def _gather_gemm_worker(rank, world):
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     M, K, rps = 2048, 1024, 352
     N = world * rps
-    plane = P2PPlane.create(rps * K * 2 + (1 << 16), torch.device("cuda", rank))
+    plane = P2PPlane.create((rps + 384) * K * 2 + (1 << 16), torch.device("cuda", rank))
     torch.manual_seed(5)
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()                 # same on every rank
     x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -96,6 +96,18 @@ def _gather_gemm_worker(rank, world):
     ptrs = plane.peer_ptrs(mine)
     y = gemm.linear_fwd_gathered(x, ptrs, rps)
     dx = gemm.linear_dgrad_gathered(dy, ptrs, rps, K)
+    # staged variant: slices cut on whole tiles; the remote slices cross the link once into a local staging matrix
+    rps2 = 384
+    N2 = world * rps2
+    w2 = (torch.randn(N2, K, device="cuda") * 0.5).bfloat16()
+    dy2 = (torch.randn(M, N2, device="cuda") * 0.5).bfloat16()
+    mine2 = plane.alloc(rps2 * K, torch.bfloat16).view(rps2, K)
+    mine2.copy_(w2[rank * rps2:(rank + 1) * rps2])
+    torch.cuda.synchronize()
+    plane.barrier()
+    ptrs2 = plane.peer_ptrs(mine2)
+    ys = [gemm.linear_fwd_gathered(x, ptrs2, rps2, me=rank, staged=True) for _ in range(3)]
+    dxs = gemm.linear_dgrad_gathered(dy2, ptrs2, rps2, K, me=rank, staged=True)
     torch.cuda.synchronize()
     plane.barrier()                                                          # nobody frees a shard still being read
     torch.cuda.synchronize()
@@ -103,7 +115,12 @@ def _gather_gemm_worker(rank, world):
     ref_y, ref_dx = x.float() @ w.float().t(), dy.float() @ w.float()
     err_y = ((y.float() - ref_y).norm() / ref_y.norm()).item()
     err_dx = ((dx.float() - ref_dx).norm() / ref_dx.norm()).item()
-    return {"err_y": err_y, "err_dx": err_dx}
+    old = gemm.set_mode(3)
+    same_bits = all(torch.equal(v, gemm.linear_fwd(x, w2)) for v in ys)
+    gemm.set_mode(old)
+    ref_dx2 = dy2.float() @ w2.float()
+    err_dxs = ((dxs.float() - ref_dx2).norm() / ref_dx2.norm()).item()
+    return {"err_y": err_y, "err_dx": err_dx, "staged_same_bits": same_bits, "err_dx_staged": err_dxs}
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
@@ -114,6 +131,7 @@ def test_gather_gemm_over_nvlink_peers():
     res = _spawn(_gather_gemm_worker, world)
     for r in range(world):
         assert res[r]["err_y"] < 8e-3 and res[r]["err_dx"] < 8e-3, res[r]
+        assert res[r]["staged_same_bits"] and res[r]["err_dx_staged"] < 8e-3, res[r]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
