@@ -169,7 +169,12 @@ def main(args, parser):
         scheduler = CombinedScheduler(opt, args) if args.opt == "muon" else build_scheduler(args, opt)
 
     if args.resume_from is None:
-        if checkpoint_exists(exp_dir / "ckpts" / "latest"):
+        # rank 0 looks and tells the others: a slower rank that looked for itself could find the checkpoint that
+        # rank 0 has meanwhile begun to write at iteration 0
+        found = [checkpoint_exists(exp_dir / "ckpts" / "latest")]
+        if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+            torch.distributed.broadcast_object_list(found, src=0)
+        if found[0]:
             if not args.auto_resume:
                 raise ValueError(f"The experiment dir {exp_dir} already exists. To resume training, set "
                                  "auto_resume=True. Otherwise, specify a different experiment name. ")
