@@ -116,8 +116,10 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
   }
 }
 
+// Registers decide how many rows an SM has in flight: only dy, x and the old dx of the row are held across the
+// reduction (g and xhat are recomputed after it), which fits three CTAs of 256 threads per SM for cols <= 3072.
 template <typename TDY, typename TX, int KIND, int NORM_MAXV>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, NORM_MAXV <= 3 ? 3 : 1)
 norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                 float* __restrict__ dx, int accumulate_dx, float* __restrict__ dw_partial, int rows,
@@ -142,7 +144,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     const TDY* dyr = dy + (size_t)row * cols;
     const TX* xr = x + (size_t)row * cols;
     float* dxr = dx + (size_t)row * cols;
-    float4 g[NORM_MAXV], xh[NORM_MAXV], prev[NORM_MAXV];
+    float4 prev[NORM_MAXV];
     // every load of the row is issued before anything waits on one of them
     float4 dv[NORM_MAXV], xv[NORM_MAXV];
 #pragma unroll
@@ -160,15 +162,15 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nv) {
         const float4 d = dv[i];
-        xh[i] = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
-                            (xv[i].w - mean) * rstd);
-        dwacc[i].x += d.x * xh[i].x;
-        dwacc[i].y += d.y * xh[i].y;
-        dwacc[i].z += d.z * xh[i].z;
-        dwacc[i].w += d.w * xh[i].w;
-        g[i] = make_float4(d.x * wreg[i].x, d.y * wreg[i].y, d.z * wreg[i].z, d.w * wreg[i].w);
-        s1 += g[i].x + g[i].y + g[i].z + g[i].w;
-        s2 += g[i].x * xh[i].x + g[i].y * xh[i].y + g[i].z * xh[i].z + g[i].w * xh[i].w;
+        const float4 xh = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
+                                      (xv[i].w - mean) * rstd);
+        dwacc[i].x += d.x * xh.x;
+        dwacc[i].y += d.y * xh.y;
+        dwacc[i].z += d.z * xh.z;
+        dwacc[i].w += d.w * xh.w;
+        const float4 g = make_float4(d.x * wreg[i].x, d.y * wreg[i].y, d.z * wreg[i].z, d.w * wreg[i].w);
+        s1 += g.x + g.y + g.z + g.w;
+        s2 += g.x * xh.x + g.y * xh.y + g.z * xh.z + g.w * xh.w;
       }
     }
     s1 = warp_sum(s1);
@@ -188,11 +190,14 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     for (int i = 0; i < NORM_MAXV; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nv) {
+        const float4 d = dv[i];
+        const float4 xh = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
+                                      (xv[i].w - mean) * rstd);
         float4 o;
-        o.x = rstd * (g[i].x - m1 - xh[i].x * m2);
-        o.y = rstd * (g[i].y - m1 - xh[i].y * m2);
-        o.z = rstd * (g[i].z - m1 - xh[i].z * m2);
-        o.w = rstd * (g[i].w - m1 - xh[i].w * m2);
+        o.x = rstd * (d.x * wreg[i].x - m1 - xh.x * m2);
+        o.y = rstd * (d.y * wreg[i].y - m1 - xh.y * m2);
+        o.z = rstd * (d.z * wreg[i].z - m1 - xh.z * m2);
+        o.w = rstd * (d.w * wreg[i].w - m1 - xh.w * m2);
         if (accumulate_dx) {
           o.x += prev[i].x; o.y += prev[i].y; o.z += prev[i].z; o.w += prev[i].w;
         }
@@ -211,13 +216,26 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
   }
 }
 
-__global__ void colsum_kernel(const float* __restrict__ partial, int n_rows, int cols,
-                              float* __restrict__ out, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// out[c] (+)= sum over rows of partial[r][c], in a fixed order (deterministic).  A 32 x 16 CTA owns 32 columns:
+// thread (x, y) adds rows y, y + 16, ... of column x, the 16 sums are folded through shared memory.
+constexpr int CS_TX = 32, CS_TY = 16;
+__global__ void __launch_bounds__(CS_TX * CS_TY)
+colsum_kernel(const float* __restrict__ partial, int n_rows, int cols, float* __restrict__ out, int accumulate) {
+  __shared__ float red[CS_TY][CS_TX + 1];
+  const int c = blockIdx.x * CS_TX + threadIdx.x;
   float s = 0.f;
-  for (int r = 0; r < n_rows; ++r) s += partial[(size_t)r * cols + c];
-  out[c] = accumulate ? out[c] + s : s;
+  if (c < cols) {
+#pragma unroll 4
+    for (int r = threadIdx.y; r < n_rows; r += CS_TY) s += partial[(size_t)r * cols + c];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < CS_TY; ++j) t += red[j][threadIdx.x];
+    out[c] = accumulate ? out[c] + t : t;
+  }
 }
 
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
@@ -336,7 +354,8 @@ extern "C" int adana_norm_bwd(const void* dy, int dy_is_bf16, const void* x, int
 extern "C" int adana_colsum_f32(const float* partial, int n_partial_rows, int cols, float* out,
                                 int accumulate, void* stream_) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  colsum_kernel<<<(cols + 127) / 128, 128, 0, st>>>(partial, n_partial_rows, cols, out, accumulate);
+  if (cols <= 0) return 0;
+  colsum_kernel<<<(cols + CS_TX - 1) / CS_TX, dim3(CS_TX, CS_TY), 0, st>>>(partial, n_partial_rows, cols, out, accumulate);
   return (int)cudaGetLastError();
 }
 

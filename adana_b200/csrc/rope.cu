@@ -23,7 +23,7 @@ namespace adana {
 
 constexpr int ROPE_THREADS = 256;
 constexpr int ROPE_EPL = 8;     // elements per lane: one 16-byte load of bf16
-constexpr int ROPE_UNROLL = 2;  // vectors in flight per lane group: hides load latency
+constexpr int ROPE_UNROLL = 3;  // vectors in flight per lane group: hides load latency (12 heads of 64 per pass)
 
 // A (token, head) vector of HD elements is owned by LPV = HD/8 neighbouring lanes (8 for head_dim
 // 64, 16 for 128), so a warp works on 32/LPV vectors at a time, every global access is 16 bytes per
@@ -54,29 +54,21 @@ __device__ __forceinline__ void load8f(const float* p, float (&x)[8]) {
   x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
 
-// Which vector a lane group works on, and where it lives.
-struct RopeItem {
-  long long src_off;  // element offset of this lane's 8 values inside the projection output
-  long long out_off;  // element offset inside q_out / k_out ([token, head, hd])
-  int pos;
+// Work is dealt by token: a warp takes a token, loads the token's (cos, sin) row once, and walks over the token's
+// q and k heads VPW * ROPE_UNROLL at a time, so the inner loop has no division and one angle load per token.
+struct RopeHead {
+  int src;   // element offset of the head inside the token's projection row
+  int hh;    // head index inside q or k
   bool isq, ok;
 };
-
-template <int HD>
-__device__ __forceinline__ RopeItem rope_item(long long item, long long total, int Hq, int Hk, int S,
-                                              long long row_stride, int q_off, int q_hstride, int k_off,
-                                              int k_hstride, int sub) {
-  RopeItem r;
-  r.ok = item < total;
-  const long long it = r.ok ? item : 0;
-  const int Hall = Hq + Hk;
-  const long long tok = it / Hall;
-  const int h = (int)(it - tok * Hall);
-  r.isq = h < Hq;
-  const int hh = r.isq ? h : h - Hq;
-  r.src_off = tok * row_stride + (r.isq ? q_off + hh * q_hstride : k_off + hh * k_hstride) + sub * ROPE_EPL;
-  r.out_off = (tok * (r.isq ? Hq : Hk) + hh) * HD + sub * ROPE_EPL;
-  r.pos = (int)(tok % S);
+__device__ __forceinline__ RopeHead rope_head(int h, int Hq, int Hall, int q_off, int q_hstride, int k_off,
+                                              int k_hstride) {
+  RopeHead r;
+  r.ok = h < Hall;
+  const int hc = r.ok ? h : 0;
+  r.isq = hc < Hq;
+  r.hh = r.isq ? hc : hc - Hq;
+  r.src = r.isq ? q_off + r.hh * q_hstride : k_off + r.hh * k_hstride;
   return r;
 }
 
@@ -94,47 +86,52 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
   const int sub = lane % LPV, grp = lane / LPV;
   const long long warp_global = ((long long)blockIdx.x * ROPE_THREADS + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
-  const long long total = n_tokens * (Hq + Hk);
   float wqr[8], wkr[8];
   if (KIND != 2) {
     load8f(wq + sub * ROPE_EPL, wqr);
     load8f(wk + sub * ROPE_EPL, wkr);
   }
-  for (long long base = warp_global * (VPW * U); base < total; base += n_warps * (VPW * U)) {
-    float x[U][8], cs[U][8];
-    RopeItem it[U];
+  const int Hall = Hq + Hk;
+  for (long long tok = warp_global; tok < n_tokens; tok += n_warps) {
+    float cs[8];  // 4 (cos, sin) pairs of this lane's columns at the token's position
+    load8f(freqs + (long long)(tok % S) * HD + sub * ROPE_EPL, cs);
+    const __nv_bfloat16* row = qkv + tok * row_stride + sub * ROPE_EPL;
+    __nv_bfloat16* qo = q_out + tok * Hq * HD + sub * ROPE_EPL;
+    __nv_bfloat16* ko = k_out + tok * Hk * HD + sub * ROPE_EPL;
+    for (int h0 = 0; h0 < Hall; h0 += VPW * U) {
+      float x[U][8];
+      RopeHead it[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      it[u] = rope_item<HD>(base + u * VPW + grp, total, Hq, Hk, S, row_stride, q_off, q_hstride, k_off,
-                            k_hstride, sub);
-      load8(qkv + it[u].src_off, x[u]);
-      load8f(freqs + (long long)it[u].pos * HD + sub * ROPE_EPL, cs[u]);  // 4 (cos, sin) pairs
-    }
+      for (int u = 0; u < U; ++u) {
+        it[u] = rope_head(h0 + u * VPW + grp, Hq, Hall, q_off, q_hstride, k_off, k_hstride);
+        load8(row + it[u].src, x[u]);
+      }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (KIND != 2) {
-        float mean = 0.f;
-        if (KIND == 0) {
-          float s = 0.f;
+      for (int u = 0; u < U; ++u) {
+        if (KIND != 2) {
+          float mean = 0.f;
+          if (KIND == 0) {
+            float s = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) s += x[u][i];
-          mean = group_sum<LPV>(s) * (1.f / HD);
+            for (int i = 0; i < 8; ++i) s += x[u][i];
+            mean = group_sum<LPV>(s) * (1.f / HD);
+          }
+          float q = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
+          const float rstd = rsqrtf(group_sum<LPV>(q) * (1.f / HD) + eps);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[u][i] = (x[u][i] - mean) * rstd * (it[u].isq ? wqr[i] : wkr[i]);
         }
-        float q = 0.f;
+        float o[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q += (x[u][i] - mean) * (x[u][i] - mean);
-        const float rstd = rsqrtf(group_sum<LPV>(q) * (1.f / HD) + eps);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[u][i] = (x[u][i] - mean) * rstd * (it[u].isq ? wqr[i] : wkr[i]);
+        for (int i = 0; i < 4; ++i) {
+          const float c = cs[2 * i], s = cs[2 * i + 1];
+          o[2 * i] = x[u][2 * i] * c - x[u][2 * i + 1] * s;
+          o[2 * i + 1] = x[u][2 * i] * s + x[u][2 * i + 1] * c;
+        }
+        if (it[u].ok) store8((it[u].isq ? qo : ko) + it[u].hh * HD, o);
       }
-      float o[8];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float c = cs[u][2 * i], s = cs[u][2 * i + 1];
-        o[2 * i] = x[u][2 * i] * c - x[u][2 * i + 1] * s;
-        o[2 * i + 1] = x[u][2 * i] * s + x[u][2 * i + 1] * c;
-      }
-      if (it[u].ok) store8((it[u].isq ? q_out : k_out) + it[u].out_off, o);
     }
   }
 }
@@ -147,7 +144,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
                        const float* __restrict__ wk, const float* __restrict__ freqs,
                        __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dwq_partial,
                        float* __restrict__ dwk_partial, long long n_tokens, int S, int Hq, int Hk,
-                       float eps) {
+                       float eps, long long active_warps) {
   constexpr int LPV = HD / ROPE_EPL;
   constexpr int VPW = 32 / LPV;
   constexpr int U = ROPE_UNROLL;
@@ -156,8 +153,6 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
   const int warp = threadIdx.x >> 5;
   const int sub = lane % LPV, grp = lane / LPV;
   const long long warp_global = ((long long)blockIdx.x * ROPE_THREADS + threadIdx.x) >> 5;
-  const long long n_warps = ((long long)gridDim.x * ROPE_THREADS) >> 5;
-  const long long total = n_tokens * (Hq + Hk);
   float dwq_acc[8], dwk_acc[8], wqr[8], wkr[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) dwq_acc[i] = dwk_acc[i] = 0.f;
@@ -165,16 +160,22 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
     load8f(wq + sub * ROPE_EPL, wqr);
     load8f(wk + sub * ROPE_EPL, wkr);
   }
-  for (long long base = warp_global * (VPW * U); base < total; base += n_warps * (VPW * U)) {
-    float x[U][8], d[U][8], cs[U][8];
-    RopeItem it[U];
+  const int Hall = Hq + Hk;
+  // warps beyond active_warps take no token (their partial rows are zero): the others get equal shares
+  for (long long tok = warp_global < active_warps ? warp_global : n_tokens; tok < n_tokens; tok += active_warps) {
+    float cs[8];
+    load8f(freqs + (long long)(tok % S) * HD + sub * ROPE_EPL, cs);
+    const long long row = tok * row_stride + sub * ROPE_EPL;
+    const __nv_bfloat16* dqo = dq + tok * Hq * HD + sub * ROPE_EPL;
+    const __nv_bfloat16* dko = dk + tok * Hk * HD + sub * ROPE_EPL;
+    for (int h0 = 0; h0 < Hall; h0 += VPW * U) {
+    float x[U][8], d[U][8];
+    RopeHead it[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      it[u] = rope_item<HD>(base + u * VPW + grp, total, Hq, Hk, S, row_stride, q_off, q_hstride, k_off,
-                            k_hstride, sub);
-      load8(qkv + it[u].src_off, x[u]);
-      load8((it[u].isq ? dq : dk) + it[u].out_off, d[u]);
-      load8f(freqs + (long long)it[u].pos * HD + sub * ROPE_EPL, cs[u]);
+      it[u] = rope_head(h0 + u * VPW + grp, Hq, Hall, q_off, q_hstride, k_off, k_hstride);
+      load8(qkv + row + it[u].src, x[u]);
+      load8((it[u].isq ? dqo : dko) + it[u].hh * HD, d[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -182,7 +183,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
       float dn[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float c = cs[u][2 * i], s = cs[u][2 * i + 1];
+        const float c = cs[2 * i], s = cs[2 * i + 1];
         dn[2 * i] = d[u][2 * i] * c + d[u][2 * i + 1] * s;
         dn[2 * i + 1] = -d[u][2 * i] * s + d[u][2 * i + 1] * c;
       }
@@ -218,7 +219,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
 #pragma unroll
         for (int i = 0; i < 8; ++i) dx[i] = rstd * (g[i] - m1 - xh[i] * m2);
       }
-      if (it[u].ok) store8(dqkv + it[u].src_off, dx);
+      if (it[u].ok) store8(dqkv + row + it[u].src, dx);
+    }
     }
   }
   if (KIND != 2 && dwq_partial) {
@@ -249,6 +251,14 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
   }
 }
 
+// Every warp takes the same number of tokens (the last ones one fewer at most): how many warps that needs when at
+// most max_blocks CTAs may run.
+static long long rope_active_warps(long long n_tokens, long long max_blocks) {
+  const long long max_warps = max_blocks * (ROPE_THREADS / 32);
+  const long long per_warp = (n_tokens + max_warps - 1) / max_warps;
+  return (n_tokens + per_warp - 1) / per_warp;
+}
+
 }  // namespace adana
 
 using namespace adana;
@@ -262,11 +272,7 @@ extern "C" int adana_qknorm_rope_fwd(const void* qkv, long long row_stride, int 
   if (n_tokens <= 0) return 0;
   if (hd != 64 && hd != 128) return -1;
   if ((row_stride & 7) || (q_off & 7) || (k_off & 7) || (q_hstride & 7) || (k_hstride & 7)) return -2;  // 16-byte lanes
-  const long long items = n_tokens * (Hq + Hk);
-  const int per_block = (ROPE_THREADS / 32) * (32 / (hd / ROPE_EPL)) * ROPE_UNROLL;
-  long long blocks = (items + per_block - 1) / per_block;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  if (blocks < 1) blocks = 1;
+  const long long blocks = (rope_active_warps(n_tokens, 148 * 8) + ROPE_THREADS / 32 - 1) / (ROPE_THREADS / 32);
 #define RF(HD_, K_)                                                                          \
   qknorm_rope_fwd_kernel<HD_, K_><<<(int)blocks, ROPE_THREADS, 0, st>>>(                     \
       (const __nv_bfloat16*)qkv, row_stride, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, \
@@ -292,11 +298,12 @@ extern "C" int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void*
   if (kind != 2 && n_partial <= 0) return -3;
   if ((row_stride & 7) || (q_off & 7) || (k_off & 7) || (q_hstride & 7) || (k_hstride & 7)) return -2;
   const int blocks = kind != 2 ? n_partial : 148 * 8;
+  const long long active = rope_active_warps(n_tokens, blocks);
 #define RB(HD_, K_)                                                                          \
   qknorm_rope_bwd_kernel<HD_, K_><<<blocks, ROPE_THREADS, 0, st>>>(                          \
       (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv, row_stride, \
       q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, (__nv_bfloat16*)dqkv, dwq_partial,  \
-      dwk_partial, n_tokens, S, Hq, Hk, eps)
+      dwk_partial, n_tokens, S, Hq, Hk, eps, active)
   if (hd == 64) {
     if (kind == 0) RB(64, 0); else if (kind == 1) RB(64, 1); else RB(64, 2);
   } else {

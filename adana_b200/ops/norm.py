@@ -10,7 +10,7 @@ import torch
 from . import _lib
 
 LAYERNORM, RMSNORM = 0, 1
-_PARTIAL_ROWS = 148 * 4
+_PARTIAL_ROWS = 148 * 3   # CTAs of the backward kernel: three of them fit an SM at cols <= 3072
 _MAX_COLS = 8192
 
 

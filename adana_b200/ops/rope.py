@@ -12,7 +12,7 @@ import torch
 from . import _lib
 
 LAYERNORM, RMSNORM, NONORM = 0, 1, 2
-_PARTIAL = 148 * 4
+_PARTIAL = 148 * 2      # CTAs of the backward kernel (two of its 128-register CTAs fit an SM) = partial weight-gradient rows
 
 
 def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0) -> torch.Tensor:
