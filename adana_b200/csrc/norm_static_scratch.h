@@ -13,7 +13,7 @@
 // memory beyond its arguments.
 //
 // Limits.  The scratch holds ADANA_NORM_STATIC_MAX_PARTIAL_ROWS x ADANA_NORM_STATIC_MAX_COLS floats
-// (592 x 4096 x 4 B = 9.25 MiB per device, reserved when the library's module is loaded).  `cols` above
+// (444 x 4096 x 4 B = 6.9 MiB per device, reserved when the library's module is loaded).  `cols` above
 // ADANA_NORM_STATIC_MAX_COLS, or not a multiple of 4, is rejected with ADANA_NORM_STATIC_E_COLS before
 // anything is launched, with a one-line message on stderr; `rows` is unlimited (the grid is capped at the
 // number of partial rows and strides over the rows).
@@ -36,7 +36,7 @@
 extern "C" {
 #endif
 
-#define ADANA_NORM_STATIC_MAX_PARTIAL_ROWS 592
+#define ADANA_NORM_STATIC_MAX_PARTIAL_ROWS 444
 #define ADANA_NORM_STATIC_MAX_COLS 4096
 
 #define ADANA_NORM_STATIC_E_COLS (-21)    // cols > ADANA_NORM_STATIC_MAX_COLS or cols % 4 != 0
