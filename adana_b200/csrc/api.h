@@ -16,6 +16,7 @@ enum {
   EPI_DSWIGLU = 6,    // acc = dH; R = [gate|up]; C = [dGate|dUp]
   EPI_AXPBY_BF16 = 7, // C(bf16) = alpha * acc + beta * R(bf16); C may alias R
   EPI_F32_ATOMIC = 8, // C(f32) += alpha * acc with vector atomics (internal: stream-K partial tiles)
+  EPI_F32_RS = 9,     // rows added into the fp32 buffer of the rank that owns them (adana_gemm_bf16_reduce_scatter)
 };
 
 #ifdef __cplusplus
@@ -24,6 +25,17 @@ extern "C" {
 
 // D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
 // a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
+// GEMM fused with the reduce-scatter that follows a row-parallel linear: this rank holds a K-slice of the operands,
+// A [M, K] and B [N, K] (both K-major), and its partial product alpha * A * B^T is ADDED, tile by tile from the
+// epilogue (`red.global.add.v4.f32`, over NVLink for remote rows), into the buffer of the rank that owns the rows:
+// rank r keeps output rows [r * rows_per_rank, (r + 1) * rows_per_rank) in C_ranks[r] ([rows_per_rank, ldc] fp32).
+// The caller zero-fills (or pre-loads a residual into) its own buffer and synchronises the ranks before the launch,
+// and again before anyone reads: after that second barrier every buffer holds the sum over ranks.  Row tiles are
+// taken starting at the rows of rank my_rank + 1, so the ranks do not all push to the same destination at once.
+int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* C_ranks, int n_ranks, int my_rank,
+                                   int rows_per_rank, int M, int N, int K, long long lda, long long ldb,
+                                   long long ldc, float alpha, int* status, void* stream);
+
 // All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks: rank r holds rows
 // [row_starts[r], row_starts[r+1]) (multiples of 32; nullptr = equal slices of rows_per_shard rows) at B_shards[r]
 // (local or peer memory, row pitch ldb).  b_mn = 0: C[M,N] = epi(A[M,K] * W[N,K]^T); b_mn = 1: C[M,N] = epi(A[M,K] *

@@ -47,6 +47,11 @@ struct GemmArgs {
   int tiles_m, tiles_n, group_m;
   int streamk;  // CTA-pair kernel, fp32 output: 0 whole tiles, 1 every K loop cut, 2 only the last wave's
   int* status;
+  // EPI_F32_RS (GEMM fused with a reduce-scatter over peers): output rows [r * rs_rows, (r + 1) * rs_rows) are
+  // ADDED into rank r's buffer peerC[r] ([rs_rows, ldc] fp32, its own memory or a peer's over NVLink)
+  void* peerC[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int rs_rows = 0;
+  int rot_m = 0;  // row-tile rotation: with it every rank starts on another destination
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& mi,
@@ -176,6 +181,17 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& args, uint32_t tad
         for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
         store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
                            ncols_ok);
+      } else if constexpr (EPI == EPI_F32_RS) {
+        // this rank's partial product of a row that rank `owner` keeps: added in the owner's L2
+        const int owner = row / args.rs_rows;
+        float* cp = reinterpret_cast<float*>(args.peerC[owner]) + (long long)(row - owner * args.rs_rows) * args.ldc + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j * 4 < ncols_ok)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + j * 4),
+                         "f"(v[j * 4]), "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]), "f"(v[j * 4 + 3])
+                         : "memory");
+        }
       } else if constexpr (EPI == EPI_F32_ATOMIC) {
         // several CTAs hold partial sums of this tile (split K): add them into C in L2
         float* cp = reinterpret_cast<float*>(args.C) + (long long)row * args.ldc + col;
@@ -282,6 +298,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int mi, ni;
         tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        mi += args.rot_m;
+        if (mi >= args.tiles_m) mi -= args.tiles_m;
         const int m0 = mi * BM;
         const int n0 = ni * TILE_N;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -390,6 +408,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       int mi, ni;
       tile_coords(t, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      mi += args.rot_m;
+      if (mi >= args.tiles_m) mi -= args.tiles_m;
       const int buf = it & 1;
       const uint32_t use = (uint32_t)(it >> 1);
       if (!mbar_wait(&tfull_bar[buf], use & 1, abort_flag, args.status, ST_TIMEOUT_TMEM_FULL)) {
@@ -682,6 +702,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       while (ok && w.next()) {
         int mi, ni;
         tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+        mi += args.rot_m;
+        if (mi >= args.tiles_m) mi -= args.tiles_m;
         if constexpr (SHARDED == 2 && !B_MN) {  // tiles on this rank's own slice first
           ni += shards->rot_tile;
           if (ni >= args.tiles_n) ni -= args.tiles_n;
@@ -871,6 +893,8 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
     for (; ok && w.next(); ++it) {
       int mi, ni;
       tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
+      mi += args.rot_m;
+      if (mi >= args.tiles_m) mi -= args.tiles_m;
       if constexpr (SHARDED == 2 && !B_MN) {
         ni += shards->rot_tile;
         if (ni >= args.tiles_n) ni -= args.tiles_n;
@@ -1120,6 +1144,46 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
   ADANA_GEMM_CASE(true, false, EPI_F32)
 #undef ADANA_GEMM_CASE
   return -103;
+}
+
+extern "C" int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* C_ranks, int n_ranks,
+                                              int my_rank, int rows_per_rank, int M, int N, int K, long long lda,
+                                              long long ldb, long long ldc, float alpha, int* status,
+                                              void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n_ranks < 1 || n_ranks > 8 || my_rank < 0 || my_rank >= n_ranks || rows_per_rank <= 0) return -110;
+  if ((long long)rows_per_rank * n_ranks < M) return -111;
+  if ((N % 8) != 0 || (ldc % 4) != 0) return -100;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tmA, tmB;
+  if (encode_tmap_2d(&tmA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, BM, 2)) return -101;
+  if (encode_tmap_2d(&tmB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 128, 2)) return -102;
+  GemmArgs args;
+  args.M = M; args.N = N; args.K = K;
+  args.C = nullptr; args.ldc = ldc; args.C2 = nullptr; args.ldc2 = 0; args.R = nullptr; args.ldr = 0;
+  args.alpha = alpha; args.beta = 0.f; args.b_off2 = 0;
+  args.tiles_n = (N + BN - 1) / BN;
+  args.group_m = 16;
+  args.streamk = 0;
+  args.status = status;
+  for (int r = 0; r < 8; ++r) {
+    args.peerC[r] = C_ranks[r < n_ranks ? r : 0];
+    if ((reinterpret_cast<uintptr_t>(args.peerC[r]) % 16) != 0) return -100;
+  }
+  args.rs_rows = rows_per_rank;
+  const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
+  const bool use_pair = g_gemm_mode >= 2 || (g_gemm_mode == 0 && pair_tiles >= 2 * (g_sm_count / 2));
+  const int tile_rows = use_pair ? P_BM : BM;
+  args.tiles_m = (M + tile_rows - 1) / tile_rows;
+  // first row tile of the next rank's rows
+  args.rot_m = (int)(((long long)((my_rank + 1) % n_ranks) * rows_per_rank / tile_rows) % args.tiles_m);
+  return use_pair ? launch_gemm_pair<false, false, EPI_F32_RS>(tmA, tmB, args, g_sm_count, stream)
+                  : launch_gemm<false, false, EPI_F32_RS>(tmA, tmB, args, g_sm_count, stream);
 }
 
 // C = epilogue(A * W^T) (b_mn = 0, W [N, K] split by rows over the ranks) or C = epilogue(A * W) (b_mn = 1,

@@ -339,6 +339,24 @@ def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, 
     return out
 
 
+def linear_fwd_reduce_scatter(x, w, out_ptrs, rows_per_rank: int, me: int, alpha: float = 1.0, ldc=None):
+    """Row-parallel linear fused with its reduce-scatter: this rank's partial product x [M, K_local] · w [N, K_local]ᵀ
+    is ADDED, from the GEMM epilogue, into the fp32 buffer of the rank that owns each output row: rank r keeps rows
+    [r · rows_per_rank, (r + 1) · rows_per_rank) in `out_ptrs[r]` ([rows_per_rank, ldc] fp32; tensors or addresses,
+    this rank's memory or a peer's).  The caller zeroes its buffer and synchronises the ranks before the call and
+    again before reading.  (The reduce-scatter after `RowwiseParallel` of the reference's tensor-parallel plans,
+    src/distributed/fsdp.py:88-103.)"""
+    _check2d(x, "x")
+    _check2d(w, "w")
+    M, K = x.shape
+    N = w.shape[0]
+    arr, n = _ptr_array(out_ptrs)
+    rc = _lib.lib().adana_gemm_bf16_reduce_scatter(
+        x.data_ptr(), w.data_ptr(), arr, n, int(me), int(rows_per_rank), M, N, K, x.stride(0), w.stride(0),
+        int(ldc if ldc is not None else N), float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_gemm_bf16_reduce_scatter")
+
+
 def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None, me=None, staged=None):
     """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows over the shards (equal slices or `row_starts`)."""
     _, n = _ptr_array(w_shards)

@@ -395,6 +395,32 @@ def test_attention_jvp_matches_torch_func_jvp(hd, Hq, Hk, S):
     assert rel_err(out, fwd_out) < 1e-2
 
 
+@pytest.mark.parametrize("world,M,N,Kl", [(4, 1024, 512, 256), (4, 384, 384, 192), (8, 8192, 2304, 288), (2, 4096, 2304, 1152)])
+def test_gemm_fused_with_reduce_scatter_over_fake_peers(world, M, N, Kl, gemm_mode):
+    """Row-parallel linear whose epilogue does the reduce-scatter: every "rank" (here: one launch per rank on this
+    GPU, the ranks' output buffers separate allocations) adds its partial product's rows into the buffer of the
+    rank that owns them.  After all launches buffer r holds rows [r * M/world, ...) of the full product."""
+    torch.manual_seed(31)
+    K = world * Kl
+    x, w = rnd(M, K), rnd(N, K)
+    rows = M // world
+    outs = [torch.zeros(rows, N, device=DEV) for _ in range(world)]
+    for r in range(world):
+        xr, wr = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
+        gemm.linear_fwd_reduce_scatter(xr, wr, outs, rows, r)
+    ref = x.float() @ w.float().t()
+    got = torch.cat(outs, 0)
+    assert rel_err(got, ref) < 5e-3
+    # alpha and a pre-loaded residual: the epilogue adds, it never overwrites
+    base = [torch.randn(rows, N, device=DEV) for _ in range(world)]
+    outs2 = [b.clone() for b in base]
+    for r in range(world):
+        xr, wr = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
+        gemm.linear_fwd_reduce_scatter(xr, wr, outs2, rows, r, alpha=0.5)
+    assert rel_err(torch.cat(outs2, 0), torch.cat(base, 0) + 0.5 * ref) < 5e-3
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("world,me,N,K", [(2, 0, 768, 512), (2, 1, 768, 512), (8, 3, 2304, 640), (8, 7, 6912, 512),
                                           (4, 2, 1280, 1152), (3, 1, 896, 576)])
 def test_staged_gather_gemm_copies_each_remote_slice_once(world, me, N, K):

@@ -134,6 +134,48 @@ def test_gather_gemm_over_nvlink_peers():
         assert res[r]["staged_same_bits"] and res[r]["err_dx_staged"] < 8e-3, res[r]
 
 
+def _gemm_rs_worker(rank, world):
+    """Row-parallel linear fused with its reduce-scatter over real peers (parallel/tensor_parallel.FusedRowParallel):
+    every rank multiplies its K-slice and the epilogue adds each row into its owner's buffer over NVLink."""
+    import torch.distributed as dist
+
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.p2p import P2PPlane
+    from adana_b200.parallel.tensor_parallel import FusedRowParallel
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    M, N, Kl = 4096, 2304, 576
+    K = world * Kl
+    torch.manual_seed(9)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()                 # same on every rank
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    plane = P2PPlane.create((M // world) * N * 4 + (1 << 16), torch.device("cuda", rank))
+    op = FusedRowParallel(plane, M, N)
+    xr, wr = x[:, rank * Kl:(rank + 1) * Kl].contiguous(), w[:, rank * Kl:(rank + 1) * Kl].contiguous()
+    errs = []
+    for _ in range(3):                                                       # the buffers are reused call after call
+        out = op(xr, wr)
+        torch.cuda.synchronize()
+        ref = (x.float() @ w.float().t())[rank * op.rows:(rank + 1) * op.rows]
+        errs.append(((out - ref).norm() / ref.norm()).item())
+        plane.barrier()                                                      # nobody zeroes a buffer still being read
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return {"errs": errs}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gemm_fused_with_reduce_scatter_over_nvlink_peers():
+    from test_distributed_cpu import _spawn
+
+    world = min(torch.cuda.device_count(), 8)
+    res = _spawn(_gemm_rs_worker, world)
+    for r in range(world):
+        assert max(res[r]["errs"]) < 5e-3, res[r]
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_gathered_weights_over_peers_match_resident_weights():
     """Every rank keeps only its row slices of the block matrices; forward / backward GEMMs fetch the other rows
