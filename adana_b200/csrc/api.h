@@ -17,6 +17,7 @@ enum {
   EPI_AXPBY_BF16 = 7, // C(bf16) = alpha * acc + beta * R(bf16); C may alias R
   EPI_F32_ATOMIC = 8, // C(f32) += alpha * acc with vector atomics (internal: stream-K partial tiles)
   EPI_F32_RS = 9,     // rows added into the fp32 buffer of the rank that owns them (adana_gemm_bf16_reduce_scatter)
+  EPI_BF16_PUSH = 10, // rows stored (bf16) into this rank's slot at the rank that owns them (same entry point)
 };
 
 #ifdef __cplusplus
@@ -26,15 +27,23 @@ extern "C" {
 // D = epilogue(A * B^T), bf16 operands, fp32 accumulate on tcgen05 tensor cores.
 // a_mn / b_mn select MN-major operands (see gemm_tcgen05.cu).  ld* are row pitches in elements.
 // GEMM fused with the reduce-scatter that follows a row-parallel linear: this rank holds a K-slice of the operands,
-// A [M, K] and B [N, K] (both K-major), and its partial product alpha * A * B^T is ADDED, tile by tile from the
-// epilogue (`red.global.add.v4.f32`, over NVLink for remote rows), into the buffer of the rank that owns the rows:
-// rank r keeps output rows [r * rows_per_rank, (r + 1) * rows_per_rank) in C_ranks[r] ([rows_per_rank, ldc] fp32).
-// The caller zero-fills (or pre-loads a residual into) its own buffer and synchronises the ranks before the launch,
-// and again before anyone reads: after that second barrier every buffer holds the sum over ranks.  Row tiles are
-// taken starting at the rows of rank my_rank + 1, so the ranks do not all push to the same destination at once.
+// A [M, K] and B [N, K] (both K-major); rank r keeps output rows [r * rows_per_rank, (r + 1) * rows_per_rank).
+// Row tiles are taken starting at the rows of rank my_rank + 1, so the ranks do not all send to one destination.
+//  push_bf16 = 1 (preferred): the epilogue STORES this rank's partial rows (bf16, plain 16-byte stores, over NVLink
+//   for remote rows) into slot my_rank of the owner's slot array C_ranks[owner] ([n_ranks, rows_per_rank, ldc] bf16).
+//   After a barrier over the ranks the owner sums its n_ranks slots in fp32 in a fixed order (adana_sum_slots_bf16):
+//   deterministic, nothing to zero, no atomics.  The caller synchronises the ranks before the launch too, so that no
+//   slot is overwritten while its owner still reads it.
+//  push_bf16 = 0: the partial product is ADDED (`red.global.add.v4.f32`) into C_ranks[owner] ([rows_per_rank, ldc]
+//   fp32, zero-filled or pre-loaded by its owner before a barrier); bound by the L2's fp32 atomic rate (~0.5 TB/s).
 int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* C_ranks, int n_ranks, int my_rank,
                                    int rows_per_rank, int M, int N, int K, long long lda, long long ldb,
-                                   long long ldc, float alpha, int* status, void* stream);
+                                   long long ldc, float alpha, int push_bf16, int* status, void* stream);
+// out [rows, N] (fp32, pitch ld_out) = (resid ? resid : 0) + sum over s < n_slots of slots[s][rows][N] (bf16, pitch
+// ld_slot), summed in fp32 in slot order; out_bf16 (optional) receives a bf16 copy.  N a multiple of 8.
+int adana_sum_slots_bf16(const void* slots, int n_slots, int rows, int N, long long ld_slot, float* out,
+                         long long ld_out, const float* resid, long long ld_resid, void* out_bf16,
+                         long long ld_out16, void* stream);
 
 // All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks: rank r holds rows
 // [row_starts[r], row_starts[r+1]) (multiples of 32; nullptr = equal slices of rows_per_shard rows) at B_shards[r]

@@ -208,6 +208,55 @@ p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, flo
   }
 }
 
+// Second half of the push-style reduce-scatter (first half: the GEMM epilogue EPI_BF16_PUSH stores every rank's
+// partial rows into its slot here): out = resid + sum over slots, fp32 accumulation in slot order, 8 columns per thread.
+__global__ void __launch_bounds__(256)
+sum_slots_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, int rows, int N, long long ld_slot,
+                      float* __restrict__ out, long long ld_out, const float* __restrict__ resid, long long ld_resid,
+                      __nv_bfloat16* __restrict__ out16, long long ld_out16) {
+  const int vec_per_row = N >> 3;
+  const long long total = (long long)rows * vec_per_row;
+  const long long slot_stride = (long long)rows * ld_slot;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row);
+    const int c = (int)(i - (long long)r * vec_per_row) * 8;
+    float acc[8];
+    if (resid) {
+      const float4 a = *reinterpret_cast<const float4*>(resid + (long long)r * ld_resid + c);
+      const float4 b = *reinterpret_cast<const float4*>(resid + (long long)r * ld_resid + c + 4);
+      acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    uint4 u[8];
+#pragma unroll
+    for (int sidx = 0; sidx < 8; ++sidx)
+      if (sidx < n_slots) u[sidx] = *reinterpret_cast<const uint4*>(slots + sidx * slot_stride + (long long)r * ld_slot + c);
+#pragma unroll
+    for (int sidx = 0; sidx < 8; ++sidx) {
+      if (sidx < n_slots) {
+        const float2 p0 = unpack_bf16x2(u[sidx].x), p1 = unpack_bf16x2(u[sidx].y), p2 = unpack_bf16x2(u[sidx].z),
+                     p3 = unpack_bf16x2(u[sidx].w);
+        acc[0] += p0.x; acc[1] += p0.y; acc[2] += p1.x; acc[3] += p1.y;
+        acc[4] += p2.x; acc[5] += p2.y; acc[6] += p3.x; acc[7] += p3.y;
+      }
+    }
+    float* o = out + (long long)r * ld_out + c;
+    *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (out16) {
+      uint4 w;
+      w.x = pack_bf16x2(acc[0], acc[1]);
+      w.y = pack_bf16x2(acc[2], acc[3]);
+      w.z = pack_bf16x2(acc[4], acc[5]);
+      w.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out16 + (long long)r * ld_out16 + c) = w;
+    }
+  }
+}
+
 }  // namespace adana
 
 using namespace adana;
@@ -282,5 +331,20 @@ extern "C" int adana_p2p_opt_step_push(float* p, const float* g, float* m, float
     case 3: p2p_opt_step_push_kernel<3><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
     default: return -3;
   }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int adana_sum_slots_bf16(const void* slots, int n_slots, int rows, int N, long long ld_slot, float* out,
+                                    long long ld_out, const float* resid, long long ld_resid, void* out_bf16,
+                                    long long ld_out16, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0 || N <= 0) return 0;
+  if (n_slots < 1 || n_slots > 8 || (N % 8) != 0 || (ld_slot % 8) != 0 || (ld_out % 4) != 0) return -1;
+  if ((resid && (ld_resid % 4) != 0) || (out_bf16 && (ld_out16 % 8) != 0)) return -1;
+  const long long total = (long long)rows * (N / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sum_slots_bf16_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)slots, n_slots, rows, N, ld_slot, out,
+                                                     ld_out, resid, ld_resid, (__nv_bfloat16*)out_bf16, ld_out16);
   return (int)cudaGetLastError();
 }

@@ -51,6 +51,7 @@ struct GemmArgs {
   // ADDED into rank r's buffer peerC[r] ([rs_rows, ldc] fp32, its own memory or a peer's over NVLink)
   void* peerC[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int rs_rows = 0;
+  int rs_me = 0;  // EPI_BF16_PUSH: this rank's slot in the owner's [n_ranks, rs_rows, ldc] bf16 slot array
   int rot_m = 0;  // row-tile rotation: with it every rank starts on another destination
 };
 
@@ -181,6 +182,12 @@ __device__ __forceinline__ void epilogue_rows(const GemmArgs& args, uint32_t tad
         for (int i = 0; i < 32; ++i) v[i] = fmaf(args.beta, z[i], v[i]);
         store_bf16x32<EPI>(reinterpret_cast<__nv_bfloat16*>(args.C) + (long long)row * args.ldc + col, v,
                            ncols_ok);
+      } else if constexpr (EPI == EPI_BF16_PUSH) {
+        // this rank's partial row goes, with plain stores, into its own slot at the rank that owns the row
+        const int owner = row / args.rs_rows;
+        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(args.peerC[owner]) +
+                            ((long long)args.rs_me * args.rs_rows + (row - owner * args.rs_rows)) * args.ldc + col;
+        store_bf16x32<EPI>(cp, v, ncols_ok);
       } else if constexpr (EPI == EPI_F32_RS) {
         // this rank's partial product of a row that rank `owner` keeps: added in the owner's L2
         const int owner = row / args.rs_rows;
@@ -1148,11 +1155,12 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
 
 extern "C" int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* C_ranks, int n_ranks,
                                               int my_rank, int rows_per_rank, int M, int N, int K, long long lda,
-                                              long long ldb, long long ldc, float alpha, int* status,
-                                              void* stream_) {
+                                              long long ldb, long long ldc, float alpha, int push_bf16,
+                                              int* status, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (n_ranks < 1 || n_ranks > 8 || my_rank < 0 || my_rank >= n_ranks || rows_per_rank <= 0) return -110;
+  if (push_bf16 && (ldc % 8) != 0) return -100;
   if ((long long)rows_per_rank * n_ranks < M) return -111;
   if ((N % 8) != 0 || (ldc % 4) != 0) return -100;
   if (g_sm_count == 0) {
@@ -1176,12 +1184,16 @@ extern "C" int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void
     if ((reinterpret_cast<uintptr_t>(args.peerC[r]) % 16) != 0) return -100;
   }
   args.rs_rows = rows_per_rank;
+  args.rs_me = my_rank;
   const long long pair_tiles = (long long)((M + P_BM - 1) / P_BM) * args.tiles_n;
   const bool use_pair = g_gemm_mode >= 2 || (g_gemm_mode == 0 && pair_tiles >= 2 * (g_sm_count / 2));
   const int tile_rows = use_pair ? P_BM : BM;
   args.tiles_m = (M + tile_rows - 1) / tile_rows;
   // first row tile of the next rank's rows
   args.rot_m = (int)(((long long)((my_rank + 1) % n_ranks) * rows_per_rank / tile_rows) % args.tiles_m);
+  if (push_bf16)
+    return use_pair ? launch_gemm_pair<false, false, EPI_BF16_PUSH>(tmA, tmB, args, g_sm_count, stream)
+                    : launch_gemm<false, false, EPI_BF16_PUSH>(tmA, tmB, args, g_sm_count, stream);
   return use_pair ? launch_gemm_pair<false, false, EPI_F32_RS>(tmA, tmB, args, g_sm_count, stream)
                   : launch_gemm<false, false, EPI_F32_RS>(tmA, tmB, args, g_sm_count, stream);
 }

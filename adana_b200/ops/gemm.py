@@ -339,13 +339,17 @@ def gather_gemm(x, shards, rows_per_shard, N, *, ldb, b_mn=False, epi=EPI_BF16, 
     return out
 
 
-def linear_fwd_reduce_scatter(x, w, out_ptrs, rows_per_rank: int, me: int, alpha: float = 1.0, ldc=None):
+def linear_fwd_reduce_scatter(x, w, out_ptrs, rows_per_rank: int, me: int, alpha: float = 1.0, ldc=None, push=True):
     """Row-parallel linear fused with its reduce-scatter: this rank's partial product x [M, K_local] · w [N, K_local]ᵀ
-    is ADDED, from the GEMM epilogue, into the fp32 buffer of the rank that owns each output row: rank r keeps rows
-    [r · rows_per_rank, (r + 1) · rows_per_rank) in `out_ptrs[r]` ([rows_per_rank, ldc] fp32; tensors or addresses,
-    this rank's memory or a peer's).  The caller zeroes its buffer and synchronises the ranks before the call and
-    again before reading.  (The reduce-scatter after `RowwiseParallel` of the reference's tensor-parallel plans,
-    src/distributed/fsdp.py:88-103.)"""
+    leaves the GEMM epilogue straight for the rank that owns each output row (rank r keeps rows
+    [r · rows_per_rank, (r + 1) · rows_per_rank)); `out_ptrs[r]` (tensors or addresses) is rank r's memory, local or
+    a peer's over NVLink.
+      push=True : bf16 partial rows are STORED into slot `me` of the owner's slot array [n_ranks, rows_per_rank, ldc]
+                  (bf16); after a barrier the owner adds its slots with `sum_slots`.  Deterministic, no atomics.
+      push=False: fp32 partial rows are ADDED (vector atomics) into the owner's [rows_per_rank, ldc] fp32 buffer, which
+                  the owner zeroed (or pre-loaded) before a barrier.
+    The caller synchronises the ranks before the call and again before reading.  (The reduce-scatter after
+    `RowwiseParallel` in the reference's tensor-parallel plans, src/distributed/fsdp.py:88-103.)"""
     _check2d(x, "x")
     _check2d(w, "w")
     M, K = x.shape
@@ -353,8 +357,29 @@ def linear_fwd_reduce_scatter(x, w, out_ptrs, rows_per_rank: int, me: int, alpha
     arr, n = _ptr_array(out_ptrs)
     rc = _lib.lib().adana_gemm_bf16_reduce_scatter(
         x.data_ptr(), w.data_ptr(), arr, n, int(me), int(rows_per_rank), M, N, K, x.stride(0), w.stride(0),
-        int(ldc if ldc is not None else N), float(alpha), _lib.status_buffer(x.device).data_ptr(), _lib.stream_ptr())
+        int(ldc if ldc is not None else N), float(alpha), int(bool(push)), _lib.status_buffer(x.device).data_ptr(),
+        _lib.stream_ptr())
     _lib.check_rc(rc, "adana_gemm_bf16_reduce_scatter")
+
+
+def sum_slots(slots, out=None, resid=None, out_lowp=None):
+    """out [rows, N] fp32 = (resid or 0) + Σ_s slots[s] (slots [n, rows, N] bf16), fp32 accumulation in slot order;
+    `out_lowp` (bf16) optionally receives a copy.  Second half of the push-style reduce-scatter."""
+    n, rows, N = slots.shape
+    if out is None:
+        out = torch.empty((rows, N), dtype=torch.float32, device=slots.device)
+    if not (slots.is_cuda and _lib.available()):
+        r = slots.float().sum(0) + (0 if resid is None else resid)
+        out.copy_(r)
+        if out_lowp is not None:
+            out_lowp.copy_(r)
+        return out
+    rc = _lib.lib().adana_sum_slots_bf16(
+        slots.data_ptr(), n, rows, N, slots.stride(1), out.data_ptr(), out.stride(0), _lib.ptr(resid),
+        0 if resid is None else resid.stride(0), _lib.ptr(out_lowp), 0 if out_lowp is None else out_lowp.stride(0),
+        _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_sum_slots_bf16")
+    return out
 
 
 def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None, me=None, staged=None):

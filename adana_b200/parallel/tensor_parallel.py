@@ -31,28 +31,44 @@ def apply_tensor_parallel(model, tp_mesh) -> None:
 
 
 class FusedRowParallel:
-    """Row-parallel linear + reduce-scatter in one kernel over a peer-memory plane.
+    """Row-parallel linear + reduce-scatter over a peer-memory plane, the transfer inside the GEMM's epilogue.
 
     Every rank holds a K-slice of the input x [M, K/tp] and of the weight w [N, K/tp]; the full product is the sum
     of the ranks' partial products.  `__call__` leaves rank r with rows [r·M/tp, (r+1)·M/tp) of that sum (fp32), the
-    sequence-parallel layout that the next norm / column-parallel linear consumes.  Two plane barriers bracket the
-    launch: one after the buffers are zeroed, one before they are read."""
+    sequence-parallel layout that the next norm / column-parallel linear consumes.
+      mode "push" (default): partial rows travel as bf16 plain stores into per-source slots at their owner, which
+        then adds its slots in fp32 in a fixed order (one small kernel): barrier, GEMM, barrier, sum.
+      mode "atomic": partial rows are added with fp32 vector atomics into the owner's zeroed buffer."""
 
-    def __init__(self, plane, M: int, N: int):
+    def __init__(self, plane, M: int, N: int, mode: str = "push"):
         import torch
 
         if M % plane.world != 0:
             raise ValueError(f"M={M} must divide by the {plane.world} tensor-parallel ranks")
-        self.plane, self.M, self.N = plane, M, N
+        if mode not in ("push", "atomic"):
+            raise ValueError(mode)
+        self.plane, self.M, self.N, self.mode = plane, M, N, mode
         self.rows = M // plane.world
-        self.out = plane.alloc(self.rows * N, torch.float32).view(self.rows, N)
-        self.ptrs = plane.peer_ptrs(self.out)
+        if mode == "push":
+            self.slots = plane.alloc(plane.world * self.rows * N, torch.bfloat16).view(plane.world, self.rows, N)
+            self.ptrs = plane.peer_ptrs(self.slots)
+            self.out = torch.empty((self.rows, N), dtype=torch.float32, device=plane.device)
+        else:
+            self.out = plane.alloc(self.rows * N, torch.float32).view(self.rows, N)
+            self.ptrs = plane.peer_ptrs(self.out)
 
-    def __call__(self, x_local, w_local, alpha: float = 1.0):
+    def __call__(self, x_local, w_local, alpha: float = 1.0, resid=None):
         from ..ops import gemm
 
-        self.out.zero_()
-        self.plane.barrier()
-        gemm.linear_fwd_reduce_scatter(x_local, w_local, self.ptrs, self.rows, self.plane.rank, alpha)
-        self.plane.barrier()
+        push = self.mode == "push"
+        if not push:
+            if resid is None:
+                self.out.zero_()
+            else:
+                self.out.copy_(resid)
+        self.plane.barrier()          # push: nobody still reads the slots; atomic: every buffer is initialised
+        gemm.linear_fwd_reduce_scatter(x_local, w_local, self.ptrs, self.rows, self.plane.rank, alpha, push=push)
+        self.plane.barrier()          # every rank's rows have arrived
+        if push:
+            gemm.sum_slots(self.slots, out=self.out, resid=resid)
         return self.out

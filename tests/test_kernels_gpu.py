@@ -407,7 +407,7 @@ def test_gemm_fused_with_reduce_scatter_over_fake_peers(world, M, N, Kl, gemm_mo
     outs = [torch.zeros(rows, N, device=DEV) for _ in range(world)]
     for r in range(world):
         xr, wr = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
-        gemm.linear_fwd_reduce_scatter(xr, wr, outs, rows, r)
+        gemm.linear_fwd_reduce_scatter(xr, wr, outs, rows, r, push=False)
     ref = x.float() @ w.float().t()
     got = torch.cat(outs, 0)
     assert rel_err(got, ref) < 5e-3
@@ -416,8 +416,20 @@ def test_gemm_fused_with_reduce_scatter_over_fake_peers(world, M, N, Kl, gemm_mo
     outs2 = [b.clone() for b in base]
     for r in range(world):
         xr, wr = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
-        gemm.linear_fwd_reduce_scatter(xr, wr, outs2, rows, r, alpha=0.5)
+        gemm.linear_fwd_reduce_scatter(xr, wr, outs2, rows, r, alpha=0.5, push=False)
     assert rel_err(torch.cat(outs2, 0), torch.cat(base, 0) + 0.5 * ref) < 5e-3
+    # push mode: bf16 partial rows stored into per-source slots at the owner, then summed in slot order
+    slots = [torch.full((world, rows, N), float("nan"), device=DEV, dtype=torch.bfloat16) for _ in range(world)]
+    for r in range(world):
+        xr, wr = x[:, r * Kl:(r + 1) * Kl].contiguous(), w[:, r * Kl:(r + 1) * Kl].contiguous()
+        gemm.linear_fwd_reduce_scatter(xr, wr, slots, rows, r, push=True)
+    got = torch.cat([gemm.sum_slots(sl) for sl in slots], 0)
+    assert rel_err(got, ref) < 6e-3
+    part = torch.stack([(x[:, r * Kl:(r + 1) * Kl].float() @ w[:, r * Kl:(r + 1) * Kl].float().t()) for r in range(world)])
+    assert rel_err(slots[0], part[:, :rows]) < 6e-3          # slot s of rank 0 = rank s's partial of rank 0's rows
+    lowp = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
+    withres = gemm.sum_slots(slots[1], resid=base[1], out_lowp=lowp)
+    assert rel_err(withres, base[1] + ref[rows:2 * rows]) < 6e-3 and rel_err(lowp, withres) < 5e-3
     _lib.check_status()
 
 

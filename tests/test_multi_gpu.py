@@ -151,16 +151,17 @@ def _gemm_rs_worker(rank, world):
     torch.manual_seed(9)
     x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()                 # same on every rank
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
-    plane = P2PPlane.create((M // world) * N * 4 + (1 << 16), torch.device("cuda", rank))
-    op = FusedRowParallel(plane, M, N)
+    plane = P2PPlane.create((M // world) * N * 4 + M * N * 2 + (1 << 16), torch.device("cuda", rank))
     xr, wr = x[:, rank * Kl:(rank + 1) * Kl].contiguous(), w[:, rank * Kl:(rank + 1) * Kl].contiguous()
     errs = []
-    for _ in range(3):                                                       # the buffers are reused call after call
-        out = op(xr, wr)
-        torch.cuda.synchronize()
-        ref = (x.float() @ w.float().t())[rank * op.rows:(rank + 1) * op.rows]
-        errs.append(((out - ref).norm() / ref.norm()).item())
-        plane.barrier()                                                      # nobody zeroes a buffer still being read
+    for mode in ("push", "atomic"):
+        op = FusedRowParallel(plane, M, N, mode=mode)
+        for _ in range(3):                                                   # the buffers are reused call after call
+            out = op(xr, wr)
+            torch.cuda.synchronize()
+            ref = (x.float() @ w.float().t())[rank * op.rows:(rank + 1) * op.rows]
+            errs.append(((out - ref).norm() / ref.norm()).item())
+            plane.barrier()                                                  # nobody zeroes a buffer still being read
     torch.cuda.synchronize()
     _lib.check_status()
     return {"errs": errs}
@@ -173,7 +174,7 @@ def test_gemm_fused_with_reduce_scatter_over_nvlink_peers():
     world = min(torch.cuda.device_count(), 8)
     res = _spawn(_gemm_rs_worker, world)
     for r in range(world):
-        assert max(res[r]["errs"]) < 5e-3, res[r]
+        assert max(res[r]["errs"]) < 6e-3, res[r]
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
