@@ -44,6 +44,12 @@ int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void* const* C_
 int adana_sum_slots_bf16(const void* slots, int n_slots, int rows, int N, long long ld_slot, float* out,
                          long long ld_out, const float* resid, long long ld_resid, void* out_bf16,
                          long long ld_out16, void* stream);
+// Pull-style reduce-scatter of bf16 partial matrices: rank r's partial product P_r [M, N] (pitch ld) sits at
+// partial_ptrs[r] (local or peer memory); out = (resid or 0) + sum over r of P_r[first_row : first_row + rows], fp32
+// accumulation in rank order, the peers' rows read over NVLink.  Call between two barriers over the ranks.
+int adana_p2p_reduce_scatter_bf16(const unsigned long long* partial_ptrs, int n_ranks, long long first_row, int rows,
+                                  int N, long long ld, float* out, long long ld_out, const float* resid,
+                                  long long ld_resid, void* out_bf16, long long ld_out16, void* stream);
 
 // All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks: rank r holds rows
 // [row_starts[r], row_starts[r+1]) (multiples of 32; nullptr = equal slices of rows_per_shard rows) at B_shards[r]

@@ -210,13 +210,15 @@ p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, flo
 
 // Second half of the push-style reduce-scatter (first half: the GEMM epilogue EPI_BF16_PUSH stores every rank's
 // partial rows into its slot here): out = resid + sum over slots, fp32 accumulation in slot order, 8 columns per thread.
+struct SlotPtrs {
+  const __nv_bfloat16* p[8];  // first row of slot s: consecutive slots of one array, or one partial matrix per peer
+};
 __global__ void __launch_bounds__(256)
-sum_slots_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, int rows, int N, long long ld_slot,
+sum_slots_bf16_kernel(const SlotPtrs slots, int n_slots, int rows, int N, long long ld_slot,
                       float* __restrict__ out, long long ld_out, const float* __restrict__ resid, long long ld_resid,
                       __nv_bfloat16* __restrict__ out16, long long ld_out16) {
   const int vec_per_row = N >> 3;
   const long long total = (long long)rows * vec_per_row;
-  const long long slot_stride = (long long)rows * ld_slot;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / vec_per_row);
@@ -233,7 +235,7 @@ sum_slots_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, int 
     uint4 u[8];
 #pragma unroll
     for (int sidx = 0; sidx < 8; ++sidx)
-      if (sidx < n_slots) u[sidx] = *reinterpret_cast<const uint4*>(slots + sidx * slot_stride + (long long)r * ld_slot + c);
+      if (sidx < n_slots) u[sidx] = *reinterpret_cast<const uint4*>(slots.p[sidx] + (long long)r * ld_slot + c);
 #pragma unroll
     for (int sidx = 0; sidx < 8; ++sidx) {
       if (sidx < n_slots) {
@@ -344,7 +346,32 @@ extern "C" int adana_sum_slots_bf16(const void* slots, int n_slots, int rows, in
   const long long total = (long long)rows * (N / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  sum_slots_bf16_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)slots, n_slots, rows, N, ld_slot, out,
-                                                     ld_out, resid, ld_resid, (__nv_bfloat16*)out_bf16, ld_out16);
+  SlotPtrs sp;
+  for (int i = 0; i < 8; ++i)
+    sp.p[i] = reinterpret_cast<const __nv_bfloat16*>(slots) + (long long)(i < n_slots ? i : 0) * rows * ld_slot;
+  sum_slots_bf16_kernel<<<(int)blocks, 256, 0, st>>>(sp, n_slots, rows, N, ld_slot, out, ld_out, resid, ld_resid,
+                                                     (__nv_bfloat16*)out_bf16, ld_out16);
+  return (int)cudaGetLastError();
+}
+
+// Pull-style reduce-scatter of bf16 partial matrices: every rank r holds its partial product P_r [M, N] (pitch ld)
+// in memory the others can read; this rank adds rows [first_row, first_row + rows) of all n_ranks partials in fp32,
+// in rank order, reading the peers' rows over NVLink with 16-byte coalesced loads.
+extern "C" int adana_p2p_reduce_scatter_bf16(const unsigned long long* partial_ptrs, int n_ranks, long long first_row,
+                                             int rows, int N, long long ld, float* out, long long ld_out,
+                                             const float* resid, long long ld_resid, void* out_bf16,
+                                             long long ld_out16, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0 || N <= 0) return 0;
+  if (n_ranks < 1 || n_ranks > 8 || (N % 8) != 0 || (ld % 8) != 0 || (ld_out % 4) != 0) return -1;
+  if ((resid && (ld_resid % 4) != 0) || (out_bf16 && (ld_out16 % 8) != 0)) return -1;
+  SlotPtrs sp;
+  for (int i = 0; i < 8; ++i)
+    sp.p[i] = reinterpret_cast<const __nv_bfloat16*>(partial_ptrs[i < n_ranks ? i : 0]) + first_row * ld;
+  const long long total = (long long)rows * (N / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sum_slots_bf16_kernel<<<(int)blocks, 256, 0, st>>>(sp, n_ranks, rows, N, ld, out, ld_out, resid, ld_resid,
+                                                     (__nv_bfloat16*)out_bf16, ld_out16);
   return (int)cudaGetLastError();
 }

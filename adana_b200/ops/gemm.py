@@ -382,6 +382,18 @@ def sum_slots(slots, out=None, resid=None, out_lowp=None):
     return out
 
 
+def reduce_scatter_partials(partial_ptrs, first_row: int, rows: int, N: int, ld: int, out, resid=None, out_lowp=None):
+    """out [rows, N] fp32 = (resid or 0) + Σ_r P_r[first_row : first_row + rows] where rank r's bf16 partial matrix
+    P_r (row pitch `ld`) lives at `partial_ptrs[r]` (tensors or addresses; peers are read over NVLink)."""
+    arr, n = _ptr_array(partial_ptrs)
+    rc = _lib.lib().adana_p2p_reduce_scatter_bf16(
+        arr, n, int(first_row), int(rows), int(N), int(ld), out.data_ptr(), out.stride(0), _lib.ptr(resid),
+        0 if resid is None else resid.stride(0), _lib.ptr(out_lowp), 0 if out_lowp is None else out_lowp.stride(0),
+        _lib.stream_ptr())
+    _lib.check_rc(rc, "adana_p2p_reduce_scatter_bf16")
+    return out
+
+
 def linear_fwd_gathered(x, w_shards, rows_per_shard=None, out=None, row_starts=None, me=None, staged=None):
     """y [M, N] = x [M, K] · Wᵀ with W [N, K] split by rows over the shards (equal slices or `row_starts`)."""
     _, n = _ptr_array(w_shards)

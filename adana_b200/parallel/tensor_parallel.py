@@ -7,9 +7,12 @@ calls on every block, before FSDP wraps the block on the data-parallel sub-mesh
 (reference: src/distributed/fsdp.py:88-103; plans src/models/enoki.py:239-251,
 src/models/qwen3.py:312-327).  Embeddings, norms and the LM head stay replicated over tp.
 
-`FusedRowParallel` is the kernel-path building block for the row-parallel half: the GEMM whose epilogue does the
-reduce-scatter over peer memory (csrc/gemm_tcgen05.cu, EPI_F32_RS), so the partial products never exist as a
-tensor and the transfer overlaps the math tile by tile.
+`RowParallelLinear` is the kernel-path building block for the row-parallel half (GEMM on a K-slice, then a
+reduce-scatter of the partial products over peer memory), in three variants that were measured against each other
+and against NCCL: the default writes the bf16 partial product locally and lets every rank pull and add the rows it
+owns (coalesced 16-byte loads over NVLink); two fused variants move the partial rows out of the GEMM's epilogue
+(bf16 stores into per-source slots, or fp32 vector atomics) and are slower on NVLink because an epilogue lane owns a
+row, so its remote accesses are 16-byte pieces.
 """
 from __future__ import annotations
 
@@ -30,28 +33,36 @@ def apply_tensor_parallel(model, tp_mesh) -> None:
         parallelize_module(blk, tp_mesh, plan)
 
 
-class FusedRowParallel:
-    """Row-parallel linear + reduce-scatter over a peer-memory plane, the transfer inside the GEMM's epilogue.
+class RowParallelLinear:
+    """Row-parallel linear + reduce-scatter over a peer-memory plane.
 
     Every rank holds a K-slice of the input x [M, K/tp] and of the weight w [N, K/tp]; the full product is the sum
     of the ranks' partial products.  `__call__` leaves rank r with rows [r·M/tp, (r+1)·M/tp) of that sum (fp32), the
     sequence-parallel layout that the next norm / column-parallel linear consumes.
-      mode "push" (default): partial rows travel as bf16 plain stores into per-source slots at their owner, which
+      mode "push": fused; partial rows travel as bf16 plain stores into per-source slots at their owner, which
         then adds its slots in fp32 in a fixed order (one small kernel): barrier, GEMM, barrier, sum.
-      mode "atomic": partial rows are added with fp32 vector atomics into the owner's zeroed buffer."""
+      mode "atomic": fused; partial rows are added with fp32 vector atomics into the owner's zeroed buffer.
+      mode "pull" (default; fastest measured: 0.152 ms against 0.342 ms for GEMM + NCCL reduce-scatter at
+        16384 x 2304 x 1152 on two B200s): the GEMM writes its whole bf16 partial product locally, and after a barrier every rank
+        adds the rows it owns out of all ranks' partials, reading the peers' rows over NVLink with coalesced 16-byte
+        loads (`adana_p2p_reduce_scatter_bf16`)."""
 
-    def __init__(self, plane, M: int, N: int, mode: str = "push"):
+    def __init__(self, plane, M: int, N: int, mode: str = "pull"):
         import torch
 
         if M % plane.world != 0:
             raise ValueError(f"M={M} must divide by the {plane.world} tensor-parallel ranks")
-        if mode not in ("push", "atomic"):
+        if mode not in ("push", "atomic", "pull"):
             raise ValueError(mode)
         self.plane, self.M, self.N, self.mode = plane, M, N, mode
         self.rows = M // plane.world
         if mode == "push":
             self.slots = plane.alloc(plane.world * self.rows * N, torch.bfloat16).view(plane.world, self.rows, N)
             self.ptrs = plane.peer_ptrs(self.slots)
+            self.out = torch.empty((self.rows, N), dtype=torch.float32, device=plane.device)
+        elif mode == "pull":
+            self.partial = plane.alloc(M * N, torch.bfloat16).view(M, N)
+            self.ptrs = plane.peer_ptrs(self.partial)
             self.out = torch.empty((self.rows, N), dtype=torch.float32, device=plane.device)
         else:
             self.out = plane.alloc(self.rows * N, torch.float32).view(self.rows, N)
@@ -60,6 +71,13 @@ class FusedRowParallel:
     def __call__(self, x_local, w_local, alpha: float = 1.0, resid=None):
         from ..ops import gemm
 
+        if self.mode == "pull":
+            self.plane.barrier()      # nobody still reads my previous partial
+            gemm.linear_fwd(x_local, w_local, out=self.partial) if alpha == 1.0 else \
+                gemm.gemm(x_local, w_local, self.partial, M=self.M, N=self.N, K=x_local.shape[1], alpha=alpha)
+            self.plane.barrier()      # every partial is complete
+            return gemm.reduce_scatter_partials(self.ptrs, self.plane.rank * self.rows, self.rows, self.N, self.N,
+                                                self.out, resid=resid)
         push = self.mode == "push"
         if not push:
             if resid is None:

@@ -427,6 +427,12 @@ def test_gemm_fused_with_reduce_scatter_over_fake_peers(world, M, N, Kl, gemm_mo
     assert rel_err(got, ref) < 6e-3
     part = torch.stack([(x[:, r * Kl:(r + 1) * Kl].float() @ w[:, r * Kl:(r + 1) * Kl].float().t()) for r in range(world)])
     assert rel_err(slots[0], part[:, :rows]) < 6e-3          # slot s of rank 0 = rank s's partial of rank 0's rows
+    # pull-style reduce-scatter over whole bf16 partial matrices (one per "rank")
+    partials = [part[r].bfloat16() for r in range(world)]
+    for me in (0, world - 1):
+        out = torch.empty(rows, N, device=DEV)
+        gemm.reduce_scatter_partials(partials, me * rows, rows, N, N, out)
+        assert rel_err(out, ref[me * rows:(me + 1) * rows]) < 6e-3
     lowp = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
     withres = gemm.sum_slots(slots[1], resid=base[1], out_lowp=lowp)
     assert rel_err(withres, base[1] + ref[rows:2 * rows]) < 6e-3 and rel_err(lowp, withres) < 5e-3

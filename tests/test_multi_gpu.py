@@ -135,13 +135,13 @@ def test_gather_gemm_over_nvlink_peers():
 
 
 def _gemm_rs_worker(rank, world):
-    """Row-parallel linear fused with its reduce-scatter over real peers (parallel/tensor_parallel.FusedRowParallel):
+    """Row-parallel linear fused with its reduce-scatter over real peers (parallel/tensor_parallel.RowParallelLinear):
     every rank multiplies its K-slice and the epilogue adds each row into its owner's buffer over NVLink."""
     import torch.distributed as dist
 
     from adana_b200.ops import _lib
     from adana_b200.parallel.p2p import P2PPlane
-    from adana_b200.parallel.tensor_parallel import FusedRowParallel
+    from adana_b200.parallel.tensor_parallel import RowParallelLinear
 
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     torch.cuda.set_device(rank)
@@ -151,11 +151,11 @@ def _gemm_rs_worker(rank, world):
     torch.manual_seed(9)
     x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()                 # same on every rank
     w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
-    plane = P2PPlane.create((M // world) * N * 4 + M * N * 2 + (1 << 16), torch.device("cuda", rank))
+    plane = P2PPlane.create((M // world) * N * 4 + 2 * M * N * 2 + (1 << 16), torch.device("cuda", rank))
     xr, wr = x[:, rank * Kl:(rank + 1) * Kl].contiguous(), w[:, rank * Kl:(rank + 1) * Kl].contiguous()
     errs = []
-    for mode in ("push", "atomic"):
-        op = FusedRowParallel(plane, M, N, mode=mode)
+    for mode in ("push", "atomic", "pull"):
+        op = RowParallelLinear(plane, M, N, mode=mode)
         for _ in range(3):                                                   # the buffers are reused call after call
             out = op(xr, wr)
             torch.cuda.synchronize()
