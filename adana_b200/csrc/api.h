@@ -57,7 +57,7 @@ int adana_p2p_reduce_scatter_bf16(const unsigned long long* partial_ptrs, int n_
 // W[K,N]).  Each CTA pair fetches its B tiles straight from the owning rank — whole-tile TMA boxes inside a slice,
 // 32-row boxes where a tile straddles two slices — so no gathered copy of W exists.  epi: EPI_BF16, EPI_GELU_DUAL,
 // EPI_RESID_F32 (b_mn = 0) or EPI_BF16, EPI_DGELU (b_mn = 1).
-// With `stage` (a [rows of W, ldb] bf16 matrix of this rank), `flags` (2 + rows / 64 ints) and `my_rank`, extra
+// With `stage` (a [rows of W, ldb] bf16 matrix of this rank), `flags` (64 + rows / 8 ints) and `my_rank`, extra
 // warps of the same kernel copy the remote slices into `stage` once, while the tiles on my_rank's own slice run,
 // and the other tiles read the staged copy: every weight byte crosses the link once.  Slices must then be cut on
 // multiples of 128 rows (64 for b_mn = 1), and launches that share `stage`/`flags` be ordered on one stream.

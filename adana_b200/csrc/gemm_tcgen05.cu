@@ -518,13 +518,21 @@ constexpr int MAX_SHARDS = 8;
 constexpr int GATHER_COPY_WARPS = 8;
 constexpr int GATHER_THREADS = GEMM_THREADS + 32 * GATHER_COPY_WARPS;
 constexpr int STAGE_UNIT_ROWS = 4;
+// Counter layout (ints).  The ticket counter takes an atomic per unit from a thousand warps and the producers poll
+// the others, so each of the first two sits on a 128-byte line of its own and the chunk counters are spread one per
+// 32-byte sector: polling one chunk does not queue behind the ticket atomics.
+constexpr int FLAG_TICKET = 0;
+constexpr int FLAG_DONE = 32;
+constexpr int FLAG_CHUNK0 = 64;
+constexpr int FLAG_CHUNK_STRIDE = 8;
+__host__ __device__ constexpr int stage_flag_ints(int nchunks) { return FLAG_CHUNK0 + FLAG_CHUNK_STRIDE * nchunks; }
 struct ShardedB {
   CUtensorMap map[MAX_SHARDS];       // 32-row boxes: used where a tile straddles two ranks' slices
   CUtensorMap map_big[MAX_SHARDS];   // whole-tile boxes (128 rows K-major / 64 rows MN-major) for the common case
   CUtensorMap map_stage;             // whole-tile boxes over the staging matrix (rows by their global index)
   const void* ptr[MAX_SHARDS];       // base address of each rank's slice
   void* stage;                 // staging matrix [rows_total, pitch] of this rank
-  int* flags;                  // [0] next unit ticket, [1] units finished, [2 + c] units finished of chunk c
+  int* flags;                  // counters, see FLAG_* (ticket, units finished, units finished of chunk c)
   long long pitch_bytes;       // row pitch of the slices and of the staging matrix
   int row_bytes;               // bytes of one weight row (a multiple of 16)
   int rows_total;
@@ -572,19 +580,20 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
 
 // Producer side of the staged variant: has chunk `c` of the staging matrix been filled?  `all_ready` caches the
 // answer "every unit is done", after which no counter is read any more.  Bounded like every other wait here.
-__device__ __forceinline__ bool stage_wait(const ShardedB* sh, int c, bool& all_ready, volatile int* abort_flag,
-                                           int* status) {
+__device__ __forceinline__ bool stage_wait(const ShardedB* sh, int c, bool& all_ready, bool check_all,
+                                           volatile int* abort_flag, int* status) {
   if (all_ready) return true;
-  if (ld_acquire_gpu(sh->flags + 1) >= sh->total_units()) {
+  if (check_all && ld_acquire_gpu(sh->flags + FLAG_DONE) >= sh->total_units()) {
     all_ready = true;
-    fence_proxy_async_all();
     return true;
   }
   const int target = sh->units_of_chunk(c);
-  const int* f = sh->flags + 2 + c;
+  const int* f = sh->flags + FLAG_CHUNK0 + FLAG_CHUNK_STRIDE * c;
+  if (ld_acquire_gpu(f) >= target) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (ld_acquire_gpu(f) < target) {
+    __nanosleep(200);  // the copier warps need the memory pipes more than this poll does
     if (((++spins) & 0x3fu) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > ADANA_WAIT_TIMEOUT_NS) {
@@ -594,7 +603,6 @@ __device__ __forceinline__ bool stage_wait(const ShardedB* sh, int c, bool& all_
       }
     }
   }
-  fence_proxy_async_all();  // the chunk was written through the generic proxy; TMA reads it through the async one
   return true;
 }
 
@@ -617,11 +625,11 @@ __device__ __forceinline__ void stage_copy_loop(const ShardedB* sh, int lane) {
   const int nv = sh->row_bytes >> 4;
   const bool dense = sh->pitch_bytes == (long long)sh->row_bytes;
   int u = 0;
-  if (lane == 0) u = atomicAdd(sh->flags, 1);
+  if (lane == 0) u = atomicAdd(sh->flags + FLAG_TICKET, 1);
   u = __shfl_sync(0xffffffffu, u, 0);
   while (u < total) {
     int next = 0;
-    if (lane == 0) next = atomicAdd(sh->flags, 1);  // the next ticket is on its way while this unit is copied
+    if (lane == 0) next = atomicAdd(sh->flags + FLAG_TICKET, 1);  // the next ticket is on its way while this unit is copied
     int row = u * STAGE_UNIT_ROWS + sh->rot_row;
     if (row >= sh->rows_total) row -= sh->rows_total;
     const int rows = min(STAGE_UNIT_ROWS, sh->rows_total - row);
@@ -640,10 +648,10 @@ __device__ __forceinline__ void stage_copy_loop(const ShardedB* sh, int lane) {
       __syncwarp();
       if (lane == 0) {
         __threadfence();
-        red_release_gpu_add(sh->flags + 2 + row / sh->chunk_rows, 1);
+        red_release_gpu_add(sh->flags + FLAG_CHUNK0 + FLAG_CHUNK_STRIDE * (row / sh->chunk_rows), 1);
       }
     }
-    if (lane == 0) red_release_gpu_add(sh->flags + 1, 1);
+    if (lane == 0) red_release_gpu_add(sh->flags + FLAG_DONE, 1);
     u = __shfl_sync(0xffffffffu, next, 0);
   }
 }
@@ -706,13 +714,28 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       bool ok = true;
       PairWork w(pair, npairs, num_tiles, num_kb, args.streamk);
       bool all_ready = false;  // staged variant: every remote chunk is known to be in the staging matrix
+      // staged variant: what the k-loop needs of the slice table, read once (the copies and waits below are
+      // volatile, so nothing read through `shards` inside the loops would stay in a register)
+      int loc_lo = 0, loc_hi = 0, st_rot = 0, st_rows = 0, st_chunk = 1;
+      const CUtensorMap* map_local = &tmB;
+      const CUtensorMap* map_staged = &tmB;
+      if constexpr (SHARDED == 2) {
+        const int me = shards->me;
+        loc_lo = shards->start[me];
+        loc_hi = shards->start[me + 1];
+        st_rot = shards->rot_tile;
+        st_rows = shards->rows_total;
+        st_chunk = shards->chunk_rows;
+        map_local = &shards->map_big[me];
+        map_staged = &shards->map_stage;
+      }
       while (ok && w.next()) {
         int mi, ni;
         tile_coords(w.tile, args.tiles_m, args.tiles_n, args.group_m, mi, ni);
         mi += args.rot_m;
         if (mi >= args.tiles_m) mi -= args.tiles_m;
         if constexpr (SHARDED == 2 && !B_MN) {  // tiles on this rank's own slice first
-          ni += shards->rot_tile;
+          ni += st_rot;
           if (ni >= args.tiles_n) ni -= args.tiles_n;
         }
         const int m0 = mi * P_BM + (int)rank * 128;  // this CTA's rows of A and of the output
@@ -721,9 +744,9 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
         const int nb0 = GATED_FWD ? (leader ? n0 : args.b_off2 + n0) : n0 + (int)rank * 128;
         bool b_staged = false;  // staged variant, weight rows = output columns: one owner per tile half
         if constexpr (SHARDED == 2 && !B_MN) {
-          b_staged = nb0 >= shards->rows_total || shards->owner_of(nb0) != shards->me;
-          if (b_staged && nb0 < shards->rows_total &&
-              !stage_wait(shards, nb0 / shards->chunk_rows, all_ready, abort_flag, args.status)) {
+          b_staged = nb0 < loc_lo || nb0 >= loc_hi;
+          if (b_staged && nb0 < st_rows &&
+              !stage_wait(shards, nb0 / st_chunk, all_ready, true, abort_flag, args.status)) {
             ok = false;
             break;
           }
@@ -731,12 +754,12 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           int kbr = kb;
           if constexpr (SHARDED == 2 && B_MN) {  // the k-loop starts on this rank's own slice
-            kbr += shards->rot_tile;
+            kbr += st_rot;
             if (kbr >= num_kb) kbr -= num_kb;
             const int kr = kbr * BK;
-            b_staged = kr >= shards->rows_total || shards->owner_of(kr) != shards->me;
-            if (b_staged && kr < shards->rows_total &&
-                !stage_wait(shards, kbr, all_ready, abort_flag, args.status)) {
+            b_staged = kr < loc_lo || kr >= loc_hi;
+            if (b_staged && kr < st_rows &&
+                !stage_wait(shards, kbr, all_ready, ((kb - w.kb0) & 7) == 0, abort_flag, args.status)) {
               ok = false;
               break;
             }
@@ -760,17 +783,13 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
           }
           if constexpr (SHARDED == 2) {
             // slices are cut on whole chunks here: the local slice is read in place, the rest from staging
-            const int me = shards->me;
+            const CUtensorMap* mp = b_staged ? map_staged : map_local;
+            const int off = b_staged ? 0 : loc_lo;
             if constexpr (!B_MN) {
-              if (b_staged) tma_load_2d_pair(sB, &shards->map_stage, bar, k0, nb0);
-              else tma_load_2d_pair(sB, &shards->map_big[me], bar, k0, nb0 - shards->start[me]);
+              tma_load_2d_pair(sB, mp, bar, k0, nb0 - off);
             } else {
 #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                if (b_staged) tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_stage, bar, nb0 + c * 64, k0);
-                else tma_load_2d_pair(sB + c * CHUNK_BYTES, &shards->map_big[me], bar, nb0 + c * 64,
-                                      k0 - shards->start[me]);
-              }
+              for (int c = 0; c < 2; ++c) tma_load_2d_pair(sB + c * CHUNK_BYTES, mp, bar, nb0 + c * 64, k0 - off);
             }
           } else if constexpr (SHARDED == 1) {
             if constexpr (!B_MN) {
@@ -1034,7 +1053,7 @@ static int launch_gemm_gather_impl(const CUtensorMap& tmA, const ShardedB& shard
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   if (STAGED) {
     const int nchunks = (shards.rows_total + shards.chunk_rows - 1) / shards.chunk_rows;
-    cudaError_t e = cudaMemsetAsync(shards.flags, 0, sizeof(int) * (2 + nchunks), stream);
+    cudaError_t e = cudaMemsetAsync(shards.flags, 0, sizeof(int) * stage_flag_ints(nchunks), stream);
     if (e != cudaSuccess) return (int)e;
   }
   kern<<<2 * pairs, threads, P_SMEM, stream>>>(tmA, shards, args);
@@ -1203,7 +1222,7 @@ extern "C" int adana_gemm_bf16_reduce_scatter(const void* A, const void* B, void
 // memory or a peer's) with row pitch ldb; every start is a multiple of 32.  row_starts == nullptr: equal slices
 // of rows_per_shard rows.  Slices cut on multiples of 128 rows (64 for b_mn = 1) are fetched with whole-tile boxes
 // only.  stage == nullptr: every B box is fetched from its owner each time it is used, nothing is staged.
-// stage != nullptr (a [rows of W, ldb] bf16 matrix of this rank) with flags (2 + rows / 64 ints) and my_rank: the
+// stage != nullptr (a [rows of W, ldb] bf16 matrix of this rank) with flags (64 + rows / 8 ints) and my_rank: the
 // remote slices are copied into `stage` once, inside the same kernel, while the tiles on my_rank's own slice run;
 // needs every slice cut on multiples of 128 rows (64 for b_mn = 1).  Launches that share `stage` and `flags` must
 // be ordered on one stream.

@@ -298,7 +298,7 @@ def _stage_workspace(device, nbytes: int):
     ws = _stage_ws.get(key)
     if ws is None or ws[0].numel() < nbytes:
         ws = (torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device),
-              torch.zeros(4096, dtype=torch.int32, device=device))
+              torch.zeros(64 + 8 * 4096, dtype=torch.int32, device=device))
         _stage_ws[key] = ws
     return ws
 
