@@ -262,8 +262,10 @@ def linear_wgrad(dy, x, out=None, accumulate=False, alpha=1.0):
 
 
 # ----------------------------------------------------------------------------------------------
-# All-gather fused into the GEMM: the weight is row-sharded over ranks and every CTA pair fetches its
-# B tiles straight from the owning rank (local or peer memory) — no gathered copy of the weight.
+# All-gather fused into the GEMM: the weight is row-sharded over ranks.  Tall inputs use the staged kernel (copier
+# warps of the GEMM bring each remote slice over the link once into a staging matrix while the tiles of the local
+# slice run); short inputs fetch every B tile straight from its owner.  Also here: the row-parallel GEMM with the
+# reduce-scatter of its partial products.
 # ----------------------------------------------------------------------------------------------
 def _ptr_array(shards):
     """list of tensors / ints, or a ready ctypes array -> (c_uint64 array, count)."""
