@@ -3,9 +3,9 @@
 same token batches and the same optimizer settings, trained once with this framework (kernel engine, bf16 compute,
 fp32 master weights, fused Dana-Star-MK4) and once with the reference's own model / optimizer classes (bf16 autocast).
 
-    python benchmarks/loss_parity.py --arm ours      --steps 1000 --out gpurun_out/parity_ours.json
-    python benchmarks/loss_parity.py --arm reference --steps 1000 --out gpurun_out/parity_ref.json
-    python benchmarks/loss_parity.py --compare gpurun_out/parity_ours.json gpurun_out/parity_ref.json
+    python benchmarks/loss_parity.py --arm ours      --steps 1000 --out out/parity_ours.json
+    python benchmarks/loss_parity.py --arm reference --steps 1000 --out out/parity_ref.json
+    python benchmarks/loss_parity.py --compare out/parity_ours.json out/parity_ref.json
 
 The reference arm imports the unmodified reference from baseline/_ref/src (tiktoken stubbed: no network).
 """
