@@ -6,7 +6,9 @@
 Same command line and checkpoint discovery as the reference's `inference.py` (1-463): the experiment
 directory's `summary.json` supplies the model arguments, `ckpts/latest/main.pt` (or `main.pt` / `ckpt.pt`)
 the weights, key prefixes from DDP (`module.`) and compiled models (`_orig_mod.`) are stripped, and
-without `--prompt` the tool drops into an interactive loop.
+without `--prompt` the tool drops into an interactive loop.  A checkpoint of an FSDP run, which has no `main.pt`,
+is read too: its `sharded/layout.json` + `rank*.pt` files are reassembled into full tensors without a process group
+(`train/checkpoint.py::full_state_from_sharded`); the reference's tool reads DDP/single checkpoints only.
 
 The decode loop is new: the reference re-runs the whole context through the network for every new token
 (models/base.py generate: O(T²) per sequence).  `KVDecoder` keeps per-layer key/value caches for the RoPE
@@ -28,8 +30,15 @@ import torch.nn.functional as F
 from .models.enoki import apply_rotary_emb
 
 
+def _sharded_marker(ckpt_dir: Path):
+    """The `sharded/layout.json` of a checkpoint directory written by an FSDP run, or None."""
+    f = ckpt_dir / "sharded" / "layout.json"
+    return f if f.exists() else None
+
+
 def find_checkpoint_file(path):
-    """-> (checkpoint file, experiment directory) for a file, an exp dir, `ckpts/` or `ckpts/<name>/`."""
+    """-> (checkpoint file, experiment directory) for a file, an exp dir, `ckpts/` or `ckpts/<name>/`.  For a
+    checkpoint of an FSDP run (no `main.pt`) the file returned is its `sharded/layout.json`."""
     p = Path(path)
     if p.is_file() and p.suffix == ".pt":
         exp = p.parent.parent.parent if p.parent.parent.name == "ckpts" else p.parent
@@ -42,6 +51,9 @@ def find_checkpoint_file(path):
         for cand in (p / "ckpts" / "latest" / "main.pt", p / "main.pt", p / "ckpt.pt"):
             if cand.exists():
                 return cand, p
+        for d, exp in ((p / "ckpts" / "latest", p), (p / "latest", p.parent), (p, p.parent.parent)):
+            if _sharded_marker(d) is not None:
+                return _sharded_marker(d), exp
     tried = [str(p / "ckpts" / "latest" / "main.pt"), str(p / "main.pt"), str(p / "ckpt.pt")]
     raise FileNotFoundError("could not find a checkpoint file; tried:\n  " + "\n  ".join(tried))
 
@@ -73,7 +85,15 @@ def load_model(path, device="cpu"):
     cfg.device = device
     cfg.dropout = 0.0
     model = get_model(cfg)
-    blob = torch.load(ckpt, map_location="cpu", weights_only=False)
+    if ckpt.name == "layout.json":      # sharded checkpoint of an FSDP run: reassemble the full tensors
+        from .train.checkpoint import full_state_from_sharded
+
+        blob = {"model": full_state_from_sharded(ckpt.parent)}
+        meta = ckpt.parent.parent / "meta.pt"
+        if meta.exists():
+            blob["itr"] = torch.load(meta, map_location="cpu", weights_only=False).get("itr")
+    else:
+        blob = torch.load(ckpt, map_location="cpu", weights_only=False)
     state = strip_prefixes(blob["model"] if "model" in blob else blob)
     missing, unexpected = model.load_state_dict(state, strict=False)
     if missing:

@@ -260,6 +260,35 @@ def _load_sharded(eng, opt, sharded_dir: Path):
     eng.refresh_from_master()
 
 
+def full_state_from_sharded(sharded_dir: Path, which: str = "master") -> Dict[str, torch.Tensor]:
+    """Reassemble the full fp32 tensors (`which`: master | m | v | tau) of a sharded checkpoint without an engine or a
+    process group: name -> tensor, from `layout.json` and the `rank*.pt` files of any world size.  What inference
+    and single-file export need from an FSDP run (the reference's inference reads DDP/single checkpoints only,
+    inference.py:165-191)."""
+    sharded_dir = Path(sharded_dir)
+    layout = json.loads((sharded_dir / "layout.json").read_text())
+    world = layout["world"]
+    files = [_load(sharded_dir / f"rank{r:05d}.pt") for r in range(world)]
+    out: Dict[str, torch.Tensor] = {}
+    for lu in layout["units"]:
+        parts = []
+        for r in range(world):
+            entry = files[r]["units"][lu["name"]]
+            if which not in entry:
+                parts = None
+                break
+            parts.append(entry[which].reshape(-1).float())
+        if parts is None:
+            continue
+        flat = torch.cat(parts)[:lu["numel"]]
+        for sl in lu["slots"]:
+            n = 1
+            for d in sl["shape"]:
+                n *= d
+            out[sl["name"]] = flat[sl["offset"]:sl["offset"] + n].view(sl["shape"]).clone()
+    return out
+
+
 def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_backend=None) -> int:
     """Restores model, optimizer and scheduler; returns the iteration stored in the checkpoint."""
     ckpt_path = Path(ckpt_path)

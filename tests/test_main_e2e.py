@@ -94,6 +94,21 @@ def test_two_rank_fsdp_cli_run_writes_sharded_checkpoint_and_resumes(tmp_path):
     iters = [r["iter"] for r in rows if "train/loss" in r]
     assert iters == sorted(set(iters)) and iters[-1] == 8                     # no iteration logged twice
     assert json.loads((exp / "summary.json").read_text())["args"]["distributed_backend"] == "fsdp"
+    # the sharded checkpoint can be read without an engine or a process group: inference loads it
+    from adana_b200 import inference
+    from adana_b200.train.checkpoint import full_state_from_sharded
+
+    full = full_state_from_sharded(exp / "ckpts" / "latest" / "sharded")
+    model = inference.load_model(exp)
+    params = dict(model.named_parameters())
+    assert set(full) == set(params)
+    for k, v in full.items():
+        assert v.shape == params[k].shape and torch.isfinite(v).all()
+        assert torch.equal(v, params[k].detach().float())
+    moments = full_state_from_sharded(exp / "ckpts" / "latest" / "sharded", "v")
+    assert set(moments) == set(full) and all((t >= 0).all() for t in moments.values())
+    toks = list(inference.generate_tokens(model, torch.tensor([[1, 2, 3]]), 4, temperature=0.0))
+    assert len(toks) == 4 and all(t.shape == (1, 1) for t in toks)
 
 
 @pytest.mark.timeout(600)
