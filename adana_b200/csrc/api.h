@@ -50,6 +50,15 @@ int adana_sum_slots_bf16(const void* slots, int n_slots, int rows, int N, long l
 int adana_p2p_reduce_scatter_bf16(const unsigned long long* partial_ptrs, int n_ranks, long long first_row, int rows,
                                   int N, long long ld, float* out, long long ld_out, const float* resid,
                                   long long ld_resid, void* out_bf16, long long ld_out16, void* stream);
+// Variable-size all-to-all of rows over peer memory, pull style (expert-parallel dispatch / combine): every rank has
+// published a row buffer sorted by destination (buf_ptrs[p]) and an int32 table (tab_ptrs[p]) of 2 * world +
+// world * segs_per_rank entries: first row and row count of the group held for each rank, then the row counts of the
+// segments inside the groups, destination rank major; rank `me` copies the rows every peer holds for it, peers in rank order, into
+// `out` (nullptr: counts only) and the peers' counts for it into out_counts [world * segs_per_rank].  More than
+// max_rows_out rows: the copy is clamped and *status set.  Call between two barriers over the ranks.
+int adana_p2p_all_to_all_pull(const unsigned long long* buf_ptrs, const unsigned long long* tab_ptrs, int me,
+                              int world, int segs_per_rank, long long row_bytes, void* out, long long max_rows_out,
+                              int* out_counts, int* status, void* stream);
 
 // All-gather fused into the GEMM.  The weight W is split by rows over `n_shards` ranks: rank r holds rows
 // [row_starts[r], row_starts[r+1]) (multiples of 32; nullptr = equal slices of rows_per_shard rows) at B_shards[r]

@@ -259,6 +259,71 @@ sum_slots_bf16_kernel(const SlotPtrs slots, int n_slots, int rows, int N, long l
   }
 }
 
+// Variable-size all-to-all of rows over peer memory, pull style (expert-parallel dispatch and combine).
+// Every rank publishes, in memory its peers can read, a buffer of rows sorted by destination and an int32 table
+// [2 * world + world * segs_per_rank]: first row and number of rows of the group it holds for each rank, then the
+// row counts of the segments inside the groups (destination rank major: for MoE, one count per routed expert).
+// After a barrier over the ranks, rank `me` copies from every peer p the group p holds for it.
+// The output holds the peers' segments in rank order; out_counts[p * segs_per_rank + j] receives peer p's counts
+// for this rank (what an all-to-all of the count table would deliver).  One warp per row, 16-byte lanes: every
+// access over NVLink is a coalesced 512-byte line.  With out == nullptr only the counts are produced.
+constexpr int A2A_MAX_SEG = 2048;  // world * segs_per_rank the shared-memory table can hold
+struct A2APeers {
+  const uint4* buf[MAX_RANKS];
+  const int* tab[MAX_RANKS];
+};
+__global__ void __launch_bounds__(256)
+p2p_all_to_all_pull_kernel(A2APeers peers, int me, int world, int segs_per_rank, int vec_per_row,
+                           uint4* __restrict__ out, long long max_rows_out, int* __restrict__ out_counts,
+                           int* status) {
+  __shared__ int s_off[MAX_RANKS], s_cnt[MAX_RANKS], s_start[MAX_RANKS + 1];
+  const int n_seg = world * segs_per_rank;
+  if (threadIdx.x < world) {
+    const int p = threadIdx.x;
+    s_off[p] = peers.tab[p][me];
+    s_cnt[p] = peers.tab[p][world + me];
+  }
+  if (blockIdx.x == 0 && out_counts) {
+    for (int i = threadIdx.x; i < n_seg; i += blockDim.x) {
+      const int p = i / segs_per_rank, j = i - p * segs_per_rank;
+      out_counts[i] = peers.tab[p][2 * world + me * segs_per_rank + j];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int p = 0; p < world; ++p) {
+      s_start[p] = acc;
+      acc += s_cnt[p];
+    }
+    s_start[world] = acc;
+    if (out && acc > max_rows_out && status) atomicCAS(status, 0, (int)ST_BAD_ARGUMENT);
+  }
+  __syncthreads();
+  if (!out) return;
+  long long total = s_start[world];
+  if (total > max_rows_out) total = max_rows_out;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long row = warp0; row < total; row += n_warps) {
+    int p = 0;
+#pragma unroll
+    for (int q = 1; q < MAX_RANKS; ++q) p += (q < world && row >= s_start[q]) ? 1 : 0;
+    const uint4* src = peers.buf[p] + ((long long)s_off[p] + (row - s_start[p])) * vec_per_row;
+    uint4* dst = out + row * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 4 * 32) {
+      uint4 t[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (v + j * 32 < vec_per_row) t[j] = src[v + j * 32];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (v + j * 32 < vec_per_row) dst[v + j * 32] = t[j];
+    }
+  }
+}
+
 }  // namespace adana
 
 using namespace adana;
@@ -373,5 +438,27 @@ extern "C" int adana_p2p_reduce_scatter_bf16(const unsigned long long* partial_p
   if (blocks > 148 * 8) blocks = 148 * 8;
   sum_slots_bf16_kernel<<<(int)blocks, 256, 0, st>>>(sp, n_ranks, rows, N, ld, out, ld_out, resid, ld_resid,
                                                      (__nv_bfloat16*)out_bf16, ld_out16);
+  return (int)cudaGetLastError();
+}
+
+// See p2p_all_to_all_pull_kernel.  buf_ptrs[p] / tab_ptrs[p]: peer p's row buffer (row_bytes per row, a multiple of
+// 16) and its int32 count table; out may be nullptr (counts only).  Call between two barriers over the ranks.
+extern "C" int adana_p2p_all_to_all_pull(const unsigned long long* buf_ptrs, const unsigned long long* tab_ptrs,
+                                         int me, int world, int segs_per_rank, long long row_bytes, void* out,
+                                         long long max_rows_out, int* out_counts, int* status, void* stream_) {
+  if (world < 1 || world > MAX_RANKS || me < 0 || me >= world || segs_per_rank < 1) return -1;
+  if (world * segs_per_rank > A2A_MAX_SEG || (row_bytes % 16) != 0 || row_bytes <= 0) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  A2APeers peers;
+  for (int p = 0; p < MAX_RANKS; ++p) {
+    peers.buf[p] = reinterpret_cast<const uint4*>(buf_ptrs[p < world ? p : 0]);
+    peers.tab[p] = reinterpret_cast<const int*>(tab_ptrs[p < world ? p : 0]);
+  }
+  long long blocks = out ? (max_rows_out + 7) / 8 : 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  p2p_all_to_all_pull_kernel<<<(int)blocks, 256, 0, st>>>(peers, me, world, segs_per_rank, (int)(row_bytes / 16),
+                                                          reinterpret_cast<uint4*>(out), max_rows_out, out_counts,
+                                                          status);
   return (int)cudaGetLastError();
 }

@@ -48,6 +48,7 @@ def _declare(lib):
         "adana_gemm_set_mode": [I],
         "adana_gemm_bf16_reduce_scatter": [P, P, P, I, I, I, I, I, I, L, L, L, F, I, P, P],
         "adana_sum_slots_bf16": [P, I, I, I, L, P, L, P, L, P, L, P],
+        "adana_p2p_all_to_all_pull": [P, P, I, I, I, L, P, L, P, P, P],
         "adana_p2p_reduce_scatter_bf16": [P, I, L, I, I, L, P, L, P, L, P, L, P],
         "adana_gemm_bf16_gather": [P, P, I, I, P, P, I, I, I, L, L, L, I, I, P, L, P, L, F, I, P, P, P, P],
         "adana_norm_fwd": [P, I, P, P, I, P, P, I, I, F, I, P],

@@ -9,6 +9,11 @@ swapped), so expert and router gradients flow across ranks — the reference's v
 per layer and plain c10d calls that cut the graph.  `capacity_factor` is accepted for compatibility;
 when set > 0 tokens beyond `ceil(cf * T * k / E)` per expert are dropped like upstream.
 On Gloo (CPU tests) the exchange falls back to all-gather + select.
+
+On B200s of one node the two exchanges run over the peer-memory plane instead of NCCL (`P2PAllToAll`,
+csrc/comm_p2p.cu: every rank publishes its sorted rows and its count table in symmetric memory and the receivers pull
+their groups over NVLink), which also delivers the counts, so the separate count all-to-all disappears.  The ranks
+agree on the path once, at the first forward; `ADANA_EP_COMM=nccl` keeps NCCL.
 """
 from __future__ import annotations
 
@@ -57,6 +62,22 @@ class _AllToAll(torch.autograd.Function):
         return _all_to_all(g.contiguous(), ctx.in_splits, ctx.out_splits, ctx.group), None, None, None
 
 
+class _P2PExchange(torch.autograd.Function):
+    """One `P2PAllToAll.exchange`; its backward is the reverse exchange with the received counts as the table."""
+
+    @staticmethod
+    def forward(ctx, x, seg_counts, a2a, expect_rows):
+        out, recv_counts = a2a.exchange(x.contiguous(), seg_counts, expect_rows)
+        ctx.a2a, ctx.recv_counts, ctx.n_in = a2a, recv_counts, x.shape[0]
+        ctx.mark_non_differentiable(recv_counts)
+        return out, recv_counts
+
+    @staticmethod
+    def backward(ctx, g, _):
+        back, _ = ctx.a2a.exchange(g.contiguous(), ctx.recv_counts, ctx.n_in)
+        return back, None, None, None
+
+
 class ExpertParallelMoE(nn.Module):
     def __init__(self, config, mlp, group=None):
         super().__init__()
@@ -73,6 +94,46 @@ class ExpertParallelMoE(nn.Module):
         self.top_k = config.moe_num_experts_per_tok
         self.softmax_order = config.moe_softmax_order
         self.capacity_factor = float(getattr(config, "moe_expert_capacity_factor", 0.0) or 0.0)
+        self._a2a = {}            # (dtype, width) -> P2PAllToAll, or None once the ranks settled on NCCL
+        self._p2p_ok = None
+
+    def _p2p_exchange(self, x, rows_per_call: int):
+        """The peer-memory exchange for rows like `x`, created on first use; None where NCCL is to be used.  Every
+        rank must take the same path, so the outcome of the set-up is agreed with one all-reduce."""
+        import os
+
+        if self._p2p_ok is False or self.world <= 1:
+            return None
+        key = (x.dtype, x.shape[1])
+        if key in self._a2a:
+            return self._a2a[key]
+        ok, a2a = 0, None
+        try:
+            from ..ops import _lib
+            from .p2p import P2PAllToAll, P2PPlane
+
+            usable = (x.is_cuda and _lib.available() and self.world <= 8 and dist.get_backend(self.group) == "nccl"
+                      and os.environ.get("ADANA_EP_COMM", "p2p") != "nccl" and (x.shape[1] * x.element_size()) % 16 == 0
+                      and _lib.has("adana_p2p_all_to_all_pull"))
+            if usable:
+                # worst case every token of every rank comes here; cap the buffer at 2 GiB
+                per_row = x.shape[1] * x.element_size()
+                mult = max(1, min(self.world, (2 << 30) // max(1, rows_per_call * per_row)))
+                max_rows = rows_per_call * mult
+                plane = P2PPlane.create(P2PAllToAll.arena_bytes(max_rows, x.shape[1], x.dtype, self.world, self.per_rank),
+                                        x.device, group=self.group)
+                a2a = P2PAllToAll(plane, max_rows, x.shape[1], x.dtype, self.per_rank)
+                ok = 1
+        except Exception:      # no symmetric memory here: all ranks fall back together below
+            ok, a2a = 0, None
+        flag = torch.tensor([ok], device=x.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self._p2p_ok, a2a = False, None
+        else:
+            self._p2p_ok = True
+        self._a2a[key] = a2a
+        return a2a
 
     def forward(self, inputs):
         x = inputs.view(-1, inputs.shape[-1])
@@ -90,6 +151,9 @@ class ExpertParallelMoE(nn.Module):
         tok = order // k
         sorted_e = flat_e[order]
         send_counts = torch.bincount(sorted_e, minlength=self.n_routed)
+        a2a = self._p2p_exchange(x, T * k) if self.world > 1 else None
+        if a2a is not None:
+            return self._forward_p2p(inputs, x, logits, weights, selected, order, tok, send_counts, a2a)
         if self.world > 1:
             recv_counts = torch.empty_like(send_counts)
             dist.all_to_all_single(recv_counts, send_counts, group=self.group) if dist.get_backend(self.group) != "gloo" \
@@ -101,7 +165,13 @@ class ExpertParallelMoE(nn.Module):
         out_splits = recv_counts.view(self.world, self.per_rank).sum(1).tolist()
         xs = x[tok]
         recv = _AllToAll.apply(xs, out_splits, in_splits, self.group) if self.world > 1 else xs
-        # rows arrive grouped by source rank, then by local expert: run each expert on its rows
+        y = self._run_experts(recv, recv_counts)
+        back = _AllToAll.apply(y, in_splits, out_splits, self.group) if self.world > 1 else y
+        return self._combine(inputs, x, logits, weights, selected, order, tok, back)
+
+    def _run_experts(self, recv, recv_counts):
+        """Rows arrive grouped by source rank, then by local expert: run each expert on its rows."""
+        x = recv
         per_src = recv_counts.view(self.world, self.per_rank).tolist()
         y = torch.empty_like(recv)
         pos = 0
@@ -118,7 +188,15 @@ class ExpertParallelMoE(nn.Module):
             idx = torch.cat([torch.arange(s, s + n, device=x.device) for s, n in segs])
             out_e, _ = self.experts[e](recv[idx])
             y = y.index_copy(0, idx, out_e.to(y.dtype))
-        back = _AllToAll.apply(y, in_splits, out_splits, self.group) if self.world > 1 else y
+        return y
+
+    def _forward_p2p(self, inputs, x, logits, weights, selected, order, tok, send_counts, a2a):
+        recv, recv_counts = _P2PExchange.apply(x[tok], send_counts, a2a, None)
+        y = self._run_experts(recv, recv_counts)
+        back, _ = _P2PExchange.apply(y, recv_counts, a2a, tok.numel())
+        return self._combine(inputs, x, logits, weights, selected, order, tok, back)
+
+    def _combine(self, inputs, x, logits, weights, selected, order, tok, back):
         w = weights.reshape(-1)[order].to(x.dtype)
         out = torch.zeros_like(x).index_add(0, tok, back * w[:, None])
         for e in self.shared:

@@ -131,3 +131,70 @@ class P2PPlane:
         rc = _lib.lib().adana_p2p_push_f32(src.data_ptr(), self.peer_ptrs(dst_full), self.world, dst_off, src.numel(),
                                            _lib.stream_ptr())
         _lib.check_rc(rc, "adana_p2p_push_f32")
+
+
+class P2PAllToAll:
+    """Variable-size all-to-all of rows over the peer-memory plane, pull style (csrc/comm_p2p.cu:
+    p2p_all_to_all_pull_kernel): the dispatch and combine exchanges of expert parallelism without NCCL.
+
+    Every rank `publish`es its rows, sorted by destination, and a table of `world * segs_per_rank` row counts
+    (destination rank major; for MoE one count per routed expert) in its arena; after a plane barrier `collect`
+    copies the groups the peers hold for this rank, peers in rank order, with coalesced 16-byte loads over NVLink,
+    and returns them with the peers' counts for this rank (what an all-to-all of the count table would deliver).
+    `exchange` = barrier, publish, barrier, collect.  The reverse exchange (gradients, or the combine step) is the
+    same call with the received counts as the table: its result comes back in the original send order.
+    Replaces the padded-capacity all-to-alls of the reference (src/models/moe_expert_parallel.py:283-321)."""
+
+    def __init__(self, plane: P2PPlane, max_rows: int, row_elems: int, dtype, segs_per_rank: int):
+        self.plane, self.max_rows, self.d, self.dtype, self.spr = plane, int(max_rows), int(row_elems), dtype, int(segs_per_rank)
+        esize = torch.empty(0, dtype=dtype).element_size()
+        if (row_elems * esize) % 16 != 0:
+            raise ValueError("row size must be a multiple of 16 bytes")
+        self.row_bytes = row_elems * esize
+        w = plane.world
+        self.buf = plane.alloc(self.max_rows * self.d, dtype).view(self.max_rows, self.d)
+        self.tab = plane.alloc(2 * w + w * self.spr, torch.int32)
+        self._buf_ptrs = plane.peer_ptrs(self.buf)
+        self._tab_ptrs = plane.peer_ptrs(self.tab)
+
+    @staticmethod
+    def arena_bytes(max_rows: int, row_elems: int, dtype, world: int, segs_per_rank: int) -> int:
+        esize = torch.empty(0, dtype=dtype).element_size()
+        return max_rows * row_elems * esize + 4 * (2 * world + world * segs_per_rank) + 4 * ALIGN
+
+    def publish(self, rows: torch.Tensor, seg_counts: torch.Tensor):
+        """rows [n, d] sorted by destination; seg_counts [world * segs_per_rank] integer tensor on the device."""
+        n, w = rows.shape[0], self.plane.world
+        if n > self.max_rows:
+            raise RuntimeError(f"P2PAllToAll: {n} rows exceed the buffer of {self.max_rows}")
+        if n:
+            self.buf[:n].copy_(rows)
+        c = seg_counts.to(torch.int32).view(w, self.spr)
+        per_rank = c.sum(1, dtype=torch.int32)
+        first = (torch.cumsum(per_rank, 0) - per_rank).to(torch.int32)
+        self.tab.copy_(torch.cat([first, per_rank, c.reshape(-1)]))
+
+    def collect(self, expect_rows=None):
+        """-> (rows [m, d], counts [world * segs_per_rank] int32).  `expect_rows` (known in the reverse direction)
+        saves the host read of the counts."""
+        lib, w = _lib.lib(), self.plane.world
+        counts = torch.empty(w * self.spr, dtype=torch.int32, device=self.plane.device)
+        status = _lib.status_buffer(self.plane.device).data_ptr()
+        if expect_rows is None or expect_rows == 0:      # counts only (also when nothing is to be copied)
+            _lib.check_rc(lib.adana_p2p_all_to_all_pull(self._buf_ptrs, self._tab_ptrs, self.plane.rank, w, self.spr,
+                                                        self.row_bytes, None, 0, counts.data_ptr(), status,
+                                                        _lib.stream_ptr()), "adana_p2p_all_to_all_pull")
+            if expect_rows is None:
+                expect_rows = int(counts.sum().item())
+        out = torch.empty((expect_rows, self.d), dtype=self.dtype, device=self.plane.device)
+        if expect_rows:
+            _lib.check_rc(lib.adana_p2p_all_to_all_pull(self._buf_ptrs, self._tab_ptrs, self.plane.rank, w, self.spr,
+                                                        self.row_bytes, out.data_ptr(), expect_rows, counts.data_ptr(),
+                                                        status, _lib.stream_ptr()), "adana_p2p_all_to_all_pull")
+        return out, counts
+
+    def exchange(self, rows: torch.Tensor, seg_counts: torch.Tensor, expect_rows=None):
+        self.plane.barrier()          # nobody still reads what I published last time
+        self.publish(rows, seg_counts)
+        self.plane.barrier()          # every rank's rows and table are in place
+        return self.collect(expect_rows)

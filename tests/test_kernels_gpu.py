@@ -395,6 +395,43 @@ def test_attention_jvp_matches_torch_func_jvp(hd, Hq, Hk, S):
     assert rel_err(out, fwd_out) < 1e-2
 
 
+@pytest.mark.parametrize("world,spr,d", [(2, 1, 64), (4, 2, 520), (8, 4, 2048)])
+def test_p2p_all_to_all_pull_over_fake_peers(world, spr, d):
+    """Variable-size all-to-all of rows (expert-parallel dispatch / combine) with every "rank" an arena on this GPU:
+    all ranks publish, then each collects; checked against the permutation built with torch, and the reverse
+    exchange must return every row to where it came from."""
+    from adana_b200.parallel.p2p import P2PAllToAll, P2PPlane
+
+    torch.manual_seed(41)
+    n_seg = world * spr
+    max_rows = 900
+    planes = P2PPlane.fake(P2PAllToAll.arena_bytes(max_rows, d, torch.bfloat16, world, spr), world, DEV)
+    a2a = [P2PAllToAll(pl, max_rows, d, torch.bfloat16, spr) for pl in planes]
+    counts = [torch.randint(0, 40, (n_seg,), device=DEV) for _ in range(world)]
+    counts[0][:spr] = 0                                   # an empty group
+    rows = [rnd(int(c.sum()), d, scale=1.0) for c in counts]
+    for r in range(world):
+        a2a[r].publish(rows[r], counts[r])
+    got = [a2a[r].collect() for r in range(world)]
+    for me in range(world):
+        parts, cexp = [], []
+        for p in range(world):
+            c = counts[p].view(world, spr)
+            start = int(c[:me].sum())
+            parts.append(rows[p][start:start + int(c[me].sum())])
+            cexp.append(c[me])
+        assert torch.equal(got[me][0], torch.cat(parts))
+        assert torch.equal(got[me][1].long(), torch.cat(cexp))
+    # reverse: publish what was received (table = received counts); everything returns in the original order
+    for r in range(world):
+        a2a[r].publish(got[r][0], got[r][1])
+    for r in range(world):
+        back, cback = a2a[r].collect(expect_rows=rows[r].shape[0])
+        assert torch.equal(back, rows[r])
+        assert torch.equal(cback.long(), counts[r])
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("world,M,N,Kl", [(4, 1024, 512, 256), (4, 384, 384, 192), (8, 8192, 2304, 288), (2, 4096, 2304, 1152)])
 def test_gemm_fused_with_reduce_scatter_over_fake_peers(world, M, N, Kl, gemm_mode):
     """Row-parallel linear whose epilogue does the reduce-scatter: every "rank" (here: one launch per rank on this

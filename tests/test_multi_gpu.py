@@ -167,6 +167,63 @@ def _gemm_rs_worker(rank, world):
     return {"errs": errs}
 
 
+def _ep_p2p_worker(rank, world):
+    """Expert-parallel MoE with its dispatch / combine exchanges over the peer-memory plane against the local MoE
+    holding all experts (forward, input gradient, router gradient), and against the NCCL exchange."""
+    import torch.distributed as dist
+    from conftest import tiny_args
+
+    from adana_b200.models.moe import MoE
+    from adana_b200.models.qwen3 import Qwen3MLP
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.expert_parallel import ExpertParallelMoE
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    a = tiny_args("qwen3", moe=True, moe_num_experts=4 * world, moe_num_shared_experts=0, moe_num_experts_per_tok=2,
+                  moe_expert_capacity_factor=0.0, n_embd=128, mlp_hidden_dim=256)
+    torch.manual_seed(0)
+    dense = MoE(a, Qwen3MLP).cuda()                  # same weights on every rank
+    out = {}
+    for comm in ("p2p", "nccl"):
+        os.environ["ADANA_EP_COMM"] = comm
+        torch.manual_seed(1)
+        ep = ExpertParallelMoE(a, Qwen3MLP).cuda()
+        with torch.no_grad():
+            ep.router.weight.copy_(dense.router.weight)
+            for e in range(ep.per_rank):
+                ep.experts[e].load_state_dict(dense.experts[rank * ep.per_rank + e].state_dict())
+        torch.manual_seed(100 + rank)
+        x = torch.randn(4, 64, a.n_embd, device="cuda", requires_grad=True)
+        for _ in range(2):                           # the buffers are reused from call to call
+            x.grad = None
+            ep.zero_grad()
+            y, _ = ep(x)
+            y.sum().backward()
+        g_ep = x.grad.clone()
+        x.grad = None
+        y_ref, _ = dense(x)
+        y_ref.sum().backward()
+        torch.cuda.synchronize()
+        out[comm] = {"err": (y - y_ref).abs().max().item(), "gerr": (g_ep - x.grad).abs().max().item(),
+                     "router_grad": ep.router.weight.grad.abs().sum().item(), "used_p2p": bool(ep._p2p_ok)}
+    _lib.check_status()
+    return out
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_exchanges_over_peer_memory():
+    from test_distributed_cpu import _spawn
+
+    world = min(torch.cuda.device_count(), 8)
+    res = _spawn(_ep_p2p_worker, world)
+    for r in range(world):
+        assert res[r]["p2p"]["used_p2p"] and not res[r]["nccl"]["used_p2p"], res[r]
+        for comm in ("p2p", "nccl"):
+            assert res[r][comm]["err"] < 1e-4 and res[r][comm]["gerr"] < 1e-4 and res[r][comm]["router_grad"] > 0, res[r]
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_gemm_fused_with_reduce_scatter_over_nvlink_peers():
     from test_distributed_cpu import _spawn
