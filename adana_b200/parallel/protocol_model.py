@@ -1,5 +1,6 @@
-"""Host-side model of the peer-memory flag barrier (csrc/comm_p2p.cu::p2p_barrier_kernel) and an exhaustive
-interleaving checker for it.
+"""Host-side models of two device protocols, each with an exhaustive interleaving checker: the peer-memory flag
+barrier (csrc/comm_p2p.cu::p2p_barrier_kernel, `check`) and the ticket / chunk-counter copy protocol of the staged
+gather GEMM (csrc/gemm_tcgen05.cu, `check_staged_gather`).
 
 Protocol: barrier number k (k = 1, 2, ... — sequence numbers only grow) on rank r is a kernel of `world`
 threads; thread t stores k into slot r of rank t's flag array (release, system scope) and then spins until slot t
@@ -70,4 +71,73 @@ def check(world: int = 3, rounds: int = 2, reset_flags: bool = False) -> Tuple[b
                         todo.append(nxt)
         if not moved and any(k <= rounds for k, _, _ in ranks):
             return False, f"stuck: ranks {ranks}, flags {flags}", len(seen)
+    return True, None, len(seen)
+
+
+def check_staged_gather(ctas: int = 2, resident: int = 1, units: int = 4, units_per_chunk: int = 2,
+                        static_assignment: bool = False) -> Tuple[bool, Optional[str], int]:
+    """Model of the staged gather GEMM's copy protocol (csrc/gemm_tcgen05.cu: stage_copy_loop / stage_wait).
+
+    Each CTA has one copier warp and one producer.  A copier repeatedly takes the next unit from a shared ticket
+    counter, copies it and bumps the counter of the unit's chunk; a producer walks over all chunks in order and
+    passes chunk c only when its counter has reached `units_per_chunk`.  A CTA leaves when both are done.  Only
+    `resident` CTAs run at first (the grid may be larger than what fits, or another kernel may hold SMs): a waiting
+    CTA starts when a running one leaves.  Checked over every interleaving:
+
+      safety    a producer never passes a chunk with a unit not yet copied;
+      liveness  no reachable state is stuck before every CTA has left.
+
+    `static_assignment=True` models the variant in which unit u belongs to the copier of CTA u % ctas: a resident
+    producer then waits for a unit owned by a CTA that cannot start, and the checker must report it."""
+    n_chunks = (units + units_per_chunk - 1) // units_per_chunk
+    # per CTA: (running, copier_holding_unit or -1, copier_done, producer_next_chunk, static_next_unit)
+    init_ctas = tuple((i < resident, -1, False, 0, i) for i in range(ctas))
+    init = (0, tuple(0 for _ in range(n_chunks)), frozenset(), init_ctas)   # ticket, chunk counters, copied units, CTAs
+    seen = {init}
+    todo = deque([init])
+    while todo:
+        ticket, counters, copied, cs = todo.popleft()
+        succ = []
+        for i, (run, hold, cdone, pnext, snext) in enumerate(cs):
+            if not run:
+                continue
+            if not cdone:
+                if hold < 0:      # take a unit
+                    if static_assignment:
+                        u, nt, ns = (snext, ticket, snext + ctas)
+                    else:
+                        u, nt, ns = (ticket, ticket + 1, snext)
+                    c2 = list(cs)
+                    c2[i] = (run, u, False, pnext, ns) if u < units else (run, -1, True, pnext, ns)
+                    succ.append((nt, counters, copied, tuple(c2)))
+                else:             # finish the copy of the unit held and count it
+                    cn = list(counters)
+                    cn[hold // units_per_chunk] += 1
+                    c2 = list(cs)
+                    c2[i] = (run, -1, False, pnext, snext)
+                    succ.append((ticket, tuple(cn), copied | {hold}, tuple(c2)))
+            if pnext < n_chunks:
+                need = min(units_per_chunk, units - pnext * units_per_chunk)
+                if counters[pnext] >= need:
+                    for u in range(pnext * units_per_chunk, pnext * units_per_chunk + need):
+                        if u not in copied:
+                            return False, f"producer of CTA {i} passed chunk {pnext} before unit {u} was copied", len(seen)
+                    c2 = list(cs)
+                    c2[i] = (run, hold, cdone, pnext + 1, snext)
+                    succ.append((ticket, counters, copied, tuple(c2)))
+            if cdone and pnext == n_chunks:      # the CTA leaves; a waiting one takes its SM
+                c2 = list(cs)
+                c2[i] = (False, -1, True, n_chunks, snext)
+                for j, (rj, hj, dj, pj, sj) in enumerate(c2):
+                    if not rj and not (dj and pj == n_chunks):
+                        c2[j] = (True, hj, dj, pj, sj)
+                        break
+                succ.append((ticket, counters, copied, tuple(c2)))
+        all_left = all((not run) and cdone and pnext == n_chunks for run, _, cdone, pnext, _ in cs)
+        if not succ and not all_left:
+            return False, f"stuck: ticket {ticket}, counters {counters}, CTAs {cs}", len(seen)
+        for nxt in succ:
+            if nxt not in seen:
+                seen.add(nxt)
+                todo.append(nxt)
     return True, None, len(seen)

@@ -13,3 +13,21 @@ def test_checker_finds_the_bug_of_a_flag_clearing_variant():
     # clearing one's slots after a barrier loses a fast peer's early arrival for the next one: stuck or unsafe
     ok, why, _ = check(world=2, rounds=2, reset_flags=True)
     assert not ok and why
+
+
+def test_staged_gather_ticket_protocol_is_safe_and_live_with_fewer_resident_ctas_than_launched():
+    from adana_b200.parallel.protocol_model import check_staged_gather
+
+    for ctas, resident, units, upc in ((2, 1, 4, 2), (3, 1, 5, 2), (3, 2, 6, 3), (2, 2, 4, 1)):
+        ok, why, n = check_staged_gather(ctas, resident, units, upc)
+        assert ok and n > 20, (ctas, resident, units, upc, why)
+
+
+def test_staged_gather_checker_rejects_units_owned_by_fixed_ctas():
+    from adana_b200.parallel.protocol_model import check_staged_gather
+
+    # with every CTA running the static split is fine; with one waiting for an SM a resident producer waits for ever
+    ok, why, _ = check_staged_gather(2, 2, 4, 2, static_assignment=True)
+    assert ok, why
+    ok, why, _ = check_staged_gather(2, 1, 4, 2, static_assignment=True)
+    assert not ok and "stuck" in why
