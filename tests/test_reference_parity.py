@@ -23,14 +23,15 @@ from adana_b200.optim.logtime import ADana, DanaStarMK4
 from adana_b200.optim.schedule import CosInf
 
 GOLDEN = json.loads((Path(__file__).parent / "golden" / "enoki3_cpu_reference_losses.json").read_text())
+GOLDEN_QWEN3 = json.loads((Path(__file__).parent / "golden" / "qwen3_cpu_reference_losses.json").read_text())
 ITER, WARM, LR, WD_TS = 200, 100, 1e-3, 20
 
 
-def _setup():
+def _setup(model_name="enoki"):
     parser = argparse.ArgumentParser(allow_abbrev=False)
     parser.add_argument("--config_format", default="base")
     args = parse_args_with_format(format="base", base_parser=parser, namespace=None, args=[
-        "--model", "enoki", "--n_layer", "3", "--n_head", "3", "--n_embd", "192", "--qkv_dim", "64",
+        "--model", model_name, "--n_layer", "3", "--n_head", "3", "--n_embd", "192", "--qkv_dim", "64",
         "--mlp_hidden_dim", "768", "--sequence_length", "256", "--batch_size", "8", "--vocab_size", "50304",
         "--dtype", "float32", "--device", "cpu", "--weight_tying", "False", "--dropout", "0.0", "--init-scheme",
         "ScaledGPT", "--z_loss_coeff", "0.0", "--grad_clip", "0.5", "--init_compat", "reference", "--seed", "0"])
@@ -45,8 +46,8 @@ def _setup():
     return args, reader, get_model(args)
 
 
-def _run(opt_name, engine, steps):
-    args, reader, model = _setup()
+def _run(opt_name, engine, steps, model_name="enoki"):
+    args, reader, model = _setup(model_name)
     specs = model.get_parameter_group_specs()
     if engine:
         from adana_b200.runtime.engine import EngineOptimizer, attach
@@ -98,5 +99,18 @@ def test_first_steps_match_the_reference_loss_curve(opt_name, engine):
     got = _run(opt_name, engine, steps)
     want = GOLDEN[opt_name][:steps]
     assert got[0] == pytest.approx(11.124384, abs=2e-5)
+    for s, (a, b) in enumerate(zip(got, want)):
+        assert a == pytest.approx(b, rel=1e-4), (s, a, b)
+
+
+@pytest.mark.parametrize("opt_name,engine", [("adana", False), ("dana-star-mk4", True)])
+def test_qwen3_first_steps_match_the_reference_loss_curve(opt_name, engine):
+    """The same check on the Qwen3 family (RMSNorm, SwiGLU, per-head QK-norm + RoPE): seed-compatible initial
+    weights (first loss 11.374447) and six steps of the reference's curve, through autograd modules and through the
+    kernel engine's own forward/backward and fused optimizer."""
+    steps = 6
+    got = _run(opt_name, engine, steps, "qwen3")
+    want = GOLDEN_QWEN3[opt_name][:steps]
+    assert got[0] == pytest.approx(11.374447, abs=2e-5)
     for s, (a, b) in enumerate(zip(got, want)):
         assert a == pytest.approx(b, rel=1e-4), (s, a, b)
