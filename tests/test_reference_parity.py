@@ -114,3 +114,31 @@ def test_qwen3_first_steps_match_the_reference_loss_curve(opt_name, engine):
     assert got[0] == pytest.approx(11.374447, abs=2e-5)
     for s, (a, b) in enumerate(zip(got, want)):
         assert a == pytest.approx(b, rel=1e-4), (s, a, b)
+
+
+def test_engine_adamw_follows_the_reference_adamw_curve():
+    """The engine's fused AdamW (decoupled weight decay before the update, bias-corrected) on the reference's AdamW
+    baseline of the same configuration: weight decay 4 / (lr * iterations), betas (0.9, 0.999)."""
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    steps = 8
+    args, reader, model = _setup("enoki")
+    specs = model.get_parameter_group_specs()
+    for k, v in dict(opt="adamw", lr=LR, weight_decay=4.0 / (LR * ITER), beta1=0.9, beta2=0.999, wd_decaying=False,
+                     acc_steps=1).items():
+        setattr(args, k, v)
+    eng = attach(model, args, device="cpu")
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = EngineOptimizer(eng, "adamw", args, specs)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, CosInf(ITER, WARM, 1e2, 1e8, 0))
+    model.train()
+    for s in range(steps):
+        x, y = reader.sample_batch()
+        out = model(x, targets=y)
+        out["loss"].backward()
+        eng.grad_norm_and_clip(0.5)
+        opt.step()
+        sched.step()
+        opt.zero_grad(set_to_none=True)
+        assert out["loss"].item() == pytest.approx(GOLDEN["adamw"][s], rel=1e-4), s
