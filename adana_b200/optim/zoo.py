@@ -56,12 +56,14 @@ class Signum(Optimizer):
                     continue
                 d = p.grad
                 p.mul_(1 - g["lr"] * g["weight_decay"])
+                st = self.state[p]
+                st["step"] = st.get("step", 0) + 1
                 if mu != 0:
-                    st = self.state[p]
                     if "momentum_buffer" not in st:
-                        buf = st["momentum_buffer"] = d.clone()
-                    else:
-                        buf = st["momentum_buffer"].mul_(mu).add_(d, alpha=1 - g["dampening"])
+                        # as in the reference (src/optim/sign.py:43-52): the buffer starts as a copy of the
+                        # (already decayed) PARAMETER, not of the gradient, and is averaged from the first step on
+                        st["momentum_buffer"] = p.detach().clone()
+                    buf = st["momentum_buffer"].mul_(mu).add_(d, alpha=1 - g["dampening"])
                     d = d.add(buf, alpha=mu) if g["nesterov"] else buf
                 p.add_(d.sign() if g["sign_update"] else d, alpha=-g["lr"])
 
@@ -138,12 +140,22 @@ class Lamb(Optimizer):
 
 
 class Adafactor(Optimizer):
-    """Factored second moments for matrices (row and column statistics), update clipping, optional momentum."""
+    """Factored second moments for matrices (row and column statistics), update clipping, optional momentum.
 
-    def __init__(self, params, lr=1e-3, eps=(1e-30, 1e-3), clip_threshold=1.0, decay_rate=-0.8, beta1=None,
-                 weight_decay=0.0):
-        super().__init__(params, dict(lr=lr, eps=eps, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
-                                      weight_decay=weight_decay))
+    Defaults follow the reference (src/optim/adafactor.py:57-110), including the ones that make `lr` a no-op there:
+    with `relative_step` the step size is min(1e-2, 1/sqrt(t)) (or 1e-6 t with `warmup_init`), with `scale_parameter`
+    it is multiplied by max(eps2[1], RMS(parameter)); momentum averages the already scaled update and the decoupled
+    weight decay uses the same step size."""
+
+    def __init__(self, params, lr=1e-3, eps2=(1e-30, 1e-3), clip_threshold=1.0, decay_rate=-0.8, beta1=None,
+                 weight_decay=0.0, scale_parameter=True, relative_step=True, warmup_init=False):
+        super().__init__(params, dict(lr=lr, eps2=eps2, clip_threshold=clip_threshold, decay_rate=decay_rate, beta1=beta1,
+                                      weight_decay=weight_decay, scale_parameter=scale_parameter,
+                                      relative_step=relative_step, warmup_init=warmup_init))
+
+    @staticmethod
+    def _rms(t):
+        return t.norm(2) / (t.numel() ** 0.5)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -151,36 +163,45 @@ class Adafactor(Optimizer):
             for p in g["params"]:
                 if p.grad is None:
                     continue
-                grad = p.grad.float()
+                grad = p.grad
                 st = self.state[p]
                 factored = grad.dim() >= 2
                 if not st:
                     st["step"] = 0
                     if factored:
-                        st["row"] = torch.zeros(grad.shape[:-1], device=grad.device)
-                        st["col"] = torch.zeros(grad.shape[:-2] + grad.shape[-1:], device=grad.device)
+                        st["exp_avg_sq_row"] = torch.zeros(grad.shape[:-1], device=grad.device, dtype=grad.dtype)
+                        st["exp_avg_sq_col"] = torch.zeros(grad.shape[:-2] + grad.shape[-1:], device=grad.device,
+                                                           dtype=grad.dtype)
                     else:
-                        st["sq"] = torch.zeros_like(grad)
+                        st["exp_avg_sq"] = torch.zeros_like(grad)
                     if g["beta1"] is not None:
                         st["exp_avg"] = torch.zeros_like(grad)
                 st["step"] += 1
-                rho = 1.0 - st["step"] ** g["decay_rate"]
-                sq = grad * grad + g["eps"][0]
+                st["RMS"] = self._rms(p)
+                step_size = g["lr"]
+                if g["relative_step"]:
+                    floor = 1e-6 * st["step"] if g["warmup_init"] else 1e-2
+                    step_size = min(floor, 1.0 / math.sqrt(st["step"]))
+                if g["scale_parameter"]:
+                    step_size = step_size * max(g["eps2"][1], st["RMS"])
+                rho = 1.0 - math.pow(st["step"], g["decay_rate"])
+                sq = grad * grad + g["eps2"][0]
                 if factored:
-                    st["row"].mul_(rho).add_(sq.mean(-1), alpha=1 - rho)
-                    st["col"].mul_(rho).add_(sq.mean(-2), alpha=1 - rho)
-                    r = (st["row"] / st["row"].mean(-1, keepdim=True)).rsqrt().unsqueeze(-1)
-                    c = st["col"].rsqrt().unsqueeze(-2)
-                    upd = grad * r * c
+                    row, col = st["exp_avg_sq_row"], st["exp_avg_sq_col"]
+                    row.mul_(rho).add_(sq.mean(-1), alpha=1.0 - rho)
+                    col.mul_(rho).add_(sq.mean(-2), alpha=1.0 - rho)
+                    r = (row / row.mean(-1)).rsqrt_().unsqueeze(-1)
+                    upd = (r * col.unsqueeze(-2).rsqrt()).mul_(grad)
                 else:
-                    st["sq"].mul_(rho).add_(sq, alpha=1 - rho)
-                    upd = grad * st["sq"].rsqrt()
-                upd.div_((upd.pow(2).mean().sqrt() / g["clip_threshold"]).clamp_(min=1.0))
+                    st["exp_avg_sq"].mul_(rho).add_(sq, alpha=1.0 - rho)
+                    upd = st["exp_avg_sq"].rsqrt().mul_(grad)
+                upd.div_(max(1.0, self._rms(upd) / g["clip_threshold"]))
+                upd.mul_(step_size)
                 if g["beta1"] is not None:
                     upd = st["exp_avg"].mul_(g["beta1"]).add_(upd, alpha=1 - g["beta1"])
                 if g["weight_decay"] != 0:
-                    p.mul_(1 - g["lr"] * g["weight_decay"])
-                p.add_(upd.to(p.dtype), alpha=-g["lr"])
+                    p.add_(p, alpha=-g["weight_decay"] * step_size)
+                p.add_(-upd)
 
 
 class Prodigy(Optimizer):
@@ -412,7 +433,9 @@ class AdamWScheduleFree(_ScheduleFree):
         for g in self.param_groups:
             b1, b2 = g["betas"]
             bc2 = 1 - b2 ** (g["k"] + 1)
-            lr = g["lr"] * self._schedule(g) * math.sqrt(bc2)
+            # the reference's variant (src/optim/schedulefree.py:137-190): the bias correction sits inside the
+            # denominator, sqrt(v / bc2) + eps, and the step size is not rescaled by it
+            lr = g["scheduled_lr"] = g["lr"] * self._schedule(g)
             ck = self._weights(g, lr)
             for p in g["params"]:
                 if p.grad is None:
@@ -422,7 +445,7 @@ class AdamWScheduleFree(_ScheduleFree):
                     st["z"] = p.detach().clone()
                     st["exp_avg_sq"] = torch.zeros_like(p)
                 st["exp_avg_sq"].mul_(b2).addcmul_(p.grad, p.grad, value=1 - b2)
-                gn = p.grad / (st["exp_avg_sq"].sqrt() + g["eps"])
+                gn = p.grad / (st["exp_avg_sq"].div(bc2).sqrt_().add_(g["eps"]))
                 if g["weight_decay"] != 0:
                     gn.add_(p, alpha=g["weight_decay"])
                 p.lerp_(st["z"], ck)                       # y moves towards z as x does

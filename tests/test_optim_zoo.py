@@ -49,3 +49,68 @@ def test_optimizer_reduces_loss(name):
         opt.eval()
     last = ((model(x) - y) ** 2).mean().item()
     assert last == last and last < first, (name, first, last)
+
+
+# ---- the same classes against the reference's own, step for step ---------------------------------------------------
+def _ref_class(ref_src, rel, cls_name):
+    """Import `rel` of the reference's optim directory as a submodule of a private package (so that its relative
+    imports resolve) and return the class."""
+    import importlib
+    import sys
+    import types
+
+    torch.compiler.set_stance("force_eager")
+    if "adana_refoptim" not in sys.modules:
+        pkg = types.ModuleType("adana_refoptim")
+        pkg.__path__ = [str(ref_src / "optim")]
+        sys.modules["adana_refoptim"] = pkg
+    return getattr(importlib.import_module("adana_refoptim." + rel), cls_name)
+
+
+ZOO_CASES = [
+    ("lion", "Lion", {}, 0.0),
+    ("sign", "Signum", {"momentum": 0.9}, 0.0),
+    ("sign", "Signum", {"momentum": 0.9, "nesterov": True}, 0.0),
+    ("sign", "Signum", {"momentum": 0.0}, 0.0),
+    ("adopt", "ADOPT", {}, 0.0),
+    ("lamb", "Lamb", {}, 1e-7),
+    ("adafactor", "Adafactor", {}, 0.0),
+    ("adafactor", "Adafactor", {"beta1": 0.9, "relative_step": False, "scale_parameter": False}, 1e-7),
+    ("prodigy", "Prodigy", {}, 0.0),
+    ("sophia", "SophiaG", {}, 0.0),
+    ("mars", "MARS", {}, 5e-6),
+    ("mars", "MARS", {"mars_type": "mars-lion"}, 5e-6),
+    ("mars", "MARS", {"optimize_1d": True}, 5e-6),
+    ("schedulefree", "AdamWScheduleFree", {"warmup_steps": 3}, 0.0),
+    ("schedulefree", "SGDScheduleFree", {"momentum": 0.9}, 0.0),
+    ("soap", "SOAP", {}, 5e-6),
+]
+
+
+@pytest.mark.parametrize("rel,cls_name,kw,tol", ZOO_CASES, ids=[f"{c[1]}-{i}" for i, c in enumerate(ZOO_CASES)])
+def test_zoo_optimizer_follows_the_reference_class(ref_src, rel, cls_name, kw, tol):
+    """Six steps on the same random gradients: the parameters must coincide with those of the reference's class
+    (exactly where the arithmetic is the same sequence of operations, to rounding where it is regrouped)."""
+    from adana_b200.optim import zoo
+
+    ref_cls, mine = _ref_class(ref_src, rel, cls_name), getattr(zoo, cls_name)
+    torch.manual_seed(3)
+    w0 = [torch.randn(16, 8), torch.randn(8)]
+    pa = [torch.nn.Parameter(w.clone()) for w in w0]
+    pb = [torch.nn.Parameter(w.clone()) for w in w0]
+    base = dict(lr=1.0 if cls_name == "Prodigy" else 2e-3, weight_decay=0.1)
+    oa, ob = mine(pa, **base, **kw), ref_cls(pb, **base, **kw)
+    for o in (oa, ob):
+        if hasattr(o, "train"):
+            o.train()
+    for _ in range(6):
+        for a, b in zip(pa, pb):
+            g = torch.randn_like(a) * 0.05
+            a.grad, b.grad = g.clone(), g.clone()
+        if cls_name == "SophiaG":
+            oa.update_hessian()
+            ob.update_hessian()
+        oa.step()
+        ob.step()
+    for a, b in zip(pa, pb):
+        assert (a - b).abs().max().item() <= tol, (cls_name, kw, (a - b).abs().max().item())
