@@ -1,0 +1,106 @@
+"""Every model family against the reference's own class: same parameter names, and with the reference's weights
+loaded the same logits and loss (bit for bit on CPU fp32).  Needs the unmodified reference under baseline/_ref."""
+import argparse
+import sys
+import types
+
+import pytest
+import torch
+
+COMMON = ["--n_layer", "2", "--n_head", "2", "--n_embd", "128", "--sequence_length", "64", "--batch_size", "2",
+          "--vocab_size", "512", "--dtype", "float32", "--device", "cpu", "--dropout", "0.0", "--z_loss_coeff", "1e-3"]
+CASES = {
+    "base": ["--model", "base"],
+    "llama": ["--model", "llama", "--multiple_of", "32"],
+    "enoki": ["--model", "enoki", "--qkv_dim", "64", "--mlp_hidden_dim", "256"],
+    "qwen3": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256"],
+    "qwen3next": ["--model", "qwen3next", "--qkv_dim", "64", "--mlp_hidden_dim", "256"],
+    "qwen3-moe": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--moe", "--moe_num_experts", "4",
+                  "--moe_num_experts_per_tok", "2"],
+    "base-moe": ["--model", "base", "--moe", "--moe_num_experts", "4", "--moe_num_experts_per_tok", "2"],
+}
+_REF_TOP = ("config", "models", "optim", "data", "distributed", "logger")
+
+
+def _forget_reference_modules():
+    for k in [k for k in sys.modules if k.split(".")[0] in _REF_TOP]:
+        del sys.modules[k]
+
+
+def _reference_model(ref_src, argv, monkeypatch):
+    import tiktoken
+
+    monkeypatch.setattr(tiktoken, "get_encoding", lambda name: types.SimpleNamespace(name=name))   # no network here
+    _forget_reference_modules()
+    sys.path.insert(0, str(ref_src))
+    try:
+        import config as ref_config
+        from models.utils import get_model as ref_get_model
+
+        parser = argparse.ArgumentParser(allow_abbrev=False)
+        parser.add_argument("--config_format", default="base")
+        args = ref_config.parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv)
+        torch.manual_seed(0)
+        return ref_get_model(args)
+    finally:
+        sys.path.remove(str(ref_src))
+        _forget_reference_modules()
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_model_equals_the_reference_class_on_the_reference_weights(ref_src, name, monkeypatch):
+    from adana_b200.config import parse_args_with_format
+    from adana_b200.models.utils import get_model
+
+    torch.compiler.set_stance("force_eager")       # the reference decorates helpers with torch.compile
+    argv = COMMON + CASES[name]
+    ref = _reference_model(ref_src, argv, monkeypatch)
+    parser = argparse.ArgumentParser(allow_abbrev=False)
+    parser.add_argument("--config_format", default="base")
+    torch.manual_seed(1)
+    ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
+    ref_sd = ref.state_dict()
+    assert set(ref_sd) == set(ours.state_dict())                      # checkpoint-compatible names
+    for k, v in ours.state_dict().items():
+        assert v.shape == ref_sd[k].shape, k
+    ours.load_state_dict(ref_sd)
+    ref.eval()
+    ours.eval()
+    torch.manual_seed(5)
+    idx, tgt = torch.randint(0, 512, (2, 64)), torch.randint(0, 512, (2, 64))
+    with torch.no_grad():
+        want = ref(idx, targets=tgt, get_logits=True)
+        got = ours(idx, targets=tgt, get_logits=True)
+    assert torch.allclose(got["logits"], want["logits"], atol=1e-6, rtol=0)
+    assert abs(float(got["loss"]) - float(want["loss"])) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["enoki", "qwen3-moe", "qwen3next", "llama"])
+def test_training_loss_and_gradients_equal_the_reference(ref_src, name, monkeypatch):
+    """Train mode (z-loss and, for MoE, the router's auxiliary losses included): the same loss and the same
+    gradient for every parameter."""
+    from adana_b200.config import parse_args_with_format
+    from adana_b200.models.utils import get_model
+
+    torch.compiler.set_stance("force_eager")
+    argv = COMMON + CASES[name]
+    ref = _reference_model(ref_src, argv, monkeypatch)
+    parser = argparse.ArgumentParser(allow_abbrev=False)
+    parser.add_argument("--config_format", default="base")
+    ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
+    ours.load_state_dict(ref.state_dict())
+    ref.train()
+    ours.train()
+    torch.manual_seed(6)
+    idx, tgt = torch.randint(0, 512, (2, 64)), torch.randint(0, 512, (2, 64))
+    lw = ref(idx, targets=tgt)["loss"]
+    lg = ours(idx, targets=tgt)["loss"]
+    assert abs(lg.item() - lw.item()) < 1e-6
+    lw.backward()
+    lg.backward()
+    ref_grads = {k: p.grad for k, p in ref.named_parameters()}
+    for k, p in ours.named_parameters():
+        if ref_grads[k] is None:
+            assert p.grad is None or float(p.grad.abs().max()) == 0.0, k
+        else:
+            assert torch.allclose(p.grad, ref_grads[k], atol=2e-6, rtol=1e-5), (k, float((p.grad - ref_grads[k]).abs().max()))
