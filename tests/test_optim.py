@@ -172,3 +172,23 @@ def test_muon_family_steps_reduce_a_quadratic():
     assert l < 0.5 * f
     with pytest.raises(ValueError):
         Manau([{"params": [torch.nn.Parameter(torch.zeros(2, 2))]}])
+
+
+@pytest.mark.parametrize("shape", [(32, 16), (16, 32), (24, 24)])
+def test_newton_schulz_equals_the_reference_iteration(ref_src, shape):
+    """The quintic Newton-Schulz iteration against the reference's function on the same fp32 matrix (tall matrices
+    are iterated transposed on both sides)."""
+    import sys
+    import types
+
+    torch.compiler.set_stance("force_eager")
+    if "adana_refoptim" not in sys.modules:
+        pkg = types.ModuleType("adana_refoptim")
+        pkg.__path__ = [str(ref_src / "optim")]
+        sys.modules["adana_refoptim"] = pkg
+    ref = importlib.import_module("adana_refoptim.muon").zeropower_via_newtonschulz5
+    from adana_b200.optim.muon import newton_schulz5
+
+    torch.manual_seed(0)
+    G = torch.randn(*shape)
+    assert torch.allclose(newton_schulz5(G.clone(), 5).float(), ref(G.clone(), 5).float(), atol=5e-6, rtol=0)
