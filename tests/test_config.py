@@ -67,3 +67,46 @@ def test_exp_name():
     assert "lr-0.002" in name and "seed" not in name and "wandb" not in name
     args.run_prefix = "x" * 250
     assert "__hash_" in get_exp_name(args, parser)
+
+
+def test_scaling_rules_equal_the_reference_functions(ref_src):
+    """Model dimensions, learning-rate laws (every optimizer table, kappa keys and the closest-kappa fallback, the
+    batch-512 table) and `apply_scaling_rule` against the reference's own functions over a grid: same values, and
+    the same error where the reference raises."""
+    import contextlib
+    import copy
+    import importlib.util
+    import io
+    import itertools
+
+    from adana_b200.config import flags
+    from adana_b200.config import scaling as mine
+
+    spec = importlib.util.spec_from_file_location("ref_scaling", ref_src / "config" / "scaling.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+
+    def outcome(fn, *a, **k):
+        try:
+            return fn(*a, **k)
+        except Exception as e:      # the error class is part of the behaviour
+            return ("error", type(e).__name__)
+
+    for rule, heads in itertools.product(("enoki", "qwen3"), (4, 8, 12, 16, 24, 28, 32, 36, 44, 48)):
+        a, b = mine.compute_dimensions(rule, heads), ref.compute_dimensions(rule, heads)
+        assert {k: a.get(k) for k in b} == b, (rule, heads)
+    opts = ("adamw", "adamw-decaying-wd", "adana", "dana-mk4", "dana-star", "dana-star-mk4", "dana-star-mk4-tau", "ademamix",
+            "ademamix-decaying-wd", "d-muon", "lion")
+    for rule, opt, kappa, bs, P in itertools.product(("enoki", "qwen3"), opts, (None, 0.75, 0.8, 0.85, 0.9, 0.83),
+                                                     (None, 32, 512), (1e7, 2.5e9)):
+        x = outcome(mine.compute_lr, rule, opt, P, kappa=kappa, batch_size=bs)
+        y = outcome(ref.compute_lr, rule, opt, P, kappa=kappa, batch_size=bs)
+        assert x == y or (isinstance(x, float) and isinstance(y, float) and abs(x - y) <= 1e-12 * abs(y)), (rule, opt, kappa, bs, P, x, y)
+    for rule, opt, heads, B, acc in itertools.product(("enoki", "qwen3"), ("adamw", "dana-star-mk4", "d-muon"), (8, 36), (32, 64), (1, 8)):
+        a = flags.defaults()
+        a.scaling_rule, a.opt, a.heads, a.kappa, a.batch_size, a.acc_steps = rule, opt, heads, 0.85, B, acc
+        x, y = copy.deepcopy(a), copy.deepcopy(a)
+        with contextlib.redirect_stdout(io.StringIO()):
+            mine.apply_scaling_rule(x)
+            ref.apply_scaling_rule(y)
+        assert vars(x) == vars(y), (rule, opt, heads, B, acc)
