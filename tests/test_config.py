@@ -110,3 +110,30 @@ def test_scaling_rules_equal_the_reference_functions(ref_src):
             mine.apply_scaling_rule(x)
             ref.apply_scaling_rule(y)
         assert vars(x) == vars(y), (rule, opt, heads, B, acc)
+
+
+def test_flag_surface_and_defaults_equal_the_reference_parser(ref_src):
+    """Every flag of the reference's parser exists here with the same default; the two that differ are paths into
+    the reference's own source tree."""
+    import argparse
+    import importlib.util
+    import sys
+    import types
+
+    from adana_b200.config import flags
+
+    had = "distributed" in sys.modules
+    if not had:     # the reference's config imports its distributed package only for the backend names
+        sys.modules["distributed"] = types.SimpleNamespace(registered_backends=lambda: ["nccl", "gloo", "fsdp"])
+    try:
+        spec = importlib.util.spec_from_file_location("ref_config_base", ref_src / "config" / "base.py")
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        want = vars(ref.parse_args(argparse.ArgumentParser(allow_abbrev=False), args=[], namespace=None))
+    finally:
+        if not had:
+            del sys.modules["distributed"]
+    got = vars(flags.defaults())
+    assert not set(want) - set(got)
+    different = {k for k in want if got[k] != want[k]}
+    assert different == {"dynamics_logger_cfg", "datasets_dir"}, different
