@@ -277,3 +277,33 @@ def parse_args(base_parser: argparse.ArgumentParser, args, namespace=None):
     if ns.full_eval_at is None:
         ns.full_eval_at = []
     return ns
+
+
+# The order in which the reference's parser defines its flags (src/config/base.py:22-429).  Experiment directory
+# names list the non-default flags in this order (src/main.py:590-600), so a run started there and resumed here, or
+# the other way round, looks for the same directory; flags that exist only here follow in table order.
+REFERENCE_FLAG_ORDER = """
+    run_prefix experiment_name seed data_seed eval_interval full_eval_at eval_batches device distributed_backend
+    tp_size log_interval results_base_folder permanent_ckpt_interval latest_ckpt_interval resume_from
+    resume_from_swa auto_resume wandb wandb_project wandb_run_prefix eval_seq_prefix log_dynamics
+    dynamics_logger_cfg wandb_entity wandb_group log_parameter_norms norm_order scheduler div_factor
+    final_div_factor cos_inf_steps iterations iterations_to_run warmup_steps lr wsd_final_lr_scale
+    wsd_fract_decay decay_type dd_second_decay_type dd_first_lr_factor powerlaw_init_value
+    powerlaw_saturation_value powerlaw_power powerlaw_time_scale opt batch_size acc_steps weight_decay beta1
+    beta2 grad_clip momentum shampoo_beta precondition_frequency max_precond_dim merge_dims precondition_1d
+    normalize_grads soap_data_format correct_bias nesterov muon_ns_steps muon_lr_factor matched_adamw_rms
+    dana_momentum adema_beta3 lr_outer k mu adema_beta3_warmup adema_alpha_warmup schedulefree_r weight_lr_power
+    model_sharding dampening prodigy_beta3 prodigy_decouple prodigy_use_bias_correction prodigy_safeguard_warmup
+    prodigy_fsdp_in_use sophia_rho sophia_bs clipping_type clip_eta mars_type mars_vr_gamma mars_is_approx
+    mars_lr mars_beta1 mars_beta2 adafactor_decay_rate lamb_use_bias_correction sgd_sign_update normalized
+    sgd_lr_scale adopt_decouple adopt_eps g2 g3 delta kappa mk4A mk4B clipsnr weight_time wd_decaying wd_ts
+    use_v_ema v_ema_beta gamma_3_factor norm_type collect_tau_stats datasets_dir dataset tokenizer vocab_size
+    data_in_ram model scaling_rule heads parallel_block use_pretrained from_dense init_std init_scheme
+    residual_stream_scalar dropout n_head n_layer sequence_length n_embd qkv_dim mlp_hidden_dim multiple_of
+    rmsnorm_eps normalization_layer_type elementwise_attn_output_gate dtype bias weight_tying no_qknorm compile
+    activation_checkpointing checkpoint_every_n mlp_dim_exp_factor moe moe_routing moe_num_experts
+    capacity_factor moe_num_shared_experts moe_router_loss moe_num_experts_per_tok moe_expert_capacity_factor
+    moe_entropy_loss_factor moe_aux_loss_factor moe_z_loss_factor moe_softmax_order plot_router_logits
+    z_loss_coeff hoyer_loss_coeff liger_loss use_gated_shared_expert shared_expert_intermediate_size
+    decoder_sparse_step mlp_only_layers expert_parallel
+""".split()

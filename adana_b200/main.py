@@ -70,8 +70,13 @@ def get_exp_name(args, parser, distributed_backend=None, key_args=("model", "dat
     prefix = f"{args.batch_size}x{args.acc_steps}_" + "_".join(head)
     if args.run_prefix is not None:
         prefix = f"{args.run_prefix}_{prefix}"
-    tail = [f"{k}-{v}" for k, v in vars(args).items()
-            if k not in ignore_args and k in defaults and k not in key_args and v != defaults[k]]
+    from .config.flags import REFERENCE_FLAG_ORDER
+
+    # the reference's flags in the reference's order, then the flags that exist only here
+    rank_of = {k: i for i, k in enumerate(REFERENCE_FLAG_ORDER)}
+    keys = sorted(vars(args), key=lambda k: rank_of.get(k, len(rank_of)))      # stable: extras keep their own order
+    tail = [f"{k}-{getattr(args, k)}" for k in keys
+            if k not in ignore_args and k in defaults and k not in key_args and getattr(args, k) != defaults[k]]
     name = f"{prefix}__{'_'.join(tail)}" if tail else prefix
     if len(name) > 200:
         name = f"{prefix}__hash_{hashlib.md5(name.encode()).hexdigest()[:8]}"

@@ -137,3 +137,59 @@ def test_flag_surface_and_defaults_equal_the_reference_parser(ref_src):
     assert not set(want) - set(got)
     different = {k for k in want if got[k] != want[k]}
     assert different == {"dynamics_logger_cfg", "datasets_dir"}, different
+
+
+def test_experiment_directory_names_equal_the_reference(ref_src, monkeypatch):
+    """`get_exp_name` against the reference's function, the md5 tag of over-long names included: a run started with
+    one code base is found by `--auto_resume` of the other."""
+    import argparse
+    import importlib
+    import sys
+    import types
+
+    import tiktoken
+    import torch
+
+    from adana_b200 import main as ours
+    from adana_b200.config import parse_args_with_format
+
+    torch.compiler.set_stance("force_eager")
+    monkeypatch.setattr(tiktoken, "get_encoding", lambda name: types.SimpleNamespace(name=name))
+    top = ("config", "models", "optim", "data", "distributed", "logger", "main")
+
+    def forget():
+        for k in [k for k in sys.modules if k.split(".")[0] in top]:
+            del sys.modules[k]
+
+    cases = [[], ["--model", "enoki", "--opt", "dana-star-mk4", "--lr", "0.002", "--kappa", "0.8"],
+             ["--batch_size", "64", "--acc_steps", "8", "--n_layer", "36", "--distributed_backend", "fsdp"],
+             ["--opt", "adamw", "--weight_decay", "0.01", "--run_prefix", "abc", "--seed", "3", "--wd_decaying", "--wd_ts", "17"],
+             ["--model", "qwen3", "--moe", "--moe_num_experts", "16", "--z_loss_coeff", "0.001", "--scheduler", "wsd",
+              "--wsd_fract_decay", "0.2", "--dataset", "fineweb_100", "--sequence_length", "2048", "--n_embd", "2304",
+              "--n_head", "36", "--mlp_hidden_dim", "9216", "--qkv_dim", "64", "--iterations", "12345", "--warmup_steps",
+              "246", "--grad_clip", "0.5", "--delta", "8", "--clipsnr", "2.0", "--eval_interval", "115"]]
+    forget()
+    if "wandb" not in sys.modules:
+        try:
+            import wandb  # noqa: F401
+        except Exception:
+            monkeypatch.setitem(sys.modules, "wandb", types.ModuleType("wandb"))
+    sys.path.insert(0, str(ref_src))
+    try:
+        ref_main = importlib.import_module("main")
+        ref_config = importlib.import_module("config")
+        want = []
+        for argv in cases:
+            p = argparse.ArgumentParser(allow_abbrev=False)
+            p.add_argument("--config_format", default="base")
+            a = ref_config.parse_args_with_format(format="base", base_parser=p, namespace=None, args=argv)
+            want.append(ref_main.get_exp_name(a, p, types.SimpleNamespace(rank=0)))
+    finally:
+        sys.path.remove(str(ref_src))
+        forget()
+    for argv, w in zip(cases, want):
+        p = argparse.ArgumentParser(allow_abbrev=False)
+        p.add_argument("--config_format", default="base")
+        a = parse_args_with_format(format="base", base_parser=p, namespace=None, args=argv)
+        assert ours.get_exp_name(a, p, None) == w
+    assert "__hash_" in want[-1]
