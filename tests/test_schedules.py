@@ -55,3 +55,35 @@ def test_scheduler_factory_drives_optimizer_lr():
     assert lrs[0] == pytest.approx(1e-4) and max(lrs) == pytest.approx(1e-2) and lrs[-1] < 2e-3
     import pickle
     pickle.dumps(sch.state_dict())  # schedules are picklable objects, not closures
+
+
+def test_schedules_equal_the_reference_functions(ref_src):
+    """cos_inf, every WSD decay type and the power-law schedule against the reference's lambdas at every step
+    (two steps past the end included)."""
+    import importlib.util
+
+    from adana_b200.optim import schedule as mine
+
+    spec = importlib.util.spec_from_file_location("ref_schedule", ref_src / "optim" / "schedule.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+
+    def same(f, g, n):
+        for t in range(n + 2):
+            a, b = f(t), g(t)
+            assert abs(a - b) <= 1e-12 * max(1.0, abs(b)), (t, a, b)
+
+    for n, warm, n_inf in ((200, 100, 0), (500, 20, 100), (64, 1, 0)):
+        same(mine.cos_inf_schedule(n, warm, 1e2, 1e4, n_inf), ref.cos_inf_schedule(n, warm, 1e2, 1e4, n_inf), n)
+    for decay in ("linear", "cosine", "exp", "miror_cosine", "square", "sqrt"):
+        for n, warm, frac, final in ((300, 30, 0.1, 0.0), (300, 10, 0.4, 0.05)):
+            try:
+                g = ref.wsd_schedule(n, final_lr_factor=final, n_warmup=warm, init_div_factor=100, fract_decay=frac, decay_type=decay)
+                g(n - 1)
+            except Exception:
+                continue        # a decay type the reference does not have
+            same(mine.wsd_schedule(n, final_lr_factor=final, n_warmup=warm, init_div_factor=100, fract_decay=frac,
+                                   decay_type=decay), g, n)
+    for power, sat, scale in ((-0.5, 0.0, 1.0), (-1.0, 0.1, 10.0), (-0.25, 0.0, 100.0)):
+        same(mine.powerlaw_schedule_with_warmup(400, 40, 1.0, sat, power, scale),
+             ref.powerlaw_schedule_with_warmup(400, 40, 1.0, sat, power, scale), 400)
