@@ -100,3 +100,34 @@ def test_pinned_stager_cpu_path(stream):
             xr, yr = r2.sample_batch()
             assert torch.equal(x, xr) and torch.equal(y, yr)
         assert st.bytes_per_batch == 2 * 4 * 32 * 8
+
+
+def test_batch_order_equals_the_reference_reader(ref_src, monkeypatch):
+    """Same seed, same token file: the reference's DataReader and this one deliver the same batches, step after
+    step and after a jump with `set_step` (what lets a run be resumed, or compared, across the two code bases)."""
+    import importlib
+    import sys
+    import types
+
+    import numpy as np
+    import tiktoken
+    import torch
+
+    from adana_b200.data.readers import DataReader
+
+    monkeypatch.setattr(tiktoken, "get_encoding", lambda name: types.SimpleNamespace(name=name))
+    if "adana_refdata" not in sys.modules:
+        pkg = types.ModuleType("adana_refdata")
+        pkg.__path__ = [str(ref_src / "data")]
+        sys.modules["adana_refdata"] = pkg
+    ref = importlib.import_module("adana_refdata.utils")
+    toks = np.random.default_rng(0).integers(0, 50000, size=200000).astype(np.uint16)
+    kw = dict(local_batch_size=4, sequence_length=64, seed=7, keep_in_ram=True, with_replacement=False, auto_shard=False)
+    a, b = DataReader(toks, **kw), ref.DataReader(toks, **kw)
+    assert a.num_batches() == b.num_batches()
+    for start in (0, 333, 779):
+        a.set_step(start)
+        b.set_step(start)
+        for _ in range(20):
+            (xa, ya), (xb, yb) = a.sample_batch(), b.sample_batch()
+            assert torch.equal(xa, xb) and torch.equal(ya, yb)
