@@ -192,3 +192,43 @@ def test_newton_schulz_equals_the_reference_iteration(ref_src, shape):
     torch.manual_seed(0)
     G = torch.randn(*shape)
     assert torch.allclose(newton_schulz5(G.clone(), 5).float(), ref(G.clone(), 5).float(), atol=5e-6, rtol=0)
+
+
+@pytest.mark.parametrize("which", ["dana-mk4", "dana-star-mk4"])
+def test_optimizer_state_dicts_are_interchangeable_with_the_reference(ref_src, which):
+    """Four steps with one implementation, `state_dict()` loaded into the other, four more steps: the reference's
+    checkpoints resume here and the other way round (same keys in `state` and `param_groups`, same trajectories)."""
+    import copy
+
+    if which == "dana-mk4":
+        ref_cls, mine = _load_ref(ref_src, "optim/adana.py", "ref_adana_sd").ADana, ADana
+    else:
+        ref_cls, mine = _load_ref(ref_src, "optim/dana_star_mk4.py", "ref_dsmk4_sd").DANA_STAR_MK4, DanaStarMK4
+    torch.manual_seed(0)
+    w0 = [torch.randn(16, 8), torch.randn(8)]
+    grads = [[torch.randn_like(w) * 0.05 for w in w0] for _ in range(8)]
+
+    def make(cls):
+        ps = [torch.nn.Parameter(w.clone()) for w in w0]
+        return ps, cls(ps, lr=2e-3, weight_decay=0.3, delta=8.0, kappa=0.85, wd_decaying=True, wd_ts=3.0, clipsnr=2.0)
+
+    def run(ps, opt, steps):
+        for t in steps:
+            for p, g in zip(ps, grads[t]):
+                p.grad = g.clone()
+            opt.step()
+
+    for first, second in ((ref_cls, mine), (mine, ref_cls)):
+        p1, o1 = make(first)
+        run(p1, o1, range(4))
+        sd = copy.deepcopy(o1.state_dict())
+        p2, o2 = make(second)
+        assert set(sd["param_groups"][0]) == set(o2.state_dict()["param_groups"][0])
+        o2.load_state_dict(sd)
+        for a, b in zip(p2, p1):
+            a.data.copy_(b.data)
+        run(p1, o1, range(4, 8))
+        run(p2, o2, range(4, 8))
+        assert set(o1.state_dict()["state"][0]) == set(o2.state_dict()["state"][0])
+        for a, b in zip(p1, p2):
+            assert torch.allclose(a, b, rtol=0, atol=5e-7)
