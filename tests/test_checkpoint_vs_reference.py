@@ -159,3 +159,46 @@ def test_checkpoint_written_here_resumes_in_the_reference(ref_src, monkeypatch, 
         got = _train(model, opt, sched, batches[SWITCH:])
     for a, b in zip(got, want):
         assert a == pytest.approx(b, rel=2e-5), (got, want)
+
+
+def test_worker_state_files_are_interchangeable(ref_src, monkeypatch, tmp_path):
+    """`worker_0.pt` (RNG states + data reader position) written by either side is restored by the other: the next
+    batches and the next random numbers are the ones the writer would have produced."""
+    import importlib
+    import random
+
+    import numpy as np
+
+    from adana_b200.data.readers import DataReader
+    from adana_b200.train import checkpoint as ours
+
+    toks = np.random.default_rng(0).integers(0, 50000, size=60000).astype(np.uint16)
+    kw = dict(local_batch_size=4, sequence_length=32, seed=5, keep_in_ram=True, with_replacement=False, auto_shard=False)
+    with _Reference(ref_src, monkeypatch):
+        ref_utils = importlib.import_module("optim.utils")
+        ref_reader_cls = importlib.import_module("data.utils").DataReader
+        # reference writes, this side restores
+        r = ref_reader_cls(toks, **kw)
+        r.set_step(0)
+        for _ in range(7):
+            r.sample_batch()
+        torch.manual_seed(3)
+        np.random.seed(4)
+        random.seed(5)
+        ref_utils.save_worker_state(tmp_path / "a", r)
+        want = (r.sample_batch()[0], torch.rand(3), np.random.rand(), random.random())
+        m = DataReader(toks, **kw)
+        torch.manual_seed(99)
+        ours.load_worker_state(tmp_path / "a", m, verbose=False)
+        got = (m.sample_batch()[0], torch.rand(3), np.random.rand(), random.random())
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and got[2:] == want[2:]
+        # this side writes, the reference restores
+        for _ in range(5):
+            m.sample_batch()
+        ours.save_worker_state(tmp_path / "b", m, verbose=False)
+        want = (m.sample_batch()[0], torch.rand(3), np.random.rand(), random.random())
+        r2 = ref_reader_cls(toks, **kw)
+        torch.manual_seed(98)
+        ref_utils.load_worker_state(tmp_path / "b", r2)
+        got = (r2.sample_batch()[0], torch.rand(3), np.random.rand(), random.random())
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1]) and got[2:] == want[2:]
