@@ -104,3 +104,54 @@ def test_training_loss_and_gradients_equal_the_reference(ref_src, name, monkeypa
             assert p.grad is None or float(p.grad.abs().max()) == 0.0, k
         else:
             assert torch.allclose(p.grad, ref_grads[k], atol=2e-6, rtol=1e-5), (k, float((p.grad - ref_grads[k]).abs().max()))
+
+
+@pytest.mark.parametrize("name", ["enoki", "qwen3-moe"])
+def test_evaluation_equals_the_reference_eval(ref_src, name, monkeypatch):
+    """The evaluation loop (loss, accuracy, perplexity, auxiliary losses, router logits for MoE) against the
+    reference's `eval` over the same validation batches."""
+    import importlib
+
+    import numpy as np
+
+    from adana_b200.config import parse_args_with_format
+    from adana_b200.data.readers import DataReader
+    from adana_b200.models.utils import get_model
+    from adana_b200.train.loop import evaluate
+
+    torch.compiler.set_stance("force_eager")
+    argv = COMMON + CASES[name]
+    moe = "moe" in name
+    toks = np.random.default_rng(2).integers(0, 512, size=20000).astype(np.uint16)
+    kw = dict(local_batch_size=2, sequence_length=64, seed=3, keep_in_ram=True, with_replacement=False, auto_shard=False)
+    ref = _reference_model(ref_src, argv, monkeypatch)
+    if "wandb" not in sys.modules:
+        try:
+            import wandb  # noqa: F401
+        except Exception:
+            monkeypatch.setitem(sys.modules, "wandb", types.ModuleType("wandb"))
+    sys.path.insert(0, str(ref_src))
+    try:
+        ref_eval = importlib.import_module("optim.utils").eval
+        ref_reader = importlib.import_module("data.utils").DataReader(toks, **kw)
+        ref_reader.set_step(0)
+        ref.eval()
+        want = ref_eval(ref, ref_reader, max_num_batches=5, moe=moe, get_router_logits=moe)
+    finally:
+        sys.path.remove(str(ref_src))
+        _forget_reference_modules()
+    parser = argparse.ArgumentParser(allow_abbrev=False)
+    parser.add_argument("--config_format", default="base")
+    ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
+    ours.load_state_dict(ref.state_dict())
+    ours.eval()
+    reader = DataReader(toks, **kw)
+    reader.set_step(0)
+    got = evaluate(ours, reader, max_num_batches=5, moe=moe, get_router_logits=moe)
+    assert got[0] == pytest.approx(want[0], abs=1e-7) and got[1] == pytest.approx(want[1], abs=1e-6)
+    assert got[2] == pytest.approx(want[2], rel=1e-6)
+    assert set(got[3]) == set(want[3])
+    for k in want[3]:
+        assert got[3][k] == pytest.approx(want[3][k], abs=1e-6), k
+    if moe:
+        assert got[4].shape == want[4].shape and torch.allclose(got[4], want[4], atol=1e-5)
