@@ -266,7 +266,8 @@ class DynamicsLogger:
                     continue
                 if any(getattr(snap, f) is None for f in getattr(fn, "needs", ())):
                     continue
-                self.stats[stat][name].append(fn(snap).float())
+                val = fn(snap)      # angles are computed and kept in double (small angles drown in fp32 noise)
+                self.stats[stat][name].append(val if val.dtype == torch.float64 else val.float())
 
     def _maybe_flush(self):
         t_disk = self.cfg["disk_save_interval"] or 0

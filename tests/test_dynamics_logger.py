@@ -102,3 +102,49 @@ def test_engine_source_reports_updates_of_flat_buffers(tmp_path):
     assert float(lg.stats["layer_grad_norm"][name][0]) > 0
     assert float(lg.stats["layer_mean_second_grad_moment"][name][0]) > 0
     assert any(float(v[0]) > 0 for v in lg.stats["scalar_update_rms"].values())
+
+
+def test_disk_output_equals_the_reference_logger(ref_src, tmp_path):
+    """Same model, same optimizer, same steps, the reference's YAML configuration: the `dynamics.pkl` written by
+    the reference's DynamicsLogger and by this one hold the same statistics for the same parameters.  One is
+    excluded: the reference's `scalar_rms` reads a stale loop variable (src/logger/logger.py:117,271: the model's
+    last parameter, whatever the scalar being logged), here it is the RMS of the parameter itself."""
+    import copy
+    import importlib.util
+
+    import yaml
+
+    from adana_b200.logging.dynamics import DynamicsLogger
+
+    spec = importlib.util.spec_from_file_location("ref_logger", ref_src / "logger" / "logger.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    cfg = yaml.safe_load((ref_src / "logger" / "rotational_logger.yaml").read_text())
+    cfg.update(interval=1, disk_save_interval=4, disk_downsample=2, wandb_interval=None)
+    out = {}
+    for name, cls in (("ref", ref.DynamicsLogger), ("ours", DynamicsLogger)):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(12, 24, bias=True), torch.nn.LayerNorm(24), torch.nn.Linear(24, 6, bias=False))
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1)
+        folder = tmp_path / name
+        folder.mkdir()
+        cls(model, opt, copy.deepcopy(cfg), folder, wandb=False)
+        g = torch.Generator().manual_seed(1)
+        for _ in range(8):
+            loss = model(torch.randn(16, 12, generator=g)).pow(2).mean()
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+        out[name] = cls.load_stats(folder / "dynamics.pkl")
+    want, got = out["ref"], out["ours"]
+    assert set(want) == set(got) == set(cfg["stats"])
+    for stat in want:
+        assert set(want[stat]) == set(got[stat]), stat
+        if stat == "scalar_rms":
+            continue
+        for pname in want[stat]:
+            assert got[stat][pname].shape == want[stat][pname].shape == torch.Size([4, got[stat][pname].shape[1]])
+            assert got[stat][pname].dtype == want[stat][pname].dtype, (stat, pname, got[stat][pname].dtype, want[stat][pname].dtype)
+            # an angle of 0.05 rad moves by 1e-6 when an operand moves by one fp32 ulp
+            rtol = 1e-4 if "angular" in stat else 1e-5
+            assert torch.allclose(got[stat][pname], want[stat][pname], atol=1e-6, rtol=rtol), (stat, pname)
