@@ -52,7 +52,8 @@ def log_optimizer_schedules(optimizer, optimizer_name):
     else:
         return {}
     fused = getattr(optimizer, "diagnostics", None)
-    if fused:  # the fused engine optimizer reports aggregate values directly
+    if isinstance(fused, dict) and fused:  # the fused engine optimizer reports aggregate values directly
+        # (the per-tensor classes have a boolean attribute of the same name)
         return {_KEYS[k]: v for k, v in fused.items() if k in wanted and k in _KEYS}
     acc = {k: [] for k in wanted}
     for group in optimizer.param_groups:
