@@ -1,0 +1,78 @@
+"""The whole command line against the reference's: `main.py` of the unmodified reference and `adana_b200.main` are
+run as child processes with the same flags on the same token files (CPU, fp32, one process), and their training /
+evaluation log lines must agree: the same text, every printed number (iteration, epochs, loss, perplexity, learning
+rate, accuracy) equal up to a flip of its last printed digit.
+This side runs its kernel engine (the CPU statement of the kernels) and `--init_compat reference`."""
+import re
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+# launcher for the reference: the GPT-2 BPE files cannot be downloaded here and every model constructor asks for the
+# tokenizer, and wandb may be absent; nothing of the reference is modified
+REF_LAUNCHER = """
+import os, runpy, sys, types
+import tiktoken
+class _Tok:
+    eot_token = 50256
+    def encode(self, *a, **k): return [0]
+    encode_ordinary = encode
+    def decode(self, *a): return ""
+tiktoken.get_encoding = lambda name: _Tok()
+try:
+    import wandb
+except Exception:
+    sys.modules["wandb"] = types.ModuleType("wandb")
+src = sys.argv[1]
+sys.argv = ["main.py"] + sys.argv[2:]
+sys.path.insert(0, src)
+os.chdir(src)
+runpy.run_path(os.path.join(src, "main.py"), run_name="__main__")
+"""
+
+
+def _log_lines(text):
+    keep = [ln for ln in text.splitlines() if ln.startswith("Train: Iter") or ln.startswith(">Eval")]
+    return [re.sub(r"iter_dt=\S+\s*", "", ln).rstrip() for ln in keep]
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("model,opt", [("enoki", "dana-star-mk4"), ("qwen3", "adana")])
+def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt):
+    import os
+
+    data = tmp_path / "data" / "fineweb-10BT"
+    data.mkdir(parents=True)
+    rng = np.random.default_rng(0)
+    p = 1.0 / np.arange(1, 513)
+    p /= p.sum()
+    rng.choice(512, size=300000, p=p).astype(np.uint16).tofile(data / "train.bin")
+    rng.choice(512, size=40000, p=p).astype(np.uint16).tofile(data / "val.bin")
+    flags = ["--model", model, "--n_layer", "2", "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim",
+             "128", "--sequence_length", "64", "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset",
+             "fineweb", "--datasets_dir", str(tmp_path / "data"), "--opt", opt, "--kappa", "0.85", "--clipsnr", "2.0",
+             "--wd_decaying", "--wd_ts", "5", "--weight_decay", "0.1", "--lr", "1e-3", "--warmup_steps", "2", "--scheduler",
+             "cos_inf", "--iterations", "12", "--eval_interval", "4", "--eval_batches", "2", "--log_interval", "1",
+             "--device", "cpu", "--dtype", "float32", "--seed", "3", "--dropout", "0.0"]
+    env = {**os.environ, "TORCHDYNAMO_DISABLE": "1", "OMP_NUM_THREADS": "2", "WANDB_MODE": "disabled"}
+    ref = subprocess.run([sys.executable, "-c", REF_LAUNCHER, str(ref_src), *flags, "--results_base_folder", str(tmp_path / "ref")],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert ref.returncode == 0, ref.stdout[-1500:] + ref.stderr[-1500:]
+    ours = subprocess.run([sys.executable, "-m", "adana_b200.main", *flags, "--init_compat", "reference",
+                           "--results_base_folder", str(tmp_path / "ours")],
+                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert ours.returncode == 0, ours.stdout[-1500:] + ours.stderr[-1500:]
+    want, got = _log_lines(ref.stdout), _log_lines(ours.stdout)
+    assert len(want) == 12 + 4                       # 12 training lines, evaluations at 0, 4, 8 and 12
+    assert len(got) == len(want)
+    num = re.compile(r"-?\d+\.?\d*(?:e[-+]?\d+)?")
+    for g, w in zip(got, want):
+        assert num.sub("#", g) == num.sub("#", w), (g, w)          # the same text around the numbers
+        for x, y in zip(num.findall(g), num.findall(w)):
+            # printed with three decimals: a last-digit flip from fp32 summation order is not a difference
+            assert x == y or abs(float(x) - float(y)) <= max(1.5e-3, 2e-5 * abs(float(y))), (g, w)
