@@ -42,9 +42,13 @@ def _log_lines(text):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model,opt", [("enoki", "dana-star-mk4"), ("qwen3", "adana")])
-def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt):
+@pytest.mark.parametrize("model,opt,ranks", [("enoki", "dana-star-mk4", 1), ("qwen3", "adana", 1), ("enoki", "dana-star-mk4", 2)],
+                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo"])
+def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt, ranks):
+    """`ranks` = 2: both sides under torchrun with `--distributed_backend gloo` (data-parallel: the global batch is
+    split over the ranks, gradients are averaged), rank 0's log compared."""
     import os
+    import socket
 
     data = tmp_path / "data" / "fineweb-10BT"
     data.mkdir(parents=True)
@@ -60,11 +64,25 @@ def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model
              "cos_inf", "--iterations", "12", "--eval_interval", "4", "--eval_batches", "2", "--log_interval", "1",
              "--device", "cpu", "--dtype", "float32", "--seed", "3", "--dropout", "0.0"]
     env = {**os.environ, "TORCHDYNAMO_DISABLE": "1", "OMP_NUM_THREADS": "2", "WANDB_MODE": "disabled"}
-    ref = subprocess.run([sys.executable, "-c", REF_LAUNCHER, str(ref_src), *flags, "--results_base_folder", str(tmp_path / "ref")],
+    launcher = tmp_path / "ref_launcher.py"
+    launcher.write_text(REF_LAUNCHER)
+
+    def python(*tail):
+        if ranks == 1:
+            return [sys.executable, *tail]
+        with socket.socket() as sock:
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
+        return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
+                "127.0.0.1", "--master-port", str(port), *tail]
+
+    if ranks > 1:
+        flags += ["--distributed_backend", "gloo"]
+    ref = subprocess.run(python(str(launcher), str(ref_src), *flags, "--results_base_folder", str(tmp_path / "ref")),
                          capture_output=True, text=True, timeout=600, env=env)
     assert ref.returncode == 0, ref.stdout[-1500:] + ref.stderr[-1500:]
-    ours = subprocess.run([sys.executable, "-m", "adana_b200.main", *flags, "--init_compat", "reference",
-                           "--results_base_folder", str(tmp_path / "ours")],
+    ours = subprocess.run(python("-m", "adana_b200.main", *flags, "--init_compat", "reference",
+                                 "--results_base_folder", str(tmp_path / "ours")),
                           capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert ours.returncode == 0, ours.stdout[-1500:] + ours.stderr[-1500:]
     want, got = _log_lines(ref.stdout), _log_lines(ours.stdout)
