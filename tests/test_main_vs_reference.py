@@ -42,11 +42,14 @@ def _log_lines(text):
 
 
 @pytest.mark.timeout(900)
-@pytest.mark.parametrize("model,opt,ranks", [("enoki", "dana-star-mk4", 1), ("qwen3", "adana", 1), ("enoki", "dana-star-mk4", 2)],
-                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo"])
-def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt, ranks):
-    """`ranks` = 2: both sides under torchrun with `--distributed_backend gloo` (data-parallel: the global batch is
-    split over the ranks, gradients are averaged), rank 0's log compared."""
+@pytest.mark.parametrize("model,opt,ranks,ours_backend",
+                         [("enoki", "dana-star-mk4", 1, None), ("qwen3", "adana", 1, None), ("enoki", "dana-star-mk4", 2, "gloo"),
+                          ("enoki", "dana-star-mk4", 2, "fsdp")],
+                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo", "enoki-2ranks-sharded-engine"])
+def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt, ranks, ours_backend):
+    """`ranks` = 2: both sides under torchrun, the reference with `--distributed_backend gloo` (data-parallel: the
+    global batch is split over the ranks, gradients are averaged), this side with the same or with `fsdp` (the
+    sharded engine on CPU ranks: reduce-scatter, sharded optimizer step, all-gather); rank 0's log compared."""
     import os
     import socket
 
@@ -76,12 +79,14 @@ def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model
         return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
                 "127.0.0.1", "--master-port", str(port), *tail]
 
-    if ranks > 1:
-        flags += ["--distributed_backend", "gloo"]
-    ref = subprocess.run(python(str(launcher), str(ref_src), *flags, "--results_base_folder", str(tmp_path / "ref")),
+    ref_flags = flags + (["--distributed_backend", "gloo"] if ranks > 1 else [])
+    our_flags = flags + (["--distributed_backend", ours_backend] if ranks > 1 else [])
+    if ours_backend == "fsdp":
+        env["ADANA_FSDP_CPU"] = "1"
+    ref = subprocess.run(python(str(launcher), str(ref_src), *ref_flags, "--results_base_folder", str(tmp_path / "ref")),
                          capture_output=True, text=True, timeout=600, env=env)
     assert ref.returncode == 0, ref.stdout[-1500:] + ref.stderr[-1500:]
-    ours = subprocess.run(python("-m", "adana_b200.main", *flags, "--init_compat", "reference",
+    ours = subprocess.run(python("-m", "adana_b200.main", *our_flags, "--init_compat", "reference",
                                  "--results_base_folder", str(tmp_path / "ours")),
                           capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert ours.returncode == 0, ours.stdout[-1500:] + ours.stderr[-1500:]
