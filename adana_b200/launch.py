@@ -148,8 +148,9 @@ def plan(a, extra: List[str]) -> Plan:
         argv.append("--auto_resume")
     if a.iterations_to_run is not None:
         argv += ["--iterations_to_run", a.iterations_to_run]
-    if a.z_loss_coeff is not None:
-        argv += ["--z_loss_coeff", a.z_loss_coeff]
+    # passed explicitly, as the reference's launcher does (scripts/launch.sh:351-369), whatever the parser defaults are
+    argv += ["--config_format", "base", "--dropout", 0.0, "--seed", 0,
+             "--z_loss_coeff", a.z_loss_coeff if a.z_loss_coeff is not None else os.environ.get("Z_LOSS_COEFF", "1e-4")]
     if a.wandb_group:
         argv += ["--wandb_group", a.wandb_group, "--run_prefix", a.wandb_group]
     for key in ("DATASETS_DIR", "RESULTS_BASE_FOLDER"):

@@ -1,6 +1,9 @@
 """Launcher and experiment drivers: derived hyper-parameters, command construction, log parsing."""
 import math
 
+import pytest
+from pathlib import Path
+
 from adana_b200 import experiments, launch
 
 
@@ -62,3 +65,84 @@ def test_user_config_file_is_loaded_without_overriding_the_environment(tmp_path,
     monkeypatch.setenv("HOME", "/keep")
     loaded = experiments.load_user_config(str(f))
     assert loaded["WANDB_PROJECT"] == "proj" and os.environ["DATASETS_DIR"] == "/data/x" and os.environ["HOME"] == "/keep"
+
+
+def test_launcher_builds_the_same_training_command_as_the_reference_launch_script(ref_src, tmp_path):
+    """`scripts/launch.sh` of the reference is run with a stand-in `torchrun` that only prints its arguments; the flags
+    it would hand to `main.py` (model shape, learning rate, weight decay, its time scale, iterations, warm-up, schedule,
+    optimizer flags, compile / resume switches) must equal those of `python -m adana_b200.launch --dry`."""
+    import itertools
+    import os
+    import shlex
+    import shutil
+    import subprocess
+    import sys
+
+    script = ref_src.parent / "scripts" / "launch.sh"
+    if not script.exists() or shutil.which("bash") is None:
+        pytest.skip("the reference's launch script or bash is not available")
+    fake = tmp_path / "bin"
+    fake.mkdir()
+    (fake / "torchrun").write_text("#!/bin/bash\necho \"FAKE_TORCHRUN $@\"\n")
+    (fake / "torchrun").chmod(0o755)
+    env = {k: v for k, v in os.environ.items() if k not in ("DATASETS_DIR", "RESULTS_BASE_FOLDER", "WANDB_PROJECT", "WANDB_ENTITY")}
+    env["PATH"] = f"{fake}:{env['PATH']}"
+    root = Path(__file__).resolve().parent.parent
+
+    def parse(tokens):
+        flags, i = {}, 0
+        while i < len(tokens):
+            t = tokens[i]
+            if t.startswith("--") and "=" in t:
+                k, v = t.split("=", 1)
+                flags[k] = v
+                i += 1
+            elif t.startswith("--") and i + 1 < len(tokens) and not tokens[i + 1].startswith("--"):
+                flags[t] = tokens[i + 1]
+                i += 2
+            else:
+                if t.startswith("--"):
+                    flags[t] = True
+                i += 1
+        return flags
+
+    def reference(args):
+        out = subprocess.run(["bash", "scripts/launch.sh", *args], cwd=ref_src.parent, env=env, capture_output=True,
+                             text=True, timeout=120).stdout
+        line = [ln for ln in out.splitlines() if ln.startswith("FAKE_TORCHRUN")]
+        if not line:
+            assert "ERROR" in out, out[-500:]        # e.g. no learning-rate law for this optimizer and no --lr
+            return None
+        return parse(shlex.split(line[0])[1:])
+
+    def ours(args):
+        out = subprocess.run([sys.executable, "-m", "adana_b200.launch", *args, "--dry"], cwd=root, env=env,
+                             capture_output=True, text=True, timeout=120)
+        line = [ln for ln in out.stdout.splitlines() if "adana_b200.main" in ln]
+        if not line:
+            assert out.returncode != 0
+            return None
+        return parse(shlex.split(line[-1]))
+
+    cases = [["--arch", arch, "--opt", opt, "--heads", str(heads), "--no_wandb"]
+             for arch, opt, heads in itertools.product(("enoki", "qwen3"), ("adamw", "dana-mk4", "dana-star-mk4", "ademamix",
+                                                                            "d-muon", "adamw-decaying-wd"), (8, 36))
+             if (arch, heads) in (("enoki", 36), ("qwen3", 8))]
+    cases += [["--arch", "enoki", "--opt", "dana-star-mk4", "--heads", "36", "--nproc", "8", "--distributed_backend", "fsdp",
+               "--batch_size", "64", "--acc_steps", "8", "--no_wandb"],
+              ["--arch", "enoki", "--opt", "adana", "--heads", "12", "--kappa", "0.8", "--omega", "2.0", "--wd_ts_const", "1000",
+               "--no_wandb", "--no_compile"],
+              ["--arch", "qwen3", "--opt", "dana-mk4", "--heads", "16", "--lr", "0.003", "--iterations", "5000",
+               "--wd_ts_divisor", "5", "--iterations_to_run", "700", "--no_wandb"]]
+    ignore = {"--datasets_dir", "--results_base_folder", "--master-addr", "--master-port", "--nnodes", "--standalone"}
+    for args in cases:
+        want, got = reference(args), ours(args)
+        assert (want is None) == (got is None), args       # refused by both or by neither
+        if want is None:
+            continue
+        assert want.pop("--nproc_per_node") == got.pop("--nproc-per-node", got.pop("--nproc_per_node", None))
+        for key in (set(want) | set(got)) - ignore:
+            a, b = want.get(key), got.get(key)
+            if a == b:
+                continue
+            assert a is not None and b is not None and abs(float(a) - float(b)) <= 1e-12 * max(1.0, abs(float(a))), (args, key, a, b)
