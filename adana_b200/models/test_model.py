@@ -1,5 +1,7 @@
-"""`--model test`: the smallest RoPE + GELU decoder, weight-only LayerNorm (named RMSNorm2 upstream),
-full-logit cross entropy.  Kept for quick experiments (reference: src/models/test.py:1-238)."""
+"""`--model test`: the smallest RoPE + GELU decoder, weight-only LayerNorm with eps = `--rmsnorm_eps` (named RMSNorm2
+upstream), a bias-free 4x GELU MLP whose first matrix is called `w1`, token embedding always tied to the head,
+full-logit cross entropy.  Kept for quick experiments, with the reference's parameter names
+(src/models/test.py:1-238)."""
 from __future__ import annotations
 
 import torch
@@ -8,17 +10,27 @@ import torch.nn.functional as F
 
 from ..ops.rope import precompute_freqs_cis
 from .common import BaseLM, LayerNorm, cfg_get, init_module_weights
-from .gpt import MLP
 from .llama import LlamaAttention
+
+
+class TestMLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.w1 = nn.Linear(config.n_embd, 4 * config.n_embd, bias=False)
+        self.c_proj = nn.Linear(4 * config.n_embd, config.n_embd, bias=False)
+
+    def forward(self, x):
+        return self.c_proj(F.gelu(self.w1(x))), {}
 
 
 class TestBlock(nn.Module):
     def __init__(self, config):
         super().__init__()
-        self.ln_1 = LayerNorm(config.n_embd, bias=False)
+        eps = cfg_get(config, "rmsnorm_eps", 1e-5)
+        self.ln_1 = LayerNorm(config.n_embd, bias=False, eps=eps)
         self.attn = LlamaAttention(config)
-        self.ln_2 = LayerNorm(config.n_embd, bias=False)
-        self.mlp = MLP(config)
+        self.ln_2 = LayerNorm(config.n_embd, bias=False, eps=eps)
+        self.mlp = TestMLP(config)
 
     def forward(self, x, freqs_cis):
         x = x + self.attn(self.ln_1(x), freqs_cis)
@@ -36,11 +48,10 @@ class Test(BaseLM):
             wte=nn.Embedding(config.vocab_size, config.n_embd),
             drop=nn.Dropout(config.dropout),
             h=nn.ModuleList([TestBlock(config) for _ in range(config.n_layer)]),
-            ln_f=LayerNorm(config.n_embd, bias=False),
+            ln_f=LayerNorm(config.n_embd, bias=False, eps=cfg_get(config, "rmsnorm_eps", 1e-5)),
         ))
         self.lm_head = nn.Linear(config.n_embd, config.vocab_size, bias=False)
-        if config.weight_tying:
-            self.transformer.wte.weight = self.lm_head.weight
+        self.transformer.wte.weight = self.lm_head.weight      # always tied, whatever --weight_tying says
         self.apply(lambda m: init_module_weights(m, cfg_get(config, "init_scheme", "KarpathyGPT2"),
                                                  cfg_get(config, "init_std", 0.02)))
 

@@ -18,6 +18,18 @@ CASES = {
     "qwen3-moe": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--moe", "--moe_num_experts", "4",
                   "--moe_num_experts_per_tok", "2"],
     "base-moe": ["--model", "base", "--moe", "--moe_num_experts", "4", "--moe_num_experts_per_tok", "2"],
+    "test": ["--model", "test"],
+    "base-parallel-block": ["--model", "base", "--parallel_block"],
+    "enoki-bias": ["--model", "enoki", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--bias", "True"],
+    "qwen3-as-launched": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--elementwise_attn_output_gate",
+                          "--normalization_layer_type", "rmsnorm", "--weight_tying", "False"],
+    "qwen3-moe-shared-expert": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--moe", "--moe_num_experts", "4",
+                                "--moe_num_experts_per_tok", "2", "--moe_num_shared_experts", "1"],
+    "qwen3-moe-expert-choice": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--moe", "--moe_num_experts", "4",
+                                "--moe_routing", "expert_choice"],
+    "qwen3next-moe": ["--model", "qwen3next", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--moe", "--moe_num_experts", "4",
+                      "--moe_num_experts_per_tok", "2"],
+    "llama-moe": ["--model", "llama", "--multiple_of", "32", "--moe", "--moe_num_experts", "4", "--moe_num_experts_per_tok", "2"],
 }
 _REF_TOP = ("config", "models", "optim", "data", "distributed", "logger")
 
