@@ -53,7 +53,9 @@ def _reference_model(ref_src, argv, monkeypatch):
         parser.add_argument("--config_format", default="base")
         args = ref_config.parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv)
         torch.manual_seed(0)
-        return ref_get_model(args)
+        model = ref_get_model(args)
+        model._group_specs = model.get_parameter_group_specs()     # imports its packages lazily: ask while they resolve
+        return model
     finally:
         sys.path.remove(str(ref_src))
         _forget_reference_modules()
@@ -75,6 +77,9 @@ def test_model_equals_the_reference_class_on_the_reference_weights(ref_src, name
     assert set(ref_sd) == set(ours.state_dict())                      # checkpoint-compatible names
     for k, v in ours.state_dict().items():
         assert v.shape == ref_sd[k].shape, k
+    # the same split into decayed and undecayed parameters (what weight decay is applied to)
+    canon = lambda specs: sorted((tuple(sorted(g["params"])), repr({k: v for k, v in g.items() if k != "params"})) for g in specs)
+    assert canon(ours.get_parameter_group_specs()) == canon(ref._group_specs)
     ours.load_state_dict(ref_sd)
     ref.eval()
     ours.eval()
