@@ -316,9 +316,12 @@ class MARS(Optimizer):
                  weight_decay_1d=0.1):
         if mars_type not in ("mars-adamw", "mars-lion", "mars-shampoo"):
             raise ValueError(mars_type)
-        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, gamma=gamma,
-                                      is_approx=is_approx, mars_type=mars_type, optimize_1d=optimize_1d, lr_1d=lr_1d,
-                                      betas_1d=betas_1d, weight_decay_1d=weight_decay_1d))
+        # the same group keys as the reference (src/optim/mars.py:141-163), so that `state_dict()`s interchange; the
+        # approximation switch and the 1-D learning rate / betas are attributes there and here
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad,
+                                      mars_type=mars_type, gamma=gamma, optimize_1d=optimize_1d,
+                                      weight_decay_1d=weight_decay_1d))
+        self.is_approx, self.lr_1d, self.betas_1d = is_approx, lr_1d, betas_1d
 
     @torch.no_grad()
     def update_last_grad(self):
@@ -363,14 +366,14 @@ class MARS(Optimizer):
                     p.mul_(1 - g["lr"] * g["weight_decay"])
                     p.add_(upd, alpha=-g["lr"])
                 else:
-                    c1, c2 = g["betas_1d"]
+                    c1, c2 = self.betas_1d
                     st["exp_avg"].mul_(c1).add_(grad, alpha=1 - c1)
                     st["exp_avg_sq"].mul_(c2).addcmul_(grad, grad, value=1 - c2)
                     upd = (st["exp_avg"] / (1 - c1 ** t)) / ((st["exp_avg_sq"] / (1 - c2 ** t)).sqrt() + g["eps"])
-                    p.mul_(1 - g["lr_1d"] * g["weight_decay_1d"])
-                    p.add_(upd, alpha=-g["lr_1d"])
+                    p.mul_(1 - self.lr_1d * g["weight_decay_1d"])
+                    p.add_(upd, alpha=-self.lr_1d)
                 st["pending_last"] = grad.detach().clone()
-                if g["is_approx"]:
+                if self.is_approx:
                     st["last_grad"] = st["pending_last"]
 
 
@@ -379,7 +382,8 @@ class _ScheduleFree(Optimizer):
     c_t-weighted average of z; `.eval()` swaps the parameters to x, `.train()` back to y."""
 
     def __init__(self, params, defaults):
-        defaults.update(train_mode=True, k=0, weight_sum=0.0, lr_max=-1.0)
+        # as in the reference (src/optim/schedulefree.py:66-79): not in train mode until `.train()` is called
+        defaults.update(train_mode=False, k=0, weight_sum=0.0, lr_max=-1.0, scheduled_lr=0.0)
         super().__init__(params, defaults)
 
     def _beta(self, g):
@@ -407,6 +411,11 @@ class _ScheduleFree(Optimizer):
     def eval(self):
         self._swap(False)
 
+    def _require_train_mode(self):
+        if not self.param_groups[0]["train_mode"]:
+            raise RuntimeError("Optimizer was not in train mode when step is called: call .train() before training "
+                               "steps and .eval() before evaluation or checkpointing")
+
     def _schedule(self, g):
         k = g["k"]
         sched = (k + 1) / g["warmup_steps"] if k < g["warmup_steps"] else 1.0
@@ -430,6 +439,7 @@ class AdamWScheduleFree(_ScheduleFree):
 
     @torch.no_grad()
     def step(self, closure=None):
+        self._require_train_mode()
         for g in self.param_groups:
             b1, b2 = g["betas"]
             bc2 = 1 - b2 ** (g["k"] + 1)
@@ -464,9 +474,10 @@ class SGDScheduleFree(_ScheduleFree):
 
     @torch.no_grad()
     def step(self, closure=None):
+        self._require_train_mode()
         for g in self.param_groups:
             b = g["momentum"]
-            lr = g["lr"] * self._schedule(g)
+            lr = g["scheduled_lr"] = g["lr"] * self._schedule(g)
             ck = self._weights(g, lr)
             for p in g["params"]:
                 if p.grad is None:
