@@ -131,3 +131,47 @@ def test_batch_order_equals_the_reference_reader(ref_src, monkeypatch):
         for _ in range(20):
             (xa, ya), (xb, yb) = a.sample_batch(), b.sample_batch()
             assert torch.equal(xa, xb) and torch.equal(ya, yb)
+
+
+def test_multi_file_reader_equals_the_reference_reader(ref_src, monkeypatch, tmp_path, capsys):
+    """Four token files, 400 batches (several file switches): the same batches as the reference's
+    MultiFileDataReader, the same `state_dict()` keys, and each side resumes from the other's state."""
+    import copy
+    import importlib
+    import sys
+    import types
+
+    import numpy as np
+    import tiktoken
+    import torch
+
+    from adana_b200.data.readers import MultiFileDataReader
+
+    monkeypatch.setattr(tiktoken, "get_encoding", lambda name: types.SimpleNamespace(name=name))
+    if "adana_refdata" not in sys.modules:
+        pkg = types.ModuleType("adana_refdata")
+        pkg.__path__ = [str(ref_src / "data")]
+        sys.modules["adana_refdata"] = pkg
+    ref = importlib.import_module("adana_refdata.utils")
+    rng = np.random.default_rng(0)
+    files = {}
+    for i in range(4):
+        f = tmp_path / f"train_{i:04d}.bin"
+        rng.integers(0, 50000, size=20000 + 1000 * i).astype(np.uint16).tofile(f)
+        files[f"train_{i:04d}"] = str(f)
+    kw = dict(local_batch_size=4, sequence_length=64, seed=11, with_replacement=False, auto_shard=False, keep_in_ram=True)
+    a, b = MultiFileDataReader(data_files=files, **kw), ref.MultiFileDataReader(data_files=files, **kw)
+    a.set_step(0)
+    b.set_step(0)
+    for _ in range(400):
+        (xa, ya), (xb, yb) = a.sample_batch(), b.sample_batch()
+        assert torch.equal(xa, xb) and torch.equal(ya, yb)
+    sa, sb = a.state_dict(), b.state_dict()
+    assert set(sa) == set(sb) and sa["step"] == sb["step"] and sa["current_file_idx"] == sb["current_file_idx"]
+    a2, b2 = MultiFileDataReader(data_files=files, **kw), ref.MultiFileDataReader(data_files=files, **kw)
+    a2.load_state_dict(copy.deepcopy(sb))
+    b2.load_state_dict(copy.deepcopy(sa))
+    for _ in range(50):
+        x = a.sample_batch()[0]
+        assert torch.equal(x, b.sample_batch()[0]) and torch.equal(x, a2.sample_batch()[0]) and torch.equal(x, b2.sample_batch()[0])
+    capsys.readouterr()
