@@ -297,7 +297,10 @@ class CombinedScheduler:
             else:
                 continue
             self.schedulers.append(s)
-            break  # one scheduler drives every group of the optimizer
+            if cfg.scheduler == "linear":
+                break  # OneCycleLR already carries every group's peak rate
+            # otherwise one (identical, idempotent) LambdaLR per parameter group, as the reference keeps them
+            # (src/optim/muon.py:718-738): its checkpoints hold `scheduler_0 .. scheduler_{G-1}`
 
     def step(self):
         for s in self.schedulers:

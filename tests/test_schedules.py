@@ -87,3 +87,40 @@ def test_schedules_equal_the_reference_functions(ref_src):
     for power, sat, scale in ((-0.5, 0.0, 1.0), (-1.0, 0.1, 10.0), (-0.25, 0.0, 100.0)):
         same(mine.powerlaw_schedule_with_warmup(400, 40, 1.0, sat, power, scale),
              ref.powerlaw_schedule_with_warmup(400, 40, 1.0, sat, power, scale), 400)
+
+
+@pytest.mark.parametrize("sched", ["cos_inf", "wsd"])
+def test_combined_scheduler_equals_the_reference(ref_src, sched):
+    """The Muon scheduler wrapper: same learning rates step by step and the same `state_dict()` keys (one entry per
+    parameter group) as the reference's CombinedScheduler."""
+    import importlib
+    import sys
+    import types
+    import warnings
+
+    from adana_b200.config import flags
+    from adana_b200.optim import muon as mine
+
+    torch.compiler.set_stance("force_eager")
+    if "adana_refoptim" not in sys.modules:
+        pkg = types.ModuleType("adana_refoptim")
+        pkg.__path__ = [str(ref_src / "optim")]
+        sys.modules["adana_refoptim"] = pkg
+    ref = importlib.import_module("adana_refoptim.muon")
+    cfg = flags.defaults()
+    cfg.iterations, cfg.warmup_steps, cfg.scheduler, cfg.lr = 50, 5, sched, 0.02
+    out = []
+    for mod in (ref, mine):
+        ps = [torch.nn.Parameter(torch.randn(8, 4)), torch.nn.Parameter(torch.randn(6))]
+        opt = mod.DistributedMuon([{"params": [ps[0]]}, {"params": [ps[1]], "weight_decay": 0.0}], lr=0.02)
+        s = mod.CombinedScheduler(opt, cfg)
+        lrs = []
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")        # scheduler stepped without an optimizer step
+            for _ in range(50):
+                s.step()
+                lrs.append([g["lr"] for g in opt.param_groups])
+        out.append((lrs, sorted(s.state_dict())))
+    assert out[0][1] == out[1][1] == ["scheduler_0", "scheduler_1"]
+    for a, b in zip(out[0][0], out[1][0]):
+        assert a == pytest.approx(b, rel=1e-12)
