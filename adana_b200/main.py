@@ -34,7 +34,10 @@ EXP_NAME_IGNORE = ["eval_interval", "full_eval_at", "distributed_backend", "late
                    "permanent_ckpt_interval", "wandb", "wandb_project", "wandb_entity", "wandb_group",
                    "results_base_folder", "run_prefix", "wandb_run_prefix", "plot_router_logits", "auto_resume",
                    "resume_from", "device", "seed", "resume_from_swa", "datasets_dir", "iterations_to_run",
-                   "async_checkpoint", "device_timing", "nvtx", "heartbeat_timeout"]
+                   "async_checkpoint", "device_timing", "nvtx", "heartbeat_timeout",
+                   # not flags of the reference's parser: a value derived in get_args, and the switch that only makes
+                   # the initial weights those of the reference (same directory as the reference's run)
+                   "adema_alpha", "init_compat"]
 
 
 def get_args(argv=None):

@@ -99,3 +99,59 @@ def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model
         for x, y in zip(num.findall(g), num.findall(w)):
             # printed with three decimals: a last-digit flip from fp32 summation order is not a difference
             assert x == y or abs(float(x) - float(y)) <= max(1.5e-3, 2e-5 * abs(float(y))), (g, w)
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("first", ["reference", "ours"])
+def test_a_run_started_by_one_code_base_is_resumed_by_the_other(ref_src, tmp_path, first):
+    """Switching in the middle of a run: one side trains iterations 1-6 (`--iterations_to_run 6`) and leaves its
+    `ckpts/latest`; the other is started with the same flags and `--auto_resume` in the same results folder, finds the
+    same experiment directory (equal directory names), restores model, optimizer, scheduler, RNG and data position,
+    and trains 7-12.  Those log lines must equal the ones of an uninterrupted run of the reference."""
+    import os
+
+    data = tmp_path / "data" / "fineweb-10BT"
+    data.mkdir(parents=True)
+    rng = np.random.default_rng(0)
+    p = 1.0 / np.arange(1, 513)
+    p /= p.sum()
+    rng.choice(512, size=300000, p=p).astype(np.uint16).tofile(data / "train.bin")
+    rng.choice(512, size=40000, p=p).astype(np.uint16).tofile(data / "val.bin")
+    flags = ["--model", "enoki", "--n_layer", "2", "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim",
+             "128", "--sequence_length", "64", "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset",
+             "fineweb", "--datasets_dir", str(tmp_path / "data"), "--opt", "dana-star-mk4", "--kappa", "0.85", "--clipsnr",
+             "2.0", "--wd_decaying", "--wd_ts", "5", "--weight_decay", "0.1", "--lr", "1e-3", "--warmup_steps", "2",
+             "--scheduler", "cos_inf", "--iterations", "12", "--eval_interval", "4", "--eval_batches", "2", "--log_interval",
+             "1", "--device", "cpu", "--dtype", "float32", "--seed", "3", "--dropout", "0.0", "--latest_ckpt_interval", "6"]
+    env = {**os.environ, "TORCHDYNAMO_DISABLE": "1", "OMP_NUM_THREADS": "2", "WANDB_MODE": "disabled"}
+    launcher = tmp_path / "ref_launcher.py"
+    launcher.write_text(REF_LAUNCHER)
+
+    def reference(folder, *extra):
+        r = subprocess.run([sys.executable, str(launcher), str(ref_src), *flags, "--results_base_folder", str(folder), *extra],
+                           capture_output=True, text=True, timeout=600, env=env)
+        assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+        return r.stdout
+
+    def ours(folder, *extra):
+        r = subprocess.run([sys.executable, "-m", "adana_b200.main", *flags, "--init_compat", "reference",
+                            "--results_base_folder", str(folder), *extra],
+                           capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+        assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+        return r.stdout
+
+    whole = _log_lines(reference(tmp_path / "whole"))
+    starter, finisher = (reference, ours) if first == "reference" else (ours, reference)
+    starter(tmp_path / "switch", "--iterations_to_run", "6")
+    out = finisher(tmp_path / "switch", "--auto_resume")
+    assert "Resuming Training From" in out
+    assert len(list((tmp_path / "switch").iterdir())) == 1          # both used the same experiment directory
+    got = [ln for ln in _log_lines(out) if int(re.search(r"Iter=(\d+)", ln).group(1)) > 6]
+    want = [ln for ln in whole if int(re.search(r"Iter=(\d+)", ln).group(1)) > 6]
+    num = re.compile(r"-?\d+\.?\d*(?:e[-+]?\d+)?")
+    # the finisher prints its closing evaluation (and, on this side, the last training line) a second time
+    assert got[:len(want)] == want or all(
+        num.sub("#", g) == num.sub("#", w) and all(x == y or abs(float(x) - float(y)) <= max(1.5e-3, 2e-5 * abs(float(y)))
+                                                      for x, y in zip(num.findall(g), num.findall(w)))
+        for g, w in zip(got, want)), (got, want)
+    assert len(got) >= len(want) == 8
