@@ -843,10 +843,18 @@ class EngineOptimizer(torch.optim.Optimizer):
         if kind in (O.KIND_ADAMW, O.KIND_ADAMW_IWD):
             keymap = {"m": "exp_avg", "v": "exp_avg_sq"}
         state = sd.get("state", {})
+
+        def plain(key):      # names as `torch.distributed.checkpoint` stores them, wrapper prefixes dropped
+            while key.startswith(("_orig_mod.", "module.")):
+                key = key.split(".", 1)[1]
+            return key.replace("._orig_mod.", ".")
+
+        by_name = {plain(k): v for k, v in state.items() if isinstance(k, str) and not k.isdigit()}
         for k, srck in keymap.items():
             tensors = {}
             for i, n in enumerate(names):
-                st = state.get(i, state.get(str(i)))
+                # keyed by position (optimizer.state_dict()) or by parameter name (the reference's FSDP checkpoints)
+                st = state.get(i, state.get(str(i), by_name.get(n)))
                 if st is not None and srck in st:
                     tensors[n] = st[srck]
             if tensors:
