@@ -155,3 +155,12 @@ def test_a_run_started_by_one_code_base_is_resumed_by_the_other(ref_src, tmp_pat
                                                       for x, y in zip(num.findall(g), num.findall(w)))
         for g, w in zip(got, want)), (got, want)
     assert len(got) >= len(want) == 8
+    if first == "ours":
+        # the reference wrote `ckpts/latest/main.pt` and `summary.json` last: the inference tool reads its run directory
+        import torch
+
+        from adana_b200 import inference
+
+        model = inference.load_model(next((tmp_path / "switch").iterdir()))
+        toks = list(inference.generate_tokens(model, torch.tensor([[1, 2, 3]]), 3, temperature=0.0))
+        assert len(toks) == 3
