@@ -321,7 +321,10 @@ class MARS(Optimizer):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad,
                                       mars_type=mars_type, gamma=gamma, optimize_1d=optimize_1d,
                                       weight_decay_1d=weight_decay_1d))
-        self.is_approx, self.lr_1d, self.betas_1d = is_approx, lr_1d, betas_1d
+        self.is_approx, self.betas_1d = is_approx, betas_1d
+        # the 1-D tensors follow the schedule too: their rate is the group's current lr times this constant ratio
+        # (src/optim/mars.py:163, 84-86)
+        self.lr_1d_factor = lr_1d / lr
 
     @torch.no_grad()
     def update_last_grad(self):
@@ -348,7 +351,7 @@ class MARS(Optimizer):
                     st["last_grad"] = torch.zeros_like(p)
                 st["step"] += 1
                 t = st["step"]
-                if p.dim() >= 2 or g["optimize_1d"]:
+                if p.dim() == 2 or g["optimize_1d"]:
                     c = grad + g["gamma"] * (b1 / (1 - b1)) * (grad - st["last_grad"])
                     n = c.norm()
                     if n > 1.0:
@@ -370,8 +373,9 @@ class MARS(Optimizer):
                     st["exp_avg"].mul_(c1).add_(grad, alpha=1 - c1)
                     st["exp_avg_sq"].mul_(c2).addcmul_(grad, grad, value=1 - c2)
                     upd = (st["exp_avg"] / (1 - c1 ** t)) / ((st["exp_avg_sq"] / (1 - c2 ** t)).sqrt() + g["eps"])
-                    p.mul_(1 - self.lr_1d * g["weight_decay_1d"])
-                    p.add_(upd, alpha=-self.lr_1d)
+                    lr_1d = g["lr"] * self.lr_1d_factor
+                    p.mul_(1 - lr_1d * g["weight_decay_1d"])
+                    p.add_(upd, alpha=-lr_1d)
                 st["pending_last"] = grad.detach().clone()
                 if self.is_approx:
                     st["last_grad"] = st["pending_last"]

@@ -378,6 +378,8 @@ class Engine:
                         p.data = torch.empty(0, dtype=torch.float32, device=self.device)
                         p.grad = None
         self.model._engine = self
+        replicated = [params[s.name] for u in self.units if u.shard_len == u.padded for s in u.layout.slots]
+        self._first_param = replicated[0] if replicated else None
 
     # ---------------------------------------------------------------------------------------------
     # forward / backward
@@ -682,6 +684,22 @@ class Engine:
 
     def zero_grad(self):
         self.micro_step = 0
+        if not self._grads_bound():
+            self._bind_grads()
+
+    def _grads_bound(self) -> bool:
+        p = self._first_param
+        return p is None or p.grad is not None
+
+    def _bind_grads(self):
+        """An optimizer that is not the engine's own may have dropped the parameters' `.grad` (`zero_grad(set_to_none=
+        True)`): point them at the engine's gradient buffers again (replicated engines only: sharded ones expose none)."""
+        params = dict(self.model.named_parameters())
+        for u in self.units:
+            if u.shard_len != u.padded:
+                continue
+            for s in u.layout.slots:
+                params[s.name].grad = u.view(u.grads, s)
 
     # ---------------------------------------------------------------------------------------------
     # state dict (full tensors, reference key names) and sharded access

@@ -253,6 +253,12 @@ class Trainer:
         elif cfg.opt == "mars":
             opt.zero_grad(set_to_none=True)
             opt.update_last_grad()
+        if self.engine is not None and cfg.opt in ("sophiag", "mars"):
+            # their branches above drop the gradients the way the reference does (`set_to_none`): restart the engine's
+            # micro-step count and point the parameters' `.grad` back at the engine's gradient buffers
+            self.engine.zero_grad()
+        elif cfg.opt in ("sophiag", "mars"):
+            pass
         elif self.engine is not None:
             self.engine.zero_grad()  # gradient buffers are overwritten by the next first micro-step
         else:

@@ -44,8 +44,9 @@ def _log_lines(text):
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("model,opt,ranks,ours_backend",
                          [("enoki", "dana-star-mk4", 1, None), ("qwen3", "adana", 1, None), ("enoki", "dana-star-mk4", 2, "gloo"),
-                          ("enoki", "dana-star-mk4", 2, "fsdp")],
-                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo", "enoki-2ranks-sharded-engine"])
+                          ("enoki", "dana-star-mk4", 2, "fsdp"), ("enoki", "sophiag", 1, None), ("enoki", "mars", 1, None)],
+                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo", "enoki-2ranks-sharded-engine",
+                              "sophiag-hessian-hook", "mars-last-gradient-hook"])
 def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt, ranks, ours_backend):
     """`ranks` = 2: both sides under torchrun, the reference with `--distributed_backend gloo` (data-parallel: the
     global batch is split over the ranks, gradients are averaged), this side with the same or with `fsdp` (the
@@ -66,6 +67,11 @@ def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model
              "--wd_decaying", "--wd_ts", "5", "--weight_decay", "0.1", "--lr", "1e-3", "--warmup_steps", "2", "--scheduler",
              "cos_inf", "--iterations", "12", "--eval_interval", "4", "--eval_batches", "2", "--log_interval", "1",
              "--device", "cpu", "--dtype", "float32", "--seed", "3", "--dropout", "0.0"]
+    if opt == "sophiag":
+        # optimizers of the zoo run on the engine's gradients; sophiag and mars have hooks after the step that drop
+        # the gradients.  The Hessian refresh itself samples labels from the global RNG, whose state after model
+        # construction is not reproduced here, so it is kept out of these 12 iterations
+        flags += ["--precondition_frequency", "100"]
     env = {**os.environ, "TORCHDYNAMO_DISABLE": "1", "OMP_NUM_THREADS": "2", "WANDB_MODE": "disabled"}
     launcher = tmp_path / "ref_launcher.py"
     launcher.write_text(REF_LAUNCHER)
