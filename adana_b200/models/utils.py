@@ -4,6 +4,9 @@ from __future__ import annotations
 
 def get_model(args):
     name = args.model
+    if getattr(args, "init_compat", "none") == "reference" and name not in ("enoki", "diloco", "qwen3"):
+        # asked-for bit-identical initial weights must not silently become different ones
+        raise NotImplementedError(f"--init_compat reference covers --model enoki, diloco and qwen3, not {name}")
     if name in ("enoki", "diloco"):
         from .enoki import Enoki
 
