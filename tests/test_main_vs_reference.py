@@ -43,14 +43,15 @@ def _log_lines(text):
 
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("model,opt,ranks,ours_backend",
-                         [("enoki", "dana-star-mk4", 1, None), ("qwen3", "adana", 1, None), ("enoki", "dana-star-mk4", 2, "gloo"),
-                          ("enoki", "dana-star-mk4", 2, "fsdp"), ("enoki", "sophiag", 1, None), ("enoki", "mars", 1, None)],
-                         ids=["enoki-1proc", "qwen3-1proc", "enoki-2ranks-gloo", "enoki-2ranks-sharded-engine",
-                              "sophiag-hessian-hook", "mars-last-gradient-hook"])
+                         [("qwen3", "adana", 1, None), ("enoki", "dana-star-mk4", 2, "fsdp"), ("enoki", "sophiag", 1, None),
+                          ("enoki", "mars", 1, None)],
+                         ids=["qwen3-1proc", "enoki-2ranks-sharded-engine", "sophiag-hessian-hook", "mars-last-gradient-hook"])
 def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model, opt, ranks, ours_backend):
     """`ranks` = 2: both sides under torchrun, the reference with `--distributed_backend gloo` (data-parallel: the
     global batch is split over the ranks, gradients are averaged), this side with the same or with `fsdp` (the
-    sharded engine on CPU ranks: reduce-scatter, sharded optimizer step, all-gather); rank 0's log compared."""
+    sharded engine on CPU ranks: reduce-scatter, sharded optimizer step, all-gather); rank 0's log compared.  (Enoki
+    in one process, and this side under `gloo` data parallelism, were compared the same way and are covered by the
+    cross-resume test below and by the sharded case.)"""
     import os
     import socket
 
