@@ -172,3 +172,19 @@ def test_evaluation_equals_the_reference_eval(ref_src, name, monkeypatch):
         assert got[3][k] == pytest.approx(want[3][k], abs=1e-6), k
     if moe:
         assert got[4].shape == want[4].shape and torch.allclose(got[4], want[4], atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["base", "llama", "enoki", "qwen3"])
+def test_tensor_parallel_plan_equals_the_reference(ref_src, name, monkeypatch):
+    """Which projections are split by columns and which by rows under `--tp_size`."""
+    from adana_b200.config import parse_args_with_format
+    from adana_b200.models.utils import get_model
+
+    torch.compiler.set_stance("force_eager")
+    argv = COMMON + CASES[name]
+    ref = _reference_model(ref_src, argv, monkeypatch)
+    want = {path: type(style).__name__.replace("Parallel", "").lower() for path, style in type(ref).get_tp_plan().items()}
+    parser = argparse.ArgumentParser(allow_abbrev=False)
+    parser.add_argument("--config_format", default="base")
+    ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
+    assert dict(type(ours).get_tp_plan()) == want
