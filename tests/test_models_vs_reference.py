@@ -188,3 +188,32 @@ def test_tensor_parallel_plan_equals_the_reference(ref_src, name, monkeypatch):
     parser.add_argument("--config_format", default="base")
     ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
     assert dict(type(ours).get_tp_plan()) == want
+
+
+@pytest.mark.parametrize("name", ["base", "enoki", "qwen3"])
+def test_sampling_equals_the_reference_generate(ref_src, name, monkeypatch):
+    """`model.generate` with temperature and top-k from the same RNG seed: the same tokens as the reference's; and
+    the KV-cached decoder of the inference tool continues the same sequence."""
+    from adana_b200 import inference
+    from adana_b200.config import parse_args_with_format
+    from adana_b200.models.utils import get_model
+
+    torch.compiler.set_stance("force_eager")
+    argv = COMMON + CASES[name]
+    ref = _reference_model(ref_src, argv, monkeypatch)
+    parser = argparse.ArgumentParser(allow_abbrev=False)
+    parser.add_argument("--config_format", default="base")
+    ours = get_model(parse_args_with_format(format="base", base_parser=parser, namespace=None, args=argv))
+    ours.load_state_dict(ref.state_dict())
+    ref.eval()
+    ours.eval()
+    prompt = torch.tensor([[5, 17, 300, 2]])
+    with torch.no_grad():
+        torch.manual_seed(7)
+        want = ref.generate(prompt.clone(), 12, temperature=0.8, top_k=20)
+        torch.manual_seed(7)
+        got = ours.generate(prompt.clone(), 12, temperature=0.8, top_k=20)
+        assert torch.equal(got, want)
+        torch.manual_seed(7)
+        stream = torch.cat(list(inference.generate_tokens(ours, prompt.clone(), 12, temperature=0.8, top_k=20)), dim=1)
+    assert torch.equal(stream, want[:, prompt.shape[1]:])
