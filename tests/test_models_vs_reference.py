@@ -19,6 +19,7 @@ CASES = {
                   "--moe_num_experts_per_tok", "2"],
     "base-moe": ["--model", "base", "--moe", "--moe_num_experts", "4", "--moe_num_experts_per_tok", "2"],
     "test": ["--model", "test"],
+    "diloco": ["--model", "diloco", "--qkv_dim", "64", "--mlp_hidden_dim", "256"],
     "base-parallel-block": ["--model", "base", "--parallel_block"],
     "enoki-bias": ["--model", "enoki", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--bias", "True"],
     "qwen3-as-launched": ["--model", "qwen3", "--qkv_dim", "64", "--mlp_hidden_dim", "256", "--elementwise_attn_output_gate",
