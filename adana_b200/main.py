@@ -166,6 +166,7 @@ def main(args, parser):
         print("number of non-embedding parameters: %.2fM" % (counts[1] / 1e6,))
         print("number of parameters (with all embeddings): %.2fM" % (counts[2] / 1e6,))
         print("number of optimized parameters: %.2fM" % ((n_opt if backend.engine is None else backend.engine.num_params()) / 1e6,))
+    backend.param_counts = (counts[0], n_opt if backend.engine is None else backend.engine.num_params())
 
     opt = build_optimizer(args, model, specs, engine=backend.engine)
     backend.engine_optimizer = hasattr(opt, "engine")

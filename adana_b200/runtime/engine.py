@@ -458,6 +458,10 @@ class Engine:
             hv, hoyer_grad = BK.hoyer_value_and_grad(x0, ecfg.hoyer_loss_coeff, self.loss_scale, need_grad)
             aux["hoyer_loss"] = hv
             loss = loss + ecfg.hoyer_loss_coeff * hv
+        else:
+            # reported even when it does not enter the loss, as the reference's models do (src/models/enoki.py:341-343)
+            with torch.no_grad():
+                aux["hoyer_loss"] = BK.hoyer_value_and_grad(x0, 0.0, self.loss_scale, False)[0]
         accuracy = (out["correct"] / T) if compute_accuracy else None
         if need_grad:
             self._pending = dict(dx=dx, dx_lp=dx_lp, saved=saved, idx=idx_flat, B=B, S=S,

@@ -116,6 +116,9 @@ class Trainer:
         from ..logging.metrics import MetricsSink
 
         self.sink = MetricsSink(self.exp_dir, wandb if (cfg.wandb and wandb is not None) else None, enabled=self.master)
+        counts = getattr(self.backend, "param_counts", None)
+        if counts is not None:      # the first record of a run, as in the reference (src/main.py:376-379)
+            self.sink.log({"parameters": counts[0], "optimized_parameters": counts[1]})
         engine = getattr(self.backend.get_raw_model(self.model), "_engine", None)
         gathers = engine is not None and engine.sharded and engine.world > 1   # then every rank takes part
         if getattr(cfg, "log_dynamics", False) and (self.master or gathers):
@@ -217,6 +220,10 @@ class Trainer:
             raw = self.backend.get_raw_model(self.model)
             gn = self.backend.clip_grad_norm_(raw.parameters(), cfg.grad_clip)
             self.grad_norms.append(gn)  # kept on the device; read only when logging
+        if hasattr(opt, "want_diagnostics"):
+            # the engine's fused optimizer reports the `optimizer/*` schedule metrics only when asked: ask on the
+            # steps whose iteration will be logged
+            opt.want_diagnostics = bool(cfg.log_interval) and (self.curr_iter + 1) % cfg.log_interval == 0
         with nvtx_range("optimizer", cfg):
             if cfg.opt in ("sf-sgd", "sf-adamw"):
                 opt.train()

@@ -171,3 +171,81 @@ def test_a_run_started_by_one_code_base_is_resumed_by_the_other(ref_src, tmp_pat
         model = inference.load_model(next((tmp_path / "switch").iterdir()))
         toks = list(inference.generate_tokens(model, torch.tensor([[1, 2, 3]]), 3, temperature=0.0))
         assert len(toks) == 3
+
+
+FAKE_WANDB = """
+import json, os
+_path = os.environ["FAKE_WANDB_OUT"]
+class _Run:
+    id = "fakeid"; name = "fake"
+    def __getattr__(self, k): return lambda *a, **kw: None
+run = None
+class _Cfg(dict):
+    def update(self, *a, **k): pass
+config = _Cfg()
+def init(*a, **kw):
+    global run
+    run = _Run()
+    return run
+def log(d, *a, **kw):
+    def conv(v):
+        try: return float(v)
+        except Exception: return type(v).__name__
+    with open(_path, "a") as f: f.write(json.dumps({k: conv(v) for k, v in d.items()}) + "\\n")
+def finish(*a, **kw): pass
+def __getattr__(name):
+    return lambda *a, **kw: None
+"""
+
+
+@pytest.mark.timeout(900)
+def test_wandb_records_equal_the_reference(ref_src, tmp_path):
+    """Both command lines with `--wandb` and a stand-in `wandb` module that writes every `wandb.log` call to a file:
+    the same number of records, the same keys in each (what the reference's plotting scripts read: `train/*`,
+    `val/*`, `final-val/*`, `lr`, `iter`, `tokens`, `model_norm`, `parameters`, `optimizer/*`, ...) and the same values.
+    The four `optimizer/*` schedule metrics are compared by key only: the engine's fused optimizer reports them as
+    aggregates over all elements, the reference as means over parameter tensors."""
+    import json
+    import os
+
+    data = tmp_path / "data" / "fineweb-10BT"
+    data.mkdir(parents=True)
+    rng = np.random.default_rng(0)
+    p = 1.0 / np.arange(1, 513)
+    p /= p.sum()
+    rng.choice(512, size=300000, p=p).astype(np.uint16).tofile(data / "train.bin")
+    rng.choice(512, size=40000, p=p).astype(np.uint16).tofile(data / "val.bin")
+    (tmp_path / "stub" / "wandb").mkdir(parents=True)
+    (tmp_path / "stub" / "wandb" / "__init__.py").write_text(FAKE_WANDB)
+    flags = ["--model", "enoki", "--n_layer", "2", "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim",
+             "128", "--sequence_length", "64", "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset",
+             "fineweb", "--datasets_dir", str(tmp_path / "data"), "--opt", "dana-star-mk4", "--kappa", "0.85", "--clipsnr",
+             "2.0", "--wd_decaying", "--wd_ts", "5", "--weight_decay", "0.1", "--lr", "1e-3", "--warmup_steps", "2",
+             "--scheduler", "cos_inf", "--iterations", "8", "--eval_interval", "4", "--eval_batches", "2", "--log_interval",
+             "1", "--device", "cpu", "--dtype", "float32", "--seed", "3", "--dropout", "0.0", "--wandb", "--wandb_project", "p",
+             "--log_parameter_norms"]
+    launcher = tmp_path / "ref_launcher.py"
+    launcher.write_text(REF_LAUNCHER)
+    records = {}
+    for side, cmd in (("ref", [sys.executable, str(launcher), str(ref_src), *flags, "--results_base_folder", str(tmp_path / "ref")]),
+                      ("ours", [sys.executable, "-m", "adana_b200.main", *flags, "--init_compat", "reference",
+                                "--results_base_folder", str(tmp_path / "ours")])):
+        out = tmp_path / f"{side}.jsonl"
+        env = {**os.environ, "TORCHDYNAMO_DISABLE": "1", "OMP_NUM_THREADS": "2", "FAKE_WANDB_OUT": str(out),
+               "PYTHONPATH": f"{tmp_path / 'stub'}{os.pathsep}{ROOT}"}
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT if side == "ours" else None)
+        assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+        records[side] = [json.loads(ln) for ln in out.read_text().splitlines()]
+    want, got = records["ref"], records["ours"]
+    assert len(got) == len(want) and len(want) >= 8 + 3 + 1
+    assert {"parameters", "optimized_parameters"} <= set(want[0])
+    seen = set()
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert set(g) == set(w), (i, sorted(set(g) ^ set(w)))
+        seen |= set(w)
+        for k, v in w.items():
+            if k == "iter_dt" or k.startswith("optimizer/") or not isinstance(v, float):
+                continue
+            assert g[k] == pytest.approx(v, rel=2e-4, abs=1e-6), (i, k, g[k], v)
+    assert {"train/loss", "val/loss", "final-val/loss", "lr", "iter", "tokens", "model_norm", "optimizer/alpha_schedule",
+            "train/z_loss", "train/hoyer_loss"} <= seen
