@@ -168,7 +168,9 @@ def head_forward_backward(x, targets, W, Gd, sp_norm_kind: int, eps: float, z_co
 def hoyer_value_and_grad(x0: torch.Tensor, coeff: float, loss_scale: float, need_grad: bool):
     """Hoyer sparsity term on the token embeddings: mean ||x||_1 / (||x||_2 + 1e-8)."""
     if not need_grad:
-        return (x0.abs().sum(-1) / (x0.norm(dim=-1) + 1e-8)).mean(), None
+        # two row reductions that read x0 once each and write one float per token (no |x| temporary)
+        l1 = torch.linalg.vector_norm(x0, ord=1, dim=-1)
+        return (l1 / (torch.linalg.vector_norm(x0, ord=2, dim=-1) + 1e-8)).mean(), None
     xd = x0.detach().requires_grad_(True)
     with torch.enable_grad():
         val = (xd.abs().sum(-1) / (xd.norm(dim=-1) + 1e-8)).mean()
