@@ -659,8 +659,53 @@ class Engine:
         opt.step_count = t
         self.opt_step_count += 1
         self.micro_step = 0
-        if diag is not None:
+        if opt.want_diagnostics and kind in (O.KIND_ADANA, O.KIND_DANA_STAR):
+            opt.diagnostics = self._per_tensor_optimizer_metrics(opt, kind, t)
+        elif diag is not None:
             opt.absorb_diagnostics(diag, sum(u.layout.numel for u in self.units))
+
+    @torch.no_grad()
+    def _per_tensor_optimizer_metrics(self, opt, kind, t: int) -> Dict[str, float]:
+        """The `optimizer/*` schedule metrics as the per-tensor optimizers define them (src/optim/dana_star_mk4.py:
+        `current_alpha`, `auto_factor_mean`, `current_kappa_factor`, `m_norm` per parameter; src/optim/utils.py
+        `log_optimizer_schedules` averages them over parameters).  They are functions of the state after the update, so
+        they are recomputed from (m, v, tau) one parameter slot at a time on the iterations that log, and the fused step
+        stays free of per-tensor reductions.  A sharded engine sums each slot's partial sums over the ranks."""
+        expo = 1.0 - opt.kappa
+        rows = []
+        for u in self.units:
+            lo, hi = u.shard_off, u.shard_off + u.shard_len
+            for sl in u.layout.slots:
+                a, b = max(sl.offset, lo), min(sl.offset + sl.numel, hi)
+                if a >= b:
+                    rows.append(torch.zeros(3, dtype=torch.float32, device=self.device))
+                    continue
+                grp = opt.param_groups[0] if sl.decay else opt.param_groups[1]
+                eps = grp.get("epsilon", 1e-8)
+                m, v = u.state["m"][a - lo:b - lo], u.state["v"][a - lo:b - lo]
+                denom = torch.sqrt(v).add_(eps)
+                if kind == O.KIND_ADANA:
+                    mfac = m.abs().div_(denom)
+                    af = mfac * float((1.0 + t) ** expo)
+                else:
+                    tau = u.state["tau"][a - lo:b - lo]
+                    ct = tau.clamp(max=0.5)
+                    floor = 1.0 / (1.0 + t)
+                    reg = torch.relu(ct / (1.0 - ct) - floor).add_(floor)
+                    mfac = m.abs().div_(denom).div_(torch.sqrt(reg))
+                    af = (tau * t).clamp_(min=1.0).pow_(expo).mul_(mfac)
+                if opt.clipsnr is not None:
+                    af = af.clamp_(max=opt.clipsnr)
+                rows.append(torch.stack([af.sum(dtype=torch.float64), mfac.sum(dtype=torch.float64),
+                                         (m.double() ** 2).sum()]).float())
+        table = torch.stack(rows)
+        if self.sharded and self.world > 1:
+            self.comm.all_reduce_sum(table)
+        sums = table.double().cpu()
+        n = torch.tensor([float(sl.numel) for u in self.units for sl in u.layout.slots], dtype=torch.float64)
+        alpha, auto = sums[:, 0] / n, sums[:, 1] / n
+        return {"current_alpha": float(alpha.mean()), "auto_factor_mean": float(auto.mean()),
+                "current_kappa_factor": float((alpha / auto).mean()), "m_norm": float(sums[:, 2].sqrt().mean())}
 
     def _after_update(self, u: Unit):
         """Make the unit's compute weights current again after its shard was updated."""
