@@ -114,6 +114,7 @@ def _train_worker(rank, world, sharded, steps, ckpt_dir, save_at):
             (out["loss"] / 2).backward()
             losses.append(out["loss"].item())
         eng.grad_norm_and_clip(0.5)
+        opt.want_diagnostics = step + 1 == steps
         opt.step()
         opt.zero_grad()
         if ckpt_dir and step + 1 == save_at:
@@ -121,7 +122,7 @@ def _train_worker(rank, world, sharded, steps, ckpt_dir, save_at):
             dist.barrier()
     full = eng.full_param_dict("master")
     return {"losses": losses, "params": {k: v.clone() for k, v in full.items()},
-            "norm": float(eng.last_grad_norm), "sharded": eng.sharded,
+            "norm": float(eng.last_grad_norm), "sharded": eng.sharded, "diag": dict(opt.diagnostics),
             "module_param_numel": sum(p.numel() for p in m.parameters())}
 
 
@@ -145,16 +146,22 @@ def _single_reference(steps, world):
                 (out["loss"] / (2 * world)).backward()
                 n += 1
         eng.grad_norm_and_clip(0.5)
+        opt.want_diagnostics = step + 1 == steps
         opt.step()
         opt.zero_grad()
-    return eng.full_param_dict("master"), float(eng.last_grad_norm)
+    return eng.full_param_dict("master"), float(eng.last_grad_norm), dict(opt.diagnostics)
 
 
 @pytest.mark.parametrize("sharded", [True, False])
 def test_two_rank_engine_matches_single_process(sharded):
     res = _spawn(_train_worker, 2, sharded, 3, None, 0)
-    ref_params, ref_norm = _single_reference(3, 2)
+    ref_params, ref_norm, ref_diag = _single_reference(3, 2)
     assert res[0]["sharded"] == sharded
+    # the `optimizer/*` schedule metrics are per-tensor means: a slot cut by the shard boundary is summed over ranks
+    assert set(ref_diag) == {"current_alpha", "auto_factor_mean", "current_kappa_factor", "m_norm"}
+    for r in (0, 1):
+        for k, v in ref_diag.items():
+            assert res[r]["diag"][k] == pytest.approx(v, rel=2e-4), (k, r)
     if sharded:
         assert res[0]["module_param_numel"] == 0          # full fp32 parameters are not kept per rank
     assert res[0]["norm"] == pytest.approx(ref_norm, rel=1e-4)
