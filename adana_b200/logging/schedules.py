@@ -45,7 +45,7 @@ def log_prodigy_lr(opt):
 
 def log_optimizer_schedules(optimizer, optimizer_name):
     """Mean over parameters of the logged per-parameter scalars."""
-    if optimizer_name == "ademamix" or optimizer_name == "ademamix-decaying-wd":
+    if optimizer_name == "ademamix":  # not the decaying-wd variant, as in the reference (src/optim/utils.py:550)
         wanted = ("current_alpha", "current_one_minus_beta3")
     elif optimizer_name in ("adana", "dana-mk4", "dana-star", "dana-star-mk4"):
         wanted = ("current_alpha", "current_kappa_factor", "auto_factor_mean", "g2_gradient_norm", "m_norm")
