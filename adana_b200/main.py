@@ -223,9 +223,14 @@ def _init_wandb(args, exp_name, exp_dir):
     resuming = args.resume_from is not None or (args.auto_resume and checkpoint_exists(exp_dir / "ckpts" / "latest"))
     if resuming and id_file.exists():
         run_id = id_file.read_text().strip()
-    name = exp_name if args.wandb_run_prefix == "none" else f"{args.wandb_run_prefix}_{exp_name}"
-    wandb.init(project=args.wandb_project, entity=args.wandb_entity, group=args.wandb_group, name=name,
-               config=copy.copy(vars(args)), id=run_id, resume="allow" if run_id else None)
+    # The run is named after the experiment directory (`--wandb_run_prefix` is parsed and ignored, as in the reference,
+    # whose plotting scripts look runs up by this name), keeps its files inside that directory, and plots the training
+    # and validation metrics against "iter" (src/main.py:322-338).
+    wandb.init(project=args.wandb_project, entity=args.wandb_entity, group=args.wandb_group, name=exp_name,
+               config=copy.copy(vars(args)), id=run_id or None, resume="allow" if run_id else None, dir=str(exp_dir))
+    wandb.define_metric("iter")
+    for pattern in ("train/*", "val/*", "lr"):
+        wandb.define_metric(pattern, step_metric="iter")
 
 
 def cli(argv=None):

@@ -183,10 +183,17 @@ run = None
 class _Cfg(dict):
     def update(self, *a, **k): pass
 config = _Cfg()
+def _write(d):
+    with open(_path, "a") as f: f.write(json.dumps(d) + "\\n")
 def init(*a, **kw):
     global run
     run = _Run()
+    _write({"__call__": "init", "project": kw.get("project"), "name": kw.get("name"), "group": kw.get("group"),
+            "entity": kw.get("entity"), "id": kw.get("id"), "resume": kw.get("resume"),
+            "dir_tail": os.path.basename(str(kw.get("dir"))), "config_is_args": "sequence_length" in (kw.get("config") or {})})
     return run
+def define_metric(name, **kw):
+    _write({"__call__": "define_metric", "name": name, **kw})
 def log(d, *a, **kw):
     def conv(v):
         try: return float(v)
@@ -236,7 +243,9 @@ def test_wandb_records_equal_the_reference(ref_src, tmp_path):
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT if side == "ours" else None)
         assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
         records[side] = [json.loads(ln) for ln in out.read_text().splitlines()]
-    want, got = records["ref"], records["ours"]
+    calls = {side: [r for r in recs if "__call__" in r] for side, recs in records.items()}
+    assert calls["ours"] == calls["ref"] and calls["ref"][0]["dir_tail"] == calls["ref"][0]["name"]   # init, define_metric
+    want, got = ([r for r in records[side] if "__call__" not in r] for side in ("ref", "ours"))
     assert len(got) == len(want) and len(want) >= 8 + 3 + 1
     assert {"parameters", "optimized_parameters"} <= set(want[0])
     seen = set()
