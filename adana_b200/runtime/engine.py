@@ -599,7 +599,8 @@ class Engine:
         t = opt.step_count + 1
         g_decay, g_nodecay = opt.param_groups[0], opt.param_groups[1]
         diag = None
-        if opt.want_diagnostics:
+        if opt.want_diagnostics and kind not in (O.KIND_ADANA, O.KIND_DANA_STAR):
+            # (the log-time family reports per-tensor metrics instead, recomputed from its state after the step)
             self._diag.zero_()
             diag = self._diag
         for u in self.units:
