@@ -128,6 +128,10 @@ int adana_ce_fwd_bwd(float* logits, long long ld, const long long* targets, int 
                      float z_coeff, float grad_scale, void* dlogits_bf16, long long ldd,
                      float* sums /*[4]: ce, lse^2, correct, valid*/, float* lse_out,
                      void* stream);
+// The same over bf16 logits; dlogits_bf16 may be the logits buffer itself (in place) or null.
+int adana_ce_fwd_bwd_bf16(void* logits, long long ld, const long long* targets, int rows, int vocab, float z_coeff,
+                          float grad_scale, void* dlogits_bf16, long long ldd, float* sums, float* lse_out,
+                          void* stream);
 
 // ---- optimizer (optim.cu) ----------------------------------------------------------------------
 struct AdanaOptHyper {

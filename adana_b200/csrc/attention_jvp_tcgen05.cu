@@ -161,60 +161,69 @@ attn_jvp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop in lock step and one elected lane issues, so that addresses and descriptors are
+    // computed in warp-uniform code (a tcgen05.mma takes them from uniform registers); descriptors are built once
+    // and a product adds the 16-byte-unit offset of its contraction step to the address field.
+    {
+      const bool leader = elect_one();
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc_qk = make_idesc_bf16(JVP_BQ, BKV, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(JVP_BQ, HD, false, true);
-      const uint32_t sQ = smem_u32(smem + C::Q_OFF), sQt = smem_u32(smem + C::QT_OFF);
-      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+      const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + C::Q_OFF), 16, 1024);
+      const uint64_t qt_desc = make_smem_desc_sw128(smem_u32(smem + C::QT_OFF), 16, 1024);
+      const uint64_t ring_k0 = make_smem_desc_sw128(smem_u32(smem + C::RING_OFF), 16, 1024);           // K-major view
+      const uint64_t ring_mn0 = make_smem_desc_sw128(smem_u32(smem + C::RING_OFF), KV_CHUNK, 1024);    // MN-major view
+      constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, KVT16 = C::KV_TILE >> 4;
+      bool ok = mbar_wait_warp(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
       tc_fence_after_sync();
-      // K-major operands: 16 columns of head_dim per MMA step, 64-column chunks of `chunk` bytes
-      auto kdesc = [](uint32_t base, int kk, int chunk) {
-        return make_smem_desc_sw128(base + (kk >> 2) * chunk + (kk & 3) * 32, 16, 1024);
-      };
       // O += P V ; Ot += T V + P Vt for key tile jj (its stage is released afterwards)
       auto issue_pv = [&](int jj) -> bool {
         const int st = jj % JVP_STAGES;
-        if (!mbar_wait(p_full, (uint32_t)jj & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!mbar_wait_warp(p_full, (uint32_t)jj & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
         tc_fence_after_sync();
-        const uint32_t ring = smem_u32(smem + C::RING_OFF + st * C::STAGE_BYTES);
-        const uint32_t sV = ring + 2 * C::KV_TILE, sVt = ring + 3 * C::KV_TILE;
+        const uint64_t dv0 = ring_mn0 + (uint64_t)(st * STAGE16 + 2 * KVT16);
+        const uint64_t dvt0 = ring_mn0 + (uint64_t)(st * STAGE16 + 3 * KVT16);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t dv = make_smem_desc_sw128(sV + kk * 2048, KV_CHUNK, 1024);
-          const uint64_t dvt = make_smem_desc_sw128(sVt + kk * 2048, KV_CHUNK, 1024);
-          const uint32_t acc = (jj > 0 || kk > 0) ? 1u : 0u;
-          umma_ts(tmem_base + C::O_COL, tmem_base + C::P_COL + kk * 8, dv, idesc_pv, acc);
-          umma_ts(tmem_base + C::OT_COL, tmem_base + C::T_COL + kk * 8, dv, idesc_pv, acc);
-          umma_ts(tmem_base + C::OT_COL, tmem_base + C::P_COL + kk * 8, dvt, idesc_pv, 1u);
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            const uint64_t o = (uint64_t)((kk * 2048) >> 4);
+            const uint32_t acc = (jj > 0 || kk > 0) ? 1u : 0u;
+            umma_ts(tb + C::O_COL, tb + C::P_COL + kk * 8, dv0 + o, idesc_pv, acc);
+            umma_ts(tb + C::OT_COL, tb + C::T_COL + kk * 8, dv0 + o, idesc_pv, acc);
+            umma_ts(tb + C::OT_COL, tb + C::P_COL + kk * 8, dvt0 + o, idesc_pv, 1u);
+          }
+          umma_commit(&kv_empty[st]);
+          umma_commit(p_empty);
         }
-        umma_commit(&kv_empty[st]);
-        umma_commit(p_empty);
         return true;
       };
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j % JVP_STAGES;
         const uint32_t kvph = (uint32_t)(j / JVP_STAGES) & 1;
-        if (!mbar_wait(&kv_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
-            !mbar_wait(s_empty, ((uint32_t)j & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        if (!mbar_wait_warp(&kv_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
+            !mbar_wait_warp(s_empty, ((uint32_t)j & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t ring = smem_u32(smem + C::RING_OFF + st * C::STAGE_BYTES);
-        const uint32_t sK = ring, sKt = ring + C::KV_TILE;
+        const uint64_t dk0 = ring_k0 + (uint64_t)(st * STAGE16);
+        const uint64_t dkt0 = dk0 + (uint64_t)KVT16;
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint64_t dq = kdesc(sQ, kk, Q_CHUNK), dqt = kdesc(sQt, kk, Q_CHUNK);
-          const uint64_t dk = kdesc(sK, kk, KV_CHUNK), dkt = kdesc(sKt, kk, KV_CHUNK);
-          umma_ss(tmem_base + C::S_COL, dq, dk, idesc_qk, kk > 0 ? 1u : 0u);
-          umma_ss(tmem_base + C::ST_COL, dqt, dk, idesc_qk, kk > 0 ? 1u : 0u);
-          umma_ss(tmem_base + C::ST_COL, dq, dkt, idesc_qk, 1u);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            // K-major operands: 16 columns of head_dim per step, 64-column chunks Q_CHUNK / KV_CHUNK bytes apart
+            const uint64_t oq = (uint64_t)(((kk >> 2) * Q_CHUNK + (kk & 3) * 32) >> 4);
+            const uint64_t ok_ = (uint64_t)(((kk >> 2) * KV_CHUNK + (kk & 3) * 32) >> 4);
+            umma_ss(tb + C::S_COL, q_desc + oq, dk0 + ok_, idesc_qk, kk > 0 ? 1u : 0u);
+            umma_ss(tb + C::ST_COL, qt_desc + oq, dk0 + ok_, idesc_qk, kk > 0 ? 1u : 0u);
+            umma_ss(tb + C::ST_COL, q_desc + oq, dkt0 + ok_, idesc_qk, 1u);
+          }
+          umma_commit(s_full);
         }
-        umma_commit(s_full);
         if (j > 0) ok = issue_pv(j - 1);
       }
       if (ok) ok = issue_pv(n_kv - 1);
-      if (ok) umma_commit(o_full);
+      if (ok && leader) umma_commit(o_full);
     }
   } else {
     // ------------------------------ softmax + epilogue (warps 2..5) -------------------------

@@ -26,7 +26,7 @@ namespace adana {
 constexpr int ATT_BQ = 128;
 constexpr int ATT_BKV = 128;
 constexpr int ATT_THREADS = 192;
-constexpr int ATT_BWD_THREADS = 320;   // TMA warp, MMA warp, two softmax warpgroups (each takes half of the key columns)
+constexpr int ATT_BWD_THREADS = 448;   // TMA warp, MMA warp, eight score warps (two per lane quarter), four dQ drain warps
 constexpr int ATT_KV_STAGES = 2;
 constexpr float ATT_RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -154,27 +154,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop in lock step and one elected lane issues, so that addresses and descriptors are
+    // computed in warp-uniform code (a tcgen05.mma takes them from uniform registers; inside a one-lane branch every
+    // operand of every product is first moved there, which cost more than the product itself).  Descriptors are built
+    // once; a product adds the 16-byte-unit offset of its contraction step to the address field.
+    {
+      const bool leader = elect_one();
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BQ, HD, false, true);
-      const uint32_t sQ = smem_u32(smem + L::Q_OFF);
-      bool ok = mbar_wait(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+      const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + L::Q_OFF), 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + L::K_OFF), 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + L::V_OFF), CHUNK_BYTES, 1024);
+      constexpr uint32_t TILE16 = L::TILE >> 4;
+      bool ok = mbar_wait_warp(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
       tc_fence_after_sync();
       auto issue_pv = [&](int jj) -> bool {
         const int st = jj % ATT_KV_STAGES;
         const uint32_t kvph = (uint32_t)(jj / ATT_KV_STAGES) & 1;
-        if (!mbar_wait(p_full, (uint32_t)jj & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        if (!mbar_wait(&v_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!mbar_wait_warp(p_full, (uint32_t)jj & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        if (!mbar_wait_warp(&v_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
         tc_fence_after_sync();
-        const uint32_t sV = smem_u32(smem + L::V_OFF + st * L::TILE);
+        const uint64_t v_desc = v_desc0 + (uint64_t)(st * TILE16);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < ATT_BKV / 16; ++kk) {
-          // A = P_j straight from tensor memory: 16 keys = 8 columns of packed bf16 pairs per step
-          const uint64_t db = make_smem_desc_sw128(sV + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ts(tmem_base + O_COL, tmem_base + P_COL + kk * 8, db, idesc_pv, (jj > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < ATT_BKV / 16; ++kk) {
+            // A = P_j straight from tensor memory: 16 keys = 8 columns of packed bf16 pairs per step
+            umma_ts(tb + O_COL, tb + P_COL + kk * 8, v_desc + (uint64_t)((kk * 2048) >> 4), idesc_pv,
+                    (jj > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&kv_empty[st]);   // K_j / V_j stage free again
+          umma_commit(p_empty);          // P buffer free, O updated
         }
-        umma_commit(&kv_empty[st]);   // K_j / V_j stage free again
-        umma_commit(p_empty);          // P buffer free, O updated
         return true;
       };
       for (int j = 0; j < n_kv && ok; ++j) {
@@ -182,24 +193,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t kvph = (uint32_t)(j / ATT_KV_STAGES) & 1;
         const int sb = j % S_BUFS;
         const uint32_t sph = (uint32_t)(j / S_BUFS) & 1;
-        if (!mbar_wait(&k_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
-            !mbar_wait(&s_empty[sb], sph ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        if (!mbar_wait_warp(&k_full[st], kvph, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
+            !mbar_wait_warp(&s_empty[sb], sph ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t sK = smem_u32(smem + L::K_OFF + st * L::TILE);
+        const uint64_t k_desc = k_desc0 + (uint64_t)(st * TILE16);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint64_t da = make_smem_desc_sw128(sQ + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sK + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-          umma_ss(tmem_base + sb * 128, da, db, idesc_qk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint64_t o = (uint64_t)(((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4);
+            umma_ss(tb + sb * 128, q_desc + o, k_desc + o, idesc_qk, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[sb]);
         }
-        umma_commit(&s_full[sb]);
         if (j > 0) ok = issue_pv(j - 1);
       }
       if (ok) ok = issue_pv(n_kv - 1);
-      if (ok) umma_commit(o_full);
+      if (ok && leader) umma_commit(o_full);
     }
   } else {
     // ------------------------------ softmax + epilogue (warps 2..5) -------------------------
@@ -413,38 +425,50 @@ namespace adana {
 // Backward.
 //
 // One CTA = one (batch, KV head, 128-key tile j); K_j and V_j stay in shared memory while the CTA
-// walks every (query head of the group, query tile i >= j):
-//     S  = Q_i K_j^T            dP = dO_i V_j^T                       (tensor memory, fp32)
-//     P  = exp2(scale*S - lse2) dS = P o (dP - delta_i) * scale       (softmax warps, row per thread)
-//     dV_j += P^T dO_i          dK_j += dS^T Q_i                      (accumulate in tensor memory)
-//     dQ_i  = dS K_j            -> fp32 vector reductions into the dQ accumulation buffer
-// P and dS are written once to shared memory as [q rows][kv cols] 128B-swizzled tiles; the same
-// bytes serve as the K-major A operand of dS*K and as the MN-major A operand of P^T*dO / dS^T*Q
-// (the MMA descriptor selects the major-ness), and the Q / dO / K tiles likewise serve both as
-// K-major and as MN-major operands.  delta_i = rowsum(dO o O) comes from a small pre-pass kernel.
-// head_dim 64: S/dP of the next item are computed while the softmax warps still drain dQ of the
-// current one.  head_dim 128: tensor memory is full (S, dP, dV, dK), dQ aliases S and the items
-// run back to back.
+// walks every (query head of the group, query tile i >= j).  The scores are computed TRANSPOSED, so
+// that a tensor-memory lane is a key row and the probabilities can feed the dV / dK products
+// straight from tensor memory (operand A of a tcgen05.mma may live there; a lane is a row of A):
+//     S^T  = K_j Q_i^T          dP^T = V_j dO_i^T                     (tensor memory, fp32)
+//     P^T  = exp2(scale*S^T - lse2[q])        -> bf16, written over S^T in tensor memory
+//     dS^T = P^T o (dP^T - delta[q]) * scale  -> bf16, written over dP^T in tensor memory AND to shared memory
+//     dV_j += P^T dO_i          dK_j += dS^T Q_i                      (A from tensor memory)
+//     dQ_i  = dS K_j            (A = the shared-memory dS^T tile read M-major) -> TMA reduce-adds into fp32 dQ
+// Shared-memory bandwidth, not the tensor pipe, bounds this kernel (an M=128, N=64 product with both operands
+// in shared memory moves 6 KB per 32 tensor cycles), so P never touches shared memory and dV / dK read only
+// their B operand from it.
+//
+// Roles: warp 0 TMA producer (Q_i, dO_i and the tile's 128 lse2 / delta values per item), warp 1 MMA issuer,
+// warps 2..9 score warps (warp w owns the tensor-memory lane quarter w % 4 = 32 key rows; the two warps of a
+// quarter split the 128 query columns), warps 10..13 drain dQ.
+//
+// Tensor-memory columns (512):   head_dim 64: S^T | dP^T x2 | dV | dK      head_dim 128: S^T | dP^T | dV | dK
+// Packed P^T / dS^T of the two column halves sit at columns [0,32) and [96,128) of their region (each half
+// only overwrites columns whose fp32 values it has already loaded).  dQ_i lands in columns [32,96) of its
+// item's dP^T region (head_dim 64) or over the S^T region (head_dim 128, where P^T has been consumed by then).
+// head_dim 64: with two dP^T regions and two dS^T tiles the chain of an item (dP^T -> dS^T -> dK, dQ -> drain)
+// overlaps the next item's (S^T -> P^T -> dV); head_dim 128 has no columns to spare and runs the items back
+// to back.  lse2 and `delta` are per QUERY, i.e. per column here: every lane reads the same staged values.
 // =================================================================================================
 template <int HD>
 struct AttBwdSmem {
   static constexpr int TILE = ATT_BQ * HD * 2;
-  static constexpr int STAGES = (HD == 64) ? 2 : 1;
+  static constexpr int STAGES = (HD == 64) ? 3 : 1;        // Q / dO ring: a TMA load takes longer than an item
+  static constexpr int DS_BUFS = (HD == 64) ? 2 : 1;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = TILE;
   static constexpr int Q_OFF = 2 * TILE;
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
-  static constexpr int P_OFF = DO_OFF + STAGES * TILE;
-  static constexpr int DS_OFF = P_OFF + ATT_BQ * ATT_BKV * 2;
-  static constexpr int DQ_OFF = DS_OFF + ATT_BQ * ATT_BKV * 2;   // fp32 staging of 64 dQ columns: 2 boxes [128][32]
-  static constexpr int DQ_BOX = ATT_BQ * 128;
-  static constexpr int BAR_OFF = DQ_OFF + 2 * DQ_BOX;
+  static constexpr int DS_OFF = DO_OFF + STAGES * TILE;                    // dS^T tiles [128 keys][128 queries] bf16
+  static constexpr int DQ_OFF = DS_OFF + DS_BUFS * ATT_BQ * ATT_BKV * 2;   // fp32 dQ staging: 4 warps x 1 box [32][32]
+  static constexpr int DQ_BOX = 32 * 128;
+  static constexpr int STAT_OFF = DQ_OFF + 4 * DQ_BOX;                     // per stage: lse2[128] | ndelta[128]
+  static constexpr int BAR_OFF = STAT_OFF + STAGES * 1024;
   static constexpr int TOTAL = BAR_OFF + 256;
 };
 
 struct AttBwdArgs {
   const float* lse2;      // [B, Hq, S]
-  const float* delta;     // [B, Hq, S]
+  const float* ndelta;    // [B, Hq, S]: -scale * rowsum(dO o O)
   float* dq_acc;          // [T, Hq, HD] fp32, zero-initialised by the caller
   __nv_bfloat16* dk;      // [T, Hk, HD]
   __nv_bfloat16* dv;      // base of the v columns in the projection-gradient buffer
@@ -463,25 +487,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   using L = AttBwdSmem<HD>;
   constexpr int CHUNKS = HD / 64;
   constexpr int CHUNK_BYTES = ATT_BQ * 128;
-  constexpr bool PIPELINED = (HD == 64);
   constexpr int STAGES = L::STAGES;
-  constexpr uint32_t S_COL = 0, DP_COL = 128, DV_COL = 256, DK_COL = 256 + HD;
-  constexpr uint32_t DQ_COL = PIPELINED ? (256 + 2 * HD) : 0;   // aliases S when tensor memory is full
+  constexpr int DPT_BUFS = (HD == 64) ? 2 : 1;
+  constexpr bool OVERLAP = (HD == 64);
+  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = DPT_COL + DPT_BUFS * 128, DK_COL = DV_COL + HD;
+  constexpr uint32_t HALF1_COL = 96;      // packed bf16 columns of the second column half inside an S^T / dP^T region
+  static_assert(DK_COL + HD == 512, "tensor-memory plan must fill 512 columns");
+  static_assert(L::TOTAL <= 227 * 1024, "shared memory plan");
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;            // [1]
-  uint64_t* qdo_full = bars + 1;       // [2]
-  uint64_t* qdo_empty = bars + 3;      // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* dp_full = bars + 6;
-  uint64_t* sdp_free = bars + 7;       // softmax warps: S and dP are in registers
-  uint64_t* pds_full = bars + 8;       // softmax warps: P and dS tiles written
-  uint64_t* pds_free = bars + 9;       // MMA: dV/dK/dQ products retired
-  uint64_t* dq_full = bars + 10;
-  uint64_t* dq_free = bars + 11;       // softmax warps: dQ drained
-  uint64_t* acc_full = bars + 12;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* qdo_full = bars + 1;       // [4]
+  uint64_t* qdo_empty = bars + 5;      // [4]
+  uint64_t* st_full = bars + 9;        // [1]  MMA: S^T of an item is in tensor memory
+  uint64_t* p_full = bars + 10;        // [2]  score warps: P^T written                       (by item parity)
+  uint64_t* dpt_full = bars + 12;      // [2]  MMA: dP^T is in tensor memory                  (by item parity)
+  uint64_t* ds_full = bars + 14;       // [2]  score warps: dS^T in tensor and shared memory  (by item parity)
+  uint64_t* dq_full = bars + 16;       // [2]  MMA: dK / dQ products of the item retired      (by item parity)
+  uint64_t* dq_free = bars + 18;       // [2]  drain warps: dQ drained                        (by item parity)
+  uint64_t* acc_full = bars + 20;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -498,17 +524,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(st_full, 1);
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(dp_full, 1);
-    mbar_init(sdp_free, 8);
-    mbar_init(pds_full, 8);
-    mbar_init(pds_free, 1);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_free, 8);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&p_full[s], 8);
+      mbar_init(&dpt_full[s], 1);
+      mbar_init(&ds_full[s], 8);
+      mbar_init(&dq_full[s], 1);
+      mbar_init(&dq_free[s], 4);
+    }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -546,12 +573,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ok = false;
           break;
         }
-        mbar_expect_tx(&qdo_full[stage], 2 * L::TILE);
+        mbar_expect_tx(&qdo_full[stage], 2 * L::TILE + 1024);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c) {
           tma_load_3d(smem + L::Q_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmQ, &qdo_full[stage], c * 64, qrow, hq);
           tma_load_3d(smem + L::DO_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmDO, &qdo_full[stage], c * 64, qrow, hq);
         }
+        const long long stat = ((long long)b * args.Hq + hq) * args.S + i * ATT_BQ;
+        bulk_load_1d(smem + L::STAT_OFF + stage * 1024, args.lse2 + stat, 512, &qdo_full[stage]);
+        bulk_load_1d(smem + L::STAT_OFF + stage * 1024 + 512, args.ndelta + stat, 512, &qdo_full[stage]);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -565,205 +595,223 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);  // Q K^T, dO V^T
-      constexpr uint32_t idesc_t = make_idesc_bf16(ATT_BKV, HD, true, true);        // P^T dO, dS^T Q
-      constexpr uint32_t idesc_q = make_idesc_bf16(ATT_BQ, HD, false, true);        // dS K
-      const uint32_t sK = smem_u32(smem + L::K_OFF), sV = smem_u32(smem + L::V_OFF);
-      const uint32_t sP = smem_u32(smem + L::P_OFF), sDS = smem_u32(smem + L::DS_OFF);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+    // The whole warp runs this loop in lock step and one elected lane issues: addresses and descriptors are then
+    // computed in warp-uniform code instead of inside a divergent branch.
+    {
+      const bool leader = elect_one();
+      const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+      constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BKV, ATT_BQ, false, false);   // K Q^T, V dO^T (both K-major)
+      constexpr uint32_t idesc_ts = make_idesc_bf16(ATT_BKV, HD, false, true);       // P^T dO, dS^T Q (A in tensor memory)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(ATT_BQ, HD, true, true);         // dS K (A = dS^T tile read M-major)
+      // One thread issues every product, so its instruction count per product matters: the shared-memory descriptors
+      // are built once, and a product only adds the 16-byte-unit offset of its contraction step to the address field
+      // (the low 14 bits; tiles sit below 256 KB, so the sum never carries out of it).
+      const uint64_t k_kmaj = make_smem_desc_sw128(smem_u32(smem + L::K_OFF), 16, 1024);
+      const uint64_t v_kmaj = make_smem_desc_sw128(smem_u32(smem + L::V_OFF), 16, 1024);
+      const uint64_t k_mnmaj = make_smem_desc_sw128(smem_u32(smem + L::K_OFF), CHUNK_BYTES, 1024);
+      const uint64_t q_kmaj0 = make_smem_desc_sw128(smem_u32(smem + L::Q_OFF), 16, 1024);
+      const uint64_t q_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + L::Q_OFF), CHUNK_BYTES, 1024);
+      const uint64_t do_kmaj0 = make_smem_desc_sw128(smem_u32(smem + L::DO_OFF), 16, 1024);
+      const uint64_t do_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + L::DO_OFF), CHUNK_BYTES, 1024);
+      const uint64_t ds_mnmaj0 = make_smem_desc_sw128(smem_u32(smem + L::DS_OFF), CHUNK_BYTES, 1024);
+      constexpr uint32_t TILE16 = L::TILE >> 4, DS16 = (ATT_BQ * ATT_BKV * 2) >> 4;
+      // 16-byte units: K-major step kk of a tile (64-column chunks CHUNK_BYTES apart), MN-major step kk (16 rows)
+#define KMAJ_STEP(kk) (uint64_t)((((kk) >> 2) * CHUNK_BYTES + ((kk) & 3) * 32) >> 4)
+#define MNMAJ_STEP(kk) (uint64_t)(((kk) * 2048) >> 4)
+      bool ok = mbar_wait_warp(kv_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
       tc_fence_after_sync();
 
-      auto issue_scores = [&](int t) -> bool {   // S and dP of item t
-        const int st = t % STAGES;
-        const uint32_t ph = (uint32_t)(t / STAGES) & 1;
-        if (!mbar_wait(&qdo_full[st], ph, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        if (!mbar_wait(sdp_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        if (!PIPELINED) {  // dQ of the previous item lives in the S columns: wait until it is drained
-          if (!mbar_wait(dq_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        }
-        tc_fence_after_sync();
-        const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE);
-        const uint32_t sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-          umma_ss(tmem_base + S_COL, make_smem_desc_sw128(sQ + o, 16, 1024),
-                  make_smem_desc_sw128(sK + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(s_full);
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t o = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-          umma_ss(tmem_base + DP_COL, make_smem_desc_sw128(sDO + o, 16, 1024),
-                  make_smem_desc_sw128(sV + o, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(dp_full);
-        return true;
+      auto wait_qdo = [&](int t) -> bool {
+        return mbar_wait_warp(&qdo_full[t % STAGES], (uint32_t)(t / STAGES) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN);
       };
-      auto issue_grads = [&](int t) -> bool {    // dV, dK accumulation and dQ of item t
-        const int st = t % STAGES;
-        if (!mbar_wait(pds_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        if (PIPELINED) {
-          if (!mbar_wait(dq_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-        }
-        tc_fence_after_sync();
-        const uint32_t sQ = smem_u32(smem + L::Q_OFF + st * L::TILE);
-        const uint32_t sDO = smem_u32(smem + L::DO_OFF + st * L::TILE);
+      auto issue_st = [&](int t) {               // S^T of item t (its Q / dO stage has been waited for)
+        const uint64_t q = q_kmaj0 + (uint64_t)((t % STAGES) * TILE16);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < ATT_BQ / 16; ++kk) {   // contraction over the 128 query rows
-          const uint64_t a_p = make_smem_desc_sw128(sP + kk * 2048, CHUNK_BYTES, 1024);
-          const uint64_t b_do = make_smem_desc_sw128(sDO + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss(tmem_base + DV_COL, a_p, b_do, idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_ss(tmem_base + ST_COL, k_kmaj + KMAJ_STEP(kk), q + KMAJ_STEP(kk), idesc_s, kk > 0 ? 1u : 0u);
+          umma_commit(st_full);
         }
-#pragma unroll
-        for (int kk = 0; kk < ATT_BQ / 16; ++kk) {
-          const uint64_t a_ds = make_smem_desc_sw128(sDS + kk * 2048, CHUNK_BYTES, 1024);
-          const uint64_t b_q = make_smem_desc_sw128(sQ + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss(tmem_base + DK_COL, a_ds, b_q, idesc_t, (t > 0 || kk > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < ATT_BKV / 16; ++kk) {  // contraction over the 128 keys
-          const uint64_t a_ds = make_smem_desc_sw128(sDS + (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32, 16, 1024);
-          const uint64_t b_k = make_smem_desc_sw128(sK + kk * 2048, CHUNK_BYTES, 1024);
-          umma_ss(tmem_base + DQ_COL, a_ds, b_k, idesc_q, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&qdo_empty[st]);
-        umma_commit(pds_free);
-        umma_commit(dq_full);
-        return true;
       };
+      auto issue_dpt = [&](int t) {              // dP^T of item t
+        const uint64_t d_o = do_kmaj0 + (uint64_t)((t % STAGES) * TILE16);
+        const uint32_t d = tmem_base + DPT_COL + (t % DPT_BUFS) * 128;
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_ss(d, v_kmaj + KMAJ_STEP(kk), d_o + KMAJ_STEP(kk), idesc_s, kk > 0 ? 1u : 0u);
+          umma_commit(&dpt_full[t & 1]);
+        }
+      };
+      // column of the packed bf16 operand for contraction step kk (16 queries = 8 columns)
+#define PACKED_COL(kk) ((kk) < 4 ? (uint32_t)((kk) * 8) : HALF1_COL + (uint32_t)(((kk) - 4) * 8))
 
-      if (ok && n_items > 0) ok = issue_scores(0);
-      for (int t = 0; t < n_items && ok; ++t) {
-        if (PIPELINED && t + 1 < n_items) ok = issue_scores(t + 1);
-        if (ok) ok = issue_grads(t);
-        if (!PIPELINED && ok && t + 1 < n_items) ok = issue_scores(t + 1);
+      if (ok && n_items > 0) {
+        ok = wait_qdo(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_st(0);
+          issue_dpt(0);
+        }
       }
-      if (ok) umma_commit(acc_full);
+      for (int t = 0; t < n_items && ok; ++t) {
+        const int st = t % STAGES;
+        const uint64_t q_mn = q_mnmaj0 + (uint64_t)(st * TILE16);
+        const uint64_t do_mn = do_mnmaj0 + (uint64_t)(st * TILE16);
+        const uint64_t ds_mn = ds_mnmaj0 + (uint64_t)((t % L::DS_BUFS) * DS16);
+        const uint32_t dpt = tmem_base + DPT_COL + (t % DPT_BUFS) * 128;
+        const uint32_t dq_col = OVERLAP ? (dpt + 32) : (tmem_base + ST_COL);
+        const uint32_t acc = t > 0 ? 1u : 0u;
+        // dV += P^T dO
+        if (!mbar_wait_warp(&p_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < ATT_BQ / 16; ++kk)
+            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + PACKED_COL(kk), do_mn + MNMAJ_STEP(kk), idesc_ts,
+                    kk > 0 ? 1u : acc);
+        }
+        if (OVERLAP && t + 1 < n_items) {
+          // next item's S^T goes over the region whose P^T the product above consumes (same pipe, in order)
+          if (!wait_qdo(t + 1)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_st(t + 1);
+        }
+        // dK += dS^T Q ; dQ = dS K
+        if (!mbar_wait_warp(&ds_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < ATT_BQ / 16; ++kk)
+            umma_ts(tmem_base + DK_COL, dpt + PACKED_COL(kk), q_mn + MNMAJ_STEP(kk), idesc_ts, kk > 0 ? 1u : acc);
+#pragma unroll
+          for (int kk = 0; kk < ATT_BKV / 16; ++kk)
+            umma_ss(dq_col, ds_mn + MNMAJ_STEP(kk), k_mnmaj + MNMAJ_STEP(kk), idesc_dq, kk > 0 ? 1u : 0u);
+          umma_commit(&qdo_empty[st]);
+          umma_commit(&dq_full[t & 1]);
+        }
+        if (OVERLAP && t + 1 < n_items) {
+          // next item's dP^T goes into the other region once the dQ that lived there (item t-1) has been drained
+          if (t >= 1) {
+            if (!mbar_wait_warp(&dq_free[(t + 1) & 1], (uint32_t)((t - 1) >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+          issue_dpt(t + 1);
+        }
+        if (!OVERLAP && t + 1 < n_items) {
+          // dQ of this item sits in the S^T region: the next scores wait until it is drained
+          if (!mbar_wait_warp(&dq_free[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+          if (!wait_qdo(t + 1)) { ok = false; break; }
+          tc_fence_after_sync();
+          issue_st(t + 1);
+          issue_dpt(t + 1);
+        }
+      }
+#undef KMAJ_STEP
+#undef MNMAJ_STEP
+#undef PACKED_COL
+      if (ok && leader) umma_commit(acc_full);
     }
-  } else {
-    // ------------------------------ softmax / epilogue warps --------------------------------
-    // Eight warps: warp w reads the tensor-memory lane quarter w % 4 (query rows), and the two warps of a
-    // quarter split the 128 key columns of the tile (wg = column half).  No row reductions are needed in
-    // the backward (lse and delta come from memory), so the halves are independent.
+  } else if (warp < 10) {
+    // ------------------------------ score warps ---------------------------------------------
     const int quad = warp & 3;
     const int wg = (warp - 2) >> 2;
-    const int r = quad * 32 + lane;
+    const int r = quad * 32 + lane;          // key row inside the tile
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    uint8_t* sP = smem + L::P_OFF;
-    uint8_t* sDS = smem + L::DS_OFF;
+    const uint32_t pcol = wg ? HALF1_COL : 0u;
     bool ok = true;
-    uint32_t pk[32], dk_[32];   // this thread's 64 columns of P and dS of the item being prepared
+    uint32_t pk[32];                         // this thread's 64 probabilities (bf16 pairs) of the item in flight
 
-    // S_t, dP_t -> P_t, dS_t in registers (frees the S / dP columns for the next item's scores)
-    auto compute = [&](int t) -> bool {
-      const int g = t / n_i, i = j + t % n_i;
-      const int hq = hk * G + g;
-      const long long stat_idx = ((long long)b * args.Hq + hq) * args.S + i * ATT_BQ + r;
-      const float lse = args.lse2[stat_idx];
-      const float dl = args.delta[stat_idx];
-      const bool diag = (i == j);
-      if (!mbar_wait(s_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN) ||
-          !mbar_wait(dp_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN))
-        return false;
+    for (int t = 0; t < n_items && ok; ++t) {
+      const int st = t % STAGES;
+      const bool diag = (t % n_i) == 0;        // i == j
+      const float* lse = reinterpret_cast<const float*>(smem + L::STAT_OFF + st * 1024) + wg * 64;
+      const float* nd = lse + 128;
+      // ---- S^T_t -> P^T_t (bf16, over the S^T columns this thread has read) ----
+      if (!mbar_wait(st_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
       tc_fence_after_sync();
-      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2), nl2 = make_float2(-lse, -lse);
-      const float2 s2 = make_float2(args.scale, args.scale), nd2 = make_float2(-dl * args.scale, -dl * args.scale);
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = wg * 2 + cc;             // 32-column chunk of the tile
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_base + S_COL + lane_addr + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + DP_COL + lane_addr + c * 32, dv);
+      {
+        const uint32_t s_addr = tmem_base + ST_COL + lane_addr + wg * 64;
+        const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
+        uint32_t sa[32], sb[32];
+        tmem_ld_32x32b_x32(s_addr, sa);
+        tmem_ld_32x32b_x32(s_addr + 32, sb);
         tmem_wait_ld();
-        if (diag) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((c * 32 + e) > r) sv[e] = 0xff800000u;   // -inf: the probability is exactly 0
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t(&sv)[32] = cc ? sb : sa;
+          if (diag) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((wg * 64 + cc * 32 + e) < r) sv[e] = 0xff800000u;   // query before key: -inf, probability exactly 0
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float4 l = *reinterpret_cast<const float4*>(lse + cc * 32 + e);
+            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), sc2,
+                                         make_float2(-l.x, -l.y));
+            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3])), sc2,
+                                         make_float2(-l.z, -l.w));
+            pk[cc * 16 + (e >> 1)] = pack_bf16x2(ex2_approx(x0.x), ex2_approx(x0.y));
+            pk[cc * 16 + (e >> 1) + 1] = pack_bf16x2(ex2_approx(x1.x), ex2_approx(x1.y));
+          }
         }
-        // two columns per instruction: p = exp2(s*c' - lse), dS = p * (dP*c - delta*c)
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), sc2, nl2);
-          const float2 p2 = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-          const float2 t2 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2, nd2);
-          const float2 d2 = __fmul2_rn(p2, t2);
-          pk[cc * 16 + (e >> 1)] = pack_bf16x2(p2.x, p2.y);
-          dk_[cc * 16 + (e >> 1)] = pack_bf16x2(d2.x, d2.y);
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sdp_free);
-      return true;
-    };
-    // registers -> the swizzled P / dS tiles (free once the gradient products of the previous item retired)
-    auto publish = [&](int t) -> bool {
-      if (!mbar_wait(pds_free, ((uint32_t)t & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int off = wg * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);   // chunk wg = this half's 64 columns
-        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
-      return true;
-    };
-    // dQ_i of item t: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the fp32
-    // accumulation buffer.  The adds happen in L2, 128 bytes at a time, instead of 16 vector atomics per thread.
-    // Every warp stages and sends its own 32 rows of its 32-column box, so warp-level synchronisation suffices.
-    auto drain = [&](int t) -> bool {
-      const int g = t / n_i, i = j + t % n_i;
-      const int hq = hk * G + g;
-      if (!mbar_wait(dq_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
-      tc_fence_after_sync();
-      uint8_t* sDQw = smem + L::DQ_OFF + wg * L::DQ_BOX + quad * 32 * 128;
-#pragma unroll 1
-      for (int half = 0; half < HD / 64; ++half) {
-        if (lane == 0) tma_wait_group_read0();      // this warp's previous reduce has read its staging rows
+        tmem_st_32x32b_x32(tmem_base + ST_COL + lane_addr + pcol, pk);
+        tmem_wait_st();
+        tc_fence_before_sync();
         __syncwarp();
-        {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tmem_base + DQ_COL + lane_addr + half * 64 + wg * 32, o);
-          tmem_wait_ld();
+        if (lane == 0) mbar_arrive(&p_full[t & 1]);
+      }
+      // ---- dP^T_t -> dS^T_t: tensor memory (over the dP^T columns already read) and the shared-memory tile ----
+      if (!mbar_wait(&dpt_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      if (t >= L::DS_BUFS) {
+        // the shared-memory tile is free once the dQ product that read it (item t - DS_BUFS) has retired
+        const int u = t - L::DS_BUFS;
+        if (!mbar_wait(&dq_full[u & 1], (uint32_t)(u >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      }
+      tc_fence_after_sync();
+      {
+        const uint32_t dpt = tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + lane_addr;
+        uint8_t* sDS = smem + L::DS_OFF + (t % L::DS_BUFS) * (ATT_BQ * ATT_BKV * 2);
+        const float2 s2 = make_float2(args.scale, args.scale);
+        uint32_t da[16], db[16], dk_[32];
+        tmem_ld_32x32b_x16(dpt + wg * 64, da);
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            *reinterpret_cast<uint4*>(sDQw + lane * 128 + ((u ^ (lane & 7)) << 4)) =
-                make_uint4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
+        for (int cc = 0; cc < 4; ++cc) {       // 16 columns at a time, the next load in flight
+          uint32_t(&dv)[16] = (cc & 1) ? db : da;
+          uint32_t(&nx)[16] = (cc & 1) ? da : db;
+          tmem_wait_ld();
+          if (cc < 3) tmem_ld_32x32b_x16(dpt + wg * 64 + (cc + 1) * 16, nx);
+#pragma unroll
+          for (int e = 0; e < 16; e += 4) {
+            const float4 d = *reinterpret_cast<const float4*>(nd + cc * 16 + e);
+            const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2,
+                                         make_float2(d.x, d.y));
+            const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(dv[e + 2]), __uint_as_float(dv[e + 3])), s2,
+                                         make_float2(d.z, d.w));
+            const float2 g0 = __fmul2_rn(unpack_bf16x2(pk[cc * 8 + (e >> 1)]), t0);
+            const float2 g1 = __fmul2_rn(unpack_bf16x2(pk[cc * 8 + (e >> 1) + 1]), t1);
+            dk_[cc * 8 + (e >> 1)] = pack_bf16x2(g0.x, g0.y);
+            dk_[cc * 8 + (e >> 1) + 1] = pack_bf16x2(g1.x, g1.y);
+          }
+        }
+        tmem_st_32x32b_x32(dpt + pcol, dk_);
+        // the same 64 values as row r of the [keys][queries] tile, 128B-swizzled (chunk wg = this half's 64 columns)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int off = wg * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
         }
         fence_proxy_async_smem();
+        tmem_wait_st();
+        tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) {
-          const int tok0 = b * args.S + i * ATT_BQ + quad * 32;
-          tma_reduce_add_3d(&tmDQ, sDQw, half * 64 + wg * 32, hq, tok0);
-          tma_commit_group();
-        }
+        if (lane == 0) mbar_arrive(&ds_full[t & 1]);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
-      return true;
-    };
-
-    if (PIPELINED) {
-      // P / dS of item t+1 are computed while the tensor cores run the gradient products of item t
-      ok = n_items > 0 && compute(0) && publish(0);
-      for (int t = 0; t < n_items && ok; ++t) {
-        const bool more = t + 1 < n_items;
-        if (more) ok = compute(t + 1);
-        if (ok) ok = drain(t);
-        if (ok && more) ok = publish(t + 1);
-      }
-    } else {
-      // dQ aliases the S columns: the next scores cannot start before this item's dQ is drained
-      for (int t = 0; t < n_items && ok; ++t) ok = compute(t) && publish(t) && drain(t);
     }
-    if (lane == 0) tma_wait_group_read0();   // staging rows are not needed any more
-    __syncwarp();
     // ---- epilogue: dK_j, dV_j (row = key index) ----
     if (ok && mbar_wait(acc_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
       tc_fence_after_sync();
@@ -792,6 +840,50 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
     }
+  } else {
+    // ------------------------------ dQ drain warps (10..13) ----------------------------------
+    // dQ_i of item t: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the fp32
+    // accumulation buffer (the adds happen in L2, 128 bytes at a time).  A warp stages and sends its own 32 query
+    // rows, 32 columns per box.
+    const int quad = warp & 3;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    uint8_t* sDQw = smem + L::DQ_OFF + (warp - 10) * L::DQ_BOX;
+    bool ok = true;
+    for (int t = 0; t < n_items && ok; ++t) {
+      const int g = t / n_i, i = j + t % n_i;
+      const int hq = hk * G + g;
+      if (!mbar_wait(&dq_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t dq_col = OVERLAP ? (tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + 32) : (tmem_base + ST_COL);
+      const int tok0 = b * args.S + i * ATT_BQ + quad * 32;
+      uint32_t o[32], o2[32];
+      tmem_ld_32x32b_x32(dq_col + lane_addr, o);
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? o2 : o;
+        uint32_t(&nxt)[32] = (c & 1) ? o : o2;
+        tmem_wait_ld();
+        if (c + 1 < HD / 32) tmem_ld_32x32b_x32(dq_col + lane_addr + (c + 1) * 32, nxt);
+        if (lane == 0) tma_wait_group_read0();      // the previous reduce has read the box
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(sDQw + lane * 128 + ((u ^ (lane & 7)) << 4)) =
+              make_uint4(cur[u * 4], cur[u * 4 + 1], cur[u * 4 + 2], cur[u * 4 + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmDQ, sDQw, c * 32, hq, tok0);
+          tma_commit_group();
+        }
+      }
+      // every dQ column of the item is in registers or on its way: the region may be overwritten
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&dq_free[t & 1]);
+    }
+    if (lane == 0) tma_wait_group_read0();   // staging rows are not needed any more
+    __syncwarp();
   }
 
   tc_fence_before_sync();
@@ -802,11 +894,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d].  HD/8 neighbouring lanes own one (token, head) vector, each
+// delta[b, h, s] = mul * sum_d dO[t, h, d] * O[t, h, d] (the backward passes mul = -scale).  HD/8 neighbouring lanes own one (token, head) vector, each
 // with one 16-byte load per operand; the sum is a 3- or 4-step shuffle inside the lane group.
 template <int HD>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
-                                  float* __restrict__ delta, int B, int S, int H) {
+                                  float* __restrict__ delta, int B, int S, int H, float mul) {
   constexpr int LPV = HD / 8;
   constexpr int VPW = 32 / LPV;
   const int lane = threadIdx.x & 31;
@@ -830,7 +922,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const 
       const long long tok = it / H;
       const int h = (int)(it - tok * H);
       const long long bb = tok / S, s = tok - bb * S;
-      delta[(bb * H + h) * S + s] = acc;
+      delta[(bb * H + h) * S + s] = acc * mul;
     }
   }
 }
@@ -869,9 +961,9 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
     long long blocks = (items + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (hd == 64)
-      attn_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq);
+      attn_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale);
     else
-      attn_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq);
+      attn_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale);
   }
   CUtensorMap tq, tdo, tk, tv;
   uint32_t box[3] = {64, ATT_BQ, 1};
@@ -889,7 +981,7 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
     if (encode_tmap_nd(&tv, vbase, 3, dims, strv, box, 2, 1)) return -5;
   }
   AttBwdArgs a;
-  a.lse2 = lse2; a.delta = delta; a.dq_acc = dq_acc;
+  a.lse2 = lse2; a.ndelta = delta; a.dq_acc = dq_acc;
   a.dk = (__nv_bfloat16*)dk; a.dv = (__nv_bfloat16*)dvbase; a.lddv = lddv; a.dv_hstride = dv_hstride;
   a.B = B; a.S = S; a.Hq = Hq; a.Hk = Hk;
   a.scale = scale; a.scale_log2 = scale * 1.4426950408889634f;

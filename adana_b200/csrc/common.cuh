@@ -106,6 +106,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// The same wait made by every lane of a converged warp; the result is warp-uniform (false if any lane gave up),
+// so the warp's control flow stays converged.  For warps that keep their whole loop warp-uniform and predicate
+// only the issuing instructions on one elected lane: values computed in uniform control flow can live in uniform
+// registers, which is what tcgen05.mma takes its descriptors from.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  const bool r = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, r);
+}
+
 // ---- TMA (cp.async.bulk.tensor), loads into this CTA's shared memory only ----------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
@@ -133,6 +143,18 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
       "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// Untiled bulk copy global -> this CTA's shared memory (both addresses 16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// waits until at most one bulk group of this thread is still reading its shared-memory source
+__device__ __forceinline__ void tma_wait_group_read1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 
 // ---- TMA reduce: shared memory tile added into global memory (fp32 add performed in L2) ------

@@ -163,6 +163,121 @@ ce_fwd_bwd_kernel(const float* __restrict__ logits, long long ld, const long lon
   }
 }
 
+// The same loss over bf16 logits (what the bf16 GEMM epilogue writes; also what the reference's autocast
+// produces before its fp32 cross-entropy), eight columns per 16-byte access.  `dlogits` may be the logits
+// buffer itself: in pass 2 every thread overwrites exactly the eight values it has just read, so the chunk
+// of logits turns into the chunk of dlogits in place and no second [rows, vocab] buffer exists.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fwd_bwd_bf16_kernel(const __nv_bfloat16* logits, long long ld, const long long* __restrict__ targets,
+                       int rows, int vocab, float z_coeff, float grad_scale, __nv_bfloat16* dlogits, long long ldd,
+                       float* __restrict__ sums, float* __restrict__ lse_out) {
+  __shared__ float s_max[CE_THREADS / 32];
+  __shared__ float s_sum[CE_THREADS / 32];
+  __shared__ int s_arg[CE_THREADS / 32];
+  __shared__ float s_bcast[3];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nv = vocab >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16* lr = logits + (size_t)row * ld;
+    float m = -INFINITY, s = 0.f;
+    int arg = 0;
+    for (int c = threadIdx.x; c < nv; c += CE_THREADS) {
+      float v[8];
+      unpack8(*reinterpret_cast<const uint4*>(lr + c * 8), v);
+      float vm = v[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) vm = fmaxf(vm, v[i]);
+      if (vm > m) {
+        s *= __expf(m - vm);
+        m = vm;
+        int j = 7;
+#pragma unroll
+        for (int i = 6; i >= 0; --i)
+          if (v[i] == vm) j = i;      // lowest index among equal values, like torch.argmax
+        arg = c * 8 + j;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += __expf(v[i] - m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      const float nm = fmaxf(m, om);
+      s = s * rescale(m, nm) + os * rescale(om, nm);
+      if (om > m || (om == m && oa < arg)) arg = oa;
+      m = nm;
+    }
+    __syncthreads();
+    if (lane == 0) {
+      s_max[warp] = m;
+      s_sum[warp] = s;
+      s_arg[warp] = arg;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float M = s_max[0], Ssum = s_sum[0];
+      int A = s_arg[0];
+      for (int w2 = 1; w2 < CE_THREADS / 32; ++w2) {
+        const float om = s_max[w2], os = s_sum[w2];
+        const int oa = s_arg[w2];
+        const float nm = fmaxf(M, om);
+        Ssum = Ssum * rescale(M, nm) + os * rescale(om, nm);
+        if (om > M || (om == M && oa < A)) A = oa;
+        M = nm;
+      }
+      const float lse = M + __logf(Ssum);
+      const long long tgt = targets[row];
+      const bool valid = tgt >= 0 && tgt < vocab;
+      s_bcast[0] = M;
+      s_bcast[1] = lse;
+      s_bcast[2] = valid ? 1.f : 0.f;
+      if (lse_out) lse_out[row] = lse;
+      if (valid) {
+        atomicAdd(&sums[0], lse - __bfloat162float(lr[tgt]));
+        atomicAdd(&sums[3], 1.f);
+      }
+      atomicAdd(&sums[1], lse * lse);
+      if (valid && A == (int)tgt) atomicAdd(&sums[2], 1.f);
+    }
+    __syncthreads();     // (also orders thread 0's read of lr[tgt] before pass 2 overwrites it in place)
+    if (dlogits) {
+      const float lse = s_bcast[1];
+      const bool valid = s_bcast[2] != 0.f;
+      const long long tgt = targets[row];
+      const float ce_scale = valid ? grad_scale : 0.f;
+      const float pscale = ce_scale + grad_scale * 2.f * z_coeff * lse;
+      __nv_bfloat16* dr = dlogits + (size_t)row * ldd;
+      for (int c = threadIdx.x; c < nv; c += CE_THREADS) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(lr + c * 8), v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __expf(v[i] - lse) * pscale;
+        const int base = c * 8;
+        if (valid && tgt >= base && tgt < base + 8) {
+          const int j = (int)(tgt - base);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i == j) v[i] -= ce_scale;
+        }
+        uint4 u;
+        u.x = pack_bf16x2(v[0], v[1]);
+        u.y = pack_bf16x2(v[2], v[3]);
+        u.z = pack_bf16x2(v[4], v[5]);
+        u.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(dr + base) = u;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // out = a * sigmoid(gate) (Qwen3 attention output gate), and its backward.
 __global__ void sigmoid_gate_fwd_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ gate,
                                         long long gate_row_stride, int gate_off, int gate_hstride,
@@ -240,6 +355,19 @@ extern "C" int adana_ce_fwd_bwd(float* logits, long long ld, const long long* ta
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   ce_fwd_bwd_kernel<<<grid, CE_THREADS, 0, st>>>(logits, ld, targets, rows, vocab, z_coeff, grad_scale,
                                                  (__nv_bfloat16*)dlogits_bf16, ldd, sums, lse_out);
+  return (int)cudaGetLastError();
+}
+
+// bf16 logits [rows, vocab]; `dlogits_bf16` may alias `logits` (in place) or be null (forward only).
+extern "C" int adana_ce_fwd_bwd_bf16(void* logits, long long ld, const long long* targets, int rows, int vocab,
+                                     float z_coeff, float grad_scale, void* dlogits_bf16, long long ldd, float* sums,
+                                     float* lse_out, void* stream_) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  if (rows <= 0) return 0;
+  if ((vocab & 7) || (ld & 7) || (ldd & 7)) return -1;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  ce_fwd_bwd_bf16_kernel<<<grid, CE_THREADS, 0, st>>>((const __nv_bfloat16*)logits, ld, targets, rows, vocab, z_coeff,
+                                                      grad_scale, (__nv_bfloat16*)dlogits_bf16, ldd, sums, lse_out);
   return (int)cudaGetLastError();
 }
 

@@ -43,7 +43,6 @@ extern "C" int adana_norm_bwd_static_scratch(const void* dy, int dy_is_bf16, con
                                              const float* w, const float* mean, const float* rstd, float* dx,
                                              int accumulate_dx, float* dw, int accumulate_dw, int rows, int cols,
                                              int kind, void* dx_bf16, void* stream) {
-  if (rows <= 0) return 0;
   if (cols <= 0 || (cols & 3) || cols > ADANA_NORM_STATIC_MAX_COLS) {
     std::fprintf(stderr,
                  "adana_norm_bwd_static_scratch: cols=%d rejected: must be a multiple of 4 and at most %d "
@@ -51,9 +50,18 @@ extern "C" int adana_norm_bwd_static_scratch(const void* dy, int dy_is_bf16, con
                  cols, ADANA_NORM_STATIC_MAX_COLS, ADANA_NORM_STATIC_MAX_PARTIAL_ROWS, ADANA_NORM_STATIC_MAX_COLS);
     return ADANA_NORM_STATIC_E_COLS;
   }
-  if (!dy || !x || !w || !mean || !rstd || !dx || !dw) {
+  // RMSNorm (kind 1) never reads `mean`, so its callers need not invent a buffer for it.
+  if (!dy || !x || !w || (kind == 0 && !mean) || !rstd || !dx || !dw) {
     std::fprintf(stderr, "adana_norm_bwd_static_scratch: null pointer among dy/x/w/mean/rstd/dx/dw\n");
     return ADANA_NORM_STATIC_E_ARG;
+  }
+  if (rows <= 0) {
+    // no rows: the weight gradient of an empty batch is zero (an accumulating call leaves dw as it is)
+    if (!accumulate_dw) {
+      cudaError_t e = cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)cols, reinterpret_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
   }
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);

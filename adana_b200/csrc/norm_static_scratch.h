@@ -22,6 +22,11 @@
 // load the module) and caches it; every later call on that device only launches the two kernels.  Make
 // that first call during start-up, outside any stream capture and before timing.
 //
+// Device.  The address is looked up for the CURRENT device (cudaGetDevice), not for the device that `stream`
+// belongs to: make the stream's device current before the call, as for any kernel launch.  `mean` may be null
+// for RMSNorm (kind 1), which never reads it.  With `rows` <= 0 nothing is launched; `dw` is then set to zero
+// (a memset on `stream`) unless `accumulate_dw` is set.
+//
 // Initial state.  Nothing has to start at zero: every CTA overwrites its whole partial row before the
 // fold reads it.  `dw` is overwritten unless `accumulate_dw` is set, `dx` is overwritten unless
 // `accumulate_dx` is set; in the accumulate modes the caller owns the initial contents.

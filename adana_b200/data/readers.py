@@ -344,9 +344,12 @@ class PinnedBatchStager:
         x, y = self.reader.sample_batch(out=self._host[slot])
         if not self.cuda:
             return
+        # The kernels that still read this device slot were queued on the consumer's stream before this call, so the
+        # copy stream waits for everything queued there so far.  (The stream is looked up OUTSIDE the `with` block:
+        # inside it the current stream is the copy stream itself and the wait would order nothing.)
+        consumer = torch.cuda.current_stream(self.device)
         with torch.cuda.stream(self._stream):
-            # the previous consumer of this slot must be done before it is overwritten
-            self._stream.wait_stream(torch.cuda.current_stream(self.device))
+            self._stream.wait_stream(consumer)
             self._dev[slot][0].copy_(x, non_blocking=True)
             self._dev[slot][1].copy_(y, non_blocking=True)
             self._events[slot].record(self._stream)

@@ -71,6 +71,7 @@ def _declare(lib):
         "adana_embedding_fwd": [P, P, I, P, I, I, I, P],
         "adana_embedding_bwd": [P, P, P, I, I, I, P],
         "adana_ce_fwd_bwd": [P, L, P, I, I, F, F, P, L, P, P, P],
+        "adana_ce_fwd_bwd_bf16": [P, L, P, I, I, F, F, P, L, P, P, P],
         "adana_opt_step": [P, P, P, P, P, P, L, POINTER(AdanaOptHyper), P, P, P],
         "adana_sumsq_f32": [P, L, P, P],
         "adana_cast_f32_to_bf16": [P, P, L, P],

@@ -65,12 +65,15 @@ def linear_ce_ref(h, w, targets, z_coeff, loss_scale, need_grad=True, dw_out=Non
     return out
 
 
-def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out=None, chunk_rows=4096):
+def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out=None, chunk_rows=4096,
+              logits_dtype=torch.bfloat16):
     """lm_head GEMM + CE + z-loss + accuracy, forward AND backward in one sweep over row chunks.
 
-    h [T, d] bf16, w [V, d] bf16, targets [T] int64 (-1 = ignore).  Logits exist only one chunk at a
-    time (fp32, from the tcgen05 GEMM); the CE kernel turns them into dlogits (bf16), which feed the
-    dgrad GEMM (dh) and the accumulating wgrad GEMM (dw).  loss = (ce_sum + z_coeff*z_sum) / T and
+    h [T, d] bf16, w [V, d] bf16, targets [T] int64 (-1 = ignore).  Logits exist only one chunk at a time.  With
+    `logits_dtype` bf16 (the default; the reference's autocast also hands bf16 logits to its fp32 cross-entropy,
+    src/models/chunked_loss.py:68-151) the tcgen05 GEMM writes the chunk in bf16 and the CE kernel turns it into
+    dlogits IN PLACE; with fp32 the GEMM writes fp32 logits and the CE kernel writes a separate bf16 dlogits chunk.
+    dlogits feed the dgrad GEMM (dh) and the accumulating wgrad GEMM (dw).  loss = (ce_sum + z_coeff*z_sum) / T and
     the returned gradients are those of `loss_scale * loss`.
     """
     T, d = h.shape
@@ -81,8 +84,13 @@ def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out
     lib = _lib.lib()
     sums = torch.zeros(4, dtype=torch.float32, device=dev)
     chunk_rows = min(chunk_rows, T)
-    logits = torch.empty((chunk_rows, V), dtype=torch.float32, device=dev)
-    dlogits = torch.empty((chunk_rows, V), dtype=torch.bfloat16, device=dev) if need_grad else None
+    in_place = logits_dtype == torch.bfloat16 and _lib.has("adana_ce_fwd_bwd_bf16")
+    if in_place:
+        logits = torch.empty((chunk_rows, V), dtype=torch.bfloat16, device=dev)
+        dlogits = logits if need_grad else None
+    else:
+        logits = torch.empty((chunk_rows, V), dtype=torch.float32, device=dev)
+        dlogits = torch.empty((chunk_rows, V), dtype=torch.bfloat16, device=dev) if need_grad else None
     dh = torch.empty((T, d), dtype=torch.bfloat16, device=dev) if need_grad else None
     dw = None
     if need_grad:
@@ -92,9 +100,14 @@ def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out
         e = min(T, s + chunk_rows)
         n = e - s
         hc = h[s:e]
-        gemm.linear_fwd_f32(hc, w, out=logits[:n])
-        rc = lib.adana_ce_fwd_bwd(logits.data_ptr(), V, targets[s:e].data_ptr(), n, V, float(z_coeff), gscale,
-                                  _lib.ptr(dlogits), V, sums.data_ptr(), 0, _lib.stream_ptr())
+        if in_place:
+            gemm.linear_fwd(hc, w, out=logits[:n])
+            rc = lib.adana_ce_fwd_bwd_bf16(logits.data_ptr(), V, targets[s:e].data_ptr(), n, V, float(z_coeff), gscale,
+                                           _lib.ptr(dlogits), V, sums.data_ptr(), 0, _lib.stream_ptr())
+        else:
+            gemm.linear_fwd_f32(hc, w, out=logits[:n])
+            rc = lib.adana_ce_fwd_bwd(logits.data_ptr(), V, targets[s:e].data_ptr(), n, V, float(z_coeff), gscale,
+                                      _lib.ptr(dlogits), V, sums.data_ptr(), 0, _lib.stream_ptr())
         _lib.check_rc(rc, "adana_ce_fwd_bwd")
         if need_grad:
             gemm.linear_dgrad(dlogits[:n], w, out=dh[s:e])

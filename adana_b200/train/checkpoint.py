@@ -131,7 +131,14 @@ def rsync_if_slurm(ckpt_dir: Path):
     def run():
         staging = project.with_name(project.name + ".incoming")
         staging.mkdir(parents=True, exist_ok=True)
-        subprocess.run(["rsync", "-a", "--delete", f"{local}/", f"{staging}/"], check=False)
+        try:
+            subprocess.run(["rsync", "-a", "--delete", f"{local}/", f"{staging}/"], check=True)
+        except (subprocess.CalledProcessError, OSError) as e:
+            # a failed or partial copy must not replace the last good checkpoint (the reference keeps the old one
+            # too: src/optim/utils.py:19-51)
+            print(f"[Checkpoint] rsync of {local} failed ({e}); keeping the previous {project}")
+            shutil.rmtree(staging, ignore_errors=True)
+            return
         old = project.with_name(project.name + ".old")
         if project.exists():
             if old.exists():
@@ -174,7 +181,8 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
     eng = _engine_of(model)
     sched_sd = scheduler.state_dict() if scheduler is not None else None
     if eng is not None and eng.sharded:
-        payload = {"world": eng.world, "rank": eng.rank, "opt_step": getattr(opt, "step_count", 0), "units": {}}
+        payload = {"world": eng.world, "rank": eng.rank, "opt_step": getattr(opt, "step_count", 0), "itr": int(itr),
+                   "units": {}}
         for u in eng.units:
             entry = {"master": u.master.detach().cpu()}
             for k, t in u.state.items():
@@ -223,14 +231,25 @@ def _load_sharded(eng, opt, sharded_dir: Path):
     layout = json.loads((sharded_dir / "layout.json").read_text())
     saved_world = layout["world"]
     files = {}
-
-    def saved(rank):
-        if rank not in files:
-            files[rank] = _load(sharded_dir / f"rank{rank:05d}.pt")
-        return files[rank]
-
     by_name = {u["name"]: u for u in layout["units"]}
     opt_step = None
+    # A directory whose rank files come from different saves (a crash between two ranks' writes, a partial copy) must
+    # not be resumed from: every rank file carries the iteration it was written at.
+    meta_path = sharded_dir.parent / "meta.pt"
+    want_itr = _load(meta_path).get("itr") if meta_path.exists() else None
+    for r in range(saved_world):
+        if not (sharded_dir / f"rank{r:05d}.pt").exists():
+            raise RuntimeError(f"sharded checkpoint {sharded_dir} is incomplete: rank{r:05d}.pt is missing")
+
+    def saved(rank):      # (each rank opens only the files that overlap its shard; together the ranks open all)
+        if rank not in files:
+            files[rank] = _load(sharded_dir / f"rank{rank:05d}.pt")
+            got = files[rank].get("itr")
+            if want_itr is not None and got is not None and int(got) != int(want_itr):
+                raise RuntimeError(f"sharded checkpoint {sharded_dir} is inconsistent: rank{rank:05d}.pt was written at "
+                                   f"iteration {got}, meta.pt at {want_itr}")
+        return files[rank]
+
     for u in eng.units:
         lu = by_name[u.layout.name]
         if [s["name"] for s in lu["slots"]] != [s.name for s in u.layout.slots]:
@@ -391,6 +410,11 @@ def load_worker_state(ckpt_dir: Path, train_reader=None, verbose=True):
 def checkpoint_exists(ckpt_dir: Path) -> bool:
     ckpt_dir = Path(ckpt_dir)
     return (ckpt_dir / "main.pt").exists() or (ckpt_dir / "meta.pt").exists()
+
+
+def finish_pending_shard_writes():
+    """Blocks until this rank's asynchronous checkpoint file is on disk (re-raises a failed write)."""
+    _async_writer.wait()
 
 
 def finish_pending_writes():

@@ -20,6 +20,7 @@ host-side heartbeat watchdog can abort a rank whose peers stopped responding
 """
 from __future__ import annotations
 
+import contextlib
 import copy
 import time
 from contextlib import nullcontext
@@ -140,8 +141,34 @@ class Trainer:
             self.watchdog.start()
         self.model.train()
 
+    # ---- device status word ------------------------------------------------------------------------------
+    def _read_device_status(self):
+        """Raises when a kernel of this process recorded a timed-out wait (a late or dead peer, a stuck pipeline)
+        in the device status word.  Synchronises the device, so it is called only where the loop synchronises
+        anyway: on logging iterations, before a checkpoint is written and at the end of the run."""
+        if self.cuda and self.engine is not None:
+            from ..ops import _lib
+
+            _lib.check_status(self.cfg.device)
+
+    def check_device_status(self):
+        try:
+            self._read_device_status()
+        except RuntimeError as e:
+            # after a timed-out wait the gradients and weights of this step may be built on stale peer data: stop
+            # here, before they are logged as progress or written to a checkpoint
+            raise RuntimeError(f"iteration {self.curr_iter}: {e}; the run stops before this state is checkpointed") from e
+
+    def _phase(self, name):
+        return self.watchdog.phase(name) if self.watchdog is not None else contextlib.nullcontext()
+
     # ---- checkpoints ------------------------------------------------------------------------------------
     def _write_checkpoint(self, ckpt_dir: Path, label: str):
+        with self._phase("checkpoint"):
+            self.check_device_status()
+            self._write_checkpoint_files(ckpt_dir, label)
+
+    def _write_checkpoint_files(self, ckpt_dir: Path, label: str):
         cfg = self.cfg
         if self.master:
             print(f"[Checkpoint] START {label} iter={self.curr_iter} -> {ckpt_dir}")
@@ -153,6 +180,8 @@ class Trainer:
             self.exp_dir.mkdir(parents=True, exist_ok=True)
             (self.exp_dir / "wandb_run_id.txt").write_text(wandb.run.id)
         ckpt.save_worker_state(ckpt_dir, train_reader=self.train_reader)
+        # every rank's shard file is on disk before any rank passes the barrier and before rank 0 copies the directory
+        ckpt.finish_pending_shard_writes()
         if dist.is_available() and dist.is_initialized():
             dist.barrier()
         if self.master:
@@ -312,7 +341,8 @@ class Trainer:
             is_eval = (self.curr_iter % cfg.eval_interval == 0 or self.curr_iter == cfg.iterations
                        or self.curr_iter in cfg.full_eval_at)
             if is_eval:
-                self.eval_and_log(tokens, epoch, full_eval=self.curr_iter in cfg.full_eval_at)
+                with self._phase("eval"):
+                    self.eval_and_log(tokens, epoch, full_eval=self.curr_iter in cfg.full_eval_at)
                 if self.tau_stats is not None and self.tau_stats.should_collect(self.curr_iter, is_eval):
                     self.tau_stats.collect(self.opt, self.curr_iter)
             if cfg.iterations_to_run is not None and self.iters_in_run >= cfg.iterations_to_run:
@@ -336,8 +366,11 @@ class Trainer:
             if self.curr_iter == 1 and self.master and self.cuda:
                 print(f"[Memory] GPU 0: peak_allocated={torch.cuda.max_memory_allocated() / 1024 ** 3:.2f} GiB, "
                       f"peak_reserved={torch.cuda.max_memory_reserved() / 1024 ** 3:.2f} GiB")
-            if cfg.log_interval and self.curr_iter % cfg.log_interval == 0 and self.master:
-                self.log_train(outputs, loss, dt, tokens, epoch)
+            if cfg.log_interval and self.curr_iter % cfg.log_interval == 0:
+                self.check_device_status()
+                if self.master:
+                    self.log_train(outputs, loss, dt, tokens, epoch)
+        self.check_device_status()
         if self.watchdog is not None:
             self.watchdog.stop()
         ckpt.finish_pending_writes()

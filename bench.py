@@ -33,12 +33,38 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-MODEL = dict(model="enoki", n_layer=36, n_head=36, n_embd=2304, qkv_dim=64, mlp_hidden_dim=9216,
-             sequence_length=2048, vocab_size=50304)
-OPT = dict(opt="dana-star-mk4", kappa=0.85, delta=8.0, clipsnr=2.0, lr=4.6e-5, weight_decay=4.0 / 100.0,
-           wd_ts=100.0, grad_clip=0.5, z_loss_coeff=1e-4)
-PER_GPU_SEQS = 64
-MICRO_BATCH = 8
+# Benchmark configurations.  `enoki36` is the headline (the only one the default command line runs); the others are
+# the remaining training configurations of the benchmark list: the 12-layer Enoki at 32 sequences per GPU (global
+# batch 256 on 8 GPUs), and the Qwen3-style decoder (28 layers, 16 query / 8 KV heads of 128, SwiGLU 6144, RoPE
+# theta 1e6, sequence 4096) trained with distributed Muon.
+CONFIGS = {
+    "enoki36": dict(
+        label="enoki-36 (L{n_layer}, d2304, mlp9216, hd64, V50304)", metric_model="enoki-36",
+        model=dict(model="enoki", n_layer=36, n_head=36, n_embd=2304, qkv_dim=64, mlp_hidden_dim=9216,
+                   sequence_length=2048, vocab_size=50304),
+        per_gpu_seqs=64, micro_batch=8, opt="dana-star-mk4"),
+    "enoki12": dict(
+        label="enoki-12 (L{n_layer}, d768, mlp3072, hd64, V50304)", metric_model="enoki-12",
+        model=dict(model="enoki", n_layer=12, n_head=12, n_embd=768, qkv_dim=64, mlp_hidden_dim=3072,
+                   sequence_length=2048, vocab_size=50304),
+        per_gpu_seqs=32, micro_batch=16, opt="dana-star-mk4"),
+    "qwen3-muon": dict(
+        label="qwen3 (L{n_layer}, d2048, 16Q/8KV x hd128, swiglu 6144, theta 1e6, V50304)", metric_model="qwen3-1.7B",
+        model=dict(model="qwen3", n_layer=28, n_head=16, n_kv_head=8, n_embd=2048, qkv_dim=128, mlp_hidden_dim=6144,
+                   sequence_length=4096, vocab_size=50304, rope_theta=1e6, elementwise_attn_output_gate=False,
+                   normalization_layer_type="rmsnorm"),
+        per_gpu_seqs=32, micro_batch=4, opt="d-muon"),
+}
+OPTS = {
+    "dana-star-mk4": dict(opt="dana-star-mk4", kappa=0.85, delta=8.0, clipsnr=2.0, lr=4.6e-5, weight_decay=4.0 / 100.0,
+                          wd_ts=100.0, wd_decaying=True, grad_clip=0.5, z_loss_coeff=1e-4),
+    "dana-mk4": dict(opt="dana-mk4", kappa=0.85, delta=8.0, clipsnr=2.0, lr=4.6e-5, weight_decay=4.0 / 100.0,
+                     wd_ts=100.0, wd_decaying=True, grad_clip=0.5, z_loss_coeff=1e-4),
+    "adamw": dict(opt="adamw", beta1=0.9, beta2=0.95, lr=3e-4, weight_decay=0.1, grad_clip=0.5, z_loss_coeff=1e-4),
+    "d-muon": dict(opt="d-muon", lr=1e-3, momentum=0.95, nesterov=True, muon_ns_steps=5, beta1=0.8, beta2=0.999,
+                   weight_decay=0.01, grad_clip=0.5, z_loss_coeff=1e-4),
+}
+MODEL = CONFIGS["enoki36"]["model"]
 
 
 def parse():
@@ -47,15 +73,35 @@ def parse():
     p.add_argument("--steps", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--micro_batch", type=int, default=MICRO_BATCH)
-    p.add_argument("--per_gpu_seqs", type=int, default=PER_GPU_SEQS)
-    p.add_argument("--n_layer", type=int, default=MODEL["n_layer"], help="override for smoke runs only")
+    p.add_argument("--config", default="enoki36", choices=sorted(CONFIGS))
+    p.add_argument("--opt", default=None, choices=sorted(OPTS), help="default: the configuration's own optimizer")
+    p.add_argument("--micro_batch", type=int, default=None)
+    p.add_argument("--per_gpu_seqs", type=int, default=None)
+    p.add_argument("--n_layer", type=int, default=None, help="override for smoke runs only")
     p.add_argument("--no_e2e", action="store_true")
     p.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     p.add_argument("--ref_no_compile", action="store_true")
     p.add_argument("--fsdp_weights", default="resident", choices=["resident", "gathered"],
                    help="ours: keep the bf16 block matrices resident on every rank, or as row slices fetched by the GEMMs")
-    return p.parse_args()
+    a = p.parse_args()
+    c = CONFIGS[a.config]
+    a.micro_batch = a.micro_batch or c["micro_batch"]
+    a.per_gpu_seqs = a.per_gpu_seqs or c["per_gpu_seqs"]
+    a.n_layer = a.n_layer or c["model"]["n_layer"]
+    a.opt = a.opt or c["opt"]
+    return a
+
+
+def shared_config(a, world: int) -> dict:
+    """The keys that name the workload; identical for both arms (implementation choices go to `impl_detail`)."""
+    c = CONFIGS[a.config]
+    return {"model": c["label"].format(n_layer=a.n_layer), "global_batch": a.per_gpu_seqs * world,
+            "seq_len": c["model"]["sequence_length"], "micro_batch": a.micro_batch,
+            "acc_steps": a.per_gpu_seqs // a.micro_batch, "optimizer": a.opt, "parallelism": f"fsdp{world}"}
+
+
+def metric_name(a) -> str:
+    return f"tokens/sec/box FSDP {a.opt} {CONFIGS[a.config]['metric_model']}"
 
 
 def dist_env(gpus: int):
@@ -120,7 +166,8 @@ def run_ours(a):
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
     acc = a.per_gpu_seqs // a.micro_batch
     args = flags.defaults()
-    for k, v in {**MODEL, **OPT}.items():
+    conf = CONFIGS[a.config]
+    for k, v in {**conf["model"], **OPTS[a.opt]}.items():
         setattr(args, k, v)
     args.n_layer = a.n_layer
     args.dtype, args.device = "bfloat16", f"cuda:{local_rank}"
@@ -128,13 +175,14 @@ def run_ours(a):
     # the backend's split rule (acc //= gcd(acc, N); batch //= N / gcd) maps this to
     # micro-batch `micro_batch` and `acc` accumulation steps on every rank
     args.batch_size, args.acc_steps = a.micro_batch, acc * world
-    args.wd_decaying, args.weight_tying, args.init_scheme = True, False, "ScaledGPT"
-    args.scheduler, args.iterations, args.warmup_steps = "cos_inf", 100000, 1000
+    args.weight_tying, args.init_scheme = False, "ScaledGPT"
+    # (the same schedule flags as the reference arm: the two arms' learning rates, and so their losses, are comparable)
+    args.scheduler, args.iterations, args.warmup_steps = "cos_inf", a.warmup + a.steps, 1
     args.final_div_factor, args.dataset, args.log_interval = 0.1, "fineweb", 0
     args.attention = a.attention
     args.fsdp_weights = a.fsdp_weights
     steps_total = a.warmup + a.steps
-    tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
+    tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (conf["model"]["sequence_length"] + 1) + 4_000_000
     if rank == 0:
         args.datasets_dir = str(write_tokens(tokens_needed))
     torch.cuda.set_device(local_rank)
@@ -166,16 +214,28 @@ def run_ours(a):
         x, y = train_reader.sample_batch()
         dev_batches.append((x.to(args.device), y.to(args.device)))
 
-    def step_device(i):
+    phase_marks = []       # per timed step: events after (last backward launched, clip, optimizer step)
+
+    def step_device(i, mark=False):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if mark else None
+        if mark:
+            ev[0].record()
         for m in range(acc):
             x, y = dev_batches[(i * acc + m) % len(dev_batches)]
             with backend.get_context_for_microstep_forward(model, m, acc):
                 out = model(x, targets=y)
             (out["loss"] / acc).backward()
+        if mark:
+            ev[1].record()
         backend.clip_grad_norm_(None, args.grad_clip)
+        if mark:
+            ev[2].record()
         opt.step()
         sched.step()
         opt.zero_grad()
+        if mark:
+            ev[3].record()
+            phase_marks.append(ev)
 
     for i in range(a.warmup):
         step_device(i)
@@ -192,7 +252,7 @@ def run_ours(a):
     torch.cuda.synchronize()
     e0.record()
     for i in range(a.steps):
-        step_device(a.warmup + i)
+        step_device(a.warmup + i, mark=True)
     e1.record()
     torch.cuda.synchronize()
     backend.comm.barrier()
@@ -210,6 +270,19 @@ def run_ours(a):
         exposed = {"ms_per_step": float(ex.item()) / a.steps, "fraction_of_step": float(ex.item()) / a.steps / ms_per_step,
                    "what": "time the compute stream waited on gradient reduce-scatter joins, barriers and scalar exchanges (max over ranks)"}
     _lib.check_status()
+    # where the step goes, on the device: forward+backward of all micro-steps (gradient reduce-scatters of finished
+    # units overlap it), the join with the reduce-scatter stream + gradient norm + clip coefficient, and the optimizer
+    # step with the push of the new weights.  `skew` is max - min over ranks of the forward+backward time: what a
+    # rank spends waiting for the slowest one at the next barrier.
+    ph = torch.tensor([[ev[k].elapsed_time(ev[k + 1]) for k in range(3)] for ev in phase_marks],
+                      dtype=torch.float64, device=args.device).mean(0)
+    ph_max, ph_min = ph.clone(), ph.clone()
+    if world > 1:
+        dist.all_reduce(ph_max, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ph_min, op=dist.ReduceOp.MIN)
+    phases = {"fwd_bwd_ms": float(ph_max[0]), "grad_sync_tail_and_clip_ms": float(ph_max[1]),
+              "optimizer_and_weight_push_ms": float(ph_max[2]), "fwd_bwd_skew_ms": float(ph_max[0] - ph_min[0]),
+              "what": "device time per optimizer step, max over ranks (skew: max - min over ranks)"}
 
     # ---- end-to-end region: public API, pinned host batches, loss read back every step ----------------
     e2e = None
@@ -235,16 +308,17 @@ def run_ours(a):
     final_loss = float(out["loss"].item()) if not a.no_e2e else None
     mem = torch.cuda.max_memory_allocated() / 2 ** 30
     if rank == 0:
-        emit({"metric": "tokens/sec/box FSDP dana-star-mk4 enoki-36", "value": tokens_per_step / (ms_per_step / 1e3),
+        emit({"metric": metric_name(a), "value": tokens_per_step / (ms_per_step / 1e3),
               "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
               "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
               "data": "synthetic Zipf(1.0) tokens, random-init weights", "impl": "ours",
-              "config": {"model": f"enoki-36 (L{args.n_layer}, d2304, mlp9216, hd64, V50304)",
-                         "global_batch": a.per_gpu_seqs * world, "seq_len": args.sequence_length,
-                         "micro_batch": a.micro_batch, "acc_steps": acc, "optimizer": "dana-star-mk4",
-                         "parallelism": f"fsdp{world}", "l2": "inputs and weights exceed the 126 MB L2",
-                         "attention": _attention_impl(), "fsdp_weights": a.fsdp_weights},
-              "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "exposed_comm": exposed,
+              "config": shared_config(a, world),
+              "impl_detail": {"l2": "inputs and weights exceed the 126 MB L2", "attention": _attention_impl(),
+                              "fsdp_weights": a.fsdp_weights,
+                              "fsdp_comm": "peer-memory kernels" if getattr(engine, "plane", None) is not None
+                              else ("nccl" if world > 1 else "none (one GPU)"),
+                              "reduce_dtype": getattr(getattr(engine, "ecfg", None), "reduce_dtype", None)},
+              "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "exposed_comm": exposed, "phases": phases,
               "peak_mem_gib": round(mem, 2), "final_loss": final_loss})
     backend.finalize()
 
@@ -309,7 +383,8 @@ def run_reference(a):
 
         acc = a.per_gpu_seqs // a.micro_batch
         steps_total = a.warmup + a.steps
-        tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (MODEL["sequence_length"] + 1) + 4_000_000
+        seq_len = CONFIGS[a.config]["model"]["sequence_length"]
+        tokens_needed = (2 * steps_total + 4) * a.per_gpu_seqs * world * (seq_len + 1) + 4_000_000
         data_root = Path(os.environ.get("ADANA_BENCH_DATA", "/tmp/adana_bench_data"))
         # rank 0 writes the corpus; the others must not reach the reference's dataset code (which would try
         # to download a missing corpus) before the files exist, and no process group is up yet to wait on
@@ -323,20 +398,36 @@ def run_reference(a):
                 if time.time() - t_wait > 600:
                     raise RuntimeError("rank 0 did not finish writing the synthetic corpus within 600 s")
                 time.sleep(0.5)
-        argv = ["--model", "enoki", "--n_layer", str(a.n_layer), "--n_head", "36", "--n_embd", "2304",
-                "--qkv_dim", "64", "--mlp_hidden_dim", "9216", "--sequence_length", "2048", "--vocab_size", "50304",
+        conf = CONFIGS[a.config]
+        md = conf["model"]
+        if md["model"] == "qwen3" and md.get("n_kv_head", md["n_head"]) != md["n_head"]:
+            # the reference's Qwen3 has neither grouped-query attention nor a RoPE-theta flag
+            # (src/models/qwen3.py:116-133, src/config/base.py:266-348): this configuration cannot be stated on its CLI
+            emit({"impl": "reference", "unavailable": "the reference's qwen3 model has no GQA (n_kv_head) and no "
+                  "rope_theta option; config qwen3-muon cannot be expressed on its command line"})
+            done.set()
+            return
+        argv = ["--model", md["model"], "--n_layer", str(a.n_layer), "--n_head", str(md["n_head"]),
+                "--n_embd", str(md["n_embd"]), "--qkv_dim", str(md["qkv_dim"]), "--mlp_hidden_dim",
+                str(md["mlp_hidden_dim"]), "--sequence_length", str(md["sequence_length"]), "--vocab_size", "50304",
                 "--weight_tying", "False", "--init-scheme", "ScaledGPT", "--dtype", "bfloat16",
                 "--distributed_backend", "fsdp", "--device", f"cuda:{local_rank}",
                 # the reference's split rule (acc //= gcd(acc, N); batch //= N / gcd) turns this into
                 # micro-batch `micro_batch` and `acc` accumulation steps per rank
                 "--batch_size", str(a.micro_batch), "--acc_steps", str(acc * world),
-                "--opt", "dana-star-mk4", "--kappa", "0.85", "--delta", "8", "--clipsnr", "2.0", "--lr", "4.6e-5",
-                "--weight_decay", "0.04", "--wd_decaying", "--wd_ts", "100", "--grad_clip", "0.5",
-                "--z_loss_coeff", "1e-4", "--scheduler", "cos_inf", "--iterations", str(steps_total),
+                "--scheduler", "cos_inf", "--iterations", str(steps_total),
                 "--warmup_steps", "1", "--final_div_factor", "0.1", "--dataset", "fineweb",
                 "--datasets_dir", str(data_root), "--log_interval", "1000000", "--eval_interval", "1000000",
                 "--latest_ckpt_interval", "0", "--results_base_folder", "/tmp/adana_ref_exps",
                 "--run_prefix", f"bench{os.getpid()}"]
+        for k, v in OPTS[a.opt].items():
+            if isinstance(v, bool):
+                if k == "nesterov":
+                    argv += ["--nesterov", str(v)]
+                elif v:
+                    argv.append(f"--{k}")
+            else:
+                argv += [f"--{k}", str(v)]
         if not a.ref_no_compile:
             argv.append("--compile")
         sys.argv = ["main.py"] + argv
@@ -396,21 +487,18 @@ def run_reference(a):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             dist.all_reduce(wall, op=dist.ReduceOp.MAX)
         ms_per_step = float(ms.item()) / a.steps
-        tokens_per_step = a.per_gpu_seqs * world * 2048
+        tokens_per_step = a.per_gpu_seqs * world * seq_len
         mem = torch.cuda.max_memory_allocated() / 2 ** 30
         if rank == 0:
-            emit({"metric": "tokens/sec/box FSDP dana-star-mk4 enoki-36", "value": tokens_per_step / (ms_per_step / 1e3),
+            emit({"metric": metric_name(a), "value": tokens_per_step / (ms_per_step / 1e3),
                   "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
                   "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                   "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic Zipf(1.0) tokens, random-init weights",
-                  "impl": "reference",
-                  "config": {"model": f"enoki-36 (L{a.n_layer}, d2304, mlp9216, hd64, V50304)",
-                             "global_batch": a.per_gpu_seqs * world, "seq_len": 2048, "micro_batch": a.micro_batch,
-                             "acc_steps": acc, "optimizer": "dana-star-mk4", "parallelism": f"fsdp{world}",
-                             "compile": not a.ref_no_compile},
+                  "impl": "reference", "config": shared_config(a, world),
+                  "impl_detail": {"compile": not a.ref_no_compile, "attention": "torch SDPA", "fsdp": "torch FSDP2 + NCCL"},
                   "clocks": clocks,
                   "e2e": {"value": tokens_per_step * a.steps / float(wall.item()), "unit": "tokens/s",
-                          "h2d_bytes_per_step": 2 * 8 * a.micro_batch * 2048 * acc, "d2h_bytes_per_step": 4,
+                          "h2d_bytes_per_step": 2 * 8 * a.micro_batch * seq_len * acc, "d2h_bytes_per_step": 4,
                           "note": "the reference's own loop: pinned host batches, .item() on the grad norm every step"},
                   "gpu_launches": None, "peak_mem_gib": round(mem, 2)})
         done.set()

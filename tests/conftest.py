@@ -34,3 +34,10 @@ def tiny_args(model="enoki", **kw):
     for k, v in kw.items():
         setattr(a, k, v)
     return a
+
+
+def torchrun(nproc: int):
+    """Command prefix that starts `nproc` ranks on this machine; torchrun picks a free rendezvous port itself
+    (binding a port, closing it and handing the number on races with every other test that does the same)."""
+    return [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
+            "--nproc-per-node", str(nproc)]

@@ -247,12 +247,51 @@ def test_watchdog_with_fake_store_and_clock():
     b = HeartbeatWatchdog(store, 1, 2, timeout_s=5.0, clock=lambda: now[0])
     assert a.check_once() is None            # peer has not published yet: no verdict
     a.beat(1), b.beat(1)
+    assert a.check_once() is None and b.check_once() is None     # first sighting starts the local timers
     now[0] += 4.0
     assert a.check_once() is None
-    now[0] += 2.0                            # rank 1 silent for 6 s
+    now[0] += 2.0                            # rank 1's value has not changed for 6 s
     a.beat(2)
     msg = a.check_once()
     assert msg is not None and "rank 1" in msg and b.check_once() is None
+    b.beat(2)                                # it moves again: healthy again (the verdict does not latch)
+    assert a.check_once() is None
+
+
+def test_watchdog_tolerates_a_long_master_only_phase_and_ignores_wall_clocks():
+    """A rank that evaluates or checkpoints alone for longer than the timeout keeps its sequence number moving from
+    the background thread, so nobody flags it; a main thread that stops advancing is caught by the step deadline,
+    but not while it reports a phase of its own."""
+    from adana_b200.runtime.watchdog import HeartbeatWatchdog
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+    now = [0.0]
+    store = Store()
+    master = HeartbeatWatchdog(store, 0, 2, timeout_s=5.0, clock=lambda: now[0] + 1000.0)   # skewed clock
+    other = HeartbeatWatchdog(store, 1, 2, timeout_s=5.0, clock=lambda: now[0], step_deadline_s=8.0)
+    master.beat(10), other.beat(10)
+    other.check_once()
+    with master.phase("eval"):
+        for _ in range(30):                  # 30 s of evaluation on the master only; its thread keeps publishing
+            now[0] += 1.0
+            master._publish()
+            assert other.check_once() is None
+    for _ in range(7):                       # back in `train` but stuck at iteration 10
+        now[0] += 1.0
+        master._publish()
+        assert other.check_once() is None
+    now[0] += 2.0
+    master._publish()
+    msg = other.check_once()
+    assert msg is not None and "stayed at iteration 10" in msg
+    master.beat(11)
+    assert other.check_once() is None
 
 
 # ---- expert parallelism ----------------------------------------------------------------------------------------

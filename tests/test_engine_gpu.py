@@ -136,3 +136,33 @@ def test_gathered_weights_match_resident_weights_on_one_gpu():
         d = (pa[k] - pb[k]).abs()
         # sign-like updates: a different bf16 rounding of one gradient element may flip a step of size ~lr
         assert d.mean().item() < 1.5e-3 and d.max().item() < 3e-2, (k, d.mean().item(), d.max().item())
+
+
+def test_batch_stager_waits_for_queued_readers_of_a_slot():
+    """The host may run ahead of the GPU: a device slot is refilled only after the kernels that were queued on the
+    consumer's stream while it was handed out have finished (the copy stream waits for the consumer stream)."""
+    from adana_b200.data.readers import PinnedBatchStager
+
+    class Counting:
+        local_batch_size, sequence_length = 8, 1024
+
+        def __init__(self):
+            self.n = 0
+
+        def sample_batch(self, out=None):
+            x, y = out
+            x.fill_(self.n)
+            y.fill_(self.n + 1000)
+            self.n += 1
+            return x, y
+
+    for lookahead in (False, True):
+        stager = PinnedBatchStager(Counting(), "cuda", depth=2, lookahead=lookahead)
+        x0, y0 = stager.next_batch()
+        torch.cuda._sleep(400_000_000)           # ~0.2 s of work on the consumer stream "still reading" the slot
+        snap_x, snap_y = x0.clone(), y0.clone()   # queued behind the sleep
+        for _ in range(3):                       # more batches than slots: slot 0 is refilled
+            stager.next_batch()
+        torch.cuda.synchronize()
+        assert int(snap_x.min()) == 0 and int(snap_x.max()) == 0, lookahead
+        assert int(snap_y.min()) == 1000 and int(snap_y.max()) == 1000, lookahead

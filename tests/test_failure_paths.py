@@ -1,0 +1,88 @@
+"""Failure paths that must stop a run instead of corrupting it: a device wait that timed out (status word),
+a sharded checkpoint whose rank files come from different saves, a failed rsync of a checkpoint."""
+import json
+import subprocess
+from pathlib import Path
+
+import pytest
+import torch
+
+from adana_b200 import main as M
+from adana_b200.train import checkpoint as ck
+from adana_b200.train import loop as L
+
+
+def _argv(tmp_path, extra=()):
+    return ["--model", "enoki", "--n_layer", "2", "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim",
+            "128", "--sequence_length", "32", "--batch_size", "4", "--vocab_size", "512", "--dataset", "synthetic-zipf",
+            "--datasets_dir", str(tmp_path / "data"), "--opt", "dana-star-mk4", "--lr", "1e-3", "--iterations", "8",
+            "--warmup_steps", "2", "--scheduler", "cos_inf", "--eval_interval", "100", "--eval_batches", "1",
+            "--log_interval", "2", "--latest_ckpt_interval", "4", "--results_base_folder", str(tmp_path / "exps"),
+            "--device", "cpu", "--dtype", "float32", "--distributed_backend", "single", *extra]
+
+
+def test_timed_out_device_wait_stops_the_run_before_the_next_checkpoint(tmp_path, monkeypatch):
+    """The status word is read on logging iterations and before every checkpoint; once it reports a timed-out wait
+    the run raises, and the state computed after the timeout is never written."""
+    seen = []
+
+    def fake_status(self):
+        seen.append(self.curr_iter)
+        if self.curr_iter >= 3:          # "a peer flag wait ran out during iteration 3"
+            raise RuntimeError("adana_b200 kernel reported: timeout: wait on a peer flag")
+
+    monkeypatch.setattr(L.Trainer, "_read_device_status", fake_status)
+    args, parser = M.get_args(_argv(tmp_path))
+    with pytest.raises(RuntimeError, match="peer flag.*stops before this state is checkpointed"):
+        M.main(args, parser)
+    assert seen[0] == 0 and 2 in seen              # checked before the checkpoint at 0 and on the logging iteration 2
+    exp = next((tmp_path / "exps").iterdir())
+    saved = torch.load(exp / "ckpts" / "latest" / "main.pt", weights_only=False)
+    assert saved["itr"] == 0                       # the checkpoint due at iteration 4 was not written
+
+
+def test_sharded_checkpoint_from_two_different_saves_is_refused(tmp_path):
+    from conftest import tiny_args
+    from adana_b200.models.utils import get_model
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    a = tiny_args("enoki", opt="adamw")
+    m = get_model(a)
+    eng = attach(m, a, device="cpu")
+    eng.sharded = True                     # one rank writing the sharded layout
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = EngineOptimizer(eng, "adamw", a, specs)
+    d = tmp_path / "latest"
+    ck.save_checkpoint(m, opt, None, 7, d)
+    assert ck.load_checkpoint(m, opt, None, d) == 7
+    shard = d / "sharded" / "rank00000.pt"
+    payload = torch.load(shard, weights_only=False)
+    assert payload["itr"] == 7
+    payload["itr"] = 6                     # as if this rank's file were left over from the previous save
+    torch.save(payload, shard)
+    with pytest.raises(RuntimeError, match="inconsistent.*iteration 6.*meta.pt at 7"):
+        ck.load_checkpoint(m, opt, None, d)
+    shard.unlink()
+    with pytest.raises(RuntimeError, match="incomplete"):
+        ck.load_checkpoint(m, opt, None, d)
+
+
+def test_failed_rsync_keeps_the_last_good_checkpoint(tmp_path, monkeypatch):
+    project = tmp_path / "project" / "latest"
+    project.mkdir(parents=True)
+    (project / "main.pt").write_text("good")
+    local = tmp_path / "node" / "ckpts" / "latest"
+    local.mkdir(parents=True)
+    (local / "main.pt").write_text("new")
+    monkeypatch.setenv("SLURM_TMPDIR", str(tmp_path / "node"))
+
+    def failing(cmd, check=False, **kw):
+        assert check is True
+        raise subprocess.CalledProcessError(23, cmd)
+
+    monkeypatch.setattr(ck.subprocess, "run", failing)
+    ck.rsync_if_slurm(project)
+    ck.wait_for_rsync()
+    assert (project / "main.pt").read_text() == "good" and not project.with_name("latest.incoming").exists()

@@ -11,6 +11,8 @@ from pathlib import Path
 import numpy as np
 import pytest
 
+from conftest import torchrun
+
 ROOT = Path(__file__).resolve().parent.parent
 
 # launcher for the reference: the GPT-2 BPE files cannot be downloaded here and every model constructor asks for the
@@ -80,11 +82,7 @@ def test_training_log_equals_the_reference_line_by_line(ref_src, tmp_path, model
     def python(*tail):
         if ranks == 1:
             return [sys.executable, *tail]
-        with socket.socket() as sock:
-            sock.bind(("127.0.0.1", 0))
-            port = sock.getsockname()[1]
-        return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
-                "127.0.0.1", "--master-port", str(port), *tail]
+        return [*torchrun(ranks), *tail]
 
     ref_flags = flags + (["--distributed_backend", "gloo"] if ranks > 1 else [])
     our_flags = flags + (["--distributed_backend", ours_backend] if ranks > 1 else [])

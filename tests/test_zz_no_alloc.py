@@ -87,3 +87,33 @@ def test_static_scratch_accumulates_and_rejects_oversize():
               dw.data_ptr(), 0, 4, 770, 0, None, stream) == E_COLS
     torch.cuda.synchronize()
     assert torch.equal(dw, before)
+
+
+def test_static_scratch_rmsnorm_without_mean_and_empty_batch():
+    """RMSNorm never reads `mean`, so a caller may pass NULL; zero rows leave dw = 0 (or untouched when accumulating)."""
+    from adana_b200.ops import norm
+
+    fn = _symbol()
+    stream = torch.cuda.current_stream().cuda_stream
+    rows, cols = 640, 512
+    x, dy, w, mean, rstd = _case(rows, cols, 1, 3)
+    dx = torch.empty(rows, cols, device="cuda")
+    dw = torch.empty(cols, device="cuda")
+    assert fn(dy.data_ptr(), 1, x.data_ptr(), 0, w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), 0,
+              dw.data_ptr(), 0, rows, cols, 1, None, stream) == 0
+    want_dx, want_dw = norm.norm_bwd(dy, x, w, mean, rstd, kind=1)
+    torch.cuda.synchronize()
+    assert torch.allclose(dx, want_dx, rtol=1e-6, atol=1e-7)
+    assert torch.allclose(dw, want_dw, rtol=1e-6, atol=1e-6)
+    # LayerNorm does read it: NULL is refused
+    assert fn(dy.data_ptr(), 1, x.data_ptr(), 0, w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), 0,
+              dw.data_ptr(), 0, rows, cols, 0, None, stream) == -22
+    dw.fill_(5.0)
+    assert fn(dy.data_ptr(), 1, x.data_ptr(), 0, w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), 0,
+              dw.data_ptr(), 1, 0, cols, 1, None, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dw, torch.full_like(dw, 5.0))
+    assert fn(dy.data_ptr(), 1, x.data_ptr(), 0, w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), 0,
+              dw.data_ptr(), 0, 0, cols, 1, None, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dw, torch.zeros_like(dw))
