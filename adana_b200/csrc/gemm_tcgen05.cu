@@ -360,8 +360,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ---------------------------------------
-    if (lane == 0) {
+    // The whole warp runs the loop in lock step and one elected lane issues: the descriptors are then computed in
+    // warp-uniform code (a tcgen05.mma takes them from uniform registers; inside a one-lane branch every operand of
+    // every product is first moved there).  A stage's descriptors are its base descriptor plus the 16-byte-unit
+    // offset of the contraction step.
+    {
+      const bool issuer = elect_one();
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(smem0, CHUNK_BYTES, 1024) : make_smem_desc_sw128(smem0, 16, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem0 + A_BYTES, CHUNK_BYTES, 1024)
+                                    : make_smem_desc_sw128(smem0 + A_BYTES, 16, 1024);
+      constexpr uint64_t A_STEP = (A_MN ? 2048 : 32) >> 4, B_STEP = (B_MN ? 2048 : 32) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -369,42 +380,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
-        if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status,
-                       ST_TIMEOUT_TMEM_EMPTY)) {
+        if (!mbar_wait_warp(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tb + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, args.status,
-                         ST_TIMEOUT_SMEM_FULL)) {
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag, args.status, ST_TIMEOUT_SMEM_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sB = sA + A_BYTES;
+          const uint64_t da = a_desc0 + (uint64_t)((stage * STAGE_BYTES) >> 4);
+          const uint64_t db = b_desc0 + (uint64_t)((stage * STAGE_BYTES) >> 4);
+          if (issuer) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            uint64_t da, db;
-            if constexpr (!A_MN)
-              da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
-            else
-              da = make_smem_desc_sw128(sA + kk * 2048, CHUNK_BYTES, 1024);
-            if constexpr (!B_MN)
-              db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
-            else
-              db = make_smem_desc_sw128(sB + kk * 2048, CHUNK_BYTES, 1024);
-            umma_ss(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_ss(tmem_d, da + kk * A_STEP, db + kk * B_STEP, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs retire
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs retire
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) umma_commit(&tfull_bar[buf]);
+        if (ok && issuer) umma_commit(&tfull_bar[buf]);
       }
     }
   } else {
@@ -850,12 +851,20 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) -------------------------
-    if (lane == 0 && leader) {
+    // Warp-uniform loop with one elected issuing lane (see the one-CTA kernel above).
+    if (leader) {
+      const bool issuer = elect_one();
+      const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
       constexpr uint32_t idesc = make_idesc_bf16(P_BM, BN, A_MN, B_MN);
       const uint32_t own_empty0 = smem_u32(&empty_bar[0]);
       const uint32_t peer_empty0 = mapa_smem(own_empty0, 1);
       const uint32_t own_tfull0 = smem_u32(&tfull_bar[0]);
       const uint32_t peer_tfull0 = mapa_smem(own_tfull0, 1);
+      const uint32_t smem0 = smem_u32(smem);
+      const uint64_t a_desc0 = A_MN ? make_smem_desc_sw128(smem0, CHUNK_BYTES, 1024) : make_smem_desc_sw128(smem0, 16, 1024);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc_sw128(smem0 + P_TILE_BYTES, CHUNK_BYTES, 1024)
+                                    : make_smem_desc_sw128(smem0 + P_TILE_BYTES, 16, 1024);
+      constexpr uint64_t A_STEP = (A_MN ? 2048 : 32) >> 4, B_STEP = (B_MN ? 2048 : 32) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -864,43 +873,34 @@ __device__ __forceinline__ void gemm_pair_body(const CUtensorMap& tmA, const CUt
       for (; ok && w.next(); ++it) {
         const int buf = it & 1;
         const uint32_t use = (uint32_t)(it >> 1);
-        if (!mbar_wait(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status,
-                       ST_TIMEOUT_TMEM_EMPTY)) {
+        if (!mbar_wait_warp(&tempty_bar[buf], (use & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_TMEM_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tb + buf * BN;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag, args.status, ST_TIMEOUT_SMEM_FULL)) {
+          if (!mbar_wait_warp(&full_bar[stage], phase, abort_flag, args.status, ST_TIMEOUT_SMEM_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sA = smem_u32(smem + stage * P_STAGE_BYTES);
-          const uint32_t sB = sA + P_TILE_BYTES;
+          const uint64_t da = a_desc0 + (uint64_t)((stage * P_STAGE_BYTES) >> 4);
+          const uint64_t db = b_desc0 + (uint64_t)((stage * P_STAGE_BYTES) >> 4);
+          if (issuer) {
 #pragma unroll
-          for (int kk = 0; kk < BK / 16; ++kk) {
-            uint64_t da, db;
-            if constexpr (!A_MN)
-              da = make_smem_desc_sw128(sA + kk * 32, 16, 1024);
-            else
-              da = make_smem_desc_sw128(sA + kk * 2048, CHUNK_BYTES, 1024);
-            if constexpr (!B_MN)
-              db = make_smem_desc_sw128(sB + kk * 32, 16, 1024);
-            else
-              db = make_smem_desc_sw128(sB + kk * 2048, CHUNK_BYTES, 1024);
-            umma_ss_pair(tmem_d, da, db, idesc, (kb != w.kb0 || kk != 0) ? 1u : 0u);
+            for (int kk = 0; kk < BK / 16; ++kk)
+              umma_ss_pair(tmem_d, da + kk * A_STEP, db + kk * B_STEP, idesc, (kb != w.kb0 || kk != 0) ? 1u : 0u);
+            // the stage is free in BOTH CTAs once these MMAs retire
+            umma_commit_pair(own_empty0 + stage * 8);
+            umma_commit_pair(peer_empty0 + stage * 8);
           }
-          // the stage is free in BOTH CTAs once these MMAs retire
-          umma_commit_pair(own_empty0 + stage * 8);
-          umma_commit_pair(peer_empty0 + stage * 8);
           if (++stage == P_STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) {
+        if (ok && issuer) {
           umma_commit_pair(own_tfull0 + buf * 8);
           umma_commit_pair(peer_tfull0 + buf * 8);
         }
