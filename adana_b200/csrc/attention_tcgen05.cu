@@ -438,13 +438,18 @@ namespace adana {
 // their B operand from it.
 //
 // Roles: warp 0 TMA producer (Q_i, dO_i and the tile's 128 lse2 / delta values per item), warp 1 MMA issuer,
-// warps 2..9 score warps (warp w owns the tensor-memory lane quarter w % 4 = 32 key rows; the two warps of a
-// quarter split the 128 query columns), warps 10..13 drain dQ.
+// warps 2..9 exponential warps (S^T -> P^T; warp w owns the tensor-memory lane quarter w % 4 = 32 key rows, the
+// two warps of a quarter split the 128 query columns), warps 10..13 dS warps (P^T, dP^T -> dS^T for a whole key
+// row per thread, then the drain of the previous item's dQ).  The exponentials are bound by the special-function
+// unit and need two warps per scheduler to keep it busy; the dS arithmetic is bound by the FMA pipe and by
+// instruction issue: in separate warps the two overlap, and the single S^T region only has to wait for the
+// exponentials, not for the dS pass.
 //
 // Tensor-memory columns (512):   head_dim 64: S^T | dP^T x2 | dV | dK      head_dim 128: S^T | dP^T | dV | dK
-// Packed P^T / dS^T of the two column halves sit at columns [0,32) and [96,128) of their region (each half
-// only overwrites columns whose fp32 values it has already loaded).  dQ_i lands in columns [32,96) of its
-// item's dP^T region (head_dim 64) or over the S^T region (head_dim 128, where P^T has been consumed by then).
+// Packed bf16 P^T takes columns [0,32) and [64,96) of the S^T region (each column half overwrites only fp32
+// columns it has already loaded); packed dS^T takes columns [0,64) of its dP^T region.  dQ_i lands in columns
+// [64,128) of its item's dP^T region (head_dim 64) or over the S^T region (head_dim 128, where P^T has been
+// consumed by then).
 // head_dim 64: with two dP^T regions and two dS^T tiles the chain of an item (dP^T -> dS^T -> dK, dQ -> drain)
 // overlaps the next item's (S^T -> P^T -> dV); head_dim 128 has no columns to spare and runs the items back
 // to back.  lse2 and `delta` are per QUERY, i.e. per column here: every lane reads the same staged values.
@@ -491,7 +496,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr int DPT_BUFS = (HD == 64) ? 2 : 1;
   constexpr bool OVERLAP = (HD == 64);
   constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = DPT_COL + DPT_BUFS * 128, DK_COL = DV_COL + HD;
-  constexpr uint32_t HALF1_COL = 96;      // packed bf16 columns of the second column half inside an S^T / dP^T region
+  constexpr uint32_t DQ_IN_DPT = 64;      // head_dim 64: dQ's columns inside its item's dP^T region
   static_assert(DK_COL + HD == 512, "tensor-memory plan must fill 512 columns");
   static_assert(L::TOTAL <= 227 * 1024, "shared memory plan");
 
@@ -507,7 +512,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* dq_full = bars + 16;       // [2]  MMA: dK / dQ products of the item retired      (by item parity)
   uint64_t* dq_free = bars + 18;       // [2]  drain warps: dQ drained                        (by item parity)
   uint64_t* acc_full = bars + 20;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* p_read = bars + 21;        // [2]  dS warps: P^T is in their registers (S^T may be overwritten)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 23);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -531,8 +537,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&p_full[s], 8);
+      mbar_init(&p_read[s], 4);
       mbar_init(&dpt_full[s], 1);
-      mbar_init(&ds_full[s], 8);
+      mbar_init(&ds_full[s], 4);
       mbar_init(&dq_full[s], 1);
       mbar_init(&dq_free[s], 4);
     }
@@ -644,7 +651,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       };
       // column of the packed bf16 operand for contraction step kk (16 queries = 8 columns)
-#define PACKED_COL(kk) ((kk) < 4 ? (uint32_t)((kk) * 8) : HALF1_COL + (uint32_t)(((kk) - 4) * 8))
+#define PACKED_COL(kk) ((uint32_t)((kk) * 8))
+#define P_COL_OF(kk) ((kk) < 4 ? (uint32_t)((kk) * 8) : 64u + (uint32_t)(((kk) - 4) * 8))
 
       if (ok && n_items > 0) {
         ok = wait_qdo(0);
@@ -660,7 +668,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint64_t do_mn = do_mnmaj0 + (uint64_t)(st * TILE16);
         const uint64_t ds_mn = ds_mnmaj0 + (uint64_t)((t % L::DS_BUFS) * DS16);
         const uint32_t dpt = tmem_base + DPT_COL + (t % DPT_BUFS) * 128;
-        const uint32_t dq_col = OVERLAP ? (dpt + 32) : (tmem_base + ST_COL);
+        const uint32_t dq_col = OVERLAP ? (dpt + DQ_IN_DPT) : (tmem_base + ST_COL);
         const uint32_t acc = t > 0 ? 1u : 0u;
         // dV += P^T dO
         if (!mbar_wait_warp(&p_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
@@ -668,12 +676,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < ATT_BQ / 16; ++kk)
-            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + PACKED_COL(kk), do_mn + MNMAJ_STEP(kk), idesc_ts,
+            umma_ts(tmem_base + DV_COL, tmem_base + ST_COL + P_COL_OF(kk), do_mn + MNMAJ_STEP(kk), idesc_ts,
                     kk > 0 ? 1u : acc);
         }
         if (OVERLAP && t + 1 < n_items) {
-          // next item's S^T goes over the region whose P^T the product above consumes (same pipe, in order)
+          // next item's S^T goes over the region whose P^T the product above consumes (same pipe, in order) and the
+          // dS warps have copied to their registers
           if (!wait_qdo(t + 1)) { ok = false; break; }
+          if (!mbar_wait_warp(&p_read[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
           tc_fence_after_sync();
           issue_st(t + 1);
         }
@@ -713,104 +723,53 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #undef KMAJ_STEP
 #undef MNMAJ_STEP
 #undef PACKED_COL
+#undef P_COL_OF
       if (ok && leader) umma_commit(acc_full);
     }
   } else if (warp < 10) {
-    // ------------------------------ score warps ---------------------------------------------
+    // ------------------------------ exponential warps: S^T_t -> P^T_t ---------------------------
     const int quad = warp & 3;
-    const int wg = (warp - 2) >> 2;
-    const int r = quad * 32 + lane;          // key row inside the tile
+    const int wg = (warp - 2) >> 2;          // column half
+    const int r = quad * 32 + lane;          // key row inside the tile = tensor-memory lane
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    const uint32_t pcol = wg ? HALF1_COL : 0u;
     bool ok = true;
-    uint32_t pk[32];                         // this thread's 64 probabilities (bf16 pairs) of the item in flight
-
     for (int t = 0; t < n_items && ok; ++t) {
-      const int st = t % STAGES;
       const bool diag = (t % n_i) == 0;        // i == j
-      const float* lse = reinterpret_cast<const float*>(smem + L::STAT_OFF + st * 1024) + wg * 64;
-      const float* nd = lse + 128;
-      // ---- S^T_t -> P^T_t (bf16, over the S^T columns this thread has read) ----
       if (!mbar_wait(st_full, (uint32_t)t & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      // (the item's Q / dO stage, which carries lse2, arrived before the MMA warp could issue S^T)
+      const float* lse = reinterpret_cast<const float*>(smem + L::STAT_OFF + (t % STAGES) * 1024) + wg * 64;
       tc_fence_after_sync();
-      {
-        const uint32_t s_addr = tmem_base + ST_COL + lane_addr + wg * 64;
-        const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
-        uint32_t sa[32], sb[32];
-        tmem_ld_32x32b_x32(s_addr, sa);
-        tmem_ld_32x32b_x32(s_addr + 32, sb);
-        tmem_wait_ld();
+      const uint32_t s_addr = tmem_base + ST_COL + lane_addr + wg * 64;
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
+      uint32_t pk[32], sa[32], sb[32];
+      tmem_ld_32x32b_x32(s_addr, sa);
+      tmem_ld_32x32b_x32(s_addr + 32, sb);
+      tmem_wait_ld();
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t(&sv)[32] = cc ? sb : sa;
-          if (diag) {
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t(&sv)[32] = cc ? sb : sa;
+        if (diag) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if ((wg * 64 + cc * 32 + e) < r) sv[e] = 0xff800000u;   // query before key: -inf, probability exactly 0
-          }
-#pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const float4 l = *reinterpret_cast<const float4*>(lse + cc * 32 + e);
-            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), sc2,
-                                         make_float2(-l.x, -l.y));
-            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3])), sc2,
-                                         make_float2(-l.z, -l.w));
-            pk[cc * 16 + (e >> 1)] = pack_bf16x2(ex2_approx(x0.x), ex2_approx(x0.y));
-            pk[cc * 16 + (e >> 1) + 1] = pack_bf16x2(ex2_approx(x1.x), ex2_approx(x1.y));
-          }
+          for (int e = 0; e < 32; ++e)
+            if ((wg * 64 + cc * 32 + e) < r) sv[e] = 0xff800000u;   // query before key: -inf, probability exactly 0
         }
-        tmem_st_32x32b_x32(tmem_base + ST_COL + lane_addr + pcol, pk);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[t & 1]);
-      }
-      // ---- dP^T_t -> dS^T_t: tensor memory (over the dP^T columns already read) and the shared-memory tile ----
-      if (!mbar_wait(&dpt_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
-      if (t >= L::DS_BUFS) {
-        // the shared-memory tile is free once the dQ product that read it (item t - DS_BUFS) has retired
-        const int u = t - L::DS_BUFS;
-        if (!mbar_wait(&dq_full[u & 1], (uint32_t)(u >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
-      }
-      tc_fence_after_sync();
-      {
-        const uint32_t dpt = tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + lane_addr;
-        uint8_t* sDS = smem + L::DS_OFF + (t % L::DS_BUFS) * (ATT_BQ * ATT_BKV * 2);
-        const float2 s2 = make_float2(args.scale, args.scale);
-        uint32_t da[16], db[16], dk_[32];
-        tmem_ld_32x32b_x16(dpt + wg * 64, da);
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {       // 16 columns at a time, the next load in flight
-          uint32_t(&dv)[16] = (cc & 1) ? db : da;
-          uint32_t(&nx)[16] = (cc & 1) ? da : db;
-          tmem_wait_ld();
-          if (cc < 3) tmem_ld_32x32b_x16(dpt + wg * 64 + (cc + 1) * 16, nx);
-#pragma unroll
-          for (int e = 0; e < 16; e += 4) {
-            const float4 d = *reinterpret_cast<const float4*>(nd + cc * 16 + e);
-            const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2,
-                                         make_float2(d.x, d.y));
-            const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(dv[e + 2]), __uint_as_float(dv[e + 3])), s2,
-                                         make_float2(d.z, d.w));
-            const float2 g0 = __fmul2_rn(unpack_bf16x2(pk[cc * 8 + (e >> 1)]), t0);
-            const float2 g1 = __fmul2_rn(unpack_bf16x2(pk[cc * 8 + (e >> 1) + 1]), t1);
-            dk_[cc * 8 + (e >> 1)] = pack_bf16x2(g0.x, g0.y);
-            dk_[cc * 8 + (e >> 1) + 1] = pack_bf16x2(g1.x, g1.y);
-          }
+        for (int e = 0; e < 32; e += 4) {
+          const float4 l = *reinterpret_cast<const float4*>(lse + cc * 32 + e);
+          const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(sv[e]), __uint_as_float(sv[e + 1])), sc2,
+                                       make_float2(-l.x, -l.y));
+          const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(sv[e + 2]), __uint_as_float(sv[e + 3])), sc2,
+                                       make_float2(-l.z, -l.w));
+          pk[cc * 16 + (e >> 1)] = pack_bf16x2(ex2_approx(x0.x), ex2_approx(x0.y));
+          pk[cc * 16 + (e >> 1) + 1] = pack_bf16x2(ex2_approx(x1.x), ex2_approx(x1.y));
         }
-        tmem_st_32x32b_x32(dpt + pcol, dk_);
-        // the same 64 values as row r of the [keys][queries] tile, 128B-swizzled (chunk wg = this half's 64 columns)
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int off = wg * CHUNK_BYTES + r * 128 + ((u ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dk_[u * 4], dk_[u * 4 + 1], dk_[u * 4 + 2], dk_[u * 4 + 3]);
-        }
-        fence_proxy_async_smem();
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ds_full[t & 1]);
       }
+      // 64 probabilities = 32 columns of bf16 pairs, over the first 32 fp32 columns of this half
+      tmem_st_32x32b_x32(tmem_base + ST_COL + lane_addr + wg * 64, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t & 1]);
     }
     // ---- epilogue: dK_j, dV_j (row = key index) ----
     if (ok && mbar_wait(acc_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
@@ -841,35 +800,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------ dQ drain warps (10..13) ----------------------------------
-    // dQ_i of item t: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the fp32
-    // accumulation buffer (the adds happen in L2, 128 bytes at a time).  A warp stages and sends its own 32 query
-    // rows, 32 columns per box.
+    // ------------------------------ dS warps (10..13): P^T_t, dP^T_t -> dS^T_t, then drain dQ_{t-1} ----------
     const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // key row (dS), query row (dQ drain)
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     uint8_t* sDQw = smem + L::DQ_OFF + (warp - 10) * L::DQ_BOX;
     bool ok = true;
-    for (int t = 0; t < n_items && ok; ++t) {
+    // dQ_i of item t: tensor memory -> registers -> swizzled fp32 staging rows -> bulk reduce-adds into the fp32
+    // accumulation buffer (the adds happen in L2, 128 bytes at a time).  A warp stages and sends its own 32 query
+    // rows, 32 columns per box, and has ONE box: a box may be refilled only after the reduce that was sent from it
+    // has read it, so the column chunks of an item are drained at different points of the loop (chunks [c0, c1) per
+    // call) with other work in between instead of waiting for the copy engine each time.
+    auto drain = [&](int t, int c0, int c1, bool last) -> bool {
       const int g = t / n_i, i = j + t % n_i;
       const int hq = hk * G + g;
-      if (!mbar_wait(&dq_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      if (!mbar_wait(&dq_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
       tc_fence_after_sync();
-      const uint32_t dq_col = OVERLAP ? (tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + 32) : (tmem_base + ST_COL);
+      const uint32_t dq_col = OVERLAP ? (tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + DQ_IN_DPT) : (tmem_base + ST_COL);
       const int tok0 = b * args.S + i * ATT_BQ + quad * 32;
-      uint32_t o[32], o2[32];
-      tmem_ld_32x32b_x32(dq_col + lane_addr, o);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t(&cur)[32] = (c & 1) ? o2 : o;
-        uint32_t(&nxt)[32] = (c & 1) ? o : o2;
-        tmem_wait_ld();
-        if (c + 1 < HD / 32) tmem_ld_32x32b_x32(dq_col + lane_addr + (c + 1) * 32, nxt);
+      for (int c = c0; c < c1; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(dq_col + lane_addr + c * 32, o);
         if (lane == 0) tma_wait_group_read0();      // the previous reduce has read the box
         __syncwarp();
+        tmem_wait_ld();
 #pragma unroll
         for (int u = 0; u < 8; ++u)
           *reinterpret_cast<uint4*>(sDQw + lane * 128 + ((u ^ (lane & 7)) << 4)) =
-              make_uint4(cur[u * 4], cur[u * 4 + 1], cur[u * 4 + 2], cur[u * 4 + 3]);
+              make_uint4(o[u * 4], o[u * 4 + 1], o[u * 4 + 2], o[u * 4 + 3]);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -877,11 +836,86 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tma_commit_group();
         }
       }
-      // every dQ column of the item is in registers or on its way: the region may be overwritten
+      if (last) {
+        // every dQ column of the item is in registers or on its way: the region may be overwritten
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&dq_free[t & 1]);
+      }
+      return true;
+    };
+    constexpr int NCH = HD / 32;         // dQ column chunks of an item
+    for (int t = 0; t < n_items && ok; ++t) {
+      const float* nd = reinterpret_cast<const float*>(smem + L::STAT_OFF + (t % STAGES) * 1024) + 128;
+      uint32_t pk[64];
+      if (!mbar_wait(&p_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      tc_fence_after_sync();
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&pk[32]);
+        tmem_ld_32x32b_x32(tmem_base + ST_COL + lane_addr, lo);
+        tmem_ld_32x32b_x32(tmem_base + ST_COL + lane_addr + 64, hi);
+        tmem_wait_ld();
+      }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&dq_free[t & 1]);
+      if (lane == 0) mbar_arrive(&p_read[t & 1]);     // the next item's S^T may overwrite the region
+      if (OVERLAP && t > 0) {                          // first half of the previous item's dQ
+        if (!drain(t - 1, 0, NCH / 2, false)) { ok = false; break; }
+      }
+      if (!mbar_wait(&dpt_full[t & 1], (uint32_t)(t >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      if (t >= L::DS_BUFS) {
+        // the shared-memory tile is free once the dQ product that read it (item t - DS_BUFS) has retired
+        const int u = t - L::DS_BUFS;
+        if (!mbar_wait(&dq_full[u & 1], (uint32_t)(u >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) { ok = false; break; }
+      }
+      tc_fence_after_sync();
+      const uint32_t dpt = tmem_base + DPT_COL + (t % DPT_BUFS) * 128 + lane_addr;
+      uint8_t* sDS = smem + L::DS_OFF + (t % L::DS_BUFS) * (ATT_BQ * ATT_BKV * 2);
+      const float2 s2 = make_float2(args.scale, args.scale);
+      uint32_t da[16], db[16];
+      tmem_ld_32x32b_x16(dpt, da);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {            // 16 query columns at a time, the next load in flight
+        uint32_t(&dv)[16] = (c & 1) ? db : da;
+        uint32_t(&nx)[16] = (c & 1) ? da : db;
+        tmem_wait_ld();
+        if (c < 7) tmem_ld_32x32b_x16(dpt + (c + 1) * 16, nx);
+        uint32_t out[8];
+#pragma unroll
+        for (int e = 0; e < 16; e += 4) {
+          const float4 d = *reinterpret_cast<const float4*>(nd + c * 16 + e);
+          const float2 t0 = __ffma2_rn(make_float2(__uint_as_float(dv[e]), __uint_as_float(dv[e + 1])), s2,
+                                       make_float2(d.x, d.y));
+          const float2 t1 = __ffma2_rn(make_float2(__uint_as_float(dv[e + 2]), __uint_as_float(dv[e + 3])), s2,
+                                       make_float2(d.z, d.w));
+          const float2 g0 = __fmul2_rn(unpack_bf16x2(pk[c * 8 + (e >> 1)]), t0);
+          const float2 g1 = __fmul2_rn(unpack_bf16x2(pk[c * 8 + (e >> 1) + 1]), t1);
+          out[e >> 1] = pack_bf16x2(g0.x, g0.y);
+          out[(e >> 1) + 1] = pack_bf16x2(g1.x, g1.y);
+        }
+        // bf16 pairs over dP^T columns [8c, 8c+8): all of them were loaded in this or an earlier step
+        tmem_st_32x32b_x8(dpt + c * 8, out);
+        // the same 16 values in row r of the [keys][queries] tile, 128B-swizzled: 64-column chunk c / 4, two granules
+        uint8_t* row = sDS + (c >> 2) * CHUNK_BYTES + r * 128;
+        const int g = (c & 3) * 2;
+        *reinterpret_cast<uint4*>(row + (((g) ^ (r & 7)) << 4)) = make_uint4(out[0], out[1], out[2], out[3]);
+        *reinterpret_cast<uint4*>(row + (((g + 1) ^ (r & 7)) << 4)) = make_uint4(out[4], out[5], out[6], out[7]);
+      }
+      fence_proxy_async_smem();
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full[t & 1]);
+      // head_dim 64: one item behind, so that the dK / dQ products of this item run meanwhile; head_dim 128: at once,
+      // the next item's S^T waits for this dQ to leave its region
+      if (OVERLAP) {
+        if (t > 0) ok = drain(t - 1, NCH / 2, NCH, true);
+      } else {
+        ok = drain(t, 0, NCH, true);
+      }
     }
+    if (OVERLAP && ok && n_items > 0) ok = drain(n_items - 1, 0, NCH, true);
     if (lane == 0) tma_wait_group_read0();   // staging rows are not needed any more
     __syncwarp();
   }
