@@ -160,6 +160,15 @@ int adana_p2p_barrier(const unsigned long long* flag_ptrs, int rank, int world, 
                       unsigned long long timeout_ns, int* status, void* stream);
 int adana_p2p_reduce_scatter(const unsigned long long* grad_ptrs, int world, long long shard_off, long long n,
                              float* out, float* sumsq, void* stream);
+// Per-unit "ready" flags and the collectives that wait for them (see comm_p2p.cu).
+int adana_p2p_signal(const unsigned long long* flag_ptrs, int rank, int world, int slot, unsigned int seq,
+                     void* stream);
+int adana_p2p_reduce_scatter_flag(const unsigned long long* src_ptrs, int wire_bf16, const void* my_flags,
+                                  unsigned int seq, int world, long long shard_off, long long n, float* out,
+                                  float* sumsq, unsigned long long timeout_ns, int* status, void* stream);
+int adana_p2p_all_reduce_flag(const unsigned long long* src_ptrs, int wire_bf16, const unsigned long long* dst_ptrs,
+                              const void* my_flags, unsigned int seq, int world, long long slice_off, long long n,
+                              float* sumsq, unsigned long long timeout_ns, int* status, void* stream);
 int adana_p2p_publish_f32(const unsigned long long* slot_ptrs, int rank, int world, const float* value, void* stream);
 int adana_p2p_push_f32(const float* src, const unsigned long long* dst_ptrs, int world, long long dst_off, long long n,
                        void* stream);

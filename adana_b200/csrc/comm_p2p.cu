@@ -6,6 +6,17 @@
 //   p2p_reduce_scatter     one-shot pull: my shard of the gradient unit = sum over ranks of their copy
 //                          (fp32, 16-byte loads straight from peer memory), fused with the squared-norm
 //                          partial that the gradient clip needs
+//   p2p_signal             "my copy of unit u is ready": one sequence number stored into a per-unit flag slot of
+//                          every peer.  The flagged reduce-scatter / all-reduce below wait (bounded) for the
+//                          flags of the ranks they read, so no rank ever waits at a barrier for a rank whose data
+//                          it does not need yet, and a fast rank is never held up in the middle of its backward
+//   p2p_reduce_scatter_*   the same pull with a bf16 wire format (each rank first rounds its fp32 gradient unit
+//                          to a bf16 staging copy, as the reference's FSDP reduces in bf16; sums stay fp32) and
+//                          with the flag wait in front; grids are capped at the few CTAs NVLink needs, because
+//                          these kernels run beside the backward GEMMs
+//   p2p_all_reduce_*       data-parallel (replicated) engines: rank k sums slice k of every rank's unit and stores
+//                          the sum into slice k of every rank's fp32 gradient buffer (reduce-scatter and all-gather
+//                          in one kernel; slices are disjoint, so it runs in place)
 //   p2p_publish_f32        each rank stores one float (its squared-norm partial) into slot [rank] of
 //                          every peer: a scalar all-gather; after a barrier everybody sums locally
 //   p2p_opt_step_push      the fused optimizer step whose bf16 output is stored directly into every
@@ -19,6 +30,8 @@
 //
 // Replaces the NCCL reduce-scatter / all-gather issued by FSDP2 in the reference
 // (src/distributed/fsdp.py:105-116) and the per-tensor optimizer launches (src/optim/adana.py:160-227).
+#include <cstdlib>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -87,6 +100,134 @@ p2p_reduce_scatter_kernel(PeerPtrs grads, int world, long long shard_off, long l
       atomicAdd(sumsq, t);
     }
   }
+}
+
+// flags.p[t] + slot + rank <- seq on every rank t (release: everything this rank wrote before is visible first)
+__global__ void p2p_signal_kernel(PeerPtrs flags, int rank, int world, int slot, uint32_t seq) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  st_release_sys_u32(reinterpret_cast<uint32_t*>(flags.p[t]) + slot + rank, seq);
+}
+
+// Bounded wait of a CTA for the flags of ranks [0, world): my_flags[r] >= seq.  Returns false when a wait ran out
+// (status word set): the caller then leaves its output untouched.
+__device__ __forceinline__ bool wait_unit_flags(const uint32_t* my_flags, uint32_t seq, int world,
+                                                unsigned long long timeout_ns, int* status) {
+  __shared__ int s_ok;
+  if (my_flags == nullptr) return true;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys_u32(my_flags + threadIdx.x) - seq) < 0) {
+      if (((++spins) & 0x3f) == 0 && globaltimer_ns() - t0 > timeout_ns) {
+        if (status) atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+        s_ok = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4& u) {
+  const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+}
+
+// Sum over ranks of 8 consecutive elements starting at element `e` of every rank's buffer (fp32 or bf16 wire),
+// ranks in fixed order: every rank computes bitwise the same sums.
+template <bool BF16>
+__device__ __forceinline__ void pull8(const PeerPtrs& src, int world, long long e, float (&acc)[8]) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  if (BF16) {
+    uint4 u[MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) u[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + e);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r)
+      if (r < world) add8(acc, u[r]);
+  } else {
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[r]) + e);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src.p[r]) + e + 4);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void block_add_to(float* dst, float v) {
+  __shared__ float red[8];
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    atomicAdd(dst, t);
+  }
+}
+
+// out[i] = sum_r src_r[shard_off + i] (fp32), sumsq += sum out[i]^2, after every rank's flag for the unit arrived.
+// n and shard_off are multiples of 8.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+p2p_reduce_scatter_flag_kernel(PeerPtrs src, const uint32_t* my_flags, uint32_t seq, int world, long long shard_off,
+                               long long n, float* __restrict__ out, float* __restrict__ sumsq,
+                               unsigned long long timeout_ns, int* status) {
+  if (!wait_unit_flags(my_flags, seq, world, timeout_ns, status)) return;
+  float ss = 0.f;
+  const long long n8 = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    float acc[8];
+    pull8<BF16>(src, world, shard_off + i * 8, acc);
+    *reinterpret_cast<float4*>(out + i * 8) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(out + i * 8 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += acc[k] * acc[k];
+  }
+  if (sumsq) block_add_to(sumsq, ss);
+}
+
+// dst_r[slice_off + i] = sum_q src_q[slice_off + i] on EVERY rank r (fp32 destinations): all-reduce of one slice.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+p2p_all_reduce_flag_kernel(PeerPtrs src, PeerPtrs dst, const uint32_t* my_flags, uint32_t seq, int world,
+                           long long slice_off, long long n, float* __restrict__ sumsq, unsigned long long timeout_ns,
+                           int* status) {
+  if (!wait_unit_flags(my_flags, seq, world, timeout_ns, status)) return;
+  float ss = 0.f;
+  const long long n8 = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    float acc[8];
+    const long long e = slice_off + i * 8;
+    pull8<BF16>(src, world, e, acc);
+    const float4 lo = make_float4(acc[0], acc[1], acc[2], acc[3]), hi = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < world) {
+        float* d = reinterpret_cast<float*>(dst.p[r]) + e;
+        *reinterpret_cast<float4*>(d) = lo;
+        *reinterpret_cast<float4*>(d + 4) = hi;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += acc[k] * acc[k];
+  }
+  // squared norm of this rank's slice of the reduced gradient: the ranks publish these partials and add them in rank
+  // order, so every rank derives bitwise the same clip coefficient
+  if (sumsq) block_add_to(sumsq, ss);
 }
 
 __global__ void p2p_publish_f32_kernel(PeerPtrs slots, int rank, int world, const float* __restrict__ value) {
@@ -354,6 +495,70 @@ extern "C" int adana_p2p_reduce_scatter(const unsigned long long* grad_ptrs, int
   if (n == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   p2p_reduce_scatter_kernel<<<grid_for(n / 4), 256, 0, st>>>(make_ptrs(grad_ptrs, world), world, shard_off, n, out, sumsq);
+  return (int)cudaGetLastError();
+}
+
+// Largest grid of the gradient collectives that run beside the backward GEMMs.  NVLink, not the SMs, bounds them:
+// a few dozen CTAs with several 16-byte loads in flight per thread fill the links.
+static int comm_cta_cap() {
+  static int cap = -1;
+  if (cap < 0) {
+    const char* e = getenv("ADANA_COMM_CTAS");
+    cap = e ? atoi(e) : 64;
+    if (cap < 1) cap = 1;
+    if (cap > 148 * 8) cap = 148 * 8;
+  }
+  return cap;
+}
+static int capped_grid(long long work_items) {
+  long long b = (work_items + 255) / 256;
+  const long long cap = comm_cta_cap();
+  return (int)(b < 1 ? 1 : (b < cap ? b : cap));
+}
+
+extern "C" int adana_p2p_signal(const unsigned long long* flag_ptrs, int rank, int world, int slot,
+                                unsigned int seq, void* stream_) {
+  if (world < 1 || world > MAX_RANKS || slot < 0) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  p2p_signal_kernel<<<1, 32, 0, st>>>(make_ptrs(flag_ptrs, world), rank, world, slot, seq);
+  return (int)cudaGetLastError();
+}
+
+// src_ptrs: every rank's copy of the unit (fp32, or bf16 when wire_bf16); my_flags: this rank's flag slots of the
+// unit (one per rank; nullptr = do not wait); out fp32 [n]; n and shard_off multiples of 8.
+extern "C" int adana_p2p_reduce_scatter_flag(const unsigned long long* src_ptrs, int wire_bf16, const void* my_flags,
+                                             unsigned int seq, int world, long long shard_off, long long n,
+                                             float* out, float* sumsq, unsigned long long timeout_ns, int* status,
+                                             void* stream_) {
+  if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_off & 7)) return -1;
+  if (n == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = capped_grid(n / 8);
+  const PeerPtrs src = make_ptrs(src_ptrs, world);
+  const uint32_t* fl = reinterpret_cast<const uint32_t*>(my_flags);
+  if (wire_bf16)
+    p2p_reduce_scatter_flag_kernel<true><<<grid, 256, 0, st>>>(src, fl, seq, world, shard_off, n, out, sumsq, timeout_ns, status);
+  else
+    p2p_reduce_scatter_flag_kernel<false><<<grid, 256, 0, st>>>(src, fl, seq, world, shard_off, n, out, sumsq, timeout_ns, status);
+  return (int)cudaGetLastError();
+}
+
+// dst_ptrs: every rank's fp32 gradient buffer of the unit; this rank reduces [slice_off, slice_off + n) and stores it
+// on every rank.  May run in place (src == dst, fp32 wire): slices of different ranks are disjoint.
+extern "C" int adana_p2p_all_reduce_flag(const unsigned long long* src_ptrs, int wire_bf16,
+                                         const unsigned long long* dst_ptrs, const void* my_flags, unsigned int seq,
+                                         int world, long long slice_off, long long n, float* sumsq,
+                                         unsigned long long timeout_ns, int* status, void* stream_) {
+  if (world < 1 || world > MAX_RANKS || (n & 7) || (slice_off & 7)) return -1;
+  if (n == 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = capped_grid(n / 8);
+  const PeerPtrs src = make_ptrs(src_ptrs, world), dst = make_ptrs(dst_ptrs, world);
+  const uint32_t* fl = reinterpret_cast<const uint32_t*>(my_flags);
+  if (wire_bf16)
+    p2p_all_reduce_flag_kernel<true><<<grid, 256, 0, st>>>(src, dst, fl, seq, world, slice_off, n, sumsq, timeout_ns, status);
+  else
+    p2p_all_reduce_flag_kernel<false><<<grid, 256, 0, st>>>(src, dst, fl, seq, world, slice_off, n, sumsq, timeout_ns, status);
   return (int)cudaGetLastError();
 }
 

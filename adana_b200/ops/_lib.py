@@ -62,6 +62,9 @@ def _declare(lib):
         "adana_p2p_barrier": [P, I, I, I, ctypes.c_uint, ctypes.c_ulonglong, P, P],
         "adana_p2p_reduce_scatter": [P, I, L, L, P, P, P],
         "adana_p2p_publish_f32": [P, I, I, P, P],
+        "adana_p2p_signal": [P, I, I, I, ctypes.c_uint, P],
+        "adana_p2p_reduce_scatter_flag": [P, I, P, ctypes.c_uint, I, L, L, P, P, ctypes.c_ulonglong, P, P],
+        "adana_p2p_all_reduce_flag": [P, I, P, P, ctypes.c_uint, I, L, L, P, ctypes.c_ulonglong, P, P],
         "adana_p2p_push_f32": [P, P, I, L, L, P],
         "adana_clip_coef_multi": [P, I, F, F, P, P],
         "adana_p2p_opt_step_push": [P, P, P, P, P, P, I, L, L, POINTER(AdanaOptHyper), P, P],

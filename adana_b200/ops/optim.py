@@ -16,6 +16,16 @@ from ..optim.logtime import logtime_update_
 KIND_ADANA, KIND_DANA_STAR, KIND_ADAMW, KIND_ADAMW_IWD = 0, 1, 2, 3
 
 
+def cast_f32_to_bf16(src: torch.Tensor, dst: torch.Tensor):
+    """dst (bf16) = round(src (fp32)), one pass (the wire copy of a gradient unit)."""
+    if src.is_cuda and _lib.available() and src.is_contiguous() and dst.is_contiguous():
+        rc = _lib.lib().adana_cast_f32_to_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_cast_f32_to_bf16")
+    else:
+        dst.copy_(src)
+    return dst
+
+
 def sumsq_accumulate(x: torch.Tensor, out: torch.Tensor):
     """out[0] += sum(x^2) (fp32)."""
     if x.is_cuda and _lib.available() and x.dtype == torch.float32 and x.is_contiguous():

@@ -8,6 +8,8 @@ and the kernels read / write peers directly over NVLink:
 
     barrier()                       flag barrier with a bounded wait (status word on time-out)
     reduce_scatter_sumsq(...)       pull-reduce my shard from all ranks + squared-norm partial
+    signal_unit / reduce_scatter_unit / all_reduce_unit
+                                    per-unit "ready" flags instead of a barrier, bf16 or fp32 wire format
     global_clip_coef(...)           publish partials to all peers, barrier, sum locally
     opt_step_push(...)              fused optimizer step storing bf16 results into every rank's weights
     push_f32(...)                   exact fp32 copy of my slice of the norm weights to every rank
@@ -25,7 +27,8 @@ import torch.distributed as dist
 
 from ..ops import _lib
 
-FLAG_BYTES = 4096       # uint32 flag slots at the start of the arena
+FLAG_BYTES = 32768      # uint32 flag slots at the start of the arena: [0, 64) barriers, then 8 per gradient unit
+UNIT_FLAG_BASE = 64
 SLOT_BYTES = 4096       # float slots for published scalars
 ALIGN = 256
 
@@ -101,6 +104,43 @@ class P2PPlane:
         rc = _lib.lib().adana_p2p_reduce_scatter(self.peer_ptrs(full), self.world, shard_off, shard_out.numel(),
                                                  shard_out.data_ptr(), _lib.ptr(sumsq), _lib.stream_ptr())
         _lib.check_rc(rc, "adana_p2p_reduce_scatter")
+
+    # ---- flag-ordered gradient collectives -----------------------------------------------------------------
+    def unit_flag_slot(self, unit_index: int) -> int:
+        slot = UNIT_FLAG_BASE + 8 * unit_index
+        if (slot + 8) * 4 > FLAG_BYTES:
+            raise ValueError(f"no flag slots left for gradient unit {unit_index}")
+        return slot
+
+    def signal_unit(self, unit_index: int, seq: int):
+        """Tell every rank that this rank's copy of the unit is complete (everything enqueued on the current
+        stream before this call)."""
+        rc = _lib.lib().adana_p2p_signal(self._flag_ptrs, self.rank, self.world, self.unit_flag_slot(unit_index),
+                                         seq & 0xFFFFFFFF, _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_signal")
+
+    def _my_unit_flags(self, unit_index: int, wait: bool) -> int:
+        return self.base + 4 * self.unit_flag_slot(unit_index) if wait else 0
+
+    def reduce_scatter_unit(self, src_full: torch.Tensor, shard_off: int, shard_out: torch.Tensor,
+                            sumsq: Optional[torch.Tensor], unit_index: int, seq: int, wait: bool = True):
+        """shard_out (fp32) = sum over ranks of their `src_full` (fp32 or bf16, at the same arena offset) over my shard,
+        once every rank has signalled the unit with sequence number `seq`; squared norm of the result added to `sumsq`."""
+        rc = _lib.lib().adana_p2p_reduce_scatter_flag(
+            self.peer_ptrs(src_full), int(src_full.dtype == torch.bfloat16), self._my_unit_flags(unit_index, wait),
+            seq & 0xFFFFFFFF, self.world, shard_off, shard_out.numel(), shard_out.data_ptr(), _lib.ptr(sumsq),
+            self.timeout_ns, _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_reduce_scatter_flag")
+
+    def all_reduce_unit(self, src_full: torch.Tensor, dst_full: torch.Tensor, slice_off: int, n: int, unit_index: int,
+                        seq: int, wait: bool = True, sumsq: Optional[torch.Tensor] = None):
+        """Slice [slice_off, slice_off + n) of every rank's `dst_full` (fp32) = sum over ranks of `src_full`; the
+        squared norm of that slice of the result is added to `sumsq`."""
+        rc = _lib.lib().adana_p2p_all_reduce_flag(
+            self.peer_ptrs(src_full), int(src_full.dtype == torch.bfloat16), self.peer_ptrs(dst_full),
+            self._my_unit_flags(unit_index, wait), seq & 0xFFFFFFFF, self.world, slice_off, n, _lib.ptr(sumsq), self.timeout_ns,
+            _lib.status_buffer(self.device).data_ptr(), _lib.stream_ptr())
+        _lib.check_rc(rc, "adana_p2p_all_reduce_flag")
 
     def global_clip_coef(self, local_sumsq: torch.Tensor, norm_scale: float, max_norm: float, out: torch.Tensor):
         """All ranks' squared-norm partials -> clip coefficient on the device (out[0]) and the norm (out[1])."""

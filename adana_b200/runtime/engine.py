@@ -64,7 +64,7 @@ class _Bridge(torch.autograd.Function):
 
 class Unit:
     def __init__(self, layout: UnitLayout, world: int, rank: int, sharded: bool, device, cdt, plane=None,
-                 resident_weights: bool = True):
+                 resident_weights: bool = True, reduce_bf16: bool = False):
         self.layout = layout
         self.slices = {}     # gathered mode: key -> (slice buffer, row_starts, flat offset, rows, cols)
         self.segments = []   # gathered mode: (flat_lo, flat_hi, owner rank, address of the owner's slice buffer)
@@ -75,6 +75,8 @@ class Unit:
         f32 = dict(dtype=torch.float32, device=device)
         self.master = torch.zeros(self.shard_len, **f32)
         self.grads = plane.alloc(self.padded, torch.float32) if plane is not None else torch.zeros(self.padded, **f32)
+        # wire copy of the gradients for a bf16 reduce (peers read it; sums stay fp32)
+        self.grads16 = plane.alloc(self.padded, torch.bfloat16) if (plane is not None and reduce_bf16) else None
         self.grad_shard = torch.zeros(self.shard_len, **f32) if (sharded and world > 1) else self.grads
         self.low_precision = cdt != torch.float32
         if self.low_precision and not resident_weights:
@@ -147,7 +149,10 @@ class Engine:
             acc_steps=getattr(cfg, "acc_steps", 1), grad_clip=getattr(cfg, "grad_clip", 0.0),
             z_loss_coeff=getattr(cfg, "z_loss_coeff", 0.0), hoyer_loss_coeff=getattr(cfg, "hoyer_loss_coeff", 0.0),
             activation_checkpointing=getattr(cfg, "activation_checkpointing", False),
-            checkpoint_every_n=getattr(cfg, "checkpoint_every_n", 1))
+            checkpoint_every_n=getattr(cfg, "checkpoint_every_n", 1),
+            # the dtype gradients cross the links in (sums are always fp32); bf16 is what the reference's FSDP uses
+            # (src/distributed/fsdp.py:39-43).  fp32 compute keeps fp32 on the wire.
+            reduce_dtype="float32" if self.cdt == torch.float32 else getattr(cfg, "reduce_dtype", "bfloat16"))
         self.loss_scale = 1.0 / max(1, self.ecfg.acc_steps)
         self.enabled = True
         if getattr(cfg, "attention", "auto") != "auto":
@@ -156,7 +161,13 @@ class Engine:
             _att.set_mode(cfg.attention)
 
         self.layouts = build_layouts(model, self.world if self.sharded else 1)
-        self.plane = self._make_plane()
+        plane = self._make_plane()
+        # the sharded engine runs every collective on the plane; a replicated (data-parallel) engine only the
+        # gradient all-reduce
+        self.plane = plane if self.sharded else None
+        self.ar_plane = plane if not self.sharded else None
+        self.reduce_bf16 = plane is not None and self.ecfg.reduce_dtype == "bfloat16"
+        self.reduce_seq = 0
         # `--fsdp_weights gathered`: the block matrices are never all-gathered.  With the peer-memory plane every
         # rank keeps only its row slice of each matrix and the GEMMs fetch B tiles from the owners; without it
         # (one GPU) the slices are views of the resident matrix, which exercises the same GEMM path.
@@ -164,9 +175,10 @@ class Engine:
                          and self.cdt == torch.bfloat16 and getattr(model, "arch", "") == "enoki"
                          and not getattr(cfg, "moe", False))
         split = self.gathered and self.plane is not None
-        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, self.plane,
-                                       resident_weights=not (split and l.name != "root"))
+        self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, plane,
+                                       resident_weights=not (split and l.name != "root"), reduce_bf16=self.reduce_bf16)
                                   for l in self.layouts]
+        self._unit_index = {u.layout.name: i for i, u in enumerate(self.units)}
         self.spec = self._block_spec()
         if split:
             self._make_slices()
@@ -195,11 +207,12 @@ class Engine:
         """Peer-memory data plane for the sharded engine on GPUs (`--fsdp_comm auto|p2p`); None selects
         torch.distributed collectives (NCCL / Gloo)."""
         want = getattr(self.cfg, "fsdp_comm", "auto")
-        if not self.sharded or self.device.type != "cuda" or self.cdt == torch.float32 or want == "nccl":
+        if self.world < 2 or self.device.type != "cuda" or self.cdt == torch.float32 or want == "nccl":
             return None
-        if self.world > 8 or not _lib.has("adana_p2p_barrier"):
+        if self.world > 8 or not _lib.has("adana_p2p_reduce_scatter_flag"):
             return None
-        nbytes = sum(l.padded * 6 + l.numel * 4 + 4096 for l in self.layouts)
+        # per unit: fp32 gradients (4) + bf16 weights (2) + bf16 wire copy of the gradients (2) + fp32 norm weights
+        nbytes = sum(l.padded * 8 + l.numel * 4 + 4096 for l in self.layouts)
         plane, err = None, None
         try:
             from ..parallel.p2p import P2PPlane
@@ -217,6 +230,8 @@ class Engine:
         if self.rank == 0:
             print(f"[engine] peer-memory plane unavailable on {self.world - int(ok.item())} rank(s) ({err}); "
                   f"using NCCL collectives")
+        if plane is not None:
+            del plane
         return None
 
     # ---- gathered weights ----------------------------------------------------------------------------------
@@ -480,6 +495,8 @@ class Engine:
         if sync is None:
             sync = (self.micro_step + 1) >= self.ecfg.acc_steps
         root = self.units[-1]
+        if self.micro_step == 0 and (self.plane or self.ar_plane) is not None:
+            self._sumsq.zero_()      # the reductions of this optimizer step accumulate their squared-norm partials here
         with torch.no_grad():
             for i in range(len(self.units) - 2, -1, -1):
                 u = self.units[i]
@@ -506,16 +523,31 @@ class Engine:
     # gradient reduction, clipping, optimizer
     # ---------------------------------------------------------------------------------------------
     def _reduce_unit(self, u: Unit):
+        """Start the reduction of a unit's gradients (its backward has been enqueued on the current stream)."""
         if self.world == 1:
             return
-        if self.plane is not None:
-            # peers may read this unit's gradients once every rank has finished its backward of the unit
+        plane = self.plane or self.ar_plane
+        if plane is not None:
+            # This rank's copy is complete once the kernels enqueued so far have run: round it to the wire dtype,
+            # then raise the unit's flag on every rank.  The pulling kernel (side stream) waits, bounded, for the flags
+            # of all ranks: no barrier, so a fast rank is never stopped in the middle of its backward by a slow one.
+            idx = self._unit_index[u.layout.name]
+            seq = self.reduce_seq + 1
+            src = u.grads
+            if u.grads16 is not None:
+                O.cast_f32_to_bf16(u.grads, u.grads16)
+                src = u.grads16
+            plane.signal_unit(idx, seq)
             ev = torch.cuda.Event()
             ev.record()
-            with torch.cuda.stream(self.plane.stream):
-                self.plane.stream.wait_event(ev)
-                self.plane.barrier()
-                self.plane.reduce_scatter_sumsq(u.grads, u.shard_off, u.grad_shard, self._sumsq)
+            with torch.cuda.stream(plane.stream):
+                plane.stream.wait_event(ev)
+                if self.sharded:
+                    plane.reduce_scatter_unit(src, u.shard_off, u.grad_shard, self._sumsq, idx, seq)
+                else:
+                    n = -(-u.padded // (8 * self.world)) * 8          # this rank's slice, a multiple of 8 elements
+                    off = min(self.rank * n, u.padded)
+                    plane.all_reduce_unit(src, u.grads, off, min(n, u.padded - off), idx, seq, sumsq=self._sumsq)
             u.grad_work = None
             self._plane_pending = True
             return
@@ -559,8 +591,14 @@ class Engine:
     def finish_grad_sync(self):
         e0 = self._meter_begin() if (self._plane_pending or any(u.grad_work is not None for u in self.units)) else None
         if self._plane_pending:
-            torch.cuda.current_stream().wait_stream(self.plane.stream)
+            plane = self.plane or self.ar_plane
+            if self.ar_plane is not None:
+                # all-reduce: peers store their slices into this rank's buffers; all of them have landed after a barrier
+                with torch.cuda.stream(plane.stream):
+                    plane.barrier()
+            torch.cuda.current_stream().wait_stream(plane.stream)
             self._plane_pending = False
+            self.reduce_seq += 1
         for u in self.units:
             if u.grad_work is not None:
                 wait(u.grad_work)
@@ -571,10 +609,11 @@ class Engine:
         """Global L2 norm of the (rank-averaged) gradient; leaves the clip coefficient on the device.
         Returns a 0-d tensor holding the norm."""
         self.finish_grad_sync()
-        if self.plane is not None:
-            # the reduce-scatter kernels already accumulated this rank's squared-norm partial
+        plane = self.plane or self.ar_plane
+        if plane is not None:
+            # the reduce-scatter / all-reduce kernels already accumulated this rank's squared-norm partial
             e0 = self._meter_begin()
-            self.plane.global_clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
+            plane.global_clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
             self._meter_end(e0)
             self.last_grad_norm = self._clip[1]
             return self._clip[1]
@@ -655,7 +694,7 @@ class Engine:
         e0 = self._meter_begin()
         self._sync_small()     # (peer-memory plane: ends with the barrier that completes the weight pushes)
         self._meter_end(e0)
-        if self.plane is not None:
+        if (self.plane or self.ar_plane) is not None:
             self._sumsq.zero_()
         opt.step_count = t
         self.opt_step_count += 1

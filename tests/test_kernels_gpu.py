@@ -389,6 +389,51 @@ def test_p2p_push_f32_and_barrier_timeout():
         _lib.check_status()
 
 
+@pytest.mark.parametrize("wire", [torch.bfloat16, torch.float32], ids=["bf16_wire", "fp32_wire"])
+def test_p2p_flagged_reduce_scatter_and_all_reduce_fake_peers(wire):
+    """Per-unit ready flags instead of a barrier, bf16 or fp32 on the wire, fp32 sums.  All "ranks" are arenas on this
+    GPU: every rank signals first (plain launches in stream order), so the waits inside the pulling kernels find their
+    flags set; then a wait for a flag that nothing sets must give up within its limit, leave the output alone and report
+    through the status word."""
+    from adana_b200.parallel.p2p import P2PPlane
+
+    torch.manual_seed(13)
+    world, n = 4, 64 * 4 * 131
+    shard = n // world
+    planes = P2PPlane.fake(n * 8 + 8192, world, DEV)
+    grads = [pl.alloc(n, torch.float32) for pl in planes]
+    wires = [pl.alloc(n, torch.bfloat16) for pl in planes] if wire == torch.bfloat16 else grads
+    for g, w in zip(grads, wires):
+        g.copy_(torch.randn(n, device=DEV))
+        if w is not g:
+            optim.cast_f32_to_bf16(g, w)
+    total = torch.stack([w.float() for w in wires]).sum(0)      # what the wire carries, summed in fp32
+    unit, seq = 5, 7
+    for pl in planes:
+        pl.signal_unit(unit, seq)
+    for r, pl in enumerate(planes):
+        out = torch.zeros(shard, device=DEV)
+        ss = torch.zeros(1, device=DEV)
+        pl.reduce_scatter_unit(wires[r], r * shard, out, ss, unit, seq)
+        assert rel_err(out, total[r * shard:(r + 1) * shard]) < 1e-6
+        assert abs(ss.item() - out.double().pow(2).sum().item()) / ss.item() < 1e-4
+    # all-reduce: rank r sums slice r and stores it into every rank's fp32 buffer (in place for an fp32 wire)
+    for r, pl in enumerate(planes):
+        pl.all_reduce_unit(wires[r], grads[r], r * shard, shard, unit, seq)
+    for g in grads:
+        assert rel_err(g, total) < 1e-6
+    torch.cuda.synchronize()
+    _lib.check_status()
+    # a sequence number nobody has signalled: bounded wait, status word, output untouched
+    planes[0].timeout_ns = int(0.2e9)
+    out = torch.full((shard,), 3.0, device=DEV)
+    planes[0].reduce_scatter_unit(wires[0], 0, out, None, unit, seq + 1)
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.full_like(out, 3.0))
+    with pytest.raises(RuntimeError, match="peer flag"):
+        _lib.check_status()
+
+
 def test_newton_schulz_tcgen05_chain_matches_pytorch():
     from adana_b200.ops import muon_ns
     from adana_b200.optim.muon import newton_schulz5

@@ -12,7 +12,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, plane, weights="resident"):
+def _worker(rank, world, plane, weights="resident", sharded=True, reduce_dtype="bfloat16"):
     import torch.distributed as dist
 
     from conftest import tiny_args
@@ -26,12 +26,14 @@ def _worker(rank, world, plane, weights="resident"):
     dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     a = tiny_args("enoki", n_embd=256, n_head=4, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024,
                   opt="dana-star-mk4", kappa=0.85, clipsnr=2.0, lr=2e-3, weight_decay=0.1, wd_decaying=True, wd_ts=3.0,
-                  acc_steps=2, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane, fsdp_weights=weights)
+                  acc_steps=2, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane, fsdp_weights=weights,
+                  reduce_dtype=reduce_dtype)
     torch.manual_seed(0)
     m = get_model(a).to(a.device)
-    eng = attach(m, a, comm=Comm(), sharded=True, device=a.device)
-    assert (eng.plane is not None) == (plane == "p2p")
+    eng = attach(m, a, comm=Comm(), sharded=sharded, device=a.device)
+    assert ((eng.plane if sharded else eng.ar_plane) is not None) == (plane == "p2p")
     assert (eng.units[0].weights is None) == (weights == "gathered")
+    assert eng.reduce_bf16 == (plane == "p2p" and reduce_dtype == "bfloat16")
     specs = m.get_parameter_group_specs()
     for g in specs:
         g["param_names"] = g["params"]
@@ -69,6 +71,25 @@ def test_p2p_plane_matches_nccl_plane():
         d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs()
         assert d.mean().item() < 2e-4, (k, d.mean().item())
         assert torch.equal(_t(res["p2p"][0]["params"][k]), _t(res["p2p"][1]["params"][k]))
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("sharded,reduce_dtype", [(True, "float32"), (False, "bfloat16"), (False, "float32")],
+                         ids=["fsdp_fp32_wire", "ddp_all_reduce_bf16_wire", "ddp_all_reduce_fp32_wire"])
+def test_flagged_gradient_collectives_match_nccl(sharded, reduce_dtype):
+    """The flag-ordered reduce-scatter with an fp32 wire, and the replicated (data-parallel) engine whose gradient
+    all-reduce runs on the peer-memory plane, against the same engine on NCCL."""
+    from test_distributed_cpu import _spawn, _t
+
+    world = min(4, torch.cuda.device_count())
+    res = {plane: _spawn(_worker, world, plane, "resident", sharded, reduce_dtype) for plane in ("nccl", "p2p")}
+    for a, b in zip(res["nccl"][0]["norms"], res["p2p"][0]["norms"]):
+        assert abs(a - b) / a < 2e-2
+    for k, v in res["nccl"][0]["params"].items():
+        d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs()
+        assert d.mean().item() < 2e-4, (k, d.mean().item())
+        for r in range(1, world):
+            assert torch.equal(_t(res["p2p"][0]["params"][k]), _t(res["p2p"][r]["params"][k]))
 
 
 def _gather_gemm_worker(rank, world):
