@@ -145,8 +145,12 @@ struct AdanaOptHyper {
   float wd_factor;     // 1 - wd * sched / (1 + t / wd_ts)   (already folded on the host)
   float grad_scale;    // multiplies the raw gradient (1/acc_steps, 1/world); the clip
                        // coefficient is read from clip_coef_ptr on the device
-  int kind;            // 0 adana/dana-mk4, 1 dana-star(-mk4), 2 adamw, 3 adamw + independent decay
-  float beta1, beta2, bc1, bc2;  // adamw only
+  int kind;            // 0 adana/dana-mk4, 1 dana-star(-mk4), 2 adamw, 3 adamw + independent decay,
+                       // 4 ademamix (coupled decay), 5 ademamix + independent decay
+  float beta1, beta2, bc1, bc2;  // adamw and ademamix
+  float beta3;         // ademamix: decay of the slow EMA at this step (after its warm-up); `alpha` is the mixing
+                       // coefficient at this step; the slow EMA lives in the `tau` buffer
+  float wd_coupled;    // ademamix kind 4: weight decay added to the update (p -= lr * (update + wd * p))
 };
 int adana_opt_step(float* p, const float* g, float* m, float* v, float* tau, void* p_bf16,
                    long long n, const struct AdanaOptHyper* h, const float* clip_coef_ptr,

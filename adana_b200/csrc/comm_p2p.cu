@@ -284,7 +284,7 @@ p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, flo
       gv[q * 4] = b.x; gv[q * 4 + 1] = b.y; gv[q * 4 + 2] = b.z; gv[q * 4 + 3] = b.w;
       mv[q * 4] = c.x; mv[q * 4 + 1] = c.y; mv[q * 4 + 2] = c.z; mv[q * 4 + 3] = c.w;
       vv[q * 4] = d.x; vv[q * 4 + 1] = d.y; vv[q * 4 + 2] = d.z; vv[q * 4 + 3] = d.w;
-      if (KIND == 1) {
+      if (KIND == 1 || KIND == 4 || KIND == 5) {
         const float4 e = *reinterpret_cast<const float4*>(tau + base + q * 4);
         tv[q * 4] = e.x; tv[q * 4 + 1] = e.y; tv[q * 4 + 2] = e.z; tv[q * 4 + 3] = e.w;
       }
@@ -319,6 +319,16 @@ p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, flo
         }
         pi += (-h.lr) * gi * norm + (-h.lr) * h.gamma3 * longterm;
         pi *= h.wd_factor;
+      } else if (KIND == 4 || KIND == 5) {   // AdEMAMix: the slow EMA lives in the tau buffer (see optim.cu)
+        float si = tv[k];
+        mi = h.beta1 * mi + (1.f - h.beta1) * gi;
+        si = h.beta3 * si + (1.f - h.beta3) * gi;
+        vi = h.beta2 * vi + (1.f - h.beta2) * gi * gi;
+        tv[k] = si;
+        float upd = (mi / h.bc1 + h.alpha * h.gamma3 * si) / (sqrtf(vi) / sqrtf(h.bc2) + h.eps);
+        if (KIND == 5) pi *= h.wd_factor;
+        else upd += h.wd_coupled * pi;
+        pi -= h.lr * upd;
       } else {
         if (KIND == 2) pi *= h.wd_factor;
         mi = h.beta1 * mi + (1.f - h.beta1) * gi;
@@ -333,7 +343,7 @@ p2p_opt_step_push_kernel(float* __restrict__ p, const float* __restrict__ g, flo
       *reinterpret_cast<float4*>(p + base + q * 4) = make_float4(pv[q * 4], pv[q * 4 + 1], pv[q * 4 + 2], pv[q * 4 + 3]);
       *reinterpret_cast<float4*>(m + base + q * 4) = make_float4(mv[q * 4], mv[q * 4 + 1], mv[q * 4 + 2], mv[q * 4 + 3]);
       *reinterpret_cast<float4*>(v + base + q * 4) = make_float4(vv[q * 4], vv[q * 4 + 1], vv[q * 4 + 2], vv[q * 4 + 3]);
-      if (KIND == 1)
+      if (KIND == 1 || KIND == 4 || KIND == 5)
         *reinterpret_cast<float4*>(tau + base + q * 4) = make_float4(tv[q * 4], tv[q * 4 + 1], tv[q * 4 + 2], tv[q * 4 + 3]);
     }
     uint4 packed;
@@ -592,7 +602,7 @@ extern "C" int adana_p2p_opt_step_push(float* p, const float* g, float* m, float
                                        void* stream_) {
   if (world < 1 || world > MAX_RANKS || (n & 7) || (push_off & 7)) return -1;
   if (n == 0) return 0;
-  if (h->kind == 1 && !tau) return -2;
+  if ((h->kind == 1 || h->kind == 4 || h->kind == 5) && !tau) return -2;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   const int grid = grid_for(n / 8);
   const PeerPtrs w = make_ptrs(weight_ptrs, world);
@@ -601,6 +611,8 @@ extern "C" int adana_p2p_opt_step_push(float* p, const float* g, float* m, float
     case 1: p2p_opt_step_push_kernel<1><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
     case 2: p2p_opt_step_push_kernel<2><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
     case 3: p2p_opt_step_push_kernel<3><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    case 4: p2p_opt_step_push_kernel<4><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
+    case 5: p2p_opt_step_push_kernel<5><<<grid, 256, 0, st>>>(p, g, m, v, tau, w, world, push_off, n, *h, clip_coef_ptr); break;
     default: return -3;
   }
   return (int)cudaGetLastError();

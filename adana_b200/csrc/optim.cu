@@ -64,6 +64,20 @@ opt_step_kernel(float* __restrict__ p, const float* __restrict__ g, float* __res
         d_af += af;
         d_mfac += mfac;
       }
+    } else if (KIND == 4 || KIND == 5) {
+      // AdEMAMix (src/optim/ademamix.py:31-195): fast EMA m, slow EMA in the tau buffer, Adam second moment;
+      // update = (m / bc1 + gamma3 * alpha_t * slow) / (sqrt(v / bc2) + eps).  KIND 4 adds wd * p to the update,
+      // KIND 5 multiplies p by the independent (optionally decaying) factor before the step.
+      float si = tau[i];
+      mi = h.beta1 * mi + (1.f - h.beta1) * gi;
+      si = h.beta3 * si + (1.f - h.beta3) * gi;
+      vi = h.beta2 * vi + (1.f - h.beta2) * gi * gi;
+      tau[i] = si;
+      const float denom = sqrtf(vi) / sqrtf(h.bc2) + h.eps;
+      float upd = (mi / h.bc1 + h.alpha * h.gamma3 * si) / denom;
+      if (KIND == 5) pi *= h.wd_factor;
+      else upd += h.wd_coupled * pi;
+      pi -= h.lr * upd;
     } else {
       // KIND 2: AdamW (decay before the step, coupled to lr); KIND 3: Adam step, then the
       // independent (optionally decaying) decay factor.
@@ -145,7 +159,7 @@ extern "C" int adana_opt_step(float* p, const float* g, float* m, float* v, floa
   if (n <= 0) return 0;
   const int grid = opt_grid(n);
   __nv_bfloat16* p16 = reinterpret_cast<__nv_bfloat16*>(p_bf16);
-  if (h->kind == 1 && !tau) return -1;
+  if ((h->kind == 1 || h->kind == 4 || h->kind == 5) && !tau) return -1;
 #define OPT_LAUNCH(K, B, D) \
   opt_step_kernel<K, B, D><<<grid, OPT_THREADS, 0, st>>>(p, g, m, v, tau, p16, n, *h, clip_coef_ptr, diag)
 #define OPT_KIND(K)                                         \
@@ -161,6 +175,8 @@ extern "C" int adana_opt_step(float* p, const float* g, float* m, float* v, floa
     case 1: OPT_KIND(1) break;
     case 2: OPT_KIND(2) break;
     case 3: OPT_KIND(3) break;
+    case 4: OPT_KIND(4) break;
+    case 5: OPT_KIND(5) break;
     default: return -2;
   }
 #undef OPT_KIND

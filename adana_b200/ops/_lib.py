@@ -38,6 +38,7 @@ class AdanaOptHyper(Structure):
         ("clipsnr", c_float), ("eps", c_float), ("gamma3", c_float), ("wd_factor", c_float),
         ("grad_scale", c_float), ("kind", c_int),
         ("beta1", c_float), ("beta2", c_float), ("bc1", c_float), ("bc2", c_float),
+        ("beta3", c_float), ("wd_coupled", c_float),
     ]
 
 

@@ -13,7 +13,7 @@ import torch
 from . import _lib
 from ..optim.logtime import logtime_update_
 
-KIND_ADANA, KIND_DANA_STAR, KIND_ADAMW, KIND_ADAMW_IWD = 0, 1, 2, 3
+KIND_ADANA, KIND_DANA_STAR, KIND_ADAMW, KIND_ADAMW_IWD, KIND_ADEMAMIX, KIND_ADEMAMIX_IWD = 0, 1, 2, 3, 4, 5
 
 
 def cast_f32_to_bf16(src: torch.Tensor, dst: torch.Tensor):
@@ -49,7 +49,8 @@ def clip_coef(sumsq: torch.Tensor, norm_scale: float, max_norm: float, out: torc
     return out
 
 
-def make_hyper(*, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor, grad_scale=1.0, betas=(0.9, 0.999)):
+def make_hyper(*, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor, grad_scale=1.0, betas=(0.9, 0.999),
+               beta3=0.0, wd_coupled=0.0):
     """The C struct of per-launch optimizer scalars."""
     h = _lib.AdanaOptHyper()
     h.lr, h.alpha, h.step = float(lr), float(alpha), float(step)
@@ -60,18 +61,19 @@ def make_hyper(*, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor,
     b1, b2 = betas
     h.beta1, h.beta2 = float(b1), float(b2)
     h.bc1, h.bc2 = float(1 - b1 ** step), float(1 - b2 ** step)
+    h.beta3, h.wd_coupled = float(beta3), float(wd_coupled)
     return h
 
 
 def fused_step(p, g, m, v, tau, p16, *, kind, lr, alpha, step, kappa, clipsnr, eps, gamma3, wd_factor,
-               grad_scale=1.0, clip_coef_t=None, betas=(0.9, 0.999), diag=None):
+               grad_scale=1.0, clip_coef_t=None, betas=(0.9, 0.999), diag=None, beta3=0.0, wd_coupled=0.0):
     """One fused update of a flat fp32 range.  All tensors are 1-D and contiguous."""
     n = p.numel()
     if n == 0:
         return
     if p.is_cuda and _lib.available():
         h = make_hyper(kind=kind, lr=lr, alpha=alpha, step=step, kappa=kappa, clipsnr=clipsnr, eps=eps, gamma3=gamma3,
-                       wd_factor=wd_factor, grad_scale=grad_scale, betas=betas)
+                       wd_factor=wd_factor, grad_scale=grad_scale, betas=betas, beta3=beta3, wd_coupled=wd_coupled)
         rc = _lib.lib().adana_opt_step(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _lib.ptr(tau),
                                        _lib.ptr(p16), n, ctypes.byref(h), _lib.ptr(clip_coef_t), _lib.ptr(diag),
                                        _lib.stream_ptr())
@@ -91,6 +93,18 @@ def fused_step(p, g, m, v, tau, p16, *, kind, lr, alpha, step, kappa, clipsnr, e
             diag[1] += d["gradient_norm"] ** 2
             diag[2] += d["auto_factor_mean"] * nel
             diag[3] += d["m_norm"] ** 2
+    elif kind in (KIND_ADEMAMIX, KIND_ADEMAMIX_IWD):
+        b1, b2 = betas
+        m.mul_(b1).add_(gs, alpha=1 - b1)
+        tau.mul_(beta3).add_(gs, alpha=1 - beta3)
+        v.mul_(b2).addcmul_(gs, gs, value=1 - b2)
+        denom = (v.sqrt() / (1 - b2 ** step) ** 0.5).add_(eps)
+        upd = (m / (1 - b1 ** step) + alpha * gamma3 * tau) / denom
+        if kind == KIND_ADEMAMIX_IWD:
+            p.mul_(wd_factor)
+        else:
+            upd.add_(p, alpha=wd_coupled)
+        p.add_(upd, alpha=-lr)
     else:
         b1, b2 = betas
         if kind == KIND_ADAMW:

@@ -28,8 +28,22 @@ def build_optimizer(args, model, group_specs, engine=None):
             from ..parallel.dist_muon import ShardedMuon
 
             return ShardedMuon(engine, args, group_specs)
-        raise ValueError(f"--opt {args.opt} is not available with the sharded engine; use the ddp backend "
-                         f"or one of {sorted(FUSED_OPTS)} / d-muon")
+        # every other name: its per-tensor class on views of this rank's shards (element-wise updates) or on whole
+        # tensors kept by one owner rank each (updates that look at a matrix or a per-tensor norm)
+        from .sharded_adapters import ELEMENTWISE, OwnerOptimizer, ShardViewOptimizer
+
+        def make_inner(specs):
+            return _build_per_tensor(args, model, specs)
+
+        cls = ShardViewOptimizer if args.opt in ELEMENTWISE else OwnerOptimizer
+        return cls(engine, make_inner, group_specs)
+    if engine is not None:
+        engine.average_on_sync = True      # a per-tensor class on the engine's gradient views wants rank-averaged gradients
+    return _build_per_tensor(args, model, group_specs)
+
+
+def _build_per_tensor(args, model, group_specs):
+    """The per-tensor optimizer class of `args.opt` over the given parameter groups."""
 
     def adamw():
         cuda = "cuda" in str(args.device)
@@ -40,7 +54,11 @@ def build_optimizer(args, model, group_specs, engine=None):
 
     def muon():
         raw = model.module if hasattr(model, "module") else model
-        return Muon(muon_params=list(raw.parameters()), lr=args.muon_lr_factor, momentum=args.momentum,
+        params = list(raw.parameters())
+        if any(p.numel() == 0 for p in params):
+            # sharded engine: the module's parameters are released; the groups hold the tensors this rank owns
+            params = [p for g in group_specs for p in g["params"] if p.numel() > 0]
+        return Muon(muon_params=params, lr=args.muon_lr_factor, momentum=args.momentum,
                     nesterov=args.nesterov, ns_steps=args.muon_ns_steps, adamw_params=None, adamw_lr=args.lr,
                     adamw_betas=(args.beta1, args.beta2), adamw_eps=1e-8, adamw_wd=args.weight_decay)
 

@@ -150,6 +150,13 @@ def head_forward_backward(x, targets, W, Gd, sp_norm_kind: int, eps: float, z_co
     gradient w.r.t. x (and its compute-dtype copy) and accumulates dW of lm_head / ln_f."""
     T, d = x.shape
     xf, mean, rstd = N.norm_fwd(x, W["ln_f"], eps, sp_norm_kind, cdt)
+    if targets is None:
+        # labels drawn from the model's own distribution, a chunk of logits at a time
+        targets = torch.empty(T, dtype=torch.long, device=x.device)
+        with torch.no_grad():
+            for s0 in range(0, T, 4096):
+                logits = G.linear_fwd(xf[s0:s0 + 4096], W["lm_head"]).float()
+                targets[s0:s0 + 4096] = torch.distributions.Categorical(logits=logits).sample()
     if need_grad and not acc:
         Gd["lm_head"].zero_()
     res = M.linear_ce(xf, W["lm_head"], targets.reshape(-1), z_coeff, loss_scale, need_grad=need_grad,

@@ -45,7 +45,9 @@ from .layout import UnitLayout, build_layouts, engine_supported
 
 FUSED_OPTS = {"adana": (O.KIND_ADANA, False), "dana-mk4": (O.KIND_ADANA, True),
               "dana-star": (O.KIND_DANA_STAR, False), "dana-star-mk4": (O.KIND_DANA_STAR, True),
-              "adamw": (O.KIND_ADAMW, False), "adamw-decaying-wd": (O.KIND_ADAMW_IWD, False)}
+              "adamw": (O.KIND_ADAMW, False), "adamw-decaying-wd": (O.KIND_ADAMW_IWD, False),
+              "ademamix": (O.KIND_ADEMAMIX, False), "ademamix-decaying-wd": (O.KIND_ADEMAMIX_IWD, False)}
+_THREE_STATE = (O.KIND_DANA_STAR, O.KIND_ADEMAMIX, O.KIND_ADEMAMIX_IWD)     # kinds with a third moment buffer ("tau")
 
 
 class _Bridge(torch.autograd.Function):
@@ -191,6 +193,13 @@ class Engine:
         self.micro_step = 0            # micro-steps accumulated since the last optimizer step
         self.sync_on_backward = None   # None: automatic (last of acc_steps); bool: forced by the backend
         self.opt_step_count = 0
+        # a replicated engine under an optimizer that is not its own hands out averaged gradients (the fused step
+        # folds the 1 / world into its update instead); set by `optim.registry.build_optimizer`
+        self.average_on_sync = False
+        self._averaged = False
+        # report the Hoyer value of the embeddings with every forward even when it does not enter the loss, as the
+        # reference's models do; the training loop switches it off on iterations that log nothing
+        self.report_aux = True
         self.last_grad_norm = None
         self.launches = 0
         self._meter_pairs = []
@@ -443,7 +452,10 @@ class Engine:
 
     _small_all = None
 
-    def forward(self, idx, targets, compute_accuracy: bool = False):
+    def forward(self, idx, targets, compute_accuracy: bool = False, sample_targets: bool = False):
+        """`sample_targets`: ignore `targets` and draw every position's label from the model's own predictive
+        distribution, plain cross-entropy without the z term: the extra backward of Sophia's Hessian estimate
+        (src/optim/base.py:268-284), which the reference runs on full logits."""
         model, sp, ecfg = self.model, self.spec, self.ecfg
         need_grad = model.training and torch.is_grad_enabled()
         B, S = idx.shape
@@ -464,8 +476,8 @@ class Engine:
             saved.append(sv if keep else ({"x_only": x_in} if need_grad else None))
         acc = self.micro_step > 0
         out, dx, dx_lp = BK.head_forward_backward(
-            x, targets, root.W, root.Gd, sp.norm_kind, sp.eps, ecfg.z_loss_coeff, self.loss_scale,
-            self.cdt, need_grad, acc)
+            x, None if sample_targets else targets, root.W, root.Gd, sp.norm_kind, sp.eps,
+            0.0 if sample_targets else ecfg.z_loss_coeff, self.loss_scale, self.cdt, need_grad, acc)
         loss = out["loss"]
         aux = {"z_loss": out["z"]}
         hoyer_grad = None
@@ -473,8 +485,9 @@ class Engine:
             hv, hoyer_grad = BK.hoyer_value_and_grad(x0, ecfg.hoyer_loss_coeff, self.loss_scale, need_grad)
             aux["hoyer_loss"] = hv
             loss = loss + ecfg.hoyer_loss_coeff * hv
-        else:
-            # reported even when it does not enter the loss, as the reference's models do (src/models/enoki.py:341-343)
+        elif self.report_aux or not need_grad:
+            # reported even when it does not enter the loss, as the reference's models do (src/models/enoki.py:341-343):
+            # two reductions over [T, d], skipped on training iterations whose outputs nobody reads
             with torch.no_grad():
                 aux["hoyer_loss"] = BK.hoyer_value_and_grad(x0, 0.0, self.loss_scale, False)[0]
         accuracy = (out["correct"] / T) if compute_accuracy else None
@@ -495,8 +508,10 @@ class Engine:
         if sync is None:
             sync = (self.micro_step + 1) >= self.ecfg.acc_steps
         root = self.units[-1]
-        if self.micro_step == 0 and (self.plane or self.ar_plane) is not None:
-            self._sumsq.zero_()      # the reductions of this optimizer step accumulate their squared-norm partials here
+        if self.micro_step == 0:
+            self._averaged = False
+            if (self.plane or self.ar_plane) is not None:
+                self._sumsq.zero_()  # the reductions of this optimizer step accumulate their squared-norm partials here
         with torch.no_grad():
             for i in range(len(self.units) - 2, -1, -1):
                 u = self.units[i]
@@ -604,6 +619,10 @@ class Engine:
                 wait(u.grad_work)
                 u.grad_work = None
         self._meter_end(e0)
+        if self.average_on_sync and not self._averaged and self.world > 1 and not self.sharded and self.micro_step > 0:
+            for u in self.units:
+                u.grads.mul_(1.0 / self.world)
+            self._averaged = True
 
     def grad_norm_and_clip(self, max_norm: float):
         """Global L2 norm of the (rank-averaged) gradient; leaves the clip coefficient on the device.
@@ -613,6 +632,7 @@ class Engine:
         if plane is not None:
             # the reduce-scatter / all-reduce kernels already accumulated this rank's squared-norm partial
             e0 = self._meter_begin()
+            # (the partials are of the rank-SUMMED gradient, also when the buffers have been averaged since)
             plane.global_clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
             self._meter_end(e0)
             self.last_grad_norm = self._clip[1]
@@ -624,7 +644,7 @@ class Engine:
             e0 = self._meter_begin()
             self.comm.all_reduce_sum(self._sumsq)
             self._meter_end(e0)
-        O.clip_coef(self._sumsq, 1.0 / self.world, max_norm, self._clip)
+        O.clip_coef(self._sumsq, 1.0 if self._averaged else 1.0 / self.world, max_norm, self._clip)
         self.last_grad_norm = self._clip[1]
         return self._clip[1]
 
@@ -634,7 +654,7 @@ class Engine:
         if self.ecfg.grad_clip == 0.0 or opt.clip_pending is False:
             self._clip[0] = 1.0
         kind, use_clip = FUSED_OPTS[opt.opt_name]
-        state_names = ["m", "v"] + (["tau"] if kind == O.KIND_DANA_STAR else [])
+        state_names = ["m", "v"] + (["tau"] if kind in _THREE_STATE else [])
         t = opt.step_count + 1
         g_decay, g_nodecay = opt.param_groups[0], opt.param_groups[1]
         diag = None
@@ -873,7 +893,16 @@ class EngineOptimizer(torch.optim.Optimizer):
             if "weight_decay" in spec:
                 g["weight_decay"] = spec["weight_decay"]
             groups.append(g)
-        if opt_name.startswith("adamw"):
+        if opt_name.startswith("ademamix"):
+            # the per-tensor classes' group keys (src/optim/ademamix.py:31-60), so schedulers and checkpoints agree
+            defaults = dict(lr=args.lr, betas=(self.betas[0], self.betas[1], getattr(args, "adema_beta3", 0.9999)),
+                            eps=1e-8, alpha=getattr(args, "adema_alpha", 2.0),
+                            beta3_warmup=getattr(args, "adema_beta3_warmup", None),
+                            alpha_warmup=getattr(args, "adema_alpha_warmup", None), weight_decay=args.weight_decay,
+                            gamma_3_factor=self.gamma_3_factor)
+            if opt_name == "ademamix-decaying-wd":
+                defaults.update(wd_decaying=self.wd_decaying, wd_ts=self.wd_ts)
+        elif opt_name.startswith("adamw"):
             defaults = dict(lr=args.lr, betas=self.betas, epsilon=1e-8, eps=1e-8, weight_decay=args.weight_decay)
         else:
             defaults = dict(lr=args.lr, delta=getattr(args, "delta", 8.0), epsilon=1e-8,
@@ -890,6 +919,20 @@ class EngineOptimizer(torch.optim.Optimizer):
             wdf = wd_multiplier(wd, sched, t, self.wd_decaying, self.wd_ts) if wd != 0 else 1.0
         else:
             wdf = wd_multiplier(wd, sched, t, self.wd_decaying, self.wd_ts)
+        if self.opt_name.startswith("ademamix"):
+            from ..optim.adam_family import linear_hl_warmup_scheduler, linear_warmup_scheduler
+
+            b1, b2, b3 = group["betas"]
+            alpha = group["alpha"]
+            if group.get("alpha_warmup") is not None:
+                alpha = linear_warmup_scheduler(t, alpha_end=alpha, alpha_start=0, warmup=group["alpha_warmup"])
+            if group.get("beta3_warmup") is not None:
+                b3 = linear_hl_warmup_scheduler(t, beta_end=b3, beta_start=b1, warmup=group["beta3_warmup"])
+            iwd = self.opt_name == "ademamix-decaying-wd"
+            wdf = wd_multiplier(wd, sched, t, group.get("wd_decaying", False), group.get("wd_ts", 1.0)) if iwd else 1.0
+            return dict(lr=lr, alpha=alpha, step=t, kappa=1.0, clipsnr=None, eps=group.get("eps", 1e-8),
+                        gamma3=group.get("gamma_3_factor", 1.0), wd_factor=wdf, betas=(b1, b2), beta3=b3,
+                        wd_coupled=0.0 if iwd else wd)
         delta = group.get("delta", 8.0)
         return dict(lr=lr, alpha=delta / (delta + t), step=t, kappa=self.kappa, clipsnr=self.clipsnr,
                     eps=group.get("epsilon", 1e-8), gamma3=self.gamma_3_factor, wd_factor=wdf, betas=self.betas)
@@ -925,6 +968,8 @@ class EngineOptimizer(torch.optim.Optimizer):
         keys = {"m": "m", "v": "v", "tau": "tau"}
         if kind in (O.KIND_ADAMW, O.KIND_ADAMW_IWD):
             keys = {"m": "exp_avg", "v": "exp_avg_sq"}
+        elif kind in (O.KIND_ADEMAMIX, O.KIND_ADEMAMIX_IWD):
+            keys = {"m": "exp_avg_fast", "v": "exp_avg_sq", "tau": "exp_avg_slow"}
         fulls = {k: self.engine.full_param_dict(k) for k in keys}
         state = {}
         for i, n in enumerate(names):
@@ -949,6 +994,8 @@ class EngineOptimizer(torch.optim.Optimizer):
         keymap = {"m": "m", "v": "v", "tau": "tau"}
         if kind in (O.KIND_ADAMW, O.KIND_ADAMW_IWD):
             keymap = {"m": "exp_avg", "v": "exp_avg_sq"}
+        elif kind in (O.KIND_ADEMAMIX, O.KIND_ADEMAMIX_IWD):
+            keymap = {"m": "exp_avg_fast", "v": "exp_avg_sq", "tau": "exp_avg_slow"}
         state = sd.get("state", {})
 
         def plain(key):      # names as `torch.distributed.checkpoint` stores them, wrapper prefixes dropped

@@ -190,6 +190,10 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
             payload["units"][u.layout.name] = entry
         groups = [{k: v for k, v in g.items() if k != "params"} for g in opt.param_groups]
         payload["param_groups"] = groups
+        if hasattr(opt, "inner"):
+            # a per-tensor optimizer class on this rank's pieces / owned tensors (optim/sharded_adapters.py): its state
+            # is not in the engine's flat moment shards; it is restored on the same world size only
+            payload["per_tensor_opt"] = _to_cpu(opt.state_dict())
         path = local / "sharded" / f"rank{eng.rank:05d}.pt"
         if async_write:
             _async_writer.submit(payload, path)
@@ -271,6 +275,14 @@ def _load_sharded(eng, opt, sharded_dir: Path):
                 dst[a - lo:b - lo].copy_(t[a - r * s_shard:b - r * s_shard])
     if opt is not None and opt_step is not None and hasattr(opt, "step_count"):
         opt.step_count = int(opt_step)
+    if opt is not None and hasattr(opt, "inner"):
+        own = saved(eng.rank) if saved_world == eng.world else None
+        if own is None or "per_tensor_opt" not in own:
+            raise RuntimeError("the state of a per-tensor optimizer under the sharded engine can only be restored on the "
+                               f"world size it was saved with ({saved_world}); this run has {eng.world} ranks")
+        opt.load_state_dict(own["per_tensor_opt"])
+        eng.refresh_from_master()
+        return
     any_file = saved(0)
     if opt is not None and "param_groups" in any_file:
         for g, sg in zip(opt.param_groups, any_file["param_groups"]):

@@ -234,6 +234,9 @@ class Trainer:
     def train_step(self):
         cfg, model, opt = self.cfg, self.run_model, self.opt
         outputs, loss, x, y = None, None, None, None
+        if self.engine is not None:
+            # auxiliary values that do not enter the loss are only computed on iterations whose outputs are logged
+            self.engine.report_aux = bool(cfg.log_interval) and (self.curr_iter + 1) % cfg.log_interval == 0
         for micro in range(cfg.acc_steps):
             with nvtx_range("data", cfg):
                 x, y = self.stager.next_batch()
@@ -254,6 +257,8 @@ class Trainer:
             # steps whose iteration will be logged
             opt.want_diagnostics = bool(cfg.log_interval) and (self.curr_iter + 1) % cfg.log_interval == 0
         with nvtx_range("optimizer", cfg):
+            if self.engine is not None:
+                self.engine.finish_grad_sync()    # (a per-tensor optimizer reads the gradient buffers directly)
             if cfg.opt in ("sf-sgd", "sf-adamw"):
                 opt.train()
             if cfg.opt == "sophiag":
@@ -274,15 +279,22 @@ class Trainer:
             opt.zero_grad(set_to_none=True)
             f = cfg.precondition_frequency
             if self.curr_iter % f == f - 1:
-                if self.engine is not None:
-                    self.engine.enabled = False
-                out = self.run_model(x, targets=y, get_logits=True)
-                if self.engine is not None:
-                    self.engine.enabled = True
-                logits = out["logits"]
-                y_s = torch.distributions.Categorical(logits=logits).sample()
-                l = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), y_s.view(-1), ignore_index=-1)
-                (l / cfg.acc_steps).backward()
+                if self.engine is not None and self.engine.sharded:
+                    # no rank holds the module's parameters: the engine draws the labels chunk by chunk itself
+                    self.engine.sync_on_backward = True
+                    out = self.engine.forward(x, None, sample_targets=True)
+                    (out["loss"] / cfg.acc_steps).backward()
+                    self.engine.sync_on_backward = None
+                else:
+                    if self.engine is not None:
+                        self.engine.enabled = False
+                    out = self.run_model(x, targets=y, get_logits=True)
+                    if self.engine is not None:
+                        self.engine.enabled = True
+                    logits = out["logits"]
+                    y_s = torch.distributions.Categorical(logits=logits).sample()
+                    l = torch.nn.functional.cross_entropy(logits.view(-1, logits.size(-1)), y_s.view(-1), ignore_index=-1)
+                    (l / cfg.acc_steps).backward()
                 opt.update_hessian()
                 opt.zero_grad(set_to_none=True)
                 self.model.zero_grad()

@@ -187,3 +187,52 @@ def test_worker_state_roundtrip(tmp_path):
     ck.load_worker_state(tmp_path, train_reader=r2, verbose=False)
     assert torch.equal(torch.rand(3), expect[0]) and np.array_equal(np.random.rand(2), expect[1])
     assert random.random() == expect[2] and torch.equal(r2.sample_batch()[0], expect[3])
+
+
+@pytest.mark.parametrize("opt_name", ["ademamix", "ademamix-decaying-wd"])
+def test_engine_ademamix_matches_per_tensor_class(opt_name):
+    """The fused flat AdEMAMix step (fast / slow EMA + Adam second moment, alpha and beta3 warm-ups as host scalars)
+    against the per-tensor class, which is itself stepped against the reference's in tests/test_optim.py."""
+    from adana_b200.optim.adam_family import AdEMAMix, AdEMAMixDecayingWD
+
+    a = tiny_args("enoki", opt=opt_name, lr=2e-3, weight_decay=0.1, wd_decaying=True, wd_ts=3.0, grad_clip=0.5,
+                  beta1=0.9, beta2=0.95, adema_beta3=0.99, adema_alpha=3.0, adema_beta3_warmup=6, adema_alpha_warmup=6,
+                  gamma_3_factor=0.7)
+    torch.manual_seed(0)
+    ref = get_model(a)
+    m = copy.deepcopy(ref)
+    eng = attach(m, a, device="cpu")
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    e_opt = EngineOptimizer(eng, opt_name, a, specs)
+    named = dict(ref.named_parameters())
+    r_specs = ref.get_parameter_group_specs()
+    for g in r_specs:
+        g["params"] = [named[n] for n in g["params"]]
+    kw = dict(lr=a.lr, betas=(0.9, 0.95, 0.99), alpha=3.0, beta3_warmup=6, alpha_warmup=6, weight_decay=0.1,
+              gamma_3_factor=0.7)
+    r_opt = (AdEMAMixDecayingWD(r_specs, wd_decaying=True, wd_ts=3.0, **kw) if opt_name.endswith("wd")
+             else AdEMAMix(r_specs, **kw))
+    m.train()
+    for step in range(4):
+        idx, tgt = batch(a, seed=step)
+        lr = a.lr * (1 - 0.2 * step)
+        for g in list(e_opt.param_groups) + list(r_opt.param_groups):
+            g["lr"] = lr
+        m(idx, targets=tgt)["loss"].backward()
+        eng.grad_norm_and_clip(0.5)
+        e_opt.step()
+        e_opt.zero_grad()
+        ref(idx, targets=tgt)["loss"].backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        r_opt.step()
+        r_opt.zero_grad(set_to_none=True)
+    # (coordinates whose gradient is rounding noise move by up to (1 + alpha) lr per step in either run: statistical bound)
+    for (n, p), (_, q) in zip(sorted(m.named_parameters()), sorted(ref.named_parameters())):
+        d = (p - q).abs()
+        assert d.mean().item() < 3e-6 and d.max().item() < 0.1 * 4 * a.lr * 4, (n, d.mean().item(), d.max().item())
+    sd = e_opt.state_dict()
+    assert {"exp_avg_fast", "exp_avg_slow", "exp_avg_sq", "step"} <= set(sd["state"][0])
+    rs = r_opt.state_dict()["state"]
+    assert torch.allclose(sd["state"][0]["exp_avg_slow"], rs[0]["exp_avg_slow"], rtol=1e-3, atol=1e-9)

@@ -205,8 +205,12 @@ def test_linear_ce(V, d, T, logits_dtype):
     assert_close(out["dw"], ref["dw"], what="dw")
 
 
-@pytest.mark.parametrize("kind,clipsnr", [(0, None), (0, 2.0), (1, None), (1, 2.0), (2, None), (3, None)])
+@pytest.mark.parametrize("kind,clipsnr", [(0, None), (0, 2.0), (1, None), (1, 2.0), (2, None), (3, None), (4, None),
+                                          (5, None)])
 def test_fused_optimizer(kind, clipsnr):
+    """The fused flat step on the GPU against the same step through its PyTorch formulation on the CPU (which the CPU
+    tests pin to the per-tensor classes, and those to the reference's own classes): ADana, Dana-Star, AdamW with
+    coupled / independent decay, AdEMAMix with coupled / independent decay."""
     torch.manual_seed(7)
     n = 100_003
     mk = lambda: (torch.randn(n, device=DEV), torch.randn(n, device=DEV) * 1e-2,
@@ -216,14 +220,14 @@ def test_fused_optimizer(kind, clipsnr):
     p16 = torch.empty(n, device=DEV, dtype=torch.bfloat16)
     clip = torch.tensor([0.7, 0.0], device=DEV)
     kw = dict(kind=kind, lr=3e-3, alpha=8 / 15, step=7, kappa=0.85, clipsnr=clipsnr, eps=1e-8, gamma3=1.0,
-              wd_factor=0.999, grad_scale=0.5, betas=(0.9, 0.95))
+              wd_factor=0.999, grad_scale=0.5, betas=(0.9, 0.95), beta3=0.97, wd_coupled=0.05)
     diag = torch.zeros(4, device=DEV)
     optim.fused_step(p, g, m, v, tau, p16, clip_coef_t=clip, diag=diag, **kw)
     pc, gc, mc, vc, tc = cpu
     dc = torch.zeros(4)
     optim.fused_step(pc, gc, mc, vc, tc, None, clip_coef_t=clip.cpu(), diag=dc, **kw)
     assert rel_err(p.cpu(), pc) < 1e-5 and rel_err(m.cpu(), mc) < 1e-5 and rel_err(v.cpu(), vc) < 1e-5
-    if kind == 1:
+    if kind in (1, 4, 5):
         assert rel_err(tau.cpu(), tc) < 1e-5
     assert rel_err(p16.cpu(), pc) < 8e-3
     if kind in (0, 1):
