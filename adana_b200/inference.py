@@ -7,8 +7,9 @@ Same command line and checkpoint discovery as the reference's `inference.py` (1-
 directory's `summary.json` supplies the model arguments, `ckpts/latest/main.pt` (or `main.pt` / `ckpt.pt`)
 the weights, key prefixes from DDP (`module.`) and compiled models (`_orig_mod.`) are stripped, and
 without `--prompt` the tool drops into an interactive loop.  A checkpoint of an FSDP run, which has no `main.pt`,
-is read too: its `sharded/layout.json` + `rank*.pt` files are reassembled into full tensors without a process group
-(`train/checkpoint.py::full_state_from_sharded`); the reference's tool reads DDP/single checkpoints only.
+is read too: its `sharded/` directory (the `torch.distributed.checkpoint` layout, whether written here or by the
+reference) is reassembled into full tensors without a process group (`train/checkpoint.py::full_state_from_sharded`);
+the reference's tool reads DDP/single checkpoints only.
 
 The decode loop is new: the reference re-runs the whole context through the network for every new token
 (models/base.py generate: O(T²) per sequence).  `KVDecoder` keeps per-layer key/value caches for the RoPE
@@ -31,14 +32,18 @@ from .models.enoki import apply_rotary_emb
 
 
 def _sharded_marker(ckpt_dir: Path):
-    """The `sharded/layout.json` of a checkpoint directory written by an FSDP run, or None."""
-    f = ckpt_dir / "sharded" / "layout.json"
-    return f if f.exists() else None
+    """The index file of the `sharded/` directory of a checkpoint written by an FSDP run, or None (`.metadata` of a
+    torch.distributed.checkpoint directory; `layout.json` of the flat-shard files earlier versions wrote)."""
+    for name in (".metadata", "layout.json"):
+        f = ckpt_dir / "sharded" / name
+        if f.exists():
+            return f
+    return None
 
 
 def find_checkpoint_file(path):
     """-> (checkpoint file, experiment directory) for a file, an exp dir, `ckpts/` or `ckpts/<name>/`.  For a
-    checkpoint of an FSDP run (no `main.pt`) the file returned is its `sharded/layout.json`."""
+    checkpoint of an FSDP run (no `main.pt`) the file returned is the index file of its `sharded/` directory."""
     p = Path(path)
     if p.is_file() and p.suffix == ".pt":
         exp = p.parent.parent.parent if p.parent.parent.name == "ckpts" else p.parent
@@ -85,7 +90,7 @@ def load_model(path, device="cpu"):
     cfg.device = device
     cfg.dropout = 0.0
     model = get_model(cfg)
-    if ckpt.name == "layout.json":      # sharded checkpoint of an FSDP run: reassemble the full tensors
+    if ckpt.name in (".metadata", "layout.json"):      # sharded checkpoint of an FSDP run: reassemble the full tensors
         from .train.checkpoint import full_state_from_sharded
 
         blob = {"model": full_state_from_sharded(ckpt.parent)}

@@ -5,15 +5,15 @@ On-disk layouts (a run directory holds `ckpts/latest` and `ckpts/<iteration>`):
   replicated / single   `<ckpt>/main.pt` = {"model", "optimizer", "scheduler", "itr"} — the
                         reference's file (src/optim/utils.py:300-310), readable by both sides,
                         including the `_orig_mod.` / `module.` key prefixes of compiled / DDP runs.
-  sharded (fsdp)        `<ckpt>/sharded/rank{r:05d}.pt` = this rank's flat fp32 shards
-                        (parameters + optimizer moments of every unit) and
-                        `<ckpt>/sharded/layout.json` = unit layouts + world size;
-                        `<ckpt>/meta.pt` = {"scheduler", "itr"} (same file as the reference,
-                        src/optim/utils.py:291-298).  Every rank writes only what it owns, no
-                        gather, so the time to checkpoint does not grow with the model.
-                        Loading with a different world size re-slices the saved flat ranges.
-                        `export_full()` / `import_dcp()` convert to `main.pt` and from a
-                        `torch.distributed.checkpoint` directory written by the reference.
+  sharded (fsdp)        `<ckpt>/sharded/` = a `torch.distributed.checkpoint` directory holding
+                        {"model", "optimizer"} keyed by parameter name, and `<ckpt>/meta.pt` =
+                        {"scheduler", "itr"}: the reference's layout (src/optim/utils.py:275-298), which
+                        its own `dcp.load` reads.  Every rank writes only the rectangles of each tensor
+                        that its flat shards cover (train/dcp_format.py), no gather, so the time to
+                        checkpoint does not grow with the model; loading with a different world size
+                        reads the overlapping chunks.  meta.pt is written last: a directory that has it
+                        is complete.  `export_full()` / `import_dcp()` convert to `main.pt` and from a
+                        directory written by the reference.
   every rank            `<ckpt>/worker_{rank}.pt` = RNG states (torch CPU/GPU, numpy, python) and
                         the data-reader position (reference src/optim/utils.py:364-415).
 
@@ -181,34 +181,19 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
     eng = _engine_of(model)
     sched_sd = scheduler.state_dict() if scheduler is not None else None
     if eng is not None and eng.sharded:
-        payload = {"world": eng.world, "rank": eng.rank, "opt_step": getattr(opt, "step_count", 0), "itr": int(itr),
-                   "units": {}}
-        for u in eng.units:
-            entry = {"master": u.master.detach().cpu()}
-            for k, t in u.state.items():
-                entry[k] = t.detach().cpu()
-            payload["units"][u.layout.name] = entry
-        groups = [{k: v for k, v in g.items() if k != "params"} for g in opt.param_groups]
-        payload["param_groups"] = groups
-        if hasattr(opt, "inner"):
-            # a per-tensor optimizer class on this rank's pieces / owned tensors (optim/sharded_adapters.py): its state
-            # is not in the engine's flat moment shards; it is restored on the same world size only
-            payload["per_tensor_opt"] = _to_cpu(opt.state_dict())
-        path = local / "sharded" / f"rank{eng.rank:05d}.pt"
-        if async_write:
-            _async_writer.submit(payload, path)
-        else:
-            _atomic_save(payload, path)
+        # `<ckpt>/sharded/` is a torch.distributed.checkpoint directory, as in the reference (src/optim/utils.py:
+        # 275-298): every rank writes the rectangles of every tensor that its flat shards cover (train/dcp_format.py).
+        # The call is collective and returns when all ranks' files and the index are on disk; only then does rank 0
+        # write meta.pt, so a directory with a meta.pt is complete.
+        from .dcp_format import save_engine_state
+
+        _async_writer.wait()
         if eng.rank == 0:
-            layout = {"world": eng.world, "compute_dtype": str(eng.cdt), "units": [
-                {"name": u.layout.name, "numel": u.layout.numel, "padded": u.layout.padded,
-                 "decay_end": u.layout.decay_end,
-                 "slots": [{"name": s.name, "shape": list(s.shape), "offset": s.offset, "decay": s.decay}
-                           for s in u.layout.slots]} for u in eng.units]}
-            (local / "sharded").mkdir(parents=True, exist_ok=True)
-            tmp = local / "sharded" / "layout.json.tmp"
-            tmp.write_text(json.dumps(layout))
-            os.replace(tmp, local / "sharded" / "layout.json")
+            stale = local / "meta.pt"
+            if stale.exists():
+                stale.unlink()
+        save_engine_state(eng, opt, local / "sharded")
+        if eng.rank == 0:
             _atomic_save({"scheduler": sched_sd, "itr": itr}, local / "meta.pt")
         return
     if _rank() != 0:
@@ -297,6 +282,17 @@ def full_state_from_sharded(sharded_dir: Path, which: str = "master") -> Dict[st
     and single-file export need from an FSDP run (the reference's inference reads DDP/single checkpoints only,
     inference.py:165-191)."""
     sharded_dir = Path(sharded_dir)
+    if (sharded_dir / ".metadata").exists():
+        model_sd, opt_sd = import_dcp(sharded_dir)
+        if which == "master":
+            return model_sd
+        names = {"m": ("m", "exp_avg", "exp_avg_fast"), "v": ("v", "exp_avg_sq"), "tau": ("tau", "exp_avg_slow")}[which]
+        out = {}
+        for n, st in ((opt_sd or {}).get("state", {}) or {}).items():
+            for k in names:
+                if isinstance(st, dict) and k in st:
+                    out[n] = st[k]
+        return out
     layout = json.loads((sharded_dir / "layout.json").read_text())
     world = layout["world"]
     files = [_load(sharded_dir / f"rank{r:05d}.pt") for r in range(world)]
@@ -325,8 +321,18 @@ def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_
     ckpt_path = Path(ckpt_path)
     ckpt_dir = ckpt_path.parent if ckpt_path.suffix == ".pt" else ckpt_path
     eng = _engine_of(model)
+    if (ckpt_dir / "sharded" / ".metadata").exists() and eng is not None and eng.sharded:
+        from .dcp_format import load_engine_state
+
+        if not (ckpt_dir / "meta.pt").exists():
+            raise RuntimeError(f"sharded checkpoint {ckpt_dir} is incomplete: meta.pt (written last) is missing")
+        load_engine_state(eng, opt, ckpt_dir / "sharded")
+        meta = _load(ckpt_dir / "meta.pt")
+        if scheduler is not None and meta.get("scheduler") is not None:
+            scheduler.load_state_dict(meta["scheduler"])
+        return meta["itr"]
     if (ckpt_dir / "sharded" / "layout.json").exists() and eng is not None:
-        _load_sharded(eng, opt, ckpt_dir / "sharded")
+        _load_sharded(eng, opt, ckpt_dir / "sharded")      # the flat-shard files earlier versions wrote
         meta = _load(ckpt_dir / "meta.pt")
         if scheduler is not None and meta.get("scheduler") is not None:
             scheduler.load_state_dict(meta["scheduler"])

@@ -190,7 +190,9 @@ def _resume_worker(rank, world, ckpt_dir, steps_after):
 def test_sharded_checkpoint_reshards_on_load(tmp_path):
     d = tmp_path / "ckpt"
     saved = _spawn(_train_worker, 2, True, 2, str(d), 2)
-    assert (d / "sharded" / "layout.json").exists() and (d / "sharded" / "rank00001.pt").exists()
+    # a torch.distributed.checkpoint directory: the index and one data file per rank
+    assert (d / "sharded" / ".metadata").exists() and (d / "meta.pt").exists()
+    assert len(list((d / "sharded").glob("*.distcp"))) == 2
     assert (d / "meta.pt").exists()
     for world in (1, 3):
         res = _spawn(_resume_worker, world, str(d), 0)

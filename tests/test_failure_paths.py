@@ -41,7 +41,10 @@ def test_timed_out_device_wait_stops_the_run_before_the_next_checkpoint(tmp_path
     assert saved["itr"] == 0                       # the checkpoint due at iteration 4 was not written
 
 
-def test_sharded_checkpoint_from_two_different_saves_is_refused(tmp_path):
+def test_incomplete_sharded_checkpoint_is_refused(tmp_path):
+    """meta.pt is written last, after the collective write of the `torch.distributed.checkpoint` directory has
+    returned on every rank: a directory without it (a crash during the write) is not resumed from, and a directory
+    that lost a data file fails loudly instead of resuming with missing state."""
     from conftest import tiny_args
     from adana_b200.models.utils import get_model
     from adana_b200.runtime.engine import EngineOptimizer, attach
@@ -56,16 +59,16 @@ def test_sharded_checkpoint_from_two_different_saves_is_refused(tmp_path):
     opt = EngineOptimizer(eng, "adamw", a, specs)
     d = tmp_path / "latest"
     ck.save_checkpoint(m, opt, None, 7, d)
+    assert (d / "sharded" / ".metadata").exists()
     assert ck.load_checkpoint(m, opt, None, d) == 7
-    shard = d / "sharded" / "rank00000.pt"
-    payload = torch.load(shard, weights_only=False)
-    assert payload["itr"] == 7
-    payload["itr"] = 6                     # as if this rank's file were left over from the previous save
-    torch.save(payload, shard)
-    with pytest.raises(RuntimeError, match="inconsistent.*iteration 6.*meta.pt at 7"):
+    meta = (d / "meta.pt").read_bytes()
+    (d / "meta.pt").unlink()
+    with pytest.raises(RuntimeError, match="incomplete.*meta.pt"):
         ck.load_checkpoint(m, opt, None, d)
-    shard.unlink()
-    with pytest.raises(RuntimeError, match="incomplete"):
+    (d / "meta.pt").write_bytes(meta)
+    for f in (d / "sharded").glob("*.distcp"):
+        f.unlink()
+    with pytest.raises(BaseException, match="distcp|CheckpointException"):      # (torch's CheckpointException is a BaseException)
         ck.load_checkpoint(m, opt, None, d)
 
 

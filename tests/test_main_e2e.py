@@ -83,7 +83,8 @@ def test_two_rank_fsdp_cli_run_writes_sharded_checkpoint_and_resumes(tmp_path):
     out = launch(["--iterations", "8", "--iterations_to_run", "5"])
     exp = _exp_dir(tmp_path / "exps")
     latest = exp / "ckpts" / "latest"
-    assert (latest / "sharded" / "layout.json").exists() and (latest / "sharded" / "rank00001.pt").exists()
+    # the reference's FSDP layout: a torch.distributed.checkpoint directory (index + one data file per rank)
+    assert (latest / "sharded" / ".metadata").exists() and len(list((latest / "sharded").glob("*.distcp"))) == 2
     assert (latest / "meta.pt").exists() and (latest / "worker_1.pt").exists()
     assert torch.load(latest / "meta.pt", map_location="cpu", weights_only=False)["itr"] == 5
     out = launch(["--iterations", "8", "--auto_resume"])
