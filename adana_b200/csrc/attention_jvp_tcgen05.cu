@@ -413,3 +413,5 @@ extern "C" int adana_attn_jvp(const void* q, const void* tq, const void* k, cons
   if (hd == 64) return launch_attn_jvp<64>(tm, a, st);
   return launch_attn_jvp<128>(tm, a, st);
 }
+
+ADANA_DBG_BIND(attention_jvp)

@@ -334,6 +334,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after_sync();
       const float inv_l = 1.f / l_sum;
       const long long token = (long long)row0 + r;
+      if (ADANA_IN_RANGE(token, (long long)args.B * args.S)) {
       __nv_bfloat16* dst = args.out + token * ((long long)args.Hq * HD) + (long long)h * HD;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; ++c) {
@@ -351,6 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       args.lse2[((long long)b * args.Hq + h) * args.S + qt * ATT_BQ + r] = m_ref + log2f(l_sum);
+      }
     }
   }
 
@@ -775,6 +777,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok && mbar_wait(acc_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
       tc_fence_after_sync();
       const long long token = (long long)kvrow + r;
+      (void)ADANA_IN_RANGE(token, (long long)args.B * args.S);
       __nv_bfloat16* dk_dst = args.dk + (token * args.Hk + hk) * HD;
       __nv_bfloat16* dv_dst = args.dv + token * args.lddv + (long long)hk * args.dv_hstride;
 #pragma unroll 1
@@ -1030,3 +1033,5 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
   if (hd == 64) return launch_attn_bwd<64>(tq, tdo, tk, tv, tdq, a, st);
   return launch_attn_bwd<128>(tq, tdo, tk, tv, tdq, a, st);
 }
+
+ADANA_DBG_BIND(attention)

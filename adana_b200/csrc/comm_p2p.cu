@@ -679,3 +679,5 @@ extern "C" int adana_p2p_all_to_all_pull(const unsigned long long* buf_ptrs, con
                                                           status);
   return (int)cudaGetLastError();
 }
+
+ADANA_DBG_BIND(comm)

@@ -28,6 +28,32 @@ enum : int {
   ST_TIMEOUT_ATTN = 7,
 };
 
+// ---- checked build (ADANA_DEBUG) -------------------------------------------------------------------------
+// `python -m adana_b200.build --debug` compiles every kernel without NDEBUG and with ADANA_DEBUG.  Then every
+// index a kernel computes for a global access that this header wraps in ADANA_IN_RANGE is compared with the extent
+// the kernel was given; an index outside it writes ST_BAD_ARGUMENT to the status word (first error wins) and the
+// access is skipped: nothing traps and nothing is read or written out of bounds.  Each translation unit has its own
+// pointer to the status word, bound by its `adana_debug_bind_<unit>` entry point.  In the release build the macro is
+// the constant `true` and the checks compile away.  The checked build is for valid inputs: the GPU tests run once
+// under it and the status word must stay 0; malformed shapes are refused on the host before any launch.
+#ifdef ADANA_DEBUG
+static __device__ int* g_dbg_status = nullptr;      // (inside namespace adana)
+__device__ __forceinline__ bool dbg_in_range(long long i, long long n) {
+  if (i >= 0 && i < n) return true;
+  if (g_dbg_status) atomicCAS(g_dbg_status, 0, 6 /* ST_BAD_ARGUMENT */);
+  return false;
+}
+#define ADANA_IN_RANGE(i, n) adana::dbg_in_range((long long)(i), (long long)(n))
+#define ADANA_DBG_BIND(unit)                                                                        \
+  extern "C" int adana_debug_bind_##unit(int* status) {                                             \
+    return (int)cudaMemcpyToSymbol(::adana::g_dbg_status, &status, sizeof(status));                   \
+  }
+#else
+#define ADANA_IN_RANGE(i, n) true
+#define ADANA_DBG_BIND(unit) \
+  extern "C" int adana_debug_bind_##unit(int*) { return 0; }
+#endif
+
 #ifndef ADANA_WAIT_TIMEOUT_NS
 #define ADANA_WAIT_TIMEOUT_NS 2000000000ull  // 2 s for on-chip waits
 #endif

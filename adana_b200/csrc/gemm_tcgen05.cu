@@ -1318,3 +1318,5 @@ extern "C" int adana_gemm_bf16_gather(const void* A, const void* const* B_shards
   if (b_mn && epi == EPI_DGELU) return launch_gemm_gather<true, EPI_DGELU>(tmA, sh, args, g_sm_count, stream);
   return -103;
 }
+
+ADANA_DBG_BIND(gemm)

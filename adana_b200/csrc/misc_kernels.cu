@@ -15,7 +15,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ idx, const TT
   const int nv = dim >> 2;
   for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
     long long id = idx[t];
-    if (id < 0 || id >= vocab) id = 0;  // out-of-range ids read row 0 instead of faulting
+    if (!ADANA_IN_RANGE(id, vocab) || id < 0 || id >= vocab) id = 0;  // out-of-range ids read row 0 instead of faulting
     const TT* src = table + (size_t)id * dim;
     float* dst = out + (size_t)t * dim;
     for (int c = threadIdx.x; c < nv; c += blockDim.x) {
@@ -39,7 +39,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ idx, const fl
   const int nv = dim >> 2;
   for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
     const long long id = idx[t];
-    if (id < 0 || id >= vocab) continue;
+    if (!ADANA_IN_RANGE(id, vocab) || id < 0 || id >= vocab) continue;
     const float* src = dout + (size_t)t * dim;
     float* dst = dtable + (size_t)id * dim;
     for (int c = threadIdx.x; c < nv; c += blockDim.x) {
@@ -123,6 +123,7 @@ ce_fwd_bwd_kernel(const float* __restrict__ logits, long long ld, const long lon
       const float lse = M + __logf(Ssum);
       const long long tgt = targets[row];
       const bool valid = tgt >= 0 && tgt < vocab;
+      if (tgt != -1) (void)ADANA_IN_RANGE(tgt, vocab);      // only -1 (ignored) may lie outside the vocabulary
       s_bcast[0] = M;
       s_bcast[1] = lse;
       s_bcast[2] = valid ? 1.f : 0.f;
@@ -393,3 +394,5 @@ extern "C" int adana_sigmoid_gate_bwd(const void* dout, const void* a, const voi
       gate_off, gate_hstride, (__nv_bfloat16*)da, (__nv_bfloat16*)dgate_base, n_tokens, H, hd);
   return (int)cudaGetLastError();
 }
+
+ADANA_DBG_BIND(misc)

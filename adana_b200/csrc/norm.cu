@@ -370,3 +370,5 @@ extern "C" int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, 
 }
 
 extern "C" int adana_version(void) { return 1; }
+
+ADANA_DBG_BIND(norm)

@@ -197,3 +197,5 @@ extern "C" int adana_clip_coef(const float* sumsq, float norm_scale, float max_n
   clip_coef_kernel<<<1, 1, 0, st>>>(sumsq, norm_scale, max_norm, out);
   return (int)cudaGetLastError();
 }
+
+ADANA_DBG_BIND(optim)

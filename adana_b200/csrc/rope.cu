@@ -104,7 +104,9 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         it[u] = rope_head(h0 + u * VPW + grp, Hq, Hall, q_off, q_hstride, k_off, k_hstride);
-        load8(row + it[u].src, x[u]);
+        // (checked build: the last element this lane reads lies inside the token's projection row)
+        if (it[u].ok && !ADANA_IN_RANGE(it[u].src + sub * ROPE_EPL + ROPE_EPL - 1, row_stride)) it[u].ok = false;
+        load8(row + (it[u].ok ? it[u].src : 0), x[u]);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
@@ -312,3 +314,5 @@ extern "C" int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void*
 #undef RB
   return (int)cudaGetLastError();
 }
+
+ADANA_DBG_BIND(rope)

@@ -16,7 +16,11 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libadana_b200.so"
+# ADANA_DEBUG=1 selects the checked build (`python -m adana_b200.build --debug`): kernels compare the indices they
+# compute with their extents and report through the status word (csrc/common.cuh)
+DEBUG_BUILD = os.environ.get("ADANA_DEBUG", "0") not in ("", "0")
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / ("libadana_b200_debug.so" if DEBUG_BUILD else "libadana_b200.so")
+_DEBUG_UNITS = ("misc", "rope", "attention", "norm", "optim", "comm", "gemm", "attention_jvp")
 _lib = None
 _status = {}
 
@@ -135,7 +139,7 @@ def lib():
         try:
             from adana_b200 import build as _build
 
-            _build.build()
+            _build.build(debug=DEBUG_BUILD)
         except Exception as e:  # pragma: no cover - depends on toolchain
             if torch.cuda.is_available():
                 raise RuntimeError(
@@ -172,6 +176,11 @@ def status_buffer(device=None) -> torch.Tensor:
     if buf is None:
         buf = torch.zeros(4, dtype=torch.int32, device=dev)
         _status[key] = buf
+        if DEBUG_BUILD and _lib is not None:
+            # checked build: every translation unit reports its range violations into this device's status word
+            with torch.cuda.device(dev):
+                for unit in _DEBUG_UNITS:
+                    check_rc(getattr(_lib._cdll, f"adana_debug_bind_{unit}")(c_void_p(buf.data_ptr())), f"bind {unit}")
     return buf
 
 

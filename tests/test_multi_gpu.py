@@ -85,9 +85,12 @@ def test_flagged_gradient_collectives_match_nccl(sharded, reduce_dtype):
     res = {plane: _spawn(_worker, world, plane, "resident", sharded, reduce_dtype) for plane in ("nccl", "p2p")}
     for a, b in zip(res["nccl"][0]["norms"], res["p2p"][0]["norms"]):
         assert abs(a - b) / a < 2e-2
+    # (a bf16 wire rounds each rank's gradient before the sum: parameters whose gradient is tiny, like the 64 QK-norm
+    # weights, may take a normalised step of the other sign in one of the four steps of lr 2e-3)
+    tol = 2e-4 if reduce_dtype == "float32" else 1e-3
     for k, v in res["nccl"][0]["params"].items():
         d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs()
-        assert d.mean().item() < 2e-4, (k, d.mean().item())
+        assert d.mean().item() < tol, (k, d.mean().item())
         for r in range(1, world):
             assert torch.equal(_t(res["p2p"][0]["params"][k]), _t(res["p2p"][r]["params"][k]))
 
