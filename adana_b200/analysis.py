@@ -5,7 +5,7 @@ power-law fit that produces the coefficients of `config/scaling_rules.yaml`.
 Counterparts in the reference's `visualization/` tree (which reads the W&B API and draws matplotlib figures):
 compute = 6 * non_emb * tokens, PFH = / 3600e15 (compute_saved.py:232-233, 325-328); GPU-hours = mean iter_dt *
 iters * world / 3600 (compute_gpu_hours.py:383-394); the LR law lr = a * (b + P)^d with a bootstrap over sizes
-(bighead_lr_scaling.py).  The figures themselves are not reproduced; the metric names they read
+(bighead_lr_scaling.py).  `adana_b200.figures` draws the figures from these numbers; the metric names they read
 (`iter`, `tokens`, `train/loss`, `val/loss`, `final-val/loss`, `iter_dt`, `lr`) are the ones the trainer logs.
 
     python -m adana_b200.analysis summary <exp_dir> [--non_emb N] [--world W]

@@ -195,6 +195,16 @@ def get_dataset(args) -> Dict[str, object]:
         parts = [get_dataset(_with(args, dataset=d)) for d in ("arxiv", "wikitext")]
         cat = lambda k: np.concatenate([np.memmap(p[k], dtype=np.uint16, mode="r") for p in parts])
         return {"train": cat("train"), "val": cat("val")}
+    if name in ("arxiv", "arxiv2000", "shakespeare-char"):
+        # the corpora with sources of their own (data/text_sources.py); token files placed by hand still win
+        from . import text_sources as TS
+
+        found = _existing_files(base / CORPORA[name].subdir, CORPORA[name])
+        if found is not None:
+            return found
+        if name == "shakespeare-char":
+            return TS.load_shakespeare_char(base)
+        return TS.load_arxiv(base, [2000] if name == "arxiv2000" else None)
     if name not in CORPORA:
         raise NotImplementedError(f"Unknow dataset key '{name}'")
     spec = CORPORA[name]

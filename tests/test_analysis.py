@@ -46,3 +46,32 @@ def test_lr_law_fit_recovers_shipped_coefficients():
     assert compute_lr("enoki", "adamw", 63_705_728 * 36, kappa=0.85, batch_size=64) > 0
     point, samples = A.bootstrap_lr_law(sizes, lr * np.exp(np.random.default_rng(0).normal(0, 0.02, len(sizes))), n_boot=20)
     assert len(samples) > 5 and abs(point[2] - d) < 0.1
+
+
+def test_figure_scripts_write_svg(tmp_path):
+    """The figure scripts draw from files this framework writes (metrics.jsonl, the theory generators' JSON)."""
+    import json
+
+    import numpy as np
+
+    from adana_b200 import figures as F
+    from adana_b200.theory import generate as G
+
+    exp = tmp_path / "run"
+    exp.mkdir()
+    rows = [{"iter": i, "tokens": 1000 * i, "val/loss": 5.0 - 0.3 * np.log(i)} for i in range(1, 40)]
+    (exp / "metrics.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    a = F.main(["curves", str(exp), "--out", str(tmp_path / "curves.svg")])
+    b = F.main(["compute", f"{exp}:1.5e8", "--out", str(tmp_path / "compute.svg")])
+    P = np.array([2e7, 6e7, 1.5e8, 4e8, 1e9])
+    (tmp_path / "sizes.json").write_text(json.dumps({"P": P.tolist(), "lr": (12.5 * (2.4e4 + P) ** -0.51).tolist()}))
+    c = F.main(["lr-law", str(tmp_path / "sizes.json"), "--out", str(tmp_path / "law.svg")])
+    G.main(["hummingbird", "--v", "100", "--d", "24", "--m", "4", "--steps", "60", "--kappa_step", "1.0",
+            "--out", str(tmp_path / "h.json")])
+    d = F.main(["hummingbird", str(tmp_path / "h.json"), "--out", str(tmp_path / "h.svg")])
+    G.main(["taustats", "--v", "100", "--d", "24", "--m", "8", "--steps", "70", "--out", str(tmp_path / "t.json")])
+    e = F.main(["taustats", str(tmp_path / "t.json"), "--out", str(tmp_path / "t.svg")])
+    for f in (a, b, c, d, e):
+        text = f.read_text()
+        assert text.startswith("<svg") and "<polyline" in text and text.rstrip().endswith("</svg>")
+    assert "-0.51" in c.read_text()          # the fitted exponent is in the title

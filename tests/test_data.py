@@ -175,3 +175,41 @@ def test_multi_file_reader_equals_the_reference_reader(ref_src, monkeypatch, tmp
         x = a.sample_batch()[0]
         assert torch.equal(x, b.sample_batch()[0]) and torch.equal(x, a2.sample_batch()[0]) and torch.equal(x, b2.sample_batch()[0])
     capsys.readouterr()
+
+
+def test_arxiv_and_shakespeare_preparers_run_from_local_sources(tmp_path):
+    """The corpora with their own sources: a year's tar archive of LaTeX papers -> Markdown -> tokens dealt 7/2/1 by
+    position, and the character-level Shakespeare split 90/10 by lines; offline they start from local files."""
+    import io
+    import tarfile
+    import types
+
+    from adana_b200.data import text_sources as TS
+    from adana_b200.data.datasets import get_dataset
+
+    root = tmp_path / "arxiv"
+    root.mkdir()
+    with tarfile.open(root / "hep-th-2000.tar.gz", "w:gz") as tar:
+        for i in range(10):
+            body = (f"% a comment\n\\documentclass{{article}}\\begin{{document}}\\section{{Paper {i}}} We study $x_{i}$ "
+                    f"\\cite{{foo}} in detail.\\end{{document}}\n").encode()
+            info = tarfile.TarInfo(f"2000/00010{i:02d}")
+            info.size = len(body)
+            tar.addfile(info, io.BytesIO(body))
+    assert "comment" not in TS.strip_latex("text % comment\n\\cite{a} more") and "more" in TS.strip_latex("\\cite{a} more")
+    out = TS.load_arxiv(tmp_path, [2000], encode=lambda s: [ord(c) % 251 for c in s])
+    assert len(list((root / "md" / "2000").iterdir())) == 10
+    n_train, n_val = len(out["train"]), len(out["val"])
+    n_test = len(np.memmap(root / "2000" / "test.npy", dtype=np.uint16, mode="r"))
+    assert n_train > n_val > n_test > 0 and abs(n_train / (n_val / 2) - 7) < 1.5      # 7 : 2 : 1 papers
+    with pytest.raises(ValueError):
+        TS.load_arxiv(tmp_path, [1992])
+
+    sh = tmp_path / "shakespeare"
+    sh.mkdir()
+    (sh / "raw.txt").write_text("".join(f"line {i}: to be or not to be\n" for i in range(50)))
+    args = types.SimpleNamespace(dataset="shakespeare-char", datasets_dir=str(tmp_path), vocab_size=50304)
+    d = get_dataset(args)
+    vocab = (sh / "vocab.txt").read_text().split()
+    assert len(d["train"]) > 8 * len(d["val"]) > 0 and int(max(d["train"].max(), d["val"].max())) == len(vocab) - 1
+    assert chr(int(vocab[int(d["train"][0])])) == "l"
