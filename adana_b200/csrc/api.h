@@ -191,6 +191,20 @@ int adana_attn_bwd(const void* dout, const void* q, const void* k, long long ldv
 
 // ---- utility -------------------------------------------------------------------------------------
 int adana_cast_f32_to_bf16(const float* src, void* dst, long long n, void* stream);
+// ---- distributed Muon chain (muon_chain.cu) ----------------------------------------------------------------------
+// Segment tables are device arrays of 32-byte entries {int64 a, b; int32 kind, group; float shape_factor; int32 mat}.
+int adana_muon_parts(void);
+int adana_muon_momentum(const float* g, float* buf, void* ns_out, const void* segs, int n_segs, const float* clip,
+                        float gscale, float mu, int nesterov, float* parts, void* stream);
+int adana_muon_pull(const unsigned long long* staged_ptrs, const unsigned long long* parts_ptrs, int world,
+                    long long shard_len, long long off, long long n, int mat, float eps, void* X, const void* flags,
+                    unsigned int seq, unsigned long long timeout_ns, int* status, void* stream);
+int adana_muon_push(const void* X, const unsigned long long* upd_ptrs, int world, long long shard_len, long long off,
+                    long long n, void* stream);
+int adana_muon_apply(float* p, const float* g, const void* upd, float* m1, float* m2, const void* segs, int n_segs,
+                     const float* hyper, const float* clip, const unsigned long long* weight_ptrs, int n_dst,
+                     long long push_off, long long max_seg_len, const void* flags, unsigned int seq, int world,
+                     unsigned long long timeout_ns, int* status, void* stream);
 int adana_version(void);
 
 // ---- attention JVP (attention_jvp_tcgen05.cu) ---------------------------------------------------

@@ -20,7 +20,7 @@ import torch
 # compute with their extents and report through the status word (csrc/common.cuh)
 DEBUG_BUILD = os.environ.get("ADANA_DEBUG", "0") not in ("", "0")
 _LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / ("libadana_b200_debug.so" if DEBUG_BUILD else "libadana_b200.so")
-_DEBUG_UNITS = ("misc", "rope", "attention", "norm", "optim", "comm", "gemm", "attention_jvp")
+_DEBUG_UNITS = ("misc", "rope", "attention", "norm", "optim", "comm", "gemm", "attention_jvp", "muon")
 _lib = None
 _status = {}
 
@@ -83,6 +83,11 @@ def _declare(lib):
         "adana_opt_step": [P, P, P, P, P, P, L, POINTER(AdanaOptHyper), P, P, P],
         "adana_sumsq_f32": [P, L, P, P],
         "adana_cast_f32_to_bf16": [P, P, L, P],
+        "adana_muon_parts": [],
+        "adana_muon_momentum": [P, P, P, P, I, P, F, F, I, P, P],
+        "adana_muon_pull": [P, P, I, L, L, L, I, F, P, P, ctypes.c_uint, ctypes.c_ulonglong, P, P],
+        "adana_muon_push": [P, P, I, L, L, L, P],
+        "adana_muon_apply": [P, P, P, P, P, P, I, P, P, P, I, L, L, P, ctypes.c_uint, I, ctypes.c_ulonglong, P, P],
         "adana_version": [],
     }
     for name, args in sigs.items():
@@ -102,7 +107,7 @@ class _CountingLibrary:
 
     def __getattr__(self, name):
         fn = getattr(self._cdll, name)  # AttributeError for a missing symbol keeps hasattr() honest
-        if name in ("adana_version", "adana_gemm_set_mode"):   # host-only entry points launch nothing
+        if name in ("adana_version", "adana_gemm_set_mode", "adana_muon_parts"):   # host-only entry points launch nothing
             self.__dict__[name] = fn
             return fn
 

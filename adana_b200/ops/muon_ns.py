@@ -27,18 +27,29 @@ def supported(G: torch.Tensor) -> bool:
             and G.dtype in (torch.bfloat16, torch.float32, torch.float16))
 
 
-def newton_schulz5_cuda(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+def ns_chain(X: torch.Tensor, Y: torch.Tensor, A: torch.Tensor, B: torch.Tensor, steps: int = 5) -> torch.Tensor:
+    """`steps` quintic iterations on X [m, n] (bf16, contiguous, Frobenius norm <= 1) without any transpose in memory.
+    Y has X's shape, A and B are [s, s] with s = min(m, n).  A wide matrix (m <= n) iterates X <- (bA + cA^2) X + aX
+    with A = X X^T; a tall one uses the Gram matrix of the other side, A = X^T X (read MN-major by the GEMM) and
+    X <- X (bA + cA^2) + aX, which is the same map applied to X^T.  Returns whichever of X / Y holds the result."""
     a, b, c = NS_COEFFS
-    tall = G.size(0) > G.size(1)
-    X = (G.T if tall else G).to(torch.bfloat16)
-    X = (X / (X.norm() + eps)).contiguous()
     m, n = X.shape
-    Y = torch.empty_like(X)
-    A = torch.empty((m, m), dtype=torch.bfloat16, device=X.device)
-    B = torch.empty_like(A)
     for _ in range(steps):
-        gemm(X, X, A, M=m, N=m, K=n, epi=EPI_BF16)
-        gemm(A, A, B, M=m, N=m, K=m, epi=EPI_AXPBY_BF16, R=A, alpha=c, beta=b)
-        gemm(B, X, Y, M=m, N=n, K=m, b_mn=True, epi=EPI_AXPBY_BF16, R=X, alpha=1.0, beta=a)
+        if m <= n:
+            gemm(X, X, A, M=m, N=m, K=n, epi=EPI_BF16)
+            gemm(A, A, B, M=m, N=m, K=m, epi=EPI_AXPBY_BF16, R=A, alpha=c, beta=b)
+            gemm(B, X, Y, M=m, N=n, K=m, b_mn=True, epi=EPI_AXPBY_BF16, R=X, alpha=1.0, beta=a)
+        else:
+            gemm(X, X, A, M=n, N=n, K=m, a_mn=True, b_mn=True, epi=EPI_BF16)
+            gemm(A, A, B, M=n, N=n, K=n, epi=EPI_AXPBY_BF16, R=A, alpha=c, beta=b)
+            gemm(X, B, Y, M=m, N=n, K=n, epi=EPI_AXPBY_BF16, R=X, alpha=1.0, beta=a)
         X, Y = Y, X
-    return X.T if tall else X
+    return X
+
+
+def newton_schulz5_cuda(G: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    X = G.to(torch.bfloat16)
+    X = (X / (X.norm() + eps)).contiguous()
+    s = min(X.shape)
+    A = torch.empty((s, s), dtype=torch.bfloat16, device=X.device)
+    return ns_chain(X, torch.empty_like(X), A, torch.empty_like(A), steps)

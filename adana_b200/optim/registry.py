@@ -23,11 +23,12 @@ def build_optimizer(args, model, group_specs, engine=None):
 
     if engine is not None and args.opt in FUSED_OPTS and not getattr(args, "no_fused_optimizer", False):
         return EngineOptimizer(engine, args.opt, args, group_specs)
-    if engine is not None and engine.sharded:
-        if args.opt == "d-muon":
-            from ..parallel.dist_muon import ShardedMuon
+    if engine is not None and args.opt == "d-muon" and (engine.sharded or engine.world == 1):
+        # gather -> Newton-Schulz -> scatter on the engine's flat buffers (a kernel chain on a GPU), also on one rank
+        from ..parallel.dist_muon import ShardedMuon
 
-            return ShardedMuon(engine, args, group_specs)
+        return ShardedMuon(engine, args, group_specs)
+    if engine is not None and engine.sharded:
         # every other name: its per-tensor class on views of this rank's shards (element-wise updates) or on whole
         # tensors kept by one owner rank each (updates that look at a matrix or a per-tensor norm)
         from .sharded_adapters import ELEMENTWISE, OwnerOptimizer, ShardViewOptimizer

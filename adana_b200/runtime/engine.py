@@ -221,7 +221,8 @@ class Engine:
         if self.world > 8 or not _lib.has("adana_p2p_reduce_scatter_flag"):
             return None
         # per unit: fp32 gradients (4) + bf16 weights (2) + bf16 wire copy of the gradients (2) + fp32 norm weights
-        nbytes = sum(l.padded * 8 + l.numel * 4 + 4096 for l in self.layouts)
+        # plus 64 KiB for small tables of optimizers that talk over the plane (distributed Muon's partial norms)
+        nbytes = sum(l.padded * 8 + l.numel * 4 + 4096 for l in self.layouts) + (1 << 16)
         plane, err = None, None
         try:
             from ..parallel.p2p import P2PPlane

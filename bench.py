@@ -214,6 +214,8 @@ def run_ours(a):
         x, y = train_reader.sample_batch()
         dev_batches.append((x.to(args.device), y.to(args.device)))
 
+    if getattr(backend, "engine", None) is not None:
+        backend.engine.report_aux = False      # nothing logs in the timed steps (log_interval 0), as in Trainer.train_step
     phase_marks = []       # per timed step: events after (last backward launched, clip, optimizer step)
 
     def step_device(i, mark=False):

@@ -41,3 +41,24 @@ def torchrun(nproc: int):
     (binding a port, closing it and handing the number on races with every other test that does the same)."""
     return [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
             "--nproc-per-node", str(nproc)]
+
+
+@pytest.fixture(autouse=True)
+def _checked_build_status_stays_clear(request):
+    """Under the checked build (ADANA_DEBUG=1) every kernel compares the indices it computes with the extents it was
+    given and reports a violation through the device status word: after each GPU test on valid inputs the word must
+    still be 0 (tests of the bounded waits read and clear the word themselves)."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    from adana_b200.ops import _lib
+
+    if not _lib.DEBUG_BUILD:
+        return
+    import torch
+
+    if torch.cuda.is_available():
+        buf = _lib.status_buffer()
+        code = int(buf[0].item())
+        buf.zero_()
+        assert code == 0, f"checked build recorded status {_lib.STATUS_NAMES.get(code, code)}"

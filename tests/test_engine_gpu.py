@@ -166,3 +166,54 @@ def test_batch_stager_waits_for_queued_readers_of_a_slot():
         torch.cuda.synchronize()
         assert int(snap_x.min()) == 0 and int(snap_x.max()) == 0, lookahead
         assert int(snap_y.min()) == 1000 and int(snap_y.max()) == 1000, lookahead
+
+
+def test_distributed_muon_kernel_chain_matches_the_torch_path_on_one_gpu():
+    """`--opt d-muon` on the GPU engine: momentum, pull + normalise, Newton-Schulz, push and apply as kernels, against the
+    same optimizer with the kernel chain switched off (torch ops around the same Newton-Schulz GEMMs)."""
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.dist_muon import ShardedMuon
+    from adana_b200.runtime.engine import attach
+
+    results = {}
+    for chain in (True, False):
+        a, ref, _ = _models("enoki")
+        a.dtype, a.device, a.opt = "bfloat16", "cuda:0", "d-muon"
+        a.lr, a.weight_decay, a.momentum, a.nesterov, a.muon_ns_steps, a.beta1, a.beta2 = 2e-3, 0.1, 0.9, True, 5, 0.8, 0.99
+        m = ref.to("cuda:0")
+        eng = attach(m, a, device="cuda:0", sharded=True)
+        specs = m.get_parameter_group_specs()
+        for g in specs:
+            g["param_names"] = g["params"]
+        opt = ShardedMuon(eng, a, specs)
+        assert opt.chain is not None
+        if not chain:
+            opt.chain = None
+        init = {k: v.clone() for k, v in eng.full_param_dict("master").items()}
+        m.train()
+        gen = torch.Generator().manual_seed(3)
+        before = _lib.launch_count()
+        ls = []
+        for _ in range(4):
+            idx = torch.randint(0, a.vocab_size, (4, 128), generator=gen).to("cuda:0")
+            out = m(idx, targets=idx.roll(-1, 1))
+            out["loss"].backward()
+            eng.grad_norm_and_clip(0.5)
+            opt.step()
+            opt.zero_grad()
+            ls.append(out["loss"].item())
+        torch.cuda.synchronize()
+        _lib.check_status()
+        results[chain] = (ls, init, eng.full_param_dict("master"), _lib.launch_count() - before,
+                          {k: v.clone() for k, v in eng.units[0].state.items()})
+    ls_k, init, p_k, _, st_k = results[True]
+    ls_t, _, p_t, _, st_t = results[False]
+    assert ls_k[-1] < ls_k[0]
+    for x, y in zip(ls_k, ls_t):
+        assert abs(x - y) / y < 1e-2, (ls_k, ls_t)
+    for k in p_t:
+        moved = (p_t[k] - init[k]).abs().mean().item()
+        diff = (p_k[k] - p_t[k]).abs().mean().item()
+        assert moved > 0 and diff < 0.05 * moved, (k, diff, moved)
+    for k in ("muon_buffer", "adamw_exp_avg", "adamw_exp_avg_sq"):
+        assert torch.allclose(st_k[k], st_t[k], rtol=2e-2, atol=1e-6), k

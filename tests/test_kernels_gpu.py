@@ -621,3 +621,95 @@ def test_gather_gemm_reads_row_sharded_weights_in_place(world, rps):
         cut = [w[a:b].clone() for a, b in zip(starts, starts[1:])]
         assert torch.equal(gemm.linear_fwd_gathered(x, cut, row_starts=starts), y)
         assert rel_err(gemm.linear_dgrad_gathered(dy, cut, None, K, row_starts=starts), dy.float() @ w.float()) < 8e-3
+
+
+def test_muon_chain_kernels_with_fake_peers():
+    """The four kernels around the Newton-Schulz GEMMs of distributed Muon, with four "ranks" that are buffers on one
+    GPU (no flag waits: the launches run one after the other): momentum + staging + partial norms, pull + normalise,
+    push to the holders, apply + weight push; against plain PyTorch in fp32."""
+    import ctypes
+
+    import numpy as np
+
+    from adana_b200.parallel.dist_muon import SEG_DTYPE, _u64
+
+    lib = _lib.lib()
+    torch.manual_seed(11)
+    world, parts_n = 4, int(lib.adana_muon_parts())
+    slots = [("m0", (64, 96), 0, True), ("m1", (128, 64), 6144, True), ("vec", (100,), 14336, False)]
+    padded = 14592
+    shard = padded // world
+    g = torch.randn(padded, device=DEV) * 0.1
+    buf = torch.randn(padded, device=DEV) * 0.1
+    p = torch.randn(padded, device=DEV)
+    m1, m2 = torch.rand(padded, device=DEV) * 0.1, torch.rand(padded, device=DEV) * 0.01
+    clip = torch.tensor([0.7, 0.0], device=DEV)
+    gscale, mu, lr, wd, rms = 0.25, 0.9, (1e-2, 2e-2), (0.1, 0.0), 0.2
+    b1, b2, eps, bias = 0.8, 0.99, 1e-8, 0.5
+    stat = _lib.status_buffer(DEV).data_ptr()
+    st = _lib.stream_ptr()
+    # per-rank state
+    ns = [torch.zeros(padded, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    upd = [torch.zeros(padded, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    wts = [torch.zeros(padded, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+    parts = [torch.full((2 * parts_n,), 7.0, device=DEV) for _ in range(world)]
+    gs, bs, ps, m1s, m2s, tables = [], [], [], [], [], []
+    for r in range(world):
+        lo, hi = r * shard, (r + 1) * shard
+        rows = []
+        for i, (_, shape, off, decay) in enumerate(slots):
+            n = int(np.prod(shape))
+            a, b = max(off, lo), min(off + n, hi)
+            if len(shape) == 2:
+                a, b = (a - lo, b - lo) if a < b else (0, 0)
+                rows.append((a, b, 0, 0 if decay else 1, rms * max(shape) ** 0.5, i))
+            elif a < b:
+                rows.append((a - lo, b - lo, 1, 0 if decay else 1, 0.0, 0))
+        t = torch.from_numpy(np.array(rows, dtype=SEG_DTYPE).view(np.uint8).copy()).to(DEV)
+        tables.append((t, len(rows), max(x[1] - x[0] for x in rows)))
+        gs.append(g[lo:hi].clone()); bs.append(buf[lo:hi].clone()); ps.append(p[lo:hi].clone())
+        m1s.append(m1[lo:hi].clone()); m2s.append(m2[lo:hi].clone())
+        _lib.check_rc(lib.adana_muon_momentum(gs[r].data_ptr(), bs[r].data_ptr(), ns[r].data_ptr() + 2 * lo, t.data_ptr(), 2,
+                                              clip.data_ptr(), gscale, mu, 1, parts[r].data_ptr(), st), "momentum")
+    geff = g * gscale * 0.7
+    buf_ref = mu * buf + geff
+    ns_ref = (geff + mu * buf_ref).bfloat16()
+    for i, (_, shape, off, _) in enumerate(slots[:2]):
+        n = shape[0] * shape[1]
+        assert_close(torch.cat(bs)[off:off + n], buf_ref[off:off + n], 1e-5, 1e-6, "momentum buffer")
+        X = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+        _lib.check_rc(lib.adana_muon_pull(_u64([t.data_ptr() for t in ns]), _u64([t.data_ptr() for t in parts]), world, shard,
+                                          off, n, i, 1e-7, X.data_ptr(), 0, 0, 0, stat, st), "pull")
+        want = ns_ref[off:off + n].float()
+        want = want / (want.norm() + 1e-7)
+        assert_close(X.float(), want, 1e-2, 1e-5, "pulled and normalised matrix")
+        _lib.check_rc(lib.adana_muon_push(X.data_ptr(), _u64([t.data_ptr() for t in upd]), world, shard, off, n, st), "push")
+    hyper = (ctypes.c_float * 9)(lr[0], lr[1], wd[0], wd[1], b1, b2, eps, bias, gscale)
+    for r in range(world):
+        lo = r * shard
+        t, n_segs, longest = tables[r]
+        _lib.check_rc(lib.adana_muon_apply(ps[r].data_ptr(), gs[r].data_ptr(), upd[r].data_ptr() + 2 * lo, m1s[r].data_ptr(),
+                                           m2s[r].data_ptr(), t.data_ptr(), n_segs, hyper, clip.data_ptr(),
+                                           _u64([w.data_ptr() for w in wts]), world, lo, longest, 0, 0, world, 0, stat, st), "apply")
+    torch.cuda.synchronize()
+    _lib.check_status()
+    got = torch.cat(ps)
+    want_p = p.clone()
+    for i, (_, shape, off, _) in enumerate(slots[:2]):
+        n = shape[0] * shape[1]
+        x = ns_ref[off:off + n].float()
+        x = (x / (x.norm() + 1e-7)).bfloat16().float()
+        want_p[off:off + n] = p[off:off + n] * (1 - lr[0] * wd[0]) - lr[0] * rms * max(shape) ** 0.5 * x
+    off, n = slots[2][2], 100
+    ge = geff[off:off + n]
+    a = m1[off:off + n] + (1 - b1) * (ge - m1[off:off + n])
+    b = m2[off:off + n] + (1 - b2) * (ge * ge - m2[off:off + n])
+    want_p[off:off + n] = p[off:off + n] * (1 - lr[1] * wd[1]) - lr[1] / bias * a / (eps + b.sqrt())
+    used = torch.zeros(padded, dtype=torch.bool, device=DEV)
+    for _, shape, off, _ in slots:
+        used[off:off + int(np.prod(shape))] = True
+    assert_close(got[used], want_p[used], 1e-2, 1e-4, "updated parameters")
+    assert torch.equal(got[~used], p[~used])                                   # padding is never touched
+    assert_close(torch.cat(m1s)[off:off + n], a, 1e-5, 1e-7, "AdamW first moment")
+    for w in wts:                                                              # every rank received every new weight
+        assert torch.equal(w[used], got[used].bfloat16())

@@ -272,3 +272,63 @@ def test_gathered_weights_over_peers_match_resident_weights():
         d = (_t(res["gathered"][0]["params"][k]) - _t(v)).abs()
         assert d.mean().item() < 2e-4 and d.max().item() < 2e-2, (k, d.mean().item(), d.max().item())
         assert torch.equal(_t(res["gathered"][0]["params"][k]), _t(res["gathered"][1]["params"][k]))
+
+
+def _muon_worker(rank, world, plane):
+    import torch.distributed as dist
+
+    from conftest import tiny_args
+    from adana_b200.models.utils import get_model
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.comm import Comm
+    from adana_b200.parallel.dist_muon import ShardedMuon
+    from adana_b200.runtime.engine import attach
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    a = tiny_args("qwen3", n_embd=256, n_head=4, n_kv_head=2, mlp_hidden_dim=512, sequence_length=128, vocab_size=1024,
+                  opt="d-muon", lr=2e-3, weight_decay=0.1, momentum=0.9, nesterov=True, muon_ns_steps=5, beta1=0.8,
+                  beta2=0.99, acc_steps=1, dtype="bfloat16", device=f"cuda:{rank}", fsdp_comm=plane)
+    torch.manual_seed(0)
+    m = get_model(a).to(a.device)
+    eng = attach(m, a, comm=Comm(), sharded=True, device=a.device)
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = ShardedMuon(eng, a, specs)
+    assert (opt.chain is not None) == (plane == "p2p")
+    m.train()
+    losses = []
+    for step in range(4):
+        g = torch.Generator().manual_seed(1000 * step + rank)
+        idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g).to(a.device)
+        out = m(idx, targets=idx.roll(-1, 1))
+        out["loss"].backward()
+        eng.grad_norm_and_clip(0.5)
+        opt.step()
+        opt.zero_grad()
+        losses.append(out["loss"].item())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    full = eng.full_param_dict("master")
+    w0 = eng.units[0].weights.float().cpu()
+    return {"losses": losses, "params": {k: v.float().cpu() for k, v in full.items()}, "w0": w0}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_distributed_muon_chain_over_peers_matches_the_collective_path():
+    """`d-muon` under the sharded engine: owners pull their matrices over NVLink, orthogonalise and push the results to
+    the holders (kernel chain) against the all-gather / reduce-scatter fallback over NCCL; both on every GPU here."""
+    from test_distributed_cpu import _spawn, _t
+
+    world = min(torch.cuda.device_count(), 4)
+    res = {plane: _spawn(_muon_worker, world, plane) for plane in ("nccl", "p2p")}
+    for r in range(world):
+        assert res["p2p"][r]["losses"][-1] < res["p2p"][r]["losses"][0]
+        assert torch.equal(_t(res["p2p"][r]["w0"]), _t(res["p2p"][0]["w0"]))       # the pushed bf16 weights agree everywhere
+    for x, y in zip(res["nccl"][0]["losses"], res["p2p"][0]["losses"]):
+        assert abs(x - y) / x < 1e-2
+    for k, v in res["nccl"][0]["params"].items():
+        d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs().mean().item()
+        assert d < 3e-4, (k, d)
