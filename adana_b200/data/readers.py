@@ -28,7 +28,19 @@ import torch
 import torch.distributed as dist
 
 
+_DP_LAYOUT = None      # (data-parallel size, this process's data-parallel rank) when it differs from the process group's
+
+
+def set_data_parallel_layout(size: int, rank: int):
+    """Tensor parallelism: the ranks of one tp group must read the same batches, so readers shard the data over the
+    data-parallel replicas instead of over all processes.  `None, None` restores the default."""
+    global _DP_LAYOUT
+    _DP_LAYOUT = None if size is None else (int(size), int(rank))
+
+
 def _dist_info(auto_shard: bool):
+    if auto_shard and _DP_LAYOUT is not None:
+        return _DP_LAYOUT
     if auto_shard and dist.is_available() and dist.is_initialized():
         return dist.get_world_size(), dist.get_rank()
     return 1, 0

@@ -210,6 +210,13 @@ class FSDPBackend(_ProcessGroupBackend):
         self._is_fsdp = True
         self._torch_fsdp = False
         self.tp_mesh = self.dp_mesh = None
+        self.tp_group = self.dp_group = None
+        if self.tp_size > 1:
+            # rank = dp index * tp_size + tp index (the layout of a (dp, tp) device mesh); the ranks of one tp group work
+            # on the same batches
+            from ..data.readers import set_data_parallel_layout
+
+            set_data_parallel_layout(ws // self.tp_size, self.rank // self.tp_size)
 
     @property
     def dp_size(self):
@@ -218,8 +225,37 @@ class FSDPBackend(_ProcessGroupBackend):
     def all_ranks_checkpoint(self) -> bool:
         return True
 
+    def _make_groups(self):
+        """Process groups of the 2-D layout (every rank creates every group, in the same order)."""
+        ws, tp = self.get_world_size(), self.tp_size
+        for i in range(ws // tp):
+            ranks = list(range(i * tp, (i + 1) * tp))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                self.tp_group = g
+        for j in range(tp):
+            ranks = list(range(j, ws, tp))
+            g = dist.new_group(ranks)
+            if self.rank in ranks:
+                self.dp_group = g
+
     def transform_model(self, model):
-        if self.tp_size == 1 and self._maybe_attach_engine(model, self.args, sharded=True, comm=self.comm):
+        if self.tp_size == 1:
+            if self._maybe_attach_engine(model, self.args, sharded=True, comm=self.comm):
+                return model
+            return self._torch_fully_shard(model)
+        # dp x tp on the kernel engine: flat shards over the data-parallel group of this tp index, heads and hidden units
+        # cut over the tp group (parallel/tensor_parallel.py); models without a kernel path take DTensor plans + FSDP2
+        from ..parallel.tensor_parallel import check_divisible
+        from ..runtime.layout import engine_supported
+
+        if not getattr(self.args, "no_cuda_kernels", False) and engine_supported(model, self.args) is None:
+            check_divisible(model, self.tp_size)
+            self._make_groups()
+            from ..runtime.engine import attach
+
+            self.engine = attach(model, self.args, comm=Comm(self.dp_group), sharded=True, device=self.args.device,
+                                 tp_group=self.tp_group)
             return model
         return self._torch_fully_shard(model)
 

@@ -23,6 +23,12 @@ def build_optimizer(args, model, group_specs, engine=None):
 
     if engine is not None and args.opt in FUSED_OPTS and not getattr(args, "no_fused_optimizer", False):
         return EngineOptimizer(engine, args.opt, args, group_specs)
+    if engine is not None and getattr(engine, "tp", None) is not None:
+        from .sharded_adapters import WHOLE_TENSOR
+
+        if args.opt in WHOLE_TENSOR or args.opt == "d-muon":
+            raise ValueError(f"--opt {args.opt} looks at whole matrices, which --tp_size > 1 cuts into per-rank parts on the "
+                             f"kernel engine; use an element-wise optimizer or --tp_size 1")
     if engine is not None and args.opt == "d-muon" and (engine.sharded or engine.world == 1):
         # gather -> Newton-Schulz -> scatter on the engine's flat buffers (a kernel chain on a GPU), also on one rank
         from ..parallel.dist_muon import ShardedMuon

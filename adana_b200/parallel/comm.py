@@ -80,7 +80,9 @@ class Comm:
     def broadcast(self, t: torch.Tensor, src: int = 0):
         if self.world == 1:
             return None
-        return dist.broadcast(t, src=src, group=self.group)
+        if self.group is None:
+            return dist.broadcast(t, src=src, group=self.group)
+        return dist.broadcast(t, group=self.group, group_src=src)      # `src` counts inside this group
 
     def barrier(self):
         if self.world > 1:

@@ -1,4 +1,19 @@
-"""Tensor-parallel plans for the PyTorch path (2-D data x tensor parallel under `--tp_size`).
+"""Tensor parallelism (2-D data x tensor parallel under `--tp_size`): the kernel engine's own, and the DTensor plans of
+the PyTorch path.
+
+Kernel engine (`shard_model_for_tp`, `TensorParallelGroup`, used by runtime/engine.py and runtime/blocks.py).  The
+heads and the MLP hidden units are dealt to the tp ranks: the fused q|k|v projection and the first MLP matrix keep the
+rows of their own heads / hidden units (column-parallel: the output features are split), the attention output
+projection and the second MLP matrix keep the matching columns (row-parallel: every rank computes a partial
+product over its slice of the contraction).  Activations between blocks, norms, the embedding and the LM head are
+replicated over tp, as in the reference's plans.  Four sums over the tp ranks per block and micro-step remain: after
+the two row-parallel GEMMs in forward and after the dgrad GEMMs of the two column-parallel ones in backward.  On GPUs
+each is: the GEMM writes its bf16 partial product into a buffer in symmetric memory, one flag barrier, and every
+rank adds all ranks' partials in a fixed order (16-byte loads over NVLink) with the residual folded in - so the
+result is bitwise the same on every tp rank and the replicated state never drifts.  Two alternating buffers make one
+barrier per sum enough.  Elsewhere (CPU / Gloo, or no peer memory) the sum is a `torch.distributed` all-reduce.
+
+PyTorch path.
 
 Each model exposes `get_tp_plan()`: block-relative module path -> "colwise" | "rowwise"
 (column-parallel projections feed row-parallel ones, so one all-reduce follows each
@@ -15,6 +30,151 @@ owns (coalesced 16-byte loads over NVLink); two fused variants move the partial 
 row, so its remote accesses are 16-byte pieces.
 """
 from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+# block-relative parameter suffix -> ("rows", number of equal row groups that are each split) | ("cols", 1)
+TP_RULES = {
+    "enoki": {"attn.c_attn.weight": ("rows", 3), "attn.c_proj.weight": ("cols", 1),
+              "mlp.c_fc.weight": ("rows", 1), "mlp.c_proj.weight": ("cols", 1)},
+    "qwen3": {"attn.q_proj.weight": ("rows", 1), "attn.k_proj.weight": ("rows", 1), "attn.v_proj.weight": ("rows", 1),
+              "attn.o_proj.weight": ("cols", 1), "mlp.gate_proj.weight": ("rows", 1), "mlp.up_proj.weight": ("rows", 1),
+              "mlp.down_proj.weight": ("cols", 1)},
+}
+
+
+def tp_rule(arch: str, name: str) -> Optional[Tuple[str, int]]:
+    if ".h." not in name:
+        return None
+    for suffix, rule in TP_RULES.get(arch, {}).items():
+        if name.endswith(suffix):
+            return rule
+    return None
+
+
+def tp_slice(full: torch.Tensor, rule: Tuple[str, int], rank: int, size: int) -> torch.Tensor:
+    """This rank's part of a full matrix."""
+    kind, groups = rule
+    if kind == "cols":
+        n = full.shape[1] // size
+        return full[:, rank * n:(rank + 1) * n]
+    g = full.shape[0] // groups
+    n = g // size
+    return torch.cat([full[i * g + rank * n: i * g + (rank + 1) * n] for i in range(groups)], 0)
+
+
+def tp_unslice(pieces: List[torch.Tensor], rule: Tuple[str, int]) -> torch.Tensor:
+    """The full matrix from the ranks' parts (rank order)."""
+    kind, groups = rule
+    if kind == "cols":
+        return torch.cat(pieces, 1)
+    n = pieces[0].shape[0] // groups
+    return torch.cat([p[i * n:(i + 1) * n] for i in range(groups) for p in pieces], 0)
+
+
+def check_divisible(model, size: int):
+    cfg = model.config
+    n_kv = getattr(model.transformer.h[0].attn, "n_kv_head", cfg.n_head)
+    if cfg.n_head % size or n_kv % size:
+        raise ValueError(f"n_head={cfg.n_head} / n_kv_head={n_kv} is not divisible by tp_size={size}")
+    for name, p in model.named_parameters():
+        rule = tp_rule(model.arch, name)
+        if rule is not None:
+            extent = p.shape[1] if rule[0] == "cols" else p.shape[0] // rule[1]
+            if extent % size:
+                raise ValueError(f"{name}: extent {extent} is not divisible by tp_size={size}")
+
+
+def shard_model_for_tp(model, rank: int, size: int) -> Dict[str, Tuple[str, int]]:
+    """Replace every tensor-parallel block matrix of the module tree by this rank's part, in place.  Returns
+    name -> rule for the parameters that were cut (everything else stays replicated)."""
+    check_divisible(model, size)
+    cut = {}
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            rule = tp_rule(model.arch, name)
+            if rule is not None:
+                p.data = tp_slice(p.data, rule, rank, size).contiguous()
+                cut[name] = rule
+    return cut
+
+
+class TensorParallelGroup:
+    """The tp ranks of one data-parallel replica and the sums over them that a block needs."""
+
+    def __init__(self, group, device, cdt):
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.cdt = cdt
+        self.cut: Dict[str, Tuple[str, int]] = {}
+        self.plane = None
+        self._bufs = None
+        self._turn = 0
+        self._want_plane = self.device.type == "cuda" and cdt == torch.bfloat16
+
+    # ---- symmetric partial-product buffers (made at the first sum, when the activation extent is known) ---------
+    def _ensure_plane(self, M: int, N: int):
+        if self._bufs is False or not self._want_plane:
+            return False
+        if self._bufs is not None and self._bufs[0].shape[0] >= M and self._bufs[0].shape[1] == N:
+            return True
+        from ..ops import _lib
+        from .p2p import P2PPlane
+
+        plane = None
+        try:
+            if _lib.has("adana_p2p_reduce_scatter_bf16"):
+                plane = P2PPlane.create(2 * M * N * 2 + 4096, self.device, group=self.group)
+        except Exception:
+            plane = None
+        ok = torch.tensor([0.0 if plane is None else 1.0], device=self.device)
+        dist.all_reduce(ok, group=self.group)
+        if int(ok.item()) != self.size:
+            self._bufs = False          # every rank takes the same route
+            return False
+        self.plane = plane
+        self._bufs = [plane.alloc(M * N, torch.bfloat16).view(M, N) for _ in range(2)]
+        self._ptrs = [plane.peer_ptrs(b) for b in self._bufs]
+        return True
+
+    def sum_partials(self, produce, M: int, N: int, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 [M, N] = (resid or 0) + sum over tp ranks of the [M, N] product that `produce(out)` computes (into `out`
+        when given a buffer, else returned)."""
+        if self._ensure_plane(M, N):
+            from ..ops import gemm
+
+            i = self._turn
+            self._turn ^= 1
+            part = self._bufs[i][:M]
+            produce(part)
+            self.plane.barrier()          # every rank's partial is complete (and nobody still reads the other buffer's turn)
+            out = torch.empty((M, N), dtype=torch.float32, device=self.device)
+            return gemm.reduce_scatter_partials(self._ptrs[i], 0, M, N, N, out, resid=resid)
+        part = produce(None).float()
+        dist.all_reduce(part, group=self.group)
+        return part if resid is None else part.add_(resid)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def gather_full(self, name: str, local: torch.Tensor) -> torch.Tensor:
+        """Full tensor of a parameter-shaped value from every tp rank's part (collective); replicated ones pass."""
+        rule = self.cut.get(name)
+        if rule is None:
+            return local
+        pieces = [torch.empty_like(local) for _ in range(self.size)]
+        dist.all_gather(pieces, local.contiguous(), group=self.group)
+        return tp_unslice(pieces, rule)
+
+    def local_part(self, name: str, full: torch.Tensor) -> torch.Tensor:
+        rule = self.cut.get(name)
+        return full if rule is None else tp_slice(full, rule, self.rank, self.size)
 
 
 def apply_tensor_parallel(model, tp_mesh) -> None:

@@ -75,22 +75,48 @@ class BlockSpec:
         return self.nq + 2 * self.nkv
 
 
+def _row_parallel_resid(tp, a, w, resid, alpha):
+    """resid + alpha * sum over tp ranks of a_r · w_rᵀ (each rank holds a slice of the contraction)."""
+    M, N = a.shape[0], w.shape[0]
+
+    def produce(out):
+        if out is None:
+            return (a.float() @ w.float().t()) * alpha
+        return G.gemm(a, w, out, M=M, N=N, K=a.shape[1], alpha=alpha)
+
+    return tp.sum_partials(produce, M, N, resid=resid)
+
+
+def _col_parallel_dgrad(tp, dy, w):
+    """sum over tp ranks of dy_r · w_r: the input gradient of a column-parallel linear."""
+    M, K = dy.shape[0], w.shape[1]
+
+    def produce(out):
+        if out is None:
+            return dy.float() @ w.float()
+        return G.linear_dgrad(dy, w, out=out)
+
+    return tp.sum_partials(produce, M, K)
+
+
 def block_forward(x, W: Dict[str, torch.Tensor], sp: BlockSpec, freqs, B: int, S: int, cdt,
-                  need_grad: bool = True):
-    """x fp32 [T, d] -> (x_out fp32 [T, d], saved dict or None)."""
+                  need_grad: bool = True, tp=None):
+    """x fp32 [T, d] -> (x_out fp32 [T, d], saved dict or None).  With `tp` (a TensorParallelGroup) the weights are this
+    rank's slices, `sp` counts its heads and hidden units, and the two row-parallel products are summed over tp."""
     ln1, mean1, rstd1 = N.norm_fwd(x, W["ln_1"], sp.eps, sp.norm_kind, cdt)
     qkv = G.linear_fwd(ln1, W["qkv"])
     q, k = R.qknorm_rope_fwd(qkv, 0, sp.q_hstride, sp.k_off, sp.hd, W.get("q_norm"), W.get("k_norm"),
                              freqs, S, sp.n_head, sp.n_kv_head, sp.hd, sp.qk_eps, sp.qk_kind)
     y, actx = A.attention_fwd(q, k, qkv, sp.v_off, sp.hd, B, S, need_grad=need_grad)
     yg = M.sigmoid_gate_fwd(y, qkv, sp.hd, sp.q_hstride, sp.n_head, sp.hd) if sp.gate else y
-    x_mid = G.linear_resid_fwd(yg, W["o"], x, alpha=sp.scale)
+    x_mid = G.linear_resid_fwd(yg, W["o"], x, alpha=sp.scale) if tp is None else _row_parallel_resid(tp, yg, W["o"], x, sp.scale)
     ln2, mean2, rstd2 = N.norm_fwd(x_mid, W["ln_2"], sp.eps, sp.norm_kind, cdt)
     if sp.mlp_kind == "gelu":
         z, h = G.linear_gelu_fwd(ln2, W["fc"])
     else:
         z, h = G.linear_swiglu_fwd(ln2, W["fc"])
-    x_out = G.linear_resid_fwd(h, W["down"], x_mid, alpha=sp.scale)
+    x_out = (G.linear_resid_fwd(h, W["down"], x_mid, alpha=sp.scale) if tp is None
+             else _row_parallel_resid(tp, h, W["down"], x_mid, sp.scale))
     if not need_grad:
         return x_out, None
     saved = dict(x=x, ln1=ln1, mean1=mean1, rstd1=rstd1, qkv=qkv, q=q, k=k, y=y, yg=yg, actx=actx,
@@ -99,7 +125,7 @@ def block_forward(x, W: Dict[str, torch.Tensor], sp: BlockSpec, freqs, B: int, S
 
 
 def block_backward(dx, dx_lp, sv, W, Gd: Dict[str, torch.Tensor], sp: BlockSpec, freqs, B: int, S: int,
-                   acc: bool):
+                   acc: bool, tp=None):
     """dx (fp32, grad w.r.t. the block output) is updated in place to the grad w.r.t. the block
     input; dx_lp is its compute-dtype copy (also updated).  Weight grads go to `Gd` (fp32 views),
     accumulated when `acc` else overwritten."""
@@ -111,7 +137,7 @@ def block_backward(dx, dx_lp, sv, W, Gd: Dict[str, torch.Tensor], sp: BlockSpec,
         dz = G.linear_dgrad_dswiglu(dx_lp, W["down"], sv["z"], alpha=s)
     G.linear_wgrad(dx_lp, sv["h"], out=Gd["down"], accumulate=acc, alpha=s)
     G.linear_wgrad(dz, sv["ln2"], out=Gd["fc"], accumulate=acc)
-    dln2 = G.linear_dgrad(dz, W["fc"])
+    dln2 = G.linear_dgrad(dz, W["fc"]) if tp is None else _col_parallel_dgrad(tp, dz, W["fc"])
     del dz
     N.norm_bwd(dln2, sv["x_mid"], W["ln_2"], sv["mean2"], sv["rstd2"], sp.norm_kind, dx_accum=dx,
                dw_out=Gd["ln_2"], dw_accumulate=acc, dx_lowp=dx_lp)
@@ -130,6 +156,9 @@ def block_backward(dx, dx_lp, sv, W, Gd: Dict[str, torch.Tensor], sp: BlockSpec,
                                  W.get("k_norm"), freqs, S, sp.n_head, sp.n_kv_head, sp.hd, sp.qk_eps,
                                  sp.qk_kind)
     if dwq is not None:
+        if tp is not None:          # the per-head norm weights are shared by all heads: their gradient sums over tp
+            both = tp.all_reduce_(torch.cat([dwq.reshape(-1), dwk.reshape(-1)]))
+            dwq, dwk = both[:dwq.numel()].view_as(dwq), both[dwq.numel():].view_as(dwk)
         for key, val in (("q_norm", dwq), ("k_norm", dwk)):
             if acc:
                 Gd[key] += val
@@ -137,7 +166,7 @@ def block_backward(dx, dx_lp, sv, W, Gd: Dict[str, torch.Tensor], sp: BlockSpec,
                 Gd[key].copy_(val)
     del dq, dk, dy, dyg
     G.linear_wgrad(dqkv, sv["ln1"], out=Gd["qkv"], accumulate=acc)
-    dln1 = G.linear_dgrad(dqkv, W["qkv"])
+    dln1 = G.linear_dgrad(dqkv, W["qkv"]) if tp is None else _col_parallel_dgrad(tp, dqkv, W["qkv"])
     del dqkv
     N.norm_bwd(dln1, sv["x"], W["ln_1"], sv["mean1"], sv["rstd1"], sp.norm_kind, dx_accum=dx,
                dw_out=Gd["ln_1"], dw_accumulate=acc, dx_lowp=dx_lp)

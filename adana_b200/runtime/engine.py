@@ -131,7 +131,7 @@ class EngineConfig:
 
 class Engine:
     def __init__(self, model, cfg, comm: Optional[Comm] = None, sharded: bool = True,
-                 device=None, compute_dtype: Optional[torch.dtype] = None):
+                 device=None, compute_dtype: Optional[torch.dtype] = None, tp_group=None):
         reason = engine_supported(model, cfg)
         if reason is not None:
             raise ValueError(f"kernel engine unavailable: {reason}")
@@ -162,6 +162,17 @@ class Engine:
 
             _att.set_mode(cfg.attention)
 
+        # tensor parallelism: `comm` is then the data-parallel group of this rank's tp index, and the module tree is
+        # cut down to this rank's heads and hidden units before the flat layout is made
+        self.tp = None
+        if tp_group is not None and torch.distributed.get_world_size(tp_group) > 1:
+            from ..parallel.tensor_parallel import TensorParallelGroup, shard_model_for_tp
+
+            with torch.no_grad():
+                for p in model.parameters():        # every rank cuts the same initialisation: global rank 0's
+                    torch.distributed.broadcast(p.data, src=0)
+            self.tp = TensorParallelGroup(tp_group, self.device, self.cdt)
+            self.tp.cut = shard_model_for_tp(model, self.tp.rank, self.tp.size)
         self.layouts = build_layouts(model, self.world if self.sharded else 1)
         plane = self._make_plane()
         # the sharded engine runs every collective on the plane; a replicated (data-parallel) engine only the
@@ -175,7 +186,7 @@ class Engine:
         # (one GPU) the slices are views of the resident matrix, which exercises the same GEMM path.
         self.gathered = (getattr(cfg, "fsdp_weights", "resident") == "gathered" and self.device.type == "cuda"
                          and self.cdt == torch.bfloat16 and getattr(model, "arch", "") == "enoki"
-                         and not getattr(cfg, "moe", False))
+                         and not getattr(cfg, "moe", False) and self.tp is None)
         split = self.gathered and self.plane is not None
         self.units: List[Unit] = [Unit(l, self.world, self.rank, self.sharded, self.device, self.cdt, plane,
                                        resident_weights=not (split and l.name != "root"), reduce_bf16=self.reduce_bf16)
@@ -279,10 +290,11 @@ class Engine:
     def _block_spec(self) -> BK.BlockSpec:
         m, c = self.model, self.cfg
         hd = m.head_dim
+        tp = self.tp.size if self.tp is not None else 1        # (the MLP width is read off the already cut matrices)
         if m.arch == "enoki":
             mlp = m.transformer.h[0].mlp.c_fc.weight.shape[0]
             qk_kind = BK.R.NONORM if getattr(c, "no_qknorm", False) else BK.R.LAYERNORM
-            return BK.BlockSpec(d=c.n_embd, n_head=c.n_head, n_kv_head=c.n_head, hd=hd, mlp=mlp,
+            return BK.BlockSpec(d=c.n_embd, n_head=c.n_head // tp, n_kv_head=c.n_head // tp, hd=hd, mlp=mlp,
                                 mlp_kind="gelu", norm_kind=BK.N.LAYERNORM, qk_kind=qk_kind, gate=False,
                                 eps=1e-5, qk_eps=1e-5, scale=float(getattr(c, "residual_stream_scalar", 1.0)),
                                 seq_len=c.sequence_length)
@@ -290,7 +302,7 @@ class Engine:
         rms = getattr(c, "normalization_layer_type", "rmsnorm") == "rmsnorm"
         eps = float(getattr(c, "rmsnorm_eps", 1e-5)) if rms else 1e-5
         qk_kind = BK.R.NONORM if getattr(c, "no_qknorm", False) else (BK.R.RMSNORM if rms else BK.R.LAYERNORM)
-        return BK.BlockSpec(d=c.n_embd, n_head=c.n_head, n_kv_head=blk.attn.n_kv_head, hd=hd,
+        return BK.BlockSpec(d=c.n_embd, n_head=c.n_head // tp, n_kv_head=blk.attn.n_kv_head // tp, hd=hd,
                             mlp=blk.mlp.gate_proj.weight.shape[0], mlp_kind="swiglu",
                             norm_kind=BK.N.RMSNORM if rms else BK.N.LAYERNORM, qk_kind=qk_kind,
                             gate=blk.attn.gate, eps=eps, qk_eps=eps,
@@ -473,7 +485,7 @@ class Engine:
             self._wait_unit(u)
             keep = need_grad and not (ckpt and i % ecfg.checkpoint_every_n == 0)
             x_in = x
-            x, sv = BK.block_forward(x, u.W, sp, self.freqs, B, S, self.cdt, need_grad=keep)
+            x, sv = BK.block_forward(x, u.W, sp, self.freqs, B, S, self.cdt, need_grad=keep, tp=self.tp)
             saved.append(sv if keep else ({"x_only": x_in} if need_grad else None))
         acc = self.micro_step > 0
         out, dx, dx_lp = BK.head_forward_backward(
@@ -519,8 +531,8 @@ class Engine:
                 sv = saved[i]
                 saved[i] = None
                 if "x_only" in sv:  # activation checkpoint: rebuild the block's activations
-                    _, sv = BK.block_forward(sv["x_only"], u.W, sp, self.freqs, B, S, self.cdt, need_grad=True)
-                BK.block_backward(dx, dx_lp, sv, u.W, u.Gd, sp, self.freqs, B, S, acc)
+                    _, sv = BK.block_forward(sv["x_only"], u.W, sp, self.freqs, B, S, self.cdt, need_grad=True, tp=self.tp)
+                BK.block_backward(dx, dx_lp, sv, u.W, u.Gd, sp, self.freqs, B, S, acc, tp=self.tp)
                 u.grads_dirty = True
                 del sv
                 if sync:
@@ -630,6 +642,8 @@ class Engine:
         Returns a 0-d tensor holding the norm."""
         self.finish_grad_sync()
         plane = self.plane or self.ar_plane
+        if self.tp is not None:
+            return self._grad_norm_and_clip_tp(max_norm, plane is not None)
         if plane is not None:
             # the reduce-scatter / all-reduce kernels already accumulated this rank's squared-norm partial
             e0 = self._meter_begin()
@@ -646,6 +660,29 @@ class Engine:
             self.comm.all_reduce_sum(self._sumsq)
             self._meter_end(e0)
         O.clip_coef(self._sumsq, 1.0 if self._averaged else 1.0 / self.world, max_norm, self._clip)
+        self.last_grad_norm = self._clip[1]
+        return self._clip[1]
+
+    def _grad_norm_and_clip_tp(self, max_norm: float, have_partial: bool):
+        """Tensor parallelism: the cut matrices count once per tp rank, the replicated parameters (the whole root unit
+        and every block's vectors) once in all.  Two small sums: over this rank's data-parallel group, then over tp."""
+        if not have_partial:
+            self._sumsq.zero_()
+            for u in self.units:
+                O.sumsq_accumulate(u.grad_shard, self._sumsq)
+        repl = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for u in self.units:
+            lo, hi = u.shard_off, u.shard_off + u.shard_len
+            a = lo if u is self.units[-1] else max(u.small_off, lo)
+            b = min(u.layout.numel, hi)
+            if a < b:
+                O.sumsq_accumulate(u.grad_shard[a - lo:b - lo], repl)
+        both = torch.cat([self._sumsq - repl, repl / self.tp.size])
+        if self.sharded:
+            self.comm.all_reduce_sum(both)
+        self.tp.all_reduce_(both)
+        total = both.sum().reshape(1)
+        O.clip_coef(total, 1.0 if self._averaged else 1.0 / self.world, max_norm, self._clip)
         self.last_grad_norm = self._clip[1]
         return self._clip[1]
 
@@ -834,6 +871,8 @@ class Engine:
             full = self._gather_full(src, u)
             for s in u.layout.slots:
                 out[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
+                if self.tp is not None:          # (collective over tp for the cut matrices)
+                    out[s.name] = self.tp.gather_full(s.name, out[s.name])
         return out
 
     def load_full_param_dict(self, tensors: Dict[str, torch.Tensor], which: str = "master"):
@@ -849,7 +888,10 @@ class Engine:
                     a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
                     if a >= b:
                         continue
-                    src = tensors[s.name].reshape(-1)[a - s.offset:b - s.offset]
+                    t = tensors[s.name]
+                    if self.tp is not None and tuple(t.shape) != tuple(s.shape):
+                        t = self.tp.local_part(s.name, t)           # a full tensor: keep this rank's heads / hidden units
+                    src = t.reshape(-1)[a - s.offset:b - s.offset]
                     dst[a - lo:b - lo].copy_(src.to(dst.dtype))
         if which == "master":
             self.refresh_from_master()
@@ -1024,5 +1066,5 @@ class EngineOptimizer(torch.optim.Optimizer):
 
 
 def attach(model, cfg, comm: Optional[Comm] = None, sharded: bool = True, device=None,
-           compute_dtype=None) -> Engine:
-    return Engine(model, cfg, comm=comm, sharded=sharded, device=device, compute_dtype=compute_dtype)
+           compute_dtype=None, tp_group=None) -> Engine:
+    return Engine(model, cfg, comm=comm, sharded=sharded, device=device, compute_dtype=compute_dtype, tp_group=tp_group)

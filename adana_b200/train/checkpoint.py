@@ -165,7 +165,7 @@ def _is_sharded(model) -> bool:
 def model_state_dict(model) -> Dict[str, torch.Tensor]:
     """Full fp32 state dict under every backend (collective when the engine is sharded)."""
     eng = _engine_of(model)
-    if eng is not None and eng.sharded:
+    if eng is not None and (eng.sharded or getattr(eng, "tp", None) is not None):
         return {k: v.cpu() for k, v in eng.full_param_dict("master").items()}
     if isinstance(model, torch.nn.parallel.DistributedDataParallel):
         model = model.module
@@ -180,6 +180,13 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
     local.mkdir(parents=True, exist_ok=True)
     eng = _engine_of(model)
     sched_sd = scheduler.state_dict() if scheduler is not None else None
+    if eng is not None and getattr(eng, "tp", None) is not None:
+        # tensor parallelism: every rank takes part in reassembling the full tensors (over its data-parallel group and
+        # over tp), global rank 0 writes one reference-format main.pt that any layout can load again
+        ckpt = {"model": model_state_dict(model), "optimizer": _to_cpu(opt.state_dict()), "scheduler": sched_sd, "itr": itr}
+        if _rank() == 0:
+            _atomic_save(ckpt, local / "main.pt")
+        return
     if eng is not None and eng.sharded:
         # `<ckpt>/sharded/` is a torch.distributed.checkpoint directory, as in the reference (src/optim/utils.py:
         # 275-298): every rank writes the rectangles of every tensor that its flat shards cover (train/dcp_format.py).

@@ -133,3 +133,33 @@ def test_two_rank_sharded_muon_cli_run(tmp_path):
     val = [r["val/loss"] for r in rows if "val/loss" in r] + [r["final-val/loss"] for r in rows if "final-val/loss" in r]
     # (the run is seeded: the same numbers every time; the loss of the last evaluation is below the untrained one)
     assert len(val) >= 4 and all(v == v for v in val) and val[-1] < val[0], val
+
+
+@pytest.mark.timeout(900)
+def test_four_rank_dp_by_tp_cli_run_saves_and_resumes(tmp_path):
+    """`--tp_size 2` on four CPU ranks (2 data-parallel x 2 tensor-parallel) through the command line on the kernel engine:
+    trains, writes one full checkpoint assembled over both groups, and a second run resumes from it."""
+    import os
+
+    base = [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
+            "--nproc-per-node", "4", "-m", "adana_b200.main", "--model", "enoki", "--n_layer", "2", "--n_head", "4",
+            "--n_embd", "64", "--qkv_dim", "16", "--mlp_hidden_dim", "128", "--sequence_length", "64", "--batch_size", "8",
+            "--acc_steps", "2", "--vocab_size", "512", "--dataset", "synthetic-zipf", "--datasets_dir", str(tmp_path / "data"),
+            "--opt", "dana-star-mk4", "--lr", "2e-3", "--warmup_steps", "2", "--scheduler", "cos_inf", "--eval_interval", "4",
+            "--eval_batches", "2", "--log_interval", "2", "--results_base_folder", str(tmp_path / "exps"), "--device", "cpu",
+            "--dtype", "float32", "--distributed_backend", "fsdp", "--tp_size", "2", "--seed", "3", "--permanent_ckpt_interval", "4"]
+    env = {**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1"}
+    p = subprocess.run(base + ["--iterations", "8"], cwd=ROOT, capture_output=True, text=True, timeout=400, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    exp = _exp_dir(tmp_path / "exps")
+    rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
+    val = [r["val/loss"] for r in rows if "val/loss" in r] + [r["final-val/loss"] for r in rows if "final-val/loss" in r]
+    assert len(val) >= 2 and all(v == v for v in val) and val[-1] < val[0], val
+    ckpts = sorted((exp / "ckpts").glob("*/main.pt"))
+    assert ckpts, list((exp / "ckpts").rglob("*"))
+    sd = torch.load(ckpts[-1], map_location="cpu", weights_only=False)
+    assert tuple(sd["model"]["transformer.h.0.attn.c_attn.weight"].shape) == (3 * 4 * 16, 64)      # full, not a tp part
+    assert tuple(sd["model"]["transformer.h.0.mlp.c_proj.weight"].shape) == (64, 128)
+    p = subprocess.run(base + ["--iterations", "10", "--resume_from", str(ckpts[-1].parent)], cwd=ROOT, capture_output=True,
+                       text=True, timeout=400, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]

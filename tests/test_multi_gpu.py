@@ -332,3 +332,77 @@ def test_distributed_muon_chain_over_peers_matches_the_collective_path():
     for k, v in res["nccl"][0]["params"].items():
         d = (_t(res["p2p"][0]["params"][k]) - _t(v)).abs().mean().item()
         assert d < 3e-4, (k, d)
+
+
+def _tp_worker(rank, world, tp):
+    import torch.distributed as dist
+
+    from conftest import tiny_args
+    from adana_b200.models.utils import get_model
+    from adana_b200.ops import _lib
+    from adana_b200.parallel.comm import Comm
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    tp_group = dp_group = None
+    if tp > 1:
+        for i in range(world // tp):
+            ranks = list(range(i * tp, (i + 1) * tp))
+            g = dist.new_group(ranks)
+            if rank in ranks:
+                tp_group = g
+        for j in range(tp):
+            ranks = list(range(j, world, tp))
+            g = dist.new_group(ranks)
+            if rank in ranks:
+                dp_group = g
+    a = tiny_args("qwen3", n_embd=256, n_head=4, n_kv_head=2, qkv_dim=64, mlp_hidden_dim=512, sequence_length=128,
+                  vocab_size=1024, opt="adamw", lr=1e-3, weight_decay=0.1, beta1=0.9, beta2=0.99, acc_steps=1,
+                  dtype="bfloat16", device=f"cuda:{rank}")
+    torch.manual_seed(0)
+    m = get_model(a).to(a.device)
+    eng = attach(m, a, comm=Comm(dp_group) if tp > 1 else Comm(), sharded=True, device=a.device, tp_group=tp_group)
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = EngineOptimizer(eng, a.opt, a, specs)
+    m.train()
+    losses, norms = [], []
+    for step in range(4):
+        g = torch.Generator().manual_seed(1000 * step + (rank // tp if tp > 1 else rank))
+        idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g).to(a.device)
+        out = m(idx, targets=idx.roll(-1, 1))
+        out["loss"].backward()
+        norms.append(float(eng.grad_norm_and_clip(0.5)))
+        opt.step()
+        opt.zero_grad()
+        losses.append(out["loss"].item())
+    torch.cuda.synchronize()
+    _lib.check_status()
+    full = eng.full_param_dict("master")
+    on_plane = eng.tp is not None and eng.tp.plane is not None
+    return {"losses": losses, "norms": norms, "params": {k: v.float().cpu() for k, v in full.items()}, "plane": on_plane}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_engine_over_peer_memory_matches_one_gpu():
+    """`--tp_size 2` on the kernel engine: the partial products of the row-parallel GEMMs and of the column-parallel
+    dgrads are summed over NVLink from symmetric buffers; against the same model on one GPU."""
+    from test_distributed_cpu import _spawn, _t
+
+    one = _spawn(_tp_worker, 1, 1)[0]
+    two = _spawn(_tp_worker, 2, 2)
+    assert two[0]["plane"] and two[1]["plane"]
+    for r in range(2):
+        for x, y in zip(two[r]["losses"], one["losses"]):
+            assert abs(x - y) / y < 5e-3, (two[r]["losses"], one["losses"])
+        for x, y in zip(two[r]["norms"], one["norms"]):
+            assert abs(x - y) / y < 2e-2
+        for k, v in one["params"].items():
+            got = _t(two[r]["params"][k])
+            assert tuple(got.shape) == tuple(_t(v).shape)
+            assert (got - _t(v)).abs().mean().item() < 3e-4, k
+    for k in one["params"]:            # both tp ranks hold bitwise the same replicated state and assemble the same tensors
+        assert torch.equal(_t(two[0]["params"][k]), _t(two[1]["params"][k])), k
