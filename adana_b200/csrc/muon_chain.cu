@@ -33,7 +33,7 @@ struct Ptrs {
 
 // One entry per (parameter slot of the unit) x (this rank's shard): the shard-local element range it covers.
 struct Seg {
-  long long a, b;        // [a, b) in shard coordinates, multiples of 8 for matrices (a == b: nothing of it lives here)
+  long long a, b;        // [a, b) in shard coordinates; a is a multiple of 64, b of 8 for matrices (a == b: nothing lives here)
   int kind;              // 0: orthogonalised matrix, 1: AdamW
   int group;             // 0: weight-decayed group, 1: the other
   float shape_factor;    // matrices: matched_rms * sqrt(max(rows, cols))
@@ -205,9 +205,32 @@ muon_apply_kernel(float* __restrict__ p, const float* __restrict__ g, const __nv
         if (r < n_dst) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(weights.p[r]) + push_off + e) = w;
     }
   } else {
-    // element by element: these ranges (vectors, embeddings, the head) start and end anywhere
+    // vectors, embeddings, the head: ranges start on a 64-element boundary (slot and shard boundaries) and end anywhere;
+    // four elements per thread, then a scalar tail
     const float step = lr / h.bias;
-    for (long long e = sg.a + (long long)blockIdx.x * 256 + threadIdx.x; e < sg.b; e += stride) {
+    const long long n4 = (sg.b - sg.a) >> 2;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+      const long long e = sg.a + i * 4;
+      const float4 gv = *reinterpret_cast<const float4*>(g + e);
+      float4 a = *reinterpret_cast<const float4*>(m1 + e), b = *reinterpret_cast<const float4*>(m2 + e);
+      float4 pv = *reinterpret_cast<const float4*>(p + e);
+      const float g4[4] = {gv.x * gs, gv.y * gs, gv.z * gs, gv.w * gs};
+      float a4[4] = {a.x, a.y, a.z, a.w}, b4[4] = {b.x, b.y, b.z, b.w}, p4[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a4[k] += (1.f - h.b1) * (g4[k] - a4[k]);
+        b4[k] += (1.f - h.b2) * (g4[k] * g4[k] - b4[k]);
+        p4[k] = p4[k] * keep - step * a4[k] / (h.eps + sqrtf(b4[k]));
+      }
+      *reinterpret_cast<float4*>(m1 + e) = make_float4(a4[0], a4[1], a4[2], a4[3]);
+      *reinterpret_cast<float4*>(m2 + e) = make_float4(b4[0], b4[1], b4[2], b4[3]);
+      *reinterpret_cast<float4*>(p + e) = make_float4(p4[0], p4[1], p4[2], p4[3]);
+      const uint2 w = make_uint2(pack_bf16x2(p4[0], p4[1]), pack_bf16x2(p4[2], p4[3]));
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < n_dst) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(weights.p[r]) + push_off + e) = w;
+    }
+    for (long long e = sg.a + n4 * 4 + (long long)blockIdx.x * 256 + threadIdx.x; e < sg.b; e += stride) {
       const float gk = g[e] * gs;
       const float a = m1[e] + (1.f - h.b1) * (gk - m1[e]);
       const float b = m2[e] + (1.f - h.b2) * (gk * gk - m2[e]);
@@ -294,7 +317,7 @@ extern "C" int adana_muon_apply(float* p, const float* g, const void* upd, float
   h.lr[0] = hyper[0]; h.lr[1] = hyper[1]; h.wd[0] = hyper[2]; h.wd[1] = hyper[3];
   h.b1 = hyper[4]; h.b2 = hyper[5]; h.eps = hyper[6]; h.bias = hyper[7]; h.gscale = hyper[8];
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  const int gx = grid_for(max_seg_len / 8, 148);
+  const int gx = grid_for(max_seg_len / 8, 148 * 8);
   muon_apply_kernel<<<dim3(gx, n_segs), 256, 0, st>>>(p, g, reinterpret_cast<const __nv_bfloat16*>(upd), m1, m2,
                                                       reinterpret_cast<const Seg*>(segs), h, clip,
                                                       make_ptrs(weight_ptrs ? weight_ptrs : nullptr, weight_ptrs ? n_dst : 0),

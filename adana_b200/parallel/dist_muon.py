@@ -31,6 +31,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import numpy as np
 import torch
@@ -94,6 +95,8 @@ class ShardedMuon(torch.optim.Optimizer):
             rest = [s for s in u.layout.slots if (ui, s.name) not in owner_of]
             self.plan.append((u, mats, rest))
         self.chain = None
+        self._graphs = {}
+        self._graph_ok = os.environ.get("ADANA_MUON_GRAPHS", "1") != "0"
         if self._chain_supported():
             self._setup_chain()
 
@@ -173,6 +176,31 @@ class ShardedMuon(torch.optim.Optimizer):
                           X=torch.empty(big, dtype=bf, device=dev), Y=torch.empty(big, dtype=bf, device=dev),
                           A=torch.empty(big_s * big_s, dtype=bf, device=dev), B=torch.empty(big_s * big_s, dtype=bf, device=dev))
 
+    def _ns_graphed(self, X, Y, A, B, steps: int):
+        """The 3 * steps GEMM launches of one orthogonalisation, replayed from a CUDA graph per matrix shape (the
+        workspace is fixed, so the captured pointers stay valid): small matrices are bound by launch rate otherwise.
+        The first use of a shape runs eagerly, the second is captured; ADANA_MUON_GRAPHS=0 keeps everything eager."""
+        from ..ops.muon_ns import ns_chain
+
+        key = (tuple(X.shape), int(steps))
+        g = self._graphs.get(key)
+        if g is None or g == "eager":
+            if g is None and self._graph_ok:
+                self._graphs[key] = "warm"
+            return ns_chain(X, Y, A, B, steps)
+        if g == "warm":
+            try:
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize(self.engine.device)
+                with torch.cuda.graph(graph):
+                    out = ns_chain(X, Y, A, B, steps)
+                self._graphs[key] = g = (graph, out)
+            except Exception:
+                self._graphs[key] = "eager"
+                return ns_chain(X, Y, A, B, steps)
+        g[0].replay()
+        return g[1]
+
     def _flags(self, base: int, unit_index: int) -> int:
         return self.engine.plane.base + 4 * (base + 8 * unit_index)
 
@@ -221,7 +249,7 @@ class ShardedMuon(torch.optim.Optimizer):
                 _lib.check_rc(lib.adana_muon_pull(
                     d["ns_ptrs"], ch["parts_ptrs"], world, u.shard_len, s.offset, s.numel, mat, 1e-7, X.data_ptr(),
                     self._flags(MUON_FLAG_STAGED, d["index"]) if multi else 0, seq, tmo, status, stream), "adana_muon_pull")
-                out = ns_chain(X, Y, A, B, steps)
+                out = self._ns_graphed(X, Y, A, B, steps)
                 _lib.check_rc(lib.adana_muon_push(out.data_ptr(), d["upd_ptrs"], world, u.shard_len, s.offset, s.numel,
                                                   stream), "adana_muon_push")
             if multi:

@@ -163,6 +163,11 @@ class TensorParallelGroup:
         dist.all_reduce(t, group=self.group)
         return t
 
+    def broadcast_(self, t: torch.Tensor) -> torch.Tensor:
+        """Everybody takes tp rank 0's copy (for replicated values that come out of an order-dependent reduction)."""
+        dist.broadcast(t, group=self.group, group_src=0)
+        return t
+
     def gather_full(self, name: str, local: torch.Tensor) -> torch.Tensor:
         """Full tensor of a parameter-shaped value from every tp rank's part (collective); replicated ones pass."""
         rule = self.cut.get(name)

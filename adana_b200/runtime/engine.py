@@ -543,6 +543,10 @@ class Engine:
                 root.Gd["wte"].zero_()
             M.embedding_bwd(pend["idx"], dx, root.Gd["wte"])
             root.grads_dirty = True
+            if sync and self.tp is not None and self.device.type == "cuda":
+                # the embedding gradient is summed with atomics, in an order that differs from run to run: the tp ranks
+                # (which hold this replicated table) all continue with tp rank 0's sum, so the table never drifts apart
+                self.tp.broadcast_(root.Gd["wte"])
             if sync:
                 self._reduce_unit(root)
         self.micro_step += 1

@@ -78,6 +78,7 @@ def parse():
     p.add_argument("--micro_batch", type=int, default=None)
     p.add_argument("--per_gpu_seqs", type=int, default=None)
     p.add_argument("--n_layer", type=int, default=None, help="override for smoke runs only")
+    p.add_argument("--tp_size", type=int, default=1, help="tensor-parallel ranks per data-parallel replica (both arms)")
     p.add_argument("--no_e2e", action="store_true")
     p.add_argument("--attention", default="auto", choices=["auto", "native", "sdpa"])
     p.add_argument("--ref_no_compile", action="store_true")
@@ -95,9 +96,11 @@ def parse():
 def shared_config(a, world: int) -> dict:
     """The keys that name the workload; identical for both arms (implementation choices go to `impl_detail`)."""
     c = CONFIGS[a.config]
-    return {"model": c["label"].format(n_layer=a.n_layer), "global_batch": a.per_gpu_seqs * world,
+    dp = world // a.tp_size
+    return {"model": c["label"].format(n_layer=a.n_layer), "global_batch": a.per_gpu_seqs * dp,
             "seq_len": c["model"]["sequence_length"], "micro_batch": a.micro_batch,
-            "acc_steps": a.per_gpu_seqs // a.micro_batch, "optimizer": a.opt, "parallelism": f"fsdp{world}"}
+            "acc_steps": a.per_gpu_seqs // a.micro_batch, "optimizer": a.opt,
+            "parallelism": f"fsdp{dp}" + (f"xtp{a.tp_size}" if a.tp_size > 1 else "")}
 
 
 def metric_name(a) -> str:
@@ -174,7 +177,9 @@ def run_ours(a):
     args.distributed_backend = "fsdp"
     # the backend's split rule (acc //= gcd(acc, N); batch //= N / gcd) maps this to
     # micro-batch `micro_batch` and `acc` accumulation steps on every rank
-    args.batch_size, args.acc_steps = a.micro_batch, acc * world
+    dp = world // a.tp_size
+    args.tp_size = a.tp_size
+    args.batch_size, args.acc_steps = a.micro_batch, acc * dp
     args.weight_tying, args.init_scheme = False, "ScaledGPT"
     # (the same schedule flags as the reference arm: the two arms' learning rates, and so their losses, are comparable)
     args.scheduler, args.iterations, args.warmup_steps = "cos_inf", a.warmup + a.steps, 1
@@ -206,7 +211,7 @@ def run_ours(a):
     trainer = Trainer(model, opt, {"train": train_reader, "val": val_reader}, sched, "/tmp/adana_bench_exp",
                       backend, args)
     model.train()
-    tokens_per_step = a.per_gpu_seqs * world * args.sequence_length
+    tokens_per_step = a.per_gpu_seqs * dp * args.sequence_length
 
     # ---- device-timed region: batches pre-staged on the device ---------------------------------------
     dev_batches = []
@@ -416,7 +421,7 @@ def run_reference(a):
                 "--distributed_backend", "fsdp", "--device", f"cuda:{local_rank}",
                 # the reference's split rule (acc //= gcd(acc, N); batch //= N / gcd) turns this into
                 # micro-batch `micro_batch` and `acc` accumulation steps per rank
-                "--batch_size", str(a.micro_batch), "--acc_steps", str(acc * world),
+                "--batch_size", str(a.micro_batch), "--acc_steps", str(acc * (world // a.tp_size)),
                 "--scheduler", "cos_inf", "--iterations", str(steps_total),
                 "--warmup_steps", "1", "--final_div_factor", "0.1", "--dataset", "fineweb",
                 "--datasets_dir", str(data_root), "--log_interval", "1000000", "--eval_interval", "1000000",
@@ -430,6 +435,8 @@ def run_reference(a):
                     argv.append(f"--{k}")
             else:
                 argv += [f"--{k}", str(v)]
+        if a.tp_size > 1:
+            argv += ["--tp_size", str(a.tp_size)]
         if not a.ref_no_compile:
             argv.append("--compile")
         sys.argv = ["main.py"] + argv
@@ -489,7 +496,7 @@ def run_reference(a):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             dist.all_reduce(wall, op=dist.ReduceOp.MAX)
         ms_per_step = float(ms.item()) / a.steps
-        tokens_per_step = a.per_gpu_seqs * world * seq_len
+        tokens_per_step = a.per_gpu_seqs * (world // a.tp_size) * seq_len
         mem = torch.cuda.max_memory_allocated() / 2 ** 30
         if rank == 0:
             emit({"metric": metric_name(a), "value": tokens_per_step / (ms_per_step / 1e3),

@@ -150,7 +150,7 @@ def test_four_rank_dp_by_tp_cli_run_saves_and_resumes(tmp_path):
             "--dtype", "float32", "--distributed_backend", "fsdp", "--tp_size", "2", "--seed", "3", "--permanent_ckpt_interval", "4"]
     env = {**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1"}
     p = subprocess.run(base + ["--iterations", "8"], cwd=ROOT, capture_output=True, text=True, timeout=400, env=env)
-    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert p.returncode == 0, "\n".join(l for l in p.stderr.splitlines() if "Error" in l or "error" in l)[-3000:]
     exp = _exp_dir(tmp_path / "exps")
     rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
     val = [r["val/loss"] for r in rows if "val/loss" in r] + [r["final-val/loss"] for r in rows if "final-val/loss" in r]

@@ -270,7 +270,9 @@ def test_gathered_weights_over_peers_match_resident_weights():
         assert abs(a - b) < 5e-3
     for k, v in res["resident"][0]["params"].items():
         d = (_t(res["gathered"][0]["params"][k]) - _t(v)).abs()
-        assert d.mean().item() < 2e-4 and d.max().item() < 2e-2, (k, d.mean().item(), d.max().item())
+        # (a sign-like update: the few elements whose gradient is next to zero may move by a step in either direction)
+        assert d.mean().item() < 2e-4 and (d > 5e-3).float().mean().item() < 1e-3 and d.max().item() < 5e-2, \
+            (k, d.mean().item(), d.max().item())
         assert torch.equal(_t(res["gathered"][0]["params"][k]), _t(res["gathered"][1]["params"][k]))
 
 
