@@ -8,6 +8,10 @@
 //               row max / row sum need no shuffles), writes P_j as bf16 into shared memory in the
 //               128B-swizzled K-major layout the MMA reads, rescales O in tensor memory lazily (only
 //               when the running max grew by more than 2^8), and finally normalises and stores O.
+// With head_dim 128 one CTA fills an SM and four softmax warps (one per scheduler) cannot keep the exponential unit
+// busy, so there eight warps do the softmax (SW = 8): two per 32 rows, each taking 64 of the tile's 128 key columns;
+// the pair agrees on the row maximum through shared memory (one 64-thread named barrier per tile) and shares the
+// rescaling of O, the P store and the epilogue by columns.
 // QK_{j+1} is issued before PV_j waits for P_j, so the tensor cores compute the next scores while
 // the softmax of the current tile runs; with head_dim 64 two CTAs share an SM and overlap each other.
 // Grouped-query attention: query head h reads KV head h / (Hq/Hk).  V is read in place from the fused
@@ -18,6 +22,8 @@
 //
 // Replaces F.scaled_dot_product_attention(is_causal=True) of the reference
 // (src/models/enoki.py:134-136, src/models/qwen3.py:212-217).
+#include <cstdlib>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -25,7 +31,6 @@ namespace adana {
 
 constexpr int ATT_BQ = 128;
 constexpr int ATT_BKV = 128;
-constexpr int ATT_THREADS = 192;
 constexpr int ATT_BWD_THREADS = 448;   // TMA warp, MMA warp, eight score warps (two per lane quarter), four dQ drain warps
 constexpr int ATT_KV_STAGES = 2;
 constexpr float ATT_RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -48,8 +53,19 @@ struct AttFwdArgs {
   int* status;
 };
 
-template <int HD, int S_BUFS>
-__global__ void __launch_bounds__(ATT_THREADS, (HD == 64 ? 2 : 1))
+// 64-thread barrier of the two softmax warps that share 32 rows; the id is an immediate so that the kernel reserves
+// five barriers, not all sixteen
+__device__ __forceinline__ void pair_barrier(int quad) {
+  switch (quad) {
+    case 0: named_barrier_sync(1, 64); break;
+    case 1: named_barrier_sync(2, 64); break;
+    case 2: named_barrier_sync(3, 64); break;
+    default: named_barrier_sync(4, 64); break;
+  }
+}
+
+template <int HD, int S_BUFS, int SW>
+__global__ void __launch_bounds__(64 + 32 * SW, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttFwdArgs args) {
   using L = AttFwdSmem<HD>;
@@ -65,13 +81,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* q_full = bars;                 // [1]
   uint64_t* k_full = bars + 1;             // [STAGES]
   uint64_t* v_full = bars + 3;             // [STAGES]
-  uint64_t* kv_empty = bars + 5;           // [STAGES]
+  uint64_t* k_empty = bars + 5;            // [STAGES]  K_j is free once QK_j has run ...
+  uint64_t* v_empty = bars + 14;           // [STAGES]  ... V_j only after PV_j: K_{j+2} is fetched a whole tile earlier
   uint64_t* s_full = bars + 7;             // [2]
   uint64_t* s_empty = bars + 9;            // [2]
   uint64_t* p_full = bars + 11;            // [1]
   uint64_t* p_empty = bars + 12;           // [1]
   uint64_t* o_full = bars + 13;            // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -90,13 +107,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     for (int s = 0; s < ATT_KV_STAGES; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4);
+      mbar_init(&s_empty[s], SW);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, SW);
     mbar_init(p_empty, 1);
     mbar_init(o_full, 1);
     *abort_flag = 0;
@@ -121,29 +139,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int c = 0; c < CHUNKS; ++c)
         tma_load_3d(smem + L::Q_OFF + c * CHUNK_BYTES, &tmQ, q_full, c * 64, row0, h);
-      int stage = 0;
-      uint32_t phase = 0;
+      // K tiles run one ahead of V tiles, in the order in which the tensor pipe frees their stages
+      // (QK_{j-1} retires before PV_{j-2}): K_0, K_1, V_0, K_2, V_1, ...
       bool ok = true;
-      int issued = 0;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
-          ok = false;
-          break;
-        }
+      auto load_k = [&](int j) -> bool {
+        const int stage = j % ATT_KV_STAGES;
+        if (!mbar_wait(&k_empty[stage], ((uint32_t)(j / ATT_KV_STAGES) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN))
+          return false;
         const int kvrow = b * args.S + j * ATT_BKV;
         mbar_expect_tx(&k_full[stage], L::TILE);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c)
           tma_load_3d(smem + L::K_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmK, &k_full[stage], c * 64, kvrow, hk);
+        return true;
+      };
+      auto load_v = [&](int j) -> bool {
+        const int stage = j % ATT_KV_STAGES;
+        if (!mbar_wait(&v_empty[stage], ((uint32_t)(j / ATT_KV_STAGES) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN))
+          return false;
+        const int kvrow = b * args.S + j * ATT_BKV;
         mbar_expect_tx(&v_full[stage], L::TILE);
 #pragma unroll
         for (int c = 0; c < CHUNKS; ++c)
           tma_load_3d(smem + L::V_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmV, &v_full[stage], c * 64, kvrow, hk);
-        ++issued;
-        if (++stage == ATT_KV_STAGES) {
-          stage = 0;
-          phase ^= 1;
-        }
+        return true;
+      };
+      ok = load_k(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) ok = load_k(j + 1);
+        if (ok) ok = load_v(j);
       }
       if (!ok) {
         // aborting: give copies in flight time to land before the CTA exits
@@ -183,7 +207,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             umma_ts(tb + O_COL, tb + P_COL + kk * 8, v_desc + (uint64_t)((kk * 2048) >> 4), idesc_pv,
                     (jj > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&kv_empty[st]);   // K_j / V_j stage free again
+          umma_commit(&v_empty[st]);    // V_j's stage free again
           umma_commit(p_empty);          // P buffer free, O updated
         }
         return true;
@@ -207,11 +231,165 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             umma_ss(tb + sb * 128, q_desc + o, k_desc + o, idesc_qk, kk > 0 ? 1u : 0u);
           }
           umma_commit(&s_full[sb]);
+          umma_commit(&k_empty[st]);    // K_j's stage free again as soon as these products retire
         }
         if (j > 0) ok = issue_pv(j - 1);
       }
       if (ok) ok = issue_pv(n_kv - 1);
       if (ok && leader) umma_commit(o_full);
+    }
+  } else if (SW == 8) {
+    // ------------------------------ softmax + epilogue, two warps per 32 rows ----------------
+    __shared__ float xmax[2][2][ATT_BQ];       // [tile parity][column half][row]
+    __shared__ float xsum[2][ATT_BQ];
+    const int quad = warp & 3;                   // tensor-memory lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;            // which 64 of the tile's 128 key columns
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int sb = j % S_BUFS;
+      const uint32_t sph = (uint32_t)(j / S_BUFS) & 1;
+      if (!mbar_wait(&s_full[sb], sph, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t s_addr = tmem_base + sb * 128 + lane_addr + half * 64;
+      const bool diag = (j == n_kv - 1);
+      // With two CTAs per SM (head_dim 64) a thread has about a hundred registers: the scores are then read twice from
+      // tensor memory, 32 columns at a time (once for the maximum, once for the exponentials), instead of being held.
+      constexpr bool RELOAD = (HD == 64);
+      uint32_t va[32], vb[RELOAD ? 1 : 32];
+      auto chunk_max = [&](uint32_t (&v)[32], int col0) -> float {
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((col0 + i) > r) v[i] = 0xff800000u;        // -inf: exp2 gives exactly 0
+        }
+        float m = fmax3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2) m = fmax3(m, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        return fmaxf(m, __uint_as_float(v[31]));
+      };
+      float cmax;
+      if (RELOAD) {
+        tmem_ld_32x32b_x32(s_addr, va);
+        tmem_wait_ld();
+        cmax = chunk_max(va, half * 64);
+        tmem_ld_32x32b_x32(s_addr + 32, va);
+        tmem_wait_ld();
+        cmax = fmaxf(cmax, chunk_max(va, half * 64 + 32));
+      } else {
+        uint32_t(&vb2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&vb[0]);
+        tmem_ld_32x32b_x32(s_addr, va);
+        tmem_ld_32x32b_x32(s_addr + 32, vb2);
+        tmem_wait_ld();
+        cmax = fmaxf(chunk_max(va, half * 64), chunk_max(vb2, half * 64 + 32));
+      }
+      // the two warps of a row agree on the tile's maximum (and therefore on every rescaling decision)
+      xmax[j & 1][half][r] = cmax;
+      pair_barrier(quad);
+      const float m_c = fmaxf(cmax, xmax[j & 1][half ^ 1][r]) * args.scale_log2;
+      float factor = 1.f;
+      bool grow = false;
+      if (m_c > m_ref + ATT_RESCALE_THRESHOLD) {
+        factor = ex2_approx(m_ref - m_c);       // 0 on the first tile (m_ref = -inf)
+        l_sum *= factor;
+        m_ref = m_c;
+        grow = true;
+      }
+      uint32_t pk[32];
+      float2 lacc2 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
+      const float2 nm2 = make_float2(-m_ref, -m_ref);
+      auto chunk_exp = [&](uint32_t (&v)[32], int col0, int out0) {
+        if (RELOAD && diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((col0 + i) > r) v[i] = 0xff800000u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
+          const float2 p2 = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+          lacc2 = __fadd2_rn(lacc2, p2);
+          pk[out0 + (i >> 1)] = pack_bf16x2(p2.x, p2.y);
+        }
+      };
+      if (RELOAD) {
+        tmem_ld_32x32b_x32(s_addr, va);
+        tmem_wait_ld();
+        chunk_exp(va, half * 64, 0);
+        tmem_ld_32x32b_x32(s_addr + 32, va);
+        tmem_wait_ld();
+        chunk_exp(va, half * 64 + 32, 16);
+      } else {
+        uint32_t(&vb2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&vb[0]);
+        chunk_exp(va, half * 64, 0);
+        chunk_exp(vb2, half * 64 + 32, 16);
+      }
+      l_sum += lacc2.x + lacc2.y;
+      // S_j is in registers now: the next QK may overwrite the buffer
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (j > 0) {
+        if (!mbar_wait(p_empty, (uint32_t)(j - 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, grow)) {
+          // this warp rescales its half of the output columns
+#pragma unroll 1
+          for (int c = 0; c < HD / 64; ++c) {
+            uint32_t o[32];
+            const uint32_t addr = tmem_base + O_COL + lane_addr + half * (HD / 2) + c * 32;
+            tmem_ld_32x32b_x32(addr, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st_32x32b_x32(addr, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // this warp's 64 keys = 32 packed columns of P
+      tmem_st_32x32b_x32(tmem_base + P_COL + lane_addr + half * 32, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> bf16 (each warp its half of the columns), lse2 ----
+    if (ok && mbar_wait(o_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+      tc_fence_after_sync();
+      xsum[half][r] = l_sum;
+      pair_barrier(quad);
+      const float l_tot = l_sum + xsum[half ^ 1][r];
+      const float inv_l = 1.f / l_tot;
+      const long long token = (long long)row0 + r;
+      if (ADANA_IN_RANGE(token, (long long)args.B * args.S)) {
+        __nv_bfloat16* dst = args.out + token * ((long long)args.Hq * HD) + (long long)h * HD + half * (HD / 2);
+#pragma unroll 1
+        for (int c = 0; c < HD / 64; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_base + O_COL + lane_addr + half * (HD / 2) + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 val;
+            val.x = pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv_l, __uint_as_float(o[q4 * 8 + 1]) * inv_l);
+            val.y = pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv_l, __uint_as_float(o[q4 * 8 + 3]) * inv_l);
+            val.z = pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv_l, __uint_as_float(o[q4 * 8 + 5]) * inv_l);
+            val.w = pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv_l, __uint_as_float(o[q4 * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = val;
+          }
+        }
+        if (half == 0) args.lse2[((long long)b * args.Hq + h) * args.S + qt * ATT_BQ + r] = m_ref + log2f(l_tot);
+      }
     }
   } else {
     // ------------------------------ softmax + epilogue (warps 2..5) -------------------------
@@ -364,10 +542,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-template <int HD, int S_BUFS>
-static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                           const AttFwdArgs& a, cudaStream_t st) {
-  auto kern = attn_fwd_kernel<HD, S_BUFS>;
+template <int HD, int S_BUFS, int SW>
+static int launch_attn_fwd_sw(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                              const AttFwdArgs& a, cudaStream_t st) {
+  auto kern = attn_fwd_kernel<HD, S_BUFS, SW>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttFwdSmem<HD>::TOTAL);
@@ -375,8 +553,380 @@ static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const C
     configured = true;
   }
   const int grid = a.B * a.Hq * (a.S / ATT_BQ);
-  kern<<<grid, ATT_THREADS, AttFwdSmem<HD>::TOTAL, st>>>(tq, tk, tv, a);
+  kern<<<grid, 64 + 32 * SW, AttFwdSmem<HD>::TOTAL, st>>>(tq, tk, tv, a);
   return (int)cudaGetLastError();
+}
+
+// ---- forward, two softmax groups on alternate key tiles ------------------------------------------------------------
+// A clock trace of the kernel above showed its softmax warps as the critical path, and only half of their time per
+// tile in the exponentials: the rest (tensor-memory loads, row maximum, hand-offs) left the exponential unit idle,
+// because all softmax warps of the CTA go through the same phase at the same time.  Here one CTA per SM runs TWO groups
+// of four softmax warps: group g takes the key tiles j = g (mod 2) and keeps its own running reference maximum, row sum
+// and output accumulator O_g, so the groups never wait for one another and one group's exponentials run under the other
+// group's loads and hand-offs.  A group is eight warps, two per 32 rows, each taking 64 of the tile's 128 key columns
+// (the pair agrees on the row maximum through shared memory, as above): sixteen softmax warps per SM, four per
+// scheduler, which is what it takes to keep the exponential unit fed while other warps are between phases.
+// Tensor memory: S_0 | S_1 | O_0 | O_1; P_j is written over the first 64 columns of its
+// own S_j (free once the scores are in registers).  The tensor pipe runs QK_0, QK_1, PV_0, QK_2, PV_1, ...; products of
+// one thread retire in order, so QK_{j+2} cannot overwrite S_j / P_j before PV_j has read it, and "S_{j+2} is full"
+// implies "PV_j has retired", which is all a group needs before it rescales O_g.  The epilogue joins the two streams:
+// out = (2^(m_0 - m) O_0 + 2^(m_1 - m) O_1) / (2^(m_0 - m) l_0 + 2^(m_1 - m) l_1), m = max(m_0, m_1).
+template <int HD>
+struct AttFwdPPSmem {
+  static constexpr int STAGES = HD == 64 ? 4 : 2;
+  static constexpr int TILE = ATT_BQ * HD * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;
+  static constexpr int V_OFF = K_OFF + STAGES * TILE;
+  static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
+  static constexpr int TOTAL = BAR_OFF + 512;
+};
+constexpr int ATT_PP_THREADS = 576;       // TMA warp, MMA warp, 2 groups x 8 softmax warps
+
+template <int HD>
+__global__ void __launch_bounds__(ATT_PP_THREADS, 1)
+attn_fwd_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const AttFwdArgs args) {
+  using L = AttFwdPPSmem<HD>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int CHUNKS = HD / 64;
+  constexpr int CHUNK_BYTES = ATT_BQ * 128;
+  constexpr uint32_t O_COL = 256;                  // O_g at O_COL + g * HD
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* k_full = bars + 1;             // [STAGES]
+  uint64_t* v_full = bars + 1 + STAGES;    // [STAGES]
+  uint64_t* k_empty = bars + 1 + 2 * STAGES;
+  uint64_t* v_empty = bars + 1 + 3 * STAGES;
+  uint64_t* s_full = bars + 1 + 4 * STAGES;      // [2]
+  uint64_t* p_full = s_full + 2;                 // [2]
+  uint64_t* o_full = p_full + 2;                 // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float xm[2][ATT_BQ], xl[2][2][ATT_BQ];      // [group][row], [group][column half][row]
+  __shared__ float xmax[2][2][2][ATT_BQ];                // [group][tile parity][column half][row]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = args.S / ATT_BQ;
+  const int BH = args.B * args.Hq;
+  const int qt = n_qt - 1 - (int)(blockIdx.x / BH);      // heaviest query tiles first
+  const int bh = (int)(blockIdx.x % BH);
+  const int b = bh / args.Hq, h = bh % args.Hq;
+  const int hk = h / (args.Hq / args.Hk);
+  const int n_kv = qt + 1;
+  const int row0 = b * args.S + qt * ATT_BQ;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&s_full[g], 1);
+      mbar_init(&p_full[g], 8);
+    }
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, L::TILE);
+#pragma unroll
+      for (int c = 0; c < CHUNKS; ++c)
+        tma_load_3d(smem + L::Q_OFF + c * CHUNK_BYTES, &tmQ, q_full, c * 64, row0, h);
+      bool ok = true;
+      auto load_k = [&](int j) -> bool {
+        const int stage = j % STAGES;
+        if (!mbar_wait(&k_empty[stage], ((uint32_t)(j / STAGES) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        const int kvrow = b * args.S + j * ATT_BKV;
+        mbar_expect_tx(&k_full[stage], L::TILE);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(smem + L::K_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmK, &k_full[stage], c * 64, kvrow, hk);
+        return true;
+      };
+      auto load_v = [&](int j) -> bool {
+        const int stage = j % STAGES;
+        if (!mbar_wait(&v_empty[stage], ((uint32_t)(j / STAGES) & 1) ^ 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+        const int kvrow = b * args.S + j * ATT_BKV;
+        mbar_expect_tx(&v_full[stage], L::TILE);
+#pragma unroll
+        for (int c = 0; c < CHUNKS; ++c)
+          tma_load_3d(smem + L::V_OFF + stage * L::TILE + c * CHUNK_BYTES, &tmV, &v_full[stage], c * 64, kvrow, hk);
+        return true;
+      };
+      // K tiles run two ahead of V tiles, following the order in which the tensor pipe frees their stages
+      ok = load_k(0);
+      if (ok && n_kv > 1) ok = load_k(1);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 2 < n_kv) ok = load_k(j + 2);
+        if (ok) ok = load_v(j);
+      }
+      if (!ok) {
+        const uint64_t t0 = globaltimer_ns();      // aborting: give copies in flight time to land before the CTA exits
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (warp-uniform loop, one elected lane issues) --------------
+    const bool leader = elect_one();
+    const uint32_t tb = __shfl_sync(0xffffffffu, tmem_base, 0);
+    constexpr uint32_t idesc_qk = make_idesc_bf16(ATT_BQ, ATT_BKV, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(ATT_BQ, HD, false, true);
+    const uint64_t q_desc = make_smem_desc_sw128(smem_u32(smem + L::Q_OFF), 16, 1024);
+    const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(smem + L::K_OFF), 16, 1024);
+    const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(smem + L::V_OFF), CHUNK_BYTES, 1024);
+    constexpr uint32_t TILE16 = L::TILE >> 4;
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN);
+    tc_fence_after_sync();
+    auto issue_qk = [&](int j) -> bool {
+      const int st = j % STAGES;
+      if (!mbar_wait_warp(&k_full[st], (uint32_t)(j / STAGES) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+      tc_fence_after_sync();
+      const uint64_t k_desc = k_desc0 + (uint64_t)(st * TILE16);
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint64_t o = (uint64_t)(((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4);
+          umma_ss(tb + (j & 1) * 128, q_desc + o, k_desc + o, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+        umma_commit(&k_empty[st]);
+      }
+      return true;
+    };
+    auto issue_pv = [&](int j) -> bool {
+      const int st = j % STAGES, g = j & 1;
+      if (!mbar_wait_warp(&p_full[g], (uint32_t)(j >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+      if (!mbar_wait_warp(&v_full[st], (uint32_t)(j / STAGES) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) return false;
+      tc_fence_after_sync();
+      const uint64_t v_desc = v_desc0 + (uint64_t)(st * TILE16);
+      if (leader) {
+#pragma unroll
+        for (int kk = 0; kk < ATT_BKV / 16; ++kk)
+          umma_ts(tb + O_COL + g * HD, tb + g * 128 + kk * 8, v_desc + (uint64_t)((kk * 2048) >> 4), idesc_pv,
+                  (j > 1 || kk > 0) ? 1u : 0u);
+        umma_commit(&v_empty[st]);
+      }
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    for (int j = 1; j < n_kv && ok; ++j) {
+      ok = issue_qk(j);                  // S_{j&1} / P_{j-2}: the products of this thread retire in order, so PV_{j-2} has read
+      if (ok) ok = issue_pv(j - 1);      // its P before these scores land
+    }
+    if (ok) ok = issue_pv(n_kv - 1);
+    if (ok && leader) umma_commit(o_full);
+  } else {
+    // ------------------------------ softmax groups: warps 2..9 even tiles, warps 10..17 odd tiles -------------
+    const int g = (warp - 2) >> 3;
+    const int half = ((warp - 2) >> 2) & 1;          // which 64 of the tile's 128 key columns
+    const int quad = warp & 3;                        // tensor-memory lane quarter this warp may touch
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + g * 128 + lane_addr + half * 64;
+    const uint32_t o_addr = tmem_base + O_COL + g * HD + lane_addr + half * (HD / 2);
+    const int pair_id = 1 + g * 4 + quad;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = g; j < n_kv && ok; j += 2) {
+      if (!mbar_wait(&s_full[g], (uint32_t)(j >> 1) & 1, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const bool diag = (j == n_kv - 1);
+      const int par = (j >> 1) & 1;
+      // about a hundred registers per thread: the scores are read twice from tensor memory, 32 columns at a time
+      // (once for the maximum, once for the exponentials), instead of being held
+      uint32_t va[32];
+      auto chunk_mask = [&](int col0) {
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((col0 + i) > r) va[i] = 0xff800000u;        // -inf: exp2 gives exactly 0
+        }
+      };
+      auto chunk_max = [&]() -> float {
+        float m = fmax3(__uint_as_float(va[0]), __uint_as_float(va[1]), __uint_as_float(va[2]));
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2) m = fmax3(m, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+        return fmaxf(m, __uint_as_float(va[31]));
+      };
+      tmem_ld_32x32b_x32(s_addr, va);
+      tmem_wait_ld();
+      chunk_mask(half * 64);
+      float cmax = chunk_max();
+      tmem_ld_32x32b_x32(s_addr + 32, va);
+      tmem_wait_ld();
+      chunk_mask(half * 64 + 32);
+      cmax = fmaxf(cmax, chunk_max());
+      // the two warps of a row agree on the tile's maximum (and therefore on every rescaling decision)
+      xmax[g][par][half][r] = cmax;
+      named_barrier_sync(pair_id, 64);
+      const float m_c = fmaxf(cmax, xmax[g][par][half ^ 1][r]) * args.scale_log2;
+      float factor = 1.f;
+      bool grow = false;
+      if (m_c > m_ref + ATT_RESCALE_THRESHOLD) {
+        factor = ex2_approx(m_ref - m_c);       // 0 on the group's first tile (m_ref = -inf)
+        l_sum *= factor;
+        m_ref = m_c;
+        grow = true;
+      }
+      uint32_t pk[32];
+      float2 lacc2 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(args.scale_log2, args.scale_log2);
+      const float2 nm2 = make_float2(-m_ref, -m_ref);
+      auto chunk_exp = [&](int out0) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(va[i]), __uint_as_float(va[i + 1])), sc2, nm2);
+          const float2 p2 = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+          lacc2 = __fadd2_rn(lacc2, p2);
+          pk[out0 + (i >> 1)] = pack_bf16x2(p2.x, p2.y);
+        }
+      };
+      chunk_exp(16);                             // the second 32 columns are still in registers
+      tmem_ld_32x32b_x32(s_addr, va);
+      tmem_wait_ld();
+      // (the warp with keys 0..63 has now read all its scores: its partner may overwrite columns 32..63 with P)
+      if (half == 0) {
+        tc_fence_before_sync();
+        named_barrier_arrive(pair_id, 64);
+      }
+      chunk_mask(half * 64);
+      chunk_exp(0);
+      l_sum += lacc2.x + lacc2.y;
+      if (j >= 2 && __any_sync(0xffffffffu, grow)) {
+        // PV_{j-2} has retired (it precedes QK_j in the tensor pipe): rescale this warp's half of the group's accumulator
+#pragma unroll 1
+        for (int c = 0; c < HD / 64; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(o_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_32x32b_x32(o_addr + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      // P_j over the first 64 columns of S_j: this warp's 64 keys are 32 packed columns.  The warp with keys 64..127
+      // writes columns 32..63, which hold scores of its partner: it waits until the partner has read them
+      if (half == 1) {
+        named_barrier_sync(pair_id, 64);
+        tc_fence_after_sync();
+      }
+      tmem_st_32x32b_x32(tmem_base + g * 128 + lane_addr + half * 32, pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[g]);
+    }
+    // ---- epilogue: join the two streams; every (group, half) writes a quarter of the output columns ----
+    if (half == 0) xm[g][r] = m_ref;
+    xl[g][half][r] = l_sum;
+    named_barrier_sync(9, 512);
+    if (ok && mbar_wait(o_full, 0, abort_flag, args.status, ST_TIMEOUT_ATTN)) {
+      tc_fence_after_sync();
+      const bool two = n_kv > 1;                       // with one key tile the odd group never ran: O_1 holds nothing
+      const float m0 = xm[0][r], m1 = two ? xm[1][r] : -INFINITY;
+      const float m = fmaxf(m0, m1);
+      const float w0 = ex2_approx(m0 - m), w1 = two ? ex2_approx(m1 - m) : 0.f;
+      const float l_tot = (xl[0][0][r] + xl[0][1][r]) * w0 + (two ? (xl[1][0][r] + xl[1][1][r]) * w1 : 0.f);
+      const float inv_l = 1.f / l_tot;
+      const float a0 = w0 * inv_l, a1 = w1 * inv_l;
+      const long long token = (long long)row0 + r;
+      constexpr int QC = HD / 4;                       // output columns of this warp
+      const int c0 = (g * 2 + half) * QC;
+      if (ADANA_IN_RANGE(token, (long long)args.B * args.S)) {
+        __nv_bfloat16* dst = args.out + token * ((long long)args.Hq * HD) + (long long)h * HD + c0;
+        const uint32_t oa = tmem_base + O_COL + lane_addr + c0;
+#pragma unroll 1
+        for (int c = 0; c < QC / 16; ++c) {
+          uint32_t o0[16], o1[16];
+          tmem_ld_32x32b_x16(oa + c * 16, o0);
+          if (two) tmem_ld_32x32b_x16(oa + HD + c * 16, o1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q4 = 0; q4 < 2; ++q4) {
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              f[e] = __uint_as_float(o0[q4 * 8 + e]) * a0 + (two ? __uint_as_float(o1[q4 * 8 + e]) * a1 : 0.f);
+            uint4 val;
+            val.x = pack_bf16x2(f[0], f[1]);
+            val.y = pack_bf16x2(f[2], f[3]);
+            val.z = pack_bf16x2(f[4], f[5]);
+            val.w = pack_bf16x2(f[6], f[7]);
+            *reinterpret_cast<uint4*>(dst + c * 16 + q4 * 8) = val;
+          }
+        }
+        if (g == 0 && half == 0) args.lse2[((long long)b * args.Hq + h) * args.S + qt * ATT_BQ + r] = m + log2f(l_tot);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int HD>
+static int launch_attn_fwd_pp(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttFwdArgs& a,
+                              cudaStream_t st) {
+  auto kern = attn_fwd_pp_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AttFwdPPSmem<HD>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int grid = a.B * a.Hq * (a.S / ATT_BQ);
+  kern<<<grid, ATT_PP_THREADS, AttFwdPPSmem<HD>::TOTAL, st>>>(tq, tk, tv, a);
+  return (int)cudaGetLastError();
+}
+
+template <int HD, int S_BUFS>
+static int launch_attn_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                           const AttFwdArgs& a, cudaStream_t st) {
+  // Default: the single-stream kernel at the top of this file, with four softmax warps and two CTAs per SM at head_dim
+  // 64 and eight softmax warps at head_dim 128 (ADANA_ATT_FWD_SW overrides).  ADANA_ATT_FWD=pp selects the kernel with
+  // two softmax groups on alternate key tiles: its steady state is faster (1758 against 2179 clocks per key tile at
+  // head_dim 128), but with one CTA per SM nothing hides the start and the epilogue of a CTA, and over whole problems
+  // it measures 3 % behind at head_dim 128 and 20 % behind at head_dim 64; it needs a persistent tile loop to pay off.
+  static int sw = -1;
+  if (sw < 0) {
+    const char* f = getenv("ADANA_ATT_FWD");
+    const char* e = getenv("ADANA_ATT_FWD_SW");
+    if (f && f[0] == 'p') sw = 0;
+    else sw = (e && atoi(e) == 8) ? 8 : (e && atoi(e) == 4) ? 4 : (HD == 128 ? 8 : 4);
+  }
+  if (sw == 0) return launch_attn_fwd_pp<HD>(tq, tk, tv, a, st);
+  return sw == 4 ? launch_attn_fwd_sw<HD, S_BUFS, 4>(tq, tk, tv, a, st) : launch_attn_fwd_sw<HD, S_BUFS, 8>(tq, tk, tv, a, st);
 }
 
 }  // namespace adana

