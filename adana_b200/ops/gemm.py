@@ -82,7 +82,10 @@ def gemm(A, B, C, *, M, N, K, a_mn=False, b_mn=False, epi=EPI_BF16, C2=None, R=N
 # nn.Linear GEMMs: x [M,K] (bf16), w [N,K] (bf16, the nn.Linear weight), dy [M,N] (bf16)
 # ----------------------------------------------------------------------------------------------
 def use_cuda(*ts) -> bool:
-    return all(t is None or t.is_cuda for t in ts) and _lib.available()
+    """The tcgen05 path: CUDA tensors whose two GEMM operands (the first two arguments) are bf16; anything else (fp32
+    compute on a GPU included) takes the PyTorch fp32 path of the same op."""
+    return (all(t is None or t.is_cuda for t in ts) and _lib.available()
+            and all(torch.is_tensor(t) and t.dtype == torch.bfloat16 for t in ts[:2]))
 
 
 def linear_fwd(x, w, out=None):
