@@ -18,6 +18,8 @@
 //
 // Replaces the cuBLASLt calls behind nn.Linear in the reference model code
 // (src/models/enoki.py:111,150,176-178; src/models/qwen3.py:104-106,173-175,235).
+#include <cstdlib>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -64,6 +66,27 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   const int r = t - g * per_group;
   mi = first_m + (r % gm);
   ni = r / gm;
+}
+
+// Rows of tiles per raster group.  The tiles that run at the same time (one per CTA or CTA pair) form a block of
+// group_m x (concurrency / group_m) tiles; every operand panel is fetched from DRAM once per block that touches it, so
+// the operand traffic of a sweep is proportional to 1 / rows + 1 / columns of that block: smallest for a square block,
+// and with few tile columns (weight gradients: N / 256 = 9) for a block that spans all of them.
+static int pick_group_m(int tiles_m, int tiles_n, int concurrency) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("ADANA_GEMM_GROUP_M");
+    forced = e ? atoi(e) : 0;
+  }
+  if (forced > 0) return forced;
+  int side = 1;
+  while ((side + 1) * (side + 1) <= concurrency) ++side;
+  if ((side + 1) * (side + 1) - concurrency < concurrency - side * side) ++side;      // nearest square
+  const int gn = tiles_n < side ? tiles_n : side;
+  int gm = concurrency / (gn > 0 ? gn : 1);
+  if (gm < 1) gm = 1;
+  if (gm > tiles_m) gm = tiles_m;
+  return gm;
 }
 
 template <int EPI>
@@ -1144,6 +1167,8 @@ extern "C" int adana_gemm_bf16(const void* A, const void* B, void* C, int M, int
       }
     }
   }
+  args.group_m = pick_group_m(use_pair ? (M + P_BM - 1) / P_BM : args.tiles_m, args.tiles_n,
+                              use_pair ? g_sm_count / 2 : g_sm_count);
 #define ADANA_GEMM_CASE(AM, BMN, E)                                                     \
   if (a_mn == (AM ? 1 : 0) && b_mn == (BMN ? 1 : 0) && epi == E)                        \
     return use_pair ? launch_gemm_pair<AM, BMN, E>(tmA, tmB, args, g_sm_count, stream)  \
