@@ -65,7 +65,7 @@ def linear_ce_ref(h, w, targets, z_coeff, loss_scale, need_grad=True, dw_out=Non
     return out
 
 
-def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out=None, chunk_rows=4096,
+def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out=None, chunk_rows=8192,
               logits_dtype=torch.bfloat16):
     """lm_head GEMM + CE + z-loss + accuracy, forward AND backward in one sweep over row chunks.
 
@@ -74,7 +74,9 @@ def linear_ce(h, w, targets, z_coeff=0.0, loss_scale=1.0, need_grad=True, dw_out
     src/models/chunked_loss.py:68-151) the tcgen05 GEMM writes the chunk in bf16 and the CE kernel turns it into
     dlogits IN PLACE; with fp32 the GEMM writes fp32 logits and the CE kernel writes a separate bf16 dlogits chunk.
     dlogits feed the dgrad GEMM (dh) and the accumulating wgrad GEMM (dw).  loss = (ce_sum + z_coeff*z_sum) / T and
-    the returned gradients are those of `loss_scale * loss`.
+    the returned gradients are those of `loss_scale * loss`.  8192-row chunks measured best at V = 50304, d = 2304
+    (8.6 ms per 16384 tokens against 9.9 ms with 4096 rows, where the fp32 weight gradient is re-read twice as often,
+    and 9.5 ms with one 16384-row chunk).
     """
     T, d = h.shape
     V = w.shape[0]

@@ -124,9 +124,13 @@ def main():
     w = (torch.randn(V, d, device=dev) * 0.02).bfloat16()
     tgt = torch.randint(0, V, (T,), device=dev)
     dwbuf = torch.zeros(V, d, device=dev)
-    ms = timeit([lambda: misc.linear_ce(h, w, tgt, z_coeff=1e-4, loss_scale=1.0 / T, dw_out=dwbuf)], max(4, a.iters // 4))
-    report("linear + cross-entropy + z-loss, forward and both gradients (V = 50304)", ms,
-           T * V * (4 + 4 + 2), flops=3 * 2.0 * T * V * d, note="bytes: the fp32 logits chunk written and read, bf16 dlogits written")
+    for chunk in (4096, 8192, 16384):
+        ms = timeit([lambda: misc.linear_ce(h, w, tgt, z_coeff=1e-4, loss_scale=1.0 / T, dw_out=dwbuf, chunk_rows=chunk)],
+                    max(4, a.iters // 4))
+        report(f"linear + cross-entropy + z-loss, forward and both gradients (V = 50304), {chunk}-row chunks", ms,
+               T * V * 2 * 5 + (T // chunk) * V * d * 8, flops=3 * 2.0 * T * V * d,
+               note="bytes: bf16 logits written, read and rewritten as dlogits, read by two GEMMs; the fp32 weight gradient "
+                    "read and written once per chunk")
     torch.cuda.synchronize()
     _lib.check_status()
 

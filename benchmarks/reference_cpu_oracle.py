@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Loss-curve oracle: trains the small Enoki configuration on CPU with the UNMODIFIED reference classes and writes the
-per-step losses (the source of `tests/golden/enoki3_cpu_reference_losses.json` and of the CPU table in BASELINE.md).
+per-step losses (the source of `tests/golden/enoki3_cpu_reference_losses.json` and of the timed CPU baseline table).
 
     python benchmarks/reference_cpu_oracle.py --opt adana|dana-mk4|dana-star-mk4|adamw [--steps 200]
                                                [--ref_src baseline/_ref/src] [--out losses.json]
