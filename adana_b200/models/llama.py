@@ -1,6 +1,8 @@
 """Llama-style decoder (`--model llama`): RMSNorm (eps `--rmsnorm_eps`), RoPE, fused QKV, SwiGLU MLP
 whose width is 8/3·d rounded up to `--multiple_of`, always-tied embeddings.  Names as in the
-reference (src/models/llama.py:66-215): attn.{c_attn,c_proj}, mlp.{w1,w2,c_proj}.  PyTorch path.
+reference (src/models/llama.py:66-215): attn.{c_attn,c_proj}, mlp.{w1,w2,c_proj}.  Dense models run on the kernel
+engine (RMSNorm, fused q|k|v, RoPE without a per-head norm, SwiGLU over the adjacent w1 | w2, one table as embedding and
+LM head); MoE variants on the PyTorch path.
 """
 from __future__ import annotations
 
@@ -105,6 +107,8 @@ class Llama(BaseLM):
         return n
 
     def forward(self, idx, targets=None, get_logits=False, moe=False, compute_accuracy=False):
+        if self._engine is not None and self._engine.handles(self, idx, targets, get_logits):
+            return self._engine.forward(idx, targets, compute_accuracy=compute_accuracy)
         cfg = self.config
         b, t = idx.shape
         assert t <= cfg.sequence_length, \

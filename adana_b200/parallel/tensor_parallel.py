@@ -40,6 +40,8 @@ import torch.distributed as dist
 TP_RULES = {
     "enoki": {"attn.c_attn.weight": ("rows", 3), "attn.c_proj.weight": ("cols", 1),
               "mlp.c_fc.weight": ("rows", 1), "mlp.c_proj.weight": ("cols", 1)},
+    "llama": {"attn.c_attn.weight": ("rows", 3), "attn.c_proj.weight": ("cols", 1), "mlp.w1.weight": ("rows", 1),
+              "mlp.w2.weight": ("rows", 1), "mlp.c_proj.weight": ("cols", 1)},
     "qwen3": {"attn.q_proj.weight": ("rows", 1), "attn.k_proj.weight": ("rows", 1), "attn.v_proj.weight": ("rows", 1),
               "attn.o_proj.weight": ("cols", 1), "mlp.gate_proj.weight": ("rows", 1), "mlp.up_proj.weight": ("rows", 1),
               "mlp.down_proj.weight": ("cols", 1)},

@@ -193,6 +193,9 @@ class Engine:
                                   for l in self.layouts]
         self._unit_index = {u.layout.name: i for i, u in enumerate(self.units)}
         self.spec = self._block_spec()
+        self.tied = False
+        # plain cross-entropy without the z term and without auxiliary outputs (src/models/llama.py:197-215)
+        self.plain_loss = getattr(model, "arch", "") == "llama"
         if split:
             self._make_slices()
         self.freqs = model.freqs_cis.to(self.device).contiguous()
@@ -298,6 +301,12 @@ class Engine:
                                 mlp_kind="gelu", norm_kind=BK.N.LAYERNORM, qk_kind=qk_kind, gate=False,
                                 eps=1e-5, qk_eps=1e-5, scale=float(getattr(c, "residual_stream_scalar", 1.0)),
                                 seq_len=c.sequence_length)
+        if m.arch == "llama":
+            # RMSNorm, fused q|k|v, RoPE without a per-head norm, SwiGLU (w1 = gate, w2 = up), tied embeddings
+            return BK.BlockSpec(d=c.n_embd, n_head=c.n_head // tp, n_kv_head=c.n_head // tp, hd=hd,
+                                mlp=m.transformer.h[0].mlp.w1.weight.shape[0], mlp_kind="swiglu", norm_kind=BK.N.RMSNORM,
+                                qk_kind=BK.R.NONORM, gate=False, eps=float(getattr(c, "rmsnorm_eps", 1e-5)),
+                                qk_eps=1e-5, scale=1.0, seq_len=c.sequence_length)
         blk = m.transformer.h[0]
         rms = getattr(c, "normalization_layer_type", "rmsnorm") == "rmsnorm"
         eps = float(getattr(c, "rmsnorm_eps", 1e-5)) if rms else 1e-5
@@ -345,8 +354,13 @@ class Engine:
             W, Gd = {}, {}
             if lay.name == "root":
                 for key, suffix in (("lm_head", "lm_head.weight"), ("wte", "transformer.wte.weight")):
+                    if not lay.has(suffix):
+                        continue
                     sl = lay.slot(suffix)
                     W[key], Gd[key] = u.view(u.weights, sl), u.view(u.grads, sl)
+                self.tied = "lm_head" not in W
+                if self.tied:                   # one table serves as embedding and as LM head: both gradients meet in it
+                    W["lm_head"], Gd["lm_head"] = W["wte"], Gd["wte"]
                 sl = lay.slot("transformer.ln_f.weight")
                 W["ln_f"], Gd["ln_f"] = small(sl), u.view(u.grads, sl)
             else:
@@ -364,7 +378,13 @@ class Engine:
                     if u.weights is None:
                         return None, gview                 # gathered: the weight entry is set below
                     return u.weights[first.offset:first.offset + n].view(r, c), gview
-                if self.model.arch == "enoki":
+                if self.model.arch == "llama":
+                    W["qkv"], Gd["qkv"] = fused(["attn.c_attn.weight"], (sp.proj_out, sp.d))
+                    W["o"], Gd["o"] = fused(["attn.c_proj.weight"], (sp.d, sp.n_head * sp.hd))
+                    W["fc"], Gd["fc"] = fused(["mlp.w1.weight", "mlp.w2.weight"], (2 * sp.mlp, sp.d))
+                    W["down"], Gd["down"] = fused(["mlp.c_proj.weight"], (sp.d, sp.mlp))
+                    qn = kn = "attn.no_such_norm.weight"
+                elif self.model.arch == "enoki":
                     W["qkv"], Gd["qkv"] = fused(["attn.c_attn.weight"], (sp.proj_out, sp.d))
                     W["o"], Gd["o"] = fused(["attn.c_proj.weight"], (sp.d, sp.n_head * sp.hd))
                     W["fc"], Gd["fc"] = fused(["mlp.c_fc.weight"], (sp.mlp, sp.d))
@@ -490,11 +510,13 @@ class Engine:
         acc = self.micro_step > 0
         out, dx, dx_lp = BK.head_forward_backward(
             x, None if sample_targets else targets, root.W, root.Gd, sp.norm_kind, sp.eps,
-            0.0 if sample_targets else ecfg.z_loss_coeff, self.loss_scale, self.cdt, need_grad, acc)
+            0.0 if (sample_targets or self.plain_loss) else ecfg.z_loss_coeff, self.loss_scale, self.cdt, need_grad, acc)
         loss = out["loss"]
         aux = {"z_loss": out["z"]}
         hoyer_grad = None
-        if ecfg.hoyer_loss_coeff != 0.0:
+        if self.plain_loss:
+            aux = {}                # (this model family reports no auxiliary terms)
+        elif ecfg.hoyer_loss_coeff != 0.0:
             hv, hoyer_grad = BK.hoyer_value_and_grad(x0, ecfg.hoyer_loss_coeff, self.loss_scale, need_grad)
             aux["hoyer_loss"] = hv
             loss = loss + ecfg.hoyer_loss_coeff * hv
@@ -539,7 +561,7 @@ class Engine:
                     self._reduce_unit(u)
             if pend["hoyer_grad"] is not None:
                 dx += pend["hoyer_grad"]
-            if not acc:
+            if not acc and not self.tied:        # (a tied table already holds the LM head's gradient of this micro-step)
                 root.Gd["wte"].zero_()
             M.embedding_bwd(pend["idx"], dx, root.Gd["wte"])
             root.grads_dirty = True
@@ -877,6 +899,8 @@ class Engine:
                 out[s.name] = full[s.offset:s.offset + s.numel].view(s.shape).clone()
                 if self.tp is not None:          # (collective over tp for the cut matrices)
                     out[s.name] = self.tp.gather_full(s.name, out[s.name])
+                if self.tied and s.name == "transformer.wte.weight" and which == "master":
+                    out["lm_head.weight"] = out[s.name]      # a state dict of tied modules names the tensor twice
         return out
 
     def load_full_param_dict(self, tensors: Dict[str, torch.Tensor], which: str = "master"):

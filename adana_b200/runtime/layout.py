@@ -86,17 +86,20 @@ ENOKI_BLOCK_ORDER = ["attn.c_attn.weight", "attn.c_proj.weight", "mlp.c_fc.weigh
 QWEN3_BLOCK_ORDER = ["attn.q_proj.weight", "attn.k_proj.weight", "attn.v_proj.weight", "attn.o_proj.weight",
                      "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight",
                      "ln_1.weight", "ln_2.weight", "attn.q_norm.weight", "attn.k_norm.weight"]
+LLAMA_BLOCK_ORDER = ["attn.c_attn.weight", "attn.c_proj.weight", "mlp.w1.weight", "mlp.w2.weight", "mlp.c_proj.weight",
+                     "ln_1.weight", "ln_2.weight"]
+BLOCK_ORDERS = {"enoki": ENOKI_BLOCK_ORDER, "qwen3": QWEN3_BLOCK_ORDER, "llama": LLAMA_BLOCK_ORDER}
 ROOT_ORDER = ["lm_head.weight", "transformer.wte.weight", "transformer.ln_f.weight"]
 
 
 def build_layouts(model, world: int) -> List[UnitLayout]:
     """Units in execution order: blocks 0..L-1, then the root unit (last)."""
     arch = getattr(model, "arch", None)
-    if arch not in ("enoki", "qwen3"):
-        raise ValueError(f"kernel engine supports enoki and qwen3 models, got {arch!r}")
+    if arch not in BLOCK_ORDERS:
+        raise ValueError(f"kernel engine supports enoki, qwen3 and llama models, got {arch!r}")
     specs = model.get_parameter_group_specs()
     decay_names = set(specs[0]["params"])
-    order = ENOKI_BLOCK_ORDER if arch == "enoki" else QWEN3_BLOCK_ORDER
+    order = BLOCK_ORDERS[arch]
     units: List[UnitLayout] = []
     for i, blk in enumerate(model.transformer.h):
         prefix = f"transformer.h.{i}."
@@ -109,7 +112,7 @@ def build_layouts(model, world: int) -> List[UnitLayout]:
 
 def engine_supported(model, cfg) -> Optional[str]:
     """None when the kernel engine can run this model, else the reason it cannot."""
-    if getattr(model, "arch", None) not in ("enoki", "qwen3"):
+    if getattr(model, "arch", None) not in BLOCK_ORDERS:
         return f"architecture {type(model).__name__} has no kernel path"
     if getattr(cfg, "bias", False):
         return "bias terms are not supported by the kernel path"
@@ -117,7 +120,7 @@ def engine_supported(model, cfg) -> Optional[str]:
         return "dropout is not supported by the kernel path"
     if getattr(cfg, "moe", False):
         return "MoE blocks run on the PyTorch path"
-    if getattr(cfg, "weight_tying", False) and model.arch != "enoki":
+    if getattr(cfg, "weight_tying", False) and model.arch == "qwen3":
         return "tied embeddings run on the PyTorch path"
     hd = getattr(model, "head_dim", 0)
     if hd % 2:

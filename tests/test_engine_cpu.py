@@ -13,7 +13,7 @@ from adana_b200.runtime.engine import EngineOptimizer, attach
 
 CASES = [("enoki", {}), ("enoki", dict(no_qknorm=True, residual_stream_scalar=0.5, hoyer_loss_coeff=0.01)),
          ("qwen3", dict(elementwise_attn_output_gate=True, n_kv_head=1)),
-         ("qwen3", dict(normalization_layer_type="layernorm"))]
+         ("qwen3", dict(normalization_layer_type="layernorm")), ("llama", dict(multiple_of=32))]
 
 
 def batch(a, seed=0, B=2):
@@ -39,7 +39,9 @@ def test_manual_backward_matches_autograd(name, kw):
     o["loss"].backward()
     assert o["loss"].item() == pytest.approx(o_ref["loss"].item(), rel=1e-5)
     assert o["accuracy"].item() == pytest.approx(o_ref["accuracy"].item())
-    assert o["aux_losses"]["z_loss"].item() == pytest.approx(o_ref["aux_losses"]["z_loss"].item(), rel=1e-4)
+    assert set(o["aux_losses"]) >= set(o_ref["aux_losses"])
+    if "z_loss" in o_ref["aux_losses"]:
+        assert o["aux_losses"]["z_loss"].item() == pytest.approx(o_ref["aux_losses"]["z_loss"].item(), rel=1e-4)
     ref_g = {n: p.grad for n, p in ref.named_parameters()}
     for n, p in m.named_parameters():
         assert torch.allclose(p.grad, ref_g[n], rtol=1e-3, atol=1e-6), n

@@ -22,7 +22,8 @@ def _models(name, **kw):
 
 
 @pytest.mark.parametrize("name,kw", [("enoki", {}), ("qwen3", dict(elementwise_attn_output_gate=True, n_kv_head=2)),
-                                       ("qwen3", dict(normalization_layer_type="layernorm", qkv_dim=128, n_head=2))])
+                                       ("qwen3", dict(normalization_layer_type="layernorm", qkv_dim=128, n_head=2)),
+                                       ("llama", dict(multiple_of=64))])
 def test_engine_grads_match_fp32_reference(name, kw):
     from adana_b200.ops import _lib
     from adana_b200.runtime.engine import attach
