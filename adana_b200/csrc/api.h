@@ -109,7 +109,7 @@ int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, long 
                           int q_off, int q_hstride, int k_off, int k_hstride, const float* wq,
                           const float* wk, const float* freqs, void* dqkv, float* dwq_partial,
                           float* dwk_partial, int n_partial, long long n_tokens, int S, int Hq,
-                          int Hk, int hd, float eps, int kind, void* stream);
+                          int Hk, int hd, float eps, int kind, int dq_is_f32, void* stream);
 int adana_sigmoid_gate_fwd(const void* a, const void* gate, long long gate_row_stride, int gate_off,
                            int gate_hstride, void* out, long long n_tokens, int H, int hd,
                            void* stream);

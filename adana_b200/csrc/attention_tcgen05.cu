@@ -1026,7 +1026,7 @@ struct AttBwdSmem {
 struct AttBwdArgs {
   const float* lse2;      // [B, Hq, S]
   const float* ndelta;    // [B, Hq, S]: -scale * rowsum(dO o O)
-  float* dq_acc;          // [T, Hq, HD] fp32, zero-initialised by the caller
+  float* dq_acc;          // [T, Hq, HD] fp32, cleared by the delta kernel that runs before this one
   __nv_bfloat16* dk;      // [T, Hk, HD]
   __nv_bfloat16* dv;      // base of the v columns in the projection-gradient buffer
   long long lddv;
@@ -1485,7 +1485,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // with one 16-byte load per operand; the sum is a 3- or 4-step shuffle inside the lane group.
 template <int HD>
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
-                                  float* __restrict__ delta, int B, int S, int H, float mul) {
+                                  float* __restrict__ delta, int B, int S, int H, float mul,
+                                  float* __restrict__ dq_zero) {
   constexpr int LPV = HD / 8;
   constexpr int VPW = 32 / LPV;
   const int lane = threadIdx.x & 31;
@@ -1500,6 +1501,10 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const 
     const long long off = it * HD + sub * 8;
     const uint4 ua = *reinterpret_cast<const uint4*>(dout + off);
     const uint4 uo = *reinterpret_cast<const uint4*>(out + off);
+    if (ok && dq_zero) {        // the fp32 dQ accumulator of the same (token, head) vector starts from zero
+      *reinterpret_cast<float4*>(dq_zero + off) = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(dq_zero + off + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const float2 a0 = unpack_bf16x2(ua.x), a1 = unpack_bf16x2(ua.y), a2 = unpack_bf16x2(ua.z), a3 = unpack_bf16x2(ua.w);
     const float2 o0 = unpack_bf16x2(uo.x), o1 = unpack_bf16x2(uo.y), o2 = unpack_bf16x2(uo.z), o3 = unpack_bf16x2(uo.w);
     float acc = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y + a2.x * o2.x + a2.y * o2.y + a3.x * o3.x + a3.y * o3.y;
@@ -1532,8 +1537,8 @@ static int launch_attn_bwd(const CUtensorMap& tq, const CUtensorMap& tdo, const 
 }  // namespace adana
 
 // dout/out [T, Hq*hd] bf16, q [T,Hq,hd], k [T,Hk,hd], v strided as in the forward; lse2 from the
-// forward; delta [B,Hq,S] scratch (written here); dq_acc [T,Hq,hd] fp32 must be zero on entry and
-// holds dQ on exit; dk [T,Hk,hd] bf16; dv written at dvbase with row pitch lddv / head pitch dv_hstride.
+// forward; delta [B,Hq,S] scratch (written here); dq_acc [T,Hq,hd] fp32 is cleared here (by the kernel that computes
+// delta, in the same pass) and holds dQ on exit; dk [T,Hk,hd] bf16; dv written at dvbase with row pitch lddv / head pitch dv_hstride.
 extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, long long ldv, int v_hstride,
                               const void* vbase, const void* out, const float* lse2, float* delta,
                               float* dq_acc, void* dk, long long lddv, int dv_hstride, void* dvbase, int B,
@@ -1548,9 +1553,9 @@ extern "C" int adana_attn_bwd(const void* dout, const void* q, const void* k, lo
     long long blocks = (items + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (hd == 64)
-      attn_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale);
+      attn_delta_kernel<64><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale, dq_acc);
     else
-      attn_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale);
+      attn_delta_kernel<128><<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, S, Hq, -scale, dq_acc);
   }
   CUtensorMap tq, tdo, tk, tv;
   uint32_t box[3] = {64, ATT_BQ, 1};

@@ -138,9 +138,11 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long row_stri
   }
 }
 
-template <int HD, int KIND>
+// DQF32: the query gradient arrives in fp32 (straight from the attention backward's reduce-add accumulator, which saves
+// the pass that would round it to bf16 first)
+template <int HD, int KIND, bool DQF32>
 __global__ void __launch_bounds__(ROPE_THREADS)
-qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+qknorm_rope_bwd_kernel(const void* __restrict__ dq_, const __nv_bfloat16* __restrict__ dk,
                        const __nv_bfloat16* __restrict__ qkv, long long row_stride, int q_off,
                        int q_hstride, int k_off, int k_hstride, const float* __restrict__ wq,
                        const float* __restrict__ wk, const float* __restrict__ freqs,
@@ -168,7 +170,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
     float cs[8];
     load8f(freqs + (long long)(tok % S) * HD + sub * ROPE_EPL, cs);
     const long long row = tok * row_stride + sub * ROPE_EPL;
-    const __nv_bfloat16* dqo = dq + tok * Hq * HD + sub * ROPE_EPL;
+    const __nv_bfloat16* dqo = reinterpret_cast<const __nv_bfloat16*>(dq_) + tok * Hq * HD + sub * ROPE_EPL;
+    const float* dqf = reinterpret_cast<const float*>(dq_) + tok * Hq * HD + sub * ROPE_EPL;
     const __nv_bfloat16* dko = dk + tok * Hk * HD + sub * ROPE_EPL;
     for (int h0 = 0; h0 < Hall; h0 += VPW * U) {
     float x[U][8], d[U][8];
@@ -177,7 +180,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16
     for (int u = 0; u < U; ++u) {
       it[u] = rope_head(h0 + u * VPW + grp, Hq, Hall, q_off, q_hstride, k_off, k_hstride);
       load8(qkv + row + it[u].src, x[u]);
-      load8((it[u].isq ? dqo : dko) + it[u].hh * HD, d[u]);
+      if (DQF32 && it[u].isq) load8f(dqf + it[u].hh * HD, d[u]);
+      else load8((it[u].isq ? dqo : dko) + it[u].hh * HD, d[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -293,7 +297,7 @@ extern "C" int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void*
                                      int k_hstride, const float* wq, const float* wk,
                                      const float* freqs, void* dqkv, float* dwq_partial,
                                      float* dwk_partial, int n_partial, long long n_tokens, int S,
-                                     int Hq, int Hk, int hd, float eps, int kind, void* stream_) {
+                                     int Hq, int Hk, int hd, float eps, int kind, int dq_is_f32, void* stream_) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   if (n_tokens <= 0) return 0;
   if (hd != 64 && hd != 128) return -1;
@@ -302,10 +306,16 @@ extern "C" int adana_qknorm_rope_bwd(const void* dq, const void* dk, const void*
   const int blocks = kind != 2 ? n_partial : 148 * 8;
   const long long active = rope_active_warps(n_tokens, blocks);
 #define RB(HD_, K_)                                                                          \
-  qknorm_rope_bwd_kernel<HD_, K_><<<blocks, ROPE_THREADS, 0, st>>>(                          \
-      (const __nv_bfloat16*)dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv, row_stride, \
-      q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, (__nv_bfloat16*)dqkv, dwq_partial,  \
-      dwk_partial, n_tokens, S, Hq, Hk, eps, active)
+  do {                                                                                       \
+    if (dq_is_f32)                                                                           \
+      qknorm_rope_bwd_kernel<HD_, K_, true><<<blocks, ROPE_THREADS, 0, st>>>(                \
+          dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv, row_stride, q_off, q_hstride, k_off, k_hstride, wq, \
+          wk, freqs, (__nv_bfloat16*)dqkv, dwq_partial, dwk_partial, n_tokens, S, Hq, Hk, eps, active); \
+    else                                                                                     \
+      qknorm_rope_bwd_kernel<HD_, K_, false><<<blocks, ROPE_THREADS, 0, st>>>(               \
+          dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)qkv, row_stride, q_off, q_hstride, k_off, k_hstride, wq, \
+          wk, freqs, (__nv_bfloat16*)dqkv, dwq_partial, dwk_partial, n_tokens, S, Hq, Hk, eps, active); \
+  } while (0)
   if (hd == 64) {
     if (kind == 0) RB(64, 0); else if (kind == 1) RB(64, 1); else RB(64, 2);
   } else {

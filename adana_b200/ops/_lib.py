@@ -60,7 +60,7 @@ def _declare(lib):
         "adana_norm_bwd": [P, I, P, I, P, P, P, P, I, P, I, I, I, I, P, P],
         "adana_colsum_f32": [P, I, I, P, I, P],
         "adana_qknorm_rope_fwd": [P, L, I, I, I, I, P, P, P, P, P, L, I, I, I, I, F, I, P],
-        "adana_qknorm_rope_bwd": [P, P, P, L, I, I, I, I, P, P, P, P, P, P, I, L, I, I, I, I, F, I, P],
+        "adana_qknorm_rope_bwd": [P, P, P, L, I, I, I, I, P, P, P, P, P, P, I, L, I, I, I, I, F, I, I, P],
         "adana_sigmoid_gate_fwd": [P, P, L, I, I, P, L, I, I, P],
         "adana_sigmoid_gate_bwd": [P, P, P, L, I, I, P, P, L, I, I, P],
         "adana_clip_coef": [P, F, F, P, P],

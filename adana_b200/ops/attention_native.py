@@ -28,10 +28,11 @@ def bwd_available() -> bool:
 
 
 def bwd(dout, q, k, vbuf, v_off, v_hstride, B, S, scale, lse2, out, dvbuf):
-    """Returns (dq [T,Hq,hd], dk [T,Hk,hd]) and writes dv into `dvbuf` at the projection's v columns."""
+    """Returns (dq [T,Hq,hd] fp32, dk [T,Hk,hd] bf16) and writes dv into `dvbuf` at the projection's v columns.  dq is
+    the fp32 buffer the kernel's TMA reduce-adds accumulated into; the QK-norm + RoPE backward reads it as it is."""
     T, Hq, hd = q.shape
     Hk = k.shape[1]
-    dq_acc = torch.zeros((T, Hq, hd), dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty((T, Hq, hd), dtype=torch.float32, device=q.device)      # cleared by the delta pass of the kernel call
     dk = torch.empty((T, Hk, hd), dtype=torch.bfloat16, device=q.device)
     delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
     vbase = vbuf.data_ptr() + 2 * v_off
@@ -41,7 +42,7 @@ def bwd(dout, q, k, vbuf, v_off, v_hstride, B, S, scale, lse2, out, dvbuf):
                                    dk.data_ptr(), dvbuf.stride(0), v_hstride, dvbase, B, S, Hq, Hk, hd,
                                    float(scale), _lib.status_buffer(q.device).data_ptr(), _lib.stream_ptr())
     _lib.check_rc(rc, "adana_attn_bwd")
-    return dq_acc.to(torch.bfloat16), dk
+    return dq_acc, dk
 
 
 # ---- forward-mode derivative ------------------------------------------------------------------------------------

@@ -89,7 +89,8 @@ def qknorm_rope_bwd_ref(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, w
 
 def qknorm_rope_bwd(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, S, Hq, Hk, hd,
                     eps=1e-5, kind=LAYERNORM):
-    """Writes dq/dk (in the projection layout) into `dqkv`; returns (dwq, dwk) fp32 or None."""
+    """Writes dq/dk (in the projection layout) into `dqkv`; returns (dwq, dwk) fp32 or None.  `dq` may be fp32 (the
+    attention backward's accumulator as it is) or bf16; `dk` is bf16."""
     T = qkv.shape[0]
     if not (qkv.is_cuda and _lib.available() and qkv.dtype == torch.bfloat16 and hd in (64, 128)):
         return qknorm_rope_bwd_ref(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs,
@@ -104,7 +105,7 @@ def qknorm_rope_bwd(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, w
     rc = lib.adana_qknorm_rope_bwd(
         dq.data_ptr(), dk.data_ptr(), qkv.data_ptr(), qkv.stride(0), q_off, q_hstride, k_off, k_hstride,
         _lib.ptr(wq), _lib.ptr(wk), freqs.data_ptr(), dqkv.data_ptr(), _lib.ptr(pq), _lib.ptr(pk),
-        _PARTIAL, T, S, Hq, Hk, hd, float(eps), int(kind), _lib.stream_ptr())
+        _PARTIAL, T, S, Hq, Hk, hd, float(eps), int(kind), int(dq.dtype == torch.float32), _lib.stream_ptr())
     _lib.check_rc(rc, "adana_qknorm_rope_bwd")
     if kind == NONORM:
         return None, None

@@ -164,6 +164,12 @@ def test_qknorm_rope(hd, kind, gate):
     assert rel_err(dqkv, dref) < 1e-2
     if kind != 2:
         assert rel_err(dwq, dwq_r) < 5e-3 and rel_err(dwk, dwk_r) < 5e-3
+    # the query gradient may arrive in fp32 (the attention backward's accumulator): same values, same result
+    dqkv32 = torch.zeros_like(qkv)
+    dwq32, dwk32 = rope.qknorm_rope_bwd(dq.float(), dk, qkv, dqkv32, *args)
+    assert torch.equal(dqkv32, dqkv)
+    if kind != 2:
+        assert torch.equal(dwq32, dwq) and torch.equal(dwk32, dwk)
 
 
 def test_embedding():
