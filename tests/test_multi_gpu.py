@@ -335,7 +335,8 @@ def test_distributed_muon_chain_over_peers_matches_the_collective_path():
         assert d < 3e-4, (k, d)
 
 
-def _tp_worker(rank, world, tp):
+def _tp_worker(rank, world, tp, replicas=1):
+    """`replicas` > 1 (single process only): the batches of that many data-parallel replicas as accumulated micro-steps."""
     import torch.distributed as dist
 
     from conftest import tiny_args
@@ -372,10 +373,14 @@ def _tp_worker(rank, world, tp):
     m.train()
     losses, norms = [], []
     for step in range(4):
-        g = torch.Generator().manual_seed(1000 * step + (rank // tp if tp > 1 else rank))
-        idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g).to(a.device)
-        out = m(idx, targets=idx.roll(-1, 1))
-        out["loss"].backward()
+        mine = list(range(replicas)) if replicas > 1 else [rank // tp if tp > 1 else rank]
+        for i, rep in enumerate(mine):
+            g = torch.Generator().manual_seed(1000 * step + rep)
+            idx = torch.randint(0, a.vocab_size, (2, a.sequence_length), generator=g).to(a.device)
+            eng.sync_on_backward = i == len(mine) - 1
+            eng.loss_scale = 1.0 / len(mine)
+            out = m(idx, targets=idx.roll(-1, 1))
+            (out["loss"] / len(mine)).backward()
         norms.append(float(eng.grad_norm_and_clip(0.5)))
         opt.step()
         opt.zero_grad()
@@ -407,3 +412,25 @@ def test_tensor_parallel_engine_over_peer_memory_matches_one_gpu():
             assert (got - _t(v)).abs().mean().item() < 3e-4, k
     for k in one["params"]:            # both tp ranks hold bitwise the same replicated state and assemble the same tensors
         assert torch.equal(_t(two[0]["params"][k]), _t(two[1]["params"][k])), k
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_data_by_tensor_parallel_engine_on_four_gpus_matches_one_gpu():
+    """2 data-parallel x 2 tensor-parallel ranks: the flat shards and the gradient reduce-scatter run on a peer-memory plane
+    over each data-parallel pair, the tensor-parallel sums on a second plane over each tp pair; against one GPU that
+    accumulates the two replicas' batches."""
+    from test_distributed_cpu import _spawn, _t
+
+    one = _spawn(_tp_worker, 1, 1, 2)[0]
+    four = _spawn(_tp_worker, 4, 2)
+    for r in range(4):
+        assert four[r]["plane"]
+        for x, y in zip(four[r]["norms"], one["norms"]):
+            assert abs(x - y) / y < 2e-2, (four[r]["norms"], one["norms"])
+        for k, v in one["params"].items():
+            got = _t(four[r]["params"][k])
+            assert tuple(got.shape) == tuple(_t(v).shape)
+            assert (got - _t(v)).abs().mean().item() < 3e-4, k
+    for k in one["params"]:
+        for r in range(1, 4):
+            assert torch.equal(_t(four[0]["params"][k]), _t(four[r]["params"][k])), (k, r)
