@@ -18,21 +18,6 @@ namespace adana {
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_MAXV_LIMIT = 8;  // float4 per thread held in registers -> cols <= 8192
 
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncthreads();
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
-  if (warp == 0) {
-    t = warp_sum(t);
-    if (lane == 0) red[0] = t;
-  }
-  __syncthreads();
-  return red[0];
-}
-
 template <typename T>
 __device__ __forceinline__ float4 load4(const T* p);
 template <>
@@ -59,12 +44,26 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
   *reinterpret_cast<uint2*>(p) = u;
 }
 
+// One barrier per reduction: every warp leaves its partial in one of two slot rows (alternating, so that the next
+// reduction's writes cannot overtake this one's reads) and every thread adds the eight partials itself.
+__device__ __forceinline__ float block_sum_1bar(float v, float (*slots)[NORM_THREADS / 32], int& turn) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) slots[turn][threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int wv = 0; wv < NORM_THREADS / 32; ++wv) t += slots[turn][wv];
+  turn = (turn + 1) % 3;
+  return t;
+}
+
 template <typename TX, typename TY, int KIND, int NORM_MAXV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
                 float eps) {
-  __shared__ float red[32];
+  __shared__ float red[3][NORM_THREADS / 32];
+  int turn = 0;
   const int nv = cols >> 2;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const TX* xr = x + (size_t)row * cols;
@@ -81,7 +80,7 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
     }
     float mean = 0.f, rstd;
     if (KIND == 0) {
-      mean = block_sum(s, red) / cols;
+      mean = block_sum_1bar(s, red, turn) / cols;
       float q = 0.f;
 #pragma unroll
       for (int i = 0; i < NORM_MAXV; ++i) {
@@ -91,9 +90,9 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
           q += a * a + b * b + cc * cc + d * d;
         }
       }
-      rstd = rsqrtf(block_sum(q, red) / cols + eps);
+      rstd = rsqrtf(block_sum_1bar(q, red, turn) / cols + eps);
     } else {
-      rstd = rsqrtf(block_sum(s, red) / cols + eps);
+      rstd = rsqrtf(block_sum_1bar(s, red, turn) / cols + eps);
     }
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[row] = mean;
