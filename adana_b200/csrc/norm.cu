@@ -46,23 +46,26 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
 
 // One barrier per reduction: every warp leaves its partial in one of two slot rows (alternating, so that the next
 // reduction's writes cannot overtake this one's reads) and every thread adds the eight partials itself.
-__device__ __forceinline__ float block_sum_1bar(float v, float (*slots)[NORM_THREADS / 32], int& turn) {
+template <int NT>
+__device__ __forceinline__ float block_sum_1bar(float v, float (*slots)[NT / 32], int& turn) {
   v = warp_sum(v);
   if ((threadIdx.x & 31) == 0) slots[turn][threadIdx.x >> 5] = v;
   __syncthreads();
   float t = 0.f;
 #pragma unroll
-  for (int wv = 0; wv < NORM_THREADS / 32; ++wv) t += slots[turn][wv];
+  for (int wv = 0; wv < NT / 32; ++wv) t += slots[turn][wv];
   turn = (turn + 1) % 3;
   return t;
 }
 
-template <typename TX, typename TY, int KIND, int NORM_MAXV>
-__global__ void __launch_bounds__(NORM_THREADS)
+// NT threads per CTA: 256, or 192 when a row is a multiple of 192 x 4 elements (768, 1536, 2304 columns), so that no lane
+// idles in the last pass over the row.
+template <typename TX, typename TY, int KIND, int NORM_MAXV, int NT>
+__global__ void __launch_bounds__(NT)
 norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
                 float eps) {
-  __shared__ float red[3][NORM_THREADS / 32];
+  __shared__ float red[3][NT / 32];
   int turn = 0;
   const int nv = cols >> 2;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -71,7 +74,7 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) {
         v[i] = load4<TX>(xr + c * 4);
         s += (KIND == 0) ? (v[i].x + v[i].y + v[i].z + v[i].w)
@@ -80,19 +83,19 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
     }
     float mean = 0.f, rstd;
     if (KIND == 0) {
-      mean = block_sum_1bar(s, red, turn) / cols;
+      mean = block_sum_1bar<NT>(s, red, turn) / cols;
       float q = 0.f;
 #pragma unroll
       for (int i = 0; i < NORM_MAXV; ++i) {
-        const int c = threadIdx.x + i * NORM_THREADS;
+        const int c = threadIdx.x + i * NT;
         if (c < nv) {
           const float a = v[i].x - mean, b = v[i].y - mean, cc = v[i].z - mean, d = v[i].w - mean;
           q += a * a + b * b + cc * cc + d * d;
         }
       }
-      rstd = rsqrtf(block_sum_1bar(q, red, turn) / cols + eps);
+      rstd = rsqrtf(block_sum_1bar<NT>(q, red, turn) / cols + eps);
     } else {
-      rstd = rsqrtf(block_sum_1bar(s, red, turn) / cols + eps);
+      rstd = rsqrtf(block_sum_1bar<NT>(s, red, turn) / cols + eps);
     }
     if (threadIdx.x == 0) {
       if (mean_out) mean_out[row] = mean;
@@ -101,7 +104,7 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
     TY* yr = y + (size_t)row * cols;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) {
         const float4 ww = *reinterpret_cast<const float4*>(w + c * 4);
         float4 o;
@@ -117,15 +120,15 @@ norm_fwd_kernel(const TX* __restrict__ x, const float* __restrict__ w, TY* __res
 
 // Registers decide how many rows an SM has in flight: only dy, x and the old dx of the row are held across the
 // reduction (g and xhat are recomputed after it), which fits three CTAs of 256 threads per SM for cols <= 3072.
-template <typename TDY, typename TX, int KIND, int NORM_MAXV>
-__global__ void __launch_bounds__(NORM_THREADS, NORM_MAXV <= 3 ? 3 : 1)
+template <typename TDY, typename TX, int KIND, int NORM_MAXV, int NT>
+__global__ void __launch_bounds__(NT, NORM_MAXV <= 3 ? (NT == 192 ? 4 : 3) : 1)
 norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const float* __restrict__ w,
                 const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                 float* __restrict__ dx, int accumulate_dx, float* __restrict__ dw_partial, int rows,
                 int cols, __nv_bfloat16* __restrict__ dx16) {
   // per-row partial sums of the warps, double-buffered by row parity so that one barrier per row
   // separates the writes from the reads and the next row's writes cannot overtake them
-  __shared__ float2 red[2][NORM_THREADS / 32];
+  __shared__ float2 red[2][NT / 32];
   const int nv = cols >> 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float4 dwacc[NORM_MAXV];
@@ -133,7 +136,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
 #pragma unroll
   for (int i = 0; i < NORM_MAXV; ++i) {
     dwacc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int c = threadIdx.x + i * NORM_THREADS;
+    const int c = threadIdx.x + i * NT;
     wreg[i] = (c < nv) ? *reinterpret_cast<const float4*>(w + c * 4) : make_float4(0, 0, 0, 0);
   }
   int parity = 0;
@@ -148,7 +151,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     float4 dv[NORM_MAXV], xv[NORM_MAXV];
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) {
         dv[i] = load4<TDY>(dyr + c * 4);
         xv[i] = load4<TX>(xr + c * 4);
@@ -158,7 +161,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) {
         const float4 d = dv[i];
         const float4 xh = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
@@ -178,7 +181,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     __syncthreads();
     float t1 = 0.f, t2 = 0.f;
 #pragma unroll
-    for (int wv = 0; wv < NORM_THREADS / 32; ++wv) {
+    for (int wv = 0; wv < NT / 32; ++wv) {
       const float2 t = red[parity][wv];
       t1 += t.x;
       t2 += t.y;
@@ -187,7 +190,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     const float m1 = (KIND == 0) ? t1 / cols : 0.f;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) {
         const float4 d = dv[i];
         const float4 xh = make_float4((xv[i].x - mean) * rstd, (xv[i].y - mean) * rstd, (xv[i].z - mean) * rstd,
@@ -209,7 +212,7 @@ norm_bwd_kernel(const TDY* __restrict__ dy, const TX* __restrict__ x, const floa
     float* out = dw_partial + (size_t)blockIdx.x * cols;
 #pragma unroll
     for (int i = 0; i < NORM_MAXV; ++i) {
-      const int c = threadIdx.x + i * NORM_THREADS;
+      const int c = threadIdx.x + i * NT;
       if (c < nv) *reinterpret_cast<float4*>(out + c * 4) = dwacc[i];
     }
   }
@@ -259,6 +262,12 @@ static int norm_grid(int rows, int per_sm) {
   return rows < cap ? rows : cap;
 }
 
+// passes of 192 threads over a row when that divides it exactly and fits three passes, else 0
+static int fits_192(int cols) {
+  const int nv = cols / 4;
+  return (nv % 192 == 0 && nv / 192 >= 1 && nv / 192 <= 3) ? nv / 192 : 0;
+}
+
 // number of float4 per thread needed to hold one row in registers
 static int maxv_for(int cols) {
   const int need = (cols / 4 + NORM_THREADS - 1) / NORM_THREADS;
@@ -272,7 +281,12 @@ static int maxv_for(int cols) {
 template <typename TX, typename TY, int KIND>
 static void launch_norm_fwd(int mv, int grid, cudaStream_t st, const void* x, const float* w, void* y,
                             float* mean, float* rstd, int rows, int cols, float eps) {
-#define NF(V) norm_fwd_kernel<TX, TY, KIND, V><<<grid, NORM_THREADS, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, rows, cols, eps)
+#define NF(V) norm_fwd_kernel<TX, TY, KIND, V, NORM_THREADS><<<grid, NORM_THREADS, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, rows, cols, eps)
+#define NF192(V) norm_fwd_kernel<TX, TY, KIND, V, 192><<<grid, 192, 0, st>>>((const TX*)x, w, (TY*)y, mean, rstd, rows, cols, eps)
+  if (int v192 = fits_192(cols)) {
+    if (v192 == 1) NF192(1); else if (v192 == 2) NF192(2); else NF192(3);
+    return;
+  }
   switch (mv) {
     case 1: NF(1); break;
     case 2: NF(2); break;
@@ -281,13 +295,19 @@ static void launch_norm_fwd(int mv, int grid, cudaStream_t st, const void* x, co
     default: NF(8); break;
   }
 #undef NF
+#undef NF192
 }
 
 template <typename TD, typename TX, int KIND>
 static void launch_norm_bwd(int mv, int grid, cudaStream_t st, const void* dy, const void* x, const float* w,
                             const float* mean, const float* rstd, float* dx, int acc, float* dwp, int rows,
                             int cols, void* dx16) {
-#define NB(V) norm_bwd_kernel<TD, TX, KIND, V><<<grid, NORM_THREADS, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, rstd, dx, acc, dwp, rows, cols, (__nv_bfloat16*)dx16)
+#define NB(V) norm_bwd_kernel<TD, TX, KIND, V, NORM_THREADS><<<grid, NORM_THREADS, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, rstd, dx, acc, dwp, rows, cols, (__nv_bfloat16*)dx16)
+#define NB192(V) norm_bwd_kernel<TD, TX, KIND, V, 192><<<grid, 192, 0, st>>>((const TD*)dy, (const TX*)x, w, mean, rstd, dx, acc, dwp, rows, cols, (__nv_bfloat16*)dx16)
+  if (int v192 = fits_192(cols)) {
+    if (v192 == 1) NB192(1); else if (v192 == 2) NB192(2); else NB192(3);
+    return;
+  }
   switch (mv) {
     case 1: NB(1); break;
     case 2: NB(2); break;
@@ -296,6 +316,7 @@ static void launch_norm_bwd(int mv, int grid, cudaStream_t st, const void* dy, c
     default: NB(8); break;
   }
 #undef NB
+#undef NB192
 }
 
 extern "C" int adana_norm_fwd(const void* x, int x_is_bf16, const float* w, void* y,

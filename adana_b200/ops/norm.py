@@ -10,7 +10,8 @@ import torch
 from . import _lib
 
 LAYERNORM, RMSNORM = 0, 1
-_PARTIAL_ROWS = 148 * 3   # CTAs of the backward kernel: three of them fit an SM at cols <= 3072
+_PARTIAL_ROWS = 148 * 3   # CTAs of the backward kernel: three of 256 threads fit an SM at cols <= 3072 ...
+_PARTIAL_ROWS_192 = 148 * 4   # ... four of the 192-thread variant that rows of 768, 1536 or 2304 columns take
 _MAX_COLS = 8192
 
 
@@ -83,7 +84,7 @@ def norm_bwd(dy, x, w, mean, rstd, kind=LAYERNORM, dx_accum=None, dw_out=None, d
     dy = dy.contiguous()
     x = x.contiguous()
     dx = dx_accum if dx_accum is not None else torch.empty((rows, cols), dtype=torch.float32, device=x.device)
-    nparts = min(_PARTIAL_ROWS, rows)
+    nparts = min(_PARTIAL_ROWS_192 if cols in (768, 1536, 2304) else _PARTIAL_ROWS, rows)
     partial = torch.empty((nparts, cols), dtype=torch.float32, device=x.device)
     lib = _lib.lib()
     rc = lib.adana_norm_bwd(dy.data_ptr(), int(dy.dtype == torch.bfloat16), x.data_ptr(),

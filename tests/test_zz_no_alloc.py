@@ -57,7 +57,8 @@ def test_static_scratch_matches_existing_entry_point_twice_in_a_row(kind):
         want_dx, want_dw = norm.norm_bwd(dy, x, w, mean, rstd, kind=kind)
         torch.cuda.synchronize()
         assert torch.allclose(dx, want_dx, rtol=1e-6, atol=1e-7)
-        assert torch.allclose(dw, want_dw, rtol=1e-6, atol=1e-6)
+        # (the two entry points cut the rows into different numbers of partial sums: equal up to fp32 summation order)
+        assert torch.allclose(dw, want_dw, rtol=1e-5, atol=1e-4)
         ref_dx, ref_dw = norm.norm_bwd_ref(dy, x, w, mean, rstd, kind)      # plain PyTorch fp32 of the same op
         assert torch.allclose(dx, ref_dx, rtol=1e-3, atol=1e-4)
         assert torch.allclose(dw, ref_dw, rtol=1e-3, atol=2e-2)
@@ -77,7 +78,7 @@ def test_static_scratch_accumulates_and_rejects_oversize():
     want_dx, want_dw = norm.norm_bwd(dy, x, w, mean, rstd, kind=0)
     torch.cuda.synchronize()
     assert torch.allclose(dx, want_dx + 1.0, rtol=1e-5, atol=1e-6)
-    assert torch.allclose(dw, want_dw + 2.0, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(dw, want_dw + 2.0, rtol=1e-5, atol=1e-4)
     # beyond the built-in scratch: refused before any launch, outputs untouched
     before = dw.clone()
     big = MAX_COLS + 4
@@ -104,7 +105,7 @@ def test_static_scratch_rmsnorm_without_mean_and_empty_batch():
     want_dx, want_dw = norm.norm_bwd(dy, x, w, mean, rstd, kind=1)
     torch.cuda.synchronize()
     assert torch.allclose(dx, want_dx, rtol=1e-6, atol=1e-7)
-    assert torch.allclose(dw, want_dw, rtol=1e-6, atol=1e-6)
+    assert torch.allclose(dw, want_dw, rtol=1e-5, atol=1e-4)
     # LayerNorm does read it: NULL is refused
     assert fn(dy.data_ptr(), 1, x.data_ptr(), 0, w.data_ptr(), None, rstd.data_ptr(), dx.data_ptr(), 0,
               dw.data_ptr(), 0, rows, cols, 0, None, stream) == -22
