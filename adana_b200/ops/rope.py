@@ -88,13 +88,22 @@ def qknorm_rope_bwd_ref(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, w
 
 
 def qknorm_rope_bwd(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs, S, Hq, Hk, hd,
-                    eps=1e-5, kind=LAYERNORM):
+                    eps=1e-5, kind=LAYERNORM, dw_out=None, dw_accumulate=False):
     """Writes dq/dk (in the projection layout) into `dqkv`; returns (dwq, dwk) fp32 or None.  `dq` may be fp32 (the
-    attention backward's accumulator as it is) or bf16; `dk` is bf16."""
+    attention backward's accumulator as it is) or bf16; `dk` is bf16.  With `dw_out = (dwq, dwk)` (fp32 [hd] each) the
+    weight gradients are folded straight into those buffers (added when `dw_accumulate`) and are what is returned."""
     T = qkv.shape[0]
     if not (qkv.is_cuda and _lib.available() and qkv.dtype == torch.bfloat16 and hd in (64, 128)):
-        return qknorm_rope_bwd_ref(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs,
-                                   S, Hq, Hk, hd, eps, kind)
+        dwq, dwk = qknorm_rope_bwd_ref(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, wk, freqs,
+                                       S, Hq, Hk, hd, eps, kind)
+        if dw_out is not None and dwq is not None:
+            for val, out in ((dwq, dw_out[0]), (dwk, dw_out[1])):
+                if dw_accumulate:
+                    out += val
+                else:
+                    out.copy_(val)
+            return dw_out
+        return dwq, dwk
     assert dqkv.stride(0) == qkv.stride(0)
     lib = _lib.lib()
     if kind != NONORM:
@@ -109,4 +118,10 @@ def qknorm_rope_bwd(dq, dk, qkv, dqkv, q_off, q_hstride, k_off, k_hstride, wq, w
     _lib.check_rc(rc, "adana_qknorm_rope_bwd")
     if kind == NONORM:
         return None, None
+    if dw_out is not None:
+        # the deterministic column-sum kernel of the norm backward folds the per-CTA partial rows
+        for part, out in ((pq, dw_out[0]), (pk, dw_out[1])):
+            _lib.check_rc(lib.adana_colsum_f32(part.data_ptr(), _PARTIAL, hd, out.data_ptr(), int(dw_accumulate),
+                                               _lib.stream_ptr()), "adana_colsum_f32")
+        return dw_out
     return pq.sum(0), pk.sum(0)

@@ -152,10 +152,11 @@ def block_backward(dx, dx_lp, sv, W, Gd: Dict[str, torch.Tensor], sp: BlockSpec,
     else:
         dy = dyg
     dq, dk = A.attention_bwd(dy, sv["q"], sv["k"], qkv, sp.v_off, sp.hd, B, S, sv["actx"], dqkv)
+    fold = tp is None and "q_norm" in Gd        # (under tensor parallelism the two gradients are first summed over tp)
     dwq, dwk = R.qknorm_rope_bwd(dq, dk, qkv, dqkv, 0, sp.q_hstride, sp.k_off, sp.hd, W.get("q_norm"),
                                  W.get("k_norm"), freqs, S, sp.n_head, sp.n_kv_head, sp.hd, sp.qk_eps,
-                                 sp.qk_kind)
-    if dwq is not None:
+                                 sp.qk_kind, dw_out=(Gd["q_norm"], Gd["k_norm"]) if fold else None, dw_accumulate=acc)
+    if dwq is not None and not fold:
         if tp is not None:          # the per-head norm weights are shared by all heads: their gradient sums over tp
             both = tp.all_reduce_(torch.cat([dwq.reshape(-1), dwk.reshape(-1)]))
             dwq, dwk = both[:dwq.numel()].view_as(dwq), both[dwq.numel():].view_as(dwk)
