@@ -511,20 +511,26 @@ extern "C" int adana_p2p_reduce_scatter(const unsigned long long* grad_ptrs, int
 // Largest grid of the gradient collectives that run beside the backward GEMMs.  They have a whole block's backward to
 // hide behind (only the last unit's reduction is exposed), so the grid is sized for little interference rather than for
 // link speed: on eight GPUs the flagship step took 2179.7 ms with 16 CTAs against 2219.8 ms with 64 (the same step on
-// one GPU of such a box: 2171.4 ms), the forward + backward phase alone 2169 against 2209 ms.
-static int comm_cta_cap() {
-  static int cap = -1;
-  if (cap < 0) {
+// one GPU of such a box: 2171.4 ms), the forward + backward phase alone 2169 against 2209 ms.  A thread keeps one
+// 16-byte load per rank in flight, so the cap is given for eight ranks and grows as the ranks get fewer (16 at eight,
+// 32 at four, 64 at two, where 64 was measured at 2176.5 ms): the bytes in flight on the links stay the same.
+// ADANA_COMM_CTAS sets the cap itself, for every world size.
+static int comm_cta_cap(int world) {
+  static int forced = -1;
+  if (forced < 0) {
     const char* e = getenv("ADANA_COMM_CTAS");
-    cap = e ? atoi(e) : 16;
-    if (cap < 1) cap = 1;
-    if (cap > 148 * 8) cap = 148 * 8;
+    forced = e ? atoi(e) : 0;
+    if (forced < 0) forced = 0;
+    if (forced > 148 * 8) forced = 148 * 8;
   }
-  return cap;
+  if (forced > 0) return forced;
+  const int w = world < 1 ? 1 : world;
+  const int cap = 16 * MAX_RANKS / w;
+  return cap > 128 ? 128 : cap;
 }
-static int capped_grid(long long work_items) {
+static int capped_grid(long long work_items, int world) {
   long long b = (work_items + 255) / 256;
-  const long long cap = comm_cta_cap();
+  const long long cap = comm_cta_cap(world);
   return (int)(b < 1 ? 1 : (b < cap ? b : cap));
 }
 
@@ -545,7 +551,7 @@ extern "C" int adana_p2p_reduce_scatter_flag(const unsigned long long* src_ptrs,
   if (world < 1 || world > MAX_RANKS || (n & 7) || (shard_off & 7)) return -1;
   if (n == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  const int grid = capped_grid(n / 8);
+  const int grid = capped_grid(n / 8, world);
   const PeerPtrs src = make_ptrs(src_ptrs, world);
   const uint32_t* fl = reinterpret_cast<const uint32_t*>(my_flags);
   if (wire_bf16)
@@ -564,7 +570,7 @@ extern "C" int adana_p2p_all_reduce_flag(const unsigned long long* src_ptrs, int
   if (world < 1 || world > MAX_RANKS || (n & 7) || (slice_off & 7)) return -1;
   if (n == 0) return 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
-  const int grid = capped_grid(n / 8);
+  const int grid = capped_grid(n / 8, world);
   const PeerPtrs src = make_ptrs(src_ptrs, world), dst = make_ptrs(dst_ptrs, world);
   const uint32_t* fl = reinterpret_cast<const uint32_t*>(my_flags);
   if (wire_bf16)
