@@ -17,6 +17,7 @@ numbers come from `adana_b200.analysis`; the drawing needs no plotting package: 
 from __future__ import annotations
 
 import argparse
+import html
 import json
 import math
 from pathlib import Path
@@ -30,12 +31,13 @@ PALETTE = ["#1f77b4", "#d62728", "#2ca02c", "#ff7f0e", "#9467bd", "#8c564b", "#1
 class LineChart:
     """A small SVG line chart: `add(x, y, label)` any number of series, then `save(path)`."""
 
-    def __init__(self, title="", xlabel="", ylabel="", logx=False, logy=False, width=760, height=480):
+    def __init__(self, title="", xlabel="", ylabel="", logx=False, logy=False, width=760, height=480, yticks=None):
         self.title, self.xlabel, self.ylabel, self.logx, self.logy = title, xlabel, ylabel, logx, logy
         self.w, self.h = width, height
         self.series: List[dict] = []
+        self.yticks = yticks            # [(position, label)] in place of the computed ticks (transformed axes)
 
-    def add(self, x, y, label="", color=None, markers=False, dashed=False):
+    def add(self, x, y, label="", color=None, markers=False, dashed=False, line=True, opacity=1.0, width=1.6):
         x, y = np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64)
         ok = np.isfinite(x) & np.isfinite(y)
         if self.logx:
@@ -43,8 +45,14 @@ class LineChart:
         if self.logy:
             ok &= y > 0
         self.series.append(dict(x=x[ok], y=y[ok], label=label, color=color or PALETTE[len(self.series) % len(PALETTE)],
-                                markers=markers, dashed=dashed))
+                                markers=markers, dashed=dashed, line=line, opacity=opacity, width=width))
         return self
+
+    def hline(self, y, label="", color="#888888", dashed=True):
+        """Horizontal line across the range of the series added so far."""
+        have = [s["x"] for s in self.series if len(s["x"])]
+        xs = np.concatenate(have) if have else np.array([1.0 if self.logx else 0.0, 10.0 if self.logx else 1.0])
+        return self.add([xs.min(), xs.max()], [y, y], label, color, dashed=dashed)
 
     @staticmethod
     def _ticks(lo, hi, log):
@@ -80,27 +88,31 @@ class LineChart:
         out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{self.w}" height="{self.h}" font-family="sans-serif" font-size="12">',
                f'<rect width="{self.w}" height="{self.h}" fill="white"/>',
                f'<rect x="{L}" y="{T}" width="{pw}" height="{ph}" fill="none" stroke="#333"/>',
-               f'<text x="{L + pw / 2}" y="20" text-anchor="middle" font-size="14">{self.title}</text>',
-               f'<text x="{L + pw / 2}" y="{self.h - 12}" text-anchor="middle">{self.xlabel}</text>',
-               f'<text x="16" y="{T + ph / 2}" text-anchor="middle" transform="rotate(-90 16 {T + ph / 2})">{self.ylabel}</text>']
+               f'<text x="{L + pw / 2}" y="20" text-anchor="middle" font-size="14">{html.escape(self.title)}</text>',
+               f'<text x="{L + pw / 2}" y="{self.h - 12}" text-anchor="middle">{html.escape(self.xlabel)}</text>',
+               f'<text x="16" y="{T + ph / 2}" text-anchor="middle" transform="rotate(-90 16 {T + ph / 2})">{html.escape(self.ylabel)}</text>']
         fmt = lambda v: f"{v:.3g}"
         for t in self._ticks(x0, x1, self.logx):
             if x0 <= t <= x1:
                 out.append(f'<line x1="{fx(t):.1f}" y1="{T}" x2="{fx(t):.1f}" y2="{T + ph}" stroke="#ddd"/>')
                 out.append(f'<text x="{fx(t):.1f}" y="{T + ph + 16}" text-anchor="middle">{fmt(t)}</text>')
-        for t in self._ticks(y0, y1, self.logy):
+        for t, lab in (self.yticks or [(t, fmt(t)) for t in self._ticks(y0, y1, self.logy)]):
             if y0 <= t <= y1:
                 out.append(f'<line x1="{L}" y1="{fy(t):.1f}" x2="{L + pw}" y2="{fy(t):.1f}" stroke="#ddd"/>')
-                out.append(f'<text x="{L - 6}" y="{fy(t) + 4:.1f}" text-anchor="end">{fmt(t)}</text>')
+                out.append(f'<text x="{L - 6}" y="{fy(t) + 4:.1f}" text-anchor="end">{html.escape(str(lab))}</text>')
         for i, s in enumerate(pts):
             d = " ".join(f"{fx(a):.1f},{fy(b):.1f}" for a, b in zip(s["x"], s["y"]))
             dash = ' stroke-dasharray="6 4"' if s["dashed"] else ""
-            out.append(f'<polyline points="{d}" fill="none" stroke="{s["color"]}" stroke-width="1.6"{dash}/>')
-            if s["markers"]:
+            if s["line"]:
+                out.append(f'<polyline points="{d}" fill="none" stroke="{s["color"]}" stroke-width="{s["width"]:.2g}" '
+                           f'stroke-opacity="{s["opacity"]:.2g}"{dash}/>')
+            if s["markers"] or not s["line"]:
                 out += [f'<circle cx="{fx(a):.1f}" cy="{fy(b):.1f}" r="3" fill="{s["color"]}"/>' for a, b in zip(s["x"], s["y"])]
-            ly = T + 14 + 18 * i
+            if not s["label"]:
+                continue
+            ly = T + 14 + 18 * sum(1 for q in pts[:i] if q["label"])
             out.append(f'<line x1="{L + pw + 12}" y1="{ly - 4}" x2="{L + pw + 34}" y2="{ly - 4}" stroke="{s["color"]}" stroke-width="2"{dash}/>')
-            out.append(f'<text x="{L + pw + 40}" y="{ly}">{s["label"]}</text>')
+            out.append(f'<text x="{L + pw + 40}" y="{ly}">{html.escape(s["label"])}</text>')
         out.append("</svg>")
         return "\n".join(out)
 
