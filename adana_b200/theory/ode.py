@@ -14,6 +14,17 @@ O(d).  Same scheme and coefficients as the reference's `ode_resolvent_log_implic
 here the per-mode systems are one batched `numpy.linalg.solve` instead of a hand-expanded inverse, and the loop
 is plain NumPy.  `adaptive` divides g3 ('adam') or g1 ('rmsprop_dana') by sqrt(2 risk) as a stand-in for the
 gradient norm.  Returns times t and TWICE the risk, as in the paper's plots.
+
+Options of the schedule experiments (jax/kappa_sweep_plot.py:76-222, dynamical_schedule_plot.py:68-200,
+danastar_schedule_plot.py:70-222):
+  momentum=True          also return sum_j sigma_j, the squared momentum norm ||y||^2, at every time
+  risk_renormalized      "DanaStar" scaling: g2 and g3 are divided by sqrt(2 risk) at every step
+  dynamic_g3="ratio"     g3(t) is multiplied by min(2 risk / (2 ||y||^2), 1): momentum is trusted only while the risk
+                         is larger than the momentum's energy
+  dynamic_g3="inv_sqrt_risk"   g3(t) is divided by sqrt(2 risk) (on top of `risk_renormalized`, if that is set)
+  dynamic_g3=(A, B, k0)  g3(t) is multiplied by (2 risk)^A (||y||^2)^B (1+t)^k0 clipped to [1, 1+t]: a kappa
+                         schedule read off the trajectory
+  shifted_clock          g1, g2 and delta are read at t + 1 and g3 at t, as those scripts do
 """
 from __future__ import annotations
 
@@ -70,22 +81,39 @@ def _coefficients(lam, g1, g2, g3, dl, batch, approximate):
 
 
 def solve_risk_ode(inputs: ODEInputs, hp: DanaHparams, batch: int, t_max: float, dt: float = 1e-2,
-                   approximate: bool = False, adaptive: Optional[str] = None):
+                   approximate: bool = False, adaptive: Optional[str] = None, momentum: bool = False,
+                   risk_renormalized: bool = False, dynamic_g3=None, shifted_clock: bool = False):
     lam = np.asarray(inputs.eigs_K, dtype=np.float64)
     state = np.stack([inputs.rho_init, inputs.sigma_init, inputs.chi_init], axis=1).astype(np.float64)  # [d,3]
     two_r_inf = 2.0 * inputs.risk_infinity
     s_grid = np.arange(0.0, np.log(t_max), dt)
     two_risk = two_r_inf + float(lam @ state[:, 0])
     out = np.empty(len(s_grid))
+    mom_out = np.empty(len(s_grid))
+    mom = float(state[:, 1].sum())
     eye = np.eye(3)[None]
     for i, s in enumerate(s_grid):
         out[i] = two_risk
+        mom_out[i] = mom
         clock = np.exp(s + dt)             # d t / d s at the end of the step
         t = clock - 1.0
+        ts = clock if shifted_clock else t
         gn = np.sqrt(two_risk) if adaptive else 1.0
-        g1 = hp.g1(t) / (gn if adaptive == "rmsprop_dana" else 1.0)
+        g1 = hp.g1(ts) / (gn if adaptive == "rmsprop_dana" else 1.0)
         g3 = hp.g3(t) / (gn if adaptive == "adam" else 1.0)
-        om, gamma = _coefficients(lam, g1, hp.g2(t), g3, hp.delta(t), batch, approximate)
+        g2 = hp.g2(ts)
+        if dynamic_g3 == "ratio":
+            g3 *= min(two_risk / (2.0 * mom + 1e-10), 1.0)
+        elif dynamic_g3 == "inv_sqrt_risk":
+            g3 /= np.sqrt(two_risk)
+        elif dynamic_g3 is not None:
+            pa, pb, k0 = dynamic_g3
+            m_eff = mom if mom != 0.0 else 1.0
+            g3 *= min(max(two_risk ** pa * m_eff ** pb * np.exp(k0 * s), 1.0), np.exp(s))
+        if risk_renormalized:
+            scale = 1.0 / np.sqrt(two_risk + 1e-10)
+            g2, g3 = g2 * scale, g3 * scale
+        om, gamma = _coefficients(lam, g1, g2, g3, hp.delta(ts), batch, approximate)
         h = dt * clock
         A = eye - h * om                                              # [d,3,3]
         force = gamma[None, :] * lam[:, None]                         # [d,3]
@@ -96,4 +124,7 @@ def solve_risk_ode(inputs: ODEInputs, hp: DanaHparams, batch: int, t_max: float,
         coupling = h * float(lam @ x[:, 0]) / (1.0 - h * float(lam @ y[:, 0]))
         state = x + coupling * y
         two_risk = two_r_inf + float(lam @ state[:, 0])
+        mom = float(state[:, 1].sum())
+    if momentum:
+        return np.exp(s_grid) - 1.0, out, mom_out
     return np.exp(s_grid) - 1.0, out

@@ -4,6 +4,7 @@ consistency: fixed points satisfy their equations, densities integrate to what t
 import json
 
 import numpy as np
+import pytest
 
 from adana_b200 import theory as T
 from adana_b200.theory import deterministic as D
@@ -75,3 +76,94 @@ def test_generators_write_their_json(tmp_path):
     s = G.main(["spectra", "--v", "300", "--d", "60", "--out", str(tmp_path / "s.json")])
     assert s["kappa"] > 0 and s["lambda_min"] > 0 and len(s["xs"]) == len(s["density"])
     assert json.loads((tmp_path / "s.json").read_text())["limit_loss"] == s["limit_loss"]
+
+
+# ---- schedule experiments on the risk ODE ------------------------------------------------------------------------------
+def test_ode_options_momentum_renormalisation_and_dynamic_g3():
+    from adana_b200.theory import schedule_studies as S
+    from adana_b200.theory.ode import DanaHparams, solve_risk_ode
+
+    inp = S.ode_inputs(0.7, 0.5, 320, 80)
+    lr = min(1.0, 1 / S.population_trace(0.7, 320))
+    hp = DanaHparams(S.const(1.0), S.const(0.5 * lr), S.const(0.05 * lr), S.delta_schedule(0.7, 0.5))
+    t0, r0 = solve_risk_ode(inp, hp, 1, 1e3, 2e-2)
+    t1, r1, m1 = solve_risk_ode(inp, hp, 1, 1e3, 2e-2, momentum=True)
+    np.testing.assert_array_equal(r0, r1)                     # asking for the momentum does not change the risk
+    assert m1[0] == 0.0 and np.all(m1[1:] > 0) and len(m1) == len(t1)
+    _, r_ratio, m_ratio = solve_risk_ode(inp, hp, 1, 1e3, 2e-2, momentum=True, dynamic_g3="ratio")
+    sgd = DanaHparams(hp.g1, hp.g2, S.const(0.0), hp.delta)
+    _, r_sgd = solve_risk_ode(inp, sgd, 1, 1e3, 2e-2)
+    # this constant g3 is too large for a raw-sum momentum: ungated the risk turns around and grows; gated by
+    # min(R / ||y||^2, 1) it keeps falling and ends next to SGD
+    assert r0[-1] > 10 * r_sgd[-1] and r_ratio[-1] == pytest.approx(r_sgd[-1], rel=0.05) and np.all(np.diff(r_ratio) < 0)
+    _, r_star = solve_risk_ode(inp, hp, 1, 1e3, 2e-2, risk_renormalized=True)
+    assert r_star[-1] != r0[-1] and np.all(np.isfinite(r_star))
+    shifted = solve_risk_ode(inp, DanaHparams(hp.g1, hp.g2, hp.g3, lambda t: 1.0 / (1.0 + t)), 1, 1e2, 2e-2, shifted_clock=True)[1]
+    plain = solve_risk_ode(inp, DanaHparams(hp.g1, hp.g2, hp.g3, lambda t: 1.0 / (2.0 + t)), 1, 1e2, 2e-2)[1]
+    np.testing.assert_allclose(shifted, plain, rtol=1e-12)   # delta read one step later == the schedule shifted by one
+
+
+def test_optimizer_comparison_on_the_ode():
+    from adana_b200.theory import schedule_studies as S
+
+    r = S.compare_optimizers(alpha=1.2, d=80, steps=2e4, dt=2e-2)
+    final = {k: v["loss"][-1] for k, v in r["runs"].items()}
+    assert set(final) == {"sgd", "dana-constant", "dana-decay", "ademamix"}
+    assert all(r["risk_infinity"] < f < v["loss"][0] for f, v in zip(final.values(), r["runs"].values()))
+    assert final["dana-decay"] < final["sgd"] and final["dana-constant"] < final["sgd"]
+    assert r["runs"]["sgd"]["t"][0] == 1.0
+
+
+def test_kappa_sweep_checkpoints_and_self_consistent_kappa():
+    from adana_b200.theory import schedule_studies as S
+
+    ks = np.linspace(0, 1, 6, endpoint=False)
+    r = S.kappa_sweep(alpha=0.5, d=80, v=320, steps=1e4, dt=2e-2, kappas=ks)
+    assert sorted(r["checkpoints"]) == [10, 100, 1000, 10000] and len(r["runs"]) == 6
+    last = r["checkpoints"][10000]
+    assert last["best_kappa"] in ks and 0.0 <= last["effective_kappa"] <= 1.0
+    np.testing.assert_allclose(last["risk_exponent"], np.log(last["risk"]) / np.log(1e4))
+    # later in training a smaller growth exponent is the better one: the schedule must not keep growing like t
+    assert r["checkpoints"][10000]["best_kappa"] < r["checkpoints"][100]["best_kappa"]
+    res = S.alpha_crossings([0.7, 0.95, 1.2], d=100, v=400, steps=1e5, dt=2e-2, kappas=np.linspace(-1.5, -0.2, 14, endpoint=False))
+    k = [row["kappa"] for row in res["rows"]]
+    assert all(x is not None and -1.5 < x < -0.2 for x in k) and k[0] < k[1] < k[2]      # flatter spectra want faster decay
+    assert res["fit"]["r_squared"] > 0.99 and res["fit"]["slope"] < 0
+
+
+def test_dynamic_and_danastar_schedule_runs():
+    from adana_b200.theory import schedule_studies as S
+
+    plain = S.dynamic_schedules(alpha=0.7, d=100, v=400, steps=1e4, dt=2e-2)
+    star = S.danastar_schedules(alpha=0.7, d=100, v=400, steps=1e4, dt=2e-2)
+    for r in (plain, star):
+        assert set(r["runs"]) == {"dana-constant", "dana-decay", "sgd", "dynamic"}
+        for run in r["runs"].values():
+            assert np.all(np.isfinite(run["risk"])) and run["risk"][-1] < run["risk"][0]
+    assert np.all(plain["runs"]["sgd"]["momentum"][1:] > 0)        # momentum is tracked even when it is not used
+    assert star["runs"]["sgd"]["late_slope"] < 0
+
+
+def test_schedule_studies_and_generators_command_lines(tmp_path):
+    from adana_b200.theory import generate, schedule_studies as S
+
+    assert S.main(["compare", "--alpha", "1.2", "--d", "40", "--steps", "2000", "--dt", "0.05", "--out", str(tmp_path / "c.json"),
+                   "--svg", str(tmp_path / "c.svg")]) == 0
+    assert set(json.loads((tmp_path / "c.json").read_text())["runs"]) == {"sgd", "dana-constant", "dana-decay", "ademamix"}
+    assert (tmp_path / "c.svg").read_text().count("<polyline") == 4
+    assert S.main(["crossing", "--alphas", "0.8", "1.1", "--d", "60", "--steps", "20000", "--dt", "0.05", "--num-kappa", "10",
+                   "--out", str(tmp_path / "x.json"), "--svg", str(tmp_path / "x.svg")]) == 0
+    assert S.main(["dynamic", "--danastar", "--d", "40", "--steps", "2000", "--dt", "0.05", "--out", str(tmp_path / "d.json")]) == 0
+    res = generate.main(["m-sweep", "--problem", "moe", "--m_range", "3,6", "--steps", "150", "--v", "120", "--d", "30",
+                         "--batch_size", "16", "--out", str(tmp_path / "m.json")])
+    assert set(res["runs"]) == {"3", "6"} and set(res["runs"]["3"]) == {"dana-star", "dana-star-mk4", "adam"}
+    assert all(run["losses"][-1] < run["losses"][0] for m in res["runs"].values() for run in m.values())
+    res = generate.main(["m-sweep", "--problem", "logistic", "--m_range", "4", "--steps", "100", "--v", "60", "--d", "20",
+                         "--batch_size", "16", "--disable_adam", "--out", str(tmp_path / "l.json")])
+    assert set(res["runs"]["4"]) == {"dana-star", "dana-star-mk4"}
+    dbg = generate.main(["debug-steps", "--debug_steps", "3", "--v", "100", "--d", "30", "--m", "6", "--batch_size", "20",
+                         "--out", str(tmp_path / "t.json")])
+    first = dbg["trace"][0]
+    assert first["dana-star"]["m"] == first["dana-star-mk4"]["m"]            # identical gradients, identical first step
+    assert set(first["dana-star"]) == {"gradient", "m", "v", "tau", "update", "risk"}
+    assert dbg["trace"][-1]["dana-star"]["risk"] < 0.5 * 1.0 + 1.0
