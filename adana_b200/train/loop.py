@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import contextlib
 import copy
+import os
 import time
 from contextlib import nullcontext
 from pathlib import Path
@@ -101,6 +102,15 @@ class Trainer:
         self.tau_stats = None
         self.dlogger = None
         self.watchdog = None
+        # Host-side fault injection for the recovery tests: ADANA_FAULT_EXIT="<rank>:<iteration>[:<exit code>]" makes
+        # that rank leave the job at the top of that iteration, between steps, with nothing of its own in flight.
+        self._exit_at = None
+        spec = os.environ.get("ADANA_FAULT_EXIT")
+        if spec:
+            parts = spec.split(":")
+            rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+            if int(parts[0]) == rank:
+                self._exit_at = (int(parts[1]), int(parts[2]) if len(parts) > 2 else 17)
 
     # ---- set-up ---------------------------------------------------------------------------------------
     def setup(self):
@@ -365,6 +375,11 @@ class Trainer:
                 break
             if self.curr_iter == cfg.iterations:
                 break
+            if self._exit_at is not None and self.curr_iter == self._exit_at[0]:
+                print(f"[Fault] leaving at iteration {self.curr_iter} (ADANA_FAULT_EXIT)", flush=True)
+                if self.cuda:
+                    torch.cuda.synchronize()
+                os._exit(self._exit_at[1])
             if self.watchdog is not None:
                 self.watchdog.beat(self.curr_iter)
                 self.watchdog.raise_if_failed()

@@ -89,3 +89,103 @@ def test_failed_rsync_keeps_the_last_good_checkpoint(tmp_path, monkeypatch):
     ck.rsync_if_slurm(project)
     ck.wait_for_rsync()
     assert (project / "main.pt").read_text() == "good" and not project.with_name("latest.incoming").exists()
+
+
+def test_truncated_checkpoint_shard_fails_loudly(tmp_path):
+    """A data file cut short (a disk that filled up, a copy that stopped) must not load as if it were complete."""
+    from conftest import tiny_args
+    from adana_b200.models.utils import get_model
+    from adana_b200.runtime.engine import EngineOptimizer, attach
+
+    a = tiny_args("enoki", opt="adamw")
+    m = get_model(a)
+    eng = attach(m, a, device="cpu")
+    eng.sharded = True
+    specs = m.get_parameter_group_specs()
+    for g in specs:
+        g["param_names"] = g["params"]
+    opt = EngineOptimizer(eng, "adamw", a, specs)
+    d = tmp_path / "latest"
+    ck.save_checkpoint(m, opt, None, 3, d)
+    before = {k: v.clone() for k, v in eng.full_param_dict("master").items()}
+    f = next((d / "sharded").glob("*.distcp"))
+    data = f.read_bytes()
+    f.write_bytes(data[: len(data) // 2])
+    with pytest.raises(BaseException):                       # torch's CheckpointException is a BaseException
+        ck.load_checkpoint(m, opt, None, d)
+    f.write_bytes(data)                                      # the intact file loads, and into the same numbers
+    assert ck.load_checkpoint(m, opt, None, d) == 3
+    for k, v in eng.full_param_dict("master").items():
+        assert torch.equal(v, before[k])
+
+
+def _stall_worker(rank, world, port, stall_rank, q):
+    """Three ranks beat; one of them stops itself with SIGSTOP between steps (alive, but silent: its heartbeat thread
+    stops with it).  The others must name it within the timeout."""
+    import os
+    import signal
+    import time
+
+    import torch.distributed as dist
+
+    from adana_b200.runtime.watchdog import HeartbeatWatchdog, PeerFailure
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    wd = HeartbeatWatchdog.from_env(timeout_s=1.5)
+    wd.beat(0)
+    dist.barrier()
+    wd.start()
+    t0 = time.time()
+    for it in range(1, 300):
+        if rank == stall_rank and it == 3:
+            q.put((rank, f"stopping pid {os.getpid()}"))
+            time.sleep(0.5)                                  # the queue's feeder thread has to get the message out first
+            os.kill(os.getpid(), signal.SIGSTOP)             # resumes only if the parent sends SIGCONT; it kills instead
+        wd.beat(it)
+        try:
+            wd.raise_if_failed()
+        except PeerFailure as e:
+            wd.stop()
+            q.put((rank, f"detected after {time.time() - t0:.1f}s: {e}"))
+            q.close()
+            q.join_thread()
+            os._exit(0)                                      # no collective teardown with a stopped peer
+        time.sleep(0.1)
+    q.put((rank, "never detected"))
+    q.close()
+    q.join_thread()
+    os._exit(0)
+
+
+def test_watchdog_names_a_rank_that_is_alive_but_stopped():
+    import socket
+    import time
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_stall_worker, args=(r, 3, port, 1, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got, deadline = {}, time.time() + 120
+    try:
+        while len(got) < 3 and time.time() < deadline:
+            try:
+                r, msg = q.get(timeout=1.0)
+                got[r] = msg
+            except Exception:
+                pass
+    finally:
+        procs[1].kill()                                      # the stopped rank, by its own handle
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.kill()
+    assert got.get(1, "").startswith("stopping"), got
+    for r in (0, 2):
+        assert got.get(r, "").startswith("detected") and "rank 1" in got[r], got

@@ -4,6 +4,7 @@ the same weights and losses as an uninterrupted one."""
 import json
 import subprocess
 import sys
+import time
 from pathlib import Path
 
 import pytest
@@ -163,3 +164,39 @@ def test_four_rank_dp_by_tp_cli_run_saves_and_resumes(tmp_path):
     p = subprocess.run(base + ["--iterations", "10", "--resume_from", str(ckpts[-1].parent)], cwd=ROOT, capture_output=True,
                        text=True, timeout=400, env=env)
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+@pytest.mark.timeout(900)
+def test_rank_that_leaves_ends_the_job_and_the_relaunch_resumes_from_the_last_checkpoint(tmp_path):
+    """Job-level recovery, failure made on the host: rank 1 of a two-rank FSDP run leaves at iteration 6 (between
+    steps).  The survivor must not hang: the launcher ends the job with a non-zero code, the checkpoint of iteration 4
+    is complete, and a relaunch with --auto_resume — here on ONE rank, the elastic case — carries on from it."""
+    import os
+
+    def launch(nproc, extra, env_extra=None, expect_ok=True):
+        cmd = [*torchrun(nproc), "-m", "adana_b200.main", "--model", "enoki", "--n_layer", "2",
+               "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim", "128", "--sequence_length", "64",
+               "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset", "synthetic-zipf",
+               "--datasets_dir", str(tmp_path / "data"), "--opt", "dana-star-mk4", "--kappa", "0.85", "--clipsnr", "2.0",
+               "--wd_decaying", "--wd_ts", "5", "--lr", "1e-3", "--warmup_steps", "2", "--scheduler", "cos_inf",
+               "--eval_interval", "4", "--eval_batches", "2", "--log_interval", "1", "--latest_ckpt_interval", "4",
+               "--results_base_folder", str(tmp_path / "exps"), "--device", "cpu", "--dtype", "float32",
+               "--distributed_backend", "fsdp", "--seed", "3", "--heartbeat_timeout", "5", "--experiment_name", "recover", *extra]
+        env = {**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1", **(env_extra or {})}
+        p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600, env=env)
+        assert (p.returncode == 0) == expect_ok, p.stdout[-2000:] + p.stderr[-2000:]
+        return p.stdout + p.stderr
+
+    t0 = time.time()
+    out = launch(2, ["--iterations", "10"], {"ADANA_FAULT_EXIT": "1:6"}, expect_ok=False)
+    assert time.time() - t0 < 300                                   # ended by the failure, not by the test's timeout
+    assert "[Fault] leaving at iteration 6" in out and "Train: Iter=10" not in out
+    exp = _exp_dir(tmp_path / "exps")
+    latest = exp / "ckpts" / "latest"
+    assert torch.load(latest / "meta.pt", map_location="cpu", weights_only=False)["itr"] == 4
+    assert len(list((latest / "sharded").glob("*.distcp"))) == 2 and not (exp / "summary.json").exists()
+    out = launch(1, ["--iterations", "10", "--auto_resume"])
+    assert ">Eval: Iter=10" in out and (exp / "summary.json").exists()
+    rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
+    iters = [r["iter"] for r in rows if "train/loss" in r]
+    assert iters[-1] == 10 and 5 in iters and all(r["train/loss"] == r["train/loss"] for r in rows if "train/loss" in r)

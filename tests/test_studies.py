@@ -427,3 +427,34 @@ def test_panels_draw_every_family(tmp_path):
     assert panels.gamma3(rep, tmp_path / "e.svg").exists()
     by = {(6, "adamw"): [{"hoyer_coeff": c, "final_val_loss": l} for c, l in ((0.0, 3.5), (1e-4, 3.45), (1e-2, 3.7))]}
     assert panels.hoyer(by, tmp_path / "f.svg").exists()
+
+
+def test_wandb_source_through_the_cache(tmp_path):
+    """The W&B source only needs an object with `runs(path, filters)`; the cache keeps what it returned."""
+    from types import SimpleNamespace
+
+    from adana_b200.studies.runs import WandbRuns
+
+    calls = []
+
+    class FakeSummary:
+        _json_dict = {"final-val/loss": 3.21, "iter": 100}
+
+    class FakeRun(SimpleNamespace):
+        def scan_history(self):
+            calls.append("history")
+            return [{"iter": 50, "val/loss": 3.5}, {"iter": 100, "val/loss": 3.21}]
+
+    class FakeApi:
+        def runs(self, path, filters=None):
+            calls.append((path, dict(filters or {})))
+            return [FakeRun(id="abc123", name="adamw_h8", config={"opt": {"value": "adamw"}, "lr": {"value": 1e-3}, "n_head": 8,
+                                                                  "iterations": 100, "weight_decay": 40.0}, summary=FakeSummary())]
+
+    src = CachedRuns(WandbRuns("team", "proj", api=FakeApi()), tmp_path / "c")
+    runs = src.fetch({"group": "g1"})
+    assert calls == [("team/proj", {"group": "g1"})] and runs[0].opt == "adamw" and runs[0].omega() == pytest.approx(4.0)
+    assert runs[0].series("val/loss") == ([50, 100], [3.5, 3.21]) and calls.count("history") == 1
+    again = CachedRuns(WandbRuns("team", "proj", api=None), tmp_path / "c").fetch({"group": "g1"})     # no API needed any more
+    assert again[0].final_val_loss == 3.21 and again[0].series("val/loss") == ([50, 100], [3.5, 3.21])
+    assert (tmp_path / "c" / "history" / "abc123.json").exists()
