@@ -9,6 +9,11 @@
     python -m adana_b200.studies opt-stats  <experiment dir> [--svg-prefix P]
     python -m adana_b200.studies tau        <tau_stats dir> [--raw] [--all-kinds] [--svg-prefix P]
     python -m adana_b200.studies kappa      <runs root> --n-head H [--svg-prefix P]
+    python -m adana_b200.studies savings    <runs root> --opt dana-star-mk4 [--baseline adamw] [--window 1 30] [--json J] [--svg S]
+    python -m adana_b200.studies gamma3     <runs root> --opt dana-star-mk4 [--top-k 3] [--kind power] [--json J] [--svg S]
+    python -m adana_b200.studies hoyer      <runs root> [--heads 6 8] [--opts adamw dana-star-mk4] [--json J] [--svg S]
+    python -m adana_b200.studies sensitivity --bootstrap B1.json B2.json --names adamw dana-mk4 --curvature C.json \
+                                            --law 2.5 0.5 0.12 --losses 3.45 3.40 --target-size 36 [--json J]
 
 `<runs root>` is a folder that holds experiment directories (any depth); `--wandb entity/project` reads a W&B project
 instead, and `--cache DIR` keeps what was read on disk (`--refresh` to read again).
@@ -22,7 +27,7 @@ from pathlib import Path
 
 import numpy as np
 
-from . import curvature, loss_laws, lr_law, panels, sweeps, tau_cdf
+from . import curvature, gamma3, loss_laws, lr_law, panels, savings, sweeps, tau_cdf
 from .runs import CachedRuns, LocalRuns, WandbRuns, lr_sweep_table
 from .sizes import model_size, size_key
 
@@ -95,6 +100,27 @@ def main(argv=None) -> int:
     s.add_argument("--n-head", type=int, required=True)
     s.add_argument("--kappa-min", type=float, default=0.0)
     s.add_argument("--svg-prefix", default=None)
+    s = runs_cmd("savings")
+    s.add_argument("--baseline", default="adamw")
+    s.add_argument("--window", type=float, nargs=2, default=[1.0, 30.0])
+    s = runs_cmd("gamma3")
+    s.add_argument("--top-k", type=int, default=5)
+    s.add_argument("--kind", default="power", choices=["power", "linear", "exponential"])
+    s.add_argument("--fac-min", type=float, default=0.0)
+    s.add_argument("--fac-max", type=float, default=float("inf"))
+    s = runs_cmd("hoyer")
+    s.add_argument("--heads", type=int, nargs="*", default=None)
+    s.add_argument("--opts", nargs="*", default=None)
+    s = sub.add_parser("sensitivity")
+    s.add_argument("--bootstrap", nargs="+", required=True)
+    s.add_argument("--names", nargs="+", required=True)
+    s.add_argument("--curvature", required=True)
+    s.add_argument("--baseline", default=None)
+    s.add_argument("--law", type=float, nargs=3, required=True, metavar=("a", "b", "c"))
+    s.add_argument("--losses", type=float, nargs="+", required=True)
+    s.add_argument("--target-size", type=int, required=True)
+    s.add_argument("--rule", default="Enoki_Scaled")
+    s.add_argument("--json", default=None)
     s = sub.add_parser("opt-stats")
     s.add_argument("exp_dir")
     s.add_argument("--svg-prefix", default=None)
@@ -131,6 +157,13 @@ def main(argv=None) -> int:
                 panels.tau_cdf(g, f"{a.svg_prefix}_{name.replace(' ', '_').replace('.', '_')}.svg", name, a.raw)
         return 0
 
+    if a.cmd == "sensitivity":
+        boots = {n: json.loads(Path(f).read_text()) for n, f in zip(a.names, a.bootstrap)}
+        boots = {n: b.get("bootstrap", b) for n, b in boots.items()}          # a whole lr-law report or its bootstrap part
+        rep = savings.sensitivity(boots, json.loads(Path(a.curvature).read_text()), dict(zip(a.names, a.losses)),
+                                  a.baseline or a.names[0], model_size(a.target_size, a.rule).non_emb, *a.law)
+        _dump(rep, a.json)
+        return 0
     runs = _source(a).fetch({"group": a.group} if a.group else None)
     sel = dict(omega=a.omega, omega_tol=a.omega_tol, kappa=a.kappa, lr_coupled=a.lr_coupled_omega)
     if a.cmd in ("lr-law", "curvature"):
@@ -161,6 +194,43 @@ def main(argv=None) -> int:
         if a.svg:
             panels.loss_laws(curves, fit, a.svg)
         _dump(fit, a.json)
+        return 0
+    if a.cmd == "savings":
+        base = sweeps.best_runs_per_size(runs, a.rule, a.baseline)
+        baselines = {sz: {"final_loss": d["final_loss"], "final_compute": d["compute"][-1] if d["compute"] else float("nan"),
+                          "model_compute": model_size(sz, a.rule).compute_pfh(), "non_emb": d["non_emb"]} for sz, d in base.items()}
+        cands = {}
+        for r in sweeps.select(runs, opt=a.opt, **sel):
+            sz = r.config.get(size_key(a.rule))
+            if sz is None:
+                continue
+            m = model_size(int(sz), a.rule)
+            toks, losses = r.series("val/loss", x="tokens")
+            hist = [(6.0 * m.non_emb * t / 3600e15, l) for t, l in zip(toks, losses)]
+            if hist:
+                cands.setdefault(int(sz), []).append({"history": hist, "final_compute": hist[-1][0], "run_name": r.name})
+        rows = savings.saved_per_size(baselines, cands)
+        ds = [{"name": a.opt, "x": [r["model_compute"] for r in rows], "y": [r["compute_saved"] for r in rows]}]
+        lines = savings.fit_savings_lines(ds, tuple(a.window))
+        if a.svg and rows:
+            panels.savings(ds, lines, a.svg)
+        _dump({"per_size": rows, "lines": lines}, a.json)
+        return 0
+    if a.cmd == "gamma3":
+        rows = [{"size": int(r.config[size_key(a.rule)]), "iterations": int(r.config["iterations"]),
+                 "gamma_3_factor": float(r.config["gamma_3_factor"]), "val_loss": float(r.final_val_loss), "run": r.name}
+                for r in sweeps.select(runs, opt=a.opt, need=("gamma_3_factor", "iterations", size_key(a.rule)), **sel)
+                if r.final_val_loss is not None]
+        rep = gamma3.study(rows, a.rule, a.top_k, a.kind, a.fac_min, a.fac_max)
+        if a.svg and rep["points"]:
+            panels.gamma3(rep, a.svg)
+        _dump(rep, a.json)
+        return 0
+    if a.cmd == "hoyer":
+        by = sweeps.hoyer_loss_by_coefficient(sweeps.hoyer_points(runs, a.heads, a.opts))
+        if a.svg and by:
+            panels.hoyer(by, a.svg)
+        _dump({f"{h}:{o}": pts for (h, o), pts in by.items()}, a.json)
         return 0
     if a.cmd == "gpu-hours":
         rows = sweeps.gpu_hours_by_size(sweeps.gpu_hours_rows(runs, a.rule, a.opt))

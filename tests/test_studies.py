@@ -408,6 +408,43 @@ def test_command_line_writes_reports_and_figures(runs_root, tmp_path, capsys):
     assert (tmp_path / "st_alpha_schedule.svg").exists()
     assert main(["kappa", str(runs_root), "--n-head", "8", "--svg-prefix", str(tmp_path / "k"), "--json", str(tmp_path / "k.json")]) == 0
     assert (tmp_path / "k_curves.svg").exists()
+    # compute saved: every size's best candidate run reaches the baseline's final loss by its own end at the latest
+    assert main(["savings", str(runs_root), "--opt", "dana-star-mk4", "--baseline", "adamw", "--window", "0", "1e9",
+                 "--json", str(tmp_path / "sv.json"), "--svg", str(tmp_path / "sv.svg")]) == 0
+    sv = json.loads((tmp_path / "sv.json").read_text())
+    assert [r["size"] for r in sv["per_size"]] == [8, 12, 16] and all(r["compute_saved"] >= 0 for r in sv["per_size"])
+    assert sv["lines"]["curves"]["dana-star-mk4"]["n_points"] == 3
+    # sensitivity from the two reports written above
+    assert main(["lr-law", str(runs_root), "--opt", "dana-star-mk4", "--omega", "4", "--top-k", "2", "--bootstrap", "10",
+                 "--extrapolate", "16", "--json", str(tmp_path / "law2.json")]) == 0
+    assert main(["lr-law", str(runs_root), "--opt", "adamw", "--omega", "4", "--top-k", "2", "--bootstrap", "10",
+                 "--extrapolate", "16", "--json", str(tmp_path / "law1.json")]) == 0
+    assert main(["sensitivity", "--bootstrap", str(tmp_path / "law1.json"), str(tmp_path / "law2.json"), "--names", "adamw",
+                 "dana-star-mk4", "--curvature", str(tmp_path / "cur.json"), "--law", "2.0", "3.0", "0.2", "--losses", "4.9", "4.8",
+                 "--target-size", "16", "--json", str(tmp_path / "se.json")]) == 0
+    se = json.loads((tmp_path / "se.json").read_text())
+    assert [r["optimizer"] for r in se["analysis"]] == ["adamw", "dana-star-mk4"] and "compute_saved" in se["analysis"][1]
+
+
+def test_gamma3_and_hoyer_commands(tmp_path):
+    from adana_b200.studies.__main__ import main
+
+    root = tmp_path / "exps"
+    for h in (8, 12):
+        for its in (500, 1000, 2000):
+            for f in (0.5, 1.0, 2.0):
+                g = 2.0 * its ** -0.4 * f
+                _write_run(root, f"g_h{h}_{its}_{f}", {"opt": "dana-star-mk4", "n_head": h, "lr": 1e-3, "iterations": its, "gamma_3_factor": g,
+                                                       "weight_decay": 0.04, "wd_ts": 100}, 3.0 + abs(math.log(f)), [(its, 3.0)])
+    for c, l in ((0.0, 3.5), (1e-4, 3.4), (1e-2, 3.8)):
+        _write_run(root, f"hoyer_{c}", {"opt": "adamw", "n_head": 6, "lr": 1e-3, "iterations": 100, "hoyer_loss_coeff": c, "batch_size": 4,
+                                        "acc_steps": 1, "sequence_length": 512, "weight_decay": 0.1}, l, [(100, l)])
+    assert main(["gamma3", str(root), "--opt", "dana-star-mk4", "--top-k", "1", "--json", str(tmp_path / "g.json"), "--svg", str(tmp_path / "g.svg")]) == 0
+    rep = json.loads((tmp_path / "g.json").read_text())
+    assert rep["params"] == pytest.approx([2.0, -0.4], rel=1e-6) and len(rep["points"]) == 6
+    assert main(["hoyer", str(root), "--opts", "adamw", "--json", str(tmp_path / "h.json"), "--svg", str(tmp_path / "h.svg")]) == 0
+    by = json.loads((tmp_path / "h.json").read_text())
+    assert [p["hoyer_coeff"] for p in by["6:adamw"]] == [0.0, 1e-4, 1e-2] and (tmp_path / "h.svg").exists()
 
 
 def test_panels_draw_every_family(tmp_path):
