@@ -170,13 +170,21 @@ def fig_hummingbird(data: dict, out) -> Path:
     return ch.save(out)
 
 
-def fig_taustats(data: dict, out) -> Path:
-    """Order statistics of tau (largest side) at the recorded times: rank against value, one line per time
-    (reference: jax/taustats_plot_from_data.py, visualization/plot_tau_summary.py)."""
-    ch = LineChart("tau order statistics (largest first)", "rank", "tau", logx=True, logy=True)
+def fig_taustats(data: dict, out, raw: bool = False) -> Path:
+    """Distribution of tau at the recorded times as a dual-tail CDF: tau (regularised as the optimizer regularises it,
+    unless `raw`) on a log axis against the cumulative probability on a logit axis with compressed tails, one line per
+    time (reference: jax/taustats_plot_from_data.py:68-420, visualization/plot_tau_summary.py)."""
+    from .studies.tau_cdf import PROB_TICKS, cdf_from_order_stats, prob_axis, regularize_tau
+
+    n = int(data["args"]["d"]) * int(data["args"]["m"])
+    ticks = [(float(prob_axis(p)[0]), f"{100 * p:g}%") for p in PROB_TICKS]
+    ch = LineChart("tau: cumulative distribution over training", "tau" if raw else "regularised tau", "cumulative probability",
+                   logx=True, yticks=ticks)
     for snap in data["tau"][-8:]:
-        ranks = np.unique(np.floor(1.1 ** np.arange(len(snap["largest"]) + 40)).astype(int))[:len(snap["largest"])]
-        ch.add(ranks, snap["largest"], f"step {snap['step']}")
+        tau, prob = cdf_from_order_stats(snap["smallest"], snap["largest"], n)
+        if not raw:
+            tau = regularize_tau(tau, snap["step"])
+        ch.add(tau, prob_axis(prob), f"step {snap['step']}")
     return ch.save(out)
 
 

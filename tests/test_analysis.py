@@ -75,3 +75,4 @@ def test_figure_scripts_write_svg(tmp_path):
         text = f.read_text()
         assert text.startswith("<svg") and "<polyline" in text and text.rstrip().endswith("</svg>")
     assert "-0.51" in c.read_text()          # the fitted exponent is in the title
+    assert "99.9%" in e.read_text() and "50%" in e.read_text()      # tau statistics are drawn as a dual-tail CDF
