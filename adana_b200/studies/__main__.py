@@ -230,6 +230,9 @@ def main(argv=None) -> int:
         by = sweeps.hoyer_loss_by_coefficient(sweeps.hoyer_points(runs, a.heads, a.opts))
         if a.svg and by:
             panels.hoyer(by, a.svg)
+            curves = sweeps.hoyer_curves(runs, a.heads[0] if a.heads else None, a.opts[0] if a.opts else None)
+            if curves:
+                panels.hoyer_curves(curves, str(Path(a.svg).with_suffix("")) + "_curves.svg")
         _dump({f"{h}:{o}": pts for (h, o), pts in by.items()}, a.json)
         return 0
     if a.cmd == "gpu-hours":

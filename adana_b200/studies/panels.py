@@ -12,6 +12,7 @@ Figure families and the reference script each stands in for:
   tau_cdf              plot_tau_summary.py, plot_aggregated_tensors.py   tau CDFs on the compressed-logit axis
   optimizer_stats      snr_clipping_plots.py   a logged statistic against tokens with its unclipped theory
   hoyer                hoyer_final_loss.py, hoyer_vs_regularization.py   final loss against the Hoyer coefficient
+  hoyer_curves         hoyer_loss_curves.py   cross-entropy and Hoyer-term curves coloured by the coefficient
   kappa_curves / kappa_slice   llm_hummingbird_plot.py, llm_hummingbird_slice_plot.py
   size_curves          bighead_loss_curves.py   best run of each size, loss against compute
 """
@@ -157,6 +158,22 @@ def hoyer(by_coeff: Dict, out) -> Path:
     for (heads, opt), pts in sorted(by_coeff.items()):
         ch.add([p["hoyer_coeff"] or zero_at for p in pts], [p["final_val_loss"] for p in pts],
                f"{palette.display_name(opt)}, {heads} heads", palette.color(opt, None), markers=True)
+    return ch.save(out)
+
+
+def hoyer_curves(curves: Sequence[Dict], out, which: str = "loss") -> Path:
+    """curves: the output of `sweeps.hoyer_curves`; `which` = "loss" (cross-entropy) or "hoyer" (the regulariser's own
+    value).  Lines are coloured by the logarithm of the coefficient, the unregularised run is black."""
+    x_key = "pf_days" if which == "loss" else "hoyer_pf_days"
+    ch = LineChart("validation loss" if which == "loss" else "Hoyer term", "compute (PetaFLOP-days)", which, logx=True, logy=True)
+    pos = [c["hoyer_coeff"] for c in curves if c["hoyer_coeff"] > 0]
+    lo, hi = (min(pos), max(pos)) if pos else (1.0, 1.0)
+    for c in curves:
+        if not c[which]:
+            continue
+        col = "#000000" if c["hoyer_coeff"] <= 0 else palette.log_scale_color(c["hoyer_coeff"], lo, hi)
+        ch.add(c[x_key], c[which], f"{palette.hoyer_label(c['hoyer_coeff'])} ({palette.display_name(c['opt'])})", col,
+               dashed=palette.hoyer_linestyle(c["hoyer_coeff"]) != "-")
     return ch.save(out)
 
 

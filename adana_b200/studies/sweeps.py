@@ -160,6 +160,27 @@ def hoyer_points(runs: Iterable[Run], heads: Optional[Sequence[int]] = None, opt
     return rows
 
 
+def hoyer_curves(runs: Iterable[Run], heads: Optional[int] = None, opt: Optional[str] = None, key: str = "val/loss",
+                 hoyer_key: str = "train/hoyer_loss") -> List[Dict]:
+    """Per finished run of a Hoyer sweep: its coefficient, the cross-entropy curve and, where logged, the curve of the
+    Hoyer term itself, both against compute in PetaFLOP-days; sorted by coefficient (the figures colour by it)."""
+    out = []
+    for r in select(runs, opt=opt, need=()):
+        h = r.config.get("n_head")
+        if h is None or (heads is not None and h != heads):
+            continue
+        m = model_size(h, "Qwen3_Hoyer")
+        per_tok = 6.0 * m.non_emb / PF_DAY
+        toks, ce = r.series(key, x="tokens")
+        if not ce:
+            continue
+        toks_h, hv = r.series(hoyer_key, x="tokens")
+        out.append({"run": r.name, "heads": int(h), "opt": r.opt, "hoyer_coeff": float(r.config.get("hoyer_loss_coeff", 0.0) or 0.0),
+                    "pf_days": [per_tok * t for t in toks], "loss": list(ce),
+                    "hoyer_pf_days": [per_tok * t for t in toks_h], "hoyer": list(hv)})
+    return sorted(out, key=lambda d: d["hoyer_coeff"])
+
+
 def hoyer_loss_by_coefficient(points: Sequence[Dict]) -> Dict:
     """(heads, opt) -> coefficients ascending with the best final loss at each."""
     g: Dict = {}

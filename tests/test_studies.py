@@ -445,6 +445,8 @@ def test_gamma3_and_hoyer_commands(tmp_path):
     assert main(["hoyer", str(root), "--opts", "adamw", "--json", str(tmp_path / "h.json"), "--svg", str(tmp_path / "h.svg")]) == 0
     by = json.loads((tmp_path / "h.json").read_text())
     assert [p["hoyer_coeff"] for p in by["6:adamw"]] == [0.0, 1e-4, 1e-2] and (tmp_path / "h.svg").exists()
+    curves = (tmp_path / "h_curves.svg").read_text()
+    assert curves.count("<polyline") == 3 and "λ=1e-4 (AdamW)" in curves and 'stroke="#000000"' in curves
 
 
 def test_panels_draw_every_family(tmp_path):
