@@ -70,7 +70,9 @@ def cmd_sweep(a, extra):
     points = []
     for heads in a.heads:
         dims = compute_dimensions(a.arch, heads)
-        base_lr = compute_lr(a.arch, a.opt, dims["non_emb_params"], kappa=a.kappa, batch_size=a.batch_size * a.acc_steps)
+        # the learning-rate law at its default batch, as the reference's sweep does (scripts/sweep.sh:131-146): the sweep
+        # passes --lr explicitly, so the launcher's own batch-dependent table is not consulted
+        base_lr = compute_lr(a.arch, a.opt, dims["non_emb_params"], kappa=a.kappa)
         if base_lr is None:
             raise SystemExit(f"no LR law for {a.opt}; pass --base_lr")
         base_lr = a.base_lr or base_lr
@@ -81,15 +83,25 @@ def cmd_sweep(a, extra):
             largs = ["--arch", a.arch, "--opt", a.opt, "--heads", heads, "--nproc", a.nproc, "--batch_size", a.batch_size,
                      "--acc_steps", a.acc_steps, "--kappa", a.kappa, "--clipsnr", a.clipsnr, "--gamma_3_factor",
                      a.gamma_3_factor, "--lr", f"{mult * base_lr:.6e}", "--scheduler", a.scheduler,
-                     "--distributed_backend", a.distributed_backend, "--wandb_group", a.wandb_group]
+                     "--distributed_backend", a.distributed_backend, "--wandb_group", a.wandb_group,
+                     "--eval_batches", a.eval_batches]
+            if a.tp_size > 1:
+                largs += ["--tp_size", a.tp_size]
+            if a.liger_loss:
+                largs += ["--liger_loss"]
+            largs += ["--z_loss_coeff", a.z_loss_coeff]
+            if not a.auto_resume:
+                largs += ["--no_auto_resume"]
+            if a.iterations:
+                largs += ["--iterations", a.iterations]
+            if a.iterations_to_run:
+                largs += ["--iterations_to_run", a.iterations_to_run]
+            if a.wandb_offline:
+                largs += ["--wandb_offline"]
             if a.wd_ts_const is not None:
                 largs += ["--wd_ts_const", a.wd_ts_const]
             elif a.wd_ts_divisor is not None:
                 largs += ["--wd_ts_divisor", a.wd_ts_divisor]
-            if a.tp_size > 1:
-                largs += ["--tp_size", a.tp_size]
-            if a.iterations_to_run:
-                largs += ["--iterations_to_run", a.iterations_to_run]
             largs += extra
             points.append((heads, mult, largs))
     rc = 0
@@ -197,6 +209,12 @@ def main(argv=None) -> int:
     s.add_argument("--tp_size", type=int, default=1)
     s.add_argument("--wandb_group", default="fsdp-experiment")
     s.add_argument("--iterations_to_run", type=int, default=None)
+    s.add_argument("--iterations", type=int, default=None, help="instead of the Chinchilla count")
+    s.add_argument("--eval_batches", type=int, default=4)
+    s.add_argument("--z_loss_coeff", default="1e-4")
+    s.add_argument("--liger_loss", action="store_true")
+    s.add_argument("--auto_resume", action="store_true", help="resume from the latest checkpoint (default: fresh start)")
+    s.add_argument("--wandb_offline", action="store_true")
     s.add_argument("--slurm", action="store_true")
     s.add_argument("--account", default=None)
     s.add_argument("--time", default="3:00:00")

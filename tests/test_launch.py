@@ -146,3 +146,70 @@ def test_launcher_builds_the_same_training_command_as_the_reference_launch_scrip
             if a == b:
                 continue
             assert a is not None and b is not None and abs(float(a) - float(b)) <= 1e-12 * max(1.0, abs(float(a))), (args, key, a, b)
+
+
+def test_sweep_submits_the_same_grid_as_the_reference_sweep_script(ref_src, tmp_path, capsys):
+    """`scripts/sweep.sh --dry` of the reference (a copy whose configuration block is edited the way a user edits it)
+    against `python -m adana_b200.experiments sweep --slurm --dry`: the same jobs in the same order, and for every job
+    the same launcher arguments (optimizer, heads, processes, batch, kappa, clip-SNR, the learning rate of the grid
+    point, schedule, backend, group, evaluation batches, z-loss, resume switch, weight-decay time scale)."""
+    import re
+    import shlex
+    import shutil
+    import subprocess
+
+    src = ref_src.parent / "scripts"
+    if not (src / "sweep.sh").exists() or shutil.which("bash") is None:
+        pytest.skip("the reference's sweep script or bash is not available")
+    work = tmp_path / "ref"
+    shutil.copytree(ref_src.parent / "scripts", work / "scripts")
+    (work / "src" / "config").mkdir(parents=True)
+    for f in ("scaling.py", "scaling_rules.yaml"):
+        shutil.copy(ref_src / "config" / f, work / "src" / "config" / f)
+    text = (work / "scripts" / "sweep.sh").read_text()
+    edits = {r'^OPT="adana"': 'OPT="dana-star-mk4"', r"^HEADS_LIST=\( 8 \)": "HEADS_LIST=( 8 12 )",
+             r"^LR_MULTIPLIERS=\( 1.0 \)": "LR_MULTIPLIERS=( 0.5 1.0 2.0 )", r"^TP_SIZE=1": "TP_SIZE=2",
+             r'^ITERATIONS_TO_RUN=""': 'ITERATIONS_TO_RUN="2000"'}
+    for pat, rep in edits.items():
+        text, n = re.subn(pat, rep, text, count=1, flags=re.M)
+        assert n == 1, pat
+    (work / "scripts" / "sweep.sh").write_text(text)
+    out = subprocess.run(["bash", "scripts/sweep.sh", "--dry"], cwd=work, capture_output=True, text=True, timeout=300).stdout
+
+    def flags(tokens):
+        d, i = {}, 0
+        while i < len(tokens):
+            if tokens[i].startswith("--"):
+                if i + 1 < len(tokens) and not tokens[i + 1].startswith("--"):
+                    d[tokens[i]] = tokens[i + 1]
+                    i += 2
+                    continue
+                d[tokens[i]] = True
+            i += 1
+        return d
+
+    ref_jobs = []
+    for line in out.splitlines():
+        if line.strip().startswith("sbatch "):
+            toks = shlex.split(line.strip())
+            ref_jobs.append(flags(toks[toks.index("scripts/restart_enoki.sh") + 1:]))
+    assert len(ref_jobs) == 6, out[-1500:]
+
+    rc = experiments.main(["sweep", "--arch", "enoki", "--opt", "dana-star-mk4", "--heads", "8", "12", "--lr_mult", "0.5", "1.0", "2.0",
+                           "--tp_size", "2", "--iterations_to_run", "2000", "--slurm", "--dry"])
+    mine = []
+    for line in capsys.readouterr().out.splitlines():
+        if line.startswith("sbatch "):
+            wrapped = shlex.split(shlex.split(line)[-1])
+            mine.append(flags(wrapped[wrapped.index("restart") + 1:]))
+    assert rc == 0 and len(mine) == 6
+    for got, want in zip(mine, ref_jobs):
+        assert got.pop("--arch") == "enoki"                      # the reference picks the architecture by its restart script
+        assert set(got) == set(want), (sorted(got), sorted(want))
+        for k, v in want.items():
+            if k == "--lr":
+                assert float(got[k]) == pytest.approx(float(v), rel=1e-6)
+            elif isinstance(v, str) and re.fullmatch(r"[-+0-9.eE]+", v):
+                assert float(got[k]) == float(v), k
+            else:
+                assert got[k] == v, k
