@@ -55,11 +55,15 @@ def _launch_cmd(args_list):
     return [sys.executable, "-m", "adana_b200.launch", *[str(a) for a in args_list]]
 
 
-def _sbatch(cmd, job_name, nproc, time, mem, account=None, dry=False):
-    sb = ["sbatch", f"--job-name={job_name}", f"--gres=gpu:{nproc}", f"--time={time}", f"--mem={mem}", "--nodes=1",
-          f"--cpus-per-task={8 * nproc}"]
+def _sbatch(cmd, job_name, nproc, time, mem, account=None, dry=False, export=None, nodes=1):
+    """Prints the `sbatch --wrap` line and, unless `dry`, submits it.  `export` adds variables to the job's environment
+    on top of the submitting one (`--export=ALL,K=V`)."""
+    sb = ["sbatch", f"--job-name={job_name}", f"--gres=gpu:{nproc}", f"--time={time}", f"--mem={mem}", f"--nodes={nodes}",
+          f"--cpus-per-task={8 * int(nproc) if str(nproc).isdigit() else 8}"]
     if account:
         sb.append(f"--account={account}")
+    if export:
+        sb.append("--export=ALL," + ",".join(f"{k}={v}" for k, v in export.items()))
     sb += ["--wrap", " ".join(shlex.quote(c) for c in cmd)]
     print(" ".join(shlex.quote(c) for c in sb))
     return 0 if dry else subprocess.call(sb)
@@ -131,17 +135,29 @@ def cmd_restart(a, extra):
         return rc
     if "--iterations_to_run" not in largs or count + 1 >= a.max_restarts:
         return 0
-    env = {**os.environ, "RESTART_COUNT": str(count + 1)}
-    me = [sys.executable, "-m", "adana_b200.experiments", "restart", "--max_restarts", str(a.max_restarts), *largs]
-    if os.environ.get("SLURM_JOB_ID"):
-        info = subprocess.run(["scontrol", "show", "job", os.environ["SLURM_JOB_ID"]], capture_output=True, text=True).stdout
-        gres = (re.search(r"gres/gpu[:=](\S+)", info) or re.search(r"gpu[:=](\d+)", info))
-        time = re.search(r"TimeLimit=(\S+)", info)
-        return _sbatch(me, os.environ.get("SLURM_JOB_NAME", "adana-restart"), gres.group(1) if gres else 1,
-                       time.group(1) if time else "3:00:00", os.environ.get("SLURM_MEM_PER_NODE", "0"),
-                       os.environ.get("SLURM_JOB_ACCOUNT"))
-    if a.finished_marker and Path(a.finished_marker).exists():
+    if a.finished_marker and Path(a.finished_marker).exists():      # e.g. the experiment's summary.json: the run is complete
+        print(f"[restart] {a.finished_marker} exists; not resubmitting")
         return 0
+    env = {**os.environ, "RESTART_COUNT": str(count + 1)}
+    me = [sys.executable, "-m", "adana_b200.experiments", "restart", "--max_restarts", str(a.max_restarts),
+          *(["--finished_marker", a.finished_marker] if a.finished_marker else []), *largs]
+    if os.environ.get("SLURM_JOB_ID"):
+        # resubmit with the resources of the running job (scripts/restart_enoki.sh:46-94): account, time limit, nodes,
+        # GPUs per node, memory (0 = all of the node's, must be kept) and name; the restart count travels with --export
+        info = subprocess.run(["scontrol", "show", "job", os.environ["SLURM_JOB_ID"]], capture_output=True, text=True).stdout
+
+        def field(name, default):
+            m = re.search(rf"\b{name}=(\S+)", info)
+            return m.group(1) if m else default
+
+        gpus = os.environ.get("SLURM_GPUS_PER_NODE")
+        if not gpus:
+            m = re.search(r"gres/gpu[:=](\S+)", info) or re.search(r"gpu[:=](\d+)", info)
+            gpus = m.group(1) if m else 1
+        return _sbatch(me, field("JobName", os.environ.get("SLURM_JOB_NAME", "adana-restart")), gpus,
+                       field("TimeLimit", "4:00:00"), field("MinMemoryNode", os.environ.get("SLURM_MEM_PER_NODE", "0")),
+                       field("Account", os.environ.get("SLURM_JOB_ACCOUNT")), export={"RESTART_COUNT": count + 1},
+                       nodes=field("NumNodes", 1))
     return subprocess.call(me, env=env)
 
 

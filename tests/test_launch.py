@@ -213,3 +213,52 @@ def test_sweep_submits_the_same_grid_as_the_reference_sweep_script(ref_src, tmp_
                 assert float(got[k]) == float(v), k
             else:
                 assert got[k] == v, k
+
+
+def test_restart_resubmits_with_the_running_jobs_resources_and_stops_when_done(tmp_path, monkeypatch, capsys):
+    """Under SLURM the restart driver asks `scontrol` for the running job's account, time limit, nodes, memory and name,
+    and submits itself again with RESTART_COUNT + 1 (scripts/restart_enoki.sh:46-94).  `scontrol`, `sbatch` and the
+    launcher are stand-ins; nothing is submitted anywhere."""
+    import subprocess
+
+    calls = []
+
+    def fake_call(cmd, **kw):
+        calls.append(("call", [str(c) for c in cmd], kw.get("env")))
+        return 0
+
+    def fake_run(cmd, **kw):
+        calls.append(("run", list(cmd), None))
+        return subprocess.CompletedProcess(cmd, 0, stdout="JobId=77 JobName=enoki_h16 Account=def-lab TimeLimit=04:00:00 NumNodes=1 "
+                                           "MinMemoryNode=0 TresPerNode=gres/gpu:4", stderr="")
+
+    monkeypatch.setattr(experiments.subprocess, "call", fake_call)
+    monkeypatch.setattr(experiments.subprocess, "run", fake_run)
+    monkeypatch.setenv("SLURM_JOB_ID", "77")
+    monkeypatch.setenv("SLURM_GPUS_PER_NODE", "h100:4")
+    monkeypatch.setenv("RESTART_COUNT", "2")
+    args = ["restart", "--arch", "enoki", "--opt", "dana-star-mk4", "--heads", "16", "--iterations_to_run", "2000", "--no_auto_resume"]
+    assert experiments.main(args) == 0
+    launch, sbatch = calls[0][1], calls[-1][1]
+    assert "adana_b200.launch" in launch and "--no_auto_resume" not in launch and "--iterations_to_run" in launch
+    assert sbatch[0] == "sbatch" and "--export=ALL,RESTART_COUNT=3" in sbatch and "--account=def-lab" in sbatch
+    assert {"--job-name=enoki_h16", "--time=04:00:00", "--mem=0", "--nodes=1", "--gres=gpu:h100:4"} <= set(sbatch)
+    assert "experiments restart" in sbatch[-1] and "--heads 16" in sbatch[-1]
+    # a launch that fails is not resubmitted
+    calls.clear()
+    monkeypatch.setattr(experiments.subprocess, "call", lambda cmd, **kw: calls.append(cmd) or 3)
+    assert experiments.main(args) == 3 and len(calls) == 1
+    # a finished run (its marker exists) is not resubmitted either; without --iterations_to_run nothing restarts
+    monkeypatch.setattr(experiments.subprocess, "call", fake_call)
+    done = tmp_path / "summary.json"
+    done.write_text("{}")
+    calls.clear()
+    assert experiments.main(["restart", "--finished_marker", str(done), *args[1:]]) == 0
+    assert [c[0] for c in calls] == ["call"]
+    calls.clear()
+    assert experiments.main(["restart", "--arch", "enoki", "--opt", "adana", "--heads", "8"]) == 0 and len(calls) == 1
+    # outside SLURM the next segment starts right away with the count in its environment
+    monkeypatch.delenv("SLURM_JOB_ID")
+    calls.clear()
+    assert experiments.main(args) == 0
+    assert len(calls) == 2 and calls[1][2]["RESTART_COUNT"] == "3" and "restart" in calls[1][1]
