@@ -12,7 +12,7 @@ largeclass_logistic.py: mixture-of-experts and power-law logistic problems with 
 from .ode import DanaHparams, ODEInputs, solve_risk_ode  # noqa: F401
 from .plrf import PowerLawRF, train_plrf  # noqa: F401
 from .sweeps import compare_rules, final_risk_exponent, sweep, tau_order_statistics  # noqa: F401
-from .rules import (ademamix_rule, adana_rule, dana_mk4_rule, dana_star_mk4_rule, powerlaw_schedule,  # noqa: F401
+from .rules import (ademamix_rule, adana_rule, dana_mk4_rule, dana_star_mk4_rule, dana_star_rule, powerlaw_schedule,  # noqa: F401
                     scale_by_learning_rate)
 from .deterministic import (deterministic_rho_weights, deterministic_spectra, theory_empirical_measure,  # noqa: F401
                             theory_f_measure, theory_kappa, theory_lambda_min, theory_limit_loss, theory_m, theory_rhos,

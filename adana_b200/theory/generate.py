@@ -12,7 +12,7 @@ Same experiments as the reference's jax/hummingbird_generate.py:85-550 (every op
 noise from a Student-t distribution, learning rates g2 = g2_scale * min(1, batch / Tr K), one run per kappa plus an Adam
 baseline) and jax/taustats_generate.py:84-485 (tau of the Dana-Star state at log-spaced times, reduced to order
 statistics at ranks floor(1.1^k) from both tails), and the spectral figures of jax/deterministic_equivalent.py.
-`m-sweep` trains Dana-Star (unclipped, kappa = (1 - log_d batch) / (2 alpha) unless given), Dana-Star-MK4 (kappa = 1,
+`m-sweep` trains the first Dana-Star (`rules.dana_star_rule`, kappa = (1 - log_d batch) / (2 alpha) unless given), Dana-Star-MK4 (kappa = 1,
 clipped) and Adam on the same batches for several numbers of experts (jax/moe_m_sweeps_mk4.py:414-680) or of classes of
 the logistic problem (jax/lr_m_sweeps.py:294-540).  `debug-steps` walks both Dana-Star variants through the first
 steps on identical gradients and records the statistics of every buffer (jax/debug_mk4_optimizer.py:15-200).
@@ -27,7 +27,7 @@ from typing import Dict
 import numpy as np
 
 from .problems import LogisticPLRF, MixtureOfExpertsPLRF, log_spaced_steps, train_logistic_plrf, train_moe_plrf
-from .rules import ademamix_rule, dana_mk4_rule, dana_star_mk4_rule, scale_by_learning_rate
+from .rules import ademamix_rule, dana_mk4_rule, dana_star_mk4_rule, dana_star_rule, scale_by_learning_rate
 from .sweeps import tau_order_statistics
 
 
@@ -141,7 +141,7 @@ def _star_rules(a, trace_k: float) -> Dict[str, tuple]:
     g3 = a.g3_over_g2 * g2
     kappa_b = np.log(a.batch_size) / np.log(a.d)
     kappa = a.kappa if a.kappa is not None else (1.0 - kappa_b) / (2 * a.alpha)
-    rules = {"dana-star": dana_star_mk4_rule(g2, g3, a.delta, 1e-8, float(kappa), None),
+    rules = {"dana-star": dana_star_rule(g2, g3, float(kappa)),
              "dana-star-mk4": dana_star_mk4_rule(g2, g3, a.delta, 1e-8, 1.0, a.clipsnr)}
     if not a.disable_adam:
         rules["adam"] = adam_rule(a.adam_lr * min(1.0, a.batch_size / trace_k), a.adam_beta1, a.adam_beta2)

@@ -112,6 +112,42 @@ def dana_star_mk4_rule(g2=1.0, g3=1.0, delta=8.0, epsilon=1e-8, kappa=1.0, clips
     return _logtime_rule(g2, g3, delta, epsilon, kappa, clipsnr, wd, True, convention)
 
 
+def dana_star_rule(g2_constant: float, g3_constant: float, kappa: float, epsilon: float = 1e-8, clipsnr: float = 2.0,
+                   beta_time_scale: float = 6.0, wd: Optional[ScalarOrSchedule] = None):
+    """The first Dana-Star ("galaxy", jax/optimizers.py:69-85, 607-758), which the m-sweeps compare MK4 against.  Per
+    coordinate, with beta = (1 + count / 6)^-1 for all three averages and t = count:
+        v, m, tau EMAs as in MK4 (tau from |u| / (|u| + sqrt(v) + eps) with the NEW v)
+        reg = max(min(tau, 1/2) / (1 - min(tau, 1/2)), 1 / (1 + t)),  r = sqrt(reg),  eff = max(tau t, 1)
+        update = -g2 u (r / (sqrt v + eps)) min(1, clipsnr sqrt(v) / (r |u| + eps))  -  g3(eff) m r / (sqrt v + eps)
+    g3(x) = g3_constant (1 + x)^(1 - kappa) is read at each coordinate's own effective time: where MK4 clips the
+    momentum's size, this rule clips the gradient term."""
+    wd = _sched(wd, 0.0)
+    g3 = powerlaw_schedule(g3_constant, 0.0, 1.0 - kappa, 1.0)
+
+    def init(params):
+        z = np.zeros_like(params, dtype=np.float64)
+        return LogTimeState(0, z.copy(), z.copy(), z.copy())
+
+    def update(grads, state, params=None):
+        u = np.asarray(grads, dtype=np.float64)
+        t = float(state.count)
+        beta = 1.0 / (1.0 + t / beta_time_scale)
+        v = state.v * (1 - beta) + beta * u * u
+        tau = state.tau * (1 - beta) + beta * np.abs(u) / (np.abs(u) + np.sqrt(v) + epsilon)
+        m = state.m * (1 - beta) + beta * u
+        half = np.minimum(tau, 0.5)
+        r = np.sqrt(np.maximum(half / (1.0 - half), 1.0 / (1.0 + t)))
+        eff = np.maximum(tau * t, 1.0)
+        root = np.sqrt(v)
+        scale = r / (root + epsilon)
+        out = -g2_constant * u * scale * np.minimum(1.0, clipsnr * root / (r * np.abs(u) + epsilon)) - g3(eff) * m * scale
+        if params is not None:
+            out = out - wd(state.count) * np.asarray(params, dtype=np.float64)
+        return out, LogTimeState(state.count + 1, m, v, tau)
+
+    return init, update
+
+
 class AdEMAMixState(NamedTuple):
     count: int
     fast: Optional[np.ndarray]

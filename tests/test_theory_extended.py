@@ -167,3 +167,34 @@ def test_schedule_studies_and_generators_command_lines(tmp_path):
     assert first["dana-star"]["m"] == first["dana-star-mk4"]["m"]            # identical gradients, identical first step
     assert set(first["dana-star"]) == {"gradient", "m", "v", "tau", "update", "risk"}
     assert dbg["trace"][-1]["dana-star"]["risk"] < 0.5 * 1.0 + 1.0
+
+
+def test_first_dana_star_rule_against_a_scalar_restatement():
+    """`dana_star_rule` (the first Dana-Star of the JAX package) against the same formulas written out per coordinate
+    with plain floats, including the effective time max(tau t, 1) at which each coordinate reads its own g3."""
+    import math
+
+    rng = np.random.default_rng(3)
+    g2c, g3c, kappa, eps, clip = 0.05, 0.02, 0.6, 1e-8, 2.0
+    init, update = T.dana_star_rule(g2c, g3c, kappa, eps, clip, wd=1e-3)
+    p = rng.standard_normal(7)
+    state = init(p)
+    m, v, tau = [0.0] * 7, [0.0] * 7, [0.0] * 7
+    for count in range(12):
+        g = rng.standard_normal(7) * (rng.random(7) < 0.6)          # sparse gradients exercise the tau floor
+        d, state = update(g, state, p)
+        beta = 1.0 / (1.0 + count / 6.0)
+        for i in range(7):
+            u = float(g[i])
+            v[i] = v[i] * (1 - beta) + beta * u * u
+            tau[i] = tau[i] * (1 - beta) + beta * abs(u) / (abs(u) + math.sqrt(v[i]) + eps)
+            m[i] = m[i] * (1 - beta) + beta * u
+            h = min(tau[i], 0.5)
+            r = math.sqrt(max(h / (1 - h), 1.0 / (1.0 + count)))
+            eff = max(tau[i] * count, 1.0)
+            g3 = g3c * (1.0 + eff) ** (1.0 - kappa)
+            scale = r / (math.sqrt(v[i]) + eps)
+            want = -g2c * u * scale * min(1.0, clip * math.sqrt(v[i]) / (r * abs(u) + eps)) - g3 * m[i] * scale - 1e-3 * p[i]
+            assert d[i] == pytest.approx(want, rel=1e-12, abs=1e-15), (count, i)
+        p = p + d
+    assert state.count == 12
