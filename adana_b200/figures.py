@@ -12,6 +12,7 @@ numbers come from `adana_b200.analysis`; the drawing needs no plotting package: 
     python -m adana_b200.figures compute <exp_dir>:<non_emb> [...]  --out compute.svg
     python -m adana_b200.figures lr-law  sizes.json --out lr_law.svg        # {"P": [...], "lr": [...]}
     python -m adana_b200.figures hummingbird hummingbird.json --out hummingbird.svg
+    python -m adana_b200.figures hummingbird-multi mk4.json ademamix.json --out hummingbird_all.svg
     python -m adana_b200.figures taustats    taustats.json    --out taustats.svg
 """
 from __future__ import annotations
@@ -170,6 +171,34 @@ def fig_hummingbird(data: dict, out) -> Path:
     return ch.save(out)
 
 
+def fig_hummingbird_multi(datasets: Sequence[dict], out, kappa_min: float = 0.0, color_by_clipsnr: bool = False) -> Path:
+    """Several kappa sweeps (one per optimizer, each the output of `theory.generate hummingbird`) on one pair of axes:
+    one colour per optimizer (or per clip-SNR), lines faint and thin at kappa_min and opaque and thick at kappa = 1,
+    the Adam baseline once, dashed (reference: visualization/hummingbird_plot_from_data_multiopt.py:107-300)."""
+    from .studies import palette
+
+    ch = LineChart("risk against step: kappa sweeps of several optimizers", "step", "population risk", logx=True, logy=True)
+    adam_done = False
+    for data in datasets:
+        opt = data["args"].get("optimizer", "")
+        clip = 16.0 if opt == "adana" else float(data["args"].get("clipsnr", 1.0))
+        col = palette.clipsnr_color(clip) if color_by_clipsnr else palette.color(opt, "#333333")
+        first = True
+        for name, run in sorted(data["runs"].items()):
+            if name == "adam":
+                if not adam_done:
+                    ch.add(run["timestamps"], run["losses"], "Adam", "#000000", dashed=True, width=2.5)
+                    adam_done = True
+                continue
+            kappa = float(name.rsplit("kappa", 1)[1])
+            if kappa < kappa_min:
+                continue
+            opacity, width = palette.line_emphasis(kappa, kappa_min)
+            ch.add(run["timestamps"], run["losses"], palette.display_name(opt) if first else "", col, opacity=opacity, width=width)
+            first = False
+    return ch.save(out)
+
+
 def fig_taustats(data: dict, out, raw: bool = False) -> Path:
     """Distribution of tau at the recorded times as a dual-tail CDF: tau (regularised as the optimizer regularises it,
     unless `raw`) on a log axis against the cumulative probability on a logit axis with compressed tails, one line per
@@ -191,7 +220,7 @@ def fig_taustats(data: dict, out, raw: bool = False) -> Path:
 def main(argv=None):
     p = argparse.ArgumentParser(prog="python -m adana_b200.figures")
     sub = p.add_subparsers(dest="cmd", required=True)
-    for name in ("curves", "compute", "lr-law", "hummingbird", "taustats"):
+    for name in ("curves", "compute", "lr-law", "hummingbird", "hummingbird-multi", "taustats"):
         s = sub.add_parser(name)
         s.add_argument("inputs", nargs="+")
         s.add_argument("--out", required=True)
@@ -201,6 +230,8 @@ def main(argv=None):
         return fig_curves(a.inputs, a.out, a.key)
     if a.cmd == "compute":
         return fig_compute(a.inputs, a.out, a.key)
+    if a.cmd == "hummingbird-multi":
+        return fig_hummingbird_multi([json.loads(Path(f).read_text()) for f in a.inputs], a.out)
     data = json.loads(Path(a.inputs[0]).read_text())
     if a.cmd == "lr-law":
         return fig_lr_law(data["P"], data["lr"], a.out)

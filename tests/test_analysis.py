@@ -69,6 +69,10 @@ def test_figure_scripts_write_svg(tmp_path):
     G.main(["hummingbird", "--v", "100", "--d", "24", "--m", "4", "--steps", "60", "--kappa_step", "1.0",
             "--out", str(tmp_path / "h.json")])
     d = F.main(["hummingbird", str(tmp_path / "h.json"), "--out", str(tmp_path / "h.svg")])
+    G.main(["hummingbird", "--v", "100", "--d", "24", "--m", "4", "--steps", "60", "--kappa_step", "1.0", "--optimizer", "dana-mk4",
+            "--out", str(tmp_path / "h2.json")])
+    multi = F.main(["hummingbird-multi", str(tmp_path / "h.json"), str(tmp_path / "h2.json"), "--out", str(tmp_path / "hm.svg")]).read_text()
+    assert multi.count("<polyline") == 5 and multi.count(">Adam<") == 1 and "DANA-Star-MK4" in multi and "DANA-MK4" in multi
     G.main(["taustats", "--v", "100", "--d", "24", "--m", "8", "--steps", "70", "--out", str(tmp_path / "t.json")])
     e = F.main(["taustats", str(tmp_path / "t.json"), "--out", str(tmp_path / "t.svg")])
     for f in (a, b, c, d, e):
