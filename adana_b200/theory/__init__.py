@@ -14,7 +14,7 @@ from .plrf import PowerLawRF, train_plrf  # noqa: F401
 from .sweeps import compare_rules, final_risk_exponent, sweep, tau_order_statistics  # noqa: F401
 from .rules import (ademamix_rule, adana_rule, dana_mk4_rule, dana_star_mk4_rule, dana_star_rule, powerlaw_schedule,  # noqa: F401
                     scale_by_learning_rate)
-from .deterministic import (deterministic_rho_weights, deterministic_spectra, theory_empirical_measure,  # noqa: F401
+from .deterministic import (deterministic_rho_weights, deterministic_spectra, spectral_density, theory_empirical_measure,  # noqa: F401
                             theory_f_measure, theory_kappa, theory_lambda_min, theory_limit_loss, theory_m, theory_rhos,
                             theory_tau)
 from .problems import (LogisticPLRF, MixtureOfExpertsPLRF, log_spaced_steps, train_logistic_plrf,  # noqa: F401

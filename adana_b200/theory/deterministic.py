@@ -157,14 +157,8 @@ def deterministic_rho_weights(v: int, d: int, alpha: float, beta: float, a: np.n
     xs_per_split = int(xs_per_split or d)
     order = np.argsort(-np.asarray(a))
     a, b = np.asarray(a, dtype=np.float64)[order], np.asarray(b, dtype=np.float64)[order]
-    edges, cur, j = [], 2.2, 1.0
-    left = a.min() * 0.5
-    while cur >= left:
-        edges.append(cur)
-        cur *= 1.0 - 1.0 / np.sqrt(j + 2.0)
-        j += 1.0
     weights = []
-    for hi, lo in zip(edges[:-1], edges[1:]):
+    for lo, hi in _shrinking_bins(a.min() * 0.5):
         idx = np.where((a >= lo) & (a <= hi))[0]
         if len(idx) == 0:
             continue
@@ -177,10 +171,38 @@ def deterministic_rho_weights(v: int, d: int, alpha: float, beta: float, a: np.n
     return out
 
 
-def deterministic_spectra(v: int, d: int, alpha: float, xs_per_split: Optional[int] = None) -> Tuple[np.ndarray, np.ndarray]:
-    """(grid, density) of the eigenvalue distribution of the deterministic equivalent between its smallest eigenvalue
-    and just above the largest population eigenvalue (:492-551)."""
-    n = int(xs_per_split or 10 * d)
+def _shrinking_bins(left_edge: float, right_edge: float = 2.2):
+    """(left, right) ends of the bins that cut [left_edge, right_edge] from the right with ratios 1 - 1/sqrt(j + 2)."""
+    seq, cur, j = [], right_edge, 1.0
+    while cur >= left_edge:
+        seq.append(cur)
+        cur *= 1.0 - 1.0 / np.sqrt(j + 2.0)
+        j += 1.0
+    return list(zip(seq[1:], seq[:-1]))
+
+
+def spectral_density(v: int, d: int, alpha: float, points: Optional[int] = None) -> Tuple[np.ndarray, np.ndarray]:
+    """(grid, density) of the eigenvalue distribution of the deterministic equivalent between half its smallest
+    eigenvalue and just above the largest population eigenvalue, on one geometric grid (for drawing)."""
+    n = int(points or 10 * d)
     lo = max(theory_lambda_min(alpha, v, d) * 0.5, 1e-12)
     xs = np.geomspace(lo, 1.1, n)
     return xs, theory_empirical_measure(v, d, alpha, xs)
+
+
+def deterministic_spectra(v: int, d: int, alpha: float, xs_per_split: Optional[int] = None) -> np.ndarray:
+    """Eigenvalues of the deterministic equivalent, largest first: the points where the (unnormalised) distribution
+    function of its spectral measure, accumulated from the right over shrinking bins with `xs_per_split` grid points
+    each (default d), crosses a half-integer (:492-551)."""
+    n = int(xs_per_split or d)
+    spectra, carried = [], 0.0
+    for left, right in _shrinking_bins(theory_lambda_min(alpha, v, d) * 0.5):
+        xs = np.linspace(left, right, n)
+        density = theory_empirical_measure(v, d, alpha, xs, err=-20.0)
+        cdf = np.cumsum(density) * (xs[1] - xs[0])
+        cdf = (cdf[-1] + carried) - cdf            # mass to the right of each grid point
+        carried = cdf[0]
+        frac = cdf - np.floor(cdf)
+        hit = (cdf[:-1] > cdf[1:]) & (frac[:-1] > 0.5) & (frac[1:] < 0.5)
+        spectra.extend(xs[:-1][hit].tolist())
+    return np.sort(np.array(spectra))[::-1]

@@ -129,7 +129,7 @@ def cmd_taustats(a):
 def cmd_spectra(a):
     from . import deterministic as D
 
-    xs, dens = D.deterministic_spectra(a.v, a.d, a.alpha, a.points)
+    xs, dens = D.spectral_density(a.v, a.d, a.alpha, a.points)
     eigs, rho = D.theory_rhos(a.alpha, a.beta, a.d)
     return {"args": vars(a), "xs": xs.tolist(), "density": dens.tolist(), "kappa": D.theory_kappa(a.alpha, a.v, a.d),
             "lambda_min": D.theory_lambda_min(a.alpha, a.v, a.d), "limit_loss": D.theory_limit_loss(a.alpha, a.beta, a.v, a.d),

@@ -41,7 +41,7 @@ def test_fixed_point_m_solves_its_equation_and_matches_a_random_sketch():
     prob = T.PowerLawRF.initialize_random(alpha, 0.4, v, d, seed=1)
     assert abs(prob.limit_risk() / D.theory_limit_loss(alpha, 0.4, v, d) - 1.0) < 0.35
     # the density of states integrates to ~d eigenvalues (mass d / 1 per eigenvalue)
-    grid, dens = D.deterministic_spectra(v, d, alpha, 4000)
+    grid, dens = D.spectral_density(v, d, alpha, 4000)
     mass = np.trapezoid(dens, grid)
     assert 0.6 * d < mass < 1.4 * d, mass
 

@@ -1,0 +1,150 @@
+"""The NumPy theory package against the reference's own JAX files.  `benchmarks/reference_jax_oracle.py` imports
+`jax/optimizers.py` and `jax/deterministic_equivalent.py` of the reference unmodified on top of stand-in `jax` / `optax`
+modules that map the few calls they make onto NumPy, and records parameter trajectories and theory values in
+`tests/golden/theory_reference_values.json`; here the restatements in `adana_b200/theory` must reproduce them."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from adana_b200 import theory as T
+from adana_b200.theory import deterministic as D
+
+G = json.loads((Path(__file__).parent / "golden" / "theory_reference_values.json").read_text())
+LR = lambda c: 0.5 / (1.0 + c / 20.0)
+
+
+def _trajectory(rule, grads, p0):
+    init, update = T.scale_by_learning_rate(rule, LR)
+    p = np.array(p0, dtype=np.float64)
+    state = init(p)
+    out = []
+    for g in grads:
+        d, state = update(np.asarray(g), state, p)
+        p = p + d
+        out.append(p.copy())
+    return np.array(out)
+
+
+def _rule(name, kw):
+    if name.startswith("adana"):
+        return T.adana_rule(kw["g2_constant"], kw["g3_constant"], kw["delta"], 1e-8, kw["kappa"])
+    if name.startswith("dana_mk4"):
+        return T.dana_mk4_rule(kw["g2_constant"], kw["g3_constant"], kw["delta"], 1e-8, kw["kappa"], kw["clipsnr"])
+    if name.startswith("dana_star_mk4"):
+        return T.dana_star_mk4_rule(kw["g2_constant"], kw["g3_constant"], kw["delta"], 1e-8, kw["kappa"], kw["clipsnr"])
+    if name.startswith("dana_star"):
+        return T.dana_star_rule(kw["g2_constant"], kw["g3_constant"], kw["kappa_exponent"])
+    if name == "ademamix":
+        return T.ademamix_rule(0.9, 0.99, lambda c: 1.0 - 0.1 / (1.0 + c / 10.0), lambda c: min(c / 20.0, 1.0) * 3.0, 0.7, 1e-8, 0.01)
+    raise KeyError(name)
+
+
+@pytest.mark.parametrize("name", sorted(G["rules"]["runs"]))
+def test_update_rules_follow_the_reference_jax_trajectories(name):
+    """Forty steps on a partly sparse gradient sequence (the tau estimator sees zeros, the SNR clip engages in the
+    tight-clip cases): every parameter after every step equals the reference optimizer's, to rounding."""
+    run = G["rules"]["runs"][name]
+    mine = _trajectory(_rule(name, run["kwargs"]), G["rules"]["grads"], G["rules"]["p0"])
+    want = np.array(run["params"])
+    assert mine.shape == want.shape == (40, 6)
+    np.testing.assert_allclose(mine, want, rtol=1e-9, atol=1e-12)
+    assert np.abs(want[-1] - np.array(G["rules"]["p0"])).max() > 1e-3          # the trajectories actually move
+
+
+def test_powerlaw_schedule_matches():
+    g = G["powerlaw_schedule"]
+    s = T.powerlaw_schedule(*g["args"])
+    np.testing.assert_allclose([float(s(t)) for t in g["t"]], g["values"], rtol=1e-12)
+
+
+def test_deterministic_equivalent_scalars_match():
+    d = G["deterministic"]
+    for c in d["limit_loss"]:
+        assert D.theory_limit_loss(*c["args"]) == pytest.approx(c["value"], rel=2e-3)     # kappa / tau inside are iterated to 1e-3
+    for c in d["kappa"]:
+        assert D.theory_kappa(*c["args"]) == pytest.approx(c["value"], rel=2e-3)
+    for c in d["tau"]:
+        assert D.theory_tau(*c["args"]) == pytest.approx(c["value"], rel=2e-3)
+    for c in d["lambda_min"]:
+        assert D.theory_lambda_min(*c["args"]) == pytest.approx(c["value"], rel=1e-4)
+    for c in d["rhos"]:
+        eigs, rho = D.theory_rhos(*c["args"])
+        np.testing.assert_allclose(eigs, c["eigs"], rtol=1e-10)
+        np.testing.assert_allclose(rho, c["rho"], rtol=1e-10)
+    cw = d["chunk_weights"]
+    np.testing.assert_allclose(D.chunk_weights(np.array(cw["xs"]), np.array(cw["density"]), np.array(cw["a"]), np.array(cw["b"])),
+                               cw["value"], rtol=1e-10)
+
+
+def test_fixed_point_and_measures_match():
+    d = G["deterministic"]
+    m = d["m"]
+    want = np.array(m["value"]["re"]) + 1j * np.array(m["value"]["im"])
+    got = D.theory_m(m["args"]["v"], m["args"]["d"], m["args"]["alpha"], np.array(m["xs"]))
+    np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-9)
+    f = d["f_measure"]
+    np.testing.assert_allclose(D.theory_f_measure(f["args"]["v"], f["args"]["d"], f["args"]["alpha"], f["args"]["beta"], np.array(f["xs"])),
+                               f["value"], rtol=1e-5, atol=1e-9)
+    e = d["empirical_measure"]
+    np.testing.assert_allclose(D.theory_empirical_measure(e["args"]["v"], e["args"]["d"], e["args"]["alpha"], np.array(e["xs"])),
+                               e["value"], rtol=1e-5, atol=1e-9)
+
+
+def _ode_setup():
+    from adana_b200.theory.ode import DanaHparams, ODEInputs
+
+    o = G["ode"]
+    a = o["args"]
+    eigs, rho = D.theory_rhos(a["alpha"], a["beta"], a["d"])
+    z = np.zeros_like(rho)
+    inp = ODEInputs(eigs, rho, z, z.copy(), o["risk_infinity"])
+    dl = T.powerlaw_schedule(1.0, 0.0, -1.0, 6.0)
+    return o, a, inp, dl, DanaHparams
+
+
+@pytest.mark.parametrize("name,kw", [("full", {}), ("approximate", dict(approximate=True)), ("adam", dict(adaptive="adam")),
+                                     ("rmsprop_dana", dict(adaptive="rmsprop_dana"))])
+def test_risk_ode_equals_the_reference_solver(name, kw):
+    """`solve_risk_ode` against `ode_resolvent_log_implicit` of the reference's jax/dana_plrf.py, run unmodified on the
+    NumPy stand-in: the full and the approximate coefficients and both adaptive normalisations."""
+    o, a, inp, dl, DanaHparams = _ode_setup()
+    hp = DanaHparams(lambda t: 1.0, lambda t: 0.05, T.powerlaw_schedule(0.02, 0.0, -0.5, 1.0), dl)
+    t, r = T.solve_risk_ode(inp, hp, a["batch"], a["t_max"], a["dt"], **kw)
+    want = o["runs"][name]
+    np.testing.assert_allclose(t, want["t"], rtol=1e-5, atol=1e-6)        # the reference keeps its time grid in float32
+    np.testing.assert_allclose(r, want["twice_risk"], rtol=2e-4)
+    assert r[-1] < 0.05 * r[0]
+
+
+def test_momentum_tracking_and_trajectory_driven_schedules_equal_the_reference_variants():
+    """The options of `solve_risk_ode` against the solver copies inside jax/kappa_sweep_plot.py (momentum norm, DanaStar
+    renormalisation, the power rule for g3) and jax/dynamical_schedule_plot.py (the ratio rule)."""
+    o, a, inp, dl, DanaHparams = _ode_setup()
+    hp = DanaHparams(dl, lambda t: 0.01, T.powerlaw_schedule(0.01, 0.0, 0.4, 1.0), dl)
+    for name, kw in (("momentum_renormalized", dict(risk_renormalized=True)), ("momentum_plain", {}),
+                     ("momentum_dynamic", dict(risk_renormalized=True, dynamic_g3=(0.0, 0.75, 1.0)))):
+        t, r, m = T.solve_risk_ode(inp, hp, a["batch"], a["t_max"], a["dt"], momentum=True, shifted_clock=True, **kw)
+        want = o["runs"][name]
+        np.testing.assert_allclose(r, want["twice_risk"], rtol=2e-4, err_msg=name)
+        np.testing.assert_allclose(m, want["momentum"], rtol=2e-3, atol=1e-12, err_msg=name)
+    hp = DanaHparams(lambda t: 1.0, lambda t: 0.05, lambda t: 0.02, dl)
+    t, r, m = T.solve_risk_ode(inp, hp, a["batch"], a["t_max"], a["dt"], momentum=True, dynamic_g3="ratio")
+    want = o["runs"]["ratio_rule"]
+    np.testing.assert_allclose(r, want["twice_risk"], rtol=2e-4)
+    np.testing.assert_allclose(m, want["momentum"], rtol=2e-3, atol=1e-12)
+
+
+def test_deterministic_spectrum_and_rho_weights_match():
+    """Eigenvalues read off half-integer crossings of the accumulated spectral measure, and the rho weights as contour
+    pieces around the leading eigenvalues.  The reference evaluates these in single-precision complex numbers, so the
+    densities agree to a few digits and a crossing can land on the neighbouring grid point."""
+    s = G["deterministic"]["spectra"]
+    got, want = D.deterministic_spectra(**s["args"]), np.array(s["value"])
+    assert len(got) == len(want) == s["args"]["d"]
+    np.testing.assert_allclose(got, want, rtol=0.03)
+    r = G["deterministic"]["rho_weights"]
+    got = D.deterministic_rho_weights(**r["args"], a=np.array(r["a"]), b=np.array(r["b"]))
+    np.testing.assert_allclose(got, r["value"], rtol=0.03)
+    assert np.all(got > 0)
