@@ -161,6 +161,8 @@ def install_shims():
     src = types.ModuleType("optax._src")
     src.base, src.numerics, src.utils = base, numerics, utils
     optax._src = src
+    jax.random = types.ModuleType("jax.random")          # only the problem classes' samplers use it; the oracle passes W in
+    sys.modules["jax.random"] = jax.random
     sys.modules.update({"jax": jax, "jax.numpy": jnp, "chex": chex, "optax": optax, "optax.tree_utils": otu,
                         "optax._src": src, "optax._src.base": base, "optax._src.numerics": numerics, "optax._src.utils": utils})
 
@@ -315,6 +317,22 @@ def main():
     ode["runs"]["ratio_rule"] = {"t": plain(np.asarray(t, dtype=np.float64)), "twice_risk": plain(np.asarray(r, dtype=np.float64)),
                                  "momentum": plain(np.asarray(m, dtype=np.float64))}
     G["ode"] = ode
+
+    # ---- the power-law random-features problem with a given sketch ------------------------------------------------------------
+    sys.path.insert(0, str(jdir))                     # power_law_rf.py imports deterministic_equivalent by name
+    sys.modules["deterministic_equivalent"] = D
+    P = load(jdir / "power_law_rf.py", "ref_jax_power_law_rf")
+    v, dd = 60, 12
+    W = np.random.default_rng(5).standard_normal((v, dd)) / np.sqrt(dd)
+    prob = P.PowerLawRF(0.9, 0.4, _j(W))
+    ws = np.random.default_rng(6).standard_normal((3, dd))
+    G["plrf"] = {"alpha": 0.9, "beta": 0.4, "W": W.tolist(), "w": ws.tolist(),
+                 "population_trace": float(prob.population_trace),
+                 "risk": [float(prob.get_population_risk(_j(w.reshape(dd, 1)))) for w in ws],
+                 "hessian_spectra": plain(np.asarray(prob.get_hessian_spectra(), dtype=np.float64)),
+                 "rhos": plain(np.asarray(prob.get_rhos(), dtype=np.float64)),
+                 "theory_limit_loss": float(prob.get_theory_limit_loss()),
+                 "empirical_limit_loss": float(prob.get_empirical_limit_loss())}
     Path(a.out).write_text(json.dumps(plain(G)))
     print(f"wrote {a.out}")
 

@@ -148,3 +148,17 @@ def test_deterministic_spectrum_and_rho_weights_match():
     got = D.deterministic_rho_weights(**r["args"], a=np.array(r["a"]), b=np.array(r["b"]))
     np.testing.assert_allclose(got, r["value"], rtol=0.03)
     assert np.all(got > 0)
+
+
+def test_power_law_rf_problem_matches_the_reference_class():
+    """The reference's PowerLawRF built on a given sketch W: risk of arbitrary weights, Hessian spectrum, the rho_j of
+    the target, the trace that sets the stable step, and the risk of the least-squares solution."""
+    g = G["plrf"]
+    prob = T.PowerLawRF(g["alpha"], g["beta"], np.array(g["W"]))
+    assert prob.population_trace == pytest.approx(g["population_trace"], rel=1e-12)
+    for w, want in zip(g["w"], g["risk"]):
+        assert prob.population_risk(np.array(w)) == pytest.approx(want, rel=1e-10)
+    np.testing.assert_allclose(prob.hessian_spectrum(), g["hessian_spectra"], rtol=1e-9)
+    np.testing.assert_allclose(prob.rhos(), g["rhos"], rtol=1e-7)
+    assert prob.limit_risk() == pytest.approx(g["empirical_limit_loss"], rel=1e-6)
+    assert D.theory_limit_loss(g["alpha"], g["beta"], 60, 12) == pytest.approx(g["theory_limit_loss"], rel=2e-3)
