@@ -161,7 +161,9 @@ def install_shims():
     src = types.ModuleType("optax._src")
     src.base, src.numerics, src.utils = base, numerics, utils
     optax._src = src
-    jax.random = types.ModuleType("jax.random")          # only the problem classes' samplers use it; the oracle passes W in
+    jax.random = types.ModuleType("jax.random")          # a key is a NumPy seed here: enough for the constructors' sketch
+    jax.random.PRNGKey = lambda seed: int(seed)
+    jax.random.normal = lambda key, shape=(), dtype=None: _j(np.random.default_rng(key).standard_normal(shape))
     sys.modules["jax.random"] = jax.random
     sys.modules.update({"jax": jax, "jax.numpy": jnp, "chex": chex, "optax": optax, "optax.tree_utils": otu,
                         "optax._src": src, "optax._src.base": base, "optax._src.numerics": numerics, "optax._src.utils": utils})
@@ -333,6 +335,18 @@ def main():
                  "rhos": plain(np.asarray(prob.get_rhos(), dtype=np.float64)),
                  "theory_limit_loss": float(prob.get_theory_limit_loss()),
                  "empirical_limit_loss": float(prob.get_empirical_limit_loss())}
+    M = load(jdir / "moe_plrf.py", "ref_jax_moe_plrf")
+    moe = M.MixtureOfExpertsPLRF(1.1, 0.2, 50, 10, 5, 0.8, 7)
+    two = M.TwoExpertPLRF(1.0, 0.3, 40, 8, 0.7, 9) if hasattr(M, "TwoExpertPLRF") else None
+    params = np.random.default_rng(8).standard_normal((10, 5))
+    G["moe_plrf"] = {"alpha": 1.1, "beta": 0.2, "m": 5, "zeta": 0.8, "W": plain(np.asarray(moe.W)), "params": params.tolist(),
+                     "expert_probs": plain(np.asarray(moe.expert_probs, dtype=np.float64)),
+                     "risk": float(moe.population_risk(_j(params))),
+                     "per_expert": plain(np.asarray(moe.per_expert_population_risk(_j(params)), dtype=np.float64)),
+                     "single_risk": float(moe.population_risk(_j(params[:, 0]))),
+                     "optimal_risk": float(moe.optimal_risk())}
+    if two is not None:
+        G["moe_plrf"]["two_expert_probs"] = plain(np.asarray(two.expert_probs, dtype=np.float64))
     Path(a.out).write_text(json.dumps(plain(G)))
     print(f"wrote {a.out}")
 

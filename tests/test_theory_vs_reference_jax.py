@@ -162,3 +162,16 @@ def test_power_law_rf_problem_matches_the_reference_class():
     np.testing.assert_allclose(prob.rhos(), g["rhos"], rtol=1e-7)
     assert prob.limit_risk() == pytest.approx(g["empirical_limit_loss"], rel=1e-6)
     assert D.theory_limit_loss(g["alpha"], g["beta"], 60, 12) == pytest.approx(g["theory_limit_loss"], rel=2e-3)
+
+
+def test_moe_problem_matches_the_reference_class():
+    g = G["moe_plrf"]
+    prob = T.MixtureOfExpertsPLRF(g["alpha"], g["beta"], np.array(g["W"]), g["m"], g["zeta"])
+    np.testing.assert_allclose(prob.expert_probs, g["expert_probs"], rtol=1e-12)
+    params = np.array(g["params"])
+    assert prob.population_risk(params) == pytest.approx(g["risk"], rel=1e-10)
+    np.testing.assert_allclose(prob.per_expert_population_risk(params), g["per_expert"], rtol=1e-10)
+    assert T.PowerLawRF.population_risk(prob, params[:, 0]) == pytest.approx(g["single_risk"], rel=1e-10)
+    assert prob.limit_risk() == pytest.approx(g["optimal_risk"], rel=1e-6)
+    two = T.MixtureOfExpertsPLRF.two_experts(1.0, 0.3, 40, 8, 0.7)
+    np.testing.assert_allclose(two.expert_probs, g["two_expert_probs"], rtol=1e-12)
