@@ -16,7 +16,7 @@ the same minima in milliseconds and does not depend on a step count.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import numpy as np
 from scipy.optimize import brentq, least_squares, nnls

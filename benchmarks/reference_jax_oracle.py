@@ -15,7 +15,6 @@ writes `tests/golden/theory_reference_values.json` for `tests/test_theory_vs_ref
 import argparse
 import importlib.util
 import json
-import math
 import sys
 import types
 from collections import namedtuple
