@@ -14,8 +14,9 @@ drivers (`scripts/sweep.sh`, `scripts/restart_{enoki,qwen3}.sh`, `scripts/benchm
   `--iterations_to_run` was reached and the final iteration has not been, it starts (or, under SLURM,
   `sbatch`es) itself again with RESTART_COUNT+1 — a job that fits in a scheduler slot and continues
   from the `latest` checkpoint.
-* benchmark-batch: 5-iteration runs over heads x tp x micro-batch, records out-of-memory failures, the
-  `[Memory] ... peak_allocated=` line and the last `iter_dt=`; prints the largest batch that fits.
+* benchmark-batch: 5-iteration runs over heads x tp x batch in increasing batch order, stopping a (heads, tp) pair
+  at its first out-of-memory failure; records the `[Memory] ... peak_allocated=` line and the last `iter_dt=`,
+  prints and files the largest batch that fits.
 Environment (`config.sh` equivalent): `ADANA_CONFIG` may name a file of KEY=VALUE lines (WANDB_*,
 DATASETS_DIR, RESULTS_BASE_FOLDER, TIKTOKEN_CACHE_DIR, HF_HOME) that is loaded into the environment.
 """
@@ -171,30 +172,40 @@ def parse_run_log(text: str) -> dict:
 
 
 def cmd_benchmark_batch(a, extra):
-    results = []
-    for heads, tp, batch in itertools.product(a.heads, a.tp, a.batch):
-        largs = ["--arch", a.arch, "--opt", a.opt, "--heads", heads, "--nproc", a.nproc, "--batch_size", batch * (a.nproc // tp),
-                 "--acc_steps", 1, "--iterations", 5, "--warmup_steps", 1, "--no_wandb", "--no_auto_resume",
-                 "--distributed_backend", "fsdp", "--log_interval", 1, "--eval_interval", 1000000,
-                 "--latest_ckpt_interval", 0, "--dataset", a.dataset, *extra]
-        if tp > 1:
-            largs += ["--tp_size", tp]
-        if a.dry:
-            print(" ".join(shlex.quote(str(c)) for c in _launch_cmd(largs)))
-            continue
-        proc = subprocess.run(_launch_cmd(largs), capture_output=True, text=True)
-        rec = {"heads": heads, "tp": tp, "micro_batch": batch, "returncode": proc.returncode,
-               **parse_run_log(proc.stdout + proc.stderr)}
-        rec["ok"] = proc.returncode == 0 and not rec["oom"]
-        results.append(rec)
-        print(json.dumps(rec), flush=True)
-    best = {}
-    for r in results:
-        if r["ok"]:
-            key = (r["heads"], r["tp"])
-            best[key] = max(best.get(key, 0), r["micro_batch"])
-    for (heads, tp), b in sorted(best.items()):
-        print(f"heads={heads} tp={tp}: max micro-batch {b}")
+    """Largest batch that fits, per (heads, tp): 5-iteration runs in increasing batch order, stopping at the first one
+    that runs out of memory (scripts/benchmark_batch.sh:57-208).  As there, `--batch` is the batch of one step over
+    all data-parallel ranks (acc_steps 1): the backend divides it by world / tp."""
+    results, lines = [], ["# heads  tp  batch  peak_mem(GiB)  iter_dt(s)  status"]
+    for heads, tp in itertools.product(a.heads, a.tp):
+        best = 0
+        for batch in a.batch:
+            largs = ["--arch", a.arch, "--opt", a.opt, "--heads", heads, "--nproc", a.nproc, "--batch_size", batch,
+                     "--acc_steps", 1, "--iterations", a.iterations, "--warmup_steps", 3, "--scheduler", "cos", "--kappa", a.kappa,
+                     "--clipsnr", 1.0, "--no_wandb", "--no_auto_resume", "--distributed_backend", "fsdp", "--log_interval", 1,
+                     "--eval_interval", 9999, "--eval_batches", 4, "--latest_ckpt_interval", 0, "--permanent_ckpt_interval", 0,
+                     "--dataset", a.dataset, *extra]
+            if tp > 1:
+                largs += ["--tp_size", tp]
+            if a.dry:
+                print(" ".join(shlex.quote(str(c)) for c in _launch_cmd(largs)))
+                continue
+            proc = subprocess.run(_launch_cmd(largs), capture_output=True, text=True)
+            rec = {"heads": heads, "tp": tp, "batch": batch, "returncode": proc.returncode,
+                   **parse_run_log(proc.stdout + proc.stderr)}
+            rec["ok"] = proc.returncode == 0 and not rec["oom"]
+            results.append(rec)
+            print(json.dumps(rec), flush=True)
+            if not rec["ok"]:
+                lines.append(f"heads={heads}  tp={tp}  batch={batch}  STATUS={'OOM' if rec['oom'] else 'FAILED'}")
+                break                      # a larger batch cannot fit either
+            best = batch
+            lines.append(f"heads={heads}  tp={tp}  batch={batch}  peak_mem={rec['peak_allocated_gib']}  iter_dt={rec['iter_dt']}  OK")
+        if not a.dry:
+            print(f">>> heads={heads}  tp={tp}  max_batch={best}")
+            lines.append(f"heads={heads}  tp={tp}  MAX_BATCH={best}")
+    if not a.dry and a.results_file:
+        Path(a.results_file).parent.mkdir(parents=True, exist_ok=True)
+        Path(a.results_file).write_text("\n".join(lines) + "\n")
     return 0
 
 
@@ -247,6 +258,9 @@ def main(argv=None) -> int:
     b.add_argument("--batch", type=int, nargs="+", default=[4, 8, 16, 32])
     b.add_argument("--nproc", type=int, default=4)
     b.add_argument("--dataset", default="synthetic-zipf")
+    b.add_argument("--kappa", type=float, default=0.85)
+    b.add_argument("--iterations", type=int, default=5)
+    b.add_argument("--results_file", default="logs/benchmark_batch_results.txt")
     b.add_argument("--dry", action="store_true")
     sub.add_parser("jobs")
     a, extra = p.parse_known_args(argv)

@@ -262,3 +262,34 @@ def test_restart_resubmits_with_the_running_jobs_resources_and_stops_when_done(t
     calls.clear()
     assert experiments.main(args) == 0
     assert len(calls) == 2 and calls[1][2]["RESTART_COUNT"] == "3" and "restart" in calls[1][1]
+
+
+def test_batch_benchmark_stops_a_configuration_at_its_first_oom(tmp_path, monkeypatch, capsys):
+    """The batch-size benchmark with a stand-in launcher: batch 16 runs out of memory for tp 1, so 32 is not tried; the
+    run parameters are the reference script's (scripts/benchmark_batch.sh:37-50, 108-136)."""
+    import subprocess
+
+    seen = []
+
+    def fake_run(cmd, **kw):
+        args = [str(c) for c in cmd]
+        batch = int(args[args.index("--batch_size") + 1])
+        tp = int(args[args.index("--tp_size") + 1]) if "--tp_size" in args else 1
+        seen.append((tp, batch, args))
+        if tp == 1 and batch >= 16:
+            return subprocess.CompletedProcess(cmd, 1, stdout="torch.OutOfMemoryError: CUDA out of memory", stderr="")
+        out = f"[Memory] GPU 0: peak_allocated={10.0 + batch:.2f} GiB\\nTrain: Iter=5 train_loss=9.1 iter_dt=1.25e-01s lr=1e-4"
+        return subprocess.CompletedProcess(cmd, 0, stdout=out, stderr="")
+
+    monkeypatch.setattr(experiments.subprocess, "run", fake_run)
+    res = tmp_path / "logs" / "r.txt"
+    assert experiments.main(["benchmark-batch", "--heads", "28", "--tp", "1", "4", "--batch", "4", "8", "16", "32", "--results_file", str(res)]) == 0
+    assert [(tp, b) for tp, b, _ in seen] == [(1, 4), (1, 8), (1, 16), (4, 4), (4, 8), (4, 16), (4, 32)]
+    text = res.read_text()
+    assert "heads=28  tp=1  MAX_BATCH=8" in text and "heads=28  tp=4  MAX_BATCH=32" in text and "STATUS=OOM" in text
+    args = seen[0][2]
+    for flag, val in (("--iterations", "5"), ("--warmup_steps", "3"), ("--scheduler", "cos"), ("--clipsnr", "1.0"), ("--acc_steps", "1"),
+                      ("--eval_interval", "9999"), ("--eval_batches", "4"), ("--latest_ckpt_interval", "0"), ("--distributed_backend", "fsdp")):
+        assert args[args.index(flag) + 1] == val, flag
+    out = capsys.readouterr().out
+    assert ">>> heads=28  tp=1  max_batch=8" in out
