@@ -163,6 +163,21 @@ def install_shims():
     jax.random = types.ModuleType("jax.random")          # a key is a NumPy seed here: enough for the constructors' sketch
     jax.random.PRNGKey = lambda seed: int(seed)
     jax.random.normal = lambda key, shape=(), dtype=None: _j(np.random.default_rng(key).standard_normal(shape))
+    jax.random.split = lambda key, num=2: [int(key) * 1000 + i + 1 for i in range(num)]
+
+    def categorical(key, logits, shape=()):
+        p = np.exp(np.asarray(logits, dtype=np.float64))
+        return _j(np.random.default_rng(key).choice(len(p), size=shape, p=p / p.sum()))
+
+    jax.random.categorical = categorical
+
+    def softmax(x, axis=-1):
+        z = np.asarray(x) - np.max(x, axis=axis, keepdims=True)
+        e = np.exp(z)
+        return _j(e / e.sum(axis=axis, keepdims=True))
+
+    jax.nn = types.SimpleNamespace(softmax=softmax, one_hot=lambda idx, n: _j(np.eye(n)[np.asarray(idx)]),
+                                   sigmoid=lambda x: 1.0 / (1.0 + np.exp(-x)))
     sys.modules["jax.random"] = jax.random
     sys.modules.update({"jax": jax, "jax.numpy": jnp, "chex": chex, "optax": optax, "optax.tree_utils": otu,
                         "optax._src": src, "optax._src.base": base, "optax._src.numerics": numerics, "optax._src.utils": utils})
@@ -346,6 +361,17 @@ def main():
                      "optimal_risk": float(moe.optimal_risk())}
     if two is not None:
         G["moe_plrf"]["two_expert_probs"] = plain(np.asarray(two.expert_probs, dtype=np.float64))
+    L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
+    lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
+    X, Y = lp.generate_batch(21, 64)
+    theta = np.random.default_rng(12).standard_normal((8, 5)) * 0.3
+    bias = np.random.default_rng(13).standard_normal(5) * 0.1
+    G["logistic_plrf"] = {"alpha": 1.0, "beta": 0.5, "zeta": 0.8, "snr": 2.0, "v": 30, "d": 8, "m": 5,
+                          "W": plain(np.asarray(lp.W)), "mu": plain(np.asarray(lp.mu)), "class_probs": plain(np.asarray(lp.class_probs, dtype=np.float64)),
+                          "sigma_eps_diag": plain(np.asarray(lp.Sigma_eps_diag, dtype=np.float64)),
+                          "X": plain(np.asarray(X)), "classes": np.argmax(np.asarray(Y), axis=1).tolist(),
+                          "theta": theta.tolist(), "bias": bias.tolist(),
+                          "cross_entropy": float(lp.cross_entropy_loss((_j(theta), _j(bias)), X, Y))}
     Path(a.out).write_text(json.dumps(plain(G)))
     print(f"wrote {a.out}")
 

@@ -175,3 +175,29 @@ def test_moe_problem_matches_the_reference_class():
     assert prob.limit_risk() == pytest.approx(g["optimal_risk"], rel=1e-6)
     two = T.MixtureOfExpertsPLRF.two_experts(1.0, 0.3, 40, 8, 0.7)
     np.testing.assert_allclose(two.expert_probs, g["two_expert_probs"], rtol=1e-12)
+
+
+def test_logistic_problem_matches_the_reference_class():
+    """The reference's LogisticRegressionPLRF: class frequencies, the scaling of class means and noise, and the
+    cross-entropy of given parameters on a batch the reference generated (labels as class indices here)."""
+    g = G["logistic_plrf"]
+    prob = T.LogisticPLRF(g["alpha"], g["beta"], g["zeta"], g["snr"], g["v"], g["d"], g["m"], seed=0, eval_samples=16)
+    np.testing.assert_allclose(prob.class_probs, g["class_probs"], rtol=1e-12)
+    np.testing.assert_allclose(prob.noise_std ** 2, g["sigma_eps_diag"], rtol=1e-12)
+    assert prob.W.shape == np.array(g["W"]).shape and prob.mu.shape == np.array(g["mu"]).shape
+    # the class means carry variance snr * j^(-2 beta) per coordinate in both
+    j = np.arange(1, g["v"] + 1.0)
+    assert np.mean(np.array(g["mu"]) ** 2 / (g["snr"] * j ** (-2 * g["beta"]))[:, None]) == pytest.approx(1.0, rel=0.5)
+    assert np.mean(prob.mu ** 2 / (g["snr"] * j ** (-2 * g["beta"]))[:, None]) == pytest.approx(1.0, rel=0.5)
+    params = (np.array(g["theta"]), np.array(g["bias"]))
+    X, c = np.array(g["X"]), np.array(g["classes"])
+    assert prob.cross_entropy(params, X, c) == pytest.approx(g["cross_entropy"], rel=1e-6)
+    # and the analytic gradient used in training is the gradient of that loss
+    g_theta, g_b = prob.gradient(params, X, c)
+    eps = 1e-6
+    bumped = (params[0].copy(), params[1].copy())
+    bumped[0][2, 3] += eps
+    assert (prob.cross_entropy(bumped, X, c) - prob.cross_entropy(params, X, c)) / eps == pytest.approx(g_theta[2, 3], rel=1e-4)
+    bumped = (params[0].copy(), params[1].copy())
+    bumped[1][1] += eps
+    assert (prob.cross_entropy(bumped, X, c) - prob.cross_entropy(params, X, c)) / eps == pytest.approx(g_b[1], rel=1e-4)
