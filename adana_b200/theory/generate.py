@@ -77,6 +77,8 @@ def make_rules(a, trace_k: float, steps: int) -> Dict[str, tuple]:
             rules[name] = dana_star_mk4_rule(g2, g3, a.delta, 1e-8, float(k), a.clipsnr)
         elif a.optimizer == "dana-mk4":
             rules[name] = dana_mk4_rule(g2, g3, a.delta, 1e-8, float(k), a.clipsnr)
+        elif a.optimizer == "dana-star":
+            rules[name] = dana_star_rule(g2, g3, float(k))
         elif a.optimizer == "ademamix":
             alpha_final, beta3_final = float(steps ** (1.0 - k)), 1.0 - a.delta / steps
             hl = lambda b: np.log(0.5) / np.log(b + 1e-8) - 1.0
@@ -251,7 +253,7 @@ def parser():
         s.add_argument("--sigma", type=float, default=0.1 if name == "hummingbird" else 0.0)
         s.add_argument("--random_seed", type=int, default=42)
         if name == "hummingbird":
-            s.add_argument("--optimizer", default="dana-star-mk4", choices=["dana-star-mk4", "dana-mk4", "ademamix"])
+            s.add_argument("--optimizer", default="dana-star-mk4", choices=["dana-star-mk4", "dana-mk4", "dana-star", "ademamix"])
             s.add_argument("--kappa_min", type=float, default=0.0)
             s.add_argument("--kappa_max", type=float, default=1.0)
             s.add_argument("--kappa_step", type=float, default=0.1)

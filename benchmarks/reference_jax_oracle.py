@@ -154,7 +154,22 @@ def install_shims():
 
         return GradientTransformation(init, update)
 
+    def adam(learning_rate, b1=0.9, b2=0.999, eps=1e-8):
+        def init(params):
+            return (0, np.zeros_like(params), np.zeros_like(params))
+
+        def update(g, state, params=None):
+            c, m, v = state
+            c += 1
+            m = b1 * m + (1 - b1) * g
+            v = b2 * v + (1 - b2) * g * g
+            lr = learning_rate(c - 1) if callable(learning_rate) else learning_rate
+            return -lr * (m / (1 - b1 ** c)) / (np.sqrt(v / (1 - b2 ** c)) + eps), (c, m, v)
+
+        return GradientTransformation(init, update)
+
     optax = types.ModuleType("optax")
+    optax.adam = adam
     optax.chain, optax.scale_by_learning_rate, optax.tree_utils = chain, scale_by_learning_rate, otu
     optax.GradientTransformation = GradientTransformation
     src = types.ModuleType("optax._src")
@@ -361,6 +376,18 @@ def main():
                      "optimal_risk": float(moe.optimal_risk())}
     if two is not None:
         G["moe_plrf"]["two_expert_probs"] = plain(np.asarray(two.expert_probs, dtype=np.float64))
+    # ---- how the sweep generator wires its optimizers: constants from batch / trace, kappa grid, AdEMAMix warm-ups, Adam ----
+    sys.modules["optimizers"], sys.modules["moe_plrf"] = O, M
+    H = load(jdir / "hummingbird_generate.py", "ref_jax_hummingbird_generate")
+    hb_steps, hb_grads = 30, np.random.default_rng(20).standard_normal((30, 5)) * np.array([1.0, 0.2, 2.0, 0.05, 1.0])
+    hb_p0 = np.random.default_rng(21).standard_normal(5)
+    base = dict(alpha=1.0, v=400, batch_size=20, g2_scale=0.5, g3_over_g2=0.7, tanea_lr_scalar=0.8, kappa_min=0.0, kappa_max=1.0,
+                kappa_step=0.5, clipsnr=1.5, delta=6.0, ademamix_beta1=0.9, ademamix_beta2=0.99, adam_lr=0.2, adam_beta1=0.95, adam_beta2=0.99)
+    trace_k = float(H.get_traceK(base["alpha"], base["v"]))
+    G["hummingbird_rules"] = {"args": base, "traceK": trace_k, "steps": hb_steps, "grads": hb_grads.tolist(), "p0": hb_p0.tolist(), "runs": {}}
+    for opt_name in ("dana-star-mk4", "dana-mk4", "dana-star", "ademamix"):
+        opts, kappas = H.create_optimizers(types.SimpleNamespace(optimizer=opt_name, **base), trace_k, hb_steps)
+        G["hummingbird_rules"]["runs"][opt_name] = {name: plain(trajectory(o, hb_grads, hb_p0)) for name, o in opts.items()}
     L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
     lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
     X, Y = lp.generate_batch(21, 64)

@@ -201,3 +201,29 @@ def test_logistic_problem_matches_the_reference_class():
     bumped = (params[0].copy(), params[1].copy())
     bumped[1][1] += eps
     assert (prob.cross_entropy(bumped, X, c) - prob.cross_entropy(params, X, c)) / eps == pytest.approx(g_b[1], rel=1e-4)
+
+
+@pytest.mark.parametrize("optimizer", ["dana-star-mk4", "dana-mk4", "dana-star", "ademamix"])
+def test_sweep_generator_builds_the_same_optimizers_as_the_reference_generator(optimizer):
+    """`theory.generate.make_rules` against `create_optimizers` of the reference's jax/hummingbird_generate.py: the
+    constants derived from batch size and trace, one rule per kappa of the grid under the same name, AdEMAMix's alpha
+    and beta3 warm-ups, and the Adam baseline; every rule is driven over the same gradients."""
+    from types import SimpleNamespace
+
+    from adana_b200.theory import generate
+
+    g = G["hummingbird_rules"]
+    rules = generate.make_rules(SimpleNamespace(optimizer=optimizer, **g["args"]), g["traceK"], g["steps"])
+    want = g["runs"][optimizer]
+    assert sorted(rules) == sorted(want)
+    for name, rule in rules.items():
+        init, update = rule
+        p = np.array(g["p0"])
+        state = init(p)
+        out = []
+        for grad in g["grads"]:
+            d, state = update(np.asarray(grad), state, p)
+            p = p + d
+            out.append(p.copy())
+        # (the reference forms its learning-rate constants in single precision: agreement to 1e-6, not to rounding)
+        np.testing.assert_allclose(np.array(out), want[name], rtol=2e-6, atol=1e-7, err_msg=name)
