@@ -388,6 +388,17 @@ def main():
     for opt_name in ("dana-star-mk4", "dana-mk4", "dana-star", "ademamix"):
         opts, kappas = H.create_optimizers(types.SimpleNamespace(optimizer=opt_name, **base), trace_k, hb_steps)
         G["hummingbird_rules"]["runs"][opt_name] = {name: plain(trajectory(o, hb_grads, hb_p0)) for name, o in opts.items()}
+    for name in ("matplotlib", "matplotlib.pyplot"):          # imported at module level by the sweep scripts, never called here
+        sys.modules.setdefault(name, types.ModuleType(name))
+    S = load(jdir / "moe_m_sweeps_mk4.py", "ref_jax_moe_m_sweeps_mk4")
+    ms = dict(alpha=1.0, beta=0.0, d=50, batch_size=20, g2_scale=0.2, g3_over_g2=0.01, tanea_lr_scalar=1.0, adam_lr=0.2)
+    tk = float(S.get_traceK(ms["alpha"], 400))
+    common = (ms["alpha"], ms["beta"], ms["d"], ms["batch_size"], ms["g2_scale"], ms["g3_over_g2"], tk, ms["tanea_lr_scalar"], 0.0)
+    G["m_sweep_rules"] = {"args": ms, "v": 400, "traceK": tk, "grads": hb_grads.tolist(), "p0": hb_p0.tolist(), "runs": {
+        "dana-star": plain(trajectory(S.get_dana_star_optimizer(*common), hb_grads, hb_p0)),
+        "dana-star-mk4": plain(trajectory(S.get_dana_star_mk4_optimizer(*common), hb_grads, hb_p0)),
+        "dana-star_kappa0.7": plain(trajectory(S.get_dana_star_optimizer(*common, tanea_kappa=0.7), hb_grads, hb_p0))},
+        "adam_lr": float(S.get_adam_lr(*common, ms["adam_lr"]))}
     L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
     lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
     X, Y = lp.generate_batch(21, 64)

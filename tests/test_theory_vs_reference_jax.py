@@ -227,3 +227,32 @@ def test_sweep_generator_builds_the_same_optimizers_as_the_reference_generator(o
             out.append(p.copy())
         # (the reference forms its learning-rate constants in single precision: agreement to 1e-6, not to rounding)
         np.testing.assert_allclose(np.array(out), want[name], rtol=2e-6, atol=1e-7, err_msg=name)
+
+
+def test_m_sweep_builds_the_same_optimizers_as_the_reference_sweep_script():
+    """`theory.generate._star_rules` against `get_dana_star_optimizer`, `get_dana_star_mk4_optimizer` and `get_adam_lr` of
+    the reference's jax/moe_m_sweeps_mk4.py: the first Dana-Star at kappa = (1 - log_d batch) / (2 alpha) (or a given
+    kappa), Dana-Star-MK4 at kappa 1 with the default clip, Adam's step size."""
+    from types import SimpleNamespace
+
+    from adana_b200.theory import generate
+
+    g = G["m_sweep_rules"]
+
+    def run(rule):
+        init, update = rule
+        p = np.array(g["p0"])
+        state, out = init(p), []
+        for grad in g["grads"]:
+            d, state = update(np.asarray(grad), state, p)
+            p = p + d
+            out.append(p.copy())
+        return np.array(out)
+
+    a = SimpleNamespace(kappa=None, clipsnr=2.0, delta=8.0, disable_adam=False, adam_beta1=0.99, adam_beta2=0.999, **g["args"])
+    rules = generate._star_rules(a, g["traceK"])
+    for name in ("dana-star", "dana-star-mk4"):
+        np.testing.assert_allclose(run(rules[name]), g["runs"][name], rtol=2e-6, atol=1e-7, err_msg=name)
+    a.kappa = 0.7
+    np.testing.assert_allclose(run(generate._star_rules(a, g["traceK"])["dana-star"]), g["runs"]["dana-star_kappa0.7"], rtol=2e-6, atol=1e-7)
+    assert g["args"]["adam_lr"] * min(1.0, g["args"]["batch_size"] / g["traceK"]) == pytest.approx(g["adam_lr"], rel=1e-6)
