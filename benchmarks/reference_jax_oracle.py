@@ -399,6 +399,14 @@ def main():
         "dana-star-mk4": plain(trajectory(S.get_dana_star_mk4_optimizer(*common), hb_grads, hb_p0)),
         "dana-star_kappa0.7": plain(trajectory(S.get_dana_star_optimizer(*common, tanea_kappa=0.7), hb_grads, hb_p0))},
         "adam_lr": float(S.get_adam_lr(*common, ms["adam_lr"]))}
+    sys.modules["power_law_rf"], sys.modules["deterministic_equivalent"] = P, D
+    B = load(jdir / "plrf_ademamix_behavior.py", "ref_jax_plrf_ademamix_behavior")
+    cfg = dict(B.CONFIG, alpha=1.2, beta=0.3, v=200, d=40, steps=3000, batch_size=2, lr_scale=0.5, g2=0.5, g3=0.5, delta=8.0, random_seed=3)
+    res, r_inf_b = B.run_ode(cfg)
+    keep = slice(None, None, 50)
+    G["optimizer_comparison"] = {"cfg": {k: v for k, v in cfg.items() if isinstance(v, (int, float, str))}, "risk_infinity": float(r_inf_b),
+                                 "runs": {k: {"t": plain(np.asarray(v["t"], dtype=np.float64)[keep]), "loss": plain(np.asarray(v["loss"], dtype=np.float64)[keep])}
+                                          for k, v in res.items()}}
     L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
     lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
     X, Y = lp.generate_batch(21, 64)

@@ -256,3 +256,20 @@ def test_m_sweep_builds_the_same_optimizers_as_the_reference_sweep_script():
     a.kappa = 0.7
     np.testing.assert_allclose(run(generate._star_rules(a, g["traceK"])["dana-star"]), g["runs"]["dana-star_kappa0.7"], rtol=2e-6, atol=1e-7)
     assert g["args"]["adam_lr"] * min(1.0, g["args"]["batch_size"] / g["traceK"]) == pytest.approx(g["adam_lr"], rel=1e-6)
+
+
+def test_optimizer_comparison_equals_the_reference_script():
+    """`schedule_studies.compare_optimizers` against `run_ode` of the reference's jax/plrf_ademamix_behavior.py: SGD,
+    Dana with constant and with decaying g3, and AdEMAMix expressed as Dana schedules (g1 = 1/(1+t), alpha and beta3
+    warm-ups), all on the deterministic spectrum."""
+    from adana_b200.theory import schedule_studies as S
+
+    g = G["optimizer_comparison"]
+    c = g["cfg"]
+    mine = S.compare_optimizers(c["alpha"], c["beta"], c["d"], c["v"], c["batch_size"], float(c["steps"]), c["lr_scale"], c["g2"],
+                                c["g3"], c["delta"], dt=1e-3)
+    assert mine["risk_infinity"] == pytest.approx(g["risk_infinity"], rel=2e-3)
+    for name, want in g["runs"].items():
+        t, loss = mine["runs"][name]["t"][::50], mine["runs"][name]["loss"][::50]
+        np.testing.assert_allclose(t, want["t"], rtol=1e-5)
+        np.testing.assert_allclose(loss, want["loss"], rtol=3e-3, err_msg=name)       # the floor differs by its own tolerance
