@@ -168,8 +168,40 @@ def install_shims():
 
         return GradientTransformation(init, update)
 
+    def adagrad(learning_rate, initial_accumulator_value=0.1, eps=1e-7):
+        def init(params):
+            return tree_map(lambda p: np.full_like(np.asarray(p, dtype=np.float64), initial_accumulator_value), params)
+
+        def update(g, acc, params=None):
+            acc = tree_map(lambda a, x: a + np.asarray(x) ** 2, acc, g)
+            return tree_map(lambda x, a: -learning_rate * np.asarray(x) / (np.sqrt(a) + eps), g, acc), acc
+
+        return GradientTransformation(init, update)
+
+    def apply_updates(params, updates):
+        return tree_map(lambda p, u: _j(np.asarray(p) + np.asarray(u)), params, updates)
+
+    def grad(fn, argnums=0):
+        """Central differences in place of automatic differentiation (the fits have three to five parameters)."""
+        def g(*args):
+            x = np.array(args[argnums], dtype=np.float64)
+            out = np.zeros_like(x)
+            flat, of = x.reshape(-1), out.reshape(-1)
+            for i in range(flat.size):
+                h = 1e-6 * max(1.0, abs(flat[i]))
+                hi, lo = flat.copy(), flat.copy()
+                hi[i] += h
+                lo[i] -= h
+                a_hi = list(args); a_hi[argnums] = _j(hi.reshape(x.shape)) if x.ndim else float(hi[0])
+                a_lo = list(args); a_lo[argnums] = _j(lo.reshape(x.shape)) if x.ndim else float(lo[0])
+                of[i] = (float(fn(*a_hi)) - float(fn(*a_lo))) / (2 * h)
+            return _j(out) if x.ndim else float(out)
+
+        return g
+
+    jax.grad = grad
     optax = types.ModuleType("optax")
-    optax.adam = adam
+    optax.adam, optax.adagrad, optax.apply_updates = adam, adagrad, apply_updates
     optax.chain, optax.scale_by_learning_rate, optax.tree_utils = chain, scale_by_learning_rate, otu
     optax.GradientTransformation = GradientTransformation
     src = types.ModuleType("optax._src")
@@ -407,6 +439,16 @@ def main():
     G["optimizer_comparison"] = {"cfg": {k: v for k, v in cfg.items() if isinstance(v, (int, float, str))}, "risk_infinity": float(r_inf_b),
                                  "runs": {k: {"t": plain(np.asarray(v["t"], dtype=np.float64)[keep]), "loss": plain(np.asarray(v["loss"], dtype=np.float64)[keep])}
                                           for k, v in res.items()}}
+    # ---- the weighted learning-rate law as the reference fits it (Adagrad on the same objective; gradients by differences) ----
+    viz = Path(a.ref_root) / "visualization"
+    fit = cut_functions(viz / "bighead_lr_scaling.py", ["fit_saturated_power_law_weighted"],
+                        {"jit": sys.modules["jax"].jit, "grad": sys.modules["jax"].grad, "optax": sys.modules["optax"],
+                         "print": lambda *x, **k: None})
+    Ps = np.repeat(np.array([2e6, 1e7, 5e7, 2e8, 1e9]), 3)
+    ws = np.tile([3.0, 2.0, 1.0], 5)
+    lrs_fit = 12.0 * (4e4 + Ps) ** -0.52 * np.exp(np.random.default_rng(30).normal(0, 0.05, len(Ps)))
+    a_f, b_f, d_f = fit["fit_saturated_power_law_weighted"](list(Ps), list(lrs_fit), list(ws), n_steps=5000, learning_rate=0.1)
+    G["lr_law_fit"] = {"P": Ps.tolist(), "lr": lrs_fit.tolist(), "w": ws.tolist(), "a": float(a_f), "b": float(b_f), "d": float(d_f)}
     L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
     lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
     X, Y = lp.generate_batch(21, 64)

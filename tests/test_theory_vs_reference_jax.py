@@ -273,3 +273,23 @@ def test_optimizer_comparison_equals_the_reference_script():
         t, loss = mine["runs"][name]["t"][::50], mine["runs"][name]["loss"][::50]
         np.testing.assert_allclose(t, want["t"], rtol=1e-5)
         np.testing.assert_allclose(loss, want["loss"], rtol=3e-3, err_msg=name)       # the floor differs by its own tolerance
+
+
+def test_exact_lr_law_fit_is_at_least_as_good_as_the_reference_adagrad_fit():
+    """The reference fits lr = a (b + P)^d with 6000 Adagrad steps from a fixed start (run here with its own code, the
+    gradients taken by differences); `studies.lr_law.fit_weighted` solves the same weighted objective exactly.  The exact
+    fit must not be worse on that objective, and inside the range of the data both must predict the same learning rates."""
+    from adana_b200.studies import lr_law
+
+    g = G["lr_law_fit"]
+    P, lr, w = np.array(g["P"]), np.array(g["lr"]), np.array(g["w"])
+
+    def objective(a, b, d):
+        cw = w * w * P
+        return float(np.sum(cw * (np.log(lr) - np.log(a * (b + P) ** d)) ** 2) / np.sum(cw))
+
+    a, b, d, err = lr_law.fit_weighted(P, lr, w)
+    assert err == pytest.approx(objective(a, b, d), rel=1e-9)
+    assert err <= objective(g["a"], g["b"], g["d"]) * (1 + 1e-9)
+    grid = np.geomspace(P.min(), P.max(), 20)
+    np.testing.assert_allclose(lr_law.predict(grid, a, b, d), g["a"] * (g["b"] + grid) ** g["d"], rtol=0.08)
