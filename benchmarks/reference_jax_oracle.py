@@ -449,6 +449,18 @@ def main():
     lrs_fit = 12.0 * (4e4 + Ps) ** -0.52 * np.exp(np.random.default_rng(30).normal(0, 0.05, len(Ps)))
     a_f, b_f, d_f = fit["fit_saturated_power_law_weighted"](list(Ps), list(lrs_fit), list(ws), n_steps=5000, learning_rate=0.1)
     G["lr_law_fit"] = {"P": Ps.tolist(), "lr": lrs_fit.tolist(), "w": ws.tolist(), "a": float(a_f), "b": float(b_f), "d": float(d_f)}
+    # ---- the joint broken-power-law fit with a shared floor, as the scaling comparison runs it -------------------------------
+    jf = cut_functions(viz / "compare_scaling_rules_ep.py", ["broken_power_law", "fit_all_saturated_power_laws_joint"],
+                       {"jit": sys.modules["jax"].jit, "grad": sys.modules["jax"].grad, "optax": sys.modules["optax"], "np": np,
+                        "args": types.SimpleNamespace(compute_weight=False), "print": lambda *x, **k: None})
+    Cs = np.geomspace(0.05, 60, 8)
+    law = lambda C, a, b, c, e, f: a + b * C ** -c + e * C ** -f
+    data_list = [{"name": "adamw", "compute": Cs, "loss": law(Cs, 1.7, 0.5, 0.30, 1.0, 0.06)},
+                 {"name": "dana-star-mk4", "compute": Cs, "loss": law(Cs * 1.5, 1.7, 0.5, 0.30, 1.0, 0.06)}]
+    ref_fit = jf["fit_all_saturated_power_laws_joint"]([{**d, "compute": _j(d["compute"]), "loss": _j(d["loss"])} for d in data_list],
+                                                       n_steps=20000, learning_rate=0.1)
+    G["joint_fit"] = {"curves": [{"name": d["name"], "compute": d["compute"].tolist(), "loss": d["loss"].tolist()} for d in data_list],
+                      "reference": plain(ref_fit)}
     L = load(jdir / "lr_plrf.py", "ref_jax_lr_plrf")
     lp = L.LogisticRegressionPLRF(1.0, 0.5, 0.8, 2.0, 30, 8, 5, 11)
     X, Y = lp.generate_batch(21, 64)

@@ -293,3 +293,25 @@ def test_exact_lr_law_fit_is_at_least_as_good_as_the_reference_adagrad_fit():
     assert err <= objective(g["a"], g["b"], g["d"]) * (1 + 1e-9)
     grid = np.geomspace(P.min(), P.max(), 20)
     np.testing.assert_allclose(lr_law.predict(grid, a, b, d), g["a"] * (g["b"] + grid) ** g["d"], rtol=0.08)
+
+
+def test_joint_loss_law_fit_is_at_least_as_good_as_the_reference_adagrad_fit():
+    """Two optimizers, one shared floor: the reference's `fit_all_saturated_power_laws_joint` (20 000 Adagrad steps, its
+    own code on the stand-ins, gradients by differences) against `studies.loss_laws.fit_joint` on the same objective,
+    the mean squared difference of log loss over all points."""
+    from adana_b200.studies import loss_laws
+
+    g = G["joint_fit"]
+
+    def objective(fit):
+        r = []
+        for c in g["curves"]:
+            q = fit["curves"][c["name"]]
+            pred = loss_laws.broken(np.array(c["compute"]), fit["a"], q["b"], q["c"], q["e"], q["f"])
+            r.append(np.log(pred) - np.log(np.array(c["loss"])))
+        return float(np.mean(np.concatenate(r) ** 2))
+
+    mine = loss_laws.fit_joint(g["curves"], "broken")
+    assert objective(mine) <= objective(g["reference"]) * (1 + 1e-9)
+    assert min(q["r_squared"] for q in mine["curves"].values()) >= min(q["r_squared"] for q in g["reference"]["curves"].values()) - 1e-6
+    assert 0 < mine["a"] < 0.99 * min(min(c["loss"]) for c in g["curves"])
