@@ -78,7 +78,27 @@ class DistributedBackend:
                 u.grads.mul_(self.engine._clip[0])
             self.engine._clip[0] = 1.0
             return norm
+        parameters = list(parameters)
+        if any(getattr(p, "_adana_rank_local", False) for p in parameters) and dist.is_available() and dist.is_initialized():
+            return self._clip_with_rank_local(parameters, max_norm)
         return torch.nn.utils.clip_grad_norm_(parameters, max_norm)
+
+    @staticmethod
+    def _clip_with_rank_local(parameters, max_norm):
+        """Global norm when some parameters exist on one rank only (expert parallelism): the replicated gradients are
+        identical everywhere and count once, the rank-local ones are summed over the ranks, so every rank derives the
+        same norm and scales by the same coefficient."""
+        shared = [p.grad.detach() for p in parameters if p.grad is not None and not getattr(p, "_adana_rank_local", False)]
+        local = [p.grad.detach() for p in parameters if p.grad is not None and getattr(p, "_adana_rank_local", False)]
+        dev = (shared or local)[0].device
+        sq_local = torch.stack([g.float().pow(2).sum() for g in local]).sum() if local else torch.zeros((), device=dev)
+        dist.all_reduce(sq_local)
+        sq_shared = torch.stack([g.float().pow(2).sum() for g in shared]).sum() if shared else torch.zeros((), device=dev)
+        total = (sq_shared + sq_local).sqrt()
+        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+        for g in shared + local:
+            g.mul_(coef.to(g.dtype))
+        return total
 
     engine_optimizer = False
 
@@ -174,7 +194,12 @@ class DDPBackend(_ProcessGroupBackend):
             return model
         from torch.nn.parallel import DistributedDataParallel as DDP
 
+        from ..parallel.expert_parallel import rank_local_parameters
+
         self._wrapped = True
+        local = rank_local_parameters(model)
+        if local:     # expert-parallel layers: each rank's experts are its own, not replicas to keep in step
+            DDP._set_params_and_buffers_to_ignore_for_model(model, local)
         if self.pg_backend == "nccl":
             return DDP(model, device_ids=[self.local_rank])
         return DDP(model)

@@ -26,6 +26,25 @@ import torch.nn as nn
 from ..models.moe import _route
 
 
+_EP_GROUPS = {}
+
+
+def default_ep_group():
+    """A process group of all ranks that only the expert exchange uses.  The exchange runs inside forward AND backward;
+    on the default group its collectives would interleave with the gradient all-reduces that DistributedDataParallel
+    issues from its own hooks during the same backward, and the two orders differ between ranks (a collective
+    mismatch).  Created once, by every rank, the first time a layer is built."""
+    if "world" not in _EP_GROUPS:
+        _EP_GROUPS["world"] = dist.new_group(ranks=list(range(dist.get_world_size())))
+    return _EP_GROUPS["world"]
+
+
+def rank_local_parameters(model):
+    """Names of the parameters that differ between ranks on purpose (each rank's own experts): data parallelism must
+    neither broadcast nor all-reduce them."""
+    return [n for n, p in model.named_parameters() if getattr(p, "_adana_rank_local", False)]
+
+
 def _all_to_all(x, out_splits, in_splits, group):
     out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
     if dist.get_backend(group) == "gloo":
@@ -81,6 +100,8 @@ class _P2PExchange(torch.autograd.Function):
 class ExpertParallelMoE(nn.Module):
     def __init__(self, config, mlp, group=None):
         super().__init__()
+        if group is None and dist.is_initialized() and dist.get_world_size() > 1:
+            group = default_ep_group()
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -96,6 +117,14 @@ class ExpertParallelMoE(nn.Module):
         self.capacity_factor = float(getattr(config, "moe_expert_capacity_factor", 0.0) or 0.0)
         self._a2a = {}            # (dtype, width) -> P2PAllToAll, or None once the ranks settled on NCCL
         self._p2p_ok = None
+        if self.world > 1:
+            # This rank's experts exist nowhere else.  Through the exchange their gradients already sum the
+            # contributions of every rank's loss; data parallelism averages the replicated parameters' gradients over the
+            # ranks, so these are divided by the number of ranks to stay on the same scale.
+            w = float(self.world)
+            for p in self.experts.parameters():
+                p._adana_rank_local = True
+                p.register_hook(lambda g, w=w: g / w)
 
     def _p2p_exchange(self, x, rows_per_call: int):
         """The peer-memory exchange for rows like `x`, created on first use; None where NCCL is to be used.  Every

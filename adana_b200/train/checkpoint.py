@@ -205,6 +205,9 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
         return
     if _rank() != 0:
         return
+    if any(getattr(p, "_adana_rank_local", False) for p in model.parameters()):
+        print("[Checkpoint] WARNING: expert-parallel layers keep each rank's experts on that rank only; main.pt holds "
+              "rank 0's.  Train with --no_expert_parallel when the run has to be resumed from its checkpoints.")
     ckpt = {"model": model_state_dict(model), "optimizer": opt.state_dict(), "scheduler": sched_sd, "itr": itr}
     if async_write:
         ckpt = {k: (_to_cpu(v)) for k, v in ckpt.items()}

@@ -102,6 +102,8 @@ class Trainer:
         self.tau_stats = None
         self.dlogger = None
         self.watchdog = None
+        # expert-parallel layers exchange tokens between the ranks inside every forward: no rank can evaluate alone
+        self.collective_forward = any(getattr(p, "_adana_rank_local", False) for p in self.model.parameters())
         # Host-side fault injection for the recovery tests: ADANA_FAULT_EXIT="<rank>:<iteration>[:<exit code>]" makes
         # that rank leave the job at the top of that iteration, between steps, with nothing of its own in flight.
         self._exit_at = None
@@ -208,7 +210,7 @@ class Trainer:
     # ---- evaluation ---------------------------------------------------------------------------------------
     def eval_and_log(self, tokens, epoch, full_eval=False):
         cfg, it = self.cfg, self.curr_iter
-        if not self.all_ranks_ckpt and not self.master:
+        if not (self.all_ranks_ckpt or self.collective_forward) and not self.master:
             return
         self.model.eval()
         if cfg.opt in ("sf-sgd", "sf-adamw"):

@@ -413,3 +413,53 @@ def test_sharded_muon_matches_single_rank_and_per_tensor_muon():
         # the engine's gradients differ from autograd's in the last fp32 bits; bf16 Newton-Schulz amplifies that
         # along near-null singular directions, so the comparison is relative to how far the step moved
         assert d <= 0.1 * moved + 1e-7, (k, d, moved)
+
+
+def _ep_ddp_worker(rank, world):
+    """Expert-parallel layer inside DistributedDataParallel against the dense layer on the union of the ranks' data."""
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    from conftest import tiny_args
+    from adana_b200.distributed.backends import DistributedBackend
+    from adana_b200.models.moe import MoE
+    from adana_b200.models.qwen3 import Qwen3MLP
+    from adana_b200.parallel.expert_parallel import ExpertParallelMoE, rank_local_parameters
+
+    dist.init_process_group("gloo")
+    a = tiny_args("qwen3", moe=True, moe_num_experts=4, moe_num_shared_experts=0, moe_num_experts_per_tok=2,
+                  moe_expert_capacity_factor=0.0)
+    torch.manual_seed(0)
+    dense = MoE(a, Qwen3MLP)
+    torch.manual_seed(1 + rank)                    # different initial experts per rank: they are not replicas
+    ep = ExpertParallelMoE(a, Qwen3MLP)
+    with torch.no_grad():
+        ep.router.weight.copy_(dense.router.weight)
+        for e in range(ep.per_rank):
+            ep.experts[e].load_state_dict(dense.experts[rank * ep.per_rank + e].state_dict())
+    local = rank_local_parameters(ep)
+    assert local and all(n.startswith("experts.") for n in local)
+    DDP._set_params_and_buffers_to_ignore_for_model(ep, local)
+    ddp = DDP(ep)
+    xs = [torch.randn(2, 8, a.n_embd, generator=torch.Generator().manual_seed(100 + r)) for r in range(world)]
+    y, _ = ddp(xs[rank])
+    y.pow(2).sum().backward()
+    sum(dense(x)[0].pow(2).sum() for x in xs).div(world).backward()      # the loss data parallelism optimises
+    worst = 0.0
+    for e in range(ep.per_rank):
+        for (n, p), (_, q) in zip(ep.experts[e].named_parameters(), dense.experts[rank * ep.per_rank + e].named_parameters()):
+            worst = max(worst, (p.grad - q.grad).abs().max().item() / (q.grad.abs().max().item() + 1e-12))
+    router = (ep.router.weight.grad - dense.router.weight.grad).abs().max().item() / dense.router.weight.grad.abs().max().item()
+    dense_norm = torch.sqrt(sum(p.grad.pow(2).sum() for p in dense.parameters())).item()
+    total = DistributedBackend._clip_with_rank_local(list(ep.parameters()), max_norm=0.5 * dense_norm).item()
+    clipped = torch.sqrt(sum(p.grad.pow(2).sum() for p in ep.router.parameters())).item()
+    return {"expert_err": worst, "router_err": router, "norm": total, "dense_norm": dense_norm,
+            "router_scale": clipped / dense.router.weight.grad.norm().item()}
+
+
+def test_expert_parallel_under_data_parallel_has_the_gradients_of_the_dense_layer():
+    res = _spawn(_ep_ddp_worker, 2)
+    for r in (0, 1):
+        assert res[r]["expert_err"] < 1e-5 and res[r]["router_err"] < 1e-5, res[r]
+        assert res[r]["norm"] == pytest.approx(res[r]["dense_norm"], rel=1e-5)          # the same global norm on every rank
+        assert res[r]["router_scale"] == pytest.approx(0.5, rel=1e-4)
+    assert res[0]["norm"] == pytest.approx(res[1]["norm"], rel=1e-6)

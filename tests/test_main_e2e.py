@@ -200,3 +200,25 @@ def test_rank_that_leaves_ends_the_job_and_the_relaunch_resumes_from_the_last_ch
     rows = [json.loads(l) for l in (exp / "metrics.jsonl").read_text().splitlines()]
     iters = [r["iter"] for r in rows if "train/loss" in r]
     assert iters[-1] == 10 and 5 in iters and all(r["train/loss"] == r["train/loss"] for r in rows if "train/loss" in r)
+
+
+@pytest.mark.timeout(600)
+def test_two_rank_moe_run_with_expert_parallel_layers(tmp_path):
+    """Qwen3-Next with routed experts split over two data-parallel CPU ranks: training, the evaluations (every rank
+    takes part: the expert exchange is collective) and the final summary go through."""
+    import os
+
+    cmd = [*torchrun(2), "-m", "adana_b200.main", "--model", "qwen3next", "--moe", "--moe_num_experts", "4",
+           "--moe_num_experts_per_tok", "2", "--n_layer", "2", "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32",
+           "--mlp_hidden_dim", "128", "--sequence_length", "128", "--batch_size", "16", "--acc_steps", "2", "--vocab_size", "512",
+           "--dataset", "synthetic-zipf", "--datasets_dir", str(tmp_path / "data"), "--opt", "adamw", "--lr", "1e-3",
+           "--iterations", "6", "--warmup_steps", "2", "--eval_interval", "3", "--eval_batches", "2", "--log_interval", "1",
+           "--latest_ckpt_interval", "0", "--grad_clip", "0.5", "--results_base_folder", str(tmp_path / "exps"),
+           "--device", "cpu", "--dtype", "float32", "--distributed_backend", "gloo", "--seed", "2"]
+    p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=500, env={**os.environ, "OMP_NUM_THREADS": "1"})
+    out = p.stdout + p.stderr
+    assert p.returncode == 0, out[-3000:]
+    assert ">Eval: Iter=3" in out and ">Eval: Iter=6" in out and "Train: Iter=6" in out
+    rows = [json.loads(l) for l in (_exp_dir(tmp_path / "exps") / "metrics.jsonl").read_text().splitlines()]
+    losses = [r["train/loss"] for r in rows if "train/loss" in r]
+    assert len(losses) == 6 and all(l == l for l in losses)
