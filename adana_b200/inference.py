@@ -101,6 +101,10 @@ def load_model(path, device="cpu"):
         blob = torch.load(ckpt, map_location="cpu", weights_only=False)
     state = strip_prefixes(blob["model"] if "model" in blob else blob)
     missing, unexpected = model.load_state_dict(state, strict=False)
+    # a tied output head is the embedding tensor itself: a checkpoint that stores the tensor once is complete
+    params = dict(model.named_parameters(remove_duplicate=False))
+    stored = {id(params[k]) for k in state if k in params}
+    missing = [k for k in missing if k not in params or id(params[k]) not in stored]
     if missing:
         print(f"warning: {len(missing)} parameters missing from the checkpoint (e.g. {missing[0]})", file=sys.stderr)
     if unexpected:
