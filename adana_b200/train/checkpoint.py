@@ -203,6 +203,20 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
         if eng.rank == 0:
             _atomic_save({"scheduler": sched_sd, "itr": itr}, local / "meta.pt")
         return
+    if _is_torch_fsdp(model):
+        # models without a kernel path run under torch's FSDP2: their parameters are DTensor shards, saved the way the
+        # reference saves them (src/optim/utils.py:275-298) -- a collective torch.distributed.checkpoint write of the
+        # state dictionaries, then meta.pt on rank 0
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint.state_dict import get_model_state_dict, get_optimizer_state_dict
+
+        if _rank() == 0 and (local / "meta.pt").exists():
+            (local / "meta.pt").unlink()
+        dcp.save({"model": get_model_state_dict(model), "optimizer": get_optimizer_state_dict(model, opt)},
+                 checkpoint_id=str(local / "sharded"))
+        if _rank() == 0:
+            _atomic_save({"scheduler": sched_sd, "itr": itr}, local / "meta.pt")
+        return
     if _rank() != 0:
         return
     if any(getattr(p, "_adana_rank_local", False) for p in model.parameters()):
@@ -214,6 +228,15 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
         _async_writer.submit(ckpt, local / "main.pt")
     else:
         _atomic_save(ckpt, local / "main.pt")
+
+
+def _is_torch_fsdp(model) -> bool:
+    """True for a module that torch's `fully_shard` wrapped (its parameters are DTensors)."""
+    try:
+        from torch.distributed.tensor import DTensor
+    except ImportError:
+        return False
+    return any(isinstance(p, DTensor) for p in model.parameters())
 
 
 def _to_cpu(obj):
@@ -343,6 +366,22 @@ def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_
         return meta["itr"]
     if (ckpt_dir / "sharded" / "layout.json").exists() and eng is not None:
         _load_sharded(eng, opt, ckpt_dir / "sharded")      # the flat-shard files earlier versions wrote
+        meta = _load(ckpt_dir / "meta.pt")
+        if scheduler is not None and meta.get("scheduler") is not None:
+            scheduler.load_state_dict(meta["scheduler"])
+        return meta["itr"]
+    if _is_torch_fsdp(model) and (ckpt_dir / "sharded" / ".metadata").exists():
+        # the reference's loader (src/optim/utils.py:328-337): read into the sharded state dictionaries, hand them back
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint.state_dict import (get_model_state_dict, get_optimizer_state_dict,
+                                                             set_model_state_dict, set_optimizer_state_dict)
+
+        if not (ckpt_dir / "meta.pt").exists():
+            raise RuntimeError(f"sharded checkpoint {ckpt_dir} is incomplete: meta.pt (written last) is missing")
+        state = {"model": get_model_state_dict(model), "optimizer": get_optimizer_state_dict(model, opt)}
+        dcp.load(state, checkpoint_id=str(ckpt_dir / "sharded"))
+        set_model_state_dict(model, state["model"])
+        set_optimizer_state_dict(model, opt, state["optimizer"])
         meta = _load(ckpt_dir / "meta.pt")
         if scheduler is not None and meta.get("scheduler") is not None:
             scheduler.load_state_dict(meta["scheduler"])

@@ -222,3 +222,37 @@ def test_two_rank_moe_run_with_expert_parallel_layers(tmp_path):
     rows = [json.loads(l) for l in (_exp_dir(tmp_path / "exps") / "metrics.jsonl").read_text().splitlines()]
     losses = [r["train/loss"] for r in rows if "train/loss" in r]
     assert len(losses) == 6 and all(l == l for l in losses)
+
+
+@pytest.mark.timeout(900)
+def test_two_rank_library_fsdp_model_saves_a_dcp_checkpoint_and_resumes(tmp_path):
+    """A model the kernel engine does not take (Qwen3 with tied embeddings) runs under torch's FSDP2: its checkpoint is
+    a torch.distributed.checkpoint directory plus meta.pt, as the reference writes under FSDP (src/optim/utils.py:
+    275-298), not rank 0's DTensor shards in a main.pt; the relaunch resumes from it and inference reads it."""
+    import os
+
+    def launch(extra):
+        cmd = [*torchrun(2), "-m", "adana_b200.main", "--model", "qwen3", "--weight_tying", "True", "--n_layer", "2",
+               "--n_head", "2", "--n_embd", "64", "--qkv_dim", "32", "--mlp_hidden_dim", "128", "--sequence_length", "128",
+               "--batch_size", "8", "--acc_steps", "2", "--vocab_size", "512", "--dataset", "synthetic-zipf",
+               "--datasets_dir", str(tmp_path / "data"), "--opt", "adamw", "--lr", "1e-3", "--warmup_steps", "2",
+               "--eval_interval", "100", "--eval_batches", "2", "--log_interval", "1", "--latest_ckpt_interval", "3",
+               "--results_base_folder", str(tmp_path / "exps"), "--device", "cpu", "--dtype", "float32",
+               "--distributed_backend", "fsdp", "--seed", "3", "--iterations", "6", *extra]
+        p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600,
+                           env={**os.environ, "ADANA_FSDP_CPU": "1", "OMP_NUM_THREADS": "1"})
+        assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+        return p.stdout + p.stderr
+
+    launch(["--iterations_to_run", "3"])
+    latest = _exp_dir(tmp_path / "exps") / "ckpts" / "latest"
+    assert (latest / "sharded" / ".metadata").exists() and len(list((latest / "sharded").glob("*.distcp"))) == 2
+    assert not (latest / "main.pt").exists()
+    assert torch.load(latest / "meta.pt", map_location="cpu", weights_only=False)["itr"] == 3
+    out = launch(["--auto_resume"])
+    assert "Train: Iter=4" in out and "Train: Iter=6" in out and "Train: Iter=1 " not in out
+    from adana_b200 import inference
+
+    model = inference.load_model(_exp_dir(tmp_path / "exps"))
+    assert all(torch.isfinite(p).all() for p in model.parameters())
+    assert model.lm_head.weight is model.transformer.wte.weight
