@@ -134,6 +134,9 @@ class _LogTimeBase(Optimizer):
                     wd_mult=wd_multiplier(wd, sched, t, self.wd_decaying, self.wd_ts),
                     diagnostics=self.diagnostics)
                 if diag is not None:
+                    # on sharded (DTensor) parameters a norm or mean comes back as a pending cross-rank reduction;
+                    # the logged scalars are stored reduced, as plain tensors, so that the state can be checkpointed
+                    diag = {k: (v.full_tensor() if hasattr(v, "full_tensor") else v) for k, v in diag.items()}
                     state["current_alpha"] = diag["current_alpha"]
                     state["gradient_norm"] = diag["gradient_norm"]
                     state["auto_factor_mean"] = diag["auto_factor_mean"]

@@ -261,10 +261,11 @@ class Manau(Optimizer):
                                  * norm ** (2 * (-group["mk4A"] - group["mk4B"])), max=group["clipsnr"])
                 long_term = lr * (reg * torch.sign(m) * af + m * norm)
                 st["current_alpha"] = alpha
-                st["current_alpha_factor"] = af.mean()
-                st["gradient_norm"] = g.norm()
-                st["auto_factor_mean"] = mfac.mean()
-                st["m_norm"] = m.norm()
+                st["current_alpha_factor"] = af.mean().full_tensor() if hasattr(af, "full_tensor") else af.mean()
+                full = lambda v: v.full_tensor() if hasattr(v, "full_tensor") else v      # (reduced, so the state can be saved)
+                st["gradient_norm"] = full(g.norm())
+                st["auto_factor_mean"] = full(mfac.mean())
+                st["m_norm"] = full(m.norm())
                 if wd != 0:
                     p.mul_(1 - wd / (1 + t / group["wd_ts"]) * lr if group["wd_decaying"] else 1 - wd * lr)
                 p.add_(-(lr * g * norm + long_term))

@@ -46,6 +46,13 @@ def build_optimizer(args, model, group_specs, engine=None):
         return cls(engine, make_inner, group_specs)
     if engine is not None:
         engine.average_on_sync = True      # a per-tensor class on the engine's gradient views wants rank-averaged gradients
+    if engine is None and args.opt in ("muon", "soap", "adafactor") and \
+            any(hasattr(p, "to_local") for g in group_specs for p in g["params"]):
+        # a model without a kernel path under --distributed_backend fsdp: torch FSDP2 hands out DTensor shards.  These
+        # three mix them with plain tensors (soap, adafactor) or partition the work by whole parameters per rank and
+        # wait for each other (muon, the data-parallel form: src/optim/muon.py:443-602 needs `model.module`)
+        raise ValueError(f"--opt {args.opt} does not run on parameters sharded by torch FSDP2 (this model has no kernel "
+                         f"path); use --opt d-muon, --distributed_backend nccl, or a model configuration the engine takes")
     return _build_per_tensor(args, model, group_specs)
 
 

@@ -226,6 +226,7 @@ class Prodigy(Optimizer):
         num = g0["d_numerator"] * b3
         num_acc = torch.zeros((), device=self.param_groups[0]["params"][0].device)
         den_acc = torch.zeros_like(num_acc)
+        sharded = False
         for g in self.param_groups:
             for p in g["params"]:
                 if p.grad is None:
@@ -240,13 +241,16 @@ class Prodigy(Optimizer):
                 if g["weight_decay"] != 0 and not g["decouple"]:
                     grad = grad.add(p, alpha=g["weight_decay"])
                 if lr > 0:
-                    num_acc += (d / d0) * dlr * torch.dot(grad.flatten(), (st["p0"] - p).flatten())
+                    # (sharded parameters: each rank adds what its shard contributes; the sums meet in the all-reduce below)
+                    loc = lambda t: t.to_local() if hasattr(t, "to_local") else t
+                    sharded = sharded or hasattr(p, "to_local")
+                    num_acc += (d / d0) * dlr * torch.dot(loc(grad).flatten(), loc(st["p0"] - p).flatten())
                     st["exp_avg"].mul_(b1).add_(grad, alpha=d * (1 - b1))
                     st["exp_avg_sq"].mul_(b2).addcmul_(grad, grad, value=d * d * (1 - b2))
                     alpha = (d / d0) * (d if g["safeguard_warmup"] else dlr)
                     st["s"].mul_(b3).add_(grad, alpha=alpha)
-                    den_acc += st["s"].abs().sum()
-        if g0["fsdp_in_use"] and torch.distributed.is_initialized():
+                    den_acc += loc(st["s"]).abs().sum()
+        if (g0["fsdp_in_use"] or sharded) and torch.distributed.is_initialized():
             both = torch.stack([num_acc, den_acc])
             torch.distributed.all_reduce(both)
             num_acc, den_acc = both[0], both[1]

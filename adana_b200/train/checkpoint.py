@@ -212,7 +212,7 @@ def save_checkpoint(model, opt, scheduler, itr, ckpt_dir: Path, distributed_back
 
         if _rank() == 0 and (local / "meta.pt").exists():
             (local / "meta.pt").unlink()
-        dcp.save({"model": get_model_state_dict(model), "optimizer": get_optimizer_state_dict(model, opt)},
+        dcp.save({"model": get_model_state_dict(model), "optimizer": _fsdp_optimizer_state(model, opt)},
                  checkpoint_id=str(local / "sharded"))
         if _rank() == 0:
             _atomic_save({"scheduler": sched_sd, "itr": itr}, local / "meta.pt")
@@ -237,6 +237,22 @@ def _is_torch_fsdp(model) -> bool:
     except ImportError:
         return False
     return any(isinstance(p, DTensor) for p in model.parameters())
+
+
+def _fsdp_optimizer_state(model, opt):
+    """`get_optimizer_state_dict`, which takes one dry step (zero gradients, zero learning rate) when the optimizer has
+    no state yet; a schedule-free optimizer that the trainer has put into evaluation mode for the checkpoint refuses
+    steps, so it is switched to training mode around the call."""
+    from torch.distributed.checkpoint.state_dict import get_optimizer_state_dict
+
+    parked = bool(opt.param_groups) and opt.param_groups[0].get("train_mode") is False and hasattr(opt, "train")
+    if parked:
+        opt.train()
+    try:
+        return get_optimizer_state_dict(model, opt)
+    finally:
+        if parked:
+            opt.eval()
 
 
 def _to_cpu(obj):
@@ -378,7 +394,7 @@ def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_
 
         if not (ckpt_dir / "meta.pt").exists():
             raise RuntimeError(f"sharded checkpoint {ckpt_dir} is incomplete: meta.pt (written last) is missing")
-        state = {"model": get_model_state_dict(model), "optimizer": get_optimizer_state_dict(model, opt)}
+        state = {"model": get_model_state_dict(model), "optimizer": _fsdp_optimizer_state(model, opt)}
         dcp.load(state, checkpoint_id=str(ckpt_dir / "sharded"))
         set_model_state_dict(model, state["model"])
         set_optimizer_state_dict(model, opt, state["optimizer"])
