@@ -395,7 +395,11 @@ def load_checkpoint(model, opt, scheduler, ckpt_path, device="cpu", distributed_
         if not (ckpt_dir / "meta.pt").exists():
             raise RuntimeError(f"sharded checkpoint {ckpt_dir} is incomplete: meta.pt (written last) is missing")
         state = {"model": get_model_state_dict(model), "optimizer": _fsdp_optimizer_state(model, opt)}
-        dcp.load(state, checkpoint_id=str(ckpt_dir / "sharded"))
+        # (the dry step that fills an empty optimizer state can create entries a trained state no longer carries,
+        # e.g. a pending copy of the last gradient: entries absent from the checkpoint keep their fresh value)
+        from torch.distributed.checkpoint.default_planner import DefaultLoadPlanner
+
+        dcp.load(state, checkpoint_id=str(ckpt_dir / "sharded"), planner=DefaultLoadPlanner(allow_partial_load=True))
         set_model_state_dict(model, state["model"])
         set_optimizer_state_dict(model, opt, state["optimizer"])
         meta = _load(ckpt_dir / "meta.pt")
