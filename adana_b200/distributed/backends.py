@@ -289,6 +289,12 @@ class FSDPBackend(_ProcessGroupBackend):
         from torch.distributed.device_mesh import init_device_mesh
         from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
+        from ..parallel.expert_parallel import rank_local_parameters
+
+        if rank_local_parameters(model):
+            # FSDP2 shards every parameter as one tensor that all ranks hold alike; each rank's own experts are not that
+            raise ValueError("expert-parallel layers cannot be sharded by torch FSDP2: pass --no_expert_parallel, or use "
+                             "--distributed_backend nccl (data parallelism with the experts split over the ranks)")
         self._torch_fsdp = True
         dev_type = "cuda" if self.pg_backend == "nccl" else "cpu"
         mp = MixedPrecisionPolicy(param_dtype=torch.float32, reduce_dtype=torch.bfloat16)
