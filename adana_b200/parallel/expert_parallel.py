@@ -149,8 +149,11 @@ class ExpertParallelMoE(nn.Module):
                 per_row = x.shape[1] * x.element_size()
                 mult = max(1, min(self.world, (2 << 30) // max(1, rows_per_call * per_row)))
                 max_rows = rows_per_call * mult
+                # (the symmetric-memory rendezvous happens once, here, outside any backward: the exchange's own group
+                # has the same ranks as the default one, which is the one this set-up has always been run with)
+                plane_group = None if self.group is _EP_GROUPS.get("world") else self.group
                 plane = P2PPlane.create(P2PAllToAll.arena_bytes(max_rows, x.shape[1], x.dtype, self.world, self.per_rank),
-                                        x.device, group=self.group)
+                                        x.device, group=plane_group)
                 a2a = P2PAllToAll(plane, max_rows, x.shape[1], x.dtype, self.per_rank)
                 ok = 1
         except Exception:      # no symmetric memory here: all ranks fall back together below
